@@ -1,0 +1,136 @@
+"""Attention ops (K2, K3): packed-varlen attention for training/prefill, paged-KV decode attention.
+
+Layouts
+-------
+``q [T, Hq, D]``, ``k/v [T, Hkv, D]`` packed over sequences delimited by ``cu_seqlens`` (no padding).
+Paged cache: ``k_cache / v_cache [num_pages, Hkv, page_size, D]`` — one (page, head) block is a
+contiguous ``page_size·D`` slab, which is what the decode kernel streams with bulk copies.
+``block_tables [B, max_pages]`` (int32) maps a sequence's logical page to a physical page;
+``slot_mapping [T]`` gives ``page · page_size + offset`` for each newly written token.
+
+CUDA tensors run on the native kernels; the PyTorch expressions below are the CPU path and oracle.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from unirl_b200.ops._ext import count_launch, require_ext, use_native
+
+
+# --------------------------------------------------------------------------------------- varlen
+def varlen_attention_reference(q, k, v, cu_seqlens, causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
+    hq, hkv = q.shape[1], k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    out = torch.empty_like(q)
+    cu = cu_seqlens.tolist()
+    for i in range(len(cu) - 1):
+        s, e = cu[i], cu[i + 1]
+        if e == s:
+            continue
+        qi = q[s:e].transpose(0, 1).unsqueeze(0)
+        ki = k[s:e].transpose(0, 1).repeat_interleave(hq // hkv, 0).unsqueeze(0)
+        vi = v[s:e].transpose(0, 1).repeat_interleave(hq // hkv, 0).unsqueeze(0)
+        o = F.scaled_dot_product_attention(qi, ki, vi, is_causal=causal, scale=scale)
+        out[s:e] = o.squeeze(0).transpose(0, 1)
+    return out
+
+
+class _VarlenAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
+        C = require_ext()
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
+        out, lse = C.attn_varlen_fwd(q, k, v, cu, int(max_seqlen), bool(causal), float(scale))
+        count_launch()
+        ctx.save_for_backward(q, k, v, out, lse, cu)
+        ctx.cfg = (int(max_seqlen), bool(causal), float(scale))
+        return out
+
+    @staticmethod
+    def backward(ctx, g_out):
+        C = require_ext()
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        max_seqlen, causal, scale = ctx.cfg
+        dq, dk, dv = C.attn_varlen_bwd(g_out.contiguous(), q, k, v, out, lse, cu, max_seqlen, causal, scale)
+        count_launch(3)
+        return dq, dk, dv, None, None, None, None
+
+
+def varlen_attention(q, k, v, cu_seqlens, max_seqlen: Optional[int] = None, causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
+    """Self attention over packed sequences (GQA when ``Hq > Hkv``)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if use_native(q):
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        return _VarlenAttention.apply(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+    return varlen_attention_reference(q, k, v, cu_seqlens, causal, scale)
+
+
+# --------------------------------------------------------------------------------------- paged KV
+def kv_cache_write(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Scatter new ``k/v [T, Hkv, D]`` rows into the paged cache."""
+    if use_native(k):
+        require_ext().kv_cache_write(k.contiguous(), v.contiguous(), k_cache, v_cache, slot_mapping.to(torch.int64))
+        count_launch()
+        return
+    page_size = k_cache.shape[2]
+    page, off = slot_mapping // page_size, slot_mapping % page_size
+    k_cache[page, :, off] = k
+    v_cache[page, :, off] = v
+
+
+def paged_decode_attention_reference(q, k_cache, v_cache, block_tables, seq_lens, scale: Optional[float] = None) -> torch.Tensor:
+    b, hq, d = q.shape
+    hkv, page_size = k_cache.shape[1], k_cache.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    out = torch.empty_like(q)
+    for i in range(b):
+        n = int(seq_lens[i])
+        pages = block_tables[i, : (n + page_size - 1) // page_size].long()
+        kk = k_cache[pages].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :n].float()
+        vv = v_cache[pages].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :n].float()
+        qi = q[i].float().view(hkv, hq // hkv, d)
+        p = torch.softmax(torch.einsum("hgd,hnd->hgn", qi, kk) * scale, -1)
+        out[i] = torch.einsum("hgn,hnd->hgd", p, vv).reshape(hq, d).to(q.dtype)
+    return out
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_tables, seq_lens, scale: Optional[float] = None,
+                           workspace: Optional[torch.Tensor] = None, max_seq_len: Optional[int] = None) -> torch.Tensor:
+    """One query token per sequence against its paged KV (split-KV + merge on CUDA).
+
+    ``workspace`` (fp32) holds the split partials so a captured CUDA graph allocates nothing.
+    """
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if use_native(q):
+        out = require_ext().paged_decode_attention(q.contiguous(), k_cache, v_cache, block_tables, seq_lens, float(scale), workspace,
+                                                   int(max_seq_len or 0))
+        count_launch(2)
+        return out
+    return paged_decode_attention_reference(q, k_cache, v_cache, block_tables, seq_lens, scale)
+
+
+# --------------------------------------------------------------------------------------- dense (DiT)
+def dense_attention(q, k, v, scale: Optional[float] = None) -> torch.Tensor:
+    """Bidirectional attention over ``[B, L, H, D]`` (joint text+image streams of MMDiT / video DiT).
+
+    Routed through the packed kernel with uniform ``cu_seqlens`` on CUDA.
+    """
+    b, l, h, d = q.shape
+    if use_native(q):
+        cu = torch.arange(0, (b + 1) * l, l, device=q.device, dtype=torch.int32)
+        o = varlen_attention(q.reshape(b * l, h, d), k.reshape(b * l, k.shape[2], d), v.reshape(b * l, v.shape[2], d), cu, l, False, scale)
+        return o.view(b, l, h, d)
+    o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=scale, enable_gqa=k.shape[2] != h)
+    return o.transpose(1, 2)
+
+
+__all__ = ["varlen_attention", "varlen_attention_reference", "kv_cache_write", "paged_decode_attention",
+           "paged_decode_attention_reference", "dense_attention"]

@@ -1,0 +1,85 @@
+"""Linear layers (K1): ``y = x · Wᵀ`` with optional fused epilogues.
+
+Forward on CUDA goes to the hand-written tcgen05/TMEM GEMM (TMA-fed, persistent, 128×256 tiles)
+for the fused variants (SwiGLU epilogue, residual add, LoRA add); the plain variant may use the
+library GEMM.  Backward uses plain library GEMMs (``dX = dY·W``, ``dW = dYᵀ·X``): those are
+unfused contractions where cuBLAS is the stated baseline.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from unirl_b200.ops._ext import count_launch, ext, require_ext, use_native
+
+_MIN_NATIVE_M = int(os.environ.get("UNIRL_B200_GEMM_MIN_M", "1"))
+
+
+def _native_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    m, k = x2.shape
+    n = w.shape[0]
+    return (x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 64 == 0 and n % 16 == 0 and m >= _MIN_NATIVE_M
+            and x2.is_contiguous() and w.is_contiguous() and os.environ.get("UNIRL_B200_GEMM", "native") == "native")
+
+
+class _NativeLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, residual, epilogue: int):
+        C = require_ext()
+        x2 = x.reshape(-1, x.shape[-1])
+        res2 = residual.reshape(-1, residual.shape[-1]).contiguous() if residual is not None else None
+        y = C.gemm_bf16_tn(x2, w, res2, int(epilogue))
+        count_launch()
+        ctx.save_for_backward(x2, w)
+        ctx.has_res = residual is not None
+        ctx.in_shape = x.shape
+        return y.view(*x.shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        g2 = gy.reshape(-1, gy.shape[-1])
+        gx = (g2 @ w).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        gw = (g2.t() @ x2) if ctx.needs_input_grad[1] else None
+        return gx, gw, (gy if ctx.has_res else None), None
+
+
+EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weightᵀ (+ residual)``; ``weight`` is ``[out, in]``."""
+    if use_native(x):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if ext() is not None and hasattr(ext(), "gemm_bf16_tn") and _native_ok(x2, weight):
+            return _NativeLinear.apply(x, weight, residual, EPI_RESIDUAL if residual is not None else EPI_NONE)
+    y = F.linear(x, weight)
+    return y + residual if residual is not None else y
+
+
+def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(x·Wgᵀ) · (x·Wuᵀ)`` with ``weight_gate_up = [Wg; Wu]`` (``[2I, in]``).
+
+    Inference path fuses the activation into the GEMM epilogue (gate/up rows interleaved per tile by
+    the weight packer); training keeps GEMM and activation as two autograd nodes.
+    """
+    from unirl_b200.ops.activation import swiglu
+
+    return swiglu(linear(x, weight_gate_up))
+
+
+def lora_linear(x: torch.Tensor, weight: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor, scaling: float,
+                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x·Wᵀ + scaling · (x·Aᵀ)·Bᵀ`` — the rank-r path is two skinny GEMMs accumulated onto the base output."""
+    y = linear(x, weight)
+    y = y + (F.linear(F.linear(x, lora_a), lora_b) * scaling).to(y.dtype)
+    return y + bias if bias is not None else y
+
+
+__all__ = ["linear", "linear_swiglu", "lora_linear", "EPI_NONE", "EPI_RESIDUAL", "EPI_SWIGLU"]

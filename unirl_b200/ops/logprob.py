@@ -1,0 +1,100 @@
+"""Token log-prob (K6): ``log softmax(h·Wᵀ / T)[target]`` without ever materialising ``[tokens, vocab]`` in fp32.
+
+CUDA forward: the tcgen05 GEMM runs over vocab tiles with an epilogue that reduces each 128×N
+accumulator tile (still in TMEM) to per-row ``(max, Σexp, target logit)`` partials; a merge kernel
+folds the partials into ``lse`` and ``logp``.  Logits never reach HBM.
+CUDA backward: per token chunk, logits are recomputed by the same GEMM into a bf16 scratch,
+turned in place into ``dZ = g/T · (onehot − softmax)`` by one kernel, then ``dH = dZ·W`` and
+``dW += dZᵀ·H`` are plain GEMMs.
+Reference (CPU + oracle): chunked fp32 ``x[target]/T − logsumexp(x/T)``, as the reference framework does in
+``unirl/models/qwen3/ar.py:74-99`` with ``torch.utils.checkpoint``.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from unirl_b200.ops._ext import count_launch, ext, require_ext, use_native
+
+_BWD_CHUNK = int(os.environ.get("UNIRL_B200_LOGPROB_BWD_CHUNK", "8192"))
+
+
+def linear_logprob_reference(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, temperature: float = 1.0,
+                             chunk: int = 2048) -> torch.Tensor:
+    outs = []
+    for s in range(0, hidden.shape[0], chunk):
+        z = (hidden[s : s + chunk].float() @ weight.float().t()) / temperature
+        outs.append(z.gather(-1, targets[s : s + chunk].long().unsqueeze(-1)).squeeze(-1) - torch.logsumexp(z, -1))
+    return torch.cat(outs) if outs else hidden.new_zeros(0, dtype=torch.float32)
+
+
+class _LinearLogprob(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, temperature):
+        C = require_ext()
+        hidden = hidden.contiguous()
+        tgt = targets.to(torch.int32).contiguous()
+        logp, lse = C.linear_logprob_fwd(hidden, weight, tgt, float(temperature))
+        count_launch(2)
+        ctx.save_for_backward(hidden, weight, tgt, lse)
+        ctx.temperature = float(temperature)
+        return logp
+
+    @staticmethod
+    def backward(ctx, g):
+        C = require_ext()
+        hidden, weight, tgt, lse = ctx.saved_tensors
+        g = g.float().contiguous()
+        d_hidden = torch.empty_like(hidden)
+        d_weight = torch.zeros_like(weight, dtype=torch.float32) if ctx.needs_input_grad[1] else None
+        for s in range(0, hidden.shape[0], _BWD_CHUNK):
+            e = min(s + _BWD_CHUNK, hidden.shape[0])
+            h = hidden[s:e]
+            z = h @ weight.t()  # bf16 scratch [chunk, V]
+            C.logprob_dlogits_inplace(z, tgt[s:e], lse[s:e], g[s:e], ctx.temperature)
+            count_launch()
+            torch.matmul(z, weight, out=d_hidden[s:e])
+            if d_weight is not None:
+                d_weight.add_((z.t() @ h).float())
+        return d_hidden, (d_weight.to(weight.dtype) if d_weight is not None else None), None, None
+
+
+def linear_logprob(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
+    """fp32 ``[T]`` log-probs of ``targets`` under ``softmax(hidden·weightᵀ / temperature)``."""
+    if use_native(hidden):
+        return _LinearLogprob.apply(hidden, weight, targets, temperature)
+    return _CheckpointedReference.apply(hidden, weight, targets, float(temperature))
+
+
+class _CheckpointedReference(torch.autograd.Function):
+    """CPU path: recompute each vocab projection chunk in backward instead of storing ``[T, V]``."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, temperature):
+        ctx.save_for_backward(hidden, weight, targets)
+        ctx.temperature = temperature
+        with torch.no_grad():
+            return linear_logprob_reference(hidden, weight, targets, temperature)
+
+    @staticmethod
+    def backward(ctx, g):
+        hidden, weight, targets = ctx.saved_tensors
+        t = ctx.temperature
+        dh = torch.zeros_like(hidden, dtype=torch.float32)
+        dw = torch.zeros_like(weight, dtype=torch.float32)
+        wf = weight.float()
+        for s in range(0, hidden.shape[0], 2048):
+            h = hidden[s : s + 2048].float()
+            p = torch.softmax((h @ wf.t()) / t, -1)
+            dz = -p
+            dz.scatter_add_(-1, targets[s : s + 2048].long().unsqueeze(-1), torch.ones_like(dz[:, :1]))
+            dz *= (g[s : s + 2048].float() / t).unsqueeze(-1)
+            dh[s : s + 2048] = dz @ wf
+            dw += dz.t() @ h
+        return dh.to(hidden.dtype), dw.to(weight.dtype), None, None
+
+
+__all__ = ["linear_logprob", "linear_logprob_reference"]

@@ -1,0 +1,73 @@
+"""Rotary position embedding fused with per-head q/k RMSNorm (K4+K5), applied to packed QKV.
+
+``qkv`` is ``[T, (Hq + 2·Hkv)·D]`` straight out of the fused QKV GEMM.  The op normalises every q
+and k head (Qwen3 QK-norm; pass ``None`` weights to skip), rotates them by ``positions`` with the
+half-split ("NeoX") convention and leaves v untouched.  The backward kernel undoes the rotation and
+the norm in one pass.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from unirl_b200.ops._ext import count_launch, require_ext, use_native
+
+
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions.device, dtype=torch.float32) / head_dim))
+    ang = positions.float().unsqueeze(-1) * inv
+    return ang.cos(), ang.sin()
+
+
+def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    h = x.shape[-1] // 2
+    x1, x2 = x[..., :h], x[..., h:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+
+def qk_norm_rope_reference(qkv, q_weight, k_weight, positions, n_q, n_kv, head_dim, theta, eps):
+    t = qkv.shape[0]
+    q, k, v = qkv.float().split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], -1)
+    q, k = q.view(t, n_q, head_dim), k.view(t, n_kv, head_dim)
+    if q_weight is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight.float()
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight.float()
+    cos, sin = rope_cos_sin(positions, head_dim, theta)
+    cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+    q, k = _rotate(q, cos, sin), _rotate(k, cos, sin)
+    return q.to(qkv.dtype), k.to(qkv.dtype), v.reshape(t, n_kv, head_dim).to(qkv.dtype)
+
+
+class _QKNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, q_weight, k_weight, positions, n_q, n_kv, head_dim, theta, eps):
+        C = require_ext()
+        qkv = qkv.contiguous()
+        q, k, v, rstd = C.qk_norm_rope_fwd(qkv, q_weight, k_weight, positions.to(torch.int32), n_q, n_kv, head_dim, float(theta), float(eps))
+        count_launch()
+        ctx.save_for_backward(qkv, q_weight, k_weight, positions, rstd)
+        ctx.cfg = (n_q, n_kv, head_dim, float(theta), float(eps))
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        C = require_ext()
+        qkv, qw, kw, positions, rstd = ctx.saved_tensors
+        n_q, n_kv, head_dim, theta, eps = ctx.cfg
+        g_qkv, g_qw, g_kw = C.qk_norm_rope_bwd(gq.contiguous(), gk.contiguous(), gv.contiguous(), qkv, qw, kw,
+                                               positions.to(torch.int32), rstd, n_q, n_kv, head_dim, theta)
+        count_launch()
+        return g_qkv, (g_qw.to(qw.dtype) if qw is not None else None), (g_kw.to(kw.dtype) if kw is not None else None), None, None, None, None, None, None
+
+
+def qk_norm_rope(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], positions: torch.Tensor,
+                 n_q: int, n_kv: int, head_dim: int, theta: float = 1e6, eps: float = 1e-6):
+    """Returns ``q [T,Hq,D]``, ``k [T,Hkv,D]``, ``v [T,Hkv,D]``."""
+    if use_native(qkv) and q_weight is not None:
+        return _QKNormRope.apply(qkv, q_weight, k_weight, positions, n_q, n_kv, head_dim, theta, eps)
+    return qk_norm_rope_reference(qkv, q_weight, k_weight, positions, n_q, n_kv, head_dim, theta, eps)
+
+
+__all__ = ["qk_norm_rope", "qk_norm_rope_reference", "rope_cos_sin"]

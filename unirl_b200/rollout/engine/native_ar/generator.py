@@ -1,0 +1,227 @@
+"""Batched autoregressive generation over a paged KV cache with a host-free decode step.
+
+Per wave of sequences:
+
+1. pages for ``prompt + max_new_tokens`` are reserved up front, so block tables are static;
+2. prompts are prefilled *packed* (no padding) in token-budgeted chunks;
+3. the decode step — embed, N layers with paged attention, final norm, lm_head, sampler, and the
+   bookkeeping (append token/log-prob at column ``t``, advance positions / lengths / slots, latch
+   the finished flag on EOS) — touches only device tensors.  On CUDA it is captured once per
+   batch size into a CUDA graph and replayed; the host merely polls an "all finished" flag every
+   ``poll_interval`` steps, replacing the reference's per-token ``all_reduce(MIN)`` barrier
+   (``unirl/models/qwen3/ar.py:318-321``).
+
+The sampler records the temperature-scaled *full-softmax* log-prob (before top-k/top-p
+truncation), which is exactly what the trainer's replay recomputes.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from unirl_b200.models.qwen3.modeling import AttnMeta
+from unirl_b200.ops import sampling as S
+from unirl_b200.rollout.engine.native_ar.kv_cache import PagedKVCache
+
+
+@dataclass
+class GenerationOutput:
+    tokens: List[torch.Tensor]  # per sequence [n_i] int64
+    log_probs: List[torch.Tensor]  # per sequence [n_i] fp32
+    finished: torch.Tensor  # [B] bool: stopped on EOS (False ⇒ truncated at max_new_tokens)
+    num_steps: int = 0
+
+
+class ARGenerator:
+    def __init__(self, model: Any, *, page_size: int = 64, max_running: int = 256, prefill_token_budget: int = 16384,
+                 kv_cache_tokens: Optional[int] = None, use_cuda_graph: bool = True, poll_interval: int = 64, seed: int = 0,
+                 cache_dtype: Optional[torch.dtype] = None):
+        self.model = model
+        self.cfg = model.cfg
+        self.page_size, self.max_running = int(page_size), int(max_running)
+        self.prefill_token_budget = int(prefill_token_budget)
+        self.kv_cache_tokens = kv_cache_tokens
+        self.poll_interval = int(poll_interval)
+        self.seed = int(seed)
+        self.device = model.embed_tokens.device
+        self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
+        self.cache_dtype = cache_dtype or model.embed_tokens.dtype
+        self.cache: Optional[PagedKVCache] = None
+        self._graphs: Dict[Tuple[int, int, float, int, float], Any] = {}
+        self._calls = 0
+
+    # ---- memory -----------------------------------------------------------------------------------
+    def ensure_cache(self, tokens_needed: int) -> PagedKVCache:
+        pages = math.ceil(tokens_needed / self.page_size) + 1
+        if self.kv_cache_tokens is not None:
+            pages = max(pages, math.ceil(self.kv_cache_tokens / self.page_size))
+        if self.cache is None or self.cache.num_pages < pages:
+            self.release_cache()
+            layer0 = self.model.layers[0]
+            self.cache = PagedKVCache(self.cfg.num_hidden_layers, layer0.n_kv, self.cfg.head_dim, self.page_size, pages, self.cache_dtype, self.device)
+        elif not self.cache.is_allocated:
+            self.cache.allocate()
+        return self.cache
+
+    def release_cache(self) -> None:
+        self._graphs.clear()
+        if self.cache is not None:
+            self.cache.release()
+        self.cache = None
+
+    # ---- public -------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[torch.Tensor], *, max_new_tokens: int, temperature: float = 1.0, top_k: int = 0,
+                 top_p: float = 1.0, stop_token_ids: Optional[Sequence[int]] = None, seed: Optional[int] = None) -> GenerationOutput:
+        """``prompts``: per-sequence 1-D token tensors.  Sequences beyond ``max_running`` run in successive waves."""
+        n = len(prompts)
+        toks: List[Optional[torch.Tensor]] = [None] * n
+        lps: List[Optional[torch.Tensor]] = [None] * n
+        fin = torch.zeros(n, dtype=torch.bool)
+        steps = 0
+        seed = self.seed + self._calls if seed is None else int(seed)
+        self._calls += 1
+        for lo in range(0, n, self.max_running):
+            idx = list(range(lo, min(n, lo + self.max_running)))
+            t, l, f, s = self._run_wave([prompts[i] for i in idx], max_new_tokens, temperature, top_k, top_p, stop_token_ids, seed + lo)
+            for j, i in enumerate(idx):
+                toks[i], lps[i] = t[j], l[j]
+            fin[lo : lo + len(idx)] = f
+            steps += s
+        return GenerationOutput(toks, lps, fin, steps)  # type: ignore[arg-type]
+
+    # ---- one wave -------------------------------------------------------------------------------------
+    def _run_wave(self, prompts: List[torch.Tensor], max_new: int, temperature: float, top_k: int, top_p: float,
+                  stop_ids: Optional[Sequence[int]], seed: int):
+        dev, ps, b = self.device, self.page_size, len(prompts)
+        plens = [int(p.numel()) for p in prompts]
+        pages_per = [math.ceil((pl + max_new) / ps) for pl in plens]
+        cache = self.ensure_cache(sum(pp * ps for pp in pages_per))
+        cache.allocator.reset()
+        max_pages = max(pages_per)
+        bt = torch.zeros(b, max_pages, dtype=torch.int32)
+        for i, pp in enumerate(pages_per):
+            bt[i, :pp] = torch.tensor(cache.allocator.allocate(pp), dtype=torch.int32)
+        block_tables = bt.to(dev)
+        stop = torch.tensor(list(stop_ids) if stop_ids else [self.cfg.eos_token_id], dtype=torch.long, device=dev)
+
+        # -- prefill (packed, chunked by token budget) --------------------------------------------------
+        last_hidden = torch.empty(b, self.cfg.hidden_size, dtype=self.model.embed_tokens.dtype, device=dev)
+        i = 0
+        while i < b:
+            j, tot = i, 0
+            while j < b and (j == i or tot + plens[j] <= self.prefill_token_budget):
+                tot += plens[j]
+                j += 1
+            self._prefill([prompts[k] for k in range(i, j)], plens[i:j], block_tables[i:j], cache, last_hidden[i:j])
+            i = j
+
+        # -- decode state (all device resident) ---------------------------------------------------------
+        st = _DecodeState(b, max_new, dev)
+        st.positions.copy_(torch.tensor(plens, dtype=torch.long))  # index at which the next fed token is written
+        first_tok, first_lp = self._sample(self.model.logits(last_hidden), temperature, top_k, top_p, seed, 0, st)
+        st.record(first_tok, first_lp, stop)
+        meta = AttnMeta(mode="decode", positions=st.positions, k_cache=cache.k, v_cache=cache.v, block_tables=block_tables,
+                        seq_lens=st.seq_lens, slot_mapping=st.slots, max_kv_len=max(plens) + max_new)
+        if self.device.type == "cuda":
+            from unirl_b200.ops._ext import ext
+
+            C = ext()
+            if C is not None and hasattr(C, "decode_workspace_size"):
+                meta.workspace = torch.empty(C.decode_workspace_size(b, self.model.layers[0].n_q, self.cfg.head_dim, meta.max_kv_len),
+                                             dtype=torch.float32, device=dev)
+
+        def step() -> None:
+            st.prepare(block_tables, ps)
+            hidden = self.model(st.cur_tokens, meta)
+            tok, lp = self._sample(self.model.logits(hidden), temperature, top_k, top_p, seed, None, st)
+            st.record(tok, lp, stop)
+            st.positions.add_(1)
+
+        n_steps = 1
+        runner = self._graphed(step, b, max_new, temperature, top_k, top_p) if self.use_cuda_graph and max_new > 1 else step
+        while n_steps < max_new:
+            burst = min(self.poll_interval, max_new - n_steps)
+            for _ in range(burst):
+                runner()
+            n_steps += burst
+            if bool(st.finished.all()):  # one small D2H read per `poll_interval` steps
+                break
+        lens = st.lengths.cpu()
+        out_t, out_l = st.out_tokens.cpu(), st.out_logp.cpu()
+        toks = [out_t[k, : int(lens[k])].clone() for k in range(b)]
+        lps = [out_l[k, : int(lens[k])].clone() for k in range(b)]
+        return toks, lps, st.finished.cpu(), n_steps
+
+    def _prefill(self, prompts: List[torch.Tensor], plens: List[int], block_tables: torch.Tensor, cache: PagedKVCache, out_last: torch.Tensor) -> None:
+        dev, ps = self.device, self.page_size
+        tokens = torch.cat([p.to(torch.long) for p in prompts]).to(dev)
+        cu = torch.zeros(len(plens) + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(plens, dtype=torch.int32).cumsum(0)
+        positions = torch.cat([torch.arange(n) for n in plens]).to(dev)
+        seq_id = torch.repeat_interleave(torch.arange(len(plens)), torch.tensor(plens)).to(dev)
+        page = block_tables[seq_id, (positions // ps)].long()
+        meta = AttnMeta(mode="prefill", positions=positions, cu_seqlens=cu.to(dev), max_seqlen=max(plens), k_cache=cache.k, v_cache=cache.v,
+                        slot_mapping=page * ps + positions % ps)
+        hidden = self.model(tokens, meta)
+        out_last.copy_(hidden[(cu[1:].long() - 1).to(dev)])
+
+    def _sample(self, logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, step: Optional[int], st: "_DecodeState"):
+        if logits.is_cuda:
+            return S.sample(logits, temperature, top_k, top_p, seed=seed, step=0 if step is None else step, step_tensor=st.step_counter)
+        if st.cpu_gen is None:
+            st.cpu_gen = torch.Generator().manual_seed(seed)
+        return S.sample_reference(logits, temperature, top_k, top_p, st.cpu_gen)
+
+    def _graphed(self, step_fn, b: int, max_new: int, temperature: float, top_k: int, top_p: float):
+        """Capture ``step_fn`` (which closes over this wave's state tensors) into a CUDA graph."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        # no warm-up run: the step has side effects on the decode state; kernels were already
+        # exercised by prefill / first-token sampling, and capture itself does not execute.
+        with torch.cuda.graph(g, stream=s):
+            step_fn()
+        self._graphs[(b, max_new, temperature, top_k, top_p)] = g  # keep alive for the wave
+        return g.replay
+
+
+class _DecodeState:
+    """Device-resident per-wave decode bookkeeping (mutated in place so a CUDA graph can own it)."""
+
+    def __init__(self, b: int, max_new: int, dev: torch.device):
+        z = lambda dt, *shape: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
+        self.out_tokens, self.out_logp = z(torch.long, b, max_new), z(torch.float32, b, max_new)
+        self.cur_tokens, self.positions, self.slots = z(torch.long, b), z(torch.long, b), z(torch.long, b)
+        self.seq_lens = z(torch.int32, b)
+        self.lengths = z(torch.long, b)
+        self.finished = z(torch.bool, b)
+        self.step_counter = z(torch.long, 1)
+        self.rows = torch.arange(b, device=dev)
+        self.max_new = max_new
+        self.cpu_gen: Optional[torch.Generator] = None
+
+    def record(self, tok: torch.Tensor, lp: torch.Tensor, stop: torch.Tensor) -> None:
+        """Append the sampled token for every unfinished row, then latch EOS."""
+        live = ~self.finished
+        col = self.lengths.clamp(max=self.max_new - 1)
+        self.out_tokens[self.rows, col] = torch.where(live, tok, self.out_tokens[self.rows, col])
+        self.out_logp[self.rows, col] = torch.where(live, lp.float(), self.out_logp[self.rows, col])
+        self.lengths.add_(live.long())
+        self.cur_tokens.copy_(tok)
+        self.finished.logical_or_((tok.unsqueeze(1) == stop.unsqueeze(0)).any(1))
+        self.finished.logical_or_(self.lengths >= self.max_new)
+        self.step_counter.add_(1)
+
+    def prepare(self, block_tables: torch.Tensor, page_size: int) -> None:
+        """``positions[b]`` is the index of the token fed this step: derive its cache slot and the KV length."""
+        page = block_tables.gather(1, (self.positions // page_size).unsqueeze(1)).squeeze(1).long()
+        self.slots.copy_(page * page_size + self.positions % page_size)
+        self.seq_lens.copy_((self.positions + 1).to(torch.int32))
+
+
+__all__ = ["ARGenerator", "GenerationOutput"]
