@@ -130,6 +130,21 @@ class Comm:
         dist.broadcast_object_list(box, src=self._g(src), group=self.group)
         return box[0]
 
+    def split(self, groups: Sequence[Sequence[int]]) -> "Comm":
+        """Sub-communicator containing this rank; ``groups`` partition the members by GROUP-LOCAL rank.
+
+        Only the members of a sub-group take part in creating it (local synchronisation), so
+        different sub-groups can be built concurrently.
+        """
+        mine = next((list(g) for g in groups if self.rank in g), None)
+        if mine is None:
+            raise ValueError(f"rank {self.rank} is in none of the sub-groups {groups}")
+        globals_ = [self.global_ranks[r] for r in mine]
+        if len(mine) == 1 or not self.active:
+            return Comm(None, globals_, self.global_ranks[self.rank])
+        g = dist.new_group(ranks=globals_, use_local_synchronization=True)
+        return Comm(g, globals_, self.global_ranks[self.rank])
+
     # p2p takes GLOBAL worker ids (the transport plans hops between arbitrary pool workers)
     def send(self, t: torch.Tensor, dst_global: int) -> None:
         dist.send(t.contiguous(), dst=dst_global, group=self.group)

@@ -261,6 +261,36 @@ class DevicePool:
             raise errors[0]
         return out
 
+    def run_many(self, calls: Sequence[tuple], timeout: Optional[float] = None) -> List[List[Any]]:
+        """Several fan-outs in flight at once: ``calls = [(devices, op, per_worker_args), …]``.
+
+        Needed when roles on *different* workers must enter one collective together (trainer rank 0
+        broadcasting weights while the engine ranks receive).  In spmd mode every rank runs the calls
+        that target it, in order, and results are exchanged once at the end.
+        """
+        if self.backend == "spmd":
+            import traceback
+
+            mine: List[Any] = []
+            err = None
+            for devices, op, args in calls:
+                res = None
+                if self.my_rank in devices and err is None:
+                    try:
+                        res = getattr(self.local_worker, op)(*args[list(devices).index(self.my_rank)])
+                    except Exception:  # noqa: BLE001
+                        err = traceback.format_exc()
+                mine.append(res)
+            gathered = self.world_comm.all_gather_object((mine, err))
+            for r, (_m, e) in enumerate(gathered):
+                if e is not None:
+                    raise WorkerError(f"worker {r} failed in a concurrent call:\n{e}")
+            return [[gathered[d][0][i] for d in devices] for i, (devices, _op, _a) in enumerate(calls)]
+        if self.backend == "inline":
+            return [self.run_on(devices, op, args, timeout) for devices, op, args in calls]
+        futs = [[self.workers[d].submit(op, *a) for d, a in zip(devices, args)] for devices, op, args in calls]
+        return [[f.result(timeout) for f in fl] for fl in futs]
+
     def run_everywhere(self, op: str, *args: Any) -> List[Any]:
         return self.run_on(list(range(self.num_devices)), op, [args] * self.num_devices)
 

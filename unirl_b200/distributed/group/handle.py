@@ -111,6 +111,28 @@ class Handle:
             ctx.record(self, call_id, args, kwargs, out)
         return out
 
+    def prepare(self, method: str, *args: Any, **kwargs: Any) -> tuple:
+        """Plan a call without running it: returns ``(devices, "call", payloads)`` for ``pool.run_many``
+        plus what :meth:`finish` needs.  No RPC autograd on this path."""
+        cfg = getattr(getattr(self.cls, method), "_distributed_config", {"dispatch_mode": Dispatch.BROADCAST, "execute_mode": Execute.ALL})
+        mode, execute = cfg["dispatch_mode"], cfg["execute_mode"]
+        bs = infer_batch_size(args, kwargs)
+        shards = plan_dispatch(mode, self.rank_infos, self.dp_size, args, kwargs, bs)
+        devices, infos = self.devices, self.rank_infos
+        if execute is Execute.RANK_ZERO:
+            shards, devices, infos = shards[:1], devices[:1], infos[:1]
+        hops = plan_localize(shards, devices)
+        if hops:
+            mapping = self.pool.move(hops)
+            shards = [rewrite_refs(s, mapping, d) for s, d in zip(shards, devices)]
+        payloads = [(self.role_name, method, a, k, False, None) for a, k in shards]
+        return (devices, "call", payloads), (mode, infos)
+
+    def finish(self, results: List[Any], ctx: tuple) -> Any:
+        mode, infos = ctx
+        self.pool.adopt_tree(results)
+        return collect(mode, infos, results)
+
     def call(self, method: str, *args: Any, **kwargs: Any) -> Any:
         """Invoke a method that was not decorated (broadcast to all ranks, list of results)."""
         return self._invoke(method, Dispatch.BROADCAST, Execute.ALL, args, kwargs)

@@ -33,6 +33,7 @@ from unirl_b200.ops.activation import swiglu
 from unirl_b200.ops.linear import linear
 from unirl_b200.ops.norm import rmsnorm
 from unirl_b200.ops.rope import qk_norm_rope
+from unirl_b200.train.inject import lora_apply
 
 
 @dataclass
@@ -128,6 +129,21 @@ class Qwen3DecoderLayer(nn.Module):
         self.down_proj = mk(h, self.inter)
         self.scale = 1.0 / math.sqrt(d)
 
+    def lora_targets(self) -> Dict[str, Tuple[str, int, int]]:
+        d, nq, nkv, i = self.cfg.head_dim, self.n_q, self.n_kv, self.inter
+        return {"q_proj": ("qkv_proj", 0, nq * d), "k_proj": ("qkv_proj", nq * d, nkv * d), "v_proj": ("qkv_proj", (nq + nkv) * d, nkv * d),
+                "o_proj": ("o_proj", 0, self.cfg.hidden_size), "gate_proj": ("gate_up_proj", 0, i), "up_proj": ("gate_up_proj", i, i),
+                "down_proj": ("down_proj", 0, self.cfg.hidden_size)}
+
+    def hf_module_path(self, target: str) -> str:
+        return f"model.layers.{self.layer_idx}.{'self_attn' if target in ('q_proj', 'k_proj', 'v_proj', 'o_proj') else 'mlp'}.{target}"
+
+    def _proj(self, x: torch.Tensor, name: str, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if getattr(self, "_lora_index", None):
+            y = lora_apply(self, name, x, linear(x, getattr(self, name)))
+            return y if residual is None else y + residual
+        return linear(x, getattr(self, name), residual=residual)
+
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         if meta.mode == "decode":
             A.kv_cache_write(k, v, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.slot_mapping)
@@ -140,18 +156,18 @@ class Qwen3DecoderLayer(nn.Module):
     def forward(self, x: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         c = self.cfg
         h = rmsnorm(x, self.input_layernorm, c.rms_norm_eps)
-        qkv = linear(h, self.qkv_proj)
+        qkv = self._proj(h, "qkv_proj")
         q, k, v = qk_norm_rope(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps)
         attn = self.attention(q, k, v, meta).reshape(x.shape[0], self.n_q * c.head_dim)
         if self.tp.size == 1:
-            x = linear(attn, self.o_proj, residual=x)
+            x = self._proj(attn, "o_proj", residual=x)
         else:
-            x = x + self.tp.reduce(linear(attn, self.o_proj))
+            x = x + self.tp.reduce(self._proj(attn, "o_proj"))
         h = rmsnorm(x, self.post_attention_layernorm, c.rms_norm_eps)
-        act = swiglu(linear(h, self.gate_up_proj))
+        act = swiglu(self._proj(h, "gate_up_proj"))
         if self.tp.size == 1:
-            return linear(act, self.down_proj, residual=x)
-        return x + self.tp.reduce(linear(act, self.down_proj))
+            return self._proj(act, "down_proj", residual=x)
+        return x + self.tp.reduce(self._proj(act, "down_proj"))
 
 
 class Qwen3Transformer(nn.Module):

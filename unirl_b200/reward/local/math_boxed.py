@@ -1,0 +1,2 @@
+"""Reference-compatible import path (``unirl.reward.local.math_boxed``); the scorer lives in ``rules.py``."""
+from unirl_b200.reward.local.rules import *  # noqa: F401,F403

@@ -1,0 +1,256 @@
+"""``NativeARRolloutEngine`` — tensor-parallel paged-KV decoder replacing the external LLM servers.
+
+The reference drives an SGLang server subprocess over HTTP (``unirl/rollout/engine/sglang_llm/engine.py:373-581``)
+and pushes weights through CUDA-IPC / NCCL endpoints (``:1146-1302``).  Here the engine is a role in
+the same process as the trainer shard:
+
+* weights live in this engine's own (TP-sharded) parameter buffers, or — colocated with ``tp_size == 1``
+  — alias the trainer's bf16 replica, making weight sync the identity;
+* ``generate`` (``DP_SCATTER``: TP peers receive the same shard and run in lock-step; the counter-based
+  sampler makes them draw identical tokens) → :class:`ARGenerator`;
+* ``sleep`` / ``wake_up`` release / re-create KV cache and CUDA graphs (tags ``kv_cache`` / ``cuda_graph`` /
+  ``weights`` as in the reference's memory-occupation endpoints ``:1308-1411``);
+* the weight-receive surface writes full tensors through the TP slicer, or receives NCCL broadcasts.
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+
+from unirl_b200.distributed.group.dispatch import Dispatch, distributed
+from unirl_b200.models.qwen3.bundle import resolve_model_config
+from unirl_b200.models.qwen3.chat_template import Qwen3ChatTemplateStage, pad_right
+from unirl_b200.models.qwen3.modeling import Qwen3Transformer, TPContext, shard_param
+from unirl_b200.models.tokenizer import load_tokenizer
+from unirl_b200.models.types.contracts import unpad_prompts
+from unirl_b200.models.qwen3.ar import pack_text_segment
+from unirl_b200.rollout.engine.base import BaseRolloutEngine
+from unirl_b200.rollout.engine.native_ar.config import NativeAREngineConfig
+from unirl_b200.rollout.engine.native_ar.generator import ARGenerator
+from unirl_b200.types.conditions import TextTokenCondition
+from unirl_b200.types.primitives import Texts
+from unirl_b200.types.rollout_req import RolloutReq
+from unirl_b200.types.rollout_resp import RolloutResp, RolloutTrack
+from unirl_b200.types.sampling import get_ar_params
+from unirl_b200.utils.dtypes import parse_torch_dtype
+
+logger = logging.getLogger(__name__)
+
+
+class NativeARRolloutEngine(BaseRolloutEngine):
+    _component_name = "native_ar"
+
+    def __init__(self, *, config: Any = None, bundle: Any = None, **overrides: Any) -> None:
+        super().__init__()
+        if config is None:
+            config = NativeAREngineConfig(**overrides)
+        elif isinstance(config, dict):
+            config = NativeAREngineConfig(**{**config, **overrides})
+        self.config: NativeAREngineConfig = config
+        self._trainer_bundle = bundle
+        self.model: Optional[Qwen3Transformer] = None
+        self.generator: Optional[ARGenerator] = None
+        self.tokenizer: Any = None
+        self.tp_comm = None
+        self.weight_version = 0
+        self._shares_trainer = False
+        self._sync_groups: Dict[str, Any] = {}
+        self._asleep = False
+
+    # ---- construction ----------------------------------------------------------------------------------
+    def setup(self, *a: Any, **k: Any) -> None:
+        super().setup(*a, **k)
+        cfg, ri = self.config, self.rank_info
+        tp = max(int(cfg.tp_size), int(ri.tp_size))
+        if ri.tp_size != tp and ri.world_size > 1:
+            raise ValueError(f"engine config tp_size={cfg.tp_size} but the handle was created with tp={ri.tp_size}; "
+                             f"pass parallel={{'tp': {cfg.tp_size}}} to remote()")
+        dev = torch.device(self.device or "cpu")
+        if tp > 1:
+            groups = [list(range(g * tp, (g + 1) * tp)) for g in range(ri.world_size // tp)]
+            self.tp_comm = self.comm.split(groups)
+            tpc = TPContext(ri.tp_rank, tp, self._make_all_reduce())
+        else:
+            tpc = TPContext()
+        b = self._trainer_bundle
+        if b is not None and tp == 1 and cfg.share_trainer_weights and getattr(b, "transformer", None) is not None:
+            self.model, self._shares_trainer = b.transformer, True
+            self.tokenizer = b.tokenizer
+        else:
+            mcfg = resolve_model_config(cfg.pretrained_model_ckpt_path, cfg.model_overrides) if b is None else b.transformer.cfg
+            self.model = Qwen3Transformer(mcfg, dtype=parse_torch_dtype(cfg.model_precision), device=dev, tp=tpc)
+            self._init_weights(b)
+            self.model.eval().requires_grad_(False)
+            self.tokenizer = b.tokenizer if b is not None else load_tokenizer(cfg.tokenizer_ckpt_path, mcfg.vocab_size)
+        self.generator = ARGenerator(self.model, page_size=cfg.page_size, max_running=cfg.max_running_requests,
+                                     prefill_token_budget=cfg.prefill_token_budget, kv_cache_tokens=cfg.kv_cache_tokens,
+                                     use_cuda_graph=cfg.use_cuda_graph, poll_interval=cfg.poll_interval, seed=cfg.seed)
+
+    def _make_all_reduce(self):
+        comm = self.tp_comm
+        if self.config.tp_collectives == "fused" and torch.cuda.is_available():
+            try:
+                from unirl_b200.parallel.fused_collectives import make_fused_all_reduce
+
+                fused = make_fused_all_reduce(comm)
+                if fused is not None:
+                    return fused
+            except Exception as e:  # noqa: BLE001
+                logger.warning("fused TP all-reduce unavailable (%s); using NCCL", e)
+        return lambda x: comm.all_reduce(x)
+
+    @torch.no_grad()
+    def _init_weights(self, bundle: Any) -> None:
+        """Random-init runs: build the *full* tensors with the trainer's seed so shards agree across TP ranks."""
+        cfg, tp = self.model.cfg, self.model.tp
+        if bundle is not None:
+            self._load_full({n: p for n, p in bundle.transformer.named_parameters()})
+            return
+        if not self.config.pretrained_model_ckpt_path.startswith("random:"):
+            import glob
+            import os
+
+            from safetensors.torch import load_file
+
+            sd: Dict[str, torch.Tensor] = {}
+            for f in sorted(glob.glob(os.path.join(self.config.pretrained_model_ckpt_path, "*.safetensors"))):
+                sd.update(load_file(f))
+            self.model.load_hf_state_dict(sd)
+            return
+        full = Qwen3Transformer(cfg, dtype=self.model.embed_tokens.dtype, device="cpu" if tp.size > 1 else self.model.embed_tokens.device)
+        full.init_weights(self.config.init_seed)
+        self._load_full(dict(full.named_parameters()))
+
+    @torch.no_grad()
+    def _load_full(self, named_full: Dict[str, torch.Tensor]) -> int:
+        own = dict(self.model.named_parameters())
+        tp, n = self.model.tp, 0
+        for name, full in named_full.items():
+            if name not in own:
+                continue
+            own[name].copy_(shard_param(full, name, self.model.cfg, tp.rank, tp.size).to(own[name].device))
+            n += 1
+        return n
+
+    # ---- generation ----------------------------------------------------------------------------------------
+    @distributed(dispatch_mode=Dispatch.DP_SCATTER)
+    def generate(self, req: RolloutReq) -> RolloutResp:
+        if self._asleep:
+            self.wake_up()
+        cond = (req.request_conditions or {}).get("prompt")
+        if not isinstance(cond, TextTokenCondition):
+            texts = req.primitives.get("text")
+            if not isinstance(texts, Texts):
+                raise TypeError("NativeARRolloutEngine.generate: need primitives['text'] (Texts) or request_conditions['prompt']")
+            stage = Qwen3ChatTemplateStage(self, system_instruction=(req.stage_config.get("chat") or {}).get("system_instruction"),
+                                           enable_thinking=bool(self.config.chat_template_kwargs.get("enable_thinking", False)))
+            cond = stage.embed(texts).prompt
+        ar = get_ar_params(req.sampling_params)
+        c = self.config
+        max_new = int(ar.max_new_tokens) if ar is not None else c.max_new_tokens
+        temp = float(ar.temperature) if ar is not None else c.temperature
+        top_p = float(ar.top_p) if ar is not None else c.top_p
+        top_k = int(ar.top_k or 0) if ar is not None else c.top_k
+        stop = {int(self.model.cfg.eos_token_id)}
+        if ar is not None and ar.stop_token_id is not None:
+            stop.add(int(ar.stop_token_id))
+        prompts = unpad_prompts(cond.input_ids, cond.attention_mask)
+        out = self.generator.generate(prompts, max_new_tokens=max_new, temperature=temp, top_k=top_k, top_p=top_p, stop_token_ids=sorted(stop))
+        seg = pack_text_segment(out.tokens, out.log_probs, out.finished)
+        decoded = None
+        if c.detokenize:
+            decoded = Texts(texts=[self.tokenizer.decode(t.tolist(), skip_special_tokens=True) for t in out.tokens])
+        return RolloutResp(tracks={"ar": RolloutTrack(sample_ids=list(req.sample_ids), parent_ids=list(req.group_ids),
+                                                      conditions={"prompt": cond}, segment=seg, decoded=decoded)})
+
+    # ---- life cycle --------------------------------------------------------------------------------------------
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def sleep(self, tags: Optional[Sequence[str]] = None) -> None:
+        tags = set(tags or ("kv_cache", "cuda_graph"))
+        if tags & {"kv_cache", "cuda_graph"} and self.generator is not None:
+            self.generator.release_cache()
+        if "weights" in tags and not self._shares_trainer:
+            self._host_weights = {n: p.detach().to("cpu", non_blocking=True) for n, p in self.model.named_parameters()}
+            for p in self.model.parameters():
+                p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+        self._asleep = True
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def wake_up(self, tags: Optional[Sequence[str]] = None) -> None:
+        host = getattr(self, "_host_weights", None)
+        if host:
+            dev = torch.device(self.device)
+            for n, p in self.model.named_parameters():
+                p.data = host[n].to(dev, non_blocking=True)
+            self._host_weights = None
+        self._asleep = False
+
+    @property
+    def is_offloaded(self) -> bool:
+        return self._asleep
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def health_check(self) -> bool:
+        return self.model is not None and self.generator is not None
+
+    # ---- weight receive ----------------------------------------------------------------------------------------------
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def update_weights_from_tensor(self, *, serialized_named_tensors: List[Any], target_modules: Optional[List[str]] = None,
+                                   load_format: Optional[str] = None, flush_cache: bool = True, track_prefix: str = "") -> int:
+        """``serialized_named_tensors``: list of ``{name: full tensor}`` dicts (same process ⇒ no serialisation)."""
+        n = 0
+        if not self._shares_trainer:
+            for bucket in serialized_named_tensors:
+                n += self._load_full({k[len(track_prefix):] if track_prefix and k.startswith(track_prefix) else k: v for k, v in bucket.items()})
+        self.weight_version += 1
+        return n
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def init_weights_update_group(self, *, src_global_rank: int, member_global_ranks: List[int], group_name: str = "weight_sync", **_kw: Any) -> None:
+        """Join the trainer→engine broadcast group (built from pool-global ranks; the trainer rank joins from its side)."""
+        import torch.distributed as dist
+
+        from unirl_b200.distributed.group.comm import Comm
+
+        ranks = sorted(set([src_global_rank, *member_global_ranks]))
+        g = dist.new_group(ranks=ranks, use_local_synchronization=True) if dist.is_initialized() and len(ranks) > 1 else None
+        self._sync_groups[group_name] = Comm(g, ranks, self.comm.global_ranks[self.comm.rank] if self.comm.active else ranks[-1])
+        self._sync_src = ranks.index(src_global_rank)
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def update_weights_from_distributed(self, *, names: List[str], dtypes: List[str], shapes: List[List[int]], group_name: str = "weight_sync",
+                                        target_modules: Optional[List[str]] = None, flush_cache: bool = True, track_prefix: str = "") -> int:
+        comm = self._sync_groups[group_name]
+        dev = self.model.embed_tokens.device
+        got: Dict[str, torch.Tensor] = {}
+        for name, dt, shape in zip(names, dtypes, shapes):
+            buf = torch.empty(shape, dtype=parse_torch_dtype(dt), device=dev)
+            comm.broadcast(buf, src=self._sync_src)
+            got[name] = buf
+        n = self._load_full(got)
+        self.weight_version += 1
+        return n
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def destroy_weights_update_group(self, *, group_name: str = "weight_sync", track_prefix: str = "") -> None:
+        self._sync_groups.pop(group_name, None)
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def compute_local_param_checksums(self) -> Dict[str, str]:
+        from unirl_b200.distributed.weight_sync.checksum import fingerprint_tensor
+
+        return {n: fingerprint_tensor(p) for n, p in self.model.named_parameters()}
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    def get_weight_version(self) -> int:
+        return self.weight_version
+
+    def shutdown(self) -> None:
+        if self.generator is not None:
+            self.generator.release_cache()
+
+
+__all__ = ["NativeARRolloutEngine"]
