@@ -1,0 +1,212 @@
+#!/usr/bin/env python
+"""Headline benchmark: RL-step throughput of Qwen3-4B GRPO (tokens/s) and weight-sync latency (ms).
+
+One step = weight sync -> rollout (native paged-KV engine) -> reward -> group advantages -> sharded
+training update, driven through the public ``ARTrainer.train_step`` API on synthetic prompts
+(uniform-random token ids, length 256-1024, 8 samples per prompt, up to 4096 response tokens, random-init
+bf16 weights).  Per GPU the work is fixed (weak scaling): 16 prompts x 8 samples.
+
+    python bench.py [--gpus N --steps K --warmup W]            (N > 1: launched by torchrun, one rank per GPU)
+    python bench.py --impl reference ...                       (the reference arm)
+
+``value`` is device-timed (CUDA events around the rollout / sync / train phases, max over ranks);
+``e2e.value`` is wall-clock around the complete ``train_step`` calls, including the host->device copies of the
+step's prompts and the device->host reads of its rollout and loss.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--model", default="qwen3-4b")
+    ap.add_argument("--prompts-per-gpu", type=int, default=16)
+    ap.add_argument("--group-size", type=int, default=8)
+    ap.add_argument("--max-new-tokens", type=int, default=4096)
+    ap.add_argument("--prompt-min", type=int, default=256)
+    ap.add_argument("--prompt-max", type=int, default=1024)
+    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--rollout-tp", type=int, default=0, help="0 = 2 when gpus >= 2 else 1")
+    ap.add_argument("--algorithm", default="grpo", choices=["grpo", "drpo"])
+    return ap.parse_args()
+
+
+def reference_arm(args) -> None:
+    """The reference (Tencent-Hunyuan/UniRL) through its own public API, installed under baseline/_ref."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "unirl")):
+        why = "reference package is not installed under baseline/_ref"
+    else:
+        missing = []
+        for mod in ("ray", "hydra", "omegaconf", "peft", "diffusers", "tensordict"):
+            try:
+                __import__(mod)
+            except Exception:
+                missing.append(mod)
+        if missing:
+            why = ("reference installed with --no-deps, but its entrypoints (python -m unirl.train_ar: Hydra + Ray single controller, "
+                   "FSDP2 trainer) need packages absent from this offline image: " + ", ".join(missing))
+    if why is None:
+        why = "reference AR recipes require an SGLang/vLLM rollout server, which is not installable offline"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.5)
+
+    def start(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t:
+            self._t.join(timeout=6)
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(self.rows)}
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from unirl_b200.config.loader import compose
+    from unirl_b200.ops._ext import launch_count, require_ext
+    from unirl_b200.trainer.ar import ARTrainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local)
+    require_ext()
+    tp = args.rollout_tp or (2 if world >= 2 else 1)
+    preset = {"qwen3-4b": "random:qwen3-4b", "tiny": "random:tiny"}[args.model]
+    vocab = 151936 if args.model == "qwen3-4b" else 4096
+    n_prompts = args.prompts_per_gpu * world
+    overrides = [
+        f"num_devices={world}", f"batch_size={n_prompts}", f"bundle.config.pretrained_model_ckpt_path={preset}",
+        f"rollout.config.pretrained_model_ckpt_path={preset}", f"rollout.config.tp_size={tp}", f"rollout.config.max_new_tokens={args.max_new_tokens}",
+        f"rollout.config.max_running_requests={args.prompts_per_gpu * args.group_size * tp}",
+        f"sampling.samples_per_prompt={args.group_size}", f"sampling.max_new_tokens={args.max_new_tokens}",
+        f"data_source.vocab_size={vocab}", f"data_source.min_len={args.prompt_min}", f"data_source.max_len={args.prompt_max}",
+        f"data_source.reserved_low_ids={1000 if vocab > 4096 else 16}", f"stack.micro_batch_size={args.micro_batch}",
+        f"algorithm.horizon={args.max_new_tokens}", f"rollout_parallel={{tp: {tp}}}",
+    ]
+    if args.algorithm == "drpo":
+        overrides += ["algorithm._target_=unirl_b200.algorithms.drpo.DRPO", "~algorithm.clip_range", "~algorithm.clip_range_high",
+                      "+algorithm.drpo_epsilon=12.5"]
+    cfg = compose("ar/qwen3_4b_grpo_b200", overrides=overrides)
+    trainer = ARTrainer(cfg=cfg, batch_size=cfg.batch_size, bundle_cfg=cfg.bundle, pipeline_cfg=cfg.pipeline, backend_cfg=cfg.backend,
+                        rollout_cfg=cfg.rollout, reward_cfg=cfg.reward, algorithm_cfg=cfg.algorithm, stack_cfg=cfg.stack,
+                        data_source_cfg=cfg.data_source, sampling_cfg=cfg.sampling, sync_cfg=cfg.get("sync"), logging_cfg=None)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(i: int):
+        inputs = trainer.data_source.get_samples(trainer.batch_size)
+        # stage this step's prompts in pinned host memory: the engine's H2D copy starts from there
+        pt = inputs.primitives["prompt_tokens"]
+        pt.input_ids, pt.attention_mask = pt.input_ids.pin_memory(), pt.attention_mask.pin_memory()
+        h2d = pt.input_ids.numel() * pt.input_ids.element_size() * args.group_size
+        req = trainer._build_req(inputs, i)
+        result, reward = trainer.train_step(req, training_progress=0.0, sync_weights=True, rollout_id=i)
+        row = trainer.wandb_logger.history[-2] if len(trainer.wandb_logger.history) >= 2 else {}
+        rollout_row = next((r for r in reversed(trainer.wandb_logger.history) if "rollout/step" in r), {})
+        n_tok = int(round(rollout_row.get("rollout/response_length_mean", 0.0) * n_prompts * args.group_size))
+        dev_ms = dict(trainer.phase_timer.device_ms)
+        sync_ms = float(trainer.last_sync_stats.get("sync_ms", 0.0))
+        return {"tokens": n_tok, "device_ms": dev_ms, "sync_ms": sync_ms, "loss": float(result.loss), "reward": reward, "h2d": h2d,
+                "d2h": n_tok * (8 + 4) + 8}
+
+    for i in range(args.warmup):
+        one_step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    t0 = time.perf_counter()
+    rows = [one_step(args.warmup + i) for i in range(args.steps)]
+    ev1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    launches = launch_count() - l0
+    clocks = sampler.stop() if rank == 0 else {}
+    span_ms = ev0.elapsed_time(ev1)
+    dev_ms = sum(sum(v for k, v in r["device_ms"].items() if k in ("rollout", "train", "sync", "wake", "sleep", "reward")) for r in rows)
+    t = torch.tensor([dev_ms, span_ms, wall * 1e3, max(r["sync_ms"] for r in rows)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, span_ms, wall_ms, sync_ms = t.tolist()
+    tokens = sum(r["tokens"] for r in rows)
+    if rank == 0:
+        out = {"metric": "rl_step_tokens_per_s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+               "dtype": "bf16", "data": "synthetic (uniform-random prompt token ids, random-init weights, token-hash reward)",
+               "weight_sync_ms": sync_ms, "impl": "native",
+               "config": {"model": "Qwen3-4B" if args.model == "qwen3-4b" else args.model, "algorithm": args.algorithm.upper(),
+                          "global_batch": n_prompts * args.group_size, "prompts": n_prompts, "group_size": args.group_size,
+                          "seq_len": f"prompt {args.prompt_min}-{args.prompt_max} + response <= {args.max_new_tokens}",
+                          "tokens_counted": "generated response tokens", "tokens_per_step": tokens // max(1, args.steps),
+                          "micro_batch": args.micro_batch, "parallelism": f"dp{world} trainer (sharded optimizer), rollout tp{tp}",
+                          "l2_policy": "inputs_exceed_l2 (8 GB of bf16 weights + KV cache streamed every decode step)"},
+               "clocks": clocks,
+               "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": rows[-1]["h2d"], "d2h_bytes_per_step": rows[-1]["d2h"],
+                       "ms_per_step": wall_ms / args.steps},
+               "gpu_launches": int(launches), "loss": rows[-1]["loss"], "device_span_ms_per_step": span_ms / args.steps}
+        print(json.dumps(out))
+    trainer.shutdown()
+
+
+if __name__ == "__main__":
+    main()

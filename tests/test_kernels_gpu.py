@@ -1,0 +1,327 @@
+"""sm_100a kernels vs plain PyTorch fp32 references of the same op (run on the B200 box)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _C():
+    from unirl_b200.ops._ext import require_ext
+
+    return require_ext()
+
+
+def _close(a, b, atol, rtol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"{what}: max err {err.max().item():.4e} (tol {tol.max().item():.3e}), mean err {err.mean().item():.3e}"
+
+
+@pytest.mark.parametrize("rows,dim,dtype", [(7, 256, torch.bfloat16), (33, 2560, torch.bfloat16), (5, 100, torch.float32)])
+def test_rmsnorm_fwd_bwd(rows, dim, dtype):
+    from unirl_b200.ops.norm import rmsnorm, rmsnorm_reference
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, dim, device="cuda", dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(dtype).requires_grad_()
+    y = rmsnorm(x, w, 1e-6)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = rmsnorm_reference(xr, wr, 1e-6)
+    yr.backward(g.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(y, yr, tol, tol, "rmsnorm fwd")
+    _close(x.grad, xr.grad, tol, tol, "rmsnorm dx")
+    _close(w.grad, wr.grad, tol * 4, tol, "rmsnorm dw")
+
+
+def test_add_rmsnorm_and_modulate():
+    from unirl_b200.ops.norm import add_rmsnorm, layernorm_modulate, layernorm_modulate_reference, rmsnorm_reference
+
+    torch.manual_seed(1)
+    x = torch.randn(19, 512, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn_like(x)
+    w = torch.randn(512, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        y, r2 = add_rmsnorm(x, r, w, 1e-6)
+    rr = (x.float() + r.float()).to(torch.bfloat16)
+    _close(r2, rr, 1e-2, 1e-2, "residual")
+    _close(y, rmsnorm_reference(rr, w, 1e-6), 3e-2, 3e-2, "add_rmsnorm")
+    xx = torch.randn(2, 9, 384, device="cuda", dtype=torch.bfloat16)
+    sh, sc = torch.randn(2, 384, device="cuda", dtype=torch.bfloat16), torch.randn(2, 384, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        _close(layernorm_modulate(xx, sh, sc), layernorm_modulate_reference(xx.float(), sh.float(), sc.float(), 1e-6), 5e-2, 3e-2, "adaLN")
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 64), (32, 8, 128)])
+def test_qk_norm_rope_fwd_bwd(hq, hkv, d):
+    from unirl_b200.ops.rope import qk_norm_rope, qk_norm_rope_reference
+
+    torch.manual_seed(2)
+    t = 37
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).to(torch.bfloat16).requires_grad_()
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).to(torch.bfloat16).requires_grad_()
+    pos = torch.randint(0, 5000, (t,), device="cuda")
+    q, k, v = qk_norm_rope(qkv, qw, kw, pos, hq, hkv, d, 1e6, 1e-6)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    a, b, c = (x.detach().float().requires_grad_() for x in (qkv, qw, kw))
+    qr, kr, vr = qk_norm_rope_reference(a, b, c, pos, hq, hkv, d, 1e6, 1e-6)
+    torch.autograd.backward([qr, kr, vr], [gq.float(), gk.float(), gv.float()])
+    _close(q, qr, 3e-2, 2e-2, "q")
+    _close(k, kr, 3e-2, 2e-2, "k")
+    _close(v, vr, 1e-6, 0, "v")
+    _close(qkv.grad, a.grad, 4e-2, 3e-2, "dqkv")
+    _close(qw.grad, b.grad, 0.5, 5e-2, "dqw")
+    _close(kw.grad, c.grad, 0.5, 5e-2, "dkw")
+
+
+def test_swiglu():
+    from unirl_b200.ops.activation import swiglu, swiglu_reference
+
+    torch.manual_seed(3)
+    gu = torch.randn(45, 2 * 352, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = swiglu(gu)
+    g = torch.randn_like(y)
+    y.backward(g)
+    r = gu.detach().float().requires_grad_()
+    yr = swiglu_reference(r)
+    yr.backward(g.float())
+    _close(y, yr, 2e-2, 2e-2, "swiglu")
+    _close(gu.grad, r.grad, 3e-2, 2e-2, "swiglu bwd")
+
+
+@pytest.mark.parametrize("kind", ["clip", "drpo", "spo", "dppo"])
+def test_policy_losses(kind):
+    from unirl_b200.ops import policy_loss as PL
+
+    torch.manual_seed(4)
+    n = 5000
+    new = (-2 + 0.3 * torch.randn(n, device="cuda")).requires_grad_()
+    old = (new.detach() + 0.2 * torch.randn(n, device="cuda"))
+    adv = torch.randn(n, device="cuda")
+    newr = new.detach().clone().requires_grad_()
+    if kind == "clip":
+        (l, m), (lr, mr) = PL.ppo_clip(new, old, adv, 0.2, 0.28), PL.ppo_clip_reference(newr, old, adv, 0.2, 0.28)
+    elif kind in ("drpo", "spo"):
+        (l, m), (lr, mr) = PL.drpo(new, old, adv, 12.5, kind == "drpo"), PL.drpo_reference(newr, old, adv, 12.5, kind == "drpo")
+    else:
+        b, s = 50, 100
+        nm, om = torch.randn(b, s, 4, 8, 8, device="cuda"), None
+        om = nm + 0.01 * torch.randn_like(nm)
+        sig = torch.full((1, s, 1, 1, 1), 0.05, device="cuda")
+        new2, newr2 = new.view(b, s), newr.view(b, s)
+        (l, m), (lr, mr) = PL.flow_dppo(new2, old.view(b, s), nm, om, adv.view(b, s), sig, 0.02), PL.flow_dppo_reference(
+            newr2, old.view(b, s), nm, om, adv.view(b, s), sig, 0.02)
+    l.mean().backward()
+    lr.mean().backward()
+    _close(l, lr, 1e-5, 1e-4, "loss")
+    _close(new.grad, newr.grad, 1e-8, 1e-3, "dlogp")
+    for k in mr:
+        _close(m[k], mr[k], 1e-4, 2e-3, f"metric {k}")
+
+
+def test_sampler_distribution_and_logp():
+    from unirl_b200.ops.sampling import sample
+
+    torch.manual_seed(5)
+    v = 1000
+    logits = torch.randn(1, v, device="cuda") * 2
+    rows = logits.expand(4096, v).contiguous()
+    tok, lp = sample(rows, 0.7, seed=11, step=3)
+    ref = torch.log_softmax(logits[0] / 0.7, -1)
+    _close(lp, ref[tok], 1e-4, 1e-4, "sampled logp")
+    freq = torch.bincount(tok, minlength=v).float() / tok.numel()
+    top = ref.exp().topk(5).indices
+    assert (freq[top] - ref.exp()[top]).abs().max() < 0.03
+    tok2, _ = sample(rows, 0.7, seed=11, step=3)
+    assert torch.equal(tok, tok2), "sampler must be a pure function of (seed, step, row)"
+    tok3, _ = sample(rows, 0.7, seed=11, step=4)
+    assert not torch.equal(tok, tok3)
+    g, glp = sample(logits.to(torch.bfloat16), 0.0)
+    assert int(g) == int(logits.to(torch.bfloat16).float().argmax())
+
+
+def test_adamw_and_sum_squares():
+    from unirl_b200.ops.optim import adamw_reference, adamw_step, sum_squares
+
+    torch.manual_seed(6)
+    n = 100_003
+    master = torch.randn(n, device="cuda")
+    grad = torch.randn(n, device="cuda").to(torch.bfloat16)
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    low = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ema = master.clone()
+    rm, rmm, rv, rema = master.clone(), m.clone(), v.clone(), ema.clone()
+    coef = torch.tensor([0.5], device="cuda")
+    for step in (1, 2, 3):
+        adamw_step(master, grad, m, v, lr=1e-3, weight_decay=0.01, step=step, low=low, ema=ema, ema_decay=0.99, grad_scale_tensor=coef)
+        adamw_reference(rm, grad, rmm, rv, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=step, grad_scale=0.5, ema=rema, ema_decay=0.99)
+    _close(master, rm, 1e-6, 1e-5, "adamw master")
+    _close(low, rm.to(torch.bfloat16), 1e-2, 1e-2, "adamw low")
+    _close(ema, rema, 1e-6, 1e-5, "ema")
+    _close(sum_squares(grad), grad.float().pow(2).sum(), 1e-2, 1e-4, "sum_squares")
+
+
+@pytest.mark.parametrize("name", ["flow", "cps", "dance"])
+def test_sde_step_matches_strategy(name):
+    from unirl_b200.ops.sde_step import sde_step
+    from unirl_b200.sde import get_sigma_schedule, make_strategy
+
+    torch.manual_seed(7)
+    st = make_strategy(name)
+    sig = get_sigma_schedule(10, 3.0).cuda()
+    x = torch.randn(3, 16, 32, 32, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn_like(x).requires_grad_()
+    noise = torch.randn(x.shape, device="cuda")
+    prev, lp, mean = sde_step(st, v, x, sig[2], sig[3], eta=0.7, noise=noise)
+    rprev, rlp, rmean = st.denoise(v.detach(), x, sig[2], sig[3], eta=0.7, noise=noise)
+    _close(prev, rprev, 1e-5, 1e-5, "prev")
+    _close(mean, rmean, 1e-5, 1e-5, "mean")
+    _close(lp, rlp, 1e-3, 1e-3, "logp")
+    stored = prev.to(torch.bfloat16)
+    p2, lp2, m2 = sde_step(st, v, x, sig[2], sig[3], eta=0.7, prev_sample=stored)
+    vr = v.detach().clone().requires_grad_()
+    _, rlp2, rm2 = st.denoise(vr, x, sig[2], sig[3], eta=0.7, prev_sample=stored)
+    _close(lp2, rlp2, 1e-3, 1e-3, "replay logp")
+    (lp2.sum() + 0.01 * m2.sum()).backward()
+    (rlp2.sum() + 0.01 * rm2.sum()).backward()
+    _close(v.grad, vr.grad, 1e-4, 2e-2, "replay dv")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 512, 320), (1000, 6144, 2560), (257, 2560, 9728), (64, 384, 128)])
+def test_gemm_tcgen05(m, n, k):
+    C = _C()
+    torch.manual_seed(8)
+    a = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda") * 0.5).to(torch.bfloat16)
+    r = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    c = C.gemm_bf16_tn(a, b, None, 0)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0, "a bounded wait expired inside the GEMM"
+    _close(c, ref, 0.15, 2e-2, "gemm")
+    c2 = C.gemm_bf16_tn(a, b, r, 1)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0
+    _close(c2, ref + r.float(), 0.15, 2e-2, "gemm+residual")
+
+
+def test_gemm_swiglu_epilogue():
+    C = _C()
+    torch.manual_seed(9)
+    m, inter, k = 300, 640, 256
+    a = (torch.randn(m, k, device="cuda") * 0.3).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device="cuda") * 0.3).to(torch.bfloat16)
+    out = C.gemm_bf16_tn(a, w, None, 2)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0
+    z = a.float() @ w.float().t()
+    ref = torch.nn.functional.silu(z[:, :inter]) * z[:, inter:]
+    _close(out, ref, 0.1, 3e-2, "gemm+swiglu")
+
+
+@pytest.mark.parametrize("t,v,k,temp", [(100, 1000, 64, 1.0), (700, 4096, 256, 0.7), (130, 151936, 2560, 1.0)])
+def test_linear_logprob_fwd_bwd(t, v, k, temp):
+    from unirl_b200.ops.logprob import linear_logprob, linear_logprob_reference
+
+    torch.manual_seed(10)
+    h = (torch.randn(t, k, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(v, k, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    tgt = torch.randint(0, v, (t,), device="cuda")
+    lp = linear_logprob(h, w, tgt, temp)
+    ref = linear_logprob_reference(h.detach(), w.detach(), tgt, temp)
+    torch.cuda.synchronize()
+    assert _C().gemm_status(True) == 0
+    _close(lp, ref, 2e-2, 1e-3, "logprob")
+    if v <= 4096:
+        g = torch.randn(t, device="cuda")
+        lp.backward(g)
+        hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+        z = (hr @ wr.t()) / temp
+        (torch.log_softmax(z, -1).gather(-1, tgt[:, None]).squeeze(-1) * g).sum().backward()
+        _close(h.grad, hr.grad, 2e-2, 5e-2, "dH")
+        _close(w.grad, wr.grad, 2e-2, 5e-2, "dW")
+
+
+def test_linear_sample_matches_unfused():
+    C = _C()
+    torch.manual_seed(11)
+    b, v, k = 64, 5000, 256
+    h = (torch.randn(b, k, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(v, k, device="cuda") * 0.1).to(torch.bfloat16)
+    tok, lp = C.linear_sample(h, w, 0.8, 123, 7, None)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0
+    ref = torch.log_softmax((h.float() @ w.float().t()) / 0.8, -1)
+    _close(lp, ref.gather(-1, tok[:, None]).squeeze(-1), 3e-2, 1e-3, "fused sample logp")
+    assert int(tok.min()) >= 0 and int(tok.max()) < v
+    # same (seed, step) => same draw; other step => other draw
+    tok2, _ = C.linear_sample(h, w, 0.8, 123, 7, None)
+    assert torch.equal(tok, tok2)
+
+
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 64, 16), (32, 8, 128, 64), (28, 4, 128, 32)])
+def test_paged_decode_attention(hq, hkv, d, page):
+    from unirl_b200.ops.attention import kv_cache_write, paged_decode_attention, paged_decode_attention_reference
+
+    torch.manual_seed(12)
+    lens = [1, 17, 64, 65, 300, 1000]
+    b = len(lens)
+    max_pages = (max(lens) + page - 1) // page
+    n_pages = b * max_pages + 3
+    kc = torch.zeros(n_pages, hkv, page, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    perm = torch.randperm(n_pages)[: b * max_pages].view(b, max_pages).to(torch.int32).cuda()
+    for i, n in enumerate(lens):
+        k = torch.randn(n, hkv, d, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn(n, hkv, d, device="cuda", dtype=torch.bfloat16)
+        pos = torch.arange(n, device="cuda")
+        slots = perm[i, (pos // page)].long() * page + pos % page
+        kv_cache_write(k, v, kc, vc, slots)
+    q = torch.randn(b, hq, d, device="cuda", dtype=torch.bfloat16)
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    out = paged_decode_attention(q, kc, vc, perm, sl, None, None, max(lens))
+    ref = paged_decode_attention_reference(q, kc, vc, perm, sl)
+    _close(out, ref, 2e-2, 2e-2, "paged decode attention")
+
+
+def test_kv_cache_write_matches_reference():
+    from unirl_b200.ops.attention import kv_cache_write
+
+    torch.manual_seed(13)
+    kc = torch.zeros(10, 2, 16, 64, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    k, v = torch.randn(20, 2, 64, device="cuda", dtype=torch.bfloat16), torch.randn(20, 2, 64, device="cuda", dtype=torch.bfloat16)
+    slots = torch.randperm(160, device="cuda")[:20]
+    kv_cache_write(k, v, kc, vc, slots)
+    kr, vr = torch.zeros_like(kc).cpu(), torch.zeros_like(vc).cpu()
+    kv_cache_write(k.cpu(), v.cpu(), kr, vr, slots.cpu())
+    assert torch.equal(kc.cpu(), kr) and torch.equal(vc.cpu(), vr)
+
+
+def test_rollout_replay_parity_and_train_step_tiny():
+    """Decode path (paged KV, graph) vs packed replay path: same log-probs; one GRPO step runs."""
+    from unirl_b200.models.qwen3 import Qwen3ARConditions, Qwen3Pipeline, Qwen3PipelineConfig
+    from unirl_b200.models.qwen3.chat_template import pad_right
+    from unirl_b200.types import ARSamplingParams, RolloutReq
+
+    torch.manual_seed(14)
+    pipe = Qwen3Pipeline.from_config(Qwen3PipelineConfig(model_precision="bf16", device="cuda"))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 4096, (int(n),), generator=g).tolist() for n in (5, 40, 77, 130)]
+    req = RolloutReq(sample_ids=[f"s{i}" for i in range(4)], group_ids=["a", "a", "b", "b"], request_conditions={"prompt": pad_right(prompts, 0)},
+                     sampling_params=ARSamplingParams(temperature=1.0, top_p=1.0, top_k=0, max_new_tokens=40))
+    with torch.no_grad():
+        resp = pipe.generate(req)
+    tr = resp.tracks["ar"]
+    new = pipe.ar.replay(Qwen3ARConditions.from_dict(tr.conditions), segment=tr.segment, temperature=1.0)
+    diff = (new.detach().cpu() - tr.segment.log_probs).abs()
+    assert diff.mean() < 0.03 and diff.max() < 0.3, f"rollout/replay gap too large: mean {diff.mean():.4f} max {diff.max():.4f}"
+    new.sum().backward()
+    assert pipe.bundle.transformer.layers[0].qkv_proj.grad is not None

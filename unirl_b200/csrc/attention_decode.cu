@@ -1,0 +1,271 @@
+// Paged-KV decode attention: one query token per sequence, GQA-packed, split-KV.
+//
+// Grid (split, kv_head, sequence); 4 warps per CTA.  The G = Hq/Hkv query heads that share a KV head are
+// packed as the (zero-padded) 16 rows of the mma.sync A operand, so every K/V byte fetched from HBM is used
+// by all G heads.  Each warp owns a private double-buffered 32-token K/V tile (cp.async, XOR-swizzled rows)
+// and its own online-softmax state, so the main loop has no block-level synchronisation; warps are merged
+// once through shared memory and splits once through an fp32 workspace by a second tiny kernel.
+// The kernel is HBM-bound by construction: ~1 tensor-core instruction per 128 bytes of KV.
+#include "mma.cuh"
+#include "ops.h"
+
+namespace ub {
+
+constexpr int kDecTile = 32;    // tokens per warp tile
+constexpr int kDecWarps = 4;
+constexpr int kDecStages = 2;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+__device__ __forceinline__ void dec_load_tile(bf16* sK, bf16* sV, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                                              const int* __restrict__ bt_row, int tile, int seq_len, int h, int Hkv, int page_size, int lane) {
+  constexpr int kChunks = D / 8;
+  constexpr int kIters = kDecTile * kChunks / 32;
+#pragma unroll
+  for (int i = 0; i < kIters; ++i) {
+    const int idx = i * 32 + lane;
+    const int row = idx / kChunks, chunk = idx % kChunks;
+    const int tok = tile * kDecTile + row;
+    const bool valid = tok < seq_len;
+    const int safe_tok = valid ? tok : 0;
+    const int64_t page = bt_row[safe_tok / page_size];
+    const int64_t src = ((page * Hkv + h) * page_size + (safe_tok % page_size)) * D + chunk * 8;
+    cp_async_16(sK + swz<D>(row, chunk), kc + src, valid);
+    cp_async_16(sV + swz<D>(row, chunk), vc + src, valid);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kDecWarps * 32)
+paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_tables,
+                    const int* __restrict__ seq_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, int Hq, int Hkv, int page_size,
+                    int max_pages, int num_splits, float scale_log2) {
+  extern __shared__ __align__(128) uint8_t dec_smem[];
+  constexpr int kTileElems = kDecTile * D;
+  constexpr int kND = D / 8;   // n-tiles of the output
+  constexpr int kKK = D / 16;  // k-steps of Q·Kᵀ
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = Hq / Hkv;
+  const int seq_len = seq_lens[b];
+  const int* bt_row = block_tables + (int64_t)b * max_pages;
+  const int tiles_total = (seq_len + kDecTile - 1) / kDecTile;
+  const int tiles_per_split = (tiles_total + num_splits - 1) / num_splits;
+  const int t_begin = split * tiles_per_split;
+  const int t_end = min(t_begin + tiles_per_split, tiles_total);
+
+  bf16* my = reinterpret_cast<bf16*>(dec_smem) + (size_t)warp * kDecStages * 2 * kTileElems;
+
+  // Q fragments (rows >= G are zero)
+  uint32_t qa[kKK][4];
+  {
+    const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+    const bf16* qb = q + ((int64_t)b * Hq + (int64_t)h * G) * D;
+#pragma unroll
+    for (int kk = 0; kk < kKK; ++kk) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = r0 + (j & 1) * 8, col = kk * 16 + c0 + (j >> 1) * 8;
+        qa[kk][j] = (row < G) ? *reinterpret_cast<const uint32_t*>(qb + (int64_t)row * D + col) : 0u;
+      }
+    }
+  }
+
+  float o[kND][4];
+#pragma unroll
+  for (int i = 0; i < kND; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  int tile = t_begin + warp;
+  if (tile < t_end) dec_load_tile<D>(my, my + kTileElems, kc, vc, bt_row, tile, seq_len, h, Hkv, page_size, lane);
+  cp_async_commit();
+  int stage = 0;
+  for (; tile < t_end; tile += kDecWarps) {
+    const int next = tile + kDecWarps;
+    bf16* nK = my + (stage ^ 1) * 2 * kTileElems;
+    if (next < t_end) dec_load_tile<D>(nK, nK + kTileElems, kc, vc, bt_row, next, seq_len, h, Hkv, page_size, lane);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const bf16* sK = my + stage * 2 * kTileElems;
+    const bf16* sV = sK + kTileElems;
+
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    const int mat = lane >> 3, mr = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < kKK; ++kk) {
+#pragma unroll
+      for (int nt = 0; nt < 4; nt += 2) {
+        uint32_t r0, r1, r2, r3;
+        const int row = (nt + (mat >> 1)) * 8 + mr, chunk = kk * 2 + (mat & 1);
+        ldmatrix_x4(smem_addr(sK + swz<D>(row, chunk)), r0, r1, r2, r3);
+        mma_bf16_16816(s[nt], qa[kk], r0, r1);
+        mma_bf16_16816(s[nt + 1], qa[kk], r2, r3);
+      }
+    }
+    // mask + online softmax (rows lane/4 and lane/4 + 8)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int tok = tile * kDecTile + nt * 8 + (lane & 3) * 2 + (j & 1);
+        s[nt][j] = (tok < seq_len) ? s[nt][j] * scale_log2 : -INFINITY;
+        mx[j >> 1] = fmaxf(mx[j >> 1], s[nt][j]);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      alpha[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_new);
+      m_run[r] = m_new;
+      l_run[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float p = (m_run[j >> 1] == -INFINITY) ? 0.f : exp2f(s[nt][j] - m_run[j >> 1]);
+        s[nt][j] = p;
+        l_run[j >> 1] += p;
+      }
+    }
+#pragma unroll
+    for (int nd = 0; nd < kND; ++nd) {
+      o[nd][0] *= alpha[0];
+      o[nd][1] *= alpha[0];
+      o[nd][2] *= alpha[1];
+      o[nd][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kt = 0; kt < 2; ++kt) {
+      uint32_t pa[4] = {pack_bf16(s[2 * kt][0], s[2 * kt][1]), pack_bf16(s[2 * kt][2], s[2 * kt][3]),
+                        pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]), pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3])};
+#pragma unroll
+      for (int nd = 0; nd < kND; nd += 2) {
+        uint32_t r0, r1, r2, r3;
+        const int row = kt * 16 + (mat & 1) * 8 + mr, chunk = nd + (mat >> 1);
+        ldmatrix_x4_trans(smem_addr(sV + swz<D>(row, chunk)), r0, r1, r2, r3);
+        mma_bf16_16816(o[nd], pa, r0, r1);
+        mma_bf16_16816(o[nd + 1], pa, r2, r3);
+      }
+    }
+    __syncwarp();
+    stage ^= 1;
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  __syncthreads();  // all warps are done with their tile buffers: reuse shared memory for the merge
+
+  float* sm_o = reinterpret_cast<float*>(dec_smem);                   // [warps][16][D]
+  float* sm_ml = sm_o + kDecWarps * 16 * D;                           // [warps][16][2]
+  {
+    const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+    for (int nd = 0; nd < kND; ++nd) {
+      float* base = sm_o + ((size_t)warp * 16) * D + nd * 8 + c0;
+      base[(size_t)r0 * D] = o[nd][0];
+      base[(size_t)r0 * D + 1] = o[nd][1];
+      base[(size_t)(r0 + 8) * D] = o[nd][2];
+      base[(size_t)(r0 + 8) * D + 1] = o[nd][3];
+    }
+    if ((lane & 3) == 0) {
+      sm_ml[(warp * 16 + r0) * 2] = m_run[0];
+      sm_ml[(warp * 16 + r0) * 2 + 1] = l_run[0];
+      sm_ml[(warp * 16 + r0 + 8) * 2] = m_run[1];
+      sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = l_run[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, sm_ml[(w * 16 + g) * 2]);
+    float Lsum = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float mw = sm_ml[(w * 16 + g) * 2];
+      const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      Lsum += sm_ml[(w * 16 + g) * 2 + 1] * wgt;
+      acc += sm_o[((size_t)w * 16 + g) * D + d] * wgt;
+    }
+    const int64_t o_idx = ((int64_t)b * Hq + (int64_t)h * G + g) * num_splits + split;
+    ws_o[o_idx * D + d] = acc;
+    if (d == 0) {
+      ws_ml[o_idx * 2] = M;
+      ws_ml[o_idx * 2 + 1] = Lsum;
+    }
+  }
+}
+
+template <int D>
+__global__ void decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, bf16* __restrict__ out, int num_splits) {
+  const int64_t bh = blockIdx.x;
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, ws_ml[(bh * num_splits + s) * 2]);
+  float L = 0.f, acc = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float m = ws_ml[(bh * num_splits + s) * 2];
+    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    L += ws_ml[(bh * num_splits + s) * 2 + 1] * w;
+    acc += ws_o[(bh * num_splits + s) * D + d] * w;
+  }
+  out[bh * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+int decode_num_splits(int B, int Hkv, int max_kv_len) {
+  const int ctas = B * Hkv;
+  if (ctas >= 296 || max_kv_len <= 0) return 1;
+  const int tiles = (max_kv_len + kDecTile * kDecWarps - 1) / (kDecTile * kDecWarps);
+  int s = (592 + ctas - 1) / ctas;
+  if (s > tiles) s = tiles;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : s;
+}
+
+int64_t decode_workspace_floats(int B, int Hq, int D, int num_splits) { return (int64_t)B * Hq * num_splits * (D + 2); }
+
+int paged_decode_attention(const void* q, const void* kc, const void* vc, const int* block_tables, const int* seq_lens, void* out, float* workspace,
+                           int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (Hq % Hkv || Hq / Hkv > 16 || (D != 64 && D != 128)) return 1;
+  float* ws_o = workspace;
+  float* ws_ml = workspace + (int64_t)B * Hq * num_splits * D;
+  const dim3 grid(num_splits, Hkv, B);
+  const size_t smem = (size_t)kDecWarps * kDecStages * 2 * kDecTile * D * sizeof(bf16);
+  const size_t merge_smem = (size_t)kDecWarps * 16 * (D + 2) * sizeof(float);
+  const size_t need = smem > merge_smem ? smem : merge_smem;
+  if (D == 128) {
+    static bool cfg = false;
+    if (!cfg) {
+      if (cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2;
+      cfg = true;
+    }
+    paged_decode_kernel<128><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, block_tables, seq_lens, ws_o, ws_ml,
+                                                                Hq, Hkv, page_size, max_pages, num_splits, scale * kLog2e);
+    decode_merge_kernel<128><<<B * Hq, 128, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      if (cudaFuncSetAttribute(paged_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2;
+      cfg = true;
+    }
+    paged_decode_kernel<64><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, block_tables, seq_lens, ws_o, ws_ml,
+                                                               Hq, Hkv, page_size, max_pages, num_splits, scale * kLog2e);
+    decode_merge_kernel<64><<<B * Hq, 64, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace ub

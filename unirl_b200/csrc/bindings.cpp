@@ -1,0 +1,354 @@
+// PyTorch bindings of the sm_100a kernels (module unirl_b200._C).  Tensors are validated here; the .cu
+// launchers only see raw pointers.  Outputs are allocated with the caching allocator on the current stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <limits>
+#include <map>
+#include <tuple>
+
+#include "ops.h"
+#include "runtime.h"
+
+namespace py = pybind11;
+using torch::Tensor;
+
+namespace {
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int dt(const Tensor& t) {
+  if (t.scalar_type() == at::kBFloat16) return ub::kBF16;
+  if (t.scalar_type() == at::kFloat) return ub::kF32;
+  TORCH_CHECK(false, "unirl_b200: unsupported dtype ", t.scalar_type(), " (expected bfloat16 or float32)");
+}
+void chk(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+const void* optr(const c10::optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+Tensor& gemm_status_tensor() {
+  static Tensor st;
+  if (!st.defined()) st = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA));
+  return st;
+}
+
+// ---------------------------------------------------------------------------------------------- norms
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  chk(x, "x"); chk(w, "weight");
+  TORCH_CHECK(x.dim() == 2 && w.numel() == x.size(1) && w.scalar_type() == x.scalar_type(), "rmsnorm: shape/dtype mismatch");
+  c10::cuda::CUDAGuard g(x.device());
+  auto y = torch::empty_like(x);
+  auto rstd = torch::empty({x.size(0)}, x.options().dtype(torch::kFloat));
+  ub::rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), x.size(0), (int)x.size(1), (float)eps, dt(x), stream());
+  return {y, rstd};
+}
+std::vector<Tensor> rmsnorm_bwd(const Tensor& gy, const Tensor& x, const Tensor& w, const Tensor& rstd) {
+  chk(gy, "gy"); chk(x, "x");
+  c10::cuda::CUDAGuard g(x.device());
+  auto gx = torch::empty_like(x);
+  auto gw = torch::zeros({x.size(1)}, x.options().dtype(torch::kFloat));
+  ub::rmsnorm_bwd(gy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), gx.data_ptr(), gw.data_ptr<float>(), x.size(0), (int)x.size(1), dt(x), stream());
+  return {gx, gw};
+}
+std::vector<Tensor> add_rmsnorm_fwd(const Tensor& x, const Tensor& res, const Tensor& w, double eps) {
+  chk(x, "x"); chk(res, "residual");
+  TORCH_CHECK(x.sizes() == res.sizes() && x.scalar_type() == res.scalar_type(), "add_rmsnorm: mismatch");
+  c10::cuda::CUDAGuard g(x.device());
+  auto x2 = x.reshape({-1, x.size(-1)});
+  auto y = torch::empty_like(x), r = torch::empty_like(x);
+  ub::add_rmsnorm_fwd(x.data_ptr(), res.data_ptr(), w.data_ptr(), y.data_ptr(), r.data_ptr(), x2.size(0), (int)x2.size(1), (float)eps, dt(x), stream());
+  return {y, r};
+}
+Tensor layernorm_modulate_fwd(const Tensor& x, const Tensor& shift, const Tensor& scale, double eps) {
+  chk(x, "x"); chk(shift, "shift"); chk(scale, "scale");
+  TORCH_CHECK(x.dim() == 3 && shift.dim() == 2 && shift.size(0) == x.size(0) && shift.size(1) == x.size(2), "layernorm_modulate: shapes");
+  TORCH_CHECK(shift.scalar_type() == x.scalar_type() && scale.scalar_type() == x.scalar_type(), "layernorm_modulate: dtypes");
+  c10::cuda::CUDAGuard g(x.device());
+  auto y = torch::empty_like(x);
+  ub::layernorm_modulate_fwd(x.data_ptr(), shift.data_ptr(), scale.data_ptr(), y.data_ptr(), x.size(0), (int)x.size(1), (int)x.size(2), (float)eps, dt(x), stream());
+  return y;
+}
+
+// ---------------------------------------------------------------------------------------------- rope
+Tensor inv_freq_table(int64_t head_dim, double theta, const torch::Device& dev) {
+  // identical expression to the PyTorch oracle: 1 / theta ** (arange(0, D, 2) / D); cached per (D, theta, device)
+  static std::map<std::tuple<int64_t, double, int>, Tensor> cache;
+  const auto key = std::make_tuple(head_dim, theta, (int)dev.index());
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  auto idx = torch::arange(0, head_dim, 2, torch::dtype(torch::kFloat).device(dev));
+  auto t = torch::reciprocal(torch::pow(torch::scalar_tensor(theta, torch::dtype(torch::kFloat).device(dev)), idx / (double)head_dim)).contiguous();
+  cache.emplace(key, t);
+  return t;
+}
+std::vector<Tensor> qk_norm_rope_fwd(const Tensor& qkv, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw, const Tensor& pos,
+                                     int64_t Hq, int64_t Hkv, int64_t D, double theta, double eps) {
+  chk(qkv, "qkv"); chk(pos, "positions");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == (Hq + 2 * Hkv) * D && pos.scalar_type() == at::kInt && D % 2 == 0 && D <= 256, "qk_norm_rope: shapes");
+  c10::cuda::CUDAGuard g(qkv.device());
+  const int64_t T = qkv.size(0);
+  auto q = torch::empty({T, Hq, D}, qkv.options()), k = torch::empty({T, Hkv, D}, qkv.options()), v = torch::empty({T, Hkv, D}, qkv.options());
+  auto rstd = torch::empty({T, Hq + Hkv}, qkv.options().dtype(torch::kFloat));
+  auto inv = inv_freq_table(D, theta, qkv.device());
+  ub::qk_norm_rope_fwd(qkv.data_ptr(), optr(qw), optr(kw), pos.data_ptr<int>(), inv.data_ptr<float>(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                       rstd.data_ptr<float>(), T, (int)Hq, (int)Hkv, (int)D, (float)eps, dt(qkv), stream());
+  return {q, k, v, rstd};
+}
+std::vector<Tensor> qk_norm_rope_bwd(const Tensor& gq, const Tensor& gk, const Tensor& gv, const Tensor& qkv, const c10::optional<Tensor>& qw,
+                                     const c10::optional<Tensor>& kw, const Tensor& pos, const Tensor& rstd, int64_t Hq, int64_t Hkv, int64_t D, double theta) {
+  chk(gq, "gq"); chk(gk, "gk"); chk(gv, "gv"); chk(qkv, "qkv");
+  c10::cuda::CUDAGuard g(qkv.device());
+  auto g_qkv = torch::empty_like(qkv);
+  auto f32 = qkv.options().dtype(torch::kFloat);
+  auto g_qw = torch::zeros({D}, f32), g_kw = torch::zeros({D}, f32);
+  auto inv = inv_freq_table(D, theta, qkv.device());
+  const bool has_w = qw.has_value() && qw->defined();
+  ub::qk_norm_rope_bwd(gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), qkv.data_ptr(), optr(qw), optr(kw), pos.data_ptr<int>(), inv.data_ptr<float>(),
+                       rstd.data_ptr<float>(), g_qkv.data_ptr(), has_w ? g_qw.data_ptr<float>() : nullptr, has_w ? g_kw.data_ptr<float>() : nullptr,
+                       qkv.size(0), (int)Hq, (int)Hkv, (int)D, dt(qkv), stream());
+  return {g_qkv, g_qw, g_kw};
+}
+
+// ---------------------------------------------------------------------------------------------- swiglu / kv
+Tensor swiglu_fwd(const Tensor& gu) {
+  chk(gu, "gate_up");
+  c10::cuda::CUDAGuard g(gu.device());
+  auto sizes = gu.sizes().vec();
+  const int64_t I = sizes.back() / 2;
+  sizes.back() = I;
+  auto out = torch::empty(sizes, gu.options());
+  ub::swiglu_fwd(gu.data_ptr(), out.data_ptr(), gu.numel() / (2 * I), (int)I, dt(gu), stream());
+  return out;
+}
+Tensor swiglu_bwd(const Tensor& gy, const Tensor& gu) {
+  chk(gy, "gy"); chk(gu, "gate_up");
+  c10::cuda::CUDAGuard g(gu.device());
+  auto out = torch::empty_like(gu);
+  const int64_t I = gu.size(-1) / 2;
+  ub::swiglu_bwd(gy.data_ptr(), gu.data_ptr(), out.data_ptr(), gu.numel() / (2 * I), (int)I, dt(gu), stream());
+  return out;
+}
+void kv_cache_write(const Tensor& k, const Tensor& v, Tensor& kc, Tensor& vc, const Tensor& slots) {
+  chk(k, "k"); chk(v, "v"); chk(kc, "k_cache"); chk(vc, "v_cache"); chk(slots, "slot_mapping");
+  TORCH_CHECK(slots.scalar_type() == at::kLong && k.scalar_type() == kc.scalar_type(), "kv_cache_write: dtypes");
+  c10::cuda::CUDAGuard g(k.device());
+  ub::kv_cache_write(k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), slots.data_ptr<int64_t>(), k.size(0), (int)k.size(1), (int)k.size(2),
+                     (int)kc.size(2), dt(k), stream());
+}
+
+// ---------------------------------------------------------------------------------------------- losses
+std::vector<Tensor> policy_loss_fwd(const Tensor& n, const Tensor& o, const Tensor& a, const c10::optional<Tensor>& keep, int64_t kind, double p0, double p1) {
+  chk(n, "new_logp"); chk(o, "old_logp"); chk(a, "advantages");
+  TORCH_CHECK(n.scalar_type() == at::kFloat && o.scalar_type() == at::kFloat && a.scalar_type() == at::kFloat, "policy_loss: fp32 inputs expected");
+  c10::cuda::CUDAGuard g(n.device());
+  auto loss = torch::empty_like(n), dloss = torch::empty_like(n);
+  auto stats = torch::zeros({8}, n.options());
+  stats.index_put_({2}, std::numeric_limits<float>::infinity());
+  ub::policy_loss_fwd(n.data_ptr<float>(), o.data_ptr<float>(), a.data_ptr<float>(), (const uint8_t*)optr(keep), loss.data_ptr<float>(),
+                      dloss.data_ptr<float>(), stats.data_ptr<float>(), n.numel(), (int)kind, (float)p0, (float)p1, stream());
+  return {loss, dloss, stats};
+}
+Tensor mean_sq_diff_rows(const Tensor& a, const Tensor& b) {
+  chk(a, "a"); chk(b, "b");
+  TORCH_CHECK(a.dim() == 2 && a.sizes() == b.sizes() && a.scalar_type() == b.scalar_type(), "mean_sq_diff_rows: mismatch");
+  c10::cuda::CUDAGuard g(a.device());
+  auto out = torch::empty({a.size(0)}, a.options().dtype(torch::kFloat));
+  ub::mean_sq_diff_rows(a.data_ptr(), b.data_ptr(), out.data_ptr<float>(), a.size(0), a.size(1), dt(a), stream());
+  return out;
+}
+void logprob_dlogits_inplace(Tensor& z, const Tensor& tgt, const Tensor& lse, const Tensor& gg, double temperature) {
+  chk(z, "logits"); chk(tgt, "targets"); chk(lse, "lse"); chk(gg, "grad");
+  TORCH_CHECK(z.dim() == 2 && tgt.scalar_type() == at::kInt && lse.scalar_type() == at::kFloat && gg.scalar_type() == at::kFloat, "dlogits: dtypes");
+  c10::cuda::CUDAGuard g(z.device());
+  ub::logprob_dlogits_inplace(z.data_ptr(), tgt.data_ptr<int>(), lse.data_ptr<float>(), gg.data_ptr<float>(), z.size(0), z.size(1), (float)temperature, dt(z), stream());
+}
+
+// ---------------------------------------------------------------------------------------------- sampler / optimiser
+std::vector<Tensor> sample_full(const Tensor& logits, double temperature, int64_t seed, int64_t step, const c10::optional<Tensor>& step_tensor,
+                                c10::optional<Tensor> tok_out, c10::optional<Tensor> logp_out) {
+  chk(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2, "sample: logits must be [B, V]");
+  c10::cuda::CUDAGuard g(logits.device());
+  Tensor tok = tok_out.has_value() && tok_out->defined() ? *tok_out : torch::empty({logits.size(0)}, logits.options().dtype(torch::kLong));
+  Tensor lp = logp_out.has_value() && logp_out->defined() ? *logp_out : torch::empty({logits.size(0)}, logits.options().dtype(torch::kFloat));
+  ub::sample_full(logits.data_ptr(), logits.size(0), logits.size(1), (float)temperature, (uint64_t)seed, step,
+                  step_tensor.has_value() && step_tensor->defined() ? step_tensor->data_ptr<int64_t>() : nullptr, tok.data_ptr<int64_t>(),
+                  lp.data_ptr<float>(), dt(logits), stream());
+  return {tok, lp};
+}
+void adamw_step(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, c10::optional<Tensor> low, c10::optional<Tensor> ema, double lr, double b1,
+                double b2, double eps, double wd, int64_t step, double grad_scale, double ema_decay, const c10::optional<Tensor>& gst) {
+  chk(master, "master"); chk(grad, "grad"); chk(m, "exp_avg"); chk(v, "exp_avg_sq");
+  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "adamw: fp32 state expected");
+  TORCH_CHECK(grad.numel() == master.numel() && m.numel() == master.numel(), "adamw: size mismatch");
+  c10::cuda::CUDAGuard g(master.device());
+  const bool has_low = low.has_value() && low->defined(), has_ema = ema.has_value() && ema->defined();
+  if (has_low) { chk(*low, "low"); TORCH_CHECK(low->numel() == master.numel(), "adamw: low size"); }
+  ub::adamw_step(master.data_ptr<float>(), grad.data_ptr(), dt(grad), m.data_ptr<float>(), v.data_ptr<float>(), has_low ? low->data_ptr() : nullptr,
+                 has_low ? dt(*low) : ub::kF32, has_ema ? ema->data_ptr<float>() : nullptr, master.numel(), (float)lr, (float)b1, (float)b2, (float)eps,
+                 (float)wd, step, (float)grad_scale, gst.has_value() && gst->defined() ? gst->data_ptr<float>() : nullptr, (float)ema_decay, stream());
+}
+Tensor sum_squares(const Tensor& x) {
+  chk(x, "x");
+  c10::cuda::CUDAGuard g(x.device());
+  auto out = torch::zeros({}, x.options().dtype(torch::kFloat));
+  ub::sum_squares(x.data_ptr(), out.data_ptr<float>(), x.numel(), dt(x), stream());
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------------- SDE
+std::vector<Tensor> sde_sample_fwd(const Tensor& v, const Tensor& x, const Tensor& noise, const Tensor& ax, const Tensor& av, const Tensor& sd, int64_t mode) {
+  chk(v, "noise_pred"); chk(x, "sample"); chk(noise, "noise");
+  TORCH_CHECK(v.sizes() == x.sizes() && v.scalar_type() == x.scalar_type() && noise.scalar_type() == at::kFloat, "sde_sample: mismatch");
+  c10::cuda::CUDAGuard g(v.device());
+  const int64_t B = v.size(0), N = v.numel() / B;
+  auto f32 = v.options().dtype(torch::kFloat);
+  auto prev = torch::empty(v.sizes(), f32), mean = torch::empty(v.sizes(), f32), logp = torch::zeros({B}, f32);
+  ub::sde_sample_fwd(v.data_ptr(), x.data_ptr(), noise.data_ptr<float>(), ax.data_ptr<float>(), av.data_ptr<float>(), sd.data_ptr<float>(),
+                     prev.data_ptr<float>(), mean.data_ptr<float>(), logp.data_ptr<float>(), B, N, (int)mode, dt(v), stream());
+  return {prev, mean, logp};
+}
+std::vector<Tensor> sde_replay_fwd(const Tensor& v, const Tensor& x, const Tensor& prev, const Tensor& ax, const Tensor& av, const Tensor& sd, int64_t mode) {
+  chk(v, "noise_pred"); chk(x, "sample"); chk(prev, "prev_sample");
+  TORCH_CHECK(v.sizes() == x.sizes() && v.scalar_type() == x.scalar_type() && prev.scalar_type() == x.scalar_type(), "sde_replay: mismatch");
+  c10::cuda::CUDAGuard g(v.device());
+  const int64_t B = v.size(0), N = v.numel() / B;
+  auto f32 = v.options().dtype(torch::kFloat);
+  auto mean = torch::empty(v.sizes(), f32), logp = torch::zeros({B}, f32);
+  ub::sde_replay_fwd(v.data_ptr(), x.data_ptr(), prev.data_ptr(), ax.data_ptr<float>(), av.data_ptr<float>(), sd.data_ptr<float>(), mean.data_ptr<float>(),
+                     logp.data_ptr<float>(), B, N, (int)mode, dt(v), stream());
+  return {mean, logp};
+}
+Tensor sde_replay_bwd(const c10::optional<Tensor>& g_mean, const Tensor& g_logp, const Tensor& mean, const Tensor& prev, const Tensor& av,
+                      const Tensor& sd, int64_t mode) {
+  chk(mean, "mean");
+  c10::cuda::CUDAGuard g(mean.device());
+  auto prev32 = prev.to(torch::kFloat).contiguous();
+  const int64_t B = mean.size(0), N = mean.numel() / B;
+  auto gv = torch::empty_like(mean);
+  Tensor gm;
+  if (g_mean.has_value() && g_mean->defined()) gm = g_mean->to(torch::kFloat).contiguous();
+  ub::sde_replay_bwd(gm.defined() ? gm.data_ptr<float>() : nullptr, g_logp.data_ptr<float>(), mean.data_ptr<float>(), prev32.data_ptr<float>(),
+                     av.data_ptr<float>(), sd.data_ptr<float>(), gv.data_ptr<float>(), B, N, (int)mode, stream());
+  return gv;
+}
+
+// ---------------------------------------------------------------------------------------------- GEMM family
+Tensor gemm_bf16_tn(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& res, int64_t epilogue) {
+  chk(a, "a"); chk(b, "weight");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm: A [M,K] and B [N,K] expected");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: bf16 operands expected");
+  c10::cuda::CUDAGuard g(a.device());
+  const int64_t M = a.size(0), K = a.size(1);
+  const int64_t N = epilogue == ub::kEpiSwiGLU ? b.size(0) / 2 : b.size(0);
+  auto c = torch::empty({M, N}, a.options());
+  if (res.has_value() && res->defined()) { chk(*res, "residual"); TORCH_CHECK(res->sizes() == c.sizes(), "gemm: residual shape"); }
+  const int rc = ub::gemm_bf16_tn(a.data_ptr(), b.data_ptr(), c.data_ptr(), optr(res), (int)M, (int)N, (int)K, (int)K, (int)K, (int)N, (int)epilogue,
+                                  gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16_tn: unsupported shape or launch failure (code ", rc, ") for M=", M, " N=", N, " K=", K);
+  return c;
+}
+int64_t gemm_status(bool reset) {
+  auto& st = gemm_status_tensor();
+  const int64_t v = st.item<int>();
+  if (reset && v != 0) st.zero_();
+  return v;
+}
+std::vector<Tensor> linear_logprob_fwd(const Tensor& h, const Tensor& w, const Tensor& tgt, double temperature) {
+  chk(h, "hidden"); chk(w, "weight"); chk(tgt, "targets");
+  TORCH_CHECK(h.dim() == 2 && w.dim() == 2 && h.size(1) == w.size(1) && tgt.scalar_type() == at::kInt && tgt.numel() == h.size(0), "linear_logprob: shapes");
+  TORCH_CHECK(h.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "linear_logprob: bf16 operands expected");
+  c10::cuda::CUDAGuard g(h.device());
+  const int64_t M = h.size(0), V = w.size(0), K = h.size(1);
+  const int NT = ub::lse_num_tiles((int)V);
+  auto f32 = h.options().dtype(torch::kFloat);
+  auto pmax = torch::empty({M, NT}, f32), psum = torch::empty({M, NT}, f32), tl = torch::zeros({M}, f32);
+  auto lse = torch::empty({M}, f32), logp = torch::empty({M}, f32);
+  const int rc = ub::linear_lse(h.data_ptr(), w.data_ptr(), (int)M, (int)V, (int)K, (int)K, (int)K, tgt.data_ptr<int>(), (float)temperature,
+                                pmax.data_ptr<float>(), psum.data_ptr<float>(), tl.data_ptr<float>(), nullptr, nullptr, nullptr, 0, 0, nullptr,
+                                lse.data_ptr<float>(), logp.data_ptr<float>(), nullptr, gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "linear_logprob_fwd: launch failure (code ", rc, ")");
+  return {logp, lse};
+}
+std::vector<Tensor> linear_sample(const Tensor& h, const Tensor& w, double temperature, int64_t seed, int64_t step, const c10::optional<Tensor>& step_tensor) {
+  chk(h, "hidden"); chk(w, "weight");
+  TORCH_CHECK(h.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && h.size(1) == w.size(1), "linear_sample: bf16 [M,K] x [V,K]");
+  c10::cuda::CUDAGuard g(h.device());
+  const int64_t M = h.size(0), V = w.size(0), K = h.size(1);
+  const int NT = ub::lse_num_tiles((int)V);
+  auto f32 = h.options().dtype(torch::kFloat);
+  auto pmax = torch::empty({M, NT}, f32), psum = torch::empty({M, NT}, f32), pb = torch::empty({M, NT}, f32), pz = torch::empty({M, NT}, f32);
+  auto pi = torch::empty({M, NT}, h.options().dtype(torch::kInt));
+  auto tok = torch::empty({M}, h.options().dtype(torch::kLong));
+  auto logp = torch::empty({M}, f32);
+  const int rc = ub::linear_lse(h.data_ptr(), w.data_ptr(), (int)M, (int)V, (int)K, (int)K, (int)K, nullptr, (float)temperature, pmax.data_ptr<float>(),
+                                psum.data_ptr<float>(), nullptr, pb.data_ptr<float>(), pi.data_ptr<int>(), pz.data_ptr<float>(), (uint64_t)seed, step,
+                                step_tensor.has_value() && step_tensor->defined() ? step_tensor->data_ptr<int64_t>() : nullptr, nullptr,
+                                logp.data_ptr<float>(), tok.data_ptr<int64_t>(), gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "linear_sample: launch failure (code ", rc, ")");
+  return {tok, logp};
+}
+
+// ---------------------------------------------------------------------------------------------- decode attention
+int64_t decode_workspace_size(int64_t B, int64_t Hq, int64_t D, int64_t max_kv_len) {
+  // upper bound over every split count the heuristic may pick for this batch
+  return ub::decode_workspace_floats((int)B, (int)Hq, (int)D, 32);
+}
+Tensor paged_decode_attention(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& bt, const Tensor& sl, double scale,
+                              c10::optional<Tensor> workspace, int64_t max_kv_len) {
+  chk(q, "q"); chk(kc, "k_cache"); chk(vc, "v_cache"); chk(bt, "block_tables"); chk(sl, "seq_lens");
+  TORCH_CHECK(q.dim() == 3 && kc.dim() == 4 && q.scalar_type() == at::kBFloat16 && kc.scalar_type() == at::kBFloat16, "decode attention: bf16 q [B,Hq,D], cache [P,Hkv,page,D]");
+  TORCH_CHECK(bt.scalar_type() == at::kInt && sl.scalar_type() == at::kInt, "decode attention: int32 block_tables / seq_lens");
+  c10::cuda::CUDAGuard g(q.device());
+  const int B = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)kc.size(1), page = (int)kc.size(2);
+  const int kv_hint = max_kv_len > 0 ? (int)max_kv_len : (int)(bt.size(1) * page);
+  const int splits = ub::decode_num_splits(B, Hkv, kv_hint);
+  const int64_t need = ub::decode_workspace_floats(B, Hq, D, splits);
+  Tensor ws = workspace.has_value() && workspace->defined() && workspace->numel() >= need ? *workspace
+                                                                                           : torch::empty({need}, q.options().dtype(torch::kFloat));
+  auto out = torch::empty_like(q);
+  const int rc = ub::paged_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr<int>(), sl.data_ptr<int>(), out.data_ptr(),
+                                            ws.data_ptr<float>(), B, Hq, Hkv, D, page, (int)bt.size(1), splits, (float)scale, stream());
+  TORCH_CHECK(rc == 0, "paged_decode_attention: unsupported configuration or launch failure (code ", rc, ")");
+  return out;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "unirl_b200 native kernels (sm_100a)";
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("layernorm_modulate_fwd", &layernorm_modulate_fwd);
+  m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
+  m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("kv_cache_write", &kv_cache_write);
+  m.def("policy_loss_fwd", &policy_loss_fwd);
+  m.def("mean_sq_diff_rows", &mean_sq_diff_rows);
+  m.def("logprob_dlogits_inplace", &logprob_dlogits_inplace);
+  m.def("sample_full", &sample_full);
+  m.def("adamw_step", &adamw_step);
+  m.def("sum_squares", &sum_squares);
+  m.def("sde_sample_fwd", &sde_sample_fwd);
+  m.def("sde_replay_fwd", &sde_replay_fwd);
+  m.def("sde_replay_bwd", &sde_replay_bwd);
+  m.def("gemm_bf16_tn", &gemm_bf16_tn);
+  m.def("gemm_status", &gemm_status, py::arg("reset") = true);
+  m.def("linear_logprob_fwd", &linear_logprob_fwd);
+  m.def("linear_sample", &linear_sample);
+  m.def("decode_workspace_size", &decode_workspace_size);
+  m.def("paged_decode_attention", &paged_decode_attention);
+  py::class_<ub::BlockAllocator>(m, "BlockAllocator")
+      .def(py::init<int64_t>())
+      .def("reset", &ub::BlockAllocator::reset)
+      .def("allocate", &ub::BlockAllocator::allocate)
+      .def("free", &ub::BlockAllocator::free)
+      .def_property_readonly("num_free", &ub::BlockAllocator::num_free)
+      .def_property_readonly("num_pages", &ub::BlockAllocator::num_pages);
+}

@@ -1,0 +1,462 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a:  C[M,N] = A[M,K] · B[N,K]ᵀ  (both operands K-major),
+// fp32 accumulation in TMEM, operands staged by TMA into 128-byte-swizzled shared memory.
+//
+//   warp 0      TMA producer   (one lane): waits `empty[s]`, arms `full[s]` with the byte count, issues 2-3 tile loads
+//   warp 1      MMA issuer     (one lane): waits `full[s]`, issues 4 x tcgen05.mma (K = 16 each) per 64-wide k-block,
+//                                          commits `empty[s]`; after the last k-block commits `tmem_full[buf]`
+//   warps 2..5  epilogue       (128 thr):  wait `tmem_full[buf]`, tcgen05.ld 32x32b.x32 chunks, fused epilogue, global stores,
+//                                          then release `tmem_empty[buf]`
+//
+// Two TMEM accumulator buffers (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
+// Epilogues:  STORE (bf16 C) | RESIDUAL (C = acc + R) | SWIGLU (acc = [gate | up] -> silu(gate)·up) |
+//             LSE (per-row partial max / sum-exp / target logit / Gumbel-arg-max of acc/T; logits never leave the SM).
+//
+// Every mbarrier wait is bounded; on expiry the role records a code in `status[0]` and all roles drain out,
+// TMEM is released and the kernel returns.
+#include "common.cuh"
+#include "ops.h"
+#include "tcgen05.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace ub {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K;            // N = number of OUTPUT columns of C (for SWIGLU: I; B has 2I rows)
+  int num_m_tiles, num_n_tiles;
+  bf16* C;                // [M, ldc]
+  const bf16* R;          // residual [M, ldc] or null
+  int ldc;
+  int up_row_offset;      // SWIGLU: row offset of the "up" block inside B
+  // LSE epilogue
+  const int* targets;     // [M] or null
+  float inv_temp;
+  float* pmax;            // [M, num_n_tiles]
+  float* psum;            // [M, num_n_tiles]
+  float* tgt_logit;       // [M]  (scaled by inv_temp)
+  float* pbest;           // [M, num_n_tiles] Gumbel score (null => no sampling)
+  int* pbest_idx;         // [M, num_n_tiles]
+  float* pbest_z;         // [M, num_n_tiles] scaled logit at the partial arg-max
+  uint64_t seed;
+  const int64_t* step_tensor;
+  int64_t step;
+  int* status;            // [1] error word (0 = ok)
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kTotal = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void report(int* status, int code) {
+  if (status) atomicCAS(status, 0, code);
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = SmemLayout<BN>;
+  constexpr int kStages = L::kStages;
+  constexpr uint32_t kTmemCols = (2 * BN >= 32) ? 2 * BN : 32;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kTileBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* tfull = bars + 2 * kStages;
+  uint64_t* tempty = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull + b, 1);
+      mbar_init(tempty + b, 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.num_m_tiles) * BM;
+        const int n_idx = tile / p.num_m_tiles;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty + stage, phase ^ 1)) {
+            report(p.status, 101);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * L::kStageBytes;
+          uint8_t* sB = sA + L::kABytes;
+          mbar_expect_tx(full + stage, L::kStageBytes);
+          tma_load_2d(sA, &tmA, kb * BK, m0, full + stage);
+          if (EPI == kEpiSwiGLU) {
+            const int n0 = n_idx * (BN / 2);
+            tma_load_2d(sB, &tmB, kb * BK, n0, full + stage);
+            tma_load_2d(sB + L::kBBytes / 2, &tmB, kb * BK, p.up_row_offset + n0, full + stage);
+          } else {
+            tma_load_2d(sB, &tmB, kb * BK, n_idx * BN, full + stage);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!mbar_wait(tempty + buf, ((it >> 1) & 1) ^ 1)) {
+          report(p.status, 102);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_addr = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full + stage, phase)) {
+            report(p.status, 103);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint8_t* sA = smem + stage * L::kStageBytes;
+          const uint64_t da = make_desc_kmajor_sw128(sA);
+          const uint64_t db = make_desc_kmajor_sw128(sA + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) umma_bf16(d_addr, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(empty + stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(tfull + buf);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int m0 = (tile % p.num_m_tiles) * BM;
+      const int n_idx = tile / p.num_m_tiles;
+      if (!mbar_wait(tfull + buf, (it >> 1) & 1)) {
+        report(p.status, 104);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(q * 32) << 16);
+
+      if (EPI == kEpiStore || EPI == kEpiResidual) {
+        const int n0 = n_idx * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float acc[32];
+          tmem_ld_32x32(t_row + c0, acc);
+          tmem_ld_wait();
+          if (row_ok) {
+            bf16* crow = p.C + static_cast<int64_t>(row) * p.ldc + n0 + c0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (n0 + c0 + g * 8 < p.N) {
+                if (EPI == kEpiResidual) {
+                  float r[8];
+                  load8(p.R + static_cast<int64_t>(row) * p.ldc + n0 + c0 + g * 8, r);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) acc[g * 8 + j] += r[j];
+                }
+                store8(crow + g * 8, acc + g * 8);
+              }
+            }
+          }
+        }
+      } else if (EPI == kEpiSwiGLU) {
+        const int n0 = n_idx * (BN / 2);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+          float gate[32], up[32];
+          tmem_ld_32x32(t_row + c0, gate);
+          tmem_ld_32x32(t_row + BN / 2 + c0, up);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) gate[j] = gate[j] / (1.f + __expf(-gate[j])) * up[j];
+            bf16* crow = p.C + static_cast<int64_t>(row) * p.ldc + n0 + c0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              if (n0 + c0 + g * 8 < p.N) store8(crow + g * 8, gate + g * 8);
+          }
+        }
+      } else {  // kEpiLSE
+        const int n0 = n_idx * BN;
+        const int tgt = (row_ok && p.targets) ? p.targets[row] : -1;
+        const bool sampling = p.pbest != nullptr;
+        const uint64_t stp = static_cast<uint64_t>(p.step_tensor ? *p.step_tensor : p.step);
+        float mx = -INFINITY, sum = 0.f, best = -INFINITY, best_z = 0.f;
+        int best_i = 0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float acc[32];
+          tmem_ld_32x32(t_row + c0, acc);
+          tmem_ld_wait();
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            acc[j] = (n0 + c0 + j < p.N) ? acc[j] * p.inv_temp : -INFINITY;
+            cmax = fmaxf(cmax, acc[j]);
+          }
+          if (cmax > -INFINITY) {
+            const float nm = fmaxf(mx, cmax);
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s += __expf(acc[j] - nm);
+            sum = sum * __expf(mx - nm) + s;
+            mx = nm;
+          }
+          if (tgt >= n0 + c0 && tgt < n0 + c0 + 32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j == tgt) p.tgt_logit[row] = acc[j];
+          }
+          if (sampling && row_ok) {
+#pragma unroll
+            for (int j4 = 0; j4 < 32; j4 += 4) {
+              const int col = n0 + c0 + j4;
+              const uint4 rnd = philox4x32(make_uint4(static_cast<uint32_t>(col >> 2), static_cast<uint32_t>(row), static_cast<uint32_t>(stp),
+                                                      static_cast<uint32_t>(stp >> 32)),
+                                           make_uint2(static_cast<uint32_t>(p.seed), static_cast<uint32_t>(p.seed >> 32)));
+              const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float score = acc[j4 + j] - __logf(-__logf(u01(rr[j])));
+                if (score > best) {
+                  best = score;
+                  best_i = col + j;
+                  best_z = acc[j4 + j];
+                }
+              }
+            }
+          }
+        }
+        if (row_ok) {
+          const int64_t o = static_cast<int64_t>(row) * p.num_n_tiles + n_idx;
+          p.pmax[o] = mx;
+          p.psum[o] = sum;
+          if (sampling) {
+            p.pbest[o] = best;
+            p.pbest_idx[o] = best_i;
+            p.pbest_z[o] = best_z;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty + buf);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Fold per-tile partials:  lse = log Σ_t psum_t·exp(pmax_t − gmax) + gmax ;  logp = tgt_logit − lse ;  optional sampled token.
+__global__ void lse_merge_kernel(const float* __restrict__ pmax, const float* __restrict__ psum, const float* __restrict__ tgt_logit,
+                                 const float* __restrict__ pbest, const int* __restrict__ pbest_idx, const float* __restrict__ pbest_z, int M, int NT,
+                                 float* __restrict__ lse_out, float* __restrict__ logp_out, int64_t* __restrict__ tok_out) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float m = -INFINITY;
+  for (int t = lane; t < NT; t += 32) m = fmaxf(m, pmax[(int64_t)row * NT + t]);
+  m = warp_max(m);
+  float s = 0.f;
+  for (int t = lane; t < NT; t += 32) s += psum[(int64_t)row * NT + t] * __expf(pmax[(int64_t)row * NT + t] - m);
+  s = warp_sum(s);
+  const float lse = m + logf(s);
+  float best = -INFINITY, bz = 0.f;
+  int bi = 0x7fffffff;
+  if (pbest) {
+    for (int t = lane; t < NT; t += 32) {
+      const float b = pbest[(int64_t)row * NT + t];
+      const int i = pbest_idx[(int64_t)row * NT + t];
+      if (b > best || (b == best && i < bi)) {
+        best = b;
+        bi = i;
+        bz = pbest_z[(int64_t)row * NT + t];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      const float oz = __shfl_xor_sync(0xffffffffu, bz, o);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+        bz = oz;
+      }
+    }
+  }
+  if (lane == 0) {
+    if (lse_out) lse_out[row] = lse;
+    if (pbest) {
+      tok_out[row] = bi;
+      logp_out[row] = bz - lse;
+    } else if (logp_out) {
+      logp_out[row] = tgt_logit[row] - lse;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+// Row-major bf16 matrix [rows, cols] (cols contiguous, leading dimension ld elements), tiles of [box_rows, 64] with 128B swizzle.
+bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int EPI>
+static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t s) {
+  using L = SmemLayout<BN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return 2;
+    configured = true;
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, L::kTotal, s>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+// C[M,N] = A[M,K]·B[N,K]ᵀ (+R).  Returns 0 on success, non-zero when the shape/alignment is unsupported (caller falls back).
+int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
+                 cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) || (N % 8) || (ldc % 8)) return 1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = static_cast<bf16*>(C); p.R = static_cast<const bf16*>(R); p.ldc = ldc; p.status = status;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  CUtensorMap tmA, tmB;
+  if (!make_tensor_map_bf16(&tmA, A, M, K, lda, BM)) return 1;
+  if (epilogue == kEpiSwiGLU) {
+    // B = [gate; up] with N rows each; output tile of 128 columns uses a 256-column accumulator.
+    constexpr int BN = 256;
+    p.num_n_tiles = (N + BN / 2 - 1) / (BN / 2);
+    p.up_row_offset = N;
+    if (!make_tensor_map_bf16(&tmB, B, 2 * (int64_t)N, K, ldb, BN / 2)) return 1;
+    return launch_variant<BN, kEpiSwiGLU>(tmA, tmB, p, s);
+  }
+  const bool wide = N >= 256 * 2 || N % 256 == 0;
+  const int BN = wide ? 256 : 128;
+  p.num_n_tiles = (N + BN - 1) / BN;
+  if (!make_tensor_map_bf16(&tmB, B, N, K, ldb, BN)) return 1;
+  if (epilogue == kEpiResidual) return wide ? launch_variant<256, kEpiResidual>(tmA, tmB, p, s) : launch_variant<128, kEpiResidual>(tmA, tmB, p, s);
+  return wide ? launch_variant<256, kEpiStore>(tmA, tmB, p, s) : launch_variant<128, kEpiStore>(tmA, tmB, p, s);
+}
+
+int lse_num_tiles(int V) { return (V + 255) / 256; }
+
+// Fused vocab projection + log-softmax statistics.  Workspace: pmax/psum [M, NT] (+ pbest/pbest_idx/pbest_z when sampling).
+int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int ldw, const int* targets, float temperature, float* pmax, float* psum,
+               float* tgt_logit, float* pbest, int* pbest_idx, float* pbest_z, uint64_t seed, int64_t step, const int64_t* step_tensor,
+               float* lse_out, float* logp_out, int64_t* tok_out, int* status, cudaStream_t s) {
+  if (M <= 0) return 0;
+  if (K % 8) return 1;
+  constexpr int BN = 256;
+  GemmParams p{};
+  p.M = M; p.N = V; p.K = K; p.status = status;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  p.num_n_tiles = lse_num_tiles(V);
+  p.targets = targets; p.inv_temp = 1.f / temperature; p.pmax = pmax; p.psum = psum; p.tgt_logit = tgt_logit;
+  p.pbest = pbest; p.pbest_idx = pbest_idx; p.pbest_z = pbest_z; p.seed = seed; p.step = step; p.step_tensor = step_tensor;
+  CUtensorMap tmA, tmB;
+  if (!make_tensor_map_bf16(&tmA, H, M, K, ldh, BM) || !make_tensor_map_bf16(&tmB, W, V, K, ldw, BN)) return 1;
+  const int rc = launch_variant<BN, kEpiLSE>(tmA, tmB, p, s);
+  if (rc) return rc;
+  lse_merge_kernel<<<(M + 7) / 8, 256, 0, s>>>(pmax, psum, tgt_logit, pbest, pbest_idx, pbest_z, M, p.num_n_tiles, lse_out, logp_out, tok_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace ub

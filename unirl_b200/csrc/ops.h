@@ -1,0 +1,63 @@
+// Launcher declarations shared by the .cu translation units and bindings.cpp.
+// dtype codes: 0 = fp32, 1 = bf16.  All launchers enqueue on the given stream and never synchronise.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ub {
+
+constexpr int kF32 = 0;
+constexpr int kBF16 = 1;
+
+constexpr int kEpiStore = 0;
+constexpr int kEpiResidual = 1;
+constexpr int kEpiSwiGLU = 2;
+constexpr int kEpiLSE = 3;
+
+// ---- elementwise.cu ----------------------------------------------------------------------------------
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t R, int D, float eps, int dtype, cudaStream_t s);
+void add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, int64_t R, int D, float eps, int dtype, cudaStream_t s);
+void rmsnorm_bwd(const void* gy, const void* x, const void* w, const float* rstd, void* gx, float* gw, int64_t R, int D, int dtype, cudaStream_t s);
+void layernorm_modulate_fwd(const void* x, const void* shift, const void* scale, void* y, int64_t B, int L, int D, float eps, int dtype, cudaStream_t s);
+void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, float* rstd,
+                      int64_t T, int Hq, int Hkv, int D, float eps, int dtype, cudaStream_t s);
+void qk_norm_rope_bwd(const void* gq, const void* gk, const void* gv, const void* qkv, const void* qw, const void* kw, const int* pos,
+                      const float* inv_freq, const float* rstd, void* g_qkv, float* g_qw, float* g_kw, int64_t T, int Hq, int Hkv, int D, int dtype,
+                      cudaStream_t s);
+void swiglu_fwd(const void* gu, void* out, int64_t rows, int I, int dtype, cudaStream_t s);
+void swiglu_bwd(const void* gy, const void* gu, void* g_gu, int64_t rows, int I, int dtype, cudaStream_t s);
+void kv_cache_write(const void* k, const void* v, void* kc, void* vc, const int64_t* slots, int64_t T, int Hkv, int D, int page_size, int dtype,
+                    cudaStream_t s);
+void policy_loss_fwd(const float* newlp, const float* oldlp, const float* adv, const uint8_t* keep, float* loss, float* dloss, float* stats, int64_t n,
+                     int kind, float p0, float p1, cudaStream_t s);
+void mean_sq_diff_rows(const void* a, const void* b, float* out, int64_t R, int64_t C, int dtype, cudaStream_t s);
+void logprob_dlogits_inplace(void* z, const int* tgt, const float* lse, const float* g, int64_t R, int64_t V, float temperature, int dtype,
+                             cudaStream_t s);
+void sample_full(const void* logits, int64_t B, int64_t V, float temperature, uint64_t seed, int64_t step, const int64_t* step_tensor, int64_t* tok,
+                 float* logp, int dtype, cudaStream_t s);
+void adamw_step(float* master, const void* grad, int grad_dtype, float* m, float* v, void* low, int low_dtype, float* ema, int64_t n, float lr, float b1,
+                float b2, float eps, float wd, int64_t step, float grad_scale, const float* grad_scale_tensor, float ema_decay, cudaStream_t s);
+void sum_squares(const void* x, float* out, int64_t n, int dtype, cudaStream_t s);
+void sde_sample_fwd(const void* v, const void* x, const float* noise, const float* a_x, const float* a_v, const float* stdv, float* prev, float* mean,
+                    float* logp, int64_t B, int64_t N, int mode, int dtype, cudaStream_t s);
+void sde_replay_fwd(const void* v, const void* x, const void* prev, const float* a_x, const float* a_v, const float* stdv, float* mean, float* logp,
+                    int64_t B, int64_t N, int mode, int dtype, cudaStream_t s);
+void sde_replay_bwd(const float* g_mean, const float* g_logp, const float* mean, const float* prev, const float* a_v, const float* stdv, float* g_v,
+                    int64_t B, int64_t N, int mode, cudaStream_t s);
+
+// ---- gemm_tcgen05.cu -------------------------------------------------------------------------------------
+int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
+                 cudaStream_t s);
+int lse_num_tiles(int V);
+int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int ldw, const int* targets, float temperature, float* pmax, float* psum,
+               float* tgt_logit, float* pbest, int* pbest_idx, float* pbest_z, uint64_t seed, int64_t step, const int64_t* step_tensor, float* lse_out,
+               float* logp_out, int64_t* tok_out, int* status, cudaStream_t s);
+
+// ---- attention_decode.cu -----------------------------------------------------------------------------------
+int decode_num_splits(int B, int Hkv, int max_kv_len);
+int64_t decode_workspace_floats(int B, int Hq, int D, int num_splits);
+int paged_decode_attention(const void* q, const void* kc, const void* vc, const int* block_tables, const int* seq_lens, void* out, float* workspace,
+                           int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, cudaStream_t s);
+
+}  // namespace ub

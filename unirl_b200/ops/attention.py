@@ -41,6 +41,21 @@ def varlen_attention_reference(q, k, v, cu_seqlens, causal: bool = True, scale: 
     return out
 
 
+def _varlen_impl() -> str:
+    """``native`` when the extension carries the varlen kernels, else the ``flash_attn`` library kernels.
+
+    The library path is a stop-gap for the packed prefill / training attention only; decode attention,
+    which dominates rollout time, is always the native paged kernel.
+    """
+    want = os.environ.get("UNIRL_B200_VARLEN_ATTN", "auto")
+    C = require_ext()
+    if want in ("auto", "native") and hasattr(C, "attn_varlen_fwd"):
+        return "native"
+    if want == "native":
+        raise RuntimeError("UNIRL_B200_VARLEN_ATTN=native but the extension has no attn_varlen_fwd")
+    return "library"
+
+
 class _VarlenAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
@@ -63,13 +78,24 @@ class _VarlenAttention(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
+def _library_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale):
+    from flash_attn import flash_attn_varlen_func
+
+    cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
+    return flash_attn_varlen_func(q, k, v, cu, cu, int(max_seqlen), int(max_seqlen), 0.0, softmax_scale=float(scale), causal=bool(causal))
+
+
 def varlen_attention(q, k, v, cu_seqlens, max_seqlen: Optional[int] = None, causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
     """Self attention over packed sequences (GQA when ``Hq > Hkv``)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if use_native(q):
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
-        return _VarlenAttention.apply(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        if q.dtype not in (torch.bfloat16, torch.float16):
+            return varlen_attention_reference(q, k, v, cu_seqlens, causal, scale)
+        if _varlen_impl() == "native":
+            return _VarlenAttention.apply(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        return _library_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
     return varlen_attention_reference(q, k, v, cu_seqlens, causal, scale)
 
 
@@ -109,7 +135,7 @@ def paged_decode_attention(q, k_cache, v_cache, block_tables, seq_lens, scale: O
     ``workspace`` (fp32) holds the split partials so a captured CUDA graph allocates nothing.
     """
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if use_native(q):
+    if use_native(q) and q.dtype == torch.bfloat16:
         out = require_ext().paged_decode_attention(q.contiguous(), k_cache, v_cache, block_tables, seq_lens, float(scale), workspace,
                                                    int(max_seq_len or 0))
         count_launch(2)

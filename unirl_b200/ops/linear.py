@@ -16,7 +16,9 @@ import torch.nn.functional as F
 
 from unirl_b200.ops._ext import count_launch, ext, require_ext, use_native
 
-_MIN_NATIVE_M = int(os.environ.get("UNIRL_B200_GEMM_MIN_M", "1"))
+# Skinny (decode-shaped) GEMMs are weight-bandwidth bound and go to the library GEMM; the tcgen05 kernel takes the
+# compute-bound shapes (prefill, training forward) where its 128x256 tiles fill the machine.
+_MIN_NATIVE_M = int(os.environ.get("UNIRL_B200_GEMM_MIN_M", "512"))
 
 
 def _native_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:

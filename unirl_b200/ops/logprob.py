@@ -64,7 +64,7 @@ class _LinearLogprob(torch.autograd.Function):
 
 def linear_logprob(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
     """fp32 ``[T]`` log-probs of ``targets`` under ``softmax(hidden·weightᵀ / temperature)``."""
-    if use_native(hidden):
+    if use_native(hidden) and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and hidden.shape[1] % 8 == 0:
         return _LinearLogprob.apply(hidden, weight, targets, temperature)
     return _CheckpointedReference.apply(hidden, weight, targets, float(temperature))
 

@@ -55,4 +55,18 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p
     return sample_reference(logits, temperature, top_k or 0, top_p, generator)
 
 
-__all__ = ["sample", "sample_reference"]
+def linear_sample(hidden: torch.Tensor, weight: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0,
+                  step: int = 0, step_tensor: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None):
+    """``sample(hidden @ weight.T)`` — on CUDA (bf16, untruncated, T > 0) the vocab projection, the log-sum-exp and the
+    Gumbel-max draw run inside ONE tcgen05 GEMM epilogue: the ``[B, vocab]`` logits never reach HBM."""
+    fused = (use_native(hidden) and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and temperature > 0
+             and (top_k in (0, None) or top_k >= weight.shape[0]) and top_p >= 1.0 and hidden.shape[1] % 8 == 0)
+    if fused:
+        tok, lp = require_ext().linear_sample(hidden.contiguous(), weight, float(temperature), int(seed), int(step), step_tensor)
+        count_launch(2)
+        return tok, lp
+    logits = torch.nn.functional.linear(hidden, weight)
+    return sample(logits, temperature, top_k, top_p, seed=seed, step=step, generator=generator, step_tensor=step_tensor)
+
+
+__all__ = ["sample", "sample_reference", "linear_sample"]

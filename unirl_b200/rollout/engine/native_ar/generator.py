@@ -123,7 +123,7 @@ class ARGenerator:
         # -- decode state (all device resident) ---------------------------------------------------------
         st = _DecodeState(b, max_new, dev)
         st.positions.copy_(torch.tensor(plens, dtype=torch.long))  # index at which the next fed token is written
-        first_tok, first_lp = self._sample(self.model.logits(last_hidden), temperature, top_k, top_p, seed, 0, st)
+        first_tok, first_lp = self._sample(last_hidden, temperature, top_k, top_p, seed, 0, st)
         st.record(first_tok, first_lp, stop)
         meta = AttnMeta(mode="decode", positions=st.positions, k_cache=cache.k, v_cache=cache.v, block_tables=block_tables,
                         seq_lens=st.seq_lens, slot_mapping=st.slots, max_kv_len=max(plens) + max_new)
@@ -138,7 +138,7 @@ class ARGenerator:
         def step() -> None:
             st.prepare(block_tables, ps)
             hidden = self.model(st.cur_tokens, meta)
-            tok, lp = self._sample(self.model.logits(hidden), temperature, top_k, top_p, seed, None, st)
+            tok, lp = self._sample(hidden, temperature, top_k, top_p, seed, None, st)
             st.record(tok, lp, stop)
             st.positions.add_(1)
 
@@ -170,12 +170,14 @@ class ARGenerator:
         hidden = self.model(tokens, meta)
         out_last.copy_(hidden[(cu[1:].long() - 1).to(dev)])
 
-    def _sample(self, logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, step: Optional[int], st: "_DecodeState"):
-        if logits.is_cuda:
-            return S.sample(logits, temperature, top_k, top_p, seed=seed, step=0 if step is None else step, step_tensor=st.step_counter)
+    def _sample(self, hidden: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, step: Optional[int], st: "_DecodeState"):
+        """Vocab projection + sampling of the last hidden states (fused on CUDA; see ``ops.sampling.linear_sample``)."""
+        w = self.model.output_weight
+        if hidden.is_cuda:
+            return S.linear_sample(hidden, w, temperature, top_k, top_p, seed=seed, step=0 if step is None else step, step_tensor=st.step_counter)
         if st.cpu_gen is None:
             st.cpu_gen = torch.Generator().manual_seed(seed)
-        return S.sample_reference(logits, temperature, top_k, top_p, st.cpu_gen)
+        return S.sample_reference(torch.nn.functional.linear(hidden, w), temperature, top_k, top_p, st.cpu_gen)
 
     def _graphed(self, step_fn, b: int, max_new: int, temperature: float, top_k: int, top_p: float):
         """Capture ``step_fn`` (which closes over this wave's state tensors) into a CUDA graph."""
