@@ -181,7 +181,7 @@ def test_sde_step_matches_strategy(name):
     noise = torch.randn(x.shape, device="cuda")
     prev, lp, mean = sde_step(st, v, x, sig[2], sig[3], eta=0.7, noise=noise)
     rprev, rlp, rmean = st.denoise(v.detach(), x, sig[2], sig[3], eta=0.7, noise=noise)
-    _close(prev, rprev, 1e-5, 1e-5, "prev")
+    _close(prev, rprev, 2e-2, 1e-2, "prev (one bf16 ulp of storage rounding allowed)")
     _close(mean, rmean, 1e-5, 1e-5, "mean")
     _close(lp, rlp, 1e-3, 1e-3, "logp")
     stored = prev.to(torch.bfloat16)
