@@ -203,7 +203,8 @@ def main() -> None:
                "clocks": clocks,
                "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": rows[-1]["h2d"], "d2h_bytes_per_step": rows[-1]["d2h"],
                        "ms_per_step": wall_ms / args.steps},
-               "gpu_launches": int(launches), "loss": rows[-1]["loss"], "device_span_ms_per_step": span_ms / args.steps}
+               "gpu_launches": int(launches), "loss": rows[-1]["loss"],
+               "phases_device_ms_last_step": {k: round(v, 2) for k, v in rows[-1]["device_ms"].items()}, "device_span_ms_per_step": span_ms / args.steps}
         print(json.dumps(out))
     trainer.shutdown()
 

@@ -143,7 +143,10 @@ class ARGenerator:
             st.positions.add_(1)
 
         n_steps = 1
-        runner = self._graphed(step, b, max_new, temperature, top_k, top_p) if self.use_cuda_graph and max_new > 1 else step
+        if max_new > 1:
+            step()  # first decode step runs eagerly: one-time kernel attribute / library workspace set-up must not happen under capture
+            n_steps = 2
+        runner = self._graphed(step, b, max_new, temperature, top_k, top_p) if self.use_cuda_graph and max_new > 2 else step
         while n_steps < max_new:
             burst = min(self.poll_interval, max_new - n_steps)
             for _ in range(burst):
@@ -184,8 +187,7 @@ class ARGenerator:
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
-        # no warm-up run: the step has side effects on the decode state; kernels were already
-        # exercised by prefill / first-token sampling, and capture itself does not execute.
+        # capture itself does not execute the step, so the decode state is not advanced here
         with torch.cuda.graph(g, stream=s):
             step_fn()
         self._graphs[(b, max_new, temperature, top_k, top_p)] = g  # keep alive for the wave
