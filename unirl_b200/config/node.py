@@ -50,11 +50,13 @@ class ConfigNode:
             name, default = _split_top_comma(body)
             val = os.environ.get(name.strip())
             if val is not None:
-                return _parse_scalar(val) if not isinstance(val, str) else val
+                return val
             if default is _MISSING:
                 raise KeyError(f"environment variable '{name.strip()}' is not set and has no default")
             d = self._resolve_str(default.strip())
-            return _parse_scalar(d) if isinstance(d, str) else d
+            if isinstance(d, str) and d.lower() in ("null", "none", "~"):
+                return None
+            return d if d is None else str(d)
         if expr.startswith("oc.select:"):
             name, default = _split_top_comma(expr[len("oc.select:"):])
             try:
@@ -109,10 +111,9 @@ class ConfigNode:
     def __getattr__(self, key: str) -> Any:
         if key.startswith("__"):
             raise AttributeError(key)
-        try:
-            return self[key]
-        except KeyError:
-            raise AttributeError(f"config has no key '{key}'") from None
+        if key not in self._data:
+            raise AttributeError(f"config has no key '{key}'")
+        return self[key]
 
     def __setattr__(self, key: str, value: Any) -> None:
         self._data[key] = to_container(value)

@@ -2,9 +2,10 @@
 //
 // Grid (split, kv_head, sequence); 4 warps per CTA.  The G = Hq/Hkv query heads that share a KV head are
 // packed as the (zero-padded) 16 rows of the mma.sync A operand, so every K/V byte fetched from HBM is used
-// by all G heads.  Each warp owns a private double-buffered 32-token K/V tile (cp.async, XOR-swizzled rows)
-// and its own online-softmax state, so the main loop has no block-level synchronisation; warps are merged
-// once through shared memory and splits once through an fp32 workspace by a second tiny kernel.
+// by all G heads.  Each warp owns a private 3-stage ring of 32-token K/V tiles (cp.async, XOR-swizzled rows; one
+// base pointer per tile when a tile lies inside a page, so a copy costs a single add) and its own online-softmax
+// state, so the main loop has no block-level synchronisation; warps are merged once through shared memory and
+// splits once through an fp32 workspace by a second tiny kernel.
 // The kernel is HBM-bound by construction: ~1 tensor-core instruction per 128 bytes of KV.
 #include "mma.cuh"
 #include "ops.h"
@@ -13,37 +14,74 @@ namespace ub {
 
 constexpr int kDecTile = 32;    // tokens per warp tile
 constexpr int kDecWarps = 4;
-constexpr int kDecStages = 2;
+constexpr int kDecStages = 3;   // two tiles in flight per warp while one is consumed
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Tiles are row-major [32][D] bf16 with the 16-byte chunks of a row XOR-swizzled by (row & 7): conflict-free ldmatrix.
 template <int D>
-__device__ __forceinline__ void dec_load_tile(bf16* sK, bf16* sV, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
-                                              const int* __restrict__ bt_row, int tile, int seq_len, int h, int Hkv, int page_size, int lane) {
+struct DecLayout {
+  static constexpr int kTileBytes = kDecTile * D * 2;              // one K (or V) tile
+  static constexpr int kStageBytes = 2 * kTileBytes;               // K + V
+  static constexpr int kWarpBytes = kDecStages * kStageBytes;
+  static constexpr int kTotal = kDecWarps * kWarpBytes;
+};
+
+template <int D>
+__device__ __forceinline__ uint32_t dec_swz(int row, int chunk) {  // byte offset inside a tile
+  return static_cast<uint32_t>(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Issue the cp.async copies of one 32-token K/V tile.  kFast: the tile lies inside one page (page_size % 32 == 0), so
+// a single base pointer serves the whole tile and each copy costs one add; otherwise pages are looked up per row.
+template <int D, bool kFast>
+__device__ __forceinline__ void dec_issue_tile(uint32_t sK, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ bt_row,
+                                               int tile, int seq_len, int h, int Hkv, int page_size, int lane) {
+  using L = DecLayout<D>;
   constexpr int kChunks = D / 8;
-  constexpr int kIters = kDecTile * kChunks / 32;
+  constexpr int kRowsPerIter = 32 / kChunks;           // rows covered by one warp-wide copy instruction
+  constexpr int kIters = kDecTile / kRowsPerIter;
+  const int n_valid = seq_len - tile * kDecTile;       // rows >= n_valid are zero-filled
+  const int sub_row = lane / kChunks, chunk = lane % kChunks;
+  if (kFast) {
+    const int tok0 = tile * kDecTile;
+    const int64_t page = bt_row[tok0 / page_size];
+    const int64_t base = ((page * Hkv + h) * page_size + (tok0 % page_size)) * D + lane * 8;
+    const bf16* gk = kc + base;
+    const bf16* gv = vc + base;
 #pragma unroll
-  for (int i = 0; i < kIters; ++i) {
-    const int idx = i * 32 + lane;
-    const int row = idx / kChunks, chunk = idx % kChunks;
-    const int tok = tile * kDecTile + row;
-    const bool valid = tok < seq_len;
-    const int safe_tok = valid ? tok : 0;
-    const int64_t page = bt_row[safe_tok / page_size];
-    const int64_t src = ((page * Hkv + h) * page_size + (safe_tok % page_size)) * D + chunk * 8;
-    cp_async_16(sK + swz<D>(row, chunk), kc + src, valid);
-    cp_async_16(sV + swz<D>(row, chunk), vc + src, valid);
+    for (int i = 0; i < kIters; ++i) {
+      const int row = i * kRowsPerIter + sub_row;
+      const bool valid = row < n_valid;
+      const uint32_t off = dec_swz<D>(row, chunk);
+      const int bytes = valid ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sK + off), "l"(gk + (valid ? i * 32 * 8 : 0)), "r"(bytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sK + L::kTileBytes + off), "l"(gv + (valid ? i * 32 * 8 : 0)), "r"(bytes) : "memory");
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kIters; ++i) {
+      const int row = i * kRowsPerIter + sub_row;
+      const bool valid = row < n_valid;
+      const int tok = valid ? tile * kDecTile + row : 0;
+      const int64_t page = bt_row[tok / page_size];
+      const int64_t src = ((page * Hkv + h) * page_size + (tok % page_size)) * D + chunk * 8;
+      const uint32_t off = dec_swz<D>(row, chunk);
+      const int bytes = valid ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sK + off), "l"(kc + src), "r"(bytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sK + L::kTileBytes + off), "l"(vc + src), "r"(bytes) : "memory");
+    }
   }
 }
 
-template <int D>
+template <int D, bool kFast>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_tables,
                     const int* __restrict__ seq_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, int Hq, int Hkv, int page_size,
-                    int max_pages, int num_splits, float scale_log2) {
+                    int max_pages, int num_splits, float scale_log2, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t dec_smem[];
-  constexpr int kTileElems = kDecTile * D;
+  using L = DecLayout<D>;
   constexpr int kND = D / 8;   // n-tiles of the output
-  constexpr int kKK = D / 16;  // k-steps of Q·Kᵀ
+  constexpr int kKK = D / 16;  // k-steps of Q.K^T
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = Hq / Hkv;
@@ -54,7 +92,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
   const int t_begin = split * tiles_per_split;
   const int t_end = min(t_begin + tiles_per_split, tiles_total);
 
-  bf16* my = reinterpret_cast<bf16*>(dec_smem) + (size_t)warp * kDecStages * 2 * kTileElems;
+  const uint32_t my = smem_addr(dec_smem) + warp * L::kWarpBytes;
 
   // Q fragments (rows >= G are zero)
   uint32_t qa[kKK][4];
@@ -76,19 +114,26 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
   for (int i = 0; i < kND; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-  int tile = t_begin + warp;
-  if (tile < t_end) dec_load_tile<D>(my, my + kTileElems, kc, vc, bt_row, tile, seq_len, h, Hkv, page_size, lane);
-  cp_async_commit();
-  int stage = 0;
-  for (; tile < t_end; tile += kDecWarps) {
-    const int next = tile + kDecWarps;
-    bf16* nK = my + (stage ^ 1) * 2 * kTileElems;
-    if (next < t_end) dec_load_tile<D>(nK, nK + kTileElems, kc, vc, bt_row, next, seq_len, h, Hkv, page_size, lane);
+  // prologue: kDecStages - 1 tiles in flight (one cp.async group per tile, possibly empty)
+  int issue_tile = t_begin + warp;
+#pragma unroll
+  for (int st = 0; st < kDecStages - 1; ++st) {
+    if (issue_tile < t_end) dec_issue_tile<D, kFast>(my + st * L::kStageBytes, kc, vc, bt_row, issue_tile, seq_len, h, Hkv, page_size, lane);
     cp_async_commit();
-    cp_async_wait<1>();
+    issue_tile += kDecWarps;
+  }
+  int stage = 0;
+  for (int tile = t_begin + warp; tile < t_end; tile += kDecWarps) {
+    {  // refill the stage consumed in the previous iteration
+      const int st = (stage + kDecStages - 1) % kDecStages;
+      if (issue_tile < t_end) dec_issue_tile<D, kFast>(my + st * L::kStageBytes, kc, vc, bt_row, issue_tile, seq_len, h, Hkv, page_size, lane);
+      cp_async_commit();
+      issue_tile += kDecWarps;
+    }
+    cp_async_wait<kDecStages - 1>();
     __syncwarp();
-    const bf16* sK = my + stage * 2 * kTileElems;
-    const bf16* sV = sK + kTileElems;
+    const uint32_t sK = my + stage * L::kStageBytes;
+    const uint32_t sV = sK + L::kTileBytes;
 
     float s[4][4];
 #pragma unroll
@@ -100,18 +145,19 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
       for (int nt = 0; nt < 4; nt += 2) {
         uint32_t r0, r1, r2, r3;
         const int row = (nt + (mat >> 1)) * 8 + mr, chunk = kk * 2 + (mat & 1);
-        ldmatrix_x4(smem_addr(sK + swz<D>(row, chunk)), r0, r1, r2, r3);
+        ldmatrix_x4(sK + dec_swz<D>(row, chunk), r0, r1, r2, r3);
         mma_bf16_16816(s[nt], qa[kk], r0, r1);
         mma_bf16_16816(s[nt + 1], qa[kk], r2, r3);
       }
     }
     // mask + online softmax (rows lane/4 and lane/4 + 8)
     float mx[2] = {-INFINITY, -INFINITY};
+    const int tok0 = tile * kDecTile + (lane & 3) * 2;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int tok = tile * kDecTile + nt * 8 + (lane & 3) * 2 + (j & 1);
+        const int tok = tok0 + nt * 8 + (j & 1);
         s[nt][j] = (tok < seq_len) ? s[nt][j] * scale_log2 : -INFINITY;
         mx[j >> 1] = fmaxf(mx[j >> 1], s[nt][j]);
       }
@@ -150,13 +196,13 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
       for (int nd = 0; nd < kND; nd += 2) {
         uint32_t r0, r1, r2, r3;
         const int row = kt * 16 + (mat & 1) * 8 + mr, chunk = nd + (mat >> 1);
-        ldmatrix_x4_trans(smem_addr(sV + swz<D>(row, chunk)), r0, r1, r2, r3);
+        ldmatrix_x4_trans(sV + dec_swz<D>(row, chunk), r0, r1, r2, r3);
         mma_bf16_16816(o[nd], pa, r0, r1);
         mma_bf16_16816(o[nd + 1], pa, r2, r3);
       }
     }
     __syncwarp();
-    stage ^= 1;
+    stage = (stage + 1 == kDecStages) ? 0 : stage + 1;
   }
   cp_async_wait<0>();
 #pragma unroll
@@ -237,34 +283,35 @@ int decode_num_splits(int B, int Hkv, int max_kv_len) {
 int64_t decode_workspace_floats(int B, int Hq, int D, int num_splits) { return (int64_t)B * Hq * num_splits * (D + 2); }
 
 int paged_decode_attention(const void* q, const void* kc, const void* vc, const int* block_tables, const int* seq_lens, void* out, float* workspace,
-                           int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, cudaStream_t s) {
+                           int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, int* status, cudaStream_t s) {
   if (B == 0) return 0;
   if (Hq % Hkv || Hq / Hkv > 16 || (D != 64 && D != 128)) return 1;
   float* ws_o = workspace;
   float* ws_ml = workspace + (int64_t)B * Hq * num_splits * D;
   const dim3 grid(num_splits, Hkv, B);
-  const size_t smem = (size_t)kDecWarps * kDecStages * 2 * kDecTile * D * sizeof(bf16);
+  const size_t smem = D == 128 ? (size_t)DecLayout<128>::kTotal : (size_t)DecLayout<64>::kTotal;
   const size_t merge_smem = (size_t)kDecWarps * 16 * (D + 2) * sizeof(float);
   const size_t need = smem > merge_smem ? smem : merge_smem;
+  const bool fast = page_size % kDecTile == 0;
+  const float sl2 = scale * kLog2e;
+  (void)status;
+#define UB_DEC(DD, FF)                                                                                                                     \
+  do {                                                                                                                                     \
+    static bool cfg = false;                                                                                                               \
+    if (!cfg) {                                                                                                                            \
+      if (cudaFuncSetAttribute(paged_decode_kernel<DD, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2; \
+      cfg = true;                                                                                                                          \
+    }                                                                                                                                      \
+    paged_decode_kernel<DD, FF><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, block_tables, seq_lens, ws_o, \
+                                                                  ws_ml, Hq, Hkv, page_size, max_pages, num_splits, sl2, status);          \
+    decode_merge_kernel<DD><<<B * Hq, DD, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);                                                   \
+  } while (0)
   if (D == 128) {
-    static bool cfg = false;
-    if (!cfg) {
-      if (cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2;
-      cfg = true;
-    }
-    paged_decode_kernel<128><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, block_tables, seq_lens, ws_o, ws_ml,
-                                                                Hq, Hkv, page_size, max_pages, num_splits, scale * kLog2e);
-    decode_merge_kernel<128><<<B * Hq, 128, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);
+    if (fast) UB_DEC(128, true); else UB_DEC(128, false);
   } else {
-    static bool cfg = false;
-    if (!cfg) {
-      if (cudaFuncSetAttribute(paged_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2;
-      cfg = true;
-    }
-    paged_decode_kernel<64><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, block_tables, seq_lens, ws_o, ws_ml,
-                                                               Hq, Hkv, page_size, max_pages, num_splits, scale * kLog2e);
-    decode_merge_kernel<64><<<B * Hq, 64, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);
+    if (fast) UB_DEC(64, true); else UB_DEC(64, false);
   }
+#undef UB_DEC
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

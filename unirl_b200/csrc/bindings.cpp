@@ -311,7 +311,7 @@ Tensor paged_decode_attention(const Tensor& q, const Tensor& kc, const Tensor& v
                                                                                            : torch::empty({need}, q.options().dtype(torch::kFloat));
   auto out = torch::empty_like(q);
   const int rc = ub::paged_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr<int>(), sl.data_ptr<int>(), out.data_ptr(),
-                                            ws.data_ptr<float>(), B, Hq, Hkv, D, page, (int)bt.size(1), splits, (float)scale, stream());
+                                            ws.data_ptr<float>(), B, Hq, Hkv, D, page, (int)bt.size(1), splits, (float)scale, gemm_status_tensor().data_ptr<int>(), stream());
   TORCH_CHECK(rc == 0, "paged_decode_attention: unsupported configuration or launch failure (code ", rc, ")");
   return out;
 }
@@ -340,6 +340,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sde_replay_bwd", &sde_replay_bwd);
   m.def("gemm_bf16_tn", &gemm_bf16_tn);
   m.def("gemm_status", &gemm_status, py::arg("reset") = true);
+  m.def("set_gemm_tile", &ub::set_gemm_tile);
   m.def("linear_logprob_fwd", &linear_logprob_fwd);
   m.def("linear_sample", &linear_sample);
   m.def("decode_workspace_size", &decode_workspace_size);

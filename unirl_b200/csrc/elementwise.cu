@@ -75,6 +75,324 @@ __global__ void layernorm_modulate_kernel(const T* __restrict__ x, const T* __re
     y[row * D + c] = from_f<T>((to_f(x[row * D + c]) - mu) * r * (1.f + to_f(scale[b * D + c])) + to_f(shift[b * D + c]));
 }
 
+
+// ===================================================================================== vectorised bf16 fast paths
+// Rows are processed with 16-byte accesses and held in registers between the reduction and the write, so every
+// operand crosses HBM exactly once.  Used when the dtype is bf16 and the row length is a multiple of 8.
+constexpr int kVPT = 4;  // vectors (of 8) per thread held in registers => rows up to threads * 32 elements
+
+template <bool kAddResidual>
+__global__ void rmsnorm_fwd_vec_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res_in, const bf16* __restrict__ w, bf16* __restrict__ y,
+                                       bf16* __restrict__ res_out, float* __restrict__ rstd, int D, float eps) {
+  __shared__ float scratch[32];
+  const int64_t row = blockIdx.x;
+  const int nvec = D >> 3;
+  float v[kVPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kVPT; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < nvec) {
+      load8(x + row * D + c * 8, v[j]);
+      if (kAddResidual) {
+        float r[8];
+        load8(res_in + row * D + c * 8, r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] = to_f(from_f<bf16>(v[j][e] + r[e]));
+        store8(res_out + row * D + c * 8, v[j]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[j][e] * v[j][e];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int j = 0; j < kVPT; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < nvec) {
+      float ww[8];
+      load8(w + c * 8, ww);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[j][e] = v[j][e] * r * ww[e];
+      store8(y + row * D + c * 8, v[j]);
+    }
+  }
+}
+
+__global__ void rmsnorm_bwd_vec_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                       bf16* __restrict__ gx, float* __restrict__ gw, int64_t R, int D) {
+  __shared__ float scratch[32];
+  const int nvec = D >> 3;
+  float gw_acc[kVPT][8], ww[kVPT][8];
+#pragma unroll
+  for (int j = 0; j < kVPT; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) gw_acc[j][e] = 0.f;
+    if (c < nvec) load8(w + c * 8, ww[j]);
+  }
+  for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
+    const float r = rstd[row];
+    float xh[kVPT][8], g[kVPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < kVPT; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < nvec) {
+        load8(x + row * D + c * 8, xh[j]);
+        load8(gy + row * D + c * 8, g[j]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[j][e] *= r;
+          dot += g[j][e] * ww[j][e] * xh[j][e];
+        }
+      }
+    }
+    dot = block_sum(dot, scratch) / D;
+#pragma unroll
+    for (int j = 0; j < kVPT; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          o[e] = r * (g[j][e] * ww[j][e] - xh[j][e] * dot);
+          gw_acc[j][e] += g[j][e] * xh[j][e];
+        }
+        store8(gx + row * D + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kVPT; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) atomicAdd(gw + c * 8 + e, gw_acc[j][e]);
+    }
+  }
+}
+
+__global__ void swiglu_fwd_vec_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t rows, int I) {
+  const int iv = I >> 3;
+  const int64_t n = rows * iv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / iv;
+    const int c = (int)(idx - r * iv) * 8;
+    float g[8], u[8];
+    load8(gu + r * 2 * I + c, g);
+    load8(gu + r * 2 * I + I + c, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
+    store8(out + r * I + c, g);
+  }
+}
+__global__ void swiglu_bwd_vec_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ gu, bf16* __restrict__ g_gu, int64_t rows, int I) {
+  const int iv = I >> 3;
+  const int64_t n = rows * iv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / iv;
+    const int c = (int)(idx - r * iv) * 8;
+    float g[8], u[8], dy[8], dg[8], du[8];
+    load8(gu + r * 2 * I + c, g);
+    load8(gu + r * 2 * I + I + c, u);
+    load8(gy + r * I + c, dy);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sig = 1.f / (1.f + __expf(-g[e]));
+      dg[e] = dy[e] * u[e] * sig * (1.f + g[e] * (1.f - sig));
+      du[e] = dy[e] * g[e] * sig;
+    }
+    store8(g_gu + r * 2 * I + c, dg);
+    store8(g_gu + r * 2 * I + I + c, du);
+  }
+}
+
+__global__ void kv_cache_write_vec_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, bf16* __restrict__ kc, bf16* __restrict__ vc,
+                                          const int64_t* __restrict__ slots, int64_t T_tokens, int Hkv, int D, int page_size) {
+  const int dv = D >> 3;
+  const int64_t n = T_tokens * Hkv * dv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(idx % dv) * 8;
+    const int h = (int)((idx / dv) % Hkv);
+    const int64_t t = idx / ((int64_t)dv * Hkv);
+    const int64_t slot = slots[t];
+    if (slot < 0) continue;
+    const int64_t dst = (((slot / page_size) * Hkv + h) * page_size + (slot % page_size)) * D + d;
+    const int64_t src = (t * Hkv + h) * D + d;
+    *reinterpret_cast<Pack8*>(kc + dst) = *reinterpret_cast<const Pack8*>(k + src);
+    *reinterpret_cast<Pack8*>(vc + dst) = *reinterpret_cast<const Pack8*>(v + src);
+  }
+}
+
+__global__ void dlogits_vec_kernel(bf16* __restrict__ z, const int* __restrict__ tgt, const float* __restrict__ lse, const float* __restrict__ g,
+                                   int64_t R, int64_t V, float inv_t) {
+  const int64_t vv = V >> 3;
+  const int64_t n = R * vv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / vv;
+    const int64_t c = (idx - r * vv) * 8;
+    float f[8];
+    load8(z + r * V + c, f);
+    const float l = lse[r], gg = g[r] * inv_t;
+    const int64_t t = tgt[r];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = gg * ((c + e == t ? 1.f : 0.f) - __expf(f[e] * inv_t - l));
+    store8(z + r * V + c, f);
+  }
+}
+
+// QK-norm + RoPE, one warp per TOKEN looping over heads: the sin/cos of a (token, frequency) pair is evaluated once
+// and reused by every head; each lane owns the rotation pairs (i, i + D/2) for i = 2*lane, 2*lane + 1 (+ 64 per step).
+template <int D>
+__global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw, const int* __restrict__ pos,
+                                            const float* __restrict__ inv_freq, bf16* __restrict__ q, bf16* __restrict__ k, bf16* __restrict__ v,
+                                            float* __restrict__ rstd, int64_t T_tokens, int Hq, int Hkv, float eps) {
+  constexpr int half = D / 2, kJ = half / 64;  // pairs-of-2 per lane: D=128 -> 1, D=256 -> 2
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T_tokens) return;
+  const int H = Hq + 2 * Hkv;
+  const float p = (float)pos[t];
+  float cs[kJ][2], sn[kJ][2], wqa[kJ][2], wqb[kJ][2], wka[kJ][2], wkb[kJ][2];
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int i = j * 64 + lane * 2 + e;
+      sincosf(p * inv_freq[i], &sn[j][e], &cs[j][e]);
+      wqa[j][e] = to_f(qw[i]); wqb[j][e] = to_f(qw[i + half]);
+      wka[j][e] = to_f(kw[i]); wkb[j][e] = to_f(kw[i + half]);
+    }
+  }
+  for (int h = 0; h < Hq + Hkv; ++h) {
+    const bool is_q = h < Hq;
+    const bf16* src = qkv + (t * H + h) * D;
+    bf16* dst = is_q ? q + (t * Hq + h) * D : k + (t * Hkv + (h - Hq)) * D;
+    float a[kJ][2], b[kJ][2];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kJ; ++j) {
+      const float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(src + j * 64 + lane * 2));
+      const float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(src + half + j * 64 + lane * 2));
+      a[j][0] = fa.x; a[j][1] = fa.y; b[j][0] = fb.x; b[j][1] = fb.y;
+      ss += fa.x * fa.x + fa.y * fa.y + fb.x * fb.x + fb.y * fb.y;
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / D + eps);
+    if (lane == 0 && rstd) rstd[t * (Hq + Hkv) + h] = r;
+#pragma unroll
+    for (int j = 0; j < kJ; ++j) {
+      float oa[2], ob[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float na = a[j][e] * r * (is_q ? wqa[j][e] : wka[j][e]);
+        const float nb = b[j][e] * r * (is_q ? wqb[j][e] : wkb[j][e]);
+        oa[e] = na * cs[j][e] - nb * sn[j][e];
+        ob[e] = nb * cs[j][e] + na * sn[j][e];
+      }
+      *reinterpret_cast<bf162*>(dst + j * 64 + lane * 2) = __floats2bfloat162_rn(oa[0], oa[1]);
+      *reinterpret_cast<bf162*>(dst + half + j * 64 + lane * 2) = __floats2bfloat162_rn(ob[0], ob[1]);
+    }
+  }
+  // v heads: straight copy, 8 bytes per lane per step
+  const bf16* vs = qkv + (t * H + Hq + Hkv) * D;
+  bf16* vd = v + t * Hkv * D;
+  for (int c = lane * 4; c < Hkv * D; c += 128) *reinterpret_cast<uint2*>(vd + c) = *reinterpret_cast<const uint2*>(vs + c);
+}
+
+template <int D>
+__global__ void qk_norm_rope_bwd_vec_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk, const bf16* __restrict__ gv, const bf16* __restrict__ qkv,
+                                            const bf16* __restrict__ qw, const bf16* __restrict__ kw, const int* __restrict__ pos,
+                                            const float* __restrict__ inv_freq, const float* __restrict__ rstd, bf16* __restrict__ g_qkv,
+                                            float* __restrict__ g_qw, float* __restrict__ g_kw, int64_t T_tokens, int Hq, int Hkv) {
+  constexpr int half = D / 2, kJ = half / 64;
+  const int lane = threadIdx.x & 31;
+  const int H = Hq + 2 * Hkv;
+  float acc_qa[kJ][2], acc_qb[kJ][2], acc_ka[kJ][2], acc_kb[kJ][2], wqa[kJ][2], wqb[kJ][2], wka[kJ][2], wkb[kJ][2];
+#pragma unroll
+  for (int j = 0; j < kJ; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int i = j * 64 + lane * 2 + e;
+      acc_qa[j][e] = acc_qb[j][e] = acc_ka[j][e] = acc_kb[j][e] = 0.f;
+      wqa[j][e] = to_f(qw[i]); wqb[j][e] = to_f(qw[i + half]);
+      wka[j][e] = to_f(kw[i]); wkb[j][e] = to_f(kw[i + half]);
+    }
+  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T_tokens; t += stride) {
+    const float p = (float)pos[t];
+    float cs[kJ][2], sn[kJ][2];
+#pragma unroll
+    for (int j = 0; j < kJ; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) sincosf(p * inv_freq[j * 64 + lane * 2 + e], &sn[j][e], &cs[j][e]);
+    for (int h = 0; h < Hq + Hkv; ++h) {
+      const bool is_q = h < Hq;
+      const bf16* src = qkv + (t * H + h) * D;
+      const bf16* g = is_q ? gq + (t * Hq + h) * D : gk + (t * Hkv + (h - Hq)) * D;
+      bf16* dst = g_qkv + (t * H + h) * D;
+      const float r = rstd[t * (Hq + Hkv) + h];
+      float na[kJ][2], nb[kJ][2], xa[kJ][2], xb[kJ][2];
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < kJ; ++j) {
+        const float2 ga = __bfloat1622float2(*reinterpret_cast<const bf162*>(g + j * 64 + lane * 2));
+        const float2 gb = __bfloat1622float2(*reinterpret_cast<const bf162*>(g + half + j * 64 + lane * 2));
+        const float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(src + j * 64 + lane * 2));
+        const float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(src + half + j * 64 + lane * 2));
+        const float gae[2] = {ga.x, ga.y}, gbe[2] = {gb.x, gb.y}, fae[2] = {fa.x, fa.y}, fbe[2] = {fb.x, fb.y};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          na[j][e] = gae[e] * cs[j][e] + gbe[e] * sn[j][e];
+          nb[j][e] = gbe[e] * cs[j][e] - gae[e] * sn[j][e];
+          xa[j][e] = fae[e] * r;
+          xb[j][e] = fbe[e] * r;
+          const float wa = is_q ? wqa[j][e] : wka[j][e], wb = is_q ? wqb[j][e] : wkb[j][e];
+          dot += na[j][e] * wa * xa[j][e] + nb[j][e] * wb * xb[j][e];
+          if (is_q) { acc_qa[j][e] += na[j][e] * xa[j][e]; acc_qb[j][e] += nb[j][e] * xb[j][e]; }
+          else { acc_ka[j][e] += na[j][e] * xa[j][e]; acc_kb[j][e] += nb[j][e] * xb[j][e]; }
+        }
+      }
+      dot = warp_sum(dot) / D;
+#pragma unroll
+      for (int j = 0; j < kJ; ++j) {
+        float oa[2], ob[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float wa = is_q ? wqa[j][e] : wka[j][e], wb = is_q ? wqb[j][e] : wkb[j][e];
+          oa[e] = r * (na[j][e] * wa - xa[j][e] * dot);
+          ob[e] = r * (nb[j][e] * wb - xb[j][e] * dot);
+        }
+        *reinterpret_cast<bf162*>(dst + j * 64 + lane * 2) = __floats2bfloat162_rn(oa[0], oa[1]);
+        *reinterpret_cast<bf162*>(dst + half + j * 64 + lane * 2) = __floats2bfloat162_rn(ob[0], ob[1]);
+      }
+    }
+    const bf16* vs = gv + t * Hkv * D;
+    bf16* vd = g_qkv + (t * H + Hq + Hkv) * D;
+    for (int c = lane * 4; c < Hkv * D; c += 128) *reinterpret_cast<uint2*>(vd + c) = *reinterpret_cast<const uint2*>(vs + c);
+  }
+#pragma unroll
+  for (int j = 0; j < kJ; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int i = j * 64 + lane * 2 + e;
+      atomicAdd(g_qw + i, acc_qa[j][e]); atomicAdd(g_qw + i + half, acc_qb[j][e]);
+      atomicAdd(g_kw + i, acc_ka[j][e]); atomicAdd(g_kw + i + half, acc_kb[j][e]);
+    }
+}
+
+static int vec_threads(int D) {
+  const int nvec = D >> 3;
+  int t = 32;
+  while (t * kVPT < nvec && t < 1024) t <<= 1;
+  while (t > 32 && (t >> 1) >= nvec) t >>= 1;
+  return t;
+}
+static bool vec_ok(int D, int dtype) { return dtype == kBF16 && D % 8 == 0 && (D >> 3) <= 1024 * kVPT; }
+
 static int norm_threads(int D) {
   int t = 32;
   while (t < D / 4 && t < 1024) t <<= 1;
@@ -83,6 +401,10 @@ static int norm_threads(int D) {
 
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t R, int D, float eps, int dtype, cudaStream_t s) {
   if (R == 0) return;
+  if (vec_ok(D, dtype)) {
+    rmsnorm_fwd_vec_kernel<false><<<(unsigned)R, vec_threads(D), 0, s>>>((const bf16*)x, nullptr, (const bf16*)w, (bf16*)y, nullptr, rstd, D, eps);
+    return;
+  }
   if (dtype == kBF16)
     rmsnorm_fwd_kernel<bf16, false><<<(unsigned)R, norm_threads(D), 0, s>>>((const bf16*)x, nullptr, (const bf16*)w, (bf16*)y, nullptr, rstd, D, eps);
   else
@@ -90,6 +412,10 @@ void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t R, 
 }
 void add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, int64_t R, int D, float eps, int dtype, cudaStream_t s) {
   if (R == 0) return;
+  if (vec_ok(D, dtype)) {
+    rmsnorm_fwd_vec_kernel<true><<<(unsigned)R, vec_threads(D), 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)res_out, nullptr, D, eps);
+    return;
+  }
   if (dtype == kBF16)
     rmsnorm_fwd_kernel<bf16, true><<<(unsigned)R, norm_threads(D), 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)res_out, nullptr, D, eps);
   else
@@ -97,6 +423,10 @@ void add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, voi
 }
 void rmsnorm_bwd(const void* gy, const void* x, const void* w, const float* rstd, void* gx, float* gw, int64_t R, int D, int dtype, cudaStream_t s) {
   if (R == 0) return;
+  if (vec_ok(D, dtype)) {
+    rmsnorm_bwd_vec_kernel<<<(unsigned)(R < 1184 ? R : 1184), vec_threads(D), 0, s>>>((const bf16*)gy, (const bf16*)x, (const bf16*)w, rstd, (bf16*)gx, gw, R, D);
+    return;
+  }
   const int threads = norm_threads(D);
   const unsigned grid = (unsigned)(R < 592 ? R : 592);
   if (dtype == kBF16)
@@ -237,6 +567,12 @@ void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int
                       int64_t T, int Hq, int Hkv, int D, float eps, int dtype, cudaStream_t s) {
   const int64_t warps = T * (Hq + 2 * Hkv);
   if (warps == 0) return;
+  if (dtype == kBF16 && qw && kw && (D == 128 || D == 256) && (Hkv * D) % 128 == 0) {
+    const unsigned g = (unsigned)((T + 3) / 4);
+    if (D == 128) qk_norm_rope_fwd_vec_kernel<128><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, rstd, T, Hq, Hkv, eps);
+    else qk_norm_rope_fwd_vec_kernel<256><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, rstd, T, Hq, Hkv, eps);
+    return;
+  }
   const unsigned grid = (unsigned)((warps + 7) / 8);
   if (dtype == kBF16)
     qk_norm_rope_fwd_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, rstd, T, Hq, Hkv, D, eps);
@@ -248,6 +584,13 @@ void qk_norm_rope_bwd(const void* gq, const void* gk, const void* gv, const void
                       cudaStream_t s) {
   const int64_t warps = T * (Hq + 2 * Hkv);
   if (warps == 0) return;
+  if (dtype == kBF16 && qw && kw && g_qw && (D == 128 || D == 256) && (Hkv * D) % 128 == 0) {
+    const int64_t wantb = (T + 3) / 4;
+    const unsigned g = (unsigned)(wantb < 1184 ? wantb : 1184);
+    if (D == 128) qk_norm_rope_bwd_vec_kernel<128><<<g, 128, 0, s>>>((const bf16*)gq, (const bf16*)gk, (const bf16*)gv, (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, rstd, (bf16*)g_qkv, g_qw, g_kw, T, Hq, Hkv);
+    else qk_norm_rope_bwd_vec_kernel<256><<<g, 128, 0, s>>>((const bf16*)gq, (const bf16*)gk, (const bf16*)gv, (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, rstd, (bf16*)g_qkv, g_qw, g_kw, T, Hq, Hkv);
+    return;
+  }
   const int64_t want = (warps + 7) / 8;
   const unsigned grid = (unsigned)(want < 1184 ? want : 1184);
   if (dtype == kBF16)
@@ -285,11 +628,19 @@ static unsigned ew_grid(int64_t n, int threads) {
 }
 void swiglu_fwd(const void* gu, void* out, int64_t rows, int I, int dtype, cudaStream_t s) {
   if (rows * I == 0) return;
+  if (dtype == kBF16 && I % 8 == 0) {
+    swiglu_fwd_vec_kernel<<<ew_grid(rows * (I / 8), 256), 256, 0, s>>>((const bf16*)gu, (bf16*)out, rows, I);
+    return;
+  }
   if (dtype == kBF16) swiglu_fwd_kernel<bf16><<<ew_grid(rows * I, 256), 256, 0, s>>>((const bf16*)gu, (bf16*)out, rows, I);
   else swiglu_fwd_kernel<float><<<ew_grid(rows * I, 256), 256, 0, s>>>((const float*)gu, (float*)out, rows, I);
 }
 void swiglu_bwd(const void* gy, const void* gu, void* g_gu, int64_t rows, int I, int dtype, cudaStream_t s) {
   if (rows * I == 0) return;
+  if (dtype == kBF16 && I % 8 == 0) {
+    swiglu_bwd_vec_kernel<<<ew_grid(rows * (I / 8), 256), 256, 0, s>>>((const bf16*)gy, (const bf16*)gu, (bf16*)g_gu, rows, I);
+    return;
+  }
   if (dtype == kBF16) swiglu_bwd_kernel<bf16><<<ew_grid(rows * I, 256), 256, 0, s>>>((const bf16*)gy, (const bf16*)gu, (bf16*)g_gu, rows, I);
   else swiglu_bwd_kernel<float><<<ew_grid(rows * I, 256), 256, 0, s>>>((const float*)gy, (const float*)gu, (float*)g_gu, rows, I);
 }
@@ -313,6 +664,10 @@ __global__ void kv_cache_write_kernel(const T* __restrict__ k, const T* __restri
 void kv_cache_write(const void* k, const void* v, void* kc, void* vc, const int64_t* slots, int64_t T, int Hkv, int D, int page_size, int dtype, cudaStream_t s) {
   if (T == 0) return;
   const int64_t n = T * Hkv * D;
+  if (dtype == kBF16 && D % 8 == 0) {
+    kv_cache_write_vec_kernel<<<ew_grid(n / 8, 256), 256, 0, s>>>((const bf16*)k, (const bf16*)v, (bf16*)kc, (bf16*)vc, slots, T, Hkv, D, page_size);
+    return;
+  }
   if (dtype == kBF16) kv_cache_write_kernel<bf16><<<ew_grid(n, 256), 256, 0, s>>>((const bf16*)k, (const bf16*)v, (bf16*)kc, (bf16*)vc, slots, T, Hkv, D, page_size);
   else kv_cache_write_kernel<float><<<ew_grid(n, 256), 256, 0, s>>>((const float*)k, (const float*)v, (float*)kc, (float*)vc, slots, T, Hkv, D, page_size);
 }
@@ -426,6 +781,10 @@ __global__ void dlogits_kernel(T* __restrict__ z, const int* __restrict__ tgt, c
 void logprob_dlogits_inplace(void* z, const int* tgt, const float* lse, const float* g, int64_t R, int64_t V, float temperature, int dtype, cudaStream_t s) {
   if (R * V == 0) return;
   const unsigned grid = ew_grid(R * V, 256) * 4;
+  if (dtype == kBF16 && V % 8 == 0) {
+    dlogits_vec_kernel<<<ew_grid(R * (V / 8), 256) * 2, 256, 0, s>>>((bf16*)z, tgt, lse, g, R, V, 1.f / temperature);
+    return;
+  }
   if (dtype == kBF16) dlogits_kernel<bf16><<<grid, 256, 0, s>>>((bf16*)z, tgt, lse, g, R, V, 1.f / temperature);
   else dlogits_kernel<float><<<grid, 256, 0, s>>>((float*)z, tgt, lse, g, R, V, 1.f / temperature);
 }

@@ -62,6 +62,19 @@ struct SmemLayout {
   static constexpr int kTotal = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
+// Grouped rasterisation: consecutive tile ids sweep kGroupN adjacent n-tiles before advancing in m, so the ~148 tiles in
+// flight at any moment form a roughly square patch (about 18 m-tiles x 8 n-tiles) and share both operands through L2
+// instead of streaming the whole A matrix once per n-tile.
+constexpr int kGroupN = 8;
+__device__ __forceinline__ void tile_to_mn(int tile, int num_m_tiles, int num_n_tiles, int& m_idx, int& n_idx) {
+  const int per_group = kGroupN * num_m_tiles;
+  const int group = tile / per_group, in_group = tile - group * per_group;
+  const int first_n = group * kGroupN;
+  const int gsize = min(num_n_tiles - first_n, kGroupN);
+  m_idx = in_group / gsize;
+  n_idx = first_n + (in_group - m_idx * gsize);
+}
+
 __device__ __forceinline__ void report(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
@@ -114,8 +127,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.num_m_tiles) * BM;
-        const int n_idx = tile / p.num_m_tiles;
+        int m_idx, n_idx;
+        tile_to_mn(tile, p.num_m_tiles, p.num_n_tiles, m_idx, n_idx);
+        const int m0 = m_idx * BM;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty + stage, phase ^ 1)) {
             report(p.status, 101);
@@ -183,8 +197,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int buf = it & 1;
-      const int m0 = (tile % p.num_m_tiles) * BM;
-      const int n_idx = tile / p.num_m_tiles;
+      int m_idx, n_idx;
+      tile_to_mn(tile, p.num_m_tiles, p.num_n_tiles, m_idx, n_idx);
+      const int m0 = m_idx * BM;
       if (!mbar_wait(tfull + buf, (it >> 1) & 1)) {
         report(p.status, 104);
         break;
@@ -410,6 +425,9 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
+int g_force_bn = 0;  // tuning hook: 0 = heuristic, 128 / 256 = forced tile width
+void set_gemm_tile(int bn) { g_force_bn = bn; }
+
 // C[M,N] = A[M,K]·B[N,K]ᵀ (+R).  Returns 0 on success, non-zero when the shape/alignment is unsupported (caller falls back).
 int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
                  cudaStream_t s) {
@@ -428,7 +446,7 @@ int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, in
     if (!make_tensor_map_bf16(&tmB, B, 2 * (int64_t)N, K, ldb, BN / 2)) return 1;
     return launch_variant<BN, kEpiSwiGLU>(tmA, tmB, p, s);
   }
-  const bool wide = N >= 256 * 2 || N % 256 == 0;
+  const bool wide = g_force_bn ? g_force_bn == 256 : (N >= 256 * 2 || N % 256 == 0);
   const int BN = wide ? 256 : 128;
   p.num_n_tiles = (N + BN - 1) / BN;
   if (!make_tensor_map_bf16(&tmB, B, N, K, ldb, BN)) return 1;

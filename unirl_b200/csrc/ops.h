@@ -50,6 +50,7 @@ void sde_replay_bwd(const float* g_mean, const float* g_logp, const float* mean,
 int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
                  cudaStream_t s);
 int lse_num_tiles(int V);
+void set_gemm_tile(int bn);
 int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int ldw, const int* targets, float temperature, float* pmax, float* psum,
                float* tgt_logit, float* pbest, int* pbest_idx, float* pbest_z, uint64_t seed, int64_t step, const int64_t* step_tensor, float* lse_out,
                float* logp_out, int64_t* tok_out, int* status, cudaStream_t s);
@@ -58,6 +59,6 @@ int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int l
 int decode_num_splits(int B, int Hkv, int max_kv_len);
 int64_t decode_workspace_floats(int B, int Hq, int D, int num_splits);
 int paged_decode_attention(const void* q, const void* kc, const void* vc, const int* block_tables, const int* seq_lens, void* out, float* workspace,
-                           int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, cudaStream_t s);
+                           int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, int* status, cudaStream_t s);
 
 }  // namespace ub
