@@ -1,17 +1,21 @@
-"""Helper: run a function on N gloo ranks in child processes and collect its return values."""
+"""Helper: run a function on N ranks in child processes (gloo on CPU, or one CUDA device per rank over NCCL) and collect its return values."""
 import multiprocessing as mp
 import os
 import traceback
 
 
-def _entry(fn, rank, world, port, q, args):
-    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world)})
+def _entry(fn, rank, world, port, q, args, cuda=False):
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world),
+                       "LOCAL_RANK": str(rank), "NCCL_NVLS_ENABLE": "0"})
     try:
         import torch
         import torch.distributed as dist
 
         torch.set_num_threads(2)
-        dist.init_process_group("gloo", rank=rank, world_size=world, init_method=f"tcp://127.0.0.1:{port}")
+        if cuda:
+            torch.cuda.set_device(rank)
+        dist.init_process_group("cpu:gloo,cuda:nccl" if cuda else "gloo", rank=rank, world_size=world, init_method=f"tcp://127.0.0.1:{port}",
+                                **({"device_id": torch.device("cuda", rank)} if cuda else {}))
         out = fn(rank, world, *args)
         dist.barrier()
         dist.destroy_process_group()
@@ -24,13 +28,13 @@ def _entry(fn, rank, world, port, q, args):
         q.put((rank, False, traceback.format_exc()))
 
 
-def run_ranks(fn, world, *args, timeout=240):
+def run_ranks(fn, world, *args, timeout=240, cuda=False):
     from unirl_b200.distributed.utils import free_port
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args), daemon=True) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args, cuda), daemon=True) for r in range(world)]
     for p in procs:
         p.start()
     results = {}

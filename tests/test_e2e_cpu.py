@@ -66,3 +66,25 @@ def test_colocated_step_resume_and_alignment(tmp_path):
         assert tr2._resume_state.get("optimizer_step") == 2
     finally:
         tr2.shutdown()
+
+
+@pytest.mark.timeout(900)
+def test_colocated_dp2_trainer_with_tp2_rollout_over_gloo():
+    """The headline topology in miniature: two workers host a DP=2 sharded trainer AND one TP=2 rollout engine; the
+    engine's single output handle is windowed across the two trainer ranks, weights move by the reshard plan."""
+    ov = [o for o in _COLOC if not o.startswith(("num_devices", "rollout.config.tp_size", "rollout_parallel", "+pool_backend"))]
+    cfg = compose("ar/qwen3_4b_grpo_b200", overrides=ov + ["num_devices=2", "rollout.config.tp_size=2", "rollout_parallel={tp: 2}", "+pool_backend=mp",
+                                                           "rollout.config.max_running_requests=16", "rollout.config.model_precision=fp32"])
+    tr = _trainer(cfg)
+    try:
+        tr.train(num_rollouts=2, weight_sync_interval=1)
+        rows = [r for r in tr.wandb_logger.history if "train/step" in r]
+        assert rows and abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-3 and rows[0]["train/rollout_replay_logp_absdiff_max"] < 1e-3
+        tr._sync_weights()
+        eng = tr.rollout.compute_local_param_checksums()
+        trn = tr.backend.compute_local_param_checksums()
+        assert trn[0] == trn[1], "both trainer ranks hold the same replica"
+        replicated = [k for k in eng[0] if k.endswith("layernorm") or k.endswith("norm") or "embed" in k]
+        assert replicated and all(eng[0][k] == eng[1][k] == trn[0][k] for k in replicated)
+    finally:
+        tr.shutdown()

@@ -1,0 +1,186 @@
+"""Peer-memory collective kernels: single-device checks of the data path and of the bounded wait, and
+two-rank runs (one CUDA device per rank, NCCL for plumbing, NVLS off) against library collectives."""
+import pytest
+import torch
+
+from _spawn import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+BIG = 1 << 30  # an epoch no kernel reaches: a pad pre-filled with it makes every wait pass at once
+
+
+def _C():
+    from unirl_b200.ops._ext import require_ext
+
+    return require_ext()
+
+
+def _local_comm(C, arenas, rank, preset, wait_s=5.0):
+    """A world-of-len(arenas) communicator whose "peers" are buffers of this same device."""
+    flags = [torch.full((64,), preset, dtype=torch.int32, device="cuda") for _ in arenas]
+    state = torch.zeros(8, dtype=torch.int32, device="cuda")
+    pc = C.PeerComm([a.data_ptr() for a in arenas], [f.data_ptr() for f in flags], rank, state, wait_s)
+    return pc, flags, state
+
+
+def test_allreduce_residual_rmsnorm_data_path_one_device():
+    C = _C()
+    torch.manual_seed(0)
+    T, H, W = 37, 2560, 4
+    arenas = [torch.randn(T * H, device="cuda").bfloat16() for _ in range(W)]
+    res = torch.randn(T, H, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    want_x = (sum(a.float() for a in arenas).view(T, H) + res.float()).bfloat16()
+    xf = want_x.float()
+    want_h = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    outs = []
+    for r in range(W):
+        pc, flags, state = _local_comm(C, arenas, r, BIG)
+        x, h = torch.empty(T, H, device="cuda", dtype=torch.bfloat16), torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+        C.peer_allreduce_residual_rmsnorm(pc, arenas[r].view(T, H), res, w, x, h, 1e-6)
+        torch.cuda.synchronize()
+        assert int(state[4]) == 0 and int(state[0]) == 1  # no time-out; tick advanced once
+        torch.testing.assert_close(x.float(), want_x.float(), atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(h.float(), want_h, atol=3e-2, rtol=2e-2)
+        outs.append(x)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])  # every rank computes bit-identical sums
+
+
+def test_reduce_scatter_and_adamw_publish_data_path_one_device():
+    C = _C()
+    from unirl_b200.ops.optim import adamw_reference
+
+    torch.manual_seed(1)
+    W, S = 2, 4096
+    grads = [torch.randn(W * S, device="cuda") for _ in range(W)]
+    want = sum(grads) / W
+    shards = []
+    for r in range(W):
+        pc, _, state = _local_comm(C, grads, r, BIG)
+        out, ss = torch.empty(S, device="cuda"), torch.zeros(1, device="cuda")
+        C.peer_reduce_scatter_sumsq(pc, grads[r], out, ss, 1.0 / W)
+        torch.cuda.synchronize()
+        assert int(state[4]) == 0
+        torch.testing.assert_close(out, want[r * S:(r + 1) * S], atol=1e-6, rtol=1e-6)
+        torch.testing.assert_close(ss[0], out.pow(2).sum(), rtol=1e-4, atol=1e-4)
+        shards.append(out)
+    replicas = [torch.zeros(W * S, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    clip = torch.tensor([0.5], device="cuda")
+    for r in range(W):
+        pc, _, state = _local_comm(C, replicas, r, BIG)
+        master = torch.randn(S, device="cuda")
+        m, v = torch.rand(S, device="cuda") * 0.1, torch.rand(S, device="cuda") * 0.01
+        ref_p, ref_m, ref_v = master.clone(), m.clone(), v.clone()
+        adamw_reference(ref_p, shards[r] * 0.5, ref_m, ref_v, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3)
+        C.peer_adamw_publish(pc, replicas[r], master, shards[r], m, v, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, clip, 0.0)
+        torch.cuda.synchronize()
+        assert int(state[4]) == 0
+        torch.testing.assert_close(master, ref_p, atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(m, ref_m, atol=1e-6, rtol=1e-5)
+        torch.testing.assert_close(v, ref_v, atol=1e-7, rtol=1e-5)
+        for rep in replicas:  # the shard landed in EVERY replica
+            torch.testing.assert_close(rep[r * S:(r + 1) * S].float(), ref_p.bfloat16().float(), atol=0, rtol=0)
+
+
+def test_wait_runs_out_and_reports_status():
+    """A flag that nothing sets: the kernel gives up after its budget, records the code and the context stays usable."""
+    C = _C()
+    arenas = [torch.zeros(1024, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    pc, flags, state = _local_comm(C, arenas, 0, 0, wait_s=0.3)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    C.peer_barrier(pc)
+    t1.record()
+    torch.cuda.synchronize()
+    assert 250 < t0.elapsed_time(t1) < 5000
+    assert int(state[4]) == 341  # entry wait of the barrier kernel on peer 1
+    assert int(flags[1][0]) == 1  # the publish to the "peer" still happened
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def test_scatter_copy_table():
+    from unirl_b200.distributed.weight_sync.full.reshard import CopyOp, execute_copy
+    from unirl_b200.parallel.fused_collectives import reshard_scatter_local
+
+    torch.manual_seed(2)
+    src = torch.randn(64 * 96, device="cuda").bfloat16()
+    dst_a, dst_b = torch.zeros(64 * 48, device="cuda", dtype=torch.bfloat16), torch.zeros(37, device="cuda", dtype=torch.bfloat16)
+    plan = [(src, dst_a, CopyOp("w", 0, 48, 0, 64, 48, 96, 48)), (src, dst_b, CopyOp("b", 0, 5, 0, 1, 37, 37, 37))]
+    assert reshard_scatter_local(plan)
+    ra, rb = torch.zeros_like(dst_a), torch.zeros_like(dst_b)
+    execute_copy(plan[0][2], src, ra)
+    execute_copy(plan[1][2], src, rb)
+    assert torch.equal(dst_a, ra) and torch.equal(dst_b, rb)
+
+
+# ------------------------------------------------------------------------------------------------ two ranks
+def _two_rank_body(rank, world):
+    import torch.distributed as dist
+
+    from unirl_b200.distributed.group.comm import Comm
+    from unirl_b200.parallel.fused_collectives import FusedAllReduce, FusedShardComm
+    from unirl_b200.parallel.flat_shard import FlatShardedModel, ShardComm
+
+    dev = torch.device("cuda", rank)
+    comm = Comm.world()
+    out = {}
+    # -- TP projection + all-reduce + residual + norm, many calls (both staging halves, epochs advance)
+    torch.manual_seed(0)
+    T, K, H = 48, 512, 1024
+    w_full = torch.randn(H, K * world, device=dev).bfloat16() * 0.05
+    x_full = torch.randn(T, K * world, device=dev).bfloat16()
+    res = torch.randn(T, H, device=dev).bfloat16()
+    nw = (1 + 0.1 * torch.randn(H, device=dev)).bfloat16()
+    far = FusedAllReduce(comm, 64, H, dev, wait_s=10.0)
+    errs = []
+    for it in range(5):
+        xs = (x_full * (it + 1)).bfloat16()
+        x, h = far.proj_reduce_norm(xs[:, rank * K:(rank + 1) * K].contiguous(), w_full[:, rank * K:(rank + 1) * K].contiguous(), res, nw, 1e-6)
+        y = torch.matmul(xs[:, rank * K:(rank + 1) * K], w_full[:, rank * K:(rank + 1) * K].t()).float()
+        dist.all_reduce(y)
+        want = y + res.float()
+        errs.append(float((x.float() - want).abs().max() / want.abs().max()))
+        hw = want * torch.rsqrt(want.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+        errs.append(float((h.float() - hw).abs().max() / hw.abs().max()))
+    far.align()
+    far.arena.check()
+    out["ar_err"] = max(errs)
+    # -- sharded trainer: fused vs library collectives on the same toy model
+    def build(fused):
+        torch.manual_seed(3)
+        m = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 256)).to(dev).bfloat16()
+        return m, FlatShardedModel(m, comm, block_class_names=("Linear",), shard_comm=FusedShardComm(comm, wait_s=10.0) if fused else ShardComm(comm))
+    results = []
+    for fused in (False, True):
+        m, sh = build(fused)
+        for step in range(3):
+            sh.zero_grad()
+            sh.set_grad_sync(True)
+            torch.manual_seed(100 + step * world + rank)
+            xb = torch.randn(32, 256, device=dev).bfloat16()
+            m(xb).float().pow(2).mean().backward()
+            sh.finish_grad_sync()
+            norm = sh.grad_norm()
+            coef = torch.clamp(1.0 / (norm + 1e-6), max=1.0).float().reshape(1)
+            sh.optimizer_step(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01, step=step + 1, clip_coef=coef)
+            sh.shard_comm.check()
+        torch.cuda.synchronize()
+        results.append((float(norm), torch.cat([p.detach().float().reshape(-1) for p in m.parameters()]).cpu()))
+    out["norm_nccl"], out["norm_fused"] = results[0][0], results[1][0]
+    out["param_diff"] = float((results[0][1] - results[1][1]).abs().max())
+    gathered = [torch.zeros_like(results[1][1]) for _ in range(world)]
+    dist.all_gather_object(gathered, results[1][1])
+    out["replica_diff"] = float(max((g - gathered[0]).abs().max() for g in gathered))
+    return out
+
+
+@pytest.mark.multigpu
+def test_two_rank_fused_collectives_match_library():
+    outs = run_ranks(_two_rank_body, 2, cuda=True, timeout=300)
+    for o in outs:
+        assert o["ar_err"] < 2e-2, o
+        assert abs(o["norm_nccl"] - o["norm_fused"]) <= 1e-3 * max(1.0, o["norm_nccl"]), o
+        assert o["param_diff"] <= 1e-2, o  # bf16 replicas after 3 steps
+        assert o["replica_diff"] == 0.0, o  # every rank holds the same replica

@@ -112,3 +112,19 @@ def test_mp_pool_detects_dead_worker():
             c.who()
     finally:
         pool.shutdown()
+
+
+def test_tensor_meta_slice_cuts_through_a_handle_without_copy():
+    """A DP=2 consumer of a DP=1 producer: the row range is a window of the single stored tensor."""
+    from unirl_b200.distributed.tensor.transport import TensorMeta, WorkerLocalTransport
+
+    tr = WorkerLocalTransport(0, torch.device("cpu"))
+    full = torch.arange(64 * 3, dtype=torch.float32).reshape(64, 3)
+    meta = TensorMeta.from_refs([tr.put(full[:40]), tr.put(full[40:])])
+    a, b = meta.chunk(2)
+    assert a.batch_size == b.batch_size == 32 and len(a.refs) == 1 and len(b.refs) == 2
+    assert torch.equal(tr.get(a.refs), full[:32]) and torch.equal(tr.get(b.refs), full[32:])
+    assert b.refs[0].base is not None and b.refs[0].lo == 32 and b.refs[1].base is None
+    inner = b.slice(4, 12)  # window of a window
+    assert torch.equal(tr.get(inner.refs), full[36:44])
+    assert tr.get(a.refs).data_ptr() == tr.store.get(meta.refs[0].key).data_ptr()  # a view, not a copy

@@ -316,6 +316,79 @@ Tensor paged_decode_attention(const Tensor& q, const Tensor& kc, const Tensor& v
   return out;
 }
 
+// ---------------------------------------------------------------------------------------------- peer-memory collectives
+// Python owns the symmetric allocations (torch symmetric memory); this object only carries their addresses.
+struct PyPeerComm {
+  ub::PeerComm c;
+  Tensor state;  // int32[8]: [0]=tick [1..2]=ctr [4]=status — keeps the device words alive
+  PyPeerComm(std::vector<int64_t> bufs, std::vector<int64_t> flags, int rank, Tensor st, double wait_s) : state(std::move(st)) {
+    TORCH_CHECK(bufs.size() == flags.size() && !bufs.empty() && (int)bufs.size() <= ub::kMaxPeers, "PeerComm: 1..8 ranks");
+    TORCH_CHECK(state.is_cuda() && state.scalar_type() == at::kInt && state.numel() >= 8 && state.is_contiguous(), "PeerComm: state must be int32[8] on the device");
+    for (size_t i = 0; i < bufs.size(); ++i) { c.bufs[i] = bufs[i]; c.flags[i] = flags[i]; }
+    c.rank = rank; c.world = (int)bufs.size();
+    c.tick = reinterpret_cast<uint32_t*>(state.data_ptr<int>());
+    c.ctr = c.tick + 1;
+    c.status = state.data_ptr<int>() + 4;
+    c.wait_ns = (unsigned long long)(wait_s * 1e9);
+  }
+  void set_bufs(std::vector<int64_t> bufs) {
+    TORCH_CHECK((int)bufs.size() == c.world, "PeerComm.set_bufs: world mismatch");
+    for (size_t i = 0; i < bufs.size(); ++i) c.bufs[i] = bufs[i];
+  }
+  int64_t base() const { return c.bufs[c.rank]; }
+  // byte distance of a local tensor from this rank's arena base, in elements of the tensor's dtype
+  int64_t offset_of(const Tensor& t) const {
+    const int64_t d = (int64_t)reinterpret_cast<uintptr_t>(t.data_ptr()) - base();
+    TORCH_CHECK(d >= 0 && d % t.element_size() == 0, "tensor does not live in this communicator's arena");
+    return d / t.element_size();
+  }
+};
+
+void peer_allreduce_residual_rmsnorm(PyPeerComm& pc, const Tensor& part, c10::optional<Tensor> residual, c10::optional<Tensor> w, Tensor& x_out,
+                                     c10::optional<Tensor> h_out, double eps) {
+  chk(part, "partial"); chk(x_out, "x_out");
+  TORCH_CHECK(part.scalar_type() == at::kBFloat16 && part.dim() == 2 && x_out.sizes() == part.sizes(), "peer all-reduce: bf16 [T, H]");
+  c10::cuda::CUDAGuard g(part.device());
+  const int rc = ub::peer_allreduce_residual_rmsnorm(pc.c, pc.offset_of(part), optr(residual), optr(w), x_out.data_ptr(),
+                                                     h_out.has_value() && h_out->defined() ? h_out->data_ptr() : nullptr, part.size(0), (int)part.size(1),
+                                                     (float)eps, stream());
+  TORCH_CHECK(rc == 0, "peer_allreduce_residual_rmsnorm: unsupported shape or launch failure (code ", rc, ")");
+}
+void peer_reduce_scatter_sumsq(PyPeerComm& pc, const Tensor& grad_full, Tensor& out, c10::optional<Tensor> sumsq, double scale) {
+  chk(grad_full, "grad"); chk(out, "out");
+  TORCH_CHECK(grad_full.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat && grad_full.numel() == out.numel() * pc.c.world, "peer reduce-scatter: fp32, grad = world * out");
+  c10::cuda::CUDAGuard g(out.device());
+  const int rc = ub::peer_reduce_scatter_sumsq(pc.c, pc.offset_of(grad_full), out.numel(), out.data_ptr<float>(),
+                                               sumsq.has_value() && sumsq->defined() ? sumsq->data_ptr<float>() : nullptr, (float)scale, stream());
+  TORCH_CHECK(rc == 0, "peer_reduce_scatter_sumsq: unsupported shape or launch failure (code ", rc, ")");
+}
+void peer_adamw_publish(PyPeerComm& pc, const Tensor& replica_full, Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, c10::optional<Tensor> ema,
+                        double lr, double b1, double b2, double eps, double wd, int64_t step, c10::optional<Tensor> clip, double ema_decay) {
+  chk(replica_full, "replica"); chk(master, "master"); chk(grad, "grad"); chk(m, "exp_avg"); chk(v, "exp_avg_sq");
+  TORCH_CHECK(replica_full.scalar_type() == at::kBFloat16 && master.scalar_type() == at::kFloat && grad.scalar_type() == at::kFloat &&
+                  m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "peer adamw: bf16 replica, fp32 state");
+  TORCH_CHECK(replica_full.numel() == master.numel() * pc.c.world && grad.numel() == master.numel() && m.numel() == master.numel() && v.numel() == master.numel(),
+              "peer adamw: size mismatch");
+  c10::cuda::CUDAGuard g(master.device());
+  const int rc = ub::peer_adamw_publish(pc.c, pc.offset_of(replica_full), master.numel(), master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(),
+                                        v.data_ptr<float>(), ema.has_value() && ema->defined() ? ema->data_ptr<float>() : nullptr, (float)lr, (float)b1,
+                                        (float)b2, (float)eps, (float)wd, step, clip.has_value() && clip->defined() ? clip->data_ptr<float>() : nullptr,
+                                        (float)ema_decay, stream());
+  TORCH_CHECK(rc == 0, "peer_adamw_publish: unsupported shape or launch failure (code ", rc, ")");
+}
+void peer_scatter_copy(const Tensor& table, int64_t n_ops, int64_t max_vecs) {
+  chk(table, "table");
+  TORCH_CHECK(table.scalar_type() == at::kLong && table.numel() >= n_ops * 6, "scatter_copy: int64 table of 6 words per copy");
+  c10::cuda::CUDAGuard g(table.device());
+  const int rc = ub::peer_scatter_copy(table.data_ptr(), (int)n_ops, max_vecs, stream());
+  TORCH_CHECK(rc == 0, "peer_scatter_copy: launch failure (code ", rc, ")");
+}
+void peer_barrier(PyPeerComm& pc) {
+  c10::cuda::CUDAGuard g(pc.state.device());
+  const int rc = ub::peer_barrier(pc.c, stream());
+  TORCH_CHECK(rc == 0, "peer_barrier: launch failure (code ", rc, ")");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -345,6 +418,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("linear_sample", &linear_sample);
   m.def("decode_workspace_size", &decode_workspace_size);
   m.def("paged_decode_attention", &paged_decode_attention);
+  py::class_<PyPeerComm>(m, "PeerComm")
+      .def(py::init<std::vector<int64_t>, std::vector<int64_t>, int, Tensor, double>(), py::arg("bufs"), py::arg("flags"), py::arg("rank"), py::arg("state"),
+           py::arg("wait_s") = 20.0)
+      .def("set_bufs", &PyPeerComm::set_bufs)
+      .def("offset_of", &PyPeerComm::offset_of)
+      .def_readonly("state", &PyPeerComm::state);
+  m.def("peer_allreduce_residual_rmsnorm", &peer_allreduce_residual_rmsnorm);
+  m.def("peer_reduce_scatter_sumsq", &peer_reduce_scatter_sumsq);
+  m.def("peer_adamw_publish", &peer_adamw_publish);
+  m.def("peer_scatter_copy", &peer_scatter_copy);
+  m.def("peer_barrier", &peer_barrier);
   py::class_<ub::BlockAllocator>(m, "BlockAllocator")
       .def(py::init<int64_t>())
       .def("reset", &ub::BlockAllocator::reset)

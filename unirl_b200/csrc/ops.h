@@ -61,4 +61,23 @@ int64_t decode_workspace_floats(int B, int Hq, int D, int num_splits);
 int paged_decode_attention(const void* q, const void* kc, const void* vc, const int* block_tables, const int* seq_lens, void* out, float* workspace,
                            int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, int* status, cudaStream_t s);
 
+// ---- peer.cu (fused compute + collective kernels over NVLink peer memory) ----------------------------------------
+constexpr int kMaxPeers = 8;
+struct PeerComm {
+  int64_t bufs[kMaxPeers];   // base address of every rank's symmetric data arena (index = rank)
+  int64_t flags[kMaxPeers];  // every rank's symmetric flag pad (4 * kMaxPeers uint32, zero-initialised)
+  int rank = 0, world = 1;
+  uint32_t* tick = nullptr;  // local device word, starts at 0
+  uint32_t* ctr = nullptr;   // local device counters (2 words, zero)
+  int* status = nullptr;     // local device word: 0, or the code of the first wait that ran out of time
+  unsigned long long wait_ns = 20000000000ull;
+};
+int peer_allreduce_residual_rmsnorm(const PeerComm& c, int64_t part_offset, const void* residual, const void* w, void* x_out, void* h_out, int64_t T,
+                                    int H, float eps, cudaStream_t s);
+int peer_reduce_scatter_sumsq(const PeerComm& c, int64_t grad_offset, int64_t shard, float* out, float* sumsq, float scale, cudaStream_t s);
+int peer_adamw_publish(const PeerComm& c, int64_t replica_offset, int64_t shard, float* master, const float* grad, float* m, float* v, float* ema, float lr,
+                       float b1, float b2, float eps, float wd, int64_t step, const float* clip, float ema_decay, cudaStream_t s);
+int peer_scatter_copy(const void* ops_dev, int n_ops, int64_t max_vecs, cudaStream_t s);
+int peer_barrier(const PeerComm& c, cudaStream_t s);
+
 }  // namespace ub

@@ -301,7 +301,7 @@ class DevicePool:
 
     # ---- tensors -------------------------------------------------------------------------------------
     def move(self, hops: Sequence[tuple]) -> Dict[tuple, TensorRef]:
-        """Execute ``(src, dst, ref)`` hops; returns ``{(src, key, dst): new_ref}``."""
+        """Execute ``(src, dst, ref)`` hops; returns ``{(*ref.ident, dst): new_ref}``."""
         mapping: Dict[tuple, TensorRef] = {}
         for src, dst, ref in hops:
             if self.backend == "spmd":
@@ -319,7 +319,7 @@ class DevicePool:
                 fr = self.workers[dst].submit("transport_op", "recv", ref, src)
                 fs.result()
                 new = fr.result()
-            mapping[(src, ref.key, dst)] = self.adopt(new)
+            mapping[(*ref.ident, dst)] = self.adopt(new)
         return mapping
 
     def fetch(self, refs: Sequence[TensorRef]) -> torch.Tensor:
@@ -346,7 +346,9 @@ class DevicePool:
             pass
 
     def adopt(self, ref: TensorRef) -> TensorRef:
-        """Tie the stored tensor's lifetime to this controller-side ref object."""
+        """Tie the stored tensor's lifetime to this controller-side ref object (windows ride on their parent)."""
+        if ref.base is not None:
+            return ref
         weakref.finalize(ref, DevicePool._release_static, weakref.ref(self), ref.owner, ref.key, ref.shape, ref.dtype, ref.device)
         return ref
 

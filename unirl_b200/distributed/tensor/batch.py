@@ -365,7 +365,10 @@ class Batch:
                 out[f.name] = _join(vals, sizes)
             elif kind is FieldKind.PACKED:
                 live = [v for v in vals if v is not None]
-                out[f.name] = torch.cat(live, 0) if live else None
+                if live and isinstance(live[0], Batch):  # tensor handles: join the handle lists, rows stay where they are
+                    out[f.name] = type(live[0]).concat(live)
+                else:
+                    out[f.name] = torch.cat(live, 0) if live else None
             elif kind in _FOLD_KINDS:
                 out[f.name] = _fold(vals, kind)
             else:

@@ -24,7 +24,7 @@ import abc
 import contextlib
 import itertools
 import threading
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, Callable, ClassVar, Dict, Iterator, List, Optional, Sequence, Tuple
 
 import torch
@@ -35,15 +35,36 @@ from unirl_b200.distributed.utils import map_leaves
 
 @dataclass(frozen=True)
 class TensorRef:
+    """One stored tensor, or a window of ``shape[0]`` rows starting at row ``lo`` of it.
+
+    A window keeps its parent ref object alive through ``base`` (the stored tensor's lifetime is tied to the
+    parent object on the controller), so slicing a handle never copies and never frees early.
+    """
+
     owner: int
     key: int
     shape: Tuple[int, ...]
     dtype: torch.dtype
     device: str
+    lo: int = 0
+    base: Optional["TensorRef"] = field(default=None, compare=False, repr=False)
 
     @property
     def rows(self) -> int:
         return int(self.shape[0]) if self.shape else 1
+
+    def window(self, start: int, end: int) -> "TensorRef":
+        if not self.shape:
+            raise ValueError("a scalar ref has no rows to window")
+        if not (0 <= start <= end <= self.rows):
+            raise IndexError(f"window [{start}:{end}) outside {self.rows} rows")
+        if start == 0 and end == self.rows:
+            return self
+        return TensorRef(self.owner, self.key, (end - start, *self.shape[1:]), self.dtype, self.device, self.lo + start, self.base or self)
+
+    @property
+    def ident(self) -> Tuple[int, int, int, int]:
+        return (self.owner, self.key, self.lo, self.rows)
 
 
 class TensorTransportRuntime:
@@ -109,15 +130,21 @@ class TensorMeta(Batch):
         raise NotImplementedError("TensorMeta.select: hydrate first")
 
     def slice(self, start: int, end: int) -> "TensorMeta":
-        """Row range → ref range.  Only ranges that fall on ref boundaries are representable."""
-        bounds = [0, *itertools.accumulate(int(s) for s in self.sizes)]
-        try:
-            i0, i1 = bounds.index(int(start)), len(bounds) - 1 - bounds[::-1].index(int(end))
-        except ValueError:
-            raise NotImplementedError(
-                f"TensorMeta rows [{start}:{end}) do not fall on handle boundaries {bounds}; hydrate first"
-            ) from None
-        return self._with_refs(self.refs[i0:i1], self.sizes[i0:i1])
+        """Row range → the refs (whole, or windows of them) that cover it; no data moves."""
+        start, end = max(0, int(start)), min(int(end), self.batch_size)
+        refs, sizes, off = [], [], 0
+        for r, n in zip(self.refs, self.sizes):
+            a, b = max(start, off), min(end, off + int(n))
+            if a < b:
+                if a == off and b == off + int(n):
+                    refs.append(r)
+                elif isinstance(r, TensorRef):
+                    refs.append(r.window(a - off, b - off))
+                else:
+                    raise NotImplementedError(f"TensorMeta rows [{start}:{end}) cut through a non-windowable ref {type(r).__name__}; hydrate first")
+                sizes.append(b - a)
+            off += int(n)
+        return self._with_refs(refs, sizes)
 
     def __getitem__(self, key) -> "TensorMeta":
         if isinstance(key, slice) and key.step in (None, 1):
@@ -292,15 +319,21 @@ class WorkerLocalTransport(TensorTransport):
         for r in refs:
             if r.owner != self.worker_id:
                 raise RuntimeError(f"worker {self.worker_id}: ref {r.key} is owned by worker {r.owner}; localize it first")
-            parts.append(self.store.get(r.key))
+            parts.append(self._resolve(r))
         if len(parts) == 1:
             return parts[0]
         if parts and parts[0].dim() == 0:
             return torch.stack(parts)
         return torch.cat(parts, 0)
 
+    def _resolve(self, ref: TensorRef) -> torch.Tensor:
+        t = self.store.get(ref.key)
+        if t.dim() and ref.shape and (ref.lo or ref.rows != t.shape[0]):
+            t = t[ref.lo : ref.lo + ref.rows]
+        return t
+
     def free(self, ref: TensorRef) -> None:
-        if ref.owner == self.worker_id:
+        if ref.owner == self.worker_id and ref.base is None:
             self.store.decref(ref.key)
 
     # ---- remote ops (invoked by the controller through Worker.transport_op) -------------------
@@ -311,7 +344,7 @@ class WorkerLocalTransport(TensorTransport):
         self.store.decref(ref.key)
 
     def send(self, ref: TensorRef, dst: int) -> None:
-        self.comm.send(self.store.get(ref.key), dst)
+        self.comm.send(self._resolve(ref).contiguous(), dst)
 
     def recv(self, ref: TensorRef, src: int) -> TensorRef:
         dev = self.device if ref.device.startswith("cuda") else torch.device("cpu")
@@ -320,10 +353,10 @@ class WorkerLocalTransport(TensorTransport):
         return self.store.put(buf)
 
     def get_cpu(self, ref: TensorRef) -> torch.Tensor:
-        return self.store.get(ref.key).detach().cpu()
+        return self._resolve(ref).detach().cpu()
 
     def tensor_op(self, ref: TensorRef, op: str, *args: Any) -> TensorRef:
-        t = self.store.get(ref.key)
+        t = self._resolve(ref)
         if op == "getitem":
             out = t[args[0]]
         elif op == "reshape":
@@ -355,8 +388,8 @@ def plan_localize(per_worker_payloads: Sequence[Any], worker_ids: Sequence[int])
     for payload, dst in zip(per_worker_payloads, worker_ids):
         for _path, meta, _set in iter_leaves(payload, TensorMeta):
             for r in meta.refs:
-                if isinstance(r, TensorRef) and r.owner != dst and (r.owner, r.key, dst) not in seen:
-                    seen.add((r.owner, r.key, dst))
+                if isinstance(r, TensorRef) and r.owner != dst and (*r.ident, dst) not in seen:
+                    seen.add((*r.ident, dst))
                     hops.append((r.owner, dst, r))
     return hops
 
@@ -365,7 +398,7 @@ def rewrite_refs(payload: Any, mapping: Dict[Tuple[int, int, int], TensorRef], d
     """Substitute foreign refs in ``payload`` by their localized copies on ``dst``."""
 
     def fix(meta: TensorMeta) -> TensorMeta:
-        new = [mapping.get((r.owner, r.key, dst), r) if isinstance(r, TensorRef) else r for r in meta.refs]
+        new = [mapping.get((*r.ident, dst), r) if isinstance(r, TensorRef) else r for r in meta.refs]
         out = meta._with_refs(new, meta.sizes)
         out.grad, out.retain_grad_flag = meta.grad, meta.retain_grad_flag
         if new:

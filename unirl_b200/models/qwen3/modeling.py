@@ -89,6 +89,7 @@ class TPContext:
     rank: int = 0
     size: int = 1
     all_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+    fused: Optional[Any] = None  # object with proj_reduce_norm(inp, weight, residual, norm_weight, eps) -> (x, h): GEMM + reduce + add + norm
 
     def reduce(self, x: torch.Tensor) -> torch.Tensor:
         return x if self.size == 1 or self.all_reduce is None else self.all_reduce(x)
@@ -153,6 +154,18 @@ class Qwen3DecoderLayer(nn.Module):
             A.kv_cache_write(k, v, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.slot_mapping)
         return A.varlen_attention(q, k, v, meta.cu_seqlens, meta.max_seqlen, True, self.scale)
 
+    def forward_fused_tp(self, x: torch.Tensor, h: torch.Tensor, meta: AttnMeta, next_norm: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Inference path under tensor parallelism: every row-parallel projection, its all-reduce, the residual add
+        and the following RMSNorm run as one GEMM plus one peer-memory kernel.  ``h`` is the already normed input;
+        returns the new residual stream and the input of the next block normed with ``next_norm``."""
+        c, fused = self.cfg, self.tp.fused
+        qkv = self._proj(h, "qkv_proj")
+        q, k, v = qk_norm_rope(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps)
+        attn = self.attention(q, k, v, meta).reshape(x.shape[0], self.n_q * c.head_dim)
+        x, h = fused.proj_reduce_norm(attn, self.o_proj, x, self.post_attention_layernorm, c.rms_norm_eps)
+        act = swiglu(self._proj(h, "gate_up_proj"))
+        return fused.proj_reduce_norm(act, self.down_proj, x, next_norm, c.rms_norm_eps)
+
     def forward(self, x: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         c = self.cfg
         h = rmsnorm(x, self.input_layernorm, c.rms_norm_eps)
@@ -212,6 +225,13 @@ class Qwen3Transformer(nn.Module):
     def forward(self, tokens: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         """``tokens [T]`` → final-normed hidden states ``[T, H]``."""
         x = self.embed_tokens[tokens]
+        if self.tp.size > 1 and self.tp.fused is not None and not torch.is_grad_enabled() and x.is_cuda \
+                and not any(getattr(l, "_lora_index", None) for l in self.layers):
+            h = rmsnorm(x, self.layers[0].input_layernorm, self.cfg.rms_norm_eps)
+            for i, layer in enumerate(self.layers):
+                nxt = self.layers[i + 1].input_layernorm if i + 1 < len(self.layers) else self.norm
+                x, h = layer.forward_fused_tp(x, h, meta, nxt)
+            return h
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled() and meta.mode == "train"
         for layer in self.layers:
             if ckpt:

@@ -56,10 +56,36 @@ class ParamSlot:
 
 
 class ShardComm:
-    """NCCL/gloo baseline collectives for the sharded runtime."""
+    """NCCL/gloo baseline collectives for the sharded runtime.
+
+    A subclass may also own the memory of the replicas and gradient buffers (``reserve`` / ``alloc_param`` /
+    ``alloc_grad``) and fold the parameter publish into the optimizer kernel (``fused_optimizer``).
+    """
+
+    fused_optimizer = False
+    persistent_grads = False
 
     def __init__(self, comm: Comm):
         self.comm = comm
+
+    def reserve(self, param_bytes: int, grad_bytes: int, device: Any) -> None:
+        """Called once with the total bytes of all replicas / gradient buffers before any group is built."""
+
+    def alloc_param(self, numel: int, dtype: torch.dtype, device: Any) -> torch.Tensor:
+        return torch.zeros(numel, dtype=dtype, device=device)
+
+    def alloc_grad(self, numel: int, device: Any) -> torch.Tensor:
+        return torch.zeros(numel, dtype=torch.float32, device=device)
+
+    def begin_grad_sync(self) -> None:
+        """Called when the last micro-batch of a step starts (before any reduce-scatter of that step)."""
+
+    def local_sumsq(self) -> Optional[torch.Tensor]:
+        """Σ of squared reduced gradients of this rank's shards if the reduce kernels accumulated it, else None."""
+        return None
+
+    def check(self) -> None:
+        """Raise if a device-side wait failed since the last check (no-op for library collectives)."""
 
     def reduce_scatter_grad(self, group: "FlatGroup") -> None:
         """``main_grad`` (fp32, full) → ``grad_shard`` (fp32, averaged over ranks)."""
@@ -76,8 +102,10 @@ class ShardComm:
 
 class FlatGroup:
     def __init__(self, name: str, named_params: Sequence[Tuple[str, nn.Parameter]], rank: int, world: int, device: Any,
-                 low_dtype: torch.dtype = torch.bfloat16, master_dtype: torch.dtype = torch.float32):
+                 low_dtype: torch.dtype = torch.bfloat16, master_dtype: torch.dtype = torch.float32, alloc: Optional[ShardComm] = None):
         self.name, self.rank, self.world = name, rank, world
+        self._alloc = alloc
+        self._persist_grad: Optional[torch.Tensor] = None
         self.low_dtype, self.master_dtype = low_dtype, master_dtype
         self.slots: List[ParamSlot] = []
         off = 0
@@ -85,10 +113,10 @@ class FlatGroup:
             self.slots.append(ParamSlot(n, p, off, p.numel(), tuple(p.shape)))
             off += _pad(p.numel(), 8)
         self.numel = off
-        self.padded = _pad(max(off, 1), world * ALIGN)
+        self.padded = self.padded_numel(named_params, world)
         self.shard_size = self.padded // world
         dev = torch.device(device)
-        self.flat_param = torch.zeros(self.padded, dtype=low_dtype, device=dev)
+        self.flat_param = alloc.alloc_param(self.padded, low_dtype, dev) if alloc is not None else torch.zeros(self.padded, dtype=low_dtype, device=dev)
         for s in self.slots:
             view = self.flat_param[s.offset : s.offset + s.numel].view(s.shape)
             view.copy_(s.param.data.to(low_dtype))
@@ -105,11 +133,22 @@ class FlatGroup:
         self._hooks: List[Any] = []
         self.trainable = any(s.param.requires_grad for s in self.slots)
 
+    @staticmethod
+    def padded_numel(named_params: Sequence[Tuple[str, nn.Parameter]], world: int) -> int:
+        return _pad(max(sum(_pad(p.numel(), 8) for _, p in named_params), 1), world * ALIGN)
+
     # ---- gradient buffers -----------------------------------------------------------------------
     def ensure_grad_buffers(self) -> None:
         if self.main_grad is None:
             dev = self.flat_param.device
-            self.main_grad = torch.zeros(self.padded, dtype=torch.float32, device=dev)
+            if self._alloc is not None and self._alloc.persistent_grads:
+                if self._persist_grad is None:
+                    self._persist_grad = self._alloc.alloc_grad(self.padded, dev)
+                else:
+                    self._persist_grad.zero_()
+                self.main_grad = self._persist_grad
+            else:
+                self.main_grad = torch.zeros(self.padded, dtype=torch.float32, device=dev)
             self.grad_shard = torch.zeros(self.shard_size, dtype=torch.float32, device=dev) if self.world > 1 else \
                 self.main_grad[: self.shard_size]
 
@@ -150,18 +189,29 @@ class FlatShardedModel:
     def _build_groups(self, block_names: Sequence[str], root_wrap: bool, low: torch.dtype, master: torch.dtype, trainable_only: bool) -> None:
         taken: set = set()
         want = set(block_names)
+        layout: List[Tuple[str, List[Tuple[str, nn.Parameter]]]] = []
         for mod_name, mod in self.module.named_modules():
             if type(mod).__name__ in want:
                 named = [(f"{mod_name}.{n}", p) for n, p in mod.named_parameters() if id(p) not in taken and (p.requires_grad or not trainable_only)]
                 if named:
                     taken.update(id(p) for _, p in named)
-                    self.groups.append(FlatGroup(mod_name, named, self.rank, self.world, self.device, low, master))
+                    layout.append((mod_name, named))
         rest = [(n, p) for n, p in self.module.named_parameters() if id(p) not in taken and (p.requires_grad or not trainable_only)]
         if rest:
             if not root_wrap and any(p.requires_grad for _, p in rest) and self.world > 1:
                 raise ValueError("root_wrap=False leaves trainable parameters outside every sharded group: "
                                  + ", ".join(n for n, p in rest if p.requires_grad)[:200])
-            self.groups.insert(0, FlatGroup("<root>", rest, self.rank, self.world, self.device, low, master))
+            layout.insert(0, ("<root>", rest))
+        sizes = [FlatGroup.padded_numel(named, self.world) for _, named in layout]
+        low_bytes = torch.empty((), dtype=low).element_size()
+        self.shard_comm.reserve(sum(s * low_bytes + 256 for s in sizes),
+                                sum(s * 4 + 256 for s, (_, named) in zip(sizes, layout) if any(p.requires_grad for _, p in named)), self.device)
+        for name, named in layout:
+            self.groups.append(FlatGroup(name, named, self.rank, self.world, self.device, low, master, alloc=self.shard_comm))
+        if self.world > 1 and self.shard_comm.persistent_grads:
+            for g in self.groups:  # symmetric layout: every rank allocates in the same order
+                if g.trainable:
+                    g._persist_grad = self.shard_comm.alloc_grad(g.padded, self.device)
 
     def _install_hooks(self) -> None:
         for g in self.groups:
@@ -195,6 +245,8 @@ class FlatShardedModel:
         """``True`` on the last micro-batch: groups reduce-scatter as soon as their backward completes."""
         self._sync_enabled = bool(enable)
         if enable:
+            if self.world > 1:
+                self.shard_comm.begin_grad_sync()
             for g in self.groups:
                 g._pending = sum(1 for s in g.slots if s.param.requires_grad)
                 g._reduced = False
@@ -220,9 +272,13 @@ class FlatShardedModel:
 
     def grad_norm(self) -> torch.Tensor:
         """Global L2 norm of the (averaged) gradient as a device scalar."""
-        parts = [O.sum_squares(g.grad_shard) for g in self.groups if g.trainable and g.grad_shard is not None]
-        total = torch.stack(parts).sum() if parts else torch.zeros((), device=self.device)
-        total = total.reshape(1).float()
+        fused = self.shard_comm.local_sumsq() if self.world > 1 else None
+        if fused is not None:
+            total = fused.clone().reshape(1)
+        else:
+            parts = [O.sum_squares(g.grad_shard) for g in self.groups if g.trainable and g.grad_shard is not None]
+            total = torch.stack(parts).sum() if parts else torch.zeros((), device=self.device)
+            total = total.reshape(1).float()
         self.comm.all_reduce(total)
         return total.sqrt().reshape(())
 
@@ -230,6 +286,10 @@ class FlatShardedModel:
                        clip_coef: Optional[torch.Tensor] = None, ema_decay: Optional[float] = None) -> None:
         for g in self.groups:
             if not g.trainable or g.grad_shard is None:
+                continue
+            if self.world > 1 and self.shard_comm.fused_optimizer:
+                self.shard_comm.adamw_publish(g, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, step=step, clip_coef=clip_coef,
+                                              ema=g.ema if ema_decay is not None else None, ema_decay=ema_decay or 0.0)
                 continue
             O.adamw_step(g.master, g.grad_shard, g.exp_avg, g.exp_avg_sq, lr=lr, beta1=betas[0], beta2=betas[1], eps=eps,
                          weight_decay=weight_decay, step=step, low=g.param_shard, ema=g.ema if ema_decay is not None else None,

@@ -72,7 +72,8 @@ class NativeARRolloutEngine(BaseRolloutEngine):
         if tp > 1:
             groups = [list(range(g * tp, (g + 1) * tp)) for g in range(ri.world_size // tp)]
             self.tp_comm = self.comm.split(groups)
-            tpc = TPContext(ri.tp_rank, tp, self._make_all_reduce())
+            ar = self._make_all_reduce()
+            tpc = TPContext(ri.tp_rank, tp, ar, fused=ar if hasattr(ar, "proj_reduce_norm") else None)
         else:
             tpc = TPContext()
         b = self._trainer_bundle
@@ -95,7 +96,12 @@ class NativeARRolloutEngine(BaseRolloutEngine):
             try:
                 from unirl_b200.parallel.fused_collectives import make_fused_all_reduce
 
-                fused = make_fused_all_reduce(comm)
+                b = self._trainer_bundle
+                mcfg = b.transformer.cfg if b is not None and getattr(b, "transformer", None) is not None else \
+                    resolve_model_config(self.config.pretrained_model_ckpt_path, self.config.model_overrides)
+                hidden = int(mcfg.hidden_size)
+                fused = make_fused_all_reduce(comm, max_tokens=max(int(self.config.prefill_token_budget), int(self.config.max_running_requests)),
+                                              hidden=hidden, device=self.device)
                 if fused is not None:
                     return fused
             except Exception as e:  # noqa: BLE001

@@ -184,12 +184,17 @@ class ARGenerator:
 
     def _graphed(self, step_fn, b: int, max_new: int, temperature: float, top_k: int, top_p: float):
         """Capture ``step_fn`` (which closes over this wave's state tensors) into a CUDA graph."""
+        fused = getattr(getattr(self.model, "tp", None), "fused", None)  # peer-memory all-reduce: replay must start on staging half 0
+        if fused is not None:
+            fused.align()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
         # capture itself does not execute the step, so the decode state is not advanced here
         with torch.cuda.graph(g, stream=s):
             step_fn()
+            if fused is not None:
+                fused.align()
         self._graphs[(b, max_new, temperature, top_k, top_p)] = g  # keep alive for the wave
         return g.replay
 

@@ -136,6 +136,7 @@ class FSDPBackend(Remote):
         sh.finish_grad_sync()
         norm_t = sh.grad_norm()
         grad_norm = float(norm_t)  # the one host sync of the step: also the skip verdict
+        sh.shard_comm.check()  # a peer wait that ran out of time raises here instead of training on a partial reduction
         if not math.isfinite(grad_norm):
             logger.warning("non-finite grad norm (%s) at optimizer step %d; skipping the update", grad_norm, self._optimizer_step_count)
             sh.zero_grad()
