@@ -88,3 +88,22 @@ def test_colocated_dp2_trainer_with_tp2_rollout_over_gloo():
         assert replicated and all(eng[0][k] == eng[1][k] == trn[0][k] for k in replicated)
     finally:
         tr.shutdown()
+
+
+@pytest.mark.timeout(900)
+def test_torchrun_spmd_backend_two_cpu_ranks():
+    """One process per rank under torchrun (every rank is controller and worker): DP=2 trainer + TP=2 engine over gloo."""
+    import subprocess
+    import sys
+
+    from unirl_b200.distributed.utils import free_port
+
+    ov = [o for o in _COLOC if not o.startswith(("num_devices", "rollout.config.tp_size", "rollout_parallel", "+pool_backend"))]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
+           str(free_port()), "-m", "unirl_b200.train_ar", "--config-name=ar/qwen3_4b_grpo_b200", *ov, "num_devices=2", "rollout.config.tp_size=2",
+           "rollout_parallel={tp: 2}", "rollout.config.model_precision=fp32", "rollout.config.max_running_requests=16", "num_rollouts=2"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=800, env={**os.environ, "OMP_NUM_THREADS": "2"})
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
+    lines = [ln for ln in p.stdout.splitlines() if ln.startswith("rollout 2/2")]
+    assert len(lines) == 2 and lines[0] == lines[1], "both ranks run the same controller and agree on the step metrics"

@@ -140,6 +140,34 @@ class _ControllerTransport(TensorTransport):
         return tree
 
 
+class _SpmdTransport(TensorTransport):
+    """Transport of a process that is both controller and worker (one per GPU under ``torchrun``).
+
+    Inside a role method it is the worker's own store.  In controller code (which every rank runs identically) a
+    handle owned by another rank is fetched collectively, exactly like the dedicated controller would.
+    """
+
+    def __init__(self, pool: "DevicePool", inner: TensorTransport):
+        self.pool, self.inner = pool, inner
+
+    def __getattr__(self, name: str) -> Any:
+        return getattr(self.inner, name)
+
+    def put(self, tensor: torch.Tensor) -> TensorRef:
+        return self.inner.put(tensor)
+
+    def get(self, refs: Sequence[TensorRef]) -> torch.Tensor:
+        if self.pool._worker_depth == 0 and any(r.owner != self.inner.worker_id for r in refs):
+            return self.pool.fetch(refs)
+        return self.inner.get(refs)
+
+    def free(self, ref: TensorRef) -> None:
+        self.inner.free(ref)
+
+    def end_call(self) -> None:
+        self.inner.end_call()
+
+
 class DevicePool:
     def __init__(self, num_nodes: int = 1, gpus_per_node: Optional[int] = None, backend: Optional[str] = None,
                  tensor_transport: str = "colocate_store", call_timeout_s: float = 3600.0, device: Optional[str] = None,
@@ -163,10 +191,9 @@ class DevicePool:
         self.local_worker: Optional[Worker] = None
         self.world_comm = Comm.solo()
         self._force_device = device
+        self._worker_depth = 0  # > 0 while this process executes a role method (spmd: controller and worker share the process)
         getattr(self, f"_start_{self.backend}")()
-        TensorTransportRuntime.install(_ControllerTransport(self) if self.backend != "spmd" else self.local_worker.transport)
-        if self.backend == "spmd":
-            self._ctrl_transport = _ControllerTransport(self)
+        TensorTransportRuntime.install(_ControllerTransport(self) if self.backend != "spmd" else _SpmdTransport(self, self.local_worker.transport))
 
     # ---- bring-up --------------------------------------------------------------------------------
     def _dev(self, i: int) -> torch.device:
@@ -240,10 +267,13 @@ class DevicePool:
             if self.my_rank in devices:
                 import traceback
 
+                self._worker_depth += 1
                 try:
                     mine = getattr(self.local_worker, op)(*per_worker_args[list(devices).index(self.my_rank)])
                 except Exception:  # noqa: BLE001
                     err = traceback.format_exc()
+                finally:
+                    self._worker_depth -= 1
             gathered = self.world_comm.all_gather_object((mine, err))
             for r in devices:
                 if gathered[r][1] is not None:
@@ -276,10 +306,13 @@ class DevicePool:
             for devices, op, args in calls:
                 res = None
                 if self.my_rank in devices and err is None:
+                    self._worker_depth += 1
                     try:
                         res = getattr(self.local_worker, op)(*args[list(devices).index(self.my_rank)])
                     except Exception:  # noqa: BLE001
                         err = traceback.format_exc()
+                    finally:
+                        self._worker_depth -= 1
                 mine.append(res)
             gathered = self.world_comm.all_gather_object((mine, err))
             for r, (_m, e) in enumerate(gathered):
