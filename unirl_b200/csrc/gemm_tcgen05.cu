@@ -59,7 +59,9 @@ struct SmemLayout {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int kTileBytes = kStages * kStageBytes;
-  static constexpr int kTotal = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kStoreChunk = 32 * 128;                 // one epilogue store box: 32 rows x 64 bf16 (128-byte swizzled rows)
+  static constexpr int kStoreBytes = 4 * 2 * kStoreChunk;      // 4 epilogue warps x 2 buffers
+  static constexpr int kTotal = kTileBytes + kStoreBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 // Grouped rasterisation: consecutive tile ids sweep kGroupN adjacent n-tiles before advancing in m, so the ~148 tiles in
@@ -81,13 +83,15 @@ __device__ __forceinline__ void report(int* status, int code) {
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+                    const GemmParams p) {
   using L = SmemLayout<BN>;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = (2 * BN >= 32) ? 2 * BN : 32;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kTileBytes);
+  uint8_t* store_smem = smem + L::kTileBytes;  // 1024-byte aligned: the swizzle pattern of a store box starts at its first row
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kTileBytes + L::kStoreBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
   uint64_t* tfull = bars + 2 * kStages;
@@ -195,6 +199,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
+    uint32_t store_ctr = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int buf = it & 1;
       int m_idx, n_idx;
@@ -209,45 +214,59 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(q * 32) << 16);
 
-      if (EPI == kEpiStore || EPI == kEpiResidual) {
-        const int n0 = n_idx * BN;
+      if (EPI == kEpiStore || EPI == kEpiResidual || EPI == kEpiSwiGLU) {
+        // Accumulator -> bf16 -> swizzled shared-memory box -> one TMA store per 32 x 64 box.  A thread owns one row
+        // of the box (128 bytes = 8 chunks of 16 bytes); chunk j of row r lives at r * 128 + ((j ^ (r & 7)) << 4).
+        constexpr int kOutCols = (EPI == kEpiSwiGLU) ? BN / 2 : BN;
+        const int n0 = n_idx * kOutCols;
+        uint8_t* warp_stage = store_smem + q * (2 * L::kStoreChunk);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          float acc[32];
-          tmem_ld_32x32(t_row + c0, acc);
-          tmem_ld_wait();
-          if (row_ok) {
-            bf16* crow = p.C + static_cast<int64_t>(row) * p.ldc + n0 + c0;
+        for (int c0 = 0; c0 < kOutCols; c0 += 64) {
+          if (n0 + c0 >= p.N) break;  // uniform over the warp: the rest of the tile is outside the matrix
+          uint8_t* sbuf = warp_stage + (store_ctr & 1) * L::kStoreChunk;
+          if (lane == 0) tma_store_wait_read<1>();  // the store issued from this buffer two boxes ago has read it
+          __syncwarp();
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (n0 + c0 + g * 8 < p.N) {
-                if (EPI == kEpiResidual) {
-                  float r[8];
-                  load8(p.R + static_cast<int64_t>(row) * p.ldc + n0 + c0 + g * 8, r);
+          for (int h = 0; h < 2; ++h) {
+            float acc[32];
+            if (EPI == kEpiSwiGLU) {
+              float up[32];
+              tmem_ld_32x32(t_row + c0 + h * 32, acc);
+              tmem_ld_32x32(t_row + BN / 2 + c0 + h * 32, up);
+              tmem_ld_wait();
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) acc[g * 8 + j] += r[j];
+              for (int j = 0; j < 32; ++j) acc[j] = acc[j] / (1.f + __expf(-acc[j])) * up[j];
+            } else {
+              tmem_ld_32x32(t_row + c0 + h * 32, acc);
+              tmem_ld_wait();
+              if (EPI == kEpiResidual && row_ok) {
+                const bf16* rrow = p.R + static_cast<int64_t>(row) * p.ldc + n0 + c0 + h * 32;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  if (n0 + c0 + h * 32 + g * 8 < p.N) {
+                    float r[8];
+                    load8(rrow + g * 8, r);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[g * 8 + j] += r[j];
+                  }
                 }
-                store8(crow + g * 8, acc + g * 8);
               }
             }
-          }
-        }
-      } else if (EPI == kEpiSwiGLU) {
-        const int n0 = n_idx * (BN / 2);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
-          float gate[32], up[32];
-          tmem_ld_32x32(t_row + c0, gate);
-          tmem_ld_32x32(t_row + BN / 2 + c0, up);
-          tmem_ld_wait();
-          if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) gate[j] = gate[j] / (1.f + __expf(-gate[j])) * up[j];
-            bf16* crow = p.C + static_cast<int64_t>(row) * p.ldc + n0 + c0;
+            for (int g = 0; g < 4; ++g) {
+              Pack8 pk;
 #pragma unroll
-            for (int g = 0; g < 4; ++g)
-              if (n0 + c0 + g * 8 < p.N) store8(crow + g * 8, gate + g * 8);
+              for (int j = 0; j < 4; ++j) pk.h[j] = __floats2bfloat162_rn(acc[g * 8 + 2 * j], acc[g * 8 + 2 * j + 1]);
+              *reinterpret_cast<Pack8*>(sbuf + lane * 128 + (((h * 4 + g) ^ (lane & 7)) << 4)) = pk;
+            }
           }
+          fence_async_proxy();  // generic-proxy writes above become visible to the TMA engine
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, sbuf, n0 + c0, m0 + q * 32);
+            tma_store_commit();
+          }
+          ++store_ctr;
         }
       } else {  // kEpiLSE
         const int n0 = n_idx * BN;
@@ -315,6 +334,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + buf);
     }
+    if (lane == 0) tma_store_wait_all<0>();  // shared memory must outlive every store that reads it
   }
 
   tc_fence_before();
@@ -412,7 +432,7 @@ static int num_sms() {
 }
 
 template <int BN, int EPI>
-static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t s) {
+static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmParams& p, cudaStream_t s) {
   using L = SmemLayout<BN>;
   static bool configured = false;
   if (!configured) {
@@ -421,7 +441,7 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, L::kTotal, s>>>(tmA, tmB, p);
+  gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, L::kTotal, s>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -436,22 +456,23 @@ int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, in
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = static_cast<bf16*>(C); p.R = static_cast<const bf16*>(R); p.ldc = ldc; p.status = status;
   p.num_m_tiles = (M + BM - 1) / BM;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   if (!make_tensor_map_bf16(&tmA, A, M, K, lda, BM)) return 1;
+  if (!make_tensor_map_bf16(&tmC, C, M, N, ldc, 32)) return 1;  // epilogue store boxes: 32 rows x 64 columns
   if (epilogue == kEpiSwiGLU) {
     // B = [gate; up] with N rows each; output tile of 128 columns uses a 256-column accumulator.
     constexpr int BN = 256;
     p.num_n_tiles = (N + BN / 2 - 1) / (BN / 2);
     p.up_row_offset = N;
     if (!make_tensor_map_bf16(&tmB, B, 2 * (int64_t)N, K, ldb, BN / 2)) return 1;
-    return launch_variant<BN, kEpiSwiGLU>(tmA, tmB, p, s);
+    return launch_variant<BN, kEpiSwiGLU>(tmA, tmB, tmC, p, s);
   }
   const bool wide = g_force_bn ? g_force_bn == 256 : (N >= 256 * 2 || N % 256 == 0);
   const int BN = wide ? 256 : 128;
   p.num_n_tiles = (N + BN - 1) / BN;
   if (!make_tensor_map_bf16(&tmB, B, N, K, ldb, BN)) return 1;
-  if (epilogue == kEpiResidual) return wide ? launch_variant<256, kEpiResidual>(tmA, tmB, p, s) : launch_variant<128, kEpiResidual>(tmA, tmB, p, s);
-  return wide ? launch_variant<256, kEpiStore>(tmA, tmB, p, s) : launch_variant<128, kEpiStore>(tmA, tmB, p, s);
+  if (epilogue == kEpiResidual) return wide ? launch_variant<256, kEpiResidual>(tmA, tmB, tmC, p, s) : launch_variant<128, kEpiResidual>(tmA, tmB, tmC, p, s);
+  return wide ? launch_variant<256, kEpiStore>(tmA, tmB, tmC, p, s) : launch_variant<128, kEpiStore>(tmA, tmB, tmC, p, s);
 }
 
 int lse_num_tiles(int V) { return (V + 255) / 256; }
@@ -471,7 +492,7 @@ int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int l
   p.pbest = pbest; p.pbest_idx = pbest_idx; p.pbest_z = pbest_z; p.seed = seed; p.step = step; p.step_tensor = step_tensor;
   CUtensorMap tmA, tmB;
   if (!make_tensor_map_bf16(&tmA, H, M, K, ldh, BM) || !make_tensor_map_bf16(&tmB, W, V, K, ldw, BN)) return 1;
-  const int rc = launch_variant<BN, kEpiLSE>(tmA, tmB, p, s);
+  const int rc = launch_variant<BN, kEpiLSE>(tmA, tmB, tmA, p, s);  // no C matrix: the third map is unused
   if (rc) return rc;
   lse_merge_kernel<<<(M + 7) / 8, 256, 0, s>>>(pmax, psum, tgt_logit, pbest, pbest_idx, pbest_z, M, p.num_n_tiles, lse_out, logp_out, tok_out);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;

@@ -1,0 +1,441 @@
+"""Generic flow-matching diffusion transformer: one implementation, every DiT family a configuration of it.
+
+Three block kinds cover the image / video models the framework trains:
+
+``JointBlock``   two-stream MMDiT block (separate text and latent weights, one joint attention) — SD3 / SD3.5,
+                 FLUX double blocks, Qwen-Image, HunyuanVideo double blocks.  Optional second, latent-only attention
+                 (SD3.5-Medium "dual attention" layers).
+``SingleBlock``  single-stream block over the concatenated ``[text, latent]`` sequence with a fused
+                 ``[qkv | mlp-in]`` projection — FLUX / HunyuanVideo single blocks, Z-Image.
+``CrossBlock``   latent self-attention + text cross-attention + FFN with a learned per-block modulation table — WAN.
+
+Position information is either an additive 2-D sin-cos table cropped around its centre (SD3) or axial rotary
+embeddings over ``(frame, row, column)`` (everything else).  All linears go through ``ops.linear`` (tcgen05 GEMM for
+large token counts), adaLN through the fused LayerNorm-modulate kernel, attention through ``ops.attention`` — the
+model code holds no device-specific branches.
+
+Sequence parallelism (Ulysses): when ``sp`` is set, every rank holds ``L / P`` latent tokens; attention exchanges
+sequence shards for head shards with one all-to-all before and one after the core attention
+(``parallel/ulysses.py``).
+
+Reference behaviour covered: the diffusers transformers the reference wraps (``unirl/models/sd3/bundle.py``,
+``unirl/models/wan21/diffusion.py:62-158``, ``unirl/models/qwen_image/diffusion.py``, ``unirl/models/flux2_klein/diffusion.py``,
+``unirl/models/z_image/diffusion.py``, ``unirl/models/hunyuan_video*/diffusion.py``).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from unirl_b200.ops.attention import dense_attention
+from unirl_b200.ops.linear import linear
+from unirl_b200.ops.norm import layernorm_modulate, rmsnorm
+from unirl_b200.train.inject import lora_apply
+
+
+@dataclass
+class DiTConfig:
+    name: str = "dit"
+    hidden_size: int = 1536
+    num_heads: int = 24
+    head_dim: int = 64
+    in_channels: int = 16
+    out_channels: Optional[int] = None
+    patch_size: Tuple[int, int, int] = (1, 2, 2)  # (frames, rows, cols) per token
+    num_joint_blocks: int = 24
+    num_single_blocks: int = 0
+    num_cross_blocks: int = 0
+    dual_attention_blocks: Tuple[int, ...] = ()
+    text_dim: int = 4096
+    pooled_dim: int = 2048  # 0: no pooled-text conditioning
+    mlp_ratio: float = 4.0
+    ffn_dim: Optional[int] = None  # explicit FFN width (WAN); default hidden · mlp_ratio
+    qk_norm: bool = True
+    pos_embed: str = "rope"  # "sincos2d" (additive table) | "rope" (axial rotary)
+    pos_embed_max_size: int = 192
+    rope_axes: Tuple[int, int, int] = (16, 24, 24)  # head_dim split over (frame, row, col); must sum to head_dim
+    rope_theta: float = 10000.0
+    guidance_embed: bool = False
+    time_freq_dim: int = 256
+    eps: float = 1e-6
+    is_video: bool = False
+    vae_scale_factor: int = 8
+    vae_temporal_factor: int = 4
+    final_text_block: bool = True  # False: the last joint block does not update the text stream (SD3 "context_pre_only")
+
+    def __post_init__(self) -> None:
+        self.patch_size = tuple(int(p) for p in self.patch_size)
+        self.rope_axes = tuple(int(a) for a in self.rope_axes)
+        self.dual_attention_blocks = tuple(int(i) for i in self.dual_attention_blocks)
+        if self.hidden_size != self.num_heads * self.head_dim:
+            raise ValueError(f"hidden_size {self.hidden_size} != heads {self.num_heads} x head_dim {self.head_dim}")
+        if self.pos_embed == "rope" and sum(self.rope_axes) != self.head_dim:
+            raise ValueError(f"rope_axes {self.rope_axes} must sum to head_dim {self.head_dim}")
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * self.patch_size[0] * self.patch_size[1] * self.patch_size[2]
+
+    @property
+    def mlp_dim(self) -> int:
+        return int(self.ffn_dim) if self.ffn_dim else int(self.hidden_size * self.mlp_ratio)
+
+    def num_params(self) -> int:
+        h, m = self.hidden_size, self.mlp_dim
+        joint = 2 * (6 * h * h + 4 * h * h + 2 * h * m)
+        single = 3 * h * h + (3 * h + m) * h + (h + m) * h
+        cross = 4 * h * h + 4 * h * h + 2 * h * m
+        return self.num_joint_blocks * joint + self.num_single_blocks * single + self.num_cross_blocks * cross
+
+
+# --------------------------------------------------------------------------------------------------- embeddings
+def timestep_embedding(t: torch.Tensor, dim: int, max_period: float = 10000.0) -> torch.Tensor:
+    """Sinusoidal features of a scalar per sample (fp32), ``[B] → [B, dim]`` (cos first, as in DiT)."""
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
+    args = t.float()[:, None] * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], -1)
+
+
+def sincos_2d_table(dim: int, size: int, device: Any = "cpu") -> torch.Tensor:
+    """``[size, size, dim]`` fixed 2-D sin-cos table (half of the channels per axis)."""
+    def axis(n: int, d: int) -> torch.Tensor:
+        omega = 1.0 / (10000 ** (torch.arange(d // 2, dtype=torch.float64) / (d / 2)))
+        out = torch.arange(n, dtype=torch.float64)[:, None] * omega[None]
+        return torch.cat([out.sin(), out.cos()], -1)
+
+    rows, cols = axis(size, dim // 2), axis(size, dim // 2)
+    return torch.cat([rows[:, None].expand(size, size, -1), cols[None].expand(size, size, -1)], -1).float().to(device)
+
+
+def axial_rope(cfg: DiTConfig, grid: Tuple[int, int, int], device: Any, text_len: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin ``[text_len + F·H·W, head_dim/2]``: text tokens sit at the origin, latent tokens at ``(f, h, w)``."""
+    f, h, w = grid
+    pos = torch.stack(torch.meshgrid(torch.arange(f), torch.arange(h), torch.arange(w), indexing="ij"), -1).reshape(-1, 3).float()
+    if text_len:
+        pos = torch.cat([torch.zeros(text_len, 3), pos])
+    parts = []
+    for a, d in enumerate(cfg.rope_axes):
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+        parts.append(pos[:, a : a + 1] * inv[None])
+    ang = torch.cat(parts, -1).to(device)
+    return ang.cos(), ang.sin()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Interleaved-pair rotation of ``x [B, L, H, D]`` by per-token angles ``[L, D/2]``."""
+    xf = x.float().unflatten(-1, (-1, 2))
+    a, b = xf[..., 0], xf[..., 1]
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    return torch.stack([a * c - b * s, a * s + b * c], -1).flatten(-2).to(x.dtype)
+
+
+class _Lin(nn.Module):
+    """Weight (+ bias) holder whose matmul goes through the op layer; optional LoRA host.
+
+    ``targets`` names the adapter-addressable row ranges of a fused weight, e.g. a fused QKV projection exposes
+    ``{"to_q": (0, h), "to_k": (h, h), "to_v": (2h, h)}`` so recipes keep the per-projection target names.
+    """
+
+    def __init__(self, i: int, o: int, bias: bool = True, dtype: Any = None, device: Any = None, targets: Optional[Dict[str, Tuple[int, int]]] = None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(o, i, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(o, dtype=dtype, device=device)) if bias else None
+        self._targets = dict(targets or {})
+
+    def lora_targets(self) -> Dict[str, Tuple[str, int, int]]:
+        return {name: ("weight", off, rows) for name, (off, rows) in self._targets.items()}
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = linear(x, self.weight)
+        if getattr(self, "_lora_index", None):
+            y = lora_apply(self, "weight", x, y)
+        return y if self.bias is None else y + self.bias
+
+
+def _heads(x: torch.Tensor, n: int) -> torch.Tensor:
+    return x.unflatten(-1, (n, -1))
+
+
+def _qk_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    if w is None:
+        return x
+    return rmsnorm(x.reshape(-1, x.shape[-1]), w, eps).view_as(x)
+
+
+class _Attn(nn.Module):
+    """QKV + per-head RMS q/k norm + output projection for one stream."""
+
+    def __init__(self, cfg: DiTConfig, out_proj: bool = True, dtype: Any = None, device: Any = None, names: Sequence[str] = ("to_q", "to_k", "to_v", "to_out.0")):
+        super().__init__()
+        h = cfg.hidden_size
+        self.qkv = _Lin(h, 3 * h, True, dtype, device, {names[0]: (0, h), names[1]: (h, h), names[2]: (2 * h, h)})
+        self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.out = _Lin(h, h, True, dtype, device, {names[3]: (0, h)}) if out_proj else None
+        self.n, self.eps = cfg.num_heads, cfg.eps
+
+    def project(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        q, k, v = self.qkv(x).chunk(3, -1)
+        return _qk_norm(_heads(q, self.n), self.q_norm, self.eps), _qk_norm(_heads(k, self.n), self.k_norm, self.eps), _heads(v, self.n)
+
+
+class _MLP(nn.Module):
+    def __init__(self, cfg: DiTConfig, dtype: Any = None, device: Any = None, names: Sequence[str] = ("ff.net.0.proj", "ff.net.2")):
+        super().__init__()
+        self.fc1 = _Lin(cfg.hidden_size, cfg.mlp_dim, True, dtype, device, {names[0]: (0, cfg.mlp_dim)})
+        self.fc2 = _Lin(cfg.mlp_dim, cfg.hidden_size, True, dtype, device, {names[1]: (0, cfg.hidden_size)})
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.fc2(F.gelu(self.fc1(x), approximate="tanh"))
+
+
+class AttnContext:
+    """Per-forward attention geometry: rotary tables, text length, sequence-parallel context."""
+
+    def __init__(self, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], text_len: int, sp: Optional[Any] = None,
+                 text_mask: Optional[torch.Tensor] = None):
+        self.cos, self.sin, self.text_len, self.sp, self.text_mask = cos, sin, text_len, sp, text_mask
+
+    def rope(self, q: torch.Tensor, k: torch.Tensor, offset: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self.cos is None:
+            return q, k
+        c, s = self.cos[offset : offset + q.shape[1]], self.sin[offset : offset + q.shape[1]]
+        return apply_rope(q, c, s), apply_rope(k, c, s)
+
+    def attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_text: int = 0) -> torch.Tensor:
+        """``[B, L, H, D]`` bidirectional attention; with Ulysses the last ``L − n_text`` tokens are this rank's shard."""
+        if self.sp is not None and self.sp.size > 1:
+            return self.sp.attention(q, k, v, n_text)
+        return dense_attention(q, k, v)
+
+
+class JointBlock(nn.Module):
+    def __init__(self, cfg: DiTConfig, idx: int, dtype: Any = None, device: Any = None):
+        super().__init__()
+        h = cfg.hidden_size
+        self.cfg, self.idx = cfg, idx
+        self.update_text = cfg.final_text_block or idx < cfg.num_joint_blocks - 1
+        self.dual = idx in cfg.dual_attention_blocks
+        self.img_mod = _Lin(h, (9 if self.dual else 6) * h, True, dtype, device)
+        self.txt_mod = _Lin(h, (6 if self.update_text else 2) * h, True, dtype, device)
+        self.img_attn = _Attn(cfg, True, dtype, device)
+        self.txt_attn = _Attn(cfg, self.update_text, dtype, device, ("add_q_proj", "add_k_proj", "add_v_proj", "to_add_out"))
+        self.img_attn2 = _Attn(cfg, True, dtype, device, ("attn2.to_q", "attn2.to_k", "attn2.to_v", "attn2.to_out.0")) if self.dual else None
+        self.img_mlp = _MLP(cfg, dtype, device)
+        self.txt_mlp = _MLP(cfg, dtype, device, ("ff_context.net.0.proj", "ff_context.net.2")) if self.update_text else None
+
+    def forward(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor, ctx: AttnContext) -> Tuple[torch.Tensor, torch.Tensor]:
+        eps = self.cfg.eps
+        im = self.img_mod(F.silu(vec)).chunk(9 if self.dual else 6, -1)
+        tm = self.txt_mod(F.silu(vec)).chunk(6 if self.update_text else 2, -1)
+        img_n = layernorm_modulate(img, im[0], im[1], eps)
+        img_n2 = layernorm_modulate(img, im[6], im[7], eps) if self.dual else None  # both norms see the block input
+        txt_n = layernorm_modulate(txt, tm[0], tm[1], eps)
+        qi, ki, vi = self.img_attn.project(img_n)
+        qt, kt, vt = self.txt_attn.project(txt_n)
+        nt = txt.shape[1]
+        q, k, v = torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1)
+        if ctx.cos is not None:
+            q, k = ctx.rope(q, k)
+        a = ctx.attend(q, k, v, nt).flatten(-2)
+        img = img + im[2].unsqueeze(1) * self.img_attn.out(a[:, nt:])
+        if self.dual:
+            q2, k2, v2 = self.img_attn2.project(img_n2)
+            img = img + im[8].unsqueeze(1) * self.img_attn2.out(ctx.attend(q2, k2, v2, 0).flatten(-2))
+        img = img + im[5].unsqueeze(1) * self.img_mlp(layernorm_modulate(img, im[3], im[4], eps))
+        if self.update_text:
+            txt = txt + tm[2].unsqueeze(1) * self.txt_attn.out(a[:, :nt])
+            txt = txt + tm[5].unsqueeze(1) * self.txt_mlp(layernorm_modulate(txt, tm[3], tm[4], eps))
+        return img, txt
+
+
+class SingleBlock(nn.Module):
+    def __init__(self, cfg: DiTConfig, idx: int, dtype: Any = None, device: Any = None):
+        super().__init__()
+        h, m = cfg.hidden_size, cfg.mlp_dim
+        self.cfg, self.idx = cfg, idx
+        self.mod = _Lin(h, 3 * h, True, dtype, device)
+        self.in_proj = _Lin(h, 3 * h + m, True, dtype, device, {"to_q": (0, h), "to_k": (h, h), "to_v": (2 * h, h), "proj_mlp": (3 * h, m)})  # one GEMM
+        self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.out_proj = _Lin(h + m, h, True, dtype, device, {"proj_out": (0, h)})
+
+    def forward(self, x: torch.Tensor, vec: torch.Tensor, ctx: AttnContext, n_text: int) -> torch.Tensor:
+        c = self.cfg
+        shift, scale, gate = self.mod(F.silu(vec)).chunk(3, -1)
+        y = self.in_proj(layernorm_modulate(x, shift, scale, c.eps))
+        q, k, v, m = y.split([c.hidden_size, c.hidden_size, c.hidden_size, c.mlp_dim], -1)
+        q, k = _qk_norm(_heads(q, c.num_heads), self.q_norm, c.eps), _qk_norm(_heads(k, c.num_heads), self.k_norm, c.eps)
+        q, k = ctx.rope(q, k)
+        a = ctx.attend(q, k, _heads(v, c.num_heads), n_text).flatten(-2)
+        return x + gate.unsqueeze(1) * self.out_proj(torch.cat([a, F.gelu(m, approximate="tanh")], -1))
+
+
+class CrossBlock(nn.Module):
+    def __init__(self, cfg: DiTConfig, idx: int, dtype: Any = None, device: Any = None):
+        super().__init__()
+        h = cfg.hidden_size
+        self.cfg, self.idx = cfg, idx
+        self.modulation = nn.Parameter(torch.zeros(6, h, dtype=dtype, device=device))  # added to the shared time projection
+        self.self_attn = _Attn(cfg, True, dtype, device)
+        self.cross_q = _Lin(h, h, True, dtype, device, {"attn2.to_q": (0, h)})
+        self.cross_kv = _Lin(h, 2 * h, True, dtype, device, {"attn2.to_k": (0, h), "attn2.to_v": (h, h)})
+        self.cross_q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.cross_k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.cross_out = _Lin(h, h, True, dtype, device, {"attn2.to_out.0": (0, h)})
+        self.cross_norm = nn.LayerNorm(h, eps=cfg.eps, dtype=dtype, device=device)
+        self.mlp = _MLP(cfg, dtype, device)
+
+    def forward(self, img: torch.Tensor, txt: torch.Tensor, tproj: torch.Tensor, ctx: AttnContext) -> torch.Tensor:
+        c = self.cfg
+        m = (tproj.unflatten(-1, (6, -1)) + self.modulation.unsqueeze(0)).unbind(1)
+        q, k, v = self.self_attn.project(layernorm_modulate(img, m[0], m[1], c.eps))
+        q, k = ctx.rope(q, k)
+        img = img + m[2].unsqueeze(1) * self.self_attn.out(ctx.attend(q, k, v, 0).flatten(-2))
+        xq = _qk_norm(_heads(self.cross_q(self.cross_norm(img)), c.num_heads), self.cross_q_norm, c.eps)
+        xk, xv = self.cross_kv(txt).chunk(2, -1)
+        xk = _qk_norm(_heads(xk, c.num_heads), self.cross_k_norm, c.eps)
+        mask = None if ctx.text_mask is None else ctx.text_mask[:, None, None, :].bool()
+        a = F.scaled_dot_product_attention(xq.transpose(1, 2), xk.transpose(1, 2), _heads(xv, c.num_heads).transpose(1, 2), attn_mask=mask)
+        img = img + self.cross_out(a.transpose(1, 2).flatten(-2))
+        return img + m[5].unsqueeze(1) * self.mlp(layernorm_modulate(img, m[3], m[4], c.eps))
+
+
+class DiTTransformer(nn.Module):
+    """``forward(latents, timestep, text, pooled) → velocity`` with the latents' shape."""
+
+    block_class_names = ("JointBlock", "SingleBlock", "CrossBlock")
+    _no_split_modules = ["JointBlock", "SingleBlock", "CrossBlock"]
+
+    def __init__(self, cfg: DiTConfig, dtype: torch.dtype = torch.bfloat16, device: Any = "cpu", gradient_checkpointing: bool = False,
+                 sp: Optional[Any] = None):
+        super().__init__()
+        self.cfg, self.sp, self.gradient_checkpointing = cfg, sp, gradient_checkpointing
+        h = cfg.hidden_size
+        self.patch_embed = _Lin(cfg.patch_dim, h, True, dtype, device)
+        self.time_in = nn.ModuleList([_Lin(cfg.time_freq_dim, h, True, dtype, device), _Lin(h, h, True, dtype, device)])
+        self.pooled_in = nn.ModuleList([_Lin(cfg.pooled_dim, h, True, dtype, device), _Lin(h, h, True, dtype, device)]) if cfg.pooled_dim else None
+        self.guidance_in = nn.ModuleList([_Lin(cfg.time_freq_dim, h, True, dtype, device), _Lin(h, h, True, dtype, device)]) if cfg.guidance_embed else None
+        self.text_in = _Lin(cfg.text_dim, h, True, dtype, device)
+        self.time_proj = _Lin(h, 6 * h, True, dtype, device) if cfg.num_cross_blocks else None
+        self.joint_blocks = nn.ModuleList(JointBlock(cfg, i, dtype, device) for i in range(cfg.num_joint_blocks))
+        self.single_blocks = nn.ModuleList(SingleBlock(cfg, i, dtype, device) for i in range(cfg.num_single_blocks))
+        self.cross_blocks = nn.ModuleList(CrossBlock(cfg, i, dtype, device) for i in range(cfg.num_cross_blocks))
+        self.final_mod = _Lin(h, 2 * h, True, dtype, device)
+        self.final_proj = _Lin(h, (cfg.out_channels or cfg.in_channels) * cfg.patch_size[0] * cfg.patch_size[1] * cfg.patch_size[2], True, dtype, device)
+        if cfg.pos_embed == "sincos2d":
+            self.register_buffer("pos_table", sincos_2d_table(h, cfg.pos_embed_max_size, device).to(dtype), persistent=False)
+        self._rope_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+    # ---- init ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: float = 0.02) -> "DiTTransformer":
+        """Deterministic init; modulation and output projections get a smaller std so a fresh model is near-identity."""
+        for i, (name, p) in enumerate(self.named_parameters()):
+            if p.dim() < 2:
+                if "norm" in name:
+                    p.fill_(1.0)
+                else:
+                    p.zero_()
+                continue
+            g = torch.Generator(device=p.device)
+            g.manual_seed(seed * 100003 + i)
+            s = std * (0.25 if any(k in name for k in ("_mod", "mod.", "final_", "modulation")) else 1.0)
+            p.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0.0, s, generator=g))
+        return self
+
+    # ---- patch layout ----------------------------------------------------------------------------------
+    def patchify(self, x: torch.Tensor) -> Tuple[torch.Tensor, Tuple[int, int, int]]:
+        """``[B, C, (F,) H, W]`` → tokens ``[B, L, C·pf·ph·pw]`` and the token grid."""
+        if x.dim() == 4:
+            x = x.unsqueeze(2)
+        b, c, f, hh, ww = x.shape
+        pf, ph, pw = self.cfg.patch_size
+        grid = (f // pf, hh // ph, ww // pw)
+        x = x.view(b, c, grid[0], pf, grid[1], ph, grid[2], pw).permute(0, 2, 4, 6, 1, 3, 5, 7)
+        return x.reshape(b, grid[0] * grid[1] * grid[2], c * pf * ph * pw), grid
+
+    def unpatchify(self, tokens: torch.Tensor, grid: Tuple[int, int, int], video: bool) -> torch.Tensor:
+        b = tokens.shape[0]
+        pf, ph, pw = self.cfg.patch_size
+        c = tokens.shape[-1] // (pf * ph * pw)
+        x = tokens.view(b, grid[0], grid[1], grid[2], c, pf, ph, pw).permute(0, 4, 1, 5, 2, 6, 3, 7)
+        x = x.reshape(b, c, grid[0] * pf, grid[1] * ph, grid[2] * pw)
+        return x if video else x.squeeze(2)
+
+    def _pos_crop(self, grid: Tuple[int, int, int]) -> torch.Tensor:
+        m = self.cfg.pos_embed_max_size
+        top, left = (m - grid[1]) // 2, (m - grid[2]) // 2
+        return self.pos_table[top : top + grid[1], left : left + grid[2]].reshape(1, grid[1] * grid[2], -1)
+
+    def _rope(self, grid: Tuple[int, int, int], text_len: int, device: Any) -> Tuple[torch.Tensor, torch.Tensor]:
+        key = (grid, text_len, str(device))
+        if key not in self._rope_cache:
+            self._rope_cache[key] = axial_rope(self.cfg, grid, device, text_len)
+        return self._rope_cache[key]
+
+    # ---- forward ---------------------------------------------------------------------------------------
+    def forward(self, latents: torch.Tensor, timestep: torch.Tensor, text: torch.Tensor, pooled: Optional[torch.Tensor] = None,
+                text_mask: Optional[torch.Tensor] = None, guidance: Optional[torch.Tensor] = None) -> torch.Tensor:
+        cfg = self.cfg
+        video = latents.dim() == 5
+        dtype = self.patch_embed.weight.dtype
+        tokens, grid = self.patchify(latents.to(dtype))
+        img = self.patch_embed(tokens)
+        if cfg.pos_embed == "sincos2d":
+            img = img + self._pos_crop(grid).to(img.dtype)
+        vec = self.time_in[1](F.silu(self.time_in[0](timestep_embedding(timestep, cfg.time_freq_dim).to(dtype))))
+        if self.pooled_in is not None and pooled is not None:
+            vec = vec + self.pooled_in[1](F.silu(self.pooled_in[0](pooled.to(dtype))))
+        if self.guidance_in is not None and guidance is not None:
+            vec = vec + self.guidance_in[1](F.silu(self.guidance_in[0](timestep_embedding(guidance, cfg.time_freq_dim).to(dtype))))
+        txt = self.text_in(text.to(dtype))
+        nt = txt.shape[1]
+        sp = self.sp if (self.sp is not None and self.sp.size > 1) else None
+        if sp is not None:
+            img = sp.shard_sequence(img)
+        cos = sin = None
+        if cfg.pos_embed == "rope":
+            joint_text = nt if (cfg.num_joint_blocks or cfg.num_single_blocks) else 0
+            cos, sin = self._rope(grid, joint_text, img.device)
+            if sp is not None:
+                cos, sin = sp.shard_rope(cos, joint_text), sp.shard_rope(sin, joint_text)
+        ctx = AttnContext(cos, sin, nt, sp, text_mask)
+        ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
+        run = (lambda blk, *a: torch.utils.checkpoint.checkpoint(blk, *a, use_reentrant=False)) if ckpt else (lambda blk, *a: blk(*a))
+        for blk in self.joint_blocks:
+            img, txt = run(blk, img, txt, vec, ctx)
+        if len(self.single_blocks):
+            x = torch.cat([txt, img], 1)
+            for blk in self.single_blocks:
+                x = run(blk, x, vec, ctx, nt)
+            img = x[:, nt:]
+        if len(self.cross_blocks):
+            tproj = self.time_proj(F.silu(vec))
+            cross_ctx = AttnContext(cos, sin, 0, sp, text_mask)
+            for blk in self.cross_blocks:
+                img = run(blk, img, txt, tproj, cross_ctx)
+        shift, scale = self.final_mod(F.silu(vec)).chunk(2, -1)
+        out = self.final_proj(layernorm_modulate(img, shift, scale, cfg.eps))
+        if sp is not None:
+            out = sp.gather_sequence(out)
+        return self.unpatchify(out, grid, video)
+
+    def lora_target_modules(self, patterns: Sequence[str] = ("qkv", "out", "fc1", "fc2", "in_proj", "out_proj", "cross_q", "cross_kv", "cross_out")) -> List[str]:
+        """Dotted names of the ``_Lin`` modules a LoRA recipe may wrap (attention and MLP projections inside blocks)."""
+        names = []
+        for n, m in self.named_modules():
+            if isinstance(m, _Lin) and ("blocks." in n) and n.split(".")[-1] in patterns:
+                names.append(n)
+        return names
+
+
+__all__ = ["DiTConfig", "DiTTransformer", "JointBlock", "SingleBlock", "CrossBlock", "AttnContext", "timestep_embedding", "sincos_2d_table",
+           "axial_rope", "apply_rope"]

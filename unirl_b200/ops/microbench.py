@@ -1,0 +1,282 @@
+"""Operator microbenchmarks with roofline fractions: ``python -m unirl_b200.ops.microbench <case> [options]``.
+
+Cases
+-----
+``gemm``              bf16 ``A[M,K]·W[N,K]ᵀ`` — the tcgen05 kernel against the library GEMM of the same shape
+``decode_attention``  paged-KV decode attention (memory-bound: bytes = K and V of every live token)
+``linear_logprob``    fused ``lm_head → log-softmax → gather`` against materialised logits
+``linear_sample``     fused ``lm_head → Gumbel-max sampling``
+``elementwise``       RMSNorm / QK-norm+RoPE / SwiGLU streaming kernels
+``peer``              (under ``torchrun``) fused peer-memory collectives against their NCCL compositions
+
+Timing: CUDA events on the launching stream, ≥3 warm-up iterations, a 256 MiB buffer is rewritten between timed
+iterations to flush L2 (the L2 is 126 MB), best and median of ``--iters`` are reported, max over ranks for ``peer``.
+Peaks come from ``MEASURED_PEAKS.json`` at the repository root when present (fractions are "of measured"),
+otherwise 6.65 TB/s and 1.59 PFLOP/s ("of fallback").  One JSON line per result on stdout.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+from typing import Any, Callable, Dict, List
+
+import torch
+
+
+def _peaks() -> Dict[str, Any]:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d["bf16_tflops"]), "kind": "of measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "kind": "of fallback"}
+
+
+class _Timer:
+    def __init__(self, iters: int, flush: bool = True):
+        self.iters = iters
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+
+    def __call__(self, fn: Callable[[], Any], warmup: int = 3) -> Dict[str, float]:
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts: List[float] = []
+        for _ in range(self.iters):
+            if self.flush is not None:
+                self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return {"best_ms": min(ts), "median_ms": statistics.median(ts)}
+
+
+def _emit(row: Dict[str, Any]) -> None:
+    print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in row.items()}), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------- cases
+def case_gemm(args: argparse.Namespace) -> None:
+    from unirl_b200.ops._ext import require_ext
+
+    C, pk, timer = require_ext(), _peaks(), _Timer(args.iters)
+    shapes = [tuple(int(x) for x in s.split("x")) for s in args.shapes.split(",")]
+    for m, n, k in shapes:
+        a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * m * n * k
+        ours = timer(lambda: C.gemm_bf16_tn(a, w, None, 0))
+        row = {"case": "gemm", "M": m, "N": n, "K": k, "tcgen05_ms": ours["best_ms"], "tcgen05_tflops": fl / ours["best_ms"] / 1e9,
+               "frac_of_peak": fl / ours["best_ms"] / 1e9 / pk["tflops"], "peak": pk["kind"]}
+        if not args.no_library:
+            lib = timer(lambda: torch.nn.functional.linear(a, w))
+            row.update(library_ms=lib["best_ms"], library_tflops=fl / lib["best_ms"] / 1e9)
+        assert C.gemm_status(True) == 0, "a pipeline wait timed out"
+        _emit(row)
+
+
+def case_decode_attention(args: argparse.Namespace) -> None:
+    from unirl_b200.ops.attention import paged_decode_attention
+
+    pk, timer = _peaks(), _Timer(args.iters)
+    b, ctx, hq, hkv, d, ps = args.batch, args.ctx, args.q_heads, args.kv_heads, args.head_dim, args.page_size
+    pages_per = (ctx + ps - 1) // ps
+    n_pages = b * pages_per
+    kc = torch.randn(n_pages, hkv, ps, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn_like(kc)
+    bt = torch.randperm(n_pages, device="cuda").view(b, pages_per).to(torch.int32)
+    sl = torch.full((b,), ctx, dtype=torch.int32, device="cuda")
+    q = torch.randn(b, hq, d, device="cuda", dtype=torch.bfloat16)
+    ws = torch.empty(b * hq * 32 * (d + 2), device="cuda")
+    t = timer(lambda: paged_decode_attention(q, kc, vc, bt, sl, None, ws, ctx))
+    gb = 2.0 * b * ctx * hkv * d * 2 / 1e9
+    _emit({"case": "decode_attention", "batch": b, "ctx": ctx, "q_heads": hq, "kv_heads": hkv, "head_dim": d, "page_size": ps, "kv_gb": gb,
+           "best_ms": t["best_ms"], "median_ms": t["median_ms"], "gbs": gb / t["best_ms"] * 1e3, "frac_of_peak": gb / t["best_ms"] * 1e3 / pk["hbm_gbs"],
+           "peak": pk["kind"]})
+
+
+def case_linear_logprob(args: argparse.Namespace) -> None:
+    from unirl_b200.ops.logprob import linear_logprob
+
+    pk, timer = _peaks(), _Timer(args.iters)
+    t_, h, v = args.tokens, args.hidden, args.vocab
+    x = torch.randn(t_, h, device="cuda", dtype=torch.bfloat16) * 0.5
+    w = torch.randn(v, h, device="cuda", dtype=torch.bfloat16) * 0.02
+    tgt = torch.randint(0, v, (t_,), device="cuda")
+    fused = timer(lambda: linear_logprob(x, w, tgt, 1.0))
+
+    def unfused():
+        z = torch.nn.functional.linear(x, w).float()
+        return torch.log_softmax(z, -1).gather(-1, tgt[:, None])
+
+    lib = timer(unfused)
+    fl = 2.0 * t_ * h * v
+    _emit({"case": "linear_logprob", "tokens": t_, "hidden": h, "vocab": v, "fused_ms": fused["best_ms"], "fused_tflops": fl / fused["best_ms"] / 1e9,
+           "frac_of_peak": fl / fused["best_ms"] / 1e9 / pk["tflops"], "peak": pk["kind"], "materialised_logits_ms": lib["best_ms"],
+           "logits_bytes_avoided_gb": t_ * v * (2 + 4 + 4) / 1e9})
+
+
+def case_linear_sample(args: argparse.Namespace) -> None:
+    from unirl_b200.ops.sampling import linear_sample
+
+    pk, timer = _peaks(), _Timer(args.iters)
+    b, h, v = args.batch, args.hidden, args.vocab
+    x = torch.randn(b, h, device="cuda", dtype=torch.bfloat16) * 0.5
+    w = torch.randn(v, h, device="cuda", dtype=torch.bfloat16) * 0.02
+    t = timer(lambda: linear_sample(x, w, 1.0, 0, 1.0, seed=1, step=3))
+    gb = v * h * 2 / 1e9
+    _emit({"case": "linear_sample", "batch": b, "hidden": h, "vocab": v, "best_ms": t["best_ms"], "weight_gbs": gb / t["best_ms"] * 1e3,
+           "frac_of_peak": gb / t["best_ms"] * 1e3 / pk["hbm_gbs"], "peak": pk["kind"]})
+
+
+def case_elementwise(args: argparse.Namespace) -> None:
+    from unirl_b200.ops.activation import swiglu
+    from unirl_b200.ops.norm import rmsnorm
+    from unirl_b200.ops.rope import qk_norm_rope
+
+    pk, timer = _peaks(), _Timer(args.iters)
+    t_, h = args.tokens, args.hidden
+    x = torch.randn(t_, h, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+    r = timer(lambda: rmsnorm(x, w, 1e-6))
+    _emit({"case": "rmsnorm", "tokens": t_, "hidden": h, "best_ms": r["best_ms"], "gbs": 2 * x.numel() * 2 / r["best_ms"] / 1e6,
+           "frac_of_peak": 2 * x.numel() * 2 / r["best_ms"] / 1e6 / pk["hbm_gbs"], "peak": pk["kind"]})
+    inter = args.intermediate
+    gu = torch.randn(t_, 2 * inter, device="cuda", dtype=torch.bfloat16)
+    r = timer(lambda: swiglu(gu))
+    _emit({"case": "swiglu", "tokens": t_, "intermediate": inter, "best_ms": r["best_ms"], "gbs": 3 * t_ * inter * 2 / r["best_ms"] / 1e6,
+           "frac_of_peak": 3 * t_ * inter * 2 / r["best_ms"] / 1e6 / pk["hbm_gbs"], "peak": pk["kind"]})
+    hq, hkv, d = args.q_heads, args.kv_heads, args.head_dim
+    qkv = torch.randn(t_, (hq + 2 * hkv) * d, device="cuda", dtype=torch.bfloat16)
+    qw, kw = torch.ones(d, device="cuda", dtype=torch.bfloat16), torch.ones(d, device="cuda", dtype=torch.bfloat16)
+    pos = torch.arange(t_, device="cuda") % 4096
+    r = timer(lambda: qk_norm_rope(qkv, qw, kw, pos, hq, hkv, d, 1e6, 1e-6))
+    _emit({"case": "qk_norm_rope", "tokens": t_, "best_ms": r["best_ms"], "gbs": 2 * qkv.numel() * 2 / r["best_ms"] / 1e6,
+           "frac_of_peak": 2 * qkv.numel() * 2 / r["best_ms"] / 1e6 / pk["hbm_gbs"], "peak": pk["kind"]})
+
+
+def case_peer(args: argparse.Namespace) -> None:
+    """Fused peer-memory collectives vs their NCCL compositions (run under torchrun, one rank per GPU)."""
+    import torch.distributed as dist
+
+    from unirl_b200.distributed.group.comm import Comm
+    from unirl_b200.ops.norm import rmsnorm
+    from unirl_b200.parallel.fused_collectives import FusedAllReduce, PeerArena
+    from unirl_b200.ops._ext import require_ext
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist.init_process_group("cpu:gloo,cuda:nccl", device_id=torch.device("cuda", local))
+    comm, dev, C = Comm.world(), torch.device("cuda", local), require_ext()
+    timer = _Timer(args.iters, flush=False)
+
+    def tmax(x: float) -> float:
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    # -- TP decode: row-parallel projection + all-reduce + residual + RMSNorm
+    T, H, K = args.batch, args.hidden, args.hidden // world
+    inp = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(H, K, device=dev, dtype=torch.bfloat16) * 0.02
+    res = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+    nw = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    far = FusedAllReduce(comm, max(T, 64), H, dev)
+
+    def fused_pair():
+        far.proj_reduce_norm(inp, w, res, nw, 1e-6)
+        far.proj_reduce_norm(inp, w, res, nw, 1e-6)
+
+    def nccl_pair():
+        for _ in range(2):
+            y = torch.matmul(inp, w.t())
+            dist.all_reduce(y)
+            x = y + res
+            rmsnorm(x, nw, 1e-6)
+
+    f, n = timer(fused_pair), timer(nccl_pair)
+    far.arena.check()
+    fb, nb = tmax(f["median_ms"]) / 2, tmax(n["median_ms"]) / 2
+    if rank == 0:
+        _emit({"case": "peer_tp_proj_allreduce_add_norm", "world": world, "tokens": T, "hidden": H, "fused_us": fb * 1e3, "nccl_composition_us": nb * 1e3,
+               "speedup": nb / fb})
+    # -- trainer: reduce-scatter (+mean +sum of squares) and AdamW + publish over a group of `numel` parameters
+    numel = args.numel // (world * 128) * (world * 128)
+    shard = numel // world
+    ga = PeerArena(comm, numel * 4 + 4096, dev, wait_s=20.0)
+    pa = PeerArena(comm, numel * 2 + 4096, dev, wait_s=20.0)
+    grad, replica = ga.take(numel, torch.float32), pa.take(numel, torch.bfloat16)
+    grad.normal_()
+    out, ss = torch.empty(shard, device=dev), torch.zeros(1, device=dev)
+    master, m, v = torch.randn(shard, device=dev), torch.zeros(shard, device=dev), torch.zeros(shard, device=dev)
+    clip = torch.ones(1, device=dev)
+    dist.barrier()
+
+    def fused_rs():
+        C.peer_reduce_scatter_sumsq(ga.peer, grad, out, ss, 1.0 / world)
+
+    def nccl_rs():
+        dist.reduce_scatter_tensor(out, grad, op=dist.ReduceOp.AVG)
+        C.sum_squares(out)
+
+    def fused_opt():
+        C.peer_adamw_publish(pa.peer, replica, master, out, m, v, None, 1e-5, 0.9, 0.95, 1e-8, 0.0, 3, clip, 0.0)
+
+    low = torch.empty(shard, device=dev, dtype=torch.bfloat16)
+
+    def nccl_opt():
+        C.adamw_step(master, out, m, v, low, None, 1e-5, 0.9, 0.95, 1e-8, 0.0, 3, 1.0, 0.0, clip)
+        dist.all_gather_into_tensor(replica, low)
+
+    rows = {}
+    for name, fn in (("fused_reduce_scatter_norm", fused_rs), ("nccl_reduce_scatter_plus_norm", nccl_rs), ("fused_adamw_publish", fused_opt),
+                     ("nccl_adamw_plus_all_gather", nccl_opt)):
+        rows[name] = tmax(timer(fn)["median_ms"])
+    ga.check()
+    pa.check()
+    if rank == 0:
+        rs_bytes = (world - 1) * shard * 4  # bytes this rank pulls over NVLink
+        ag_bytes = (world - 1) * shard * 2  # bytes this rank pushes over NVLink
+        _emit({"case": "peer_trainer_collectives", "world": world, "numel": numel, **{k + "_ms": v for k, v in rows.items()},
+               "rs_nvlink_gbs": rs_bytes / rows["fused_reduce_scatter_norm"] / 1e6, "publish_nvlink_gbs": ag_bytes / rows["fused_adamw_publish"] / 1e6,
+               "nvlink_peer_copy_gbs_measured_reference": 770.0})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+CASES = {"gemm": case_gemm, "decode_attention": case_decode_attention, "linear_logprob": case_linear_logprob, "linear_sample": case_linear_sample,
+         "elementwise": case_elementwise, "peer": case_peer}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("case", choices=sorted(CASES))
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--shapes", default="18800x6144x2560,18800x2560x4096,18800x19456x2560,18800x2560x9728,8192x8192x8192", help="gemm: MxNxK list")
+    ap.add_argument("--no-library", action="store_true", help="gemm: skip the library GEMM (for profiler captures)")
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--ctx", type=int, default=2688)
+    ap.add_argument("--q-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--tokens", type=int, default=18800)
+    ap.add_argument("--hidden", type=int, default=2560)
+    ap.add_argument("--intermediate", type=int, default=9728)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--numel", type=int, default=101_000_000, help="peer: parameters in one sharded group (a Qwen3-4B block has 101 M)")
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device")
+    CASES[args.case](args)
+
+
+if __name__ == "__main__":
+    main()

@@ -85,7 +85,7 @@ def inject_lora(model: nn.Module, *, rank: int, alpha: float, target_modules: Se
             mod._lora_index = {}
             mod._lora_active = "default"
         for target, (param_name, off, rows) in targets.items():
-            if target not in want:
+            if not any(w == target or w.endswith("." + target) for w in want):
                 continue
             w = getattr(mod, param_name)
             ad = LoraAdapter(w.shape[1], rows, off, rank, alpha, dropout, w.dtype, w.device)
