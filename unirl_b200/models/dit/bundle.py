@@ -1,0 +1,68 @@
+"""``DiTBundle`` — trainable DiT + frozen text towers + latent codec + tokenizers + schedule policy.
+
+Built from ``random:<preset>`` (random-init weights of the named architecture) or from a native checkpoint directory.
+Parity: ``unirl/models/sd3/bundle.py``, ``unirl/models/wan21/bundle.py`` (which wrap diffusers / transformers loaders).
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Any, Dict, Optional
+
+import torch
+
+from unirl_b200.models.dit.config import DiTPipelineConfig, FamilySpec, resolve_family
+from unirl_b200.models.dit.modeling import DiTTransformer
+from unirl_b200.models.dit.text_encoder import TextEncoder
+from unirl_b200.models.dit.vae import LatentVAE
+from unirl_b200.models.tokenizer import load_tokenizer
+from unirl_b200.models.types import Bundle
+from unirl_b200.sde.runtime import FlowMatchSchedulePolicy
+from unirl_b200.types.conditions.base import Modality
+from unirl_b200.utils.dtypes import parse_torch_dtype
+
+
+class DiTBundle(Bundle):
+    def __init__(self, transformer: DiTTransformer, text_encoders: Any, vae: LatentVAE, tokenizers: Any, config: DiTPipelineConfig, spec: FamilySpec):
+        super().__init__()
+        self.transformer, self.text_encoders, self.vae, self.tokenizers = transformer, list(text_encoders), vae, list(tokenizers)
+        self.config, self.spec = config, spec
+        self.pretrained_path = None if config.pretrained_model_ckpt_path.startswith("random:") else config.pretrained_model_ckpt_path
+        self.modality = Modality.VIDEO if spec.transformer.is_video else Modality.IMAGE
+        self.concat_image_latents = False
+
+    @property
+    def model_config(self):
+        return self.transformer.cfg
+
+    def schedule_policy(self) -> FlowMatchSchedulePolicy:
+        t = self.spec.transformer
+        patch = t.patch_size[-1] * (2 if self.spec.packed_latents else 1)
+        return FlowMatchSchedulePolicy(shift=float(self.config.shift if self.config.shift is not None else self.spec.shift),
+                                       use_dynamic_shifting=self.spec.use_dynamic_shifting, vae_scale_factor=t.vae_scale_factor, patch_size=patch)
+
+    @classmethod
+    def from_config(cls, config: DiTPipelineConfig, sp: Optional[Any] = None) -> "DiTBundle":
+        path = config.pretrained_model_ckpt_path
+        spec = resolve_family(path, config.model_overrides)
+        dtype = parse_torch_dtype(config.model_precision)
+        device = config.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        model = DiTTransformer(spec.transformer, dtype=dtype, device=device, gradient_checkpointing=config.use_gradient_checkpointing, sp=sp)
+        if path.startswith("random:"):
+            model.init_weights(config.init_seed)
+        else:
+            from safetensors.torch import load_file
+
+            missing, unexpected = model.load_state_dict(load_file(os.path.join(path, "transformer.safetensors")), strict=False)
+            if missing or unexpected:
+                raise RuntimeError(f"checkpoint/key mismatch: missing {missing[:5]} unexpected {unexpected[:5]}")
+        encoders = [TextEncoder(c, dtype=dtype, device=device).init_weights(config.init_seed + 1 + i) for i, c in enumerate(spec.text_encoders)]
+        toks = [load_tokenizer(None, c.vocab_size, True) for c in spec.text_encoders]
+        vae = LatentVAE(spec.vae, device=device).init_weights(config.init_seed + 7)
+        return cls(model, encoders, vae, toks, config, spec)
+
+    def trainable_modules(self) -> Dict[str, torch.nn.Module]:
+        return {"transformer": self.transformer}
+
+
+__all__ = ["DiTBundle"]

@@ -1,0 +1,5 @@
+"""FLUX.2 klein on the generic DiT core (double + single stream blocks, empirical-mu schedule).  Parity: ``unirl/models/flux2_klein/``."""
+from unirl_b200.models.flux2_klein.pipeline import Flux2KleinBundle, Flux2KleinPipeline, Flux2KleinPipelineConfig
+from unirl_b200.models.flux2_klein.schedule import KleinSchedulePolicy
+
+__all__ = ["Flux2KleinBundle", "Flux2KleinPipeline", "Flux2KleinPipelineConfig", "KleinSchedulePolicy"]

@@ -1,0 +1,63 @@
+"""WAN 2.1 — text-to-video and image-to-video.
+
+Latents are 5-D ``(C, (F−1)/4+1, H/8, W/8)``.  Image-to-video concatenates, along channels, a 4-channel first-frame
+mask and the 16-channel encoded first frame to the noisy latents (36 input channels); the condition travels as an
+``ImageLatentCondition`` holding those 20 channels.  Parity: ``unirl/models/wan21/diffusion.py:62-158, 317-334, 340-468``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Optional
+
+import torch
+
+from unirl_b200.models.dit.bundle import DiTBundle
+from unirl_b200.models.dit.config import DiTPipelineConfig
+from unirl_b200.models.dit.pipeline import DiTPipeline
+from unirl_b200.types.conditions import ImageLatentCondition
+
+
+@dataclass
+class Wan21PipelineConfig(DiTPipelineConfig):
+    pretrained_model_ckpt_path: str = "random:wan21-14b"
+    image_to_video: bool = False
+    max_sequence_length: int = 512
+
+
+class Wan21Bundle(DiTBundle):
+    @classmethod
+    def from_config(cls, config: Wan21PipelineConfig, sp: Optional[Any] = None) -> "Wan21Bundle":
+        if config.image_to_video and "in_channels" not in config.model_overrides:
+            from dataclasses import replace
+
+            from unirl_b200.models.dit.config import resolve_family
+
+            c = resolve_family(config.pretrained_model_ckpt_path).transformer.in_channels  # noisy + 4 mask + first-frame channels enter the patch embedding
+            config = replace(config, model_overrides={**config.model_overrides, "in_channels": 2 * c + 4, "out_channels": c})
+        b = super().from_config(config, sp)
+        b.concat_image_latents = bool(config.image_to_video)
+        return b
+
+    def first_frame_condition(self, image: torch.Tensor, num_latent_frames: int) -> ImageLatentCondition:
+        """``image [B, 3, H, W]`` in [0, 1] → ``[B, 20, F, h, w]``: mask (first latent frame = 1) ++ encoded frame padded with zeros."""
+        z = self.vae.encode(image)  # [B, 16, h, w]
+        b, c, h, w = z.shape
+        lat = torch.zeros(b, c, num_latent_frames, h, w, dtype=z.dtype, device=z.device)
+        lat[:, :, 0] = z
+        mask = torch.zeros(b, 4, num_latent_frames, h, w, dtype=z.dtype, device=z.device)
+        mask[:, :, 0] = 1.0
+        return ImageLatentCondition(latents=torch.cat([mask, lat], 1))
+
+
+class Wan21Pipeline(DiTPipeline):
+    @classmethod
+    def from_config(cls, config: Wan21PipelineConfig) -> "Wan21Pipeline":
+        return cls(Wan21Bundle.from_config(config))
+
+    def latent_shape(self, sampling: Any):
+        shape = super().latent_shape(sampling)
+        t = self.bundle.model_config
+        return ((t.out_channels or t.in_channels), *shape[1:]) if self.bundle.concat_image_latents else shape
+
+
+__all__ = ["Wan21PipelineConfig", "Wan21Bundle", "Wan21Pipeline"]

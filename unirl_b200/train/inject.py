@@ -43,7 +43,12 @@ class LoraAdapter(nn.Module):
 
 
 def _key(target: str, adapter: str) -> str:
-    return f"{target}__{adapter}"
+    return f"{target.replace('.', ':')}__{adapter}"  # module names may not contain dots
+
+
+def _split_key(key: str) -> Tuple[str, str]:
+    target, adapter = key.rsplit("__", 1)
+    return target.replace(":", "."), adapter
 
 
 def lora_apply(module: nn.Module, param_name: str, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
@@ -122,7 +127,7 @@ class AdapterShadow:
             if not hasattr(mod, "lora"):
                 continue
             for key, ad in mod.lora.items():
-                target, adapter = key.rsplit("__", 1)
+                target, adapter = _split_key(key)
                 if adapter == self.default and _key(target, self.shadow) in mod.lora:
                     sh = mod.lora[_key(target, self.shadow)]
                     yield ad.lora_A, sh.lora_A
@@ -192,7 +197,7 @@ def lora_named_tensors(model: nn.Module, adapter: str = "default", prefix: str =
             continue
         hf_path = getattr(mod, "hf_module_path", lambda t: f"{name}.{t}")
         for key, ad in mod.lora.items():
-            target, ad_name = key.rsplit("__", 1)
+            target, ad_name = _split_key(key)
             if ad_name != adapter:
                 continue
             base = f"{prefix}{hf_path(target)}"

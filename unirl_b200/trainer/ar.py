@@ -81,7 +81,9 @@ class ARTrainer(BaseTrainer):
         self.bundle = remote_cfg(bundle_cfg)
         self.pipeline = remote_cfg(pipeline_cfg, bundle=self.bundle)
         self.backend = remote_cfg(backend_cfg, bundle=self.bundle)
-        self.algorithm = remote_cfg(algorithm_cfg, pipeline=self.pipeline)
+        algo_params = inspect.signature(parse_cfg(algorithm_cfg)["role_cls"]).parameters
+        extra = {"backend": self.backend} if "backend" in algo_params else {}  # e.g. DiffusionNFT reads the EMA adapter policy from it
+        self.algorithm = remote_cfg(algorithm_cfg, pipeline=self.pipeline, **extra)
         self.stack = remote_cfg(stack_cfg, fsdp_backend=self.backend, algorithm=self.algorithm)
 
     # ---- request ------------------------------------------------------------------------------------------
@@ -130,7 +132,7 @@ class ARTrainer(BaseTrainer):
         self._drop_decoded(req, resp, rollout_id=rollout_id)
         (track,) = resp.tracks.values()
         result = self.stack.train_track(track, training_progress=float(training_progress))
-        lens = track.segment.lengths if track.segment is not None else None
+        lens = getattr(track.segment, "lengths", None) if track.segment is not None else None
         light = resp.metadata_only()
         if lens is not None:
             for t in light.tracks.values():
