@@ -43,6 +43,7 @@ def _defines(path: str, names: List[str]) -> bool:
     with open(path) as f:
         tree = ast.parse(f.read())
     scope = tree.body
+    inherited = False
     for depth, name in enumerate(names):
         found = None
         for n in scope:
@@ -53,7 +54,8 @@ def _defines(path: str, names: List[str]) -> bool:
             elif isinstance(n, (ast.Import, ast.ImportFrom)) and any((a.asname or a.name.split(".")[0]) == name for a in n.names):
                 found = n
         if found is None:
-            return False
+            return inherited  # a name missing from a class body may come from a base class
+        inherited = isinstance(found, ast.ClassDef) and bool(found.bases)
         if isinstance(found, ast.ClassDef):
             scope = found.body
         elif depth < len(names) - 1:
