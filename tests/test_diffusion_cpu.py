@@ -91,3 +91,26 @@ def test_diffusion_training_loop(algo):
             assert abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-4  # first update is on-policy: replay reproduces the rollout log-probs
     finally:
         tr.shutdown()
+
+
+@pytest.mark.timeout(600)
+def test_native_diffusion_engine_own_weights_and_tensor_sync():
+    """The native engine keeps its own copy of the transformer; weights arrive by in-memory tensor sync and are fingerprinted."""
+    ov = ["rollout._target_=unirl_b200.rollout.engine.native_diffusion.engine.NativeDiffusionRolloutEngine", "~rollout.stage_attrs",
+          "+rollout.config={pipeline_cls: unirl_b200.models.sd3.pipeline.SD3Pipeline, pipeline_config_cls: unirl_b200.models.sd3.config.SD3PipelineConfig, "
+          "pretrained_model_ckpt_path: 'random:tiny-sd3', model_precision: fp32, autocast_precision: fp32, device: cpu, share_trainer_weights: false}",
+          "+sync={_target_: unirl_b200.distributed.weight_sync.full.tensor.TensorWeightSync}"]
+    tr = _trainer(ov)
+    try:
+        assert tr.rollout.compute_local_param_checksums()[0] == tr.backend.compute_local_param_checksums()[0], "engine starts from the trainer's weights"
+        tr.train(num_rollouts=2, weight_sync_interval=1)
+        assert tr.rollout.compute_local_param_checksums()[0] != tr.backend.compute_local_param_checksums()[0], "trainer moved on after the last update"
+        tr._sync_weights()
+        assert tr.rollout.compute_local_param_checksums()[0] == tr.backend.compute_local_param_checksums()[0]
+        tr.rollout.sleep()
+        assert tr.rollout.get_weight_version()[0] >= 2
+        tr.rollout.wake_up()
+        rows = [r for r in tr.wandb_logger.history if "train/step" in r]
+        assert abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-4
+    finally:
+        tr.shutdown()
