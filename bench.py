@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--rollout-tp", type=int, default=0, help="0 = 2 when gpus >= 2 else 1")
     ap.add_argument("--algorithm", default="grpo", choices=["grpo", "drpo"])
+    ap.add_argument("--ckpt-layers", type=int, default=-1, help="recompute only the first N decoder blocks in backward (-1 = recipe default)")
     return ap.parse_args()
 
 
@@ -137,6 +138,8 @@ def main() -> None:
         f"data_source.reserved_low_ids={1000 if vocab > 4096 else 16}", f"stack.micro_batch_size={args.micro_batch}",
         f"algorithm.horizon={args.max_new_tokens}", f"rollout_parallel={{tp: {tp}}}",
     ]
+    if args.ckpt_layers >= 0:
+        overrides.append(f"+backend.fsdp_cfg.checkpoint_layers={args.ckpt_layers}")
     if args.algorithm == "drpo":
         overrides += ["algorithm._target_=unirl_b200.algorithms.drpo.DRPO", "~algorithm.clip_range", "~algorithm.clip_range_high",
                       "+algorithm.drpo_epsilon=12.5"]
@@ -203,7 +206,7 @@ def main() -> None:
                "clocks": clocks,
                "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": rows[-1]["h2d"], "d2h_bytes_per_step": rows[-1]["d2h"],
                        "ms_per_step": wall_ms / args.steps},
-               "gpu_launches": int(launches), "loss": rows[-1]["loss"],
+               "gpu_launches": int(launches), "loss": rows[-1]["loss"], "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                "phases_device_ms_last_step": {k: round(v, 2) for k, v in rows[-1]["device_ms"].items()}, "device_span_ms_per_step": span_ms / args.steps}
         print(json.dumps(out))
     trainer.shutdown()

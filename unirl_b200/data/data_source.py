@@ -105,6 +105,21 @@ class MultimodalRLDataSource(DefaultDataSource):
         self.prompts_per_rollout = int((algo or {}).get("prompts_per_rollout", 0)) if algo is not None else 0
 
 
+class SyntheticImageQuestionDataSource(DefaultDataSource):
+    """Question + seeded random image per prompt: a dataset-free source for vision-language recipes and tests."""
+
+    def __init__(self, questions: List[str], image_size: Any = (28, 28), seed: int = 0, shuffle: bool = True):
+        super().__init__(list(questions), seed=seed, shuffle=shuffle)
+        self._img_hw = (int(image_size[0]), int(image_size[1]))
+        self._img_seed = int(seed)
+
+    def _build(self, rows: List[Dict[str, Any]], tag: str) -> RolloutInputs:
+        out = super()._build(rows, tag)
+        g = torch.Generator().manual_seed(self._img_seed * 7919 + self._draws)
+        out.primitives["image"] = Images(pixels=torch.rand(len(rows), 3, *self._img_hw, generator=g))
+        return out
+
+
 class SyntheticTokenDataSource:
     """Prompts of uniform-random token ids with lengths uniform in ``[min_len, max_len]`` (deterministic in ``seed``).
 
@@ -143,4 +158,4 @@ class SyntheticTokenDataSource:
         return self._draw(n, "e")
 
 
-__all__ = ["DefaultDataSource", "MultimodalRLDataSource", "SyntheticTokenDataSource", "load_media"]
+__all__ = ["SyntheticImageQuestionDataSource", "DefaultDataSource", "MultimodalRLDataSource", "SyntheticTokenDataSource", "load_media"]

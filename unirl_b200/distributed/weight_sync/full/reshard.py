@@ -47,7 +47,7 @@ def plan_param(name: str, shape: Tuple[int, ...], cfg: Any, tp_size: int) -> Lis
     for s in shape:
         numel *= s
     kind, sections = tp_slice_spec(name, cfg)
-    if tp_size == 1 or kind == "replicate" or len(shape) < 2:
+    if tp_size == 1 or kind == "replicate" or (len(shape) < 2 and kind != "rows"):
         return [CopyOp(name, r, 0, 0, 1, numel, numel, numel) for r in range(tp_size)]
     n_rows, n_cols = shape[0], numel // shape[0]
     ops: List[CopyOp] = []

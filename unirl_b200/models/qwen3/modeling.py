@@ -108,6 +108,7 @@ class AttnMeta:
     slot_mapping: Optional[torch.Tensor] = None  # [T] int64
     workspace: Optional[torch.Tensor] = None
     max_kv_len: int = 0
+    input_embeds: Optional[torch.Tensor] = None  # [T, H]: replaces the token-embedding lookup (multimodal prompts)
 
 
 class Qwen3DecoderLayer(nn.Module):
@@ -122,6 +123,7 @@ class Qwen3DecoderLayer(nn.Module):
         mk = lambda *shape: nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))  # noqa: E731
         self.input_layernorm = mk(h)
         self.qkv_proj = mk((self.n_q + 2 * self.n_kv) * d, h)
+        self.qkv_bias = mk((self.n_q + 2 * self.n_kv) * d) if cfg.attention_bias else None
         self.q_norm = mk(d) if cfg.qk_norm else None
         self.k_norm = mk(d) if cfg.qk_norm else None
         self.o_proj = mk(h, self.n_q * d)
@@ -145,6 +147,20 @@ class Qwen3DecoderLayer(nn.Module):
             return y if residual is None else y + residual
         return linear(x, getattr(self, name), residual=residual)
 
+    def _qkv_rope(self, h: torch.Tensor, meta: AttnMeta) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Fused QKV projection (+ bias) → per-head RMS q/k norm → rotary.  ``meta.positions`` is ``[T]`` (one rotary axis,
+        fused kernel) or ``[3, T]`` (temporal / height / width axes of a vision-language prompt)."""
+        c = self.cfg
+        qkv = self._proj(h, "qkv_proj")
+        if self.qkv_bias is not None:
+            qkv = qkv + self.qkv_bias
+        if meta.positions is not None and meta.positions.dim() == 2:
+            from unirl_b200.ops.rope import mrope_qk
+
+            return mrope_qk(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps,
+                            getattr(c, "mrope_section", (c.head_dim // 8, 3 * c.head_dim // 16, 3 * c.head_dim // 16)))
+        return qk_norm_rope(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps)
+
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         if meta.mode == "decode":
             A.kv_cache_write(k, v, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.slot_mapping)
@@ -159,8 +175,7 @@ class Qwen3DecoderLayer(nn.Module):
         and the following RMSNorm run as one GEMM plus one peer-memory kernel.  ``h`` is the already normed input;
         returns the new residual stream and the input of the next block normed with ``next_norm``."""
         c, fused = self.cfg, self.tp.fused
-        qkv = self._proj(h, "qkv_proj")
-        q, k, v = qk_norm_rope(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps)
+        q, k, v = self._qkv_rope(h, meta)
         attn = self.attention(q, k, v, meta).reshape(x.shape[0], self.n_q * c.head_dim)
         x, h = fused.proj_reduce_norm(attn, self.o_proj, x, self.post_attention_layernorm, c.rms_norm_eps)
         act = swiglu(self._proj(h, "gate_up_proj"))
@@ -169,8 +184,7 @@ class Qwen3DecoderLayer(nn.Module):
     def forward(self, x: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         c = self.cfg
         h = rmsnorm(x, self.input_layernorm, c.rms_norm_eps)
-        qkv = self._proj(h, "qkv_proj")
-        q, k, v = qk_norm_rope(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps)
+        q, k, v = self._qkv_rope(h, meta)
         attn = self.attention(q, k, v, meta).reshape(x.shape[0], self.n_q * c.head_dim)
         if self.tp.size == 1:
             x = self._proj(attn, "o_proj", residual=x)
@@ -195,6 +209,7 @@ class Qwen3Transformer(nn.Module):
         self.cfg = cfg
         self.tp = tp or TPContext()
         self.gradient_checkpointing = gradient_checkpointing
+        self.checkpoint_layers: Optional[int] = None  # recompute only the first N blocks in backward (None = all): 180 GB of HBM holds the rest
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
         self.layers = nn.ModuleList(Qwen3DecoderLayer(cfg, i, self.tp, dtype, device) for i in range(cfg.num_hidden_layers))
         self.norm = nn.Parameter(torch.empty(cfg.hidden_size, dtype=dtype, device=device))
@@ -210,7 +225,7 @@ class Qwen3Transformer(nn.Module):
         """
         for i, (name, p) in enumerate(self.named_parameters()):
             if p.dim() == 1:
-                p.fill_(1.0)
+                p.zero_() if name.endswith("bias") else p.fill_(1.0)
             else:
                 g = torch.Generator(device=p.device)
                 g.manual_seed(seed * 100003 + i)
@@ -224,7 +239,7 @@ class Qwen3Transformer(nn.Module):
     # ---- forward -------------------------------------------------------------------------------------
     def forward(self, tokens: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         """``tokens [T]`` → final-normed hidden states ``[T, H]``."""
-        x = self.embed_tokens[tokens]
+        x = self.embed_tokens[tokens] if meta.input_embeds is None else meta.input_embeds.to(self.embed_tokens.dtype)
         if self.tp.size > 1 and self.tp.fused is not None and not torch.is_grad_enabled() and x.is_cuda \
                 and not any(getattr(l, "_lora_index", None) for l in self.layers):
             h = rmsnorm(x, self.layers[0].input_layernorm, self.cfg.rms_norm_eps)
@@ -233,8 +248,9 @@ class Qwen3Transformer(nn.Module):
                 x, h = layer.forward_fused_tp(x, h, meta, nxt)
             return h
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled() and meta.mode == "train"
-        for layer in self.layers:
-            if ckpt:
+        n_ckpt = len(self.layers) if self.checkpoint_layers is None else int(self.checkpoint_layers)
+        for i, layer in enumerate(self.layers):
+            if ckpt and i < n_ckpt:
                 x = torch.utils.checkpoint.checkpoint(layer, x, meta, use_reentrant=False)
             else:
                 x = layer(x, meta)
@@ -258,6 +274,9 @@ class Qwen3Transformer(nn.Module):
                         p + "mlp.up_proj.weight": u, p + "mlp.down_proj.weight": l.down_proj})
             if l.q_norm is not None:
                 out[p + "self_attn.q_norm.weight"], out[p + "self_attn.k_norm.weight"] = l.q_norm, l.k_norm
+            if l.qkv_bias is not None:
+                nq, nkv = l.n_q * c.head_dim, l.n_kv * c.head_dim
+                out[p + "self_attn.q_proj.bias"], out[p + "self_attn.k_proj.bias"], out[p + "self_attn.v_proj.bias"] = l.qkv_bias.split([nq, nkv, nkv])
         out["model.norm.weight"] = self.norm
         if self.lm_head is not None:
             out["lm_head.weight"] = self.lm_head
@@ -283,6 +302,9 @@ class Qwen3Transformer(nn.Module):
             if l.q_norm is not None:
                 l.q_norm.copy_(sd[p + "self_attn.q_norm.weight"])
                 l.k_norm.copy_(sd[p + "self_attn.k_norm.weight"])
+            if l.qkv_bias is not None:
+                l.qkv_bias.copy_(torch.cat([rows(sd[p + "self_attn.q_proj.bias"], l.n_q * c.head_dim), rows(sd[p + "self_attn.k_proj.bias"], l.n_kv * c.head_dim),
+                                            rows(sd[p + "self_attn.v_proj.bias"], l.n_kv * c.head_dim)], 0))
         self.norm.copy_(sd["model.norm.weight"])
         if self.lm_head is not None:
             self.lm_head.copy_(sd.get("lm_head.weight", sd["model.embed_tokens.weight"]))
@@ -295,7 +317,7 @@ def tp_slice_spec(name: str, cfg: Qwen3Config) -> Tuple[str, Tuple[int, ...]]:
     """
     d = cfg.head_dim
     leaf = name.rsplit(".", 1)[-1]
-    if leaf == "qkv_proj":
+    if leaf in ("qkv_proj", "qkv_bias"):
         return "rows", (cfg.num_attention_heads * d, cfg.num_key_value_heads * d, cfg.num_key_value_heads * d)
     if leaf == "gate_up_proj":
         return "rows", (cfg.intermediate_size, cfg.intermediate_size)

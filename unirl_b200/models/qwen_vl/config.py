@@ -1,0 +1,17 @@
+"""Construction config of the Qwen2.5-VL pipeline (``unirl/models/qwen_vl/config.py`` field names)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from unirl_b200.models.qwen3.config import Qwen3PipelineConfig
+
+
+@dataclass
+class QwenVLPipelineConfig(Qwen3PipelineConfig):
+    pretrained_model_ckpt_path: str = "random:tiny-vl"
+    min_pixels: int = 4 * 28 * 28
+    max_pixels: int = 1280 * 28 * 28
+
+
+__all__ = ["QwenVLPipelineConfig"]

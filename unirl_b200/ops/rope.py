@@ -70,4 +70,29 @@ def qk_norm_rope(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: 
     return qk_norm_rope_reference(qkv, q_weight, k_weight, positions, n_q, n_kv, head_dim, theta, eps)
 
 
-__all__ = ["qk_norm_rope", "qk_norm_rope_reference", "rope_cos_sin"]
+def mrope_cos_sin(positions3: torch.Tensor, head_dim: int, theta: float, sections: Tuple[int, int, int]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Multimodal rotary tables: frequency ``j`` takes its position from the temporal, height or width axis according to
+    ``sections`` (counts of frequencies per axis, summing to ``head_dim / 2``).  ``positions3`` is ``[3, T]``."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions3.device, dtype=torch.float32) / head_dim))
+    axis = torch.repeat_interleave(torch.arange(3, device=positions3.device), torch.tensor(list(sections), device=positions3.device))
+    pos = positions3.float()[axis].transpose(0, 1)  # [T, D/2]: the position each frequency sees
+    ang = pos * inv
+    return ang.cos(), ang.sin()
+
+
+def mrope_qk(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], positions3: torch.Tensor, n_q: int, n_kv: int,
+             head_dim: int, theta: float, eps: float, sections: Tuple[int, int, int]):
+    """QK-norm + 3-axis rotary for vision-language prompts (prefill / training; decode positions collapse to one axis
+    and take the fused kernel).  Differentiable PyTorch composition."""
+    t = qkv.shape[0]
+    q, k, v = qkv.float().split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], -1)
+    q, k = q.view(t, n_q, head_dim), k.view(t, n_kv, head_dim)
+    if q_weight is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight.float()
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight.float()
+    cos, sin = mrope_cos_sin(positions3, head_dim, theta, sections)
+    cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+    return _rotate(q, cos, sin).to(qkv.dtype), _rotate(k, cos, sin).to(qkv.dtype), v.reshape(t, n_kv, head_dim).to(qkv.dtype)
+
+
+__all__ = ["qk_norm_rope", "qk_norm_rope_reference", "rope_cos_sin", "mrope_qk", "mrope_cos_sin"]

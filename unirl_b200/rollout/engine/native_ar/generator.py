@@ -76,8 +76,13 @@ class ARGenerator:
     # ---- public -------------------------------------------------------------------------------------
     @torch.no_grad()
     def generate(self, prompts: Sequence[torch.Tensor], *, max_new_tokens: int, temperature: float = 1.0, top_k: int = 0,
-                 top_p: float = 1.0, stop_token_ids: Optional[Sequence[int]] = None, seed: Optional[int] = None) -> GenerationOutput:
-        """``prompts``: per-sequence 1-D token tensors.  Sequences beyond ``max_running`` run in successive waves."""
+                 top_p: float = 1.0, stop_token_ids: Optional[Sequence[int]] = None, seed: Optional[int] = None,
+                 extras: Optional[Sequence[Any]] = None) -> GenerationOutput:
+        """``prompts``: per-sequence 1-D token tensors.  Sequences beyond ``max_running`` run in successive waves.
+
+        ``extras``: optional per-sequence multimodal payloads handed to ``model.prepare_multimodal`` at prefill (a
+        vision-language model merges image features into the prompt embeddings and returns 3-axis rotary positions plus
+        the per-sequence offset its decode positions carry)."""
         n = len(prompts)
         toks: List[Optional[torch.Tensor]] = [None] * n
         lps: List[Optional[torch.Tensor]] = [None] * n
@@ -87,7 +92,8 @@ class ARGenerator:
         self._calls += 1
         for lo in range(0, n, self.max_running):
             idx = list(range(lo, min(n, lo + self.max_running)))
-            t, l, f, s = self._run_wave([prompts[i] for i in idx], max_new_tokens, temperature, top_k, top_p, stop_token_ids, seed + lo)
+            t, l, f, s = self._run_wave([prompts[i] for i in idx], max_new_tokens, temperature, top_k, top_p, stop_token_ids, seed + lo,
+                                        None if extras is None else [extras[i] for i in idx])
             for j, i in enumerate(idx):
                 toks[i], lps[i] = t[j], l[j]
             fin[lo : lo + len(idx)] = f
@@ -96,8 +102,9 @@ class ARGenerator:
 
     # ---- one wave -------------------------------------------------------------------------------------
     def _run_wave(self, prompts: List[torch.Tensor], max_new: int, temperature: float, top_k: int, top_p: float,
-                  stop_ids: Optional[Sequence[int]], seed: int):
+                  stop_ids: Optional[Sequence[int]], seed: int, extras: Optional[List[Any]] = None):
         dev, ps, b = self.device, self.page_size, len(prompts)
+        rope_offset = torch.zeros(b, dtype=torch.long, device=dev)
         plens = [int(p.numel()) for p in prompts]
         pages_per = [math.ceil((pl + max_new) / ps) for pl in plens]
         cache = self.ensure_cache(sum(pp * ps for pp in pages_per))
@@ -117,15 +124,17 @@ class ARGenerator:
             while j < b and (j == i or tot + plens[j] <= self.prefill_token_budget):
                 tot += plens[j]
                 j += 1
-            self._prefill([prompts[k] for k in range(i, j)], plens[i:j], block_tables[i:j], cache, last_hidden[i:j])
+            self._prefill([prompts[k] for k in range(i, j)], plens[i:j], block_tables[i:j], cache, last_hidden[i:j],
+                          None if extras is None else extras[i:j], rope_offset[i:j])
             i = j
 
         # -- decode state (all device resident) ---------------------------------------------------------
         st = _DecodeState(b, max_new, dev)
         st.positions.copy_(torch.tensor(plens, dtype=torch.long))  # index at which the next fed token is written
+        st.rope_offset.copy_(rope_offset)
         first_tok, first_lp = self._sample(last_hidden, temperature, top_k, top_p, seed, 0, st)
         st.record(first_tok, first_lp, stop)
-        meta = AttnMeta(mode="decode", positions=st.positions, k_cache=cache.k, v_cache=cache.v, block_tables=block_tables,
+        meta = AttnMeta(mode="decode", positions=st.rope_pos, k_cache=cache.k, v_cache=cache.v, block_tables=block_tables,
                         seq_lens=st.seq_lens, slot_mapping=st.slots, max_kv_len=max(plens) + max_new)
         if self.device.type == "cuda":
             from unirl_b200.ops._ext import ext
@@ -160,7 +169,8 @@ class ARGenerator:
         lps = [out_l[k, : int(lens[k])].clone() for k in range(b)]
         return toks, lps, st.finished.cpu(), n_steps
 
-    def _prefill(self, prompts: List[torch.Tensor], plens: List[int], block_tables: torch.Tensor, cache: PagedKVCache, out_last: torch.Tensor) -> None:
+    def _prefill(self, prompts: List[torch.Tensor], plens: List[int], block_tables: torch.Tensor, cache: PagedKVCache, out_last: torch.Tensor,
+                 extras: Optional[List[Any]] = None, rope_offset_out: Optional[torch.Tensor] = None) -> None:
         dev, ps = self.device, self.page_size
         tokens = torch.cat([p.to(torch.long) for p in prompts]).to(dev)
         cu = torch.zeros(len(plens) + 1, dtype=torch.int32)
@@ -170,6 +180,10 @@ class ARGenerator:
         page = block_tables[seq_id, (positions // ps)].long()
         meta = AttnMeta(mode="prefill", positions=positions, cu_seqlens=cu.to(dev), max_seqlen=max(plens), k_cache=cache.k, v_cache=cache.v,
                         slot_mapping=page * ps + positions % ps)
+        if extras is not None and hasattr(self.model, "prepare_multimodal"):
+            deltas = self.model.prepare_multimodal(prompts, extras, meta)
+            if rope_offset_out is not None and deltas is not None:
+                rope_offset_out.copy_(deltas.to(rope_offset_out))
         hidden = self.model(tokens, meta)
         out_last.copy_(hidden[(cu[1:].long() - 1).to(dev)])
 
@@ -206,6 +220,7 @@ class _DecodeState:
         z = lambda dt, *shape: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
         self.out_tokens, self.out_logp = z(torch.long, b, max_new), z(torch.float32, b, max_new)
         self.cur_tokens, self.positions, self.slots = z(torch.long, b), z(torch.long, b), z(torch.long, b)
+        self.rope_offset, self.rope_pos = z(torch.long, b), z(torch.long, b)  # rotary position = cache index + per-sequence offset
         self.seq_lens = z(torch.int32, b)
         self.lengths = z(torch.long, b)
         self.finished = z(torch.bool, b)
@@ -231,6 +246,7 @@ class _DecodeState:
         page = block_tables.gather(1, (self.positions // page_size).unsqueeze(1)).squeeze(1).long()
         self.slots.copy_(page * page_size + self.positions % page_size)
         self.seq_lens.copy_((self.positions + 1).to(torch.int32))
+        self.rope_pos.copy_(self.positions + self.rope_offset)
 
 
 __all__ = ["ARGenerator", "GenerationOutput"]

@@ -88,6 +88,8 @@ class FSDPBackend(Remote):
         self.model.to(dev)
         if self.fsdp_cfg.activation_checkpointing and hasattr(self.model, "gradient_checkpointing"):
             self.model.gradient_checkpointing = True
+            if hasattr(self.model, "checkpoint_layers"):
+                self.model.checkpoint_layers = self.fsdp_cfg.checkpoint_layers
         low = parse_torch_dtype(self.fsdp_cfg.param_dtype) if self.fsdp_cfg.mixed_precision else next(self.model.parameters()).dtype
         if dev.type == "cpu" and not self.fsdp_cfg.mixed_precision:
             low = next(self.model.parameters()).dtype
