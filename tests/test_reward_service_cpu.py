@@ -1,0 +1,67 @@
+"""Reward scorers, the HTTP reward service and its client (served from a thread on 127.0.0.1)."""
+import os
+import sys
+import threading
+import time
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "reward_service"))
+
+from unirl_b200.distributed.utils import free_port  # noqa: E402
+from unirl_b200.reward.local.scorers import GenEvalScorer, OCRScorer, build_scorer  # noqa: E402
+from unirl_b200.reward.remote import RemoteRewardBackend, decode_image, encode_image  # noqa: E402
+from unirl_b200.types.primitives import Images, Texts  # noqa: E402
+from unirl_b200.types.reward import RewardRequest  # noqa: E402
+
+
+def _req(n=3, **kw):
+    return RewardRequest(primitives={"text": Texts.from_list([f'a sign that says "hello {i}"' for i in range(n)])},
+                         generated={"image": Images(pixels=torch.rand(n, 3, 32, 32, generator=torch.Generator().manual_seed(0)))},
+                         sample_ids=[str(i) for i in range(n)], **kw)
+
+
+def test_png_round_trip_is_lossless_to_8_bits():
+    px = torch.rand(3, 17, 23)
+    assert float((decode_image(encode_image(px)) - px).abs().max()) <= 0.5 / 255 + 1e-6
+
+
+@pytest.mark.parametrize("name,lo,hi", [("clip", -1.0, 1.0), ("pickscore", -100.0, 100.0), ("hpsv2", -100.0, 100.0), ("aesthetic", 1.0, 10.0), ("image_reward", -50, 50)])
+def test_model_scorers_are_deterministic_and_in_range(name, lo, hi):
+    s = build_scorer(name, device="cpu", seed=3)
+    a, b = s.compute_rewards(_req()).rewards, s.compute_rewards(_req()).rewards
+    assert a == b and all(lo <= r <= hi for r in a)
+
+
+def test_rule_scorers():
+    ocr = OCRScorer().compute_rewards(_req(metadata=[{"ocr_text": "hello 0"}, {"ocr_text": "hellp 1"}, {"ocr_text": ""}])).rewards
+    assert ocr[0] == 1.0 and 0.5 < ocr[1] < 1.0 and ocr[2] == 0.0
+    meta = [{"include": [{"class": "dog", "count": 2}, {"class": "ball", "color": "red"}], "detections": [{"class": "dog"}, {"class": "dog"}, {"class": "ball", "color": "blue"}]}]
+    assert GenEvalScorer().compute_rewards(RewardRequest(metadata=meta, sample_ids=["0"])).rewards == [0.5]
+
+
+@pytest.mark.timeout(120)
+def test_http_service_and_client_agree_with_local_scoring():
+    import uvicorn
+    from unirl_b200_reward_service.app import create_app
+
+    port = free_port()
+    server = uvicorn.Server(uvicorn.Config(create_app({"clip": {"seed": 3}}), host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    client = RemoteRewardBackend(f"http://127.0.0.1:{port}", scorers=["clip", "geneval"], weights={"clip": 2.0, "geneval": 1.0}, batch_size=2, concurrency=2)
+    try:
+        for _ in range(100):
+            if client.is_available():
+                break
+            time.sleep(0.1)
+        assert client.is_available()
+        meta = [{"include": [{"class": "dog"}], "detections": [{"class": "dog"}]}] * 3
+        out = client.compute_rewards(_req(metadata=meta))
+        local = build_scorer("clip", device="cpu", seed=3).compute_rewards(_req()).rewards
+        assert len(out.rewards) == 3 and all(abs(o - (2.0 * l + 1.0)) < 2e-2 for o, l in zip(out.rewards, local))  # PNG quantisation only
+        assert set(out.component_rewards) == {"clip", "geneval"}
+    finally:
+        server.should_exit = True
+        th.join(10)
