@@ -325,3 +325,40 @@ def test_rollout_replay_parity_and_train_step_tiny():
     assert diff.mean() < 0.03 and diff.max() < 0.3, f"rollout/replay gap too large: mean {diff.mean():.4f} max {diff.max():.4f}"
     new.sum().backward()
     assert pipe.bundle.transformer.layers[0].qkv_proj.grad is not None
+
+
+def test_rope_with_fused_cache_write_matches_two_step_path():
+    from unirl_b200.ops.attention import kv_cache_write
+    from unirl_b200.ops.rope import qk_norm_rope, qk_norm_rope_cached
+
+    torch.manual_seed(0)
+    T, hq, hkv, d, page, pages = 37, 8, 2, 128, 16, 9
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+    qw, kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16(), (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    pos = torch.randint(0, 4000, (T,), device="cuda")
+    slots = torch.randperm(pages * page, device="cuda")[:T]
+    with torch.no_grad():
+        q0, k0, v0 = qk_norm_rope(qkv, qw, kw, pos, hq, hkv, d, 1e6, 1e-6)
+        kc0, vc0 = torch.zeros(pages, hkv, page, d, device="cuda", dtype=torch.bfloat16), torch.zeros(pages, hkv, page, d, device="cuda", dtype=torch.bfloat16)
+        kv_cache_write(k0, v0, kc0, vc0, slots)
+        for dense in (True, False):
+            kc, vc = torch.zeros_like(kc0), torch.zeros_like(vc0)
+            q, k, v = qk_norm_rope_cached(qkv, qw, kw, pos, hq, hkv, d, 1e6, 1e-6, kc, vc, slots, dense)
+            assert torch.equal(q, q0) and torch.equal(kc, kc0) and torch.equal(vc, vc0)
+            assert (k is None and v is None) if not dense else (torch.equal(k, k0) and torch.equal(v, v0))
+
+
+def test_decode_attention_single_split_writes_output_directly():
+    from unirl_b200.ops.attention import paged_decode_attention, paged_decode_attention_reference
+
+    torch.manual_seed(1)
+    b, hq, hkv, d, page, ctx = 80, 16, 4, 128, 32, 300  # 320 CTAs: one split, no merge pass
+    pages_per = (ctx + page - 1) // page
+    kc = torch.randn(b * pages_per, hkv, page, d, device="cuda").bfloat16()
+    vc = torch.randn_like(kc)
+    bt = torch.randperm(b * pages_per, device="cuda").view(b, pages_per).to(torch.int32)
+    sl = torch.randint(ctx // 2, ctx + 1, (b,), device="cuda", dtype=torch.int32)
+    q = torch.randn(b, hq, d, device="cuda").bfloat16()
+    out = paged_decode_attention(q, kc, vc, bt, sl, None, None, ctx)
+    ref = paged_decode_attention_reference(q, kc, vc, bt, sl)
+    _close(out, ref, 2e-2, 2e-2, "decode attention, single split")

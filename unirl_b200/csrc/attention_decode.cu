@@ -77,7 +77,7 @@ template <int D, bool kFast>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_tables,
                     const int* __restrict__ seq_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, int Hq, int Hkv, int page_size,
-                    int max_pages, int num_splits, float scale_log2, int* __restrict__ status) {
+                    int max_pages, int num_splits, float scale_log2, int* __restrict__ status, bf16* __restrict__ out_direct) {
   extern __shared__ __align__(128) uint8_t dec_smem[];
   using L = DecLayout<D>;
   constexpr int kND = D / 8;   // n-tiles of the output
@@ -246,6 +246,10 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
       acc += sm_o[((size_t)w * 16 + g) * D + d] * wgt;
     }
     const int64_t o_idx = ((int64_t)b * Hq + (int64_t)h * G + g) * num_splits + split;
+    if (out_direct) {  // a single split owns the whole sequence: normalise and emit bf16 here, no merge pass
+      out_direct[o_idx * D + d] = __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
+      continue;
+    }
     ws_o[o_idx * D + d] = acc;
     if (d == 0) {
       ws_ml[o_idx * 2] = M;
@@ -303,8 +307,9 @@ int paged_decode_attention(const void* q, const void* kc, const void* vc, const 
       cfg = true;                                                                                                                          \
     }                                                                                                                                      \
     paged_decode_kernel<DD, FF><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, block_tables, seq_lens, ws_o, \
-                                                                  ws_ml, Hq, Hkv, page_size, max_pages, num_splits, sl2, status);          \
-    decode_merge_kernel<DD><<<B * Hq, DD, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);                                                   \
+                                                                  ws_ml, Hq, Hkv, page_size, max_pages, num_splits, sl2, status,           \
+                                                                  num_splits == 1 ? (bf16*)out : nullptr);                                 \
+    if (num_splits > 1) decode_merge_kernel<DD><<<B * Hq, DD, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);                               \
   } while (0)
   if (D == 128) {
     if (fast) UB_DEC(128, true); else UB_DEC(128, false);

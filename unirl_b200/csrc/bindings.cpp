@@ -97,6 +97,27 @@ std::vector<Tensor> qk_norm_rope_fwd(const Tensor& qkv, const c10::optional<Tens
                        rstd.data_ptr<float>(), T, (int)Hq, (int)Hkv, (int)D, (float)eps, dt(qkv), stream());
   return {q, k, v, rstd};
 }
+// Inference variant: QK-norm + RoPE + KV-cache write in one launch.  `dense_kv` keeps the [T, Hkv, D] k / v outputs (prefill needs
+// them for the packed attention); decode reads the cache only and skips them.
+std::vector<Tensor> qk_norm_rope_cache_fwd(const Tensor& qkv, const Tensor& qw, const Tensor& kw, const Tensor& pos, Tensor& kc, Tensor& vc, const Tensor& slots,
+                                           int64_t Hq, int64_t Hkv, int64_t D, double theta, double eps, bool dense_kv) {
+  chk(qkv, "qkv"); chk(pos, "positions"); chk(kc, "k_cache"); chk(vc, "v_cache"); chk(slots, "slots");
+  TORCH_CHECK(qkv.scalar_type() == at::kBFloat16 && kc.scalar_type() == at::kBFloat16 && qkv.dim() == 2 && qkv.size(1) == (Hq + 2 * Hkv) * D, "qk_norm_rope_cache: bf16 qkv");
+  TORCH_CHECK(pos.scalar_type() == at::kInt && slots.scalar_type() == at::kLong && slots.numel() == qkv.size(0) && kc.dim() == 4 && kc.size(1) == Hkv && kc.size(3) == D,
+              "qk_norm_rope_cache: int32 positions, int64 slots, cache [pages, Hkv, page, D]");
+  c10::cuda::CUDAGuard g(qkv.device());
+  const int64_t T = qkv.size(0);
+  auto q = torch::empty({T, Hq, D}, qkv.options());
+  Tensor k, v;
+  if (dense_kv) { k = torch::empty({T, Hkv, D}, qkv.options()); v = torch::empty({T, Hkv, D}, qkv.options()); }
+  auto inv = inv_freq_table(D, theta, qkv.device());
+  const int rc = ub::qk_norm_rope_cache_fwd(qkv.data_ptr(), qw.data_ptr(), kw.data_ptr(), pos.data_ptr<int>(), inv.data_ptr<float>(), q.data_ptr(),
+                                            dense_kv ? k.data_ptr() : nullptr, dense_kv ? v.data_ptr() : nullptr, kc.data_ptr(), vc.data_ptr(), slots.data_ptr<int64_t>(), T,
+                                            (int)Hq, (int)Hkv, (int)D, (int)kc.size(2), (float)eps, stream());
+  TORCH_CHECK(rc == 0, "qk_norm_rope_cache_fwd: unsupported head_dim or launch failure (code ", rc, ")");
+  if (dense_kv) return {q, k, v};
+  return {q};
+}
 std::vector<Tensor> qk_norm_rope_bwd(const Tensor& gq, const Tensor& gk, const Tensor& gv, const Tensor& qkv, const c10::optional<Tensor>& qw,
                                      const c10::optional<Tensor>& kw, const Tensor& pos, const Tensor& rstd, int64_t Hq, int64_t Hkv, int64_t D, double theta) {
   chk(gq, "gq"); chk(gk, "gk"); chk(gv, "gv"); chk(qkv, "qkv");
@@ -399,6 +420,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_modulate_fwd", &layernorm_modulate_fwd);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("qk_norm_rope_cache_fwd", &qk_norm_rope_cache_fwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("kv_cache_write", &kv_cache_write);

@@ -249,7 +249,10 @@ __global__ void dlogits_vec_kernel(bf16* __restrict__ z, const int* __restrict__
 template <int D>
 __global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw, const int* __restrict__ pos,
                                             const float* __restrict__ inv_freq, bf16* __restrict__ q, bf16* __restrict__ k, bf16* __restrict__ v,
-                                            float* __restrict__ rstd, int64_t T_tokens, int Hq, int Hkv, float eps) {
+                                            float* __restrict__ rstd, int64_t T_tokens, int Hq, int Hkv, float eps, bf16* __restrict__ kc = nullptr,
+                                            bf16* __restrict__ vc = nullptr, const int64_t* __restrict__ slots = nullptr, int page_size = 1) {
+  // Optional fused KV-cache write: with kc/vc/slots set, the rotated k and the v of token t also go to cache slot
+  // slots[t] (layout [pages, Hkv, page, D]); k / v may then be null (decode needs only the cache copy).
   constexpr int half = D / 2, kJ = half / 64;  // pairs-of-2 per lane: D=128 -> 1, D=256 -> 2
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -270,7 +273,12 @@ __global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const 
   for (int h = 0; h < Hq + Hkv; ++h) {
     const bool is_q = h < Hq;
     const bf16* src = qkv + (t * H + h) * D;
-    bf16* dst = is_q ? q + (t * Hq + h) * D : k + (t * Hkv + (h - Hq)) * D;
+    bf16* dst = is_q ? q + (t * Hq + h) * D : (k ? k + (t * Hkv + (h - Hq)) * D : nullptr);
+    bf16* cdst = nullptr;
+    if (!is_q && kc) {
+      const int64_t slot = slots[t];
+      cdst = kc + (((slot / page_size) * Hkv + (h - Hq)) * page_size + slot % page_size) * D;
+    }
     float a[kJ][2], b[kJ][2];
     float ss = 0.f;
 #pragma unroll
@@ -293,14 +301,30 @@ __global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const 
         oa[e] = na * cs[j][e] - nb * sn[j][e];
         ob[e] = nb * cs[j][e] + na * sn[j][e];
       }
-      *reinterpret_cast<bf162*>(dst + j * 64 + lane * 2) = __floats2bfloat162_rn(oa[0], oa[1]);
-      *reinterpret_cast<bf162*>(dst + half + j * 64 + lane * 2) = __floats2bfloat162_rn(ob[0], ob[1]);
+      const bf162 pa = __floats2bfloat162_rn(oa[0], oa[1]), pb = __floats2bfloat162_rn(ob[0], ob[1]);
+      if (dst) {
+        *reinterpret_cast<bf162*>(dst + j * 64 + lane * 2) = pa;
+        *reinterpret_cast<bf162*>(dst + half + j * 64 + lane * 2) = pb;
+      }
+      if (cdst) {
+        *reinterpret_cast<bf162*>(cdst + j * 64 + lane * 2) = pa;
+        *reinterpret_cast<bf162*>(cdst + half + j * 64 + lane * 2) = pb;
+      }
     }
   }
   // v heads: straight copy, 8 bytes per lane per step
   const bf16* vs = qkv + (t * H + Hq + Hkv) * D;
-  bf16* vd = v + t * Hkv * D;
-  for (int c = lane * 4; c < Hkv * D; c += 128) *reinterpret_cast<uint2*>(vd + c) = *reinterpret_cast<const uint2*>(vs + c);
+  if (v) {
+    bf16* vd = v + t * Hkv * D;
+    for (int c = lane * 4; c < Hkv * D; c += 128) *reinterpret_cast<uint2*>(vd + c) = *reinterpret_cast<const uint2*>(vs + c);
+  }
+  if (vc) {
+    const int64_t slot = slots[t];
+    for (int c = lane * 4; c < Hkv * D; c += 128) {
+      const int hk = c / D, dd = c - hk * D;
+      *reinterpret_cast<uint2*>(vc + (((slot / page_size) * Hkv + hk) * page_size + slot % page_size) * D + dd) = *reinterpret_cast<const uint2*>(vs + c);
+    }
+  }
 }
 
 template <int D>
@@ -561,6 +585,21 @@ __global__ void qk_norm_rope_bwd_kernel(const T* __restrict__ gq, const T* __res
       atomicAdd(g_kw + i + half, acc_k[2 * j + 1]);
     }
   }
+}
+
+// QK-norm + RoPE with the KV-cache write folded in (bf16, head_dim 128 / 256).  k / v dense outputs are optional.
+int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, void* kc, void* vc,
+                           const int64_t* slots, int64_t T, int Hq, int Hkv, int D, int page_size, float eps, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (D != 128 && D != 256) return 1;
+  const dim3 g((unsigned)((T + 3) / 4));
+  if (D == 128)
+    qk_norm_rope_fwd_vec_kernel<128><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq,
+                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size);
+  else
+    qk_norm_rope_fwd_vec_kernel<256><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq,
+                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, float* rstd,

@@ -25,6 +25,8 @@ void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int
 void qk_norm_rope_bwd(const void* gq, const void* gk, const void* gv, const void* qkv, const void* qw, const void* kw, const int* pos,
                       const float* inv_freq, const float* rstd, void* g_qkv, float* g_qw, float* g_kw, int64_t T, int Hq, int Hkv, int D, int dtype,
                       cudaStream_t s);
+int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, void* kc, void* vc,
+                           const int64_t* slots, int64_t T, int Hq, int Hkv, int D, int page_size, float eps, cudaStream_t s);
 void swiglu_fwd(const void* gu, void* out, int64_t rows, int I, int dtype, cudaStream_t s);
 void swiglu_bwd(const void* gy, const void* gu, void* g_gu, int64_t rows, int I, int dtype, cudaStream_t s);
 void kv_cache_write(const void* k, const void* v, void* kc, void* vc, const int64_t* slots, int64_t T, int Hkv, int D, int page_size, int dtype,

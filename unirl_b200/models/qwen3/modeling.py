@@ -31,7 +31,7 @@ import torch.nn as nn
 from unirl_b200.ops import attention as A
 from unirl_b200.ops.activation import swiglu
 from unirl_b200.ops.linear import linear
-from unirl_b200.ops.norm import rmsnorm
+from unirl_b200.ops.norm import add_rmsnorm, rmsnorm
 from unirl_b200.ops.rope import qk_norm_rope
 from unirl_b200.train.inject import lora_apply
 
@@ -154,21 +154,44 @@ class Qwen3DecoderLayer(nn.Module):
         qkv = self._proj(h, "qkv_proj")
         if self.qkv_bias is not None:
             qkv = qkv + self.qkv_bias
+        cached = meta.mode in ("decode", "prefill") and meta.k_cache is not None
+        if cached and (meta.positions is None or meta.positions.dim() == 1):
+            from unirl_b200.ops.rope import qk_norm_rope_cached
+
+            # rotary + KV-cache write in one pass; decode keeps no dense k / v at all (attention reads the cache)
+            return qk_norm_rope_cached(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps,
+                                       meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.slot_mapping, dense_kv=meta.mode == "prefill")
         if meta.positions is not None and meta.positions.dim() == 2:
             from unirl_b200.ops.rope import mrope_qk
 
-            return mrope_qk(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps,
-                            getattr(c, "mrope_section", (c.head_dim // 8, 3 * c.head_dim // 16, 3 * c.head_dim // 16)))
-        return qk_norm_rope(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps)
+            q, k, v = mrope_qk(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps,
+                               getattr(c, "mrope_section", (c.head_dim // 8, 3 * c.head_dim // 16, 3 * c.head_dim // 16)))
+        else:
+            q, k, v = qk_norm_rope(qkv, self.q_norm, self.k_norm, meta.positions, self.n_q, self.n_kv, c.head_dim, c.rope_theta, c.rms_norm_eps)
+        if cached:
+            A.kv_cache_write(k, v, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.slot_mapping)
+        return q, k, v
 
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
+        """The KV cache (decode / prefill) has already been written by :meth:`_qkv_rope`."""
         if meta.mode == "decode":
-            A.kv_cache_write(k, v, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.slot_mapping)
             return A.paged_decode_attention(q, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.block_tables,
                                             meta.seq_lens, self.scale, meta.workspace, meta.max_kv_len)
-        if meta.mode == "prefill":
-            A.kv_cache_write(k, v, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.slot_mapping)
         return A.varlen_attention(q, k, v, meta.cu_seqlens, meta.max_seqlen, True, self.scale)
+
+    def forward_infer(self, pending: Optional[torch.Tensor], x: torch.Tensor, meta: AttnMeta) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Inference path on one GPU: the residual add of a projection output is deferred and fused with the NEXT RMSNorm
+        (``add_rmsnorm``), so a block is 4 GEMMs + rope/cache + attention + 2 add-norms + SwiGLU.  ``pending`` is the previous
+        block's un-added down-projection output; returns ``(pending', x')`` for the next block."""
+        c = self.cfg
+        if pending is None:
+            h = rmsnorm(x, self.input_layernorm, c.rms_norm_eps)
+        else:
+            h, x = add_rmsnorm(pending, x, self.input_layernorm, c.rms_norm_eps)
+        q, k, v = self._qkv_rope(h, meta)
+        attn = self.attention(q, k, v, meta).reshape(x.shape[0], self.n_q * c.head_dim)
+        h, x = add_rmsnorm(self._proj(attn, "o_proj"), x, self.post_attention_layernorm, c.rms_norm_eps)
+        return self._proj(swiglu(self._proj(h, "gate_up_proj")), "down_proj"), x
 
     def forward_fused_tp(self, x: torch.Tensor, h: torch.Tensor, meta: AttnMeta, next_norm: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """Inference path under tensor parallelism: every row-parallel projection, its all-reduce, the residual add
@@ -246,6 +269,12 @@ class Qwen3Transformer(nn.Module):
             for i, layer in enumerate(self.layers):
                 nxt = self.layers[i + 1].input_layernorm if i + 1 < len(self.layers) else self.norm
                 x, h = layer.forward_fused_tp(x, h, meta, nxt)
+            return h
+        if not torch.is_grad_enabled() and x.is_cuda and self.tp.size == 1 and meta.mode in ("decode", "prefill"):
+            pending = None
+            for layer in self.layers:
+                pending, x = layer.forward_infer(pending, x, meta)
+            h, _ = add_rmsnorm(pending, x, self.norm, self.cfg.rms_norm_eps)
             return h
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled() and meta.mode == "train"
         n_ckpt = len(self.layers) if self.checkpoint_layers is None else int(self.checkpoint_layers)

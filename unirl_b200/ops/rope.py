@@ -70,6 +70,22 @@ def qk_norm_rope(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: 
     return qk_norm_rope_reference(qkv, q_weight, k_weight, positions, n_q, n_kv, head_dim, theta, eps)
 
 
+def qk_norm_rope_cached(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], positions: torch.Tensor, n_q: int, n_kv: int,
+                        head_dim: int, theta: float, eps: float, k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor, dense_kv: bool):
+    """Inference: QK-norm + rotary + KV-cache write.  Returns ``(q, k | None, v | None)``; ``dense_kv=False`` (decode) skips the
+    ``[T, Hkv, D]`` copies because attention reads the cache.  One launch on CUDA (bf16, head_dim 128 / 256, QK-norm on)."""
+    if use_native(qkv) and q_weight is not None and qkv.dtype == torch.bfloat16 and head_dim in (128, 256) and not torch.is_grad_enabled():
+        out = require_ext().qk_norm_rope_cache_fwd(qkv.contiguous(), q_weight, k_weight, positions.to(torch.int32), k_cache, v_cache, slot_mapping, n_q, n_kv,
+                                                   head_dim, float(theta), float(eps), bool(dense_kv))
+        count_launch()
+        return (out[0], out[1], out[2]) if dense_kv else (out[0], None, None)
+    from unirl_b200.ops.attention import kv_cache_write
+
+    q, k, v = qk_norm_rope(qkv, q_weight, k_weight, positions, n_q, n_kv, head_dim, theta, eps)
+    kv_cache_write(k, v, k_cache, v_cache, slot_mapping)
+    return q, k, v
+
+
 def mrope_cos_sin(positions3: torch.Tensor, head_dim: int, theta: float, sections: Tuple[int, int, int]) -> Tuple[torch.Tensor, torch.Tensor]:
     """Multimodal rotary tables: frequency ``j`` takes its position from the temporal, height or width axis according to
     ``sections`` (counts of frequencies per axis, summing to ``head_dim / 2``).  ``positions3`` is ``[3, T]``."""
@@ -95,4 +111,4 @@ def mrope_qk(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Opti
     return _rotate(q, cos, sin).to(qkv.dtype), _rotate(k, cos, sin).to(qkv.dtype), v.reshape(t, n_kv, head_dim).to(qkv.dtype)
 
 
-__all__ = ["qk_norm_rope", "qk_norm_rope_reference", "rope_cos_sin", "mrope_qk", "mrope_cos_sin"]
+__all__ = ["qk_norm_rope", "qk_norm_rope_reference", "qk_norm_rope_cached", "rope_cos_sin", "mrope_qk", "mrope_cos_sin"]

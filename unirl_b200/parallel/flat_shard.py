@@ -171,12 +171,15 @@ class FlatShardedModel:
 
     def __init__(self, module: nn.Module, comm: Optional[Comm] = None, *, block_class_names: Sequence[str] = (), root_wrap: bool = True,
                  reshard_after_forward: bool = False, low_dtype: torch.dtype = torch.bfloat16, master_dtype: torch.dtype = torch.float32,
-                 shard_comm: Optional[ShardComm] = None, trainable_only: bool = False):
+                 shard_comm: Optional[ShardComm] = None, trainable_only: bool = False, grad_replicas: int = 1):
         self.module = module
         self.comm = comm or Comm.solo()
         self.rank, self.world = max(self.comm.rank, 0), self.comm.size
         self.reshard_after_forward = bool(reshard_after_forward)
         self.shard_comm = shard_comm or ShardComm(self.comm)
+        # Sequence / tensor-parallel peers see the SAME samples and hold PARTIAL gradients of them: their contributions add up,
+        # only the data-parallel replicas are averaged.  The reduce averages over all ranks, so gradients are rescaled by this factor.
+        self.grad_replicas = max(1, int(grad_replicas))
         self.device = next(module.parameters()).device
         self.groups: List[FlatGroup] = []
         self._sync_enabled = True
@@ -280,13 +283,15 @@ class FlatShardedModel:
             total = torch.stack(parts).sum() if parts else torch.zeros((), device=self.device)
             total = total.reshape(1).float()
         self.comm.all_reduce(total)
-        return total.sqrt().reshape(())
+        return total.sqrt().reshape(()) * float(self.grad_replicas)
 
     def optimizer_step(self, *, lr: float, betas: Tuple[float, float], eps: float, weight_decay: float, step: int,
                        clip_coef: Optional[torch.Tensor] = None, ema_decay: Optional[float] = None) -> None:
         for g in self.groups:
             if not g.trainable or g.grad_shard is None:
                 continue
+            if self.grad_replicas > 1:
+                g.grad_shard.mul_(float(self.grad_replicas))
             if self.world > 1 and self.shard_comm.fused_optimizer:
                 self.shard_comm.adamw_publish(g, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, step=step, clip_coef=clip_coef,
                                               ema=g.ema if ema_decay is not None else None, ema_decay=ema_decay or 0.0)

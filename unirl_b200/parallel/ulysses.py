@@ -1,0 +1,137 @@
+"""Ulysses sequence parallelism for the DiT attention: ranks hold ``L / P`` latent tokens each; around the attention core
+the sequence shards are exchanged for head shards (``[B, L/P, H, D] → [B, L, H/P, D]``) and back.
+
+Text tokens of a joint block are replicated on every rank (they are few), so the exchange only moves the latent part:
+after the first all-to-all every rank holds ALL latent tokens and ALL text tokens for ITS ``H / P`` heads, runs plain
+attention, and the second all-to-all returns the latent outputs to their sequence owners; text outputs are all-gathered
+over heads.
+
+Collectives go through :class:`Comm` (NCCL all-to-all over NVLink; gloo emulation on CPU for tests).
+Parity: the ``ulysses_degree`` knob the reference passes to its external engines
+(``unirl/rollout/engine/vllm_omni/stage_configs/sd35_t2i_rl.yaml:42-54``, ``patch_denoising.py:137``) — here a first-class
+part of the model code so the trainer uses it too.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+
+from unirl_b200.distributed.group.comm import Comm
+from unirl_b200.ops.attention import dense_attention
+
+
+class _SeqToHead(torch.autograd.Function):
+    """``[B, l, H, D]`` (sequence shard, all heads) → ``[B, l·P, H/P, D]`` (all tokens, head shard); backward is the inverse exchange."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Comm) -> torch.Tensor:
+        ctx.comm = comm
+        return _a2a_seq_to_head(x, comm)
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        return _a2a_head_to_seq(g.contiguous(), ctx.comm), None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Comm) -> torch.Tensor:
+        ctx.comm = comm
+        return _a2a_head_to_seq(x, comm)
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        return _a2a_seq_to_head(g.contiguous(), ctx.comm), None
+
+
+def _a2a_seq_to_head(x: torch.Tensor, comm: Comm) -> torch.Tensor:
+    p = comm.size
+    b, l, h, d = x.shape
+    send = x.view(b, l, p, h // p, d).permute(2, 0, 1, 3, 4).contiguous()  # [P(dst head group), B, l, H/P, D]
+    recv = torch.empty_like(send)
+    comm.all_to_all_single(recv, send)  # recv[j] = rank j's tokens for my head group
+    return recv.permute(1, 0, 2, 3, 4).reshape(b, p * l, h // p, d)
+
+
+def _a2a_head_to_seq(x: torch.Tensor, comm: Comm) -> torch.Tensor:
+    p = comm.size
+    b, lp, hp, d = x.shape
+    l = lp // p
+    send = x.view(b, p, l, hp, d).permute(1, 0, 2, 3, 4).contiguous()  # [P(dst seq owner), B, l, H/P, D]
+    recv = torch.empty_like(send)
+    comm.all_to_all_single(recv, send)  # recv[j] = my tokens for rank j's head group
+    return recv.permute(1, 2, 0, 3, 4).reshape(b, l, p * hp, d)
+
+
+class _GatherHeads(torch.autograd.Function):
+    """All-gather along the head axis (text outputs); backward keeps this rank's slice of the gradient (text is replicated,
+    so every rank computes the same text gradient and no reduction is needed)."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Comm) -> torch.Tensor:
+        ctx.comm, ctx.hp = comm, x.shape[2]
+        parts = comm.all_gather(x.contiguous())
+        return torch.cat(parts, 2)
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        r = ctx.comm.rank
+        return g[:, :, r * ctx.hp : (r + 1) * ctx.hp].contiguous(), None
+
+
+class UlyssesContext:
+    def __init__(self, comm: Comm):
+        self.comm = comm
+        self.size, self.rank = comm.size, max(comm.rank, 0)
+
+    # ---- sequence sharding of the latent stream ---------------------------------------------------------------
+    def shard_sequence(self, x: torch.Tensor) -> torch.Tensor:
+        l = x.shape[1]
+        if l % self.size:
+            raise ValueError(f"latent sequence of {l} tokens does not split over {self.size} sequence-parallel ranks")
+        n = l // self.size
+        return x[:, self.rank * n : (self.rank + 1) * n]
+
+    def shard_rope(self, table: torch.Tensor, n_text: int) -> torch.Tensor:
+        """Rotary table ``[n_text + L, D/2]`` → this rank's ``[n_text + L/P, D/2]`` (text rows kept whole)."""
+        lat = table[n_text:]
+        n = lat.shape[0] // self.size
+        return torch.cat([table[:n_text], lat[self.rank * n : (self.rank + 1) * n]])
+
+    def gather_sequence(self, x: torch.Tensor) -> torch.Tensor:
+        return _GatherSeq.apply(x, self.comm)
+
+    # ---- attention ----------------------------------------------------------------------------------------------
+    def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_text: int = 0) -> torch.Tensor:
+        """``q, k, v [B, n_text + L/P, H, D]`` → attention output with the same layout."""
+        p, hp = self.size, q.shape[2] // self.size
+        if q.shape[2] % p:
+            raise ValueError(f"{q.shape[2]} heads do not split over {p} sequence-parallel ranks")
+        lat = [_SeqToHead.apply(t[:, n_text:].contiguous(), self.comm) for t in (q, k, v)]
+        if n_text:
+            txt = [t[:, :n_text, self.rank * hp : (self.rank + 1) * hp] for t in (q, k, v)]
+            qq, kk, vv = (torch.cat([a, b], 1) for a, b in zip(txt, lat))
+        else:
+            qq, kk, vv = lat
+        o = dense_attention(qq, kk, vv)
+        out_lat = _HeadToSeq.apply(o[:, n_text:].contiguous(), self.comm)
+        if not n_text:
+            return out_lat
+        return torch.cat([_GatherHeads.apply(o[:, :n_text], self.comm), out_lat], 1)
+
+
+class _GatherSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Comm) -> torch.Tensor:
+        ctx.comm, ctx.n = comm, x.shape[1]
+        return torch.cat(comm.all_gather(x.contiguous()), 1)
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        r = ctx.comm.rank
+        return g[:, r * ctx.n : (r + 1) * ctx.n].contiguous(), None
+
+
+__all__ = ["UlyssesContext"]

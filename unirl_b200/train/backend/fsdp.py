@@ -94,8 +94,21 @@ class FSDPBackend(Remote):
         if dev.type == "cpu" and not self.fsdp_cfg.mixed_precision:
             low = next(self.model.parameters()).dtype
         blocks = self._block_class_names or tuple(getattr(self.model, "_no_split_modules", ()) or ())
+        sp = int(getattr(self.fsdp_cfg, "sp_size", 1) or 1)
+        if sp > 1:
+            from unirl_b200.parallel.ulysses import UlyssesContext
+
+            if self.comm.size % sp:
+                raise ValueError(f"sp_size={sp} does not divide the trainer's {self.comm.size} ranks")
+            if self.rank_info.sp_size != sp:
+                raise ValueError(f"fsdp_cfg.sp_size={sp} but the role was placed with sp={self.rank_info.sp_size}; pass train_parallel={{sp: {sp}}}")
+            groups = [list(range(g * sp, (g + 1) * sp)) for g in range(self.comm.size // sp)]
+            ctx = UlyssesContext(self.comm.split(groups))
+            for m in self.model.modules():
+                if hasattr(m, "sp") and hasattr(m, "patchify"):
+                    m.sp = ctx
         self.sharded = FlatShardedModel(self.model, self.comm, block_class_names=blocks, root_wrap=self.fsdp_cfg.root_wrap,
-                                        reshard_after_forward=False, low_dtype=low, trainable_only=False,
+                                        reshard_after_forward=False, low_dtype=low, trainable_only=False, grad_replicas=sp,
                                         shard_comm=self._make_shard_comm())
         if shadow is not None:
             shadow.bind(self.sharded)

@@ -44,6 +44,7 @@ class FSDPConfig:
     fsdp_mode: str = "full"  # full | hybrid
     reshard_after_forward: bool = True
     activation_checkpointing: bool = False
+    sp_size: int = 1  # Ulysses sequence-parallel degree inside one data-parallel replica (the role must be created with parallel={"sp": n})
     checkpoint_layers: Optional[int] = None  # with activation_checkpointing: recompute only the first N blocks (None = every block)
     use_torch_compile: bool = False  # accepted for recipe compatibility; there is no tracing compiler here
     defer_grad_sync: bool = False

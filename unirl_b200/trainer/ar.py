@@ -47,6 +47,8 @@ class ARTrainer(BaseTrainer):
         rollout_fraction = float(get("rollout_fraction", 0.5))
         rollout_parallel = get("rollout_parallel")
         rollout_parallel = dict(rollout_parallel) if rollout_parallel else None
+        train_parallel = get("train_parallel")
+        self._train_parallel = dict(train_parallel) if train_parallel else None  # e.g. {sp: 8}: sequence-parallel peers share every batch shard
         rp = parse_cfg(rollout_cfg)
         wants_pipeline = "pipeline" in inspect.signature(rp["role_cls"]).parameters
         wants_bundle = "bundle" in inspect.signature(rp["role_cls"]).parameters
@@ -58,7 +60,7 @@ class ARTrainer(BaseTrainer):
                     extra["pipeline"] = self.pipeline
                 elif wants_bundle:
                     extra["bundle"] = self.bundle
-                self.rollout = remote(**rp, parallel=rollout_parallel, **extra)
+                self.rollout = remote(**rp, parallel=rollout_parallel if rollout_parallel is not None else (self._train_parallel if wants_pipeline else None), **extra)
                 self.reward = remote_cfg(reward_cfg)
                 if sync_cfg is not None:
                     self.weight_sync = remote_cfg(sync_cfg, backend=self.backend, rollout=self.rollout)
@@ -78,13 +80,14 @@ class ARTrainer(BaseTrainer):
         self.last_sync_stats: Dict[str, float] = {}
 
     def _build_train_roles(self, bundle_cfg: Any, pipeline_cfg: Any, backend_cfg: Any, algorithm_cfg: Any, stack_cfg: Any) -> None:
-        self.bundle = remote_cfg(bundle_cfg)
-        self.pipeline = remote_cfg(pipeline_cfg, bundle=self.bundle)
-        self.backend = remote_cfg(backend_cfg, bundle=self.bundle)
+        par = {"parallel": self._train_parallel} if self._train_parallel else {}
+        self.bundle = remote_cfg(bundle_cfg, **par)
+        self.pipeline = remote_cfg(pipeline_cfg, bundle=self.bundle, **par)
+        self.backend = remote_cfg(backend_cfg, bundle=self.bundle, **par)
         algo_params = inspect.signature(parse_cfg(algorithm_cfg)["role_cls"]).parameters
         extra = {"backend": self.backend} if "backend" in algo_params else {}  # e.g. DiffusionNFT reads the EMA adapter policy from it
-        self.algorithm = remote_cfg(algorithm_cfg, pipeline=self.pipeline, **extra)
-        self.stack = remote_cfg(stack_cfg, fsdp_backend=self.backend, algorithm=self.algorithm)
+        self.algorithm = remote_cfg(algorithm_cfg, pipeline=self.pipeline, **extra, **par)
+        self.stack = remote_cfg(stack_cfg, fsdp_backend=self.backend, algorithm=self.algorithm, **par)
 
     # ---- request ------------------------------------------------------------------------------------------
     def _build_req(self, inputs: RolloutInputs, rollout_id: int, sampling_params: Any = None) -> RolloutReq:
