@@ -53,3 +53,54 @@ def test_every_recipe_target_resolves():
 def test_compose_recipe():
     cfg = compose("ar/tiny_qwen3_grpo_cpu", overrides=["num_rollouts=3"])
     assert cfg.num_rollouts == 3 and cfg.bundle.config.pretrained_model_ckpt_path == "random:tiny"
+
+
+def test_recipe_validators_flag_cross_component_mistakes():
+    from unirl_b200.config.loader import compose
+    from unirl_b200.config.validation import ConfigValidationError, validate_recipe
+
+    validate_recipe(compose("ar/qwen3_4b_grpo_b200", overrides=[]))
+    validate_recipe(compose("diffusion/tiny_sd3_flowgrpo_cpu", overrides=[]))
+    for ov, needle in ((["rollout.config.tp_size=4"], "rollout_parallel"), (["sampling.max_new_tokens=8192"], "max_new_tokens"), (["batch_size=3", "num_devices=8", "sampling.samples_per_prompt=1"], "data-parallel")):
+        with pytest.raises(ConfigValidationError, match=needle):
+            validate_recipe(compose("ar/qwen3_4b_grpo_b200", overrides=ov))
+    with pytest.raises(ConfigValidationError, match="guidance"):
+        validate_recipe(compose("diffusion/tiny_sd3_flowgrpo_cpu", overrides=["sampling.guidance_scale=5.0"]))
+    with pytest.raises(ConfigValidationError, match="sde_indices"):
+        validate_recipe(compose("diffusion/tiny_sd3_flowgrpo_cpu", overrides=["sampling.sde_indices=[0, 9]"]))
+
+
+def test_export_hf_full_and_lora(tmp_path):
+    import torch
+    from safetensors.torch import load_file
+
+    from unirl_b200.models.qwen3.bundle import Qwen3Bundle
+    from unirl_b200.models.qwen3.config import Qwen3PipelineConfig
+    from unirl_b200.tools.export_hf import export
+    from unirl_b200.train import inject
+
+    b = Qwen3Bundle.from_config(Qwen3PipelineConfig(pretrained_model_ckpt_path="random:tiny", device="cpu", model_precision="bf16"))
+    m = b.transformer
+    (tmp_path / "full").mkdir()
+    torch.save({"policy_state_dict": {k: v.detach().clone() for k, v in m.state_dict().items()}, "lora_config": None}, tmp_path / "full" / "checkpoint.pt")
+    assert export(str(tmp_path / "full"), "random:tiny", str(tmp_path / "out_full"))["tensors"] > 10
+    hf = load_file(str(tmp_path / "out_full" / "model.safetensors"))
+    nq = m.layers[0].n_q * m.cfg.head_dim
+    assert torch.equal(hf["model.layers.0.self_attn.q_proj.weight"], m.layers[0].qkv_proj[:nq].detach())
+    # LoRA checkpoint: merged export equals W + B·A·alpha/r, adapter-only export is PEFT shaped
+    inject.inject_lora(m, rank=4, alpha=8, target_modules=("q_proj", "v_proj"))
+    for mod in m.modules():
+        if hasattr(mod, "lora"):
+            for ad in mod.lora.values():
+                torch.nn.init.normal_(ad.lora_B, std=0.05)
+    (tmp_path / "lora").mkdir()
+    torch.save({"policy_state_dict": {k: v.detach().clone() for k, v in m.state_dict().items()},
+                "lora_config": {"rank": 4, "alpha": 8, "target_modules": ["q_proj", "v_proj"]}}, tmp_path / "lora" / "checkpoint.pt")
+    export(str(tmp_path / "lora"), "random:tiny", str(tmp_path / "out_merged"))
+    merged = load_file(str(tmp_path / "out_merged" / "model.safetensors"))
+    ad = m.layers[0].lora["q_proj__default"]
+    want = (m.layers[0].qkv_proj[:nq].float() + ad.lora_B.float() @ ad.lora_A.float() * ad.scaling).to(torch.bfloat16)
+    torch.testing.assert_close(merged["model.layers.0.self_attn.q_proj.weight"].float(), want.float(), atol=1e-2, rtol=1e-2)
+    assert export(str(tmp_path / "lora"), "random:tiny", str(tmp_path / "out_adapter"), adapter_only=True)["adapter"] == 1
+    peft = load_file(str(tmp_path / "out_adapter" / "adapter_model.safetensors"))
+    assert any(k.endswith("self_attn.q_proj.lora_A.default.weight") for k in peft)

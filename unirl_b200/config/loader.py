@@ -111,6 +111,10 @@ def main_entry(default_config: Optional[str] = None) -> Callable[[Callable[[Conf
 
                 print(yaml.safe_dump(to_container(cfg, resolve=flags["resolve"]), sort_keys=False))
                 return None
+            if bool(cfg.get("validate", False)) or os.environ.get("UNIRL_B200_VALIDATE") == "1":
+                from unirl_b200.config.validation import validate_recipe
+
+                validate_recipe(cfg)
             return fn(cfg)
 
         return wrapper

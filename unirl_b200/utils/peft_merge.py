@@ -15,6 +15,12 @@ import torch
 import torch.nn as nn
 
 
+def _key(target: str, adapter: str) -> str:
+    from unirl_b200.train.inject import _key as k
+
+    return k(target, adapter)
+
+
 def _cast(t: torch.Tensor, dtype: Optional[torch.dtype]) -> torch.Tensor:
     return t.to(dtype) if dtype is not None and t.is_floating_point() and t.dtype != dtype else t
 
@@ -36,7 +42,7 @@ def merged_state_dict(model: nn.Module, dtype: Optional[torch.dtype] = None, ada
             continue
         w = p.detach().float().clone()
         for target in host._lora_index[leaf]:
-            key = f"{target}__{adapter}"
+            key = _key(target, adapter)
             if key in host.lora:
                 ad = host.lora[key]
                 w[ad.row_offset : ad.row_offset + ad.rows] += (ad.lora_B.detach().float() @ ad.lora_A.detach().float()) * ad.scaling
