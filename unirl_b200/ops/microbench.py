@@ -7,6 +7,7 @@ Cases
 ``linear_logprob``    fused ``lm_head → log-softmax → gather`` against materialised logits
 ``linear_sample``     fused ``lm_head → Gumbel-max sampling``
 ``elementwise``       RMSNorm / QK-norm+RoPE / SwiGLU streaming kernels
+``decode_step``       one whole decode step of the Qwen3-4B-shaped policy at a fixed context (eager and CUDA-graph replay)
 ``peer``              (under ``torchrun``) fused peer-memory collectives against their NCCL compositions
 
 Timing: CUDA events on the launching stream, ≥3 warm-up iterations, a 256 MiB buffer is rewritten between timed
@@ -162,6 +163,51 @@ def case_elementwise(args: argparse.Namespace) -> None:
            "frac_of_peak": 2 * qkv.numel() * 2 / r["best_ms"] / 1e6 / pk["hbm_gbs"], "peak": pk["kind"]})
 
 
+def case_decode_step(args: argparse.Namespace) -> None:
+    """One full decode step of the Qwen3-4B-shaped policy (36 blocks + fused lm_head sampling) at a fixed context length, eager launches
+    (so a profiler can list kernels) and replayed from a CUDA graph (what the rollout engine runs)."""
+    from unirl_b200.models.qwen3.modeling import AttnMeta, Qwen3Config, Qwen3Transformer
+    from unirl_b200.ops._ext import require_ext
+    from unirl_b200.ops.sampling import linear_sample
+    from unirl_b200.rollout.engine.native_ar.kv_cache import PagedKVCache
+
+    pk = _peaks()
+    cfg = Qwen3Config.qwen3_4b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    b, ctx, ps = args.batch, args.ctx, args.page_size
+    model = Qwen3Transformer(cfg, dtype=torch.bfloat16, device="cuda").init_weights(0).eval().requires_grad_(False)
+    pages_per = (ctx + 1 + ps - 1) // ps
+    cache = PagedKVCache(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim, ps, b * pages_per, torch.bfloat16, "cuda")
+    for t in cache.k + cache.v:
+        t.normal_()
+    bt = torch.randperm(b * pages_per, device="cuda").view(b, pages_per).to(torch.int32)
+    pos = torch.full((b,), ctx, dtype=torch.long, device="cuda")
+    page = bt.gather(1, (pos // ps).unsqueeze(1)).squeeze(1).long()
+    meta = AttnMeta(mode="decode", positions=pos, k_cache=cache.k, v_cache=cache.v, block_tables=bt, seq_lens=(pos + 1).to(torch.int32),
+                    slot_mapping=page * ps + pos % ps, max_kv_len=ctx + 1)
+    C = require_ext()
+    meta.workspace = torch.empty(C.decode_workspace_size(b, cfg.num_attention_heads, cfg.head_dim, ctx + 1), dtype=torch.float32, device="cuda")
+    tokens = torch.randint(0, cfg.vocab_size, (b,), device="cuda")
+
+    @torch.no_grad()
+    def step():
+        h = model(tokens, meta)
+        return linear_sample(h, model.output_weight, 1.0, 0, 1.0, seed=1, step=3)
+
+    eager = _Timer(args.iters, flush=False)(step)
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.graph(g, stream=s):
+        step()
+    graphed = _Timer(args.iters, flush=False)(g.replay)
+    n_param = sum(p.numel() for n, p in model.named_parameters() if not n.startswith("embed_tokens"))
+    gb = (n_param * 2 + 2.0 * b * ctx * cfg.num_key_value_heads * cfg.head_dim * 2 * cfg.num_hidden_layers) / 1e9
+    _emit({"case": "decode_step", "batch": b, "ctx": ctx, "layers": cfg.num_hidden_layers, "eager_ms": eager["median_ms"], "graph_ms": graphed["median_ms"],
+           "weights_plus_kv_gb": gb, "gbs": gb / graphed["median_ms"] * 1e3, "frac_of_peak": gb / graphed["median_ms"] * 1e3 / pk["hbm_gbs"], "peak": pk["kind"]})
+
+
 def case_peer(args: argparse.Namespace) -> None:
     """Fused peer-memory collectives vs their NCCL compositions (run under torchrun, one rank per GPU)."""
     import torch.distributed as dist
@@ -252,7 +298,7 @@ def case_peer(args: argparse.Namespace) -> None:
 
 
 CASES = {"gemm": case_gemm, "decode_attention": case_decode_attention, "linear_logprob": case_linear_logprob, "linear_sample": case_linear_sample,
-         "elementwise": case_elementwise, "peer": case_peer}
+         "elementwise": case_elementwise, "peer": case_peer, "decode_step": case_decode_step}
 
 
 def main() -> None:
@@ -271,6 +317,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=2560)
     ap.add_argument("--intermediate", type=int, default=9728)
     ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--layers", type=int, default=0, help="decode_step: number of decoder blocks (0 = the full 36)")
     ap.add_argument("--numel", type=int, default=101_000_000, help="peer: parameters in one sharded group (a Qwen3-4B block has 101 M)")
     args = ap.parse_args()
     if not torch.cuda.is_available():

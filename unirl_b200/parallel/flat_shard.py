@@ -132,6 +132,28 @@ class FlatGroup:
         self._pending = 0
         self._hooks: List[Any] = []
         self.trainable = any(s.param.requires_grad for s in self.slots)
+        self.module: Optional[nn.Module] = None  # the block whose forward / backward brackets the gather (ZeRO-3)
+        self.shard_resident: Optional[torch.Tensor] = None  # ZeRO-3: this rank's bf16 shard while the replica storage is released
+        self._gathered = True
+
+    # ---- ZeRO-3 residency ---------------------------------------------------------------------------
+    def release_replica(self) -> None:
+        """Keep only this rank's shard; the replica's storage is handed back to the allocator (views stay valid objects)."""
+        if not self._gathered:
+            return
+        if self.shard_resident is None:
+            self.shard_resident = self.param_shard.clone()
+        else:
+            self.shard_resident.copy_(self.param_shard)
+        self.flat_param.untyped_storage().resize_(0)
+        self._gathered = False
+
+    def restore_replica(self, gather: Callable[[torch.Tensor, torch.Tensor], None]) -> None:
+        if self._gathered:
+            return
+        self.flat_param.untyped_storage().resize_(self.padded * self.flat_param.element_size())
+        gather(self.flat_param, self.shard_resident)
+        self._gathered = True
 
     @staticmethod
     def padded_numel(named_params: Sequence[Tuple[str, nn.Parameter]], world: int) -> int:
@@ -171,8 +193,11 @@ class FlatShardedModel:
 
     def __init__(self, module: nn.Module, comm: Optional[Comm] = None, *, block_class_names: Sequence[str] = (), root_wrap: bool = True,
                  reshard_after_forward: bool = False, low_dtype: torch.dtype = torch.bfloat16, master_dtype: torch.dtype = torch.float32,
-                 shard_comm: Optional[ShardComm] = None, trainable_only: bool = False, grad_replicas: int = 1):
+                 shard_comm: Optional[ShardComm] = None, trainable_only: bool = False, grad_replicas: int = 1, replicate_comm: Optional[Comm] = None):
         self.module = module
+        # HSDP: `comm` is the SHARD group (parameters / optimizer state are sharded inside it), `replicate_comm` links the ranks that
+        # own the same shard in different replicas; gradients are reduce-scattered inside the shard group, then all-reduced across replicas.
+        self.replicate_comm = replicate_comm if replicate_comm is not None and replicate_comm.active else None
         self.comm = comm or Comm.solo()
         self.rank, self.world = max(self.comm.rank, 0), self.comm.size
         self.reshard_after_forward = bool(reshard_after_forward)
@@ -187,6 +212,8 @@ class FlatShardedModel:
         self._comm_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" and self.world > 1 else None
         self._build_groups(block_class_names, root_wrap, low_dtype, master_dtype, trainable_only)
         self._install_hooks()
+        if self.reshard_after_forward and self.world > 1:
+            self._install_zero3_hooks()
 
     # ---- construction ----------------------------------------------------------------------------
     def _build_groups(self, block_names: Sequence[str], root_wrap: bool, low: torch.dtype, master: torch.dtype, trainable_only: bool) -> None:
@@ -209,8 +236,10 @@ class FlatShardedModel:
         low_bytes = torch.empty((), dtype=low).element_size()
         self.shard_comm.reserve(sum(s * low_bytes + 256 for s in sizes),
                                 sum(s * 4 + 256 for s, (_, named) in zip(sizes, layout) if any(p.requires_grad for _, p in named)), self.device)
+        modules = dict(self.module.named_modules())
         for name, named in layout:
             self.groups.append(FlatGroup(name, named, self.rank, self.world, self.device, low, master, alloc=self.shard_comm))
+            self.groups[-1].module = modules.get(name)
         if self.world > 1 and self.shard_comm.persistent_grads:
             for g in self.groups:  # symmetric layout: every rank allocates in the same order
                 if g.trainable:
@@ -221,6 +250,34 @@ class FlatShardedModel:
             for s in g.slots:
                 if s.param.requires_grad:
                     g._hooks.append(s.param.register_post_accumulate_grad_hook(self._make_hook(g, s)))
+
+    # ---- ZeRO-3: replicas exist only around their block's forward and backward ------------------------------------
+    def _gather_into(self, out: torch.Tensor, shard: torch.Tensor) -> None:
+        self.comm.all_gather_into(out, shard)
+
+    def _install_zero3_hooks(self) -> None:
+        """Block groups release their replica after forward and after backward and gather it back right before either.  The root
+        group (embeddings, final norm, head) stays resident: it is used at both ends of every pass."""
+        if getattr(self.shard_comm, "persistent_grads", False):
+            raise ValueError("reshard_after_forward=True needs the library collectives (replica storage is released between uses)")
+        for g in self.groups:
+            if g.module is None or g.module is self.module:
+                continue
+            g._hooks.append(g.module.register_forward_pre_hook(lambda _m, _a, g=g: g.restore_replica(self._gather_into)))
+            g._hooks.append(g.module.register_forward_hook(lambda _m, _a, _o, g=g: g.release_replica()))
+            g._hooks.append(g.module.register_full_backward_pre_hook(lambda _m, _go, g=g: g.restore_replica(self._gather_into)))
+            g.release_replica()
+
+    def gather_all(self) -> None:
+        """Make every replica resident (checkpoint save, weight sync, rollout on the trainer's module)."""
+        for g in self.groups:
+            g.restore_replica(self._gather_into)
+
+    def release_all(self) -> None:
+        if self.reshard_after_forward and self.world > 1:
+            for g in self.groups:
+                if g.module is not None and g.module is not self.module:
+                    g.release_replica()
 
     def _make_hook(self, g: FlatGroup, s: ParamSlot) -> Callable[[torch.Tensor], None]:
         def hook(p: torch.Tensor) -> None:
@@ -233,6 +290,8 @@ class FlatShardedModel:
                 g._pending -= 1
                 if g._pending == 0:
                     self._launch_reduce(g)
+                    if self.reshard_after_forward and g.module is not None and g.module is not self.module:
+                        g.release_replica()  # this block's backward is complete
 
         return hook
 
@@ -261,6 +320,14 @@ class FlatShardedModel:
                 self.shard_comm.reduce_scatter_grad(g)
         else:
             self.shard_comm.reduce_scatter_grad(g)
+        if self.replicate_comm is not None:
+            if self._comm_stream is not None:
+                with torch.cuda.stream(self._comm_stream):
+                    self.replicate_comm.all_reduce(g.grad_shard)
+                    g.grad_shard.div_(self.replicate_comm.size)
+            else:
+                self.replicate_comm.all_reduce(g.grad_shard)
+                g.grad_shard.div_(self.replicate_comm.size)
         g._reduced = True
 
     def finish_grad_sync(self) -> None:
@@ -296,10 +363,12 @@ class FlatShardedModel:
                 self.shard_comm.adamw_publish(g, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, step=step, clip_coef=clip_coef,
                                               ema=g.ema if ema_decay is not None else None, ema_decay=ema_decay or 0.0)
                 continue
+            released = not g._gathered
             O.adamw_step(g.master, g.grad_shard, g.exp_avg, g.exp_avg_sq, lr=lr, beta1=betas[0], beta2=betas[1], eps=eps,
-                         weight_decay=weight_decay, step=step, low=g.param_shard, ema=g.ema if ema_decay is not None else None,
-                         ema_decay=ema_decay or 0.0, grad_scale_tensor=clip_coef)
-            self.shard_comm.publish_params(g)
+                         weight_decay=weight_decay, step=step, low=g.shard_resident if released else g.param_shard,
+                         ema=g.ema if ema_decay is not None else None, ema_decay=ema_decay or 0.0, grad_scale_tensor=clip_coef)
+            if not released:  # a released replica is rebuilt from the shards at its next use
+                self.shard_comm.publish_params(g)
 
     def release_grad_buffers(self) -> None:
         for g in self.groups:

@@ -107,8 +107,16 @@ class FSDPBackend(Remote):
             for m in self.model.modules():
                 if hasattr(m, "sp") and hasattr(m, "patchify"):
                     m.sp = ctx
-        self.sharded = FlatShardedModel(self.model, self.comm, block_class_names=blocks, root_wrap=self.fsdp_cfg.root_wrap,
-                                        reshard_after_forward=False, low_dtype=low, trainable_only=False, grad_replicas=sp,
+        shard_group, replicate_group = self.comm, None
+        hs = int(self.fsdp_cfg.hsdp_shard_size)
+        if self.fsdp_cfg.fsdp_mode == "hybrid" and self.comm.size > hs and self.comm.size % hs == 0:
+            n_rep = self.comm.size // hs
+            shard_group = self.comm.split([list(range(r * hs, (r + 1) * hs)) for r in range(n_rep)])
+            replicate_group = self.comm.split([[r * hs + i for r in range(n_rep)] for i in range(hs)])
+        self._shard_group = shard_group
+        zero3 = bool(self.fsdp_cfg.reshard_after_forward) and shard_group.active
+        self.sharded = FlatShardedModel(self.model, shard_group, block_class_names=blocks, root_wrap=self.fsdp_cfg.root_wrap,
+                                        reshard_after_forward=zero3, replicate_comm=replicate_group, low_dtype=low, trainable_only=False, grad_replicas=sp,
                                         shard_comm=self._make_shard_comm())
         if shadow is not None:
             shadow.bind(self.sharded)
@@ -121,7 +129,8 @@ class FSDPBackend(Remote):
         self._built = True
 
     def _make_shard_comm(self) -> Any:
-        if self.fsdp_cfg.collectives == "fused" and self.comm.active and torch.cuda.is_available():
+        fused_ok = not self.fsdp_cfg.reshard_after_forward and self.fsdp_cfg.fsdp_mode != "hybrid"  # peer arenas are never released and span one group
+        if fused_ok and self.fsdp_cfg.collectives == "fused" and self.comm.active and torch.cuda.is_available():
             try:
                 from unirl_b200.parallel.fused_collectives import FusedShardComm
 
@@ -132,6 +141,7 @@ class FSDPBackend(Remote):
 
     # ---- step protocol ---------------------------------------------------------------------------------
     def zero_grad(self) -> None:
+        self.sharded.release_all()  # ZeRO-3: replicas live only around their block while a train step runs (no-op otherwise)
         self.sharded.zero_grad()
 
     def set_grad_sync(self, enable: bool) -> None:
@@ -172,6 +182,7 @@ class FSDPBackend(Remote):
         if self.ema is not None:
             self.ema.on_rollout_end(self._optimizer_step_count)
         self.sharded.release_grad_buffers()
+        self.sharded.gather_all()  # ZeRO-3: rollout, weight sync and checkpointing see whole parameters
 
     @distributed(dispatch_mode=Dispatch.BROADCAST)
     def apply_eval_ema(self) -> None:

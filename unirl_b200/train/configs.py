@@ -41,8 +41,9 @@ class FSDPConfig:
     param_dtype: str = "bf16"
     cpu_offload: bool = False
     mixed_precision: bool = True
-    fsdp_mode: str = "full"  # full | hybrid
-    reshard_after_forward: bool = True
+    fsdp_mode: str = "full"  # full | hybrid (HSDP: shard inside groups of `hsdp_shard_size` ranks, replicate across them)
+    hsdp_shard_size: int = 8
+    reshard_after_forward: bool = False  # False: ZeRO-2, bf16 replica resident (default: HBM is plentiful); True: ZeRO-3, gather around each block
     activation_checkpointing: bool = False
     sp_size: int = 1  # Ulysses sequence-parallel degree inside one data-parallel replica (the role must be created with parallel={"sp": n})
     checkpoint_layers: Optional[int] = None  # with activation_checkpointing: recompute only the first N blocks (None = every block)
