@@ -250,14 +250,18 @@ template <int D>
 __global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw, const int* __restrict__ pos,
                                             const float* __restrict__ inv_freq, bf16* __restrict__ q, bf16* __restrict__ k, bf16* __restrict__ v,
                                             float* __restrict__ rstd, int64_t T_tokens, int Hq, int Hkv, float eps, bf16* __restrict__ kc = nullptr,
-                                            bf16* __restrict__ vc = nullptr, const int64_t* __restrict__ slots = nullptr, int page_size = 1) {
+                                            bf16* __restrict__ vc = nullptr, const int64_t* __restrict__ slots = nullptr, int page_size = 1, int chunks = 1) {
+  // `chunks` warps share one token, each taking a contiguous range of its Hq + 2·Hkv heads: a decode batch has too few tokens to
+  // fill the machine with one warp per token (the per-token head loop is then a 40-iteration serial chain).
   // Optional fused KV-cache write: with kc/vc/slots set, the rotated k and the v of token t also go to cache slot
   // slots[t] (layout [pages, Hkv, page, D]); k / v may then be null (decode needs only the cache copy).
   constexpr int half = D / 2, kJ = half / 64;  // pairs-of-2 per lane: D=128 -> 1, D=256 -> 2
   const int lane = threadIdx.x & 31;
-  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t t = wid / chunks;
   if (t >= T_tokens) return;
   const int H = Hq + 2 * Hkv;
+  const int per = (H + chunks - 1) / chunks, h_lo = (int)(wid - t * chunks) * per, h_hi = min(H, h_lo + per);
   const float p = (float)pos[t];
   float cs[kJ][2], sn[kJ][2], wqa[kJ][2], wqb[kJ][2], wka[kJ][2], wkb[kJ][2];
 #pragma unroll
@@ -270,7 +274,7 @@ __global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const 
       wka[j][e] = to_f(kw[i]); wkb[j][e] = to_f(kw[i + half]);
     }
   }
-  for (int h = 0; h < Hq + Hkv; ++h) {
+  for (int h = h_lo; h < min(h_hi, Hq + Hkv); ++h) {
     const bool is_q = h < Hq;
     const bf16* src = qkv + (t * H + h) * D;
     bf16* dst = is_q ? q + (t * Hq + h) * D : (k ? k + (t * Hkv + (h - Hq)) * D : nullptr);
@@ -312,17 +316,18 @@ __global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const 
       }
     }
   }
-  // v heads: straight copy, 8 bytes per lane per step
-  const bf16* vs = qkv + (t * H + Hq + Hkv) * D;
-  if (v) {
-    bf16* vd = v + t * Hkv * D;
-    for (int c = lane * 4; c < Hkv * D; c += 128) *reinterpret_cast<uint2*>(vd + c) = *reinterpret_cast<const uint2*>(vs + c);
-  }
-  if (vc) {
-    const int64_t slot = slots[t];
-    for (int c = lane * 4; c < Hkv * D; c += 128) {
-      const int hk = c / D, dd = c - hk * D;
-      *reinterpret_cast<uint2*>(vc + (((slot / page_size) * Hkv + hk) * page_size + slot % page_size) * D + dd) = *reinterpret_cast<const uint2*>(vs + c);
+  // v heads of this warp's range: straight copy, 8 bytes per lane per step
+  for (int h = max(h_lo, Hq + Hkv); h < h_hi; ++h) {
+    const int hk = h - Hq - Hkv;
+    const bf16* vs = qkv + (t * H + h) * D;
+    if (v) {
+      bf16* vd = v + (t * Hkv + hk) * D;
+      for (int c = lane * 4; c < D; c += 128) *reinterpret_cast<uint2*>(vd + c) = *reinterpret_cast<const uint2*>(vs + c);
+    }
+    if (vc) {
+      const int64_t slot = slots[t];
+      bf16* cd = vc + (((slot / page_size) * Hkv + hk) * page_size + slot % page_size) * D;
+      for (int c = lane * 4; c < D; c += 128) *reinterpret_cast<uint2*>(cd + c) = *reinterpret_cast<const uint2*>(vs + c);
     }
   }
 }
@@ -587,18 +592,26 @@ __global__ void qk_norm_rope_bwd_kernel(const T* __restrict__ gq, const T* __res
   }
 }
 
+// Warps per token for the rope kernels: enough warps to cover ~8 per SM, at most one head per warp.
+static int rope_chunks(int64_t T, int heads) {
+  if (T >= 1184) return 1;
+  int64_t c = (1184 + T - 1) / (T > 0 ? T : 1);
+  return (int)(c > heads ? heads : c);
+}
+
 // QK-norm + RoPE with the KV-cache write folded in (bf16, head_dim 128 / 256).  k / v dense outputs are optional.
 int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, void* kc, void* vc,
                            const int64_t* slots, int64_t T, int Hq, int Hkv, int D, int page_size, float eps, cudaStream_t s) {
   if (T == 0) return 0;
   if (D != 128 && D != 256) return 1;
-  const dim3 g((unsigned)((T + 3) / 4));
+  const int chunks = rope_chunks(T, Hq + 2 * Hkv);
+  const dim3 g((unsigned)((T * chunks + 3) / 4));
   if (D == 128)
     qk_norm_rope_fwd_vec_kernel<128><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq,
-                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size);
+                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size, chunks);
   else
     qk_norm_rope_fwd_vec_kernel<256><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq,
-                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size);
+                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size, chunks);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
