@@ -362,3 +362,24 @@ def test_decode_attention_single_split_writes_output_directly():
     out = paged_decode_attention(q, kc, vc, bt, sl, None, None, ctx)
     ref = paged_decode_attention_reference(q, kc, vc, bt, sl)
     _close(out, ref, 2e-2, 2e-2, "decode attention, single split")
+
+
+def test_padded_dense_attention_matches_reference_on_ragged_batch():
+    from unirl_b200.ops.attention import varlen_attention, varlen_attention_reference
+
+    torch.manual_seed(0)
+    lens = [300, 257, 288, 310]
+    t, hq, hkv, d = sum(lens), 8, 2, 128
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    q = torch.randn(t, hq, d, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(t, hkv, d, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(t, hkv, d, device="cuda").bfloat16().requires_grad_()
+    go = torch.randn(t, hq, d, device="cuda").bfloat16()
+    out = varlen_attention(q, k, v, cu, max(lens), True, None, lens)
+    out.backward(go)
+    got = (out.detach(), q.grad.clone(), k.grad.clone(), v.grad.clone())
+    qr, kr, vr = (x.detach().float().requires_grad_() for x in (q, k, v))
+    ref = varlen_attention_reference(qr, kr, vr, cu, True, d**-0.5)
+    ref.backward(go.float())
+    for a, b, name in zip(got, (ref.detach(), qr.grad, kr.grad, vr.grad), ("out", "dq", "dk", "dv")):
+        _close(a, b, 3e-2, 3e-2, f"padded dense attention {name}")

@@ -132,7 +132,8 @@ class Qwen3ARStage:
         tokens, positions, cu_dev, max_len, pred_index, targets = build_replay_batch(prompts, responses, device)
         if not targets.numel():
             return torch.zeros(0, dtype=torch.float32, device=device)
-        hidden = model(tokens, AttnMeta(mode="train", positions=positions, cu_seqlens=cu_dev, max_seqlen=max_len))
+        lens = [int(p.numel()) + int(r.numel()) for p, r in zip(prompts, responses)]
+        hidden = model(tokens, AttnMeta(mode="train", positions=positions, cu_seqlens=cu_dev, max_seqlen=max_len, seq_lens_host=lens))
         return linear_logprob(hidden.index_select(0, pred_index), model.output_weight, targets, float(temperature))
 
 

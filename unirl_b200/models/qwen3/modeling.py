@@ -108,6 +108,7 @@ class AttnMeta:
     slot_mapping: Optional[torch.Tensor] = None  # [T] int64
     workspace: Optional[torch.Tensor] = None
     max_kv_len: int = 0
+    seq_lens_host: Optional[List[int]] = None  # packed sequence lengths as host ints (saves a device read in attention dispatch)
     input_embeds: Optional[torch.Tensor] = None  # [T, H]: replaces the token-embedding lookup (multimodal prompts)
 
 
@@ -177,7 +178,7 @@ class Qwen3DecoderLayer(nn.Module):
         if meta.mode == "decode":
             return A.paged_decode_attention(q, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.block_tables,
                                             meta.seq_lens, self.scale, meta.workspace, meta.max_kv_len)
-        return A.varlen_attention(q, k, v, meta.cu_seqlens, meta.max_seqlen, True, self.scale)
+        return A.varlen_attention(q, k, v, meta.cu_seqlens, meta.max_seqlen, True, self.scale, meta.seq_lens_host)
 
     def forward_infer(self, pending: Optional[torch.Tensor], x: torch.Tensor, meta: AttnMeta) -> Tuple[torch.Tensor, torch.Tensor]:
         """Inference path on one GPU: the residual add of a projection output is deferred and fused with the NEXT RMSNorm

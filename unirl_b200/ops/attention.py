@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import math
 import os
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 import torch.nn.functional as F
@@ -85,16 +85,52 @@ def _library_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale):
     return flash_attn_varlen_func(q, k, v, cu, cu, int(max_seqlen), int(max_seqlen), 0.0, softmax_scale=float(scale), causal=bool(causal))
 
 
-def varlen_attention(q, k, v, cu_seqlens, max_seqlen: Optional[int] = None, causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
-    """Self attention over packed sequences (GQA when ``Hq > Hkv``)."""
+_PAD_WASTE_LIMIT = 1.35  # padded rows per real row above which the packed kernel is used instead of the dense one
+
+
+def _dense_sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, scale: float) -> torch.Tensor:
+    """``[B, L, H, D]`` through the dense fused-attention library kernel (cuDNN's Blackwell flash attention)."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    with sdpa_kernel([SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION]):
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=bool(causal), scale=float(scale),
+                                           enable_gqa=q.shape[2] != k.shape[2])
+    return o.transpose(1, 2)
+
+
+def _padded_dense(q, k, v, lens: Sequence[int], causal: bool, scale: float) -> Optional[torch.Tensor]:
+    """Packed sequences → one padded ``[B, Lmax]`` batch for the dense kernel (differentiable).  Padding sits at the END of every row:
+    under a causal mask no real query sees it; without a mask this path is only taken when no padding is needed."""
+    b, lmax, t = len(lens), max(lens), q.shape[0]
+    if b * lmax == t:  # equal lengths: pure views
+        return _dense_sdpa(q.view(b, lmax, *q.shape[1:]), k.view(b, lmax, *k.shape[1:]), v.view(b, lmax, *v.shape[1:]), causal, scale).reshape(t, *q.shape[1:])
+    if not causal or b * lmax > _PAD_WASTE_LIMIT * t:
+        return None
+    dst = torch.cat([torch.arange(n) + i * lmax for i, n in enumerate(lens)]).to(q.device)
+    pad = lambda x: x.new_zeros(b * lmax, *x.shape[1:]).index_copy(0, dst, x).view(b, lmax, *x.shape[1:])  # noqa: E731
+    o = _dense_sdpa(pad(q), pad(k), pad(v), causal, scale)
+    return o.reshape(b * lmax, *q.shape[1:]).index_select(0, dst)
+
+
+def varlen_attention(q, k, v, cu_seqlens, max_seqlen: Optional[int] = None, causal: bool = True, scale: Optional[float] = None,
+                     lens_host: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Self attention over packed sequences (GQA when ``Hq > Hkv``).  ``lens_host``: the sequence lengths as host integers when the
+    caller has them (avoids a device read); they let near-uniform batches run on the dense library kernel."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if use_native(q):
-        if max_seqlen is None:
-            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         if q.dtype not in (torch.bfloat16, torch.float16):
             return varlen_attention_reference(q, k, v, cu_seqlens, causal, scale)
         if _varlen_impl() == "native":
+            if max_seqlen is None:
+                max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
             return _VarlenAttention.apply(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        if lens_host is not None and os.environ.get("UNIRL_B200_DENSE_ATTN", "1") == "1" and q.shape[-1] in (64, 128):
+            out = _padded_dense(q, k, v, [int(n) for n in lens_host], causal, scale)
+            if out is not None:
+                return out
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         return _library_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
     return varlen_attention_reference(q, k, v, cu_seqlens, causal, scale)
 
@@ -151,6 +187,8 @@ def dense_attention(q, k, v, scale: Optional[float] = None) -> torch.Tensor:
     """
     b, l, h, d = q.shape
     if use_native(q):
+        if q.dtype in (torch.bfloat16, torch.float16) and d in (64, 128) and _varlen_impl() != "native" and os.environ.get("UNIRL_B200_DENSE_ATTN", "1") == "1":
+            return _dense_sdpa(q, k, v, False, scale if scale is not None else 1.0 / math.sqrt(d))
         cu = torch.arange(0, (b + 1) * l, l, device=q.device, dtype=torch.int32)
         o = varlen_attention(q.reshape(b * l, h, d), k.reshape(b * l, k.shape[2], d), v.reshape(b * l, v.shape[2], d), cu, l, False, scale)
         return o.view(b, l, h, d)

@@ -8,6 +8,8 @@ Cases
 ``linear_sample``     fused ``lm_head → Gumbel-max sampling``
 ``elementwise``       RMSNorm / QK-norm+RoPE / SwiGLU streaming kernels
 ``decode_step``       one whole decode step of the Qwen3-4B-shaped policy at a fixed context (eager and CUDA-graph replay)
+``attention``         causal self-attention forward / backward over packed sequences vs the dense library kernels
+``train_step``        forward + backward of one training micro-batch of the Qwen3-4B-shaped policy
 ``peer``              (under ``torchrun``) fused peer-memory collectives against their NCCL compositions
 
 Timing: CUDA events on the launching stream, ≥3 warm-up iterations, a 256 MiB buffer is rewritten between timed
@@ -208,6 +210,85 @@ def case_decode_step(args: argparse.Namespace) -> None:
            "weights_plus_kv_gb": gb, "gbs": gb / graphed["median_ms"] * 1e3, "frac_of_peak": gb / graphed["median_ms"] * 1e3 / pk["hbm_gbs"], "peak": pk["kind"]})
 
 
+def case_train_step(args: argparse.Namespace) -> None:
+    """Forward + backward of one training micro-batch of the Qwen3-4B-shaped policy (packed sequences, fused lm_head log-prob), no recompute."""
+    from unirl_b200.models.qwen3.modeling import AttnMeta, Qwen3Config, Qwen3Transformer
+    from unirl_b200.ops.logprob import linear_logprob
+
+    pk = _peaks()
+    cfg = Qwen3Config.qwen3_4b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    nseq, l = args.seqs, args.ctx
+    model = Qwen3Transformer(cfg, dtype=torch.bfloat16, device="cuda").init_weights(0)
+    tokens = torch.randint(0, cfg.vocab_size, (nseq * l,), device="cuda")
+    pos = torch.arange(l, device="cuda").repeat(nseq)
+    cu = torch.arange(0, (nseq + 1) * l, l, device="cuda", dtype=torch.int32)
+    idx = torch.arange(600, nseq * l - 1, device="cuda")
+
+    def step():
+        h = model(tokens, AttnMeta(mode="train", positions=pos, cu_seqlens=cu, max_seqlen=l, seq_lens_host=[l] * nseq))
+        linear_logprob(h.index_select(0, idx), model.output_weight, tokens[idx + 1], 1.0).mean().backward()
+        for p_ in model.parameters():
+            p_.grad = None
+
+    t = _Timer(args.iters, flush=False)(step, warmup=2)
+    ntok = nseq * l
+    dense = cfg.num_params() - 2 * cfg.vocab_size * cfg.hidden_size
+    flops = 6.0 * ntok * dense + 6.0 * idx.numel() * cfg.vocab_size * cfg.hidden_size + 3.0 * 4 * l * l / 2 * cfg.head_dim * cfg.num_attention_heads * cfg.num_hidden_layers * nseq
+    _emit({"case": "train_step", "seqs": nseq, "seq_len": l, "layers": cfg.num_hidden_layers, "median_ms": t["median_ms"], "tokens_per_s": ntok / t["median_ms"] * 1e3,
+           "model_tflops": flops / t["median_ms"] / 1e9, "frac_of_peak": flops / t["median_ms"] / 1e9 / pk["tflops"], "peak": pk["kind"]})
+
+
+def case_attention(args: argparse.Namespace) -> None:
+    """Causal self-attention forward + backward over a micro-batch of equal-length sequences: the packed-sequence op against the
+    dense library kernel on the same (padded) problem."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    from unirl_b200.ops.attention import varlen_attention
+
+    pk = _peaks()
+    b, l, hq, hkv, d = args.seqs, args.ctx, args.q_heads, args.kv_heads, args.head_dim
+    q = torch.randn(b * l, hq, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(b * l, hkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(b * l, hkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cu = torch.arange(0, (b + 1) * l, l, device="cuda", dtype=torch.int32)
+    go = torch.randn(b * l, hq, d, device="cuda", dtype=torch.bfloat16)
+    flops_f = 4.0 * l * l / 2 * d * hq * b
+    timer = _Timer(args.iters, flush=False)
+    lens = [l] * b if not args.ragged else None  # --ragged: dispatch without host lengths (packed kernel)
+
+    def packed():
+        varlen_attention(q, k, v, cu, l, True, None, lens).backward(go)
+        q.grad = k.grad = v.grad = None
+
+    def packed_fwd():
+        with torch.no_grad():
+            varlen_attention(q, k, v, cu, l, True, None, lens)
+
+    row = {"case": "attention", "seqs": b, "seq_len": l, "q_heads": hq, "kv_heads": hkv, "head_dim": d}
+    t = timer(packed_fwd)
+    row.update(packed_fwd_ms=t["median_ms"], packed_fwd_tflops=flops_f / t["median_ms"] / 1e9)
+    t = timer(packed)
+    row.update(packed_fwd_bwd_ms=t["median_ms"], packed_fwd_bwd_tflops=3.5 * flops_f / t["median_ms"] / 1e9)
+    qd, kd, vd = (x.detach().view(b, l, -1, d).transpose(1, 2).contiguous().requires_grad_() for x in (q, k, v))
+    god = go.view(b, l, hq, d).transpose(1, 2).contiguous()
+    for name, backend in (("cudnn", SDPBackend.CUDNN_ATTENTION), ("flash", SDPBackend.FLASH_ATTENTION)):
+        try:
+            def dense():
+                with sdpa_kernel(backend):
+                    F.scaled_dot_product_attention(qd, kd, vd, is_causal=True, enable_gqa=hq != hkv).backward(god)
+                qd.grad = kd.grad = vd.grad = None
+
+            t = timer(dense)
+            row.update({f"dense_{name}_fwd_bwd_ms": t["median_ms"], f"dense_{name}_fwd_bwd_tflops": 3.5 * flops_f / t["median_ms"] / 1e9})
+        except Exception as e:  # noqa: BLE001
+            row[f"dense_{name}_error"] = str(e)[:120]
+    row.update(frac_of_peak=row["packed_fwd_bwd_tflops"] / pk["tflops"], peak=pk["kind"])
+    _emit(row)
+
+
 def case_peer(args: argparse.Namespace) -> None:
     """Fused peer-memory collectives vs their NCCL compositions (run under torchrun, one rank per GPU)."""
     import torch.distributed as dist
@@ -298,7 +379,7 @@ def case_peer(args: argparse.Namespace) -> None:
 
 
 CASES = {"gemm": case_gemm, "decode_attention": case_decode_attention, "linear_logprob": case_linear_logprob, "linear_sample": case_linear_sample,
-         "elementwise": case_elementwise, "peer": case_peer, "decode_step": case_decode_step}
+         "elementwise": case_elementwise, "peer": case_peer, "decode_step": case_decode_step, "train_step": case_train_step, "attention": case_attention}
 
 
 def main() -> None:
@@ -317,6 +398,8 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=2560)
     ap.add_argument("--intermediate", type=int, default=9728)
     ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--ragged", action="store_true", help="attention: do not pass host sequence lengths")
+    ap.add_argument("--seqs", type=int, default=4, help="train_step: sequences per micro-batch")
     ap.add_argument("--layers", type=int, default=0, help="decode_step: number of decoder blocks (0 = the full 36)")
     ap.add_argument("--numel", type=int, default=101_000_000, help="peer: parameters in one sharded group (a Qwen3-4B block has 101 M)")
     args = ap.parse_args()

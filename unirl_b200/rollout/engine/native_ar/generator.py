@@ -179,7 +179,7 @@ class ARGenerator:
         seq_id = torch.repeat_interleave(torch.arange(len(plens)), torch.tensor(plens)).to(dev)
         page = block_tables[seq_id, (positions // ps)].long()
         meta = AttnMeta(mode="prefill", positions=positions, cu_seqlens=cu.to(dev), max_seqlen=max(plens), k_cache=cache.k, v_cache=cache.v,
-                        slot_mapping=page * ps + positions % ps)
+                        slot_mapping=page * ps + positions % ps, seq_lens_host=list(plens))
         if extras is not None and hasattr(self.model, "prepare_multimodal"):
             deltas = self.model.prepare_multimodal(prompts, extras, meta)
             if rope_offset_out is not None and deltas is not None:
