@@ -383,3 +383,61 @@ def test_padded_dense_attention_matches_reference_on_ragged_batch():
     ref.backward(go.float())
     for a, b, name in zip(got, (ref.detach(), qr.grad, kr.grad, vr.grad), ("out", "dq", "dk", "dv")):
         _close(a, b, 3e-2, 3e-2, f"padded dense attention {name}")
+
+
+def test_cascade_decode_attention_matches_per_sequence_attention():
+    """Groups of 4 sequences share their first pages: the shared-prefix kernel must equal plain paged attention over the full tables."""
+    from types import SimpleNamespace
+
+    from unirl_b200.ops.attention import paged_decode_attention, paged_decode_attention_cascade
+
+    torch.manual_seed(0)
+    b, rows, hq, hkv, d, page = 16, 4, 32, 8, 128, 64
+    pre_pages = [3, 0, 9, 5]  # shared whole pages per group (one group has none)
+    suf_len = torch.randint(1, 700, (b,))
+    suf_pages = [(int(n) + page - 1) // page for n in suf_len]
+    n_pages = sum(pre_pages) + sum(suf_pages) + 2
+    kc = torch.randn(n_pages, hkv, page, d, device="cuda").bfloat16()
+    vc = torch.randn_like(kc)
+    perm = torch.randperm(n_pages).tolist()
+    pre_t = torch.zeros(b // rows, max(pre_pages), dtype=torch.int32)
+    suf_t = torch.zeros(b, max(suf_pages), dtype=torch.int32)
+    full_t = torch.zeros(b, max(pre_pages) + max(suf_pages), dtype=torch.int32)
+    for g, n in enumerate(pre_pages):
+        pre_t[g, :n] = torch.tensor([perm.pop() for _ in range(n)], dtype=torch.int32)
+    for i in range(b):
+        own = torch.tensor([perm.pop() for _ in range(suf_pages[i])], dtype=torch.int32)
+        suf_t[i, : suf_pages[i]] = own
+        n = pre_pages[i // rows]
+        full_t[i, :n] = pre_t[i // rows, :n]
+        full_t[i, n : n + suf_pages[i]] = own
+    pre_len = torch.tensor([n * page for n in pre_pages], dtype=torch.int32)
+    full_len = (pre_len.repeat_interleave(rows) + suf_len).to(torch.int32)
+    q = torch.randn(b, hq, d, device="cuda").bfloat16()
+    want = paged_decode_attention(q, kc, vc, full_t.cuda(), full_len.cuda(), None, None, int(full_len.max()))
+    cas = SimpleNamespace(prefix_tables=pre_t.cuda(), prefix_lens=pre_len.cuda(), suffix_tables=suf_t.cuda(), suffix_lens=suf_len.to(torch.int32).cuda(), rows=rows)
+    got = paged_decode_attention_cascade(q, kc, vc, cas, None, None, int(full_len.max()))
+    _close(got, want, 2e-2, 2e-2, "cascade decode attention")
+
+
+def test_generator_with_shared_prefix_matches_unshared_generation():
+    """Same seeds, same prompts (4 samples each): sharing the prompt pages must not change a single sampled token."""
+    from unirl_b200.models.qwen3.modeling import Qwen3Config, Qwen3Transformer
+    from unirl_b200.rollout.engine.native_ar.generator import ARGenerator
+
+    cfg = Qwen3Config.tiny(num_hidden_layers=2, hidden_size=512, intermediate_size=1024, num_attention_heads=8, num_key_value_heads=2, head_dim=128, vocab_size=4096)
+    model = Qwen3Transformer(cfg, dtype=torch.bfloat16, device="cuda").init_weights(0).eval().requires_grad_(False)
+    g = torch.Generator().manual_seed(0)
+    base = [torch.randint(16, 4096, (int(n),), generator=g) for n in (150, 64, 201)]
+    prompts = [p for p in base for _ in range(4)]
+    outs = []
+    for share in (False, True):
+        gen = ARGenerator(model, page_size=64, use_cuda_graph=True, seed=5, share_prefix=share)
+        o = gen.generate(prompts, max_new_tokens=24, temperature=1.0, stop_token_ids=[2], seed=11)
+        outs.append(o)
+        gen.release_cache()
+    same = sum(int(torch.equal(a, b)) for a, b in zip(outs[0].tokens, outs[1].tokens))
+    assert same >= len(prompts) - 1, f"only {same} of {len(prompts)} sequences identical"  # a bf16 tie may flip one sample
+    for a, b in zip(outs[0].log_probs, outs[1].log_probs):
+        n = min(a.numel(), b.numel(), 4)
+        assert float((a[:n] - b[:n]).abs().max()) < 0.05

@@ -77,14 +77,33 @@ template <int D, bool kFast>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_tables,
                     const int* __restrict__ seq_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, int Hq, int Hkv, int page_size,
-                    int max_pages, int num_splits, float scale_log2, int* __restrict__ status, bf16* __restrict__ out_direct) {
+                    int max_pages, int num_splits, float scale_log2, int* __restrict__ status, bf16* __restrict__ out_direct, int n_shared = 0,
+                    int shared_rows = 1, const int* __restrict__ tables_b = nullptr, const int* __restrict__ lens_b = nullptr, int max_pages_b = 0) {
+  // Cascade launch (n_shared > 0): the first n_shared z-slices are SHARED-PREFIX jobs — `shared_rows` consecutive sequences have the same
+  // leading pages (block_tables / seq_lens describe that prefix once per group) and their query heads are stacked into one 16-row tile,
+  // so the prefix K/V is read once per group; the remaining z-slices are the per-sequence SUFFIX jobs (tables_b / lens_b).  Both kinds
+  // write (o, max, sum) partials; decode_cascade_merge_kernel combines them.
   extern __shared__ __align__(128) uint8_t dec_smem[];
   using L = DecLayout<D>;
   constexpr int kND = D / 8;   // n-tiles of the output
   constexpr int kKK = D / 16;  // k-steps of Q.K^T
-  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int split = blockIdx.x, h = blockIdx.y;
+  int b = blockIdx.z, R = 1;
+  int64_t ws_row0 = 0;
+  const int Gs = Hq / Hkv;
+  if (n_shared > 0) {
+    if (b < n_shared) {
+      R = shared_rows;
+    } else {
+      b -= n_shared;
+      block_tables = tables_b;
+      seq_lens = lens_b;
+      max_pages = max_pages_b;
+      ws_row0 = (int64_t)n_shared * Hkv * Gs * shared_rows;
+    }
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int G = Hq / Hkv;
+  const int G = Gs * R;
   const int seq_len = seq_lens[b];
   const int* bt_row = block_tables + (int64_t)b * max_pages;
   const int tiles_total = (seq_len + kDecTile - 1) / kDecTile;
@@ -98,13 +117,19 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
   uint32_t qa[kKK][4];
   {
     const int r0 = lane >> 2, c0 = (lane & 3) * 2;
-    const bf16* qb = q + ((int64_t)b * Hq + (int64_t)h * G) * D;
+    // tile row r = (sequence r / Gs of this job, query head r % Gs of kv head h)
+    const bf16* qrow[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = r0 + e * 8;
+      qrow[e] = (row < G) ? q + (((int64_t)b * R + row / Gs) * Hq + (int64_t)h * Gs + row % Gs) * D : nullptr;
+    }
 #pragma unroll
     for (int kk = 0; kk < kKK; ++kk) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int row = r0 + (j & 1) * 8, col = kk * 16 + c0 + (j >> 1) * 8;
-        qa[kk][j] = (row < G) ? *reinterpret_cast<const uint32_t*>(qb + (int64_t)row * D + col) : 0u;
+        const int col = kk * 16 + c0 + (j >> 1) * 8;
+        qa[kk][j] = qrow[j & 1] ? *reinterpret_cast<const uint32_t*>(qrow[j & 1] + col) : 0u;
       }
     }
   }
@@ -245,7 +270,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
       Lsum += sm_ml[(w * 16 + g) * 2 + 1] * wgt;
       acc += sm_o[((size_t)w * 16 + g) * D + d] * wgt;
     }
-    const int64_t o_idx = ((int64_t)b * Hq + (int64_t)h * G + g) * num_splits + split;
+    const int64_t o_idx = (ws_row0 + ((int64_t)b * Hkv + h) * G + g) * num_splits + split;
     if (out_direct) {  // a single split owns the whole sequence: normalise and emit bf16 here, no merge pass
       out_direct[o_idx * D + d] = __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
       continue;
@@ -272,6 +297,66 @@ __global__ void decode_merge_kernel(const float* __restrict__ ws_o, const float*
     acc += ws_o[(bh * num_splits + s) * D + d] * w;
   }
   out[bh * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+// out[b, hq] from the suffix partials of sequence b and the shared-prefix partials of its group (see paged_decode_kernel).
+template <int D>
+__global__ void decode_cascade_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, bf16* __restrict__ out, int num_splits, int Hq,
+                                            int Hkv, int n_shared, int R) {
+  const int b = blockIdx.x / Hq, hq = blockIdx.x % Hq, d = threadIdx.x;
+  const int Gs = Hq / Hkv, kvh = hq / Gs, g = hq % Gs;
+  const int64_t rows[2] = {((int64_t)(b / R) * Hkv + kvh) * (Gs * R) + (b % R) * Gs + g,                       // prefix job row
+                           (int64_t)n_shared * Hkv * Gs * R + ((int64_t)b * Hkv + kvh) * Gs + g};                // suffix job row
+  float M = -INFINITY;
+  for (int k = 0; k < 2; ++k)
+    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, ws_ml[(rows[k] * num_splits + s) * 2]);
+  float L = 0.f, acc = 0.f;
+  for (int k = 0; k < 2; ++k) {
+    for (int s = 0; s < num_splits; ++s) {
+      const int64_t i = rows[k] * num_splits + s;
+      const float m = ws_ml[i * 2];
+      const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+      L += ws_ml[i * 2 + 1] * w;
+      acc += ws_o[i * D + d] * w;
+    }
+  }
+  out[(int64_t)blockIdx.x * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+int64_t decode_cascade_workspace_floats(int B, int Hq, int D, int num_splits) { return 2 * (int64_t)B * Hq * num_splits * (D + 2); }
+
+// Shared-prefix ("cascade") decode attention.  Groups of R consecutive sequences share their first pages: prefix_tables / prefix_lens
+// [B / R] describe the shared part, suffix_tables / suffix_lens [B] the rest.  R * (Hq / Hkv) must not exceed 16.
+int paged_decode_attention_cascade(const void* q, const void* kc, const void* vc, const int* prefix_tables, const int* prefix_lens, int max_pages_p,
+                                   const int* suffix_tables, const int* suffix_lens, int max_pages_s, void* out, float* workspace, int B, int R, int Hq,
+                                   int Hkv, int D, int page_size, int num_splits, float scale, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (Hq % Hkv || R < 1 || B % R || (Hq / Hkv) * R > 16 || (D != 64 && D != 128)) return 1;
+  const int n_shared = B / R;
+  const int64_t rows = 2 * (int64_t)B * Hq;  // prefix rows (n_shared * Hkv * Gs * R = B * Hq) + suffix rows
+  float* ws_o = workspace;
+  float* ws_ml = workspace + rows * num_splits * D;
+  const dim3 grid(num_splits, Hkv, n_shared + B);
+  const size_t smem = D == 128 ? (size_t)DecLayout<128>::kTotal : (size_t)DecLayout<64>::kTotal;
+  const size_t merge_smem = (size_t)kDecWarps * 16 * (D + 2) * sizeof(float);
+  const size_t need = smem > merge_smem ? smem : merge_smem;
+  const bool fast = page_size % kDecTile == 0;
+  const float sl2 = scale * kLog2e;
+#define UB_CAS(DD, FF)                                                                                                                     \
+  do {                                                                                                                                     \
+    if (cudaFuncSetAttribute(paged_decode_kernel<DD, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2; \
+    paged_decode_kernel<DD, FF><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, prefix_tables, prefix_lens, ws_o, \
+                                                                  ws_ml, Hq, Hkv, page_size, max_pages_p, num_splits, sl2, nullptr, nullptr, n_shared, R, \
+                                                                  suffix_tables, suffix_lens, max_pages_s);                                \
+    decode_cascade_merge_kernel<DD><<<B * Hq, DD, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits, Hq, Hkv, n_shared, R);                    \
+  } while (0)
+  if (D == 128) {
+    if (fast) UB_CAS(128, true); else UB_CAS(128, false);
+  } else {
+    if (fast) UB_CAS(64, true); else UB_CAS(64, false);
+  }
+#undef UB_CAS
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
 int decode_num_splits(int B, int Hkv, int max_kv_len) {

@@ -410,6 +410,34 @@ void peer_barrier(PyPeerComm& pc) {
   TORCH_CHECK(rc == 0, "peer_barrier: launch failure (code ", rc, ")");
 }
 
+// Shared-prefix decode attention: groups of `rows` consecutive sequences share the pages listed in prefix_tables.
+Tensor paged_decode_attention_cascade(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& prefix_tables, const Tensor& prefix_lens,
+                                      const Tensor& suffix_tables, const Tensor& suffix_lens, int64_t rows, double scale, c10::optional<Tensor> workspace,
+                                      int64_t max_kv_len) {
+  chk(q, "q"); chk(kc, "k_cache"); chk(vc, "v_cache"); chk(prefix_tables, "prefix_tables"); chk(prefix_lens, "prefix_lens"); chk(suffix_tables, "suffix_tables");
+  chk(suffix_lens, "suffix_lens");
+  TORCH_CHECK(q.dim() == 3 && kc.dim() == 4 && q.scalar_type() == at::kBFloat16 && kc.scalar_type() == at::kBFloat16, "cascade attention: bf16 q [B,Hq,D], cache [P,Hkv,page,D]");
+  TORCH_CHECK(prefix_tables.scalar_type() == at::kInt && prefix_lens.scalar_type() == at::kInt && suffix_tables.scalar_type() == at::kInt && suffix_lens.scalar_type() == at::kInt,
+              "cascade attention: int32 tables / lengths");
+  const int B = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)kc.size(1), page = (int)kc.size(2);
+  TORCH_CHECK(rows >= 1 && B % rows == 0 && prefix_tables.size(0) == B / rows && prefix_lens.numel() == B / rows && suffix_tables.size(0) == B && suffix_lens.numel() == B,
+              "cascade attention: B / rows prefix entries and B suffix entries expected");
+  c10::cuda::CUDAGuard g(q.device());
+  const int kv_hint = max_kv_len > 0 ? (int)max_kv_len : (int)(suffix_tables.size(1) * page);
+  const int splits = ub::decode_num_splits(B + B / (int)rows, Hkv, kv_hint);
+  const int64_t need = ub::decode_cascade_workspace_floats(B, Hq, D, splits);
+  Tensor ws = workspace.has_value() && workspace->defined() && workspace->numel() >= need ? *workspace : torch::empty({need}, q.options().dtype(torch::kFloat));
+  auto out = torch::empty_like(q);
+  const int rc = ub::paged_decode_attention_cascade(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), prefix_tables.data_ptr<int>(), prefix_lens.data_ptr<int>(),
+                                                    (int)prefix_tables.size(1), suffix_tables.data_ptr<int>(), suffix_lens.data_ptr<int>(), (int)suffix_tables.size(1),
+                                                    out.data_ptr(), ws.data_ptr<float>(), B, (int)rows, Hq, Hkv, D, page, splits, (float)scale, stream());
+  TORCH_CHECK(rc == 0, "paged_decode_attention_cascade: unsupported configuration or launch failure (code ", rc, ")");
+  return out;
+}
+int64_t decode_cascade_workspace_size(int64_t B, int64_t rows, int64_t Hq, int64_t Hkv, int64_t D, int64_t max_kv_len) {
+  return ub::decode_cascade_workspace_floats((int)B, (int)Hq, (int)D, ub::decode_num_splits((int)(B + B / rows), (int)Hkv, (int)max_kv_len));
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -440,6 +468,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("linear_sample", &linear_sample);
   m.def("decode_workspace_size", &decode_workspace_size);
   m.def("paged_decode_attention", &paged_decode_attention);
+  m.def("paged_decode_attention_cascade", &paged_decode_attention_cascade);
+  m.def("decode_cascade_workspace_size", &decode_cascade_workspace_size);
   py::class_<PyPeerComm>(m, "PeerComm")
       .def(py::init<std::vector<int64_t>, std::vector<int64_t>, int, Tensor, double>(), py::arg("bufs"), py::arg("flags"), py::arg("rank"), py::arg("state"),
            py::arg("wait_s") = 20.0)

@@ -60,6 +60,10 @@ int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int l
 // ---- attention_decode.cu -----------------------------------------------------------------------------------
 int decode_num_splits(int B, int Hkv, int max_kv_len);
 int64_t decode_workspace_floats(int B, int Hq, int D, int num_splits);
+int64_t decode_cascade_workspace_floats(int B, int Hq, int D, int num_splits);
+int paged_decode_attention_cascade(const void* q, const void* kc, const void* vc, const int* prefix_tables, const int* prefix_lens, int max_pages_p,
+                                   const int* suffix_tables, const int* suffix_lens, int max_pages_s, void* out, float* workspace, int B, int R, int Hq,
+                                   int Hkv, int D, int page_size, int num_splits, float scale, cudaStream_t s);
 int paged_decode_attention(const void* q, const void* kc, const void* vc, const int* block_tables, const int* seq_lens, void* out, float* workspace,
                            int B, int Hq, int Hkv, int D, int page_size, int max_pages, int num_splits, float scale, int* status, cudaStream_t s);
 

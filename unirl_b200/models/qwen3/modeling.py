@@ -108,6 +108,7 @@ class AttnMeta:
     slot_mapping: Optional[torch.Tensor] = None  # [T] int64
     workspace: Optional[torch.Tensor] = None
     max_kv_len: int = 0
+    cascade: Optional[Any] = None  # shared-prefix decode: prefix_tables / prefix_lens / suffix_tables / suffix_lens / rows
     seq_lens_host: Optional[List[int]] = None  # packed sequence lengths as host ints (saves a device read in attention dispatch)
     input_embeds: Optional[torch.Tensor] = None  # [T, H]: replaces the token-embedding lookup (multimodal prompts)
 
@@ -175,6 +176,9 @@ class Qwen3DecoderLayer(nn.Module):
 
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         """The KV cache (decode / prefill) has already been written by :meth:`_qkv_rope`."""
+        if meta.mode == "decode" and meta.cascade is not None:
+            return A.paged_decode_attention_cascade(q, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.cascade, self.scale,
+                                                    meta.workspace, meta.max_kv_len)
         if meta.mode == "decode":
             return A.paged_decode_attention(q, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.block_tables,
                                             meta.seq_lens, self.scale, meta.workspace, meta.max_kv_len)

@@ -179,6 +179,19 @@ def paged_decode_attention(q, k_cache, v_cache, block_tables, seq_lens, scale: O
     return paged_decode_attention_reference(q, k_cache, v_cache, block_tables, seq_lens, scale)
 
 
+def paged_decode_attention_cascade(q, k_cache, v_cache, cascade, scale: Optional[float] = None, workspace: Optional[torch.Tensor] = None,
+                                   max_seq_len: Optional[int] = None) -> torch.Tensor:
+    """Decode attention for batches in which groups of ``cascade.rows`` consecutive sequences share their leading KV pages (samples of one
+    prompt): the shared prefix is read ONCE per group with the group's query heads stacked into one tile, every sequence's own suffix is
+    read separately, and the two partial results are merged by their log-sum-exp.  ``cascade`` carries ``prefix_tables [B/R, Pp]``,
+    ``prefix_lens [B/R]``, ``suffix_tables [B, Ps]``, ``suffix_lens [B]`` (int32) and ``rows``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    out = require_ext().paged_decode_attention_cascade(q.contiguous(), k_cache, v_cache, cascade.prefix_tables, cascade.prefix_lens, cascade.suffix_tables,
+                                                       cascade.suffix_lens, int(cascade.rows), float(scale), workspace, int(max_seq_len or 0))
+    count_launch(2)
+    return out
+
+
 # --------------------------------------------------------------------------------------- dense (DiT)
 def dense_attention(q, k, v, scale: Optional[float] = None) -> torch.Tensor:
     """Bidirectional attention over ``[B, L, H, D]`` (joint text+image streams of MMDiT / video DiT).
@@ -196,5 +209,5 @@ def dense_attention(q, k, v, scale: Optional[float] = None) -> torch.Tensor:
     return o.transpose(1, 2)
 
 
-__all__ = ["varlen_attention", "varlen_attention_reference", "kv_cache_write", "paged_decode_attention",
+__all__ = ["paged_decode_attention_cascade", "varlen_attention", "varlen_attention_reference", "kv_cache_write", "paged_decode_attention",
            "paged_decode_attention_reference", "dense_attention"]

@@ -37,6 +37,7 @@ class NativeAREngineConfig:
     concurrency: int = 16  # accepted for recipe compatibility (no HTTP fan-out here)
     detokenize: bool = True
     tp_collectives: str = "fused"  # fused | nccl
+    share_prefix: bool = True  # samples of one prompt share the prompt's KV pages; decode reads them once per group (cascade attention)
 
     @property
     def use_cuda_graph(self) -> bool:

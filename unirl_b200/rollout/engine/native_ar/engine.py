@@ -88,7 +88,8 @@ class NativeARRolloutEngine(BaseRolloutEngine):
             self.tokenizer = b.tokenizer if b is not None else load_tokenizer(cfg.tokenizer_ckpt_path, mcfg.vocab_size)
         self.generator = ARGenerator(self.model, page_size=cfg.page_size, max_running=cfg.max_running_requests,
                                      prefill_token_budget=cfg.prefill_token_budget, kv_cache_tokens=cfg.kv_cache_tokens,
-                                     use_cuda_graph=cfg.use_cuda_graph, poll_interval=cfg.poll_interval, seed=cfg.seed)
+                                     use_cuda_graph=cfg.use_cuda_graph, poll_interval=cfg.poll_interval, seed=cfg.seed,
+                                     share_prefix=bool(getattr(cfg, "share_prefix", True)))
 
     def _make_all_reduce(self):
         comm = self.tp_comm

@@ -39,8 +39,9 @@ class GenerationOutput:
 class ARGenerator:
     def __init__(self, model: Any, *, page_size: int = 64, max_running: int = 256, prefill_token_budget: int = 16384,
                  kv_cache_tokens: Optional[int] = None, use_cuda_graph: bool = True, poll_interval: int = 64, seed: int = 0,
-                 cache_dtype: Optional[torch.dtype] = None):
+                 cache_dtype: Optional[torch.dtype] = None, share_prefix: bool = True):
         self.model = model
+        self.share_prefix = bool(share_prefix)  # samples of one prompt share its KV pages and read them once per decode step
         self.cfg = model.cfg
         self.page_size, self.max_running = int(page_size), int(max_running)
         self.prefill_token_budget = int(prefill_token_budget)
@@ -106,27 +107,54 @@ class ARGenerator:
         dev, ps, b = self.device, self.page_size, len(prompts)
         rope_offset = torch.zeros(b, dtype=torch.long, device=dev)
         plens = [int(p.numel()) for p in prompts]
-        pages_per = [math.ceil((pl + max_new) / ps) for pl in plens]
-        cache = self.ensure_cache(sum(pp * ps for pp in pages_per))
+        rows = self._shared_rows(prompts) if (extras is None and dev.type == "cuda" and self.share_prefix) else 1
+        shared_pages = [(pl // ps if rows > 1 else 0) for pl in plens]  # whole pages of the prompt, shared inside a chunk of `rows` samples
+        own_pages = [math.ceil((pl - sp * ps + max_new) / ps) for pl, sp in zip(plens, shared_pages)]
+        total_pages = sum(own_pages) + sum(shared_pages[i] for i in range(0, b, rows))
+        cache = self.ensure_cache(total_pages * ps)
         cache.allocator.reset()
-        max_pages = max(pages_per)
+        max_pages = max(s_ + o for s_, o in zip(shared_pages, own_pages))
         bt = torch.zeros(b, max_pages, dtype=torch.int32)
-        for i, pp in enumerate(pages_per):
-            bt[i, :pp] = torch.tensor(cache.allocator.allocate(pp), dtype=torch.int32)
+        pre_t = torch.zeros(max(1, b // rows), max(1, max(shared_pages)), dtype=torch.int32)
+        suf_t = torch.zeros(b, max(own_pages), dtype=torch.int32)
+        for i in range(b):
+            if i % rows == 0:
+                lead = torch.tensor(cache.allocator.allocate(shared_pages[i]), dtype=torch.int32) if shared_pages[i] else torch.zeros(0, dtype=torch.int32)
+                pre_t[i // rows, : shared_pages[i]] = lead
+            own = torch.tensor(cache.allocator.allocate(own_pages[i]), dtype=torch.int32)
+            bt[i, : shared_pages[i]] = lead
+            bt[i, shared_pages[i] : shared_pages[i] + own_pages[i]] = own
+            suf_t[i, : own_pages[i]] = own
         block_tables = bt.to(dev)
         stop = torch.tensor(list(stop_ids) if stop_ids else [self.cfg.eos_token_id], dtype=torch.long, device=dev)
 
         # -- prefill (packed, chunked by token budget) --------------------------------------------------
         last_hidden = torch.empty(b, self.cfg.hidden_size, dtype=self.model.embed_tokens.dtype, device=dev)
+        leaders = list(range(0, b, rows))  # with shared prefixes only the first sample of a chunk runs the prompt
         i = 0
-        while i < b:
+        while i < len(leaders):
             j, tot = i, 0
-            while j < b and (j == i or tot + plens[j] <= self.prefill_token_budget):
-                tot += plens[j]
+            while j < len(leaders) and (j == i or tot + plens[leaders[j]] <= self.prefill_token_budget):
+                tot += plens[leaders[j]]
                 j += 1
-            self._prefill([prompts[k] for k in range(i, j)], plens[i:j], block_tables[i:j], cache, last_hidden[i:j],
-                          None if extras is None else extras[i:j], rope_offset[i:j])
+            idx = leaders[i:j]
+            sel = torch.tensor(idx, device=dev)
+            out = torch.empty(len(idx), self.cfg.hidden_size, dtype=last_hidden.dtype, device=dev)
+            self._prefill([prompts[k] for k in idx], [plens[k] for k in idx], block_tables[sel], cache, out,
+                          None if extras is None else [extras[k] for k in idx], rope_offset[sel] if rows == 1 else None)
+            last_hidden[sel] = out
             i = j
+        if rows > 1:
+            # followers: same last hidden state; the prompt's tail (the tokens past its last whole page) lives in the leader's first own page
+            lead_of = torch.arange(b, device=dev) // rows * rows
+            last_hidden.copy_(last_hidden[lead_of])
+            follow = [k for k in range(b) if k % rows and plens[k] % ps]
+            if follow:
+                src = torch.tensor([int(suf_t[k // rows * rows, 0]) for k in follow], device=dev)
+                dst = torch.tensor([int(suf_t[k, 0]) for k in follow], device=dev)
+                for layer_k, layer_v in zip(cache.k, cache.v):
+                    layer_k[dst] = layer_k[src]
+                    layer_v[dst] = layer_v[src]
 
         # -- decode state (all device resident) ---------------------------------------------------------
         st = _DecodeState(b, max_new, dev)
@@ -140,9 +168,18 @@ class ARGenerator:
             from unirl_b200.ops._ext import ext
 
             C = ext()
-            if C is not None and hasattr(C, "decode_workspace_size"):
-                meta.workspace = torch.empty(C.decode_workspace_size(b, self.model.layers[0].n_q, self.cfg.head_dim, meta.max_kv_len),
+            layer0 = self.model.layers[0]
+            if rows > 1 and C is not None:
+                from types import SimpleNamespace
+
+                st.prefix_len = torch.tensor([shared_pages[k] * ps for k in range(b)], dtype=torch.int32, device=dev)
+                st.suffix_lens = torch.zeros(b, dtype=torch.int32, device=dev)
+                meta.cascade = SimpleNamespace(prefix_tables=pre_t.to(dev), prefix_lens=st.prefix_len[::rows].contiguous(), suffix_tables=suf_t.to(dev),
+                                               suffix_lens=st.suffix_lens, rows=rows)
+                meta.workspace = torch.empty(C.decode_cascade_workspace_size(b, rows, layer0.n_q, layer0.n_kv, self.cfg.head_dim, meta.max_kv_len),
                                              dtype=torch.float32, device=dev)
+            elif C is not None and hasattr(C, "decode_workspace_size"):
+                meta.workspace = torch.empty(C.decode_workspace_size(b, layer0.n_q, self.cfg.head_dim, meta.max_kv_len), dtype=torch.float32, device=dev)
 
         def step() -> None:
             st.prepare(block_tables, ps)
@@ -168,6 +205,18 @@ class ARGenerator:
         toks = [out_t[k, : int(lens[k])].clone() for k in range(b)]
         lps = [out_l[k, : int(lens[k])].clone() for k in range(b)]
         return toks, lps, st.finished.cpu(), n_steps
+
+    def _shared_rows(self, prompts: List[torch.Tensor]) -> int:
+        """How many consecutive sequences can share a prefix job: the largest R in {4, 2} such that the batch is made of chunks of R
+        identical prompts and R query-head groups fit the 16-row attention tile; 1 when nothing repeats."""
+        b = len(prompts)
+        gs = self.model.layers[0].n_q // self.model.layers[0].n_kv
+        for r in (4, 2):
+            if r * gs > 16 or b % r:
+                continue
+            if all(prompts[i].numel() == prompts[i - i % r].numel() and bool(torch.equal(prompts[i], prompts[i - i % r])) for i in range(b) if i % r):
+                return r
+        return 1
 
     def _prefill(self, prompts: List[torch.Tensor], plens: List[int], block_tables: torch.Tensor, cache: PagedKVCache, out_last: torch.Tensor,
                  extras: Optional[List[Any]] = None, rope_offset_out: Optional[torch.Tensor] = None) -> None:
@@ -220,6 +269,8 @@ class _DecodeState:
         z = lambda dt, *shape: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
         self.out_tokens, self.out_logp = z(torch.long, b, max_new), z(torch.float32, b, max_new)
         self.cur_tokens, self.positions, self.slots = z(torch.long, b), z(torch.long, b), z(torch.long, b)
+        self.prefix_len: Optional[torch.Tensor] = None  # shared-prefix decode: tokens of each sequence that live in shared pages
+        self.suffix_lens: Optional[torch.Tensor] = None
         self.rope_offset, self.rope_pos = z(torch.long, b), z(torch.long, b)  # rotary position = cache index + per-sequence offset
         self.seq_lens = z(torch.int32, b)
         self.lengths = z(torch.long, b)
@@ -247,6 +298,8 @@ class _DecodeState:
         self.slots.copy_(page * page_size + self.positions % page_size)
         self.seq_lens.copy_((self.positions + 1).to(torch.int32))
         self.rope_pos.copy_(self.positions + self.rope_offset)
+        if self.suffix_lens is not None:
+            self.suffix_lens.copy_(self.seq_lens - self.prefix_len)
 
 
 __all__ = ["ARGenerator", "GenerationOutput"]
