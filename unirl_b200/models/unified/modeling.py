@@ -100,11 +100,39 @@ class MoEFFN(nn.Module):
         self.router = _p(c.num_experts, c.hidden_size, dtype=dtype, device=device)
         self.experts = nn.ModuleList(_FFN(c.hidden_size, c.intermediate_size, dtype, device) for _ in range(c.num_experts))
         self.shared = _FFN(c.hidden_size, c.intermediate_size, dtype, device) if c.shared_expert else None
+        self.ep: Optional[Any] = None  # ExpertParallelContext once the experts are sharded over a group
+        self.expert_ids: List[int] = list(range(c.num_experts))
+
+    def shard_experts(self, ep: Any) -> None:
+        """Keep only this rank's experts (``E / P`` consecutive ones); from now on forward dispatches over the expert group."""
+        from unirl_b200.parallel.expert_parallel import mark_expert_local
+
+        ids = ep.local_experts(self.c.num_experts)
+        self.experts = nn.ModuleList(self.experts[i] for i in ids)
+        self.expert_ids, self.ep = ids, ep
+        mark_expert_local(self.experts)
+
+    def _forward_ep(self, x: torch.Tensor) -> torch.Tensor:
+        c, ep = self.c, self.ep
+        xa = ep.gather_tokens(x)  # every rank's tokens, rank-major
+        probs = F.softmax(linear(xa, self.router).float(), -1)
+        w, idx = probs.topk(c.experts_per_token, -1)
+        w = (w / w.sum(-1, keepdim=True)).to(x.dtype)
+        out = torch.zeros_like(xa)
+        for slot, e in enumerate(self.expert_ids):
+            hit = (idx == e)
+            rows = hit.any(-1).nonzero().flatten()
+            if rows.numel():
+                out.index_add_(0, rows, self.experts[slot](xa[rows]) * (w * hit.to(w.dtype))[rows].sum(-1, keepdim=True))
+        y = ep.combine(out)
+        return y + self.shared(x) if self.shared is not None else y
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         c = self.c
         shape = x.shape
         x = x.reshape(-1, shape[-1])
+        if self.ep is not None and self.ep.size > 1:
+            return self._forward_ep(x).view(shape)
         probs = F.softmax(linear(x, self.router).float(), -1)
         w, idx = probs.topk(c.experts_per_token, -1)
         w = (w / w.sum(-1, keepdim=True)).to(x.dtype)

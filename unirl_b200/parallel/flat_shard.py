@@ -132,6 +132,7 @@ class FlatGroup:
         self._pending = 0
         self._hooks: List[Any] = []
         self.trainable = any(s.param.requires_grad for s in self.slots)
+        self.expert_local = False  # parameters owned by this expert-parallel rank: never reduced, sharded or published
         self.module: Optional[nn.Module] = None  # the block whose forward / backward brackets the gather (ZeRO-3)
         self.shard_resident: Optional[torch.Tensor] = None  # ZeRO-3: this rank's bf16 shard while the replica storage is released
         self._gathered = True
@@ -232,17 +233,34 @@ class FlatShardedModel:
                 raise ValueError("root_wrap=False leaves trainable parameters outside every sharded group: "
                                  + ", ".join(n for n, p in rest if p.requires_grad)[:200])
             layout.insert(0, ("<root>", rest))
-        sizes = [FlatGroup.padded_numel(named, self.world) for _, named in layout]
+        # parameters owned by one expert-parallel rank (not replicated) get groups of their own: no reduction, no sharding, local update
+        split: List[Tuple[str, List[Tuple[str, nn.Parameter]]]] = []
+        self._ep_group_names: set = set()
+        for name, named in layout:
+            rep = [(n, p) for n, p in named if not getattr(p, "_ep_local", False)]
+            loc = [(n, p) for n, p in named if getattr(p, "_ep_local", False)]
+            if rep:
+                split.append((name, rep))
+            if loc:
+                split.append((name + "#experts", loc))
+                self._ep_group_names.add(name + "#experts")
+        layout = split
+        sizes = [FlatGroup.padded_numel(named, 1 if name in self._ep_group_names else self.world) for name, named in layout]
         low_bytes = torch.empty((), dtype=low).element_size()
         self.shard_comm.reserve(sum(s * low_bytes + 256 for s in sizes),
                                 sum(s * 4 + 256 for s, (_, named) in zip(sizes, layout) if any(p.requires_grad for _, p in named)), self.device)
         modules = dict(self.module.named_modules())
         for name, named in layout:
+            if name in self._ep_group_names:
+                g = FlatGroup(name, named, 0, 1, self.device, low, master, alloc=None)
+                g.expert_local = True
+                self.groups.append(g)
+                continue
             self.groups.append(FlatGroup(name, named, self.rank, self.world, self.device, low, master, alloc=self.shard_comm))
             self.groups[-1].module = modules.get(name)
         if self.world > 1 and self.shard_comm.persistent_grads:
             for g in self.groups:  # symmetric layout: every rank allocates in the same order
-                if g.trainable:
+                if g.trainable and not g.expert_local:
                     g._persist_grad = self.shard_comm.alloc_grad(g.padded, self.device)
 
     def _install_hooks(self) -> None:
@@ -314,6 +332,10 @@ class FlatShardedModel:
                 g._reduced = False
 
     def _launch_reduce(self, g: FlatGroup) -> None:
+        if g.expert_local:  # the gradient already sums over every rank's tokens: match the rank-averaged objective
+            g.main_grad.div_(float(self.world))
+            g._reduced = True
+            return
         if self._comm_stream is not None:
             self._comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self._comm_stream):
@@ -345,6 +367,9 @@ class FlatShardedModel:
         fused = self.shard_comm.local_sumsq() if self.world > 1 else None
         if fused is not None:
             total = fused.clone().reshape(1)
+            for g in self.groups:
+                if g.expert_local and g.trainable and g.grad_shard is not None:
+                    total = total + O.sum_squares(g.grad_shard).reshape(1)
         else:
             parts = [O.sum_squares(g.grad_shard) for g in self.groups if g.trainable and g.grad_shard is not None]
             total = torch.stack(parts).sum() if parts else torch.zeros((), device=self.device)
@@ -359,6 +384,10 @@ class FlatShardedModel:
                 continue
             if self.grad_replicas > 1:
                 g.grad_shard.mul_(float(self.grad_replicas))
+            if g.expert_local:
+                O.adamw_step(g.master, g.grad_shard, g.exp_avg, g.exp_avg_sq, lr=lr, beta1=betas[0], beta2=betas[1], eps=eps, weight_decay=weight_decay,
+                             step=step, low=g.param_shard, ema=g.ema if ema_decay is not None else None, ema_decay=ema_decay or 0.0, grad_scale_tensor=clip_coef)
+                continue
             if self.world > 1 and self.shard_comm.fused_optimizer:
                 self.shard_comm.adamw_publish(g, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, step=step, clip_coef=clip_coef,
                                               ema=g.ema if ema_decay is not None else None, ema_decay=ema_decay or 0.0)
