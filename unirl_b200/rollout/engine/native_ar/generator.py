@@ -252,14 +252,23 @@ class ARGenerator:
             fused.align()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
+        from unirl_b200.ops._ext import count_launch, launch_count
+
         g = torch.cuda.CUDAGraph()
+        n0 = launch_count()
         # capture itself does not execute the step, so the decode state is not advanced here
         with torch.cuda.graph(g, stream=s):
             step_fn()
             if fused is not None:
                 fused.align()
+        per_replay = launch_count() - n0  # native kernels recorded in the graph: every replay launches them again
         self._graphs[(b, max_new, temperature, top_k, top_p)] = g  # keep alive for the wave
-        return g.replay
+
+        def replay() -> None:
+            g.replay()
+            count_launch(per_replay)
+
+        return replay
 
 
 class _DecodeState:
