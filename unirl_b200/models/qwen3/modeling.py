@@ -30,7 +30,7 @@ import torch.nn as nn
 
 from unirl_b200.ops import attention as A
 from unirl_b200.ops.activation import swiglu
-from unirl_b200.ops.linear import linear
+from unirl_b200.ops.linear import linear, linear_swiglu
 from unirl_b200.ops.norm import add_rmsnorm, rmsnorm
 from unirl_b200.ops.rope import qk_norm_rope
 from unirl_b200.train.inject import lora_apply
@@ -69,6 +69,9 @@ class Qwen3Config:
     def from_hf_dict(cls, d: Dict[str, Any]) -> "Qwen3Config":
         keys = {f for f in cls.__dataclass_fields__}
         kw = {k: v for k, v in d.items() if k in keys and v is not None}
+        rope = d.get("rope_parameters") or d.get("rope_scaling") or {}
+        if "rope_theta" not in kw and isinstance(rope, dict) and rope.get("rope_theta") is not None:
+            kw["rope_theta"] = float(rope["rope_theta"])  # newer config files nest the rotary base
         if "head_dim" not in kw:
             kw["head_dim"] = kw["hidden_size"] // kw["num_attention_heads"]
         if isinstance(kw.get("eos_token_id"), list):
@@ -149,6 +152,12 @@ class Qwen3DecoderLayer(nn.Module):
             return y if residual is None else y + residual
         return linear(x, getattr(self, name), residual=residual)
 
+    def _gate_up_act(self, h: torch.Tensor) -> torch.Tensor:
+        """``silu(h·Wgᵀ) ⊙ (h·Wuᵀ)``; without adapters the activation rides in the GEMM epilogue on decode-sized batches."""
+        if getattr(self, "_lora_index", None):
+            return swiglu(self._proj(h, "gate_up_proj"))
+        return linear_swiglu(h, self.gate_up_proj)
+
     def _qkv_rope(self, h: torch.Tensor, meta: AttnMeta) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Fused QKV projection (+ bias) → per-head RMS q/k norm → rotary.  ``meta.positions`` is ``[T]`` (one rotary axis,
         fused kernel) or ``[3, T]`` (temporal / height / width axes of a vision-language prompt)."""
@@ -196,7 +205,7 @@ class Qwen3DecoderLayer(nn.Module):
         q, k, v = self._qkv_rope(h, meta)
         attn = self.attention(q, k, v, meta).reshape(x.shape[0], self.n_q * c.head_dim)
         h, x = add_rmsnorm(self._proj(attn, "o_proj"), x, self.post_attention_layernorm, c.rms_norm_eps)
-        return self._proj(swiglu(self._proj(h, "gate_up_proj")), "down_proj"), x
+        return self._proj(self._gate_up_act(h), "down_proj"), x
 
     def forward_fused_tp(self, x: torch.Tensor, h: torch.Tensor, meta: AttnMeta, next_norm: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """Inference path under tensor parallelism: every row-parallel projection, its all-reduce, the residual add
@@ -206,8 +215,7 @@ class Qwen3DecoderLayer(nn.Module):
         q, k, v = self._qkv_rope(h, meta)
         attn = self.attention(q, k, v, meta).reshape(x.shape[0], self.n_q * c.head_dim)
         x, h = fused.proj_reduce_norm(attn, self.o_proj, x, self.post_attention_layernorm, c.rms_norm_eps)
-        act = swiglu(self._proj(h, "gate_up_proj"))
-        return fused.proj_reduce_norm(act, self.down_proj, x, next_norm, c.rms_norm_eps)
+        return fused.proj_reduce_norm(self._gate_up_act(h), self.down_proj, x, next_norm, c.rms_norm_eps)
 
     def forward(self, x: torch.Tensor, meta: AttnMeta) -> torch.Tensor:
         c = self.cfg

@@ -2,6 +2,9 @@
 
 from __future__ import annotations
 
+import glob
+import json
+import os
 from typing import Any, Dict
 
 import torch
@@ -27,15 +30,28 @@ class QwenVLBundle(Bundle):
     @classmethod
     def from_config(cls, config: QwenVLPipelineConfig) -> "QwenVLBundle":
         path = config.pretrained_model_ckpt_path
-        if not path.startswith("random:"):
-            raise NotImplementedError("QwenVLBundle loads random-init presets (random:tiny-vl, random:qwen2.5-vl-7b); HF checkpoint import is not wired yet")
-        mcfg = PRESETS[path.split(":", 1)[1].lower()]()
+        random_init = path.startswith("random:")
+        if random_init:
+            mcfg = PRESETS[path.split(":", 1)[1].lower()]()
+        else:
+            with open(os.path.join(path, "config.json")) as f:
+                mcfg = QwenVLConfig.from_hf_dict(json.load(f))
         for k, v in (config.model_overrides or {}).items():
             setattr(mcfg, k, v)
         device = config.device or ("cuda" if torch.cuda.is_available() else "cpu")
         model = QwenVLTransformer(mcfg, dtype=parse_torch_dtype(config.model_precision), device=device,
-                                  gradient_checkpointing=config.use_gradient_checkpointing).init_weights(config.init_seed)
-        return cls(model, load_tokenizer(config.tokenizer_ckpt_path, mcfg.vocab_size, config.trust_remote_code), config)
+                                  gradient_checkpointing=config.use_gradient_checkpointing)
+        if random_init:
+            model.init_weights(config.init_seed)
+        else:
+            from safetensors.torch import load_file
+
+            sd: Dict[str, torch.Tensor] = {}
+            for shard in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
+                sd.update(load_file(shard))
+            model.load_hf_state_dict(sd)
+        tok = load_tokenizer(config.tokenizer_ckpt_path or (None if random_init else path), mcfg.vocab_size, config.trust_remote_code)
+        return cls(model, tok, config)
 
     def trainable_modules(self) -> Dict[str, torch.nn.Module]:
         return {"transformer": self.transformer}

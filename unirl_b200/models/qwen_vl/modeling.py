@@ -2,8 +2,10 @@
 3-axis ("multimodal") rotary positions.
 
 Vision tower: flattened ``temporal_patch x patch x patch`` pixel patches → linear patch embedding → ``depth`` pre-norm
-blocks (RMSNorm, 2-D rotary attention restricted to each image via packed sequence boundaries, SwiGLU MLP) → 2x2 spatial
-merger MLP into the decoder width.  Decoder: the Qwen3 decoder class with QKV bias and without QK-norm.
+blocks (RMSNorm, 2-D rotary attention, SwiGLU MLP) → 2x2 spatial merger MLP into the decoder width.  Patches are reordered
+so that each attention window is contiguous: the blocks listed in ``fullatt_block_indexes`` attend over a whole frame, the
+others only inside their window (both are packed-sequence boundaries of one varlen attention call); the merger output is put
+back into raster order.  Decoder: the Qwen3 decoder class with QKV bias and without QK-norm.
 
 Positions: text tokens advance all three axes together; the ``t·h·w / 4`` placeholder tokens of an image take
 ``(t, row, col)`` offsets from the image's start position; the text after an image continues from the largest position
@@ -38,6 +40,8 @@ class VisionConfig:
     in_channels: int = 3
     out_hidden_size: int = 3584
     eps: float = 1e-6
+    window_size: int = 112  # pixels; blocks outside `fullatt_block_indexes` attend inside windows of this size
+    fullatt_block_indexes: Tuple[int, ...] = (7, 15, 23, 31)
 
     @property
     def patch_dim(self) -> int:
@@ -66,10 +70,38 @@ class QwenVLConfig(Qwen3Config):
         return cls()
 
     @classmethod
+    def from_hf_dict(cls, d: Dict[str, Any]) -> "QwenVLConfig":
+        """``config.json`` of a Qwen2.5-VL checkpoint: decoder fields live at the top level (older files) or under
+        ``text_config``; the vision tower under ``vision_config``; the rotary sections under ``rope_scaling`` / ``rope_parameters``."""
+        text = dict(d.get("text_config") or {})
+        flat = {**{k: v for k, v in d.items() if k not in ("text_config", "vision_config")}, **text}
+        keys = {f for f in cls.__dataclass_fields__} - {"vision", "mrope_section"}
+        kw = {k: v for k, v in flat.items() if k in keys and v is not None}
+        rope = flat.get("rope_parameters") or flat.get("rope_scaling") or {}
+        if "rope_theta" not in kw and rope.get("rope_theta") is not None:
+            kw["rope_theta"] = float(rope["rope_theta"])
+        if rope.get("mrope_section"):
+            kw["mrope_section"] = tuple(int(v) for v in rope["mrope_section"])
+        kw.setdefault("head_dim", kw["hidden_size"] // kw["num_attention_heads"])
+        if isinstance(kw.get("eos_token_id"), list):
+            kw["eos_token_id"] = kw["eos_token_id"][0]
+        kw["qk_norm"], kw["attention_bias"] = False, True
+        v = dict(d.get("vision_config") or {})
+        vkeys = {f for f in VisionConfig.__dataclass_fields__}
+        vkw = {k: val for k, val in v.items() if k in vkeys and val is not None}
+        if "fullatt_block_indexes" in vkw:
+            vkw["fullatt_block_indexes"] = tuple(int(i) for i in vkw["fullatt_block_indexes"])
+        if "in_chans" in v and "in_channels" not in vkw:
+            vkw["in_channels"] = int(v["in_chans"])
+        vkw.setdefault("out_hidden_size", kw["hidden_size"])
+        return cls(vision=VisionConfig(**vkw), **kw)
+
+    @classmethod
     def tiny(cls, **kw: Any) -> "QwenVLConfig":
         base = dict(vocab_size=4096, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
                     eos_token_id=2, pad_token_id=0, mrope_section=(4, 6, 6), image_token_id=5, video_token_id=6, vision_start_token_id=4,
-                    vision=VisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=128, patch_size=4, temporal_patch_size=1, out_hidden_size=128))
+                    vision=VisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=128, patch_size=4, temporal_patch_size=1, out_hidden_size=128,
+                                        window_size=16, fullatt_block_indexes=(1,)))
         base.update(kw)
         return cls(**base)
 
@@ -125,18 +157,85 @@ class VisionTower(nn.Module):
         ang = torch.cat([ang, ang], -1)  # half-split rotation convention
         return ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
 
+    def _windows(self, grid_thw: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Order of the merge groups that makes every attention window contiguous, and the window lengths in patches.
+        A window covers ``window_size / patch_size / merge`` merge groups per side; windows at the right / bottom edge are
+        partial (an image whose side divides evenly still gets an empty edge window, which is dropped)."""
+        c = self.c
+        ms, unit = c.spatial_merge_size, c.spatial_merge_size**2
+        side = max(c.window_size // ms // c.patch_size, 1)
+        order, lens, base = [], [], 0
+        for t, h, w in grid_thw.tolist():
+            gh, gw = h // ms, w // ms
+            idx = torch.arange(t * gh * gw).view(t, gh, gw)
+            ph, pw = side - gh % side, side - gw % side
+            idx = F.pad(idx, (0, pw, 0, ph), value=-1)
+            nh, nw = (gh + ph) // side, (gw + pw) // side
+            idx = idx.view(t, nh, side, nw, side).permute(0, 1, 3, 2, 4).reshape(t, nh * nw, side * side)
+            n = (idx >= 0).sum(-1).flatten()
+            flat = idx.flatten()
+            order.append(flat[flat >= 0] + base)
+            lens.append(n[n > 0] * unit)
+            base += t * gh * gw
+        return torch.cat(order), torch.cat(lens)
+
     def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
         """``pixel_values [Σ t·h·w, patch_dim]`` (merge-group order), ``grid_thw [n_img, 3]`` → ``[Σ t·h·w / 4, out_hidden]``."""
         c = self.c
+        unit = c.spatial_merge_size**2
         x = linear(pixel_values.to(self.patch_embed.dtype), self.patch_embed)
         cos, sin = self._rope(grid_thw, x.device)
-        lens = (grid_thw[:, 1] * grid_thw[:, 2]).repeat_interleave(grid_thw[:, 0])  # attention stays inside one frame of one image
-        cu = F.pad(lens.cumsum(0), (1, 0)).to(torch.int32).to(x.device)
-        for blk in self.blocks:
-            x = blk(x, cos, sin, cu, int(lens.max()))
-        x = rmsnorm(x, self.merge_norm, c.eps).view(-1, c.hidden_size * c.spatial_merge_size**2)
+        order, win_lens = self._windows(grid_thw)
+        order_dev = order.to(x.device)
+        regroup = lambda t: t.reshape(-1, unit, *t.shape[1:])[order_dev].reshape(-1, *t.shape[1:])  # noqa: E731
+        x, cos, sin = regroup(x), regroup(cos), regroup(sin)
+        lens = (grid_thw[:, 1] * grid_thw[:, 2]).repeat_interleave(grid_thw[:, 0])  # full attention stays inside one frame of one image
+        cu_full = F.pad(lens.cumsum(0), (1, 0)).to(torch.int32).to(x.device)
+        cu_win = F.pad(win_lens.cumsum(0), (1, 0)).to(torch.int32).to(x.device)
+        max_full, max_win = int(lens.max()), int(win_lens.max())
+        for i, blk in enumerate(self.blocks):
+            full = i in c.fullatt_block_indexes
+            x = blk(x, cos, sin, cu_full if full else cu_win, max_full if full else max_win)
+        x = rmsnorm(x, self.merge_norm, c.eps).view(-1, c.hidden_size * unit)
         x = F.gelu(linear(x, self.merge_fc1) + self.merge_fc1_bias)
-        return linear(x, self.merge_fc2) + self.merge_fc2_bias
+        x = linear(x, self.merge_fc2) + self.merge_fc2_bias
+        return x[torch.argsort(order).to(x.device)]
+
+    # ---- Hugging Face key grammar (``visual.*``) -------------------------------------------------------------------
+    def hf_state_dict(self, prefix: str = "model.visual.") -> Dict[str, torch.Tensor]:
+        c, out = self.c, {}
+        out[prefix + "patch_embed.proj.weight"] = self.patch_embed.view(c.hidden_size, c.in_channels, c.temporal_patch_size, c.patch_size, c.patch_size)
+        for i, b in enumerate(self.blocks):
+            p = f"{prefix}blocks.{i}."
+            g, u = b.gate_up.split(c.intermediate_size, 0)
+            gb, ub = b.gate_up_bias.split(c.intermediate_size, 0)
+            out.update({p + "norm1.weight": b.norm1, p + "norm2.weight": b.norm2, p + "attn.qkv.weight": b.qkv, p + "attn.qkv.bias": b.qkv_bias,
+                        p + "attn.proj.weight": b.proj, p + "attn.proj.bias": b.proj_bias, p + "mlp.gate_proj.weight": g, p + "mlp.gate_proj.bias": gb,
+                        p + "mlp.up_proj.weight": u, p + "mlp.up_proj.bias": ub, p + "mlp.down_proj.weight": b.down, p + "mlp.down_proj.bias": b.down_bias})
+        out.update({prefix + "merger.ln_q.weight": self.merge_norm, prefix + "merger.mlp.0.weight": self.merge_fc1, prefix + "merger.mlp.0.bias": self.merge_fc1_bias,
+                    prefix + "merger.mlp.2.weight": self.merge_fc2, prefix + "merger.mlp.2.bias": self.merge_fc2_bias})
+        return out
+
+    @torch.no_grad()
+    def load_hf_state_dict(self, sd: Dict[str, torch.Tensor], prefix: str = "model.visual.") -> None:
+        self.patch_embed.copy_(sd[prefix + "patch_embed.proj.weight"].reshape(self.patch_embed.shape))
+        for i, b in enumerate(self.blocks):
+            p = f"{prefix}blocks.{i}."
+            b.norm1.copy_(sd[p + "norm1.weight"])
+            b.norm2.copy_(sd[p + "norm2.weight"])
+            b.qkv.copy_(sd[p + "attn.qkv.weight"])
+            b.qkv_bias.copy_(sd[p + "attn.qkv.bias"])
+            b.proj.copy_(sd[p + "attn.proj.weight"])
+            b.proj_bias.copy_(sd[p + "attn.proj.bias"])
+            b.gate_up.copy_(torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]], 0))
+            b.gate_up_bias.copy_(torch.cat([sd[p + "mlp.gate_proj.bias"], sd[p + "mlp.up_proj.bias"]], 0))
+            b.down.copy_(sd[p + "mlp.down_proj.weight"])
+            b.down_bias.copy_(sd[p + "mlp.down_proj.bias"])
+        self.merge_norm.copy_(sd[prefix + "merger.ln_q.weight"])
+        self.merge_fc1.copy_(sd[prefix + "merger.mlp.0.weight"])
+        self.merge_fc1_bias.copy_(sd[prefix + "merger.mlp.0.bias"])
+        self.merge_fc2.copy_(sd[prefix + "merger.mlp.2.weight"])
+        self.merge_fc2_bias.copy_(sd[prefix + "merger.mlp.2.bias"])
 
 
 def mrope_positions(tokens: torch.Tensor, grids: Sequence[Sequence[int]], cfg: QwenVLConfig) -> Tuple[torch.Tensor, int]:
@@ -176,6 +275,39 @@ class QwenVLTransformer(Qwen3Transformer):
                  gradient_checkpointing: bool = False):
         super().__init__(cfg, dtype, device, tp, gradient_checkpointing)
         self.visual = VisionTower(cfg.vision, dtype, device)
+
+    # ---- Hugging Face key grammar ---------------------------------------------------------------------------------------
+    # Two layouts exist: checkpoint files written by older library versions use ``visual.*`` / ``model.layers.*``, newer ones
+    # ``model.visual.*`` / ``model.language_model.layers.*``.  Loading accepts both; export writes the newer one.
+    @staticmethod
+    def _split_hf(sd: Dict[str, torch.Tensor]) -> Tuple[Dict[str, torch.Tensor], Dict[str, torch.Tensor]]:
+        text, vis = {}, {}
+        for k, v in sd.items():
+            if k.startswith("model.visual."):
+                vis[k] = v
+            elif k.startswith("visual."):
+                vis["model." + k] = v
+            elif k.startswith("model.language_model."):
+                text["model." + k[len("model.language_model."):]] = v
+            else:
+                text[k] = v
+        return text, vis
+
+    def hf_state_dict(self) -> Dict[str, torch.Tensor]:
+        out = {}
+        for k, v in super().hf_state_dict().items():
+            out[("model.language_model." + k[len("model."):]) if k.startswith("model.") else k] = v
+        out.update(self.visual.hf_state_dict())
+        return out
+
+    @torch.no_grad()
+    def load_hf_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> None:
+        text, vis = self._split_hf(sd)
+        super().load_hf_state_dict(text, strict)
+        if vis:
+            self.visual.load_hf_state_dict(vis)
+        elif strict:
+            raise KeyError("checkpoint holds no vision tower tensors (visual.* / model.visual.*)")
 
     def embed_multimodal(self, tokens: torch.Tensor, pixel_values: Optional[torch.Tensor], grid_thw: Optional[torch.Tensor]) -> torch.Tensor:
         x = self.embed_tokens[tokens]

@@ -140,8 +140,11 @@ class ARGenerator:
             idx = leaders[i:j]
             sel = torch.tensor(idx, device=dev)
             out = torch.empty(len(idx), self.cfg.hidden_size, dtype=last_hidden.dtype, device=dev)
+            deltas = torch.zeros(len(idx), dtype=torch.long, device=dev) if rows == 1 else None  # advanced indexing copies: collect, then scatter
             self._prefill([prompts[k] for k in idx], [plens[k] for k in idx], block_tables[sel], cache, out,
-                          None if extras is None else [extras[k] for k in idx], rope_offset[sel] if rows == 1 else None)
+                          None if extras is None else [extras[k] for k in idx], deltas)
+            if deltas is not None:
+                rope_offset[sel] = deltas
             last_hidden[sel] = out
             i = j
         if rows > 1:
