@@ -212,6 +212,50 @@ def test_gemm_tcgen05(m, n, k):
     _close(c2, ref + r.float(), 0.15, 2e-2, "gemm+residual")
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 6144, 2560), (128, 2560, 4096), (128, 19456, 2560), (77, 2560, 9728), (256, 2560, 4096), (130, 1096, 128)])
+def test_gemm_skinny_cluster_split_k(m, n, k):
+    C = _C()
+    torch.manual_seed(12)
+    a = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    r = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    c = C.gemm_bf16_tn_skinny(a, b)
+    c_again = C.gemm_bf16_tn_skinny(a, b)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0, "a bounded wait expired inside the GEMM"
+    _close(c, ref, 0.05, 2e-2, "skinny gemm")
+    assert torch.equal(c, c_again), "partials are summed in rank order: the result must be reproducible"
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    c2 = C.gemm_bf16_tn_skinny(a, b, r, out)
+    torch.cuda.synchronize()
+    assert c2.data_ptr() == out.data_ptr()
+    _close(c2, ref + r.float(), 0.05, 2e-2, "skinny gemm + residual")
+    for splits in (1, 2, 3, 5, 8):  # every cluster size the launcher may pick
+        C.set_gemm_skinny_splits(splits)
+        cs = C.gemm_bf16_tn_skinny(a, b, r)
+        torch.cuda.synchronize()
+        C.set_gemm_skinny_splits(0)
+        assert C.gemm_status(True) == 0
+        _close(cs, ref + r.float(), 0.05, 2e-2, f"skinny gemm, cluster of {splits}")
+
+
+@pytest.mark.parametrize("m,inter,k,splits", [(128, 9728, 2560, 0), (100, 640, 256, 0), (128, 1024, 512, 2), (256, 4864, 2560, 0)])
+def test_gemm_skinny_swiglu(m, inter, k, splits):
+    C = _C()
+    torch.manual_seed(13)
+    a = (torch.randn(m, k, device="cuda") * 0.3).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device="cuda") * 0.05).to(torch.bfloat16)
+    C.set_gemm_skinny_splits(splits)
+    out = C.gemm_bf16_tn_skinny(a, w, None, None, 2)
+    torch.cuda.synchronize()
+    C.set_gemm_skinny_splits(0)
+    assert C.gemm_status(True) == 0
+    z = a.float() @ w.float().t()
+    ref = torch.nn.functional.silu(z[:, :inter]) * z[:, inter:]
+    _close(out, ref, 0.05, 3e-2, "skinny gemm + swiglu")
+
+
 def test_gemm_swiglu_epilogue():
     C = _C()
     torch.manual_seed(9)

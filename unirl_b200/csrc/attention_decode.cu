@@ -84,6 +84,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
   // so the prefix K/V is read once per group; the remaining z-slices are the per-sequence SUFFIX jobs (tables_b / lens_b).  Both kinds
   // write (o, max, sum) partials; decode_cascade_merge_kernel combines them.
   extern __shared__ __align__(128) uint8_t dec_smem[];
+  pdl_launch_dependents();
+  pdl_wait();  // q and the newest cache rows come from the previous kernel
   using L = DecLayout<D>;
   constexpr int kND = D / 8;   // n-tiles of the output
   constexpr int kKK = D / 16;  // k-steps of Q.K^T
@@ -285,6 +287,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
 
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, bf16* __restrict__ out, int num_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t bh = blockIdx.x;
   const int d = threadIdx.x;
   float M = -INFINITY;
@@ -303,6 +307,8 @@ __global__ void decode_merge_kernel(const float* __restrict__ ws_o, const float*
 template <int D>
 __global__ void decode_cascade_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, bf16* __restrict__ out, int num_splits, int Hq,
                                             int Hkv, int n_shared, int R) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x / Hq, hq = blockIdx.x % Hq, d = threadIdx.x;
   const int Gs = Hq / Hkv, kvh = hq / Gs, g = hq % Gs;
   const int64_t rows[2] = {((int64_t)(b / R) * Hkv + kvh) * (Gs * R) + (b % R) * Gs + g,                       // prefix job row
@@ -345,10 +351,10 @@ int paged_decode_attention_cascade(const void* q, const void* kc, const void* vc
 #define UB_CAS(DD, FF)                                                                                                                     \
   do {                                                                                                                                     \
     if (cudaFuncSetAttribute(paged_decode_kernel<DD, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2; \
-    paged_decode_kernel<DD, FF><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, prefix_tables, prefix_lens, ws_o, \
-                                                                  ws_ml, Hq, Hkv, page_size, max_pages_p, num_splits, sl2, nullptr, nullptr, n_shared, R, \
-                                                                  suffix_tables, suffix_lens, max_pages_s);                                \
-    decode_cascade_merge_kernel<DD><<<B * Hq, DD, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits, Hq, Hkv, n_shared, R);                    \
+    launch_kernel(paged_decode_kernel<DD, FF>, grid, dim3(kDecWarps * 32), need, s, pdl_enabled(), (const bf16*)q, (const bf16*)kc, (const bf16*)vc, \
+                  prefix_tables, prefix_lens, ws_o, ws_ml, Hq, Hkv, page_size, max_pages_p, num_splits, sl2, nullptr, nullptr, n_shared, R, suffix_tables, \
+                  suffix_lens, max_pages_s);                                                                                               \
+    launch_kernel(decode_cascade_merge_kernel<DD>, dim3(B * Hq), dim3(DD), 0, s, pdl_enabled(), ws_o, ws_ml, (bf16*)out, num_splits, Hq, Hkv, n_shared, R); \
   } while (0)
   if (D == 128) {
     if (fast) UB_CAS(128, true); else UB_CAS(128, false);
@@ -391,10 +397,10 @@ int paged_decode_attention(const void* q, const void* kc, const void* vc, const 
       if (cudaFuncSetAttribute(paged_decode_kernel<DD, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2; \
       cfg = true;                                                                                                                          \
     }                                                                                                                                      \
-    paged_decode_kernel<DD, FF><<<grid, kDecWarps * 32, need, s>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, block_tables, seq_lens, ws_o, \
-                                                                  ws_ml, Hq, Hkv, page_size, max_pages, num_splits, sl2, status,           \
-                                                                  num_splits == 1 ? (bf16*)out : nullptr);                                 \
-    if (num_splits > 1) decode_merge_kernel<DD><<<B * Hq, DD, 0, s>>>(ws_o, ws_ml, (bf16*)out, num_splits);                               \
+    launch_kernel(paged_decode_kernel<DD, FF>, grid, dim3(kDecWarps * 32), need, s, pdl_enabled(), (const bf16*)q, (const bf16*)kc, (const bf16*)vc, \
+                  block_tables, seq_lens, ws_o, ws_ml, Hq, Hkv, page_size, max_pages, num_splits, sl2, status,                             \
+                  num_splits == 1 ? (bf16*)out : nullptr, 0, 1, nullptr, nullptr, 0);                                                      \
+    if (num_splits > 1) launch_kernel(decode_merge_kernel<DD>, dim3(B * Hq), dim3(DD), 0, s, pdl_enabled(), ws_o, ws_ml, (bf16*)out, num_splits); \
   } while (0)
   if (D == 128) {
     if (fast) UB_DEC(128, true); else UB_DEC(128, false);

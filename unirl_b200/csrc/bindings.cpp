@@ -272,6 +272,34 @@ Tensor gemm_bf16_tn(const Tensor& a, const Tensor& b, const c10::optional<Tensor
   TORCH_CHECK(rc == 0, "gemm_bf16_tn: unsupported shape or launch failure (code ", rc, ") for M=", M, " N=", N, " K=", K);
   return c;
 }
+// Decode-sized GEMM: one tile per CTA, K split over a thread-block cluster (see gemm_skinny.cu).  epilogue 0 / 1 (residual) / 2 (SwiGLU).
+Tensor gemm_bf16_tn_skinny(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& res, const c10::optional<Tensor>& out, int64_t epilogue) {
+  chk(a, "a"); chk(b, "weight");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm: A [M,K] and B [N,K] expected");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: bf16 operands expected");
+  c10::cuda::CUDAGuard g(a.device());
+  const int64_t M = a.size(0), K = a.size(1);
+  const int64_t N = epilogue == ub::kEpiSwiGLU ? b.size(0) / 2 : b.size(0);
+  Tensor c;
+  if (out.has_value() && out->defined()) {
+    chk(*out, "out");
+    TORCH_CHECK(out->scalar_type() == at::kBFloat16 && out->dim() == 2 && out->size(0) == M && out->size(1) == N, "gemm: out shape");
+    c = *out;
+  } else {
+    c = torch::empty({M, N}, a.options());
+  }
+  const bool has_res = res.has_value() && res->defined();
+  if (has_res) { chk(*res, "residual"); TORCH_CHECK(res->sizes() == c.sizes() && epilogue != ub::kEpiSwiGLU, "gemm: residual shape / epilogue"); }
+  const int rc = ub::gemm_bf16_tn_skinny(a.data_ptr(), b.data_ptr(), c.data_ptr(), optr(res), (int)M, (int)N, (int)K, (int)K, (int)K, (int)N,
+                                         has_res ? ub::kEpiResidual : (int)epilogue, gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16_tn_skinny: unsupported shape or launch failure (code ", rc, ") for M=", M, " N=", N, " K=", K);
+  return c;
+}
+std::vector<int64_t> gemm_skinny_plan(int64_t M, int64_t N, int64_t K, bool swiglu) {
+  int bn = 0, splits = 0;
+  ub::gemm_skinny_plan((int)M, (int)N, (int)K, swiglu, &bn, &splits);
+  return {bn, splits};
+}
 int64_t gemm_status(bool reset) {
   auto& st = gemm_status_tensor();
   const int64_t v = st.item<int>();
@@ -462,6 +490,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sde_replay_fwd", &sde_replay_fwd);
   m.def("sde_replay_bwd", &sde_replay_bwd);
   m.def("gemm_bf16_tn", &gemm_bf16_tn);
+  m.def("gemm_bf16_tn_skinny", &gemm_bf16_tn_skinny, py::arg("a"), py::arg("b"), py::arg("res") = py::none(), py::arg("out") = py::none(),
+        py::arg("epilogue") = 0);
+  m.def("gemm_skinny_plan", &gemm_skinny_plan);
+  m.def("set_gemm_skinny_splits", &ub::set_gemm_skinny_splits);
+  m.def("set_gemm_skinny_debug", [](const c10::optional<Tensor>& trace, bool skip_a) {
+    ub::set_gemm_skinny_debug(trace.has_value() && trace->defined() ? reinterpret_cast<unsigned long long*>(trace->data_ptr<int64_t>()) : nullptr, skip_a ? 1 : 0);
+  }, py::arg("trace") = py::none(), py::arg("skip_a") = false);
+  m.def("set_pdl", &ub::set_pdl);
   m.def("gemm_status", &gemm_status, py::arg("reset") = true);
   m.def("set_gemm_tile", &ub::set_gemm_tile);
   m.def("linear_logprob_fwd", &linear_logprob_fwd);

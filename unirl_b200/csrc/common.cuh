@@ -16,6 +16,33 @@ using bf162 = __nv_bfloat162;
 
 constexpr int kWarp = 32;
 
+// ---- programmatic dependent launch ------------------------------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the stream is still
+// running.  `pdl_wait` blocks until every predecessor grid has completed and its writes are visible; a kernel must call it
+// before it reads anything a predecessor produced and before it writes anything a predecessor may still read.
+// `pdl_launch_dependents` lets the NEXT kernel in the stream start early (once every block of this grid has called it or
+// exited).  Both are no-ops for ordinary launches, so kernels carry them unconditionally.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();  // process-wide switch (set_pdl), on by default
+
+// Launch `kernel` with or without the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -85,6 +85,8 @@ template <bool kAddResidual>
 __global__ void rmsnorm_fwd_vec_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res_in, const bf16* __restrict__ w, bf16* __restrict__ y,
                                        bf16* __restrict__ res_out, float* __restrict__ rstd, int D, float eps) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const int nvec = D >> 3;
   float v[kVPT][8];
@@ -256,6 +258,8 @@ __global__ void qk_norm_rope_fwd_vec_kernel(const bf16* __restrict__ qkv, const 
   // Optional fused KV-cache write: with kc/vc/slots set, the rotated k and the v of token t also go to cache slot
   // slots[t] (layout [pages, Hkv, page, D]); k / v may then be null (decode needs only the cache copy).
   constexpr int half = D / 2, kJ = half / 64;  // pairs-of-2 per lane: D=128 -> 1, D=256 -> 2
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t t = wid / chunks;
@@ -420,6 +424,13 @@ static int vec_threads(int D) {
   while (t > 32 && (t >> 1) >= nvec) t >>= 1;
   return t;
 }
+// Decode-sized launches (a few hundred rows) overlap their start-up with the tail of the previous kernel; the big training /
+// prefill launches keep ordinary stream order.
+constexpr int64_t kPdlMaxRows = 1024;
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
+void set_pdl(bool on) { g_pdl = on; }
+
 static bool vec_ok(int D, int dtype) { return dtype == kBF16 && D % 8 == 0 && (D >> 3) <= 1024 * kVPT; }
 
 static int norm_threads(int D) {
@@ -431,7 +442,8 @@ static int norm_threads(int D) {
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t R, int D, float eps, int dtype, cudaStream_t s) {
   if (R == 0) return;
   if (vec_ok(D, dtype)) {
-    rmsnorm_fwd_vec_kernel<false><<<(unsigned)R, vec_threads(D), 0, s>>>((const bf16*)x, nullptr, (const bf16*)w, (bf16*)y, nullptr, rstd, D, eps);
+    launch_kernel(rmsnorm_fwd_vec_kernel<false>, dim3((unsigned)R), dim3(vec_threads(D)), 0, s, pdl_enabled() && R <= kPdlMaxRows, (const bf16*)x, nullptr,
+                  (const bf16*)w, (bf16*)y, nullptr, rstd, D, eps);
     return;
   }
   if (dtype == kBF16)
@@ -442,7 +454,8 @@ void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t R, 
 void add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, int64_t R, int D, float eps, int dtype, cudaStream_t s) {
   if (R == 0) return;
   if (vec_ok(D, dtype)) {
-    rmsnorm_fwd_vec_kernel<true><<<(unsigned)R, vec_threads(D), 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)res_out, nullptr, D, eps);
+    launch_kernel(rmsnorm_fwd_vec_kernel<true>, dim3((unsigned)R), dim3(vec_threads(D)), 0, s, pdl_enabled() && R <= kPdlMaxRows, (const bf16*)x,
+                  (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)res_out, nullptr, D, eps);
     return;
   }
   if (dtype == kBF16)
@@ -607,11 +620,11 @@ int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, cons
   const int chunks = rope_chunks(T, Hq + 2 * Hkv);
   const dim3 g((unsigned)((T * chunks + 3) / 4));
   if (D == 128)
-    qk_norm_rope_fwd_vec_kernel<128><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq,
-                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size, chunks);
+    launch_kernel(qk_norm_rope_fwd_vec_kernel<128>, g, dim3(128), 0, s, pdl_enabled() && T <= kPdlMaxRows, (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos,
+                  inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq, Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size, chunks);
   else
-    qk_norm_rope_fwd_vec_kernel<256><<<g, 128, 0, s>>>((const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos, inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq,
-                                                       Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size, chunks);
+    launch_kernel(qk_norm_rope_fwd_vec_kernel<256>, g, dim3(128), 0, s, pdl_enabled() && T <= kPdlMaxRows, (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos,
+                  inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq, Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size, chunks);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

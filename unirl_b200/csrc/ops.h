@@ -51,6 +51,14 @@ void sde_replay_bwd(const float* g_mean, const float* g_logp, const float* mean,
 // ---- gemm_tcgen05.cu -------------------------------------------------------------------------------------
 int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
                  cudaStream_t s);
+// Decode-sized GEMM (M of a few hundred rows): one 128 x {128,144} tile per CTA, K split over a thread-block cluster and reduced
+// through distributed shared memory.  epilogue: kEpiStore, kEpiResidual (R != null) or kEpiSwiGLU (B = [gate; up], N = I).
+void set_pdl(bool on);  // programmatic dependent launch for the decode-sized kernels (default on)
+void gemm_skinny_plan(int M, int N, int K, bool swiglu, int* bn_out, int* splits_out);
+void set_gemm_skinny_splits(int splits);  // tuning hook: 0 = heuristic
+void set_gemm_skinny_debug(unsigned long long* trace, int skip_a);  // diagnostics: per-CTA phase timestamps [CTAs, 8]; skip_a isolates weight streaming (wrong result)
+int gemm_bf16_tn_skinny(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
+                        cudaStream_t s);
 int lse_num_tiles(int V);
 void set_gemm_tile(int bn);
 int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int ldw, const int* targets, float temperature, float* pmax, float* psum,

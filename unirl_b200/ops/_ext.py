@@ -23,6 +23,8 @@ def ext() -> Optional[Any]:
                     import torch  # noqa: F401  (the extension links against libtorch)
 
                     _mod = importlib.import_module("unirl_b200._C")
+                    if os.environ.get("UNIRL_B200_PDL", "1") == "0" and hasattr(_mod, "set_pdl"):
+                        _mod.set_pdl(False)  # decode-sized kernels then keep plain stream order
                 except BaseException as e:  # noqa: BLE001
                     _err = e
     return _mod

@@ -16,9 +16,49 @@ import torch.nn.functional as F
 
 from unirl_b200.ops._ext import count_launch, ext, require_ext, use_native
 
-# Skinny (decode-shaped) GEMMs are weight-bandwidth bound and go to the library GEMM; the tcgen05 kernel takes the
-# compute-bound shapes (prefill, training forward) where its 128x256 tiles fill the machine.
+# The persistent 128x256-tile tcgen05 kernel takes the compute-bound shapes (prefill, training forward) where whole tiles
+# fill the machine.  Decode-shaped GEMMs (M up to _MAX_SKINNY_M rows, no autograd) are weight-bandwidth bound and go to the
+# cluster split-K kernel: one tile per CTA, the K range split over a thread-block cluster and summed through distributed shared memory.
 _MIN_NATIVE_M = int(os.environ.get("UNIRL_B200_GEMM_MIN_M", "512"))
+_MAX_SKINNY_M = int(os.environ.get("UNIRL_B200_GEMM_SKINNY_MAX_M", "384"))
+# "unsplit": only shapes whose tiles fill a wave without splitting K (the cluster exchange costs about what the library's
+# split-K costs, so those shapes stay on the library GEMM); "all": every qualifying shape.
+_SKINNY_MODE = os.environ.get("UNIRL_B200_GEMM_SKINNY_MODE", "unsplit")
+_plan_cache: dict = {}
+
+
+def _skinny_unsplit(m: int, n: int, k: int, swiglu: bool) -> bool:
+    key = (m, n, k, swiglu)
+    if key not in _plan_cache:
+        _plan_cache[key] = int(ext().gemm_skinny_plan(m, n, k, swiglu)[1]) == 1
+    return _plan_cache[key]
+
+
+def _skinny_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    m, k = x2.shape
+    n = w.shape[0]
+    return (0 < m <= _MAX_SKINNY_M and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 64 == 0 and n % 8 == 0 and n >= 1024
+            and w.is_contiguous() and os.environ.get("UNIRL_B200_GEMM", "native") == "native")
+
+
+def skinny_linear(x2: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  epilogue: int = 0) -> Optional[torch.Tensor]:
+    """Inference-only ``x2 @ weightᵀ (+ residual)`` -- or, with ``epilogue=EPI_SWIGLU`` and ``weight = [Wg; Wu]``,
+    ``silu(x2·Wgᵀ) ⊙ (x2·Wuᵀ)`` -- for a decode-sized ``x2 [M, K]`` through the cluster split-K tcgen05 GEMM;
+    ``None`` when the shape does not qualify (the caller then uses the library GEMM)."""
+    C = ext()
+    if C is None or not hasattr(C, "gemm_bf16_tn_skinny") or not x2.is_cuda or not _skinny_ok(x2, weight):
+        return None
+    swiglu = int(epilogue) == EPI_SWIGLU
+    if _SKINNY_MODE != "all" and not _skinny_unsplit(x2.shape[0], weight.shape[0] // (2 if swiglu else 1), x2.shape[1], swiglu):
+        return None
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if residual is not None and not residual.is_contiguous():
+        residual = residual.contiguous()
+    y = C.gemm_bf16_tn_skinny(x2, weight, residual, out, int(epilogue))
+    count_launch()
+    return y
 
 
 def _native_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
@@ -61,6 +101,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tenso
             x2 = x2.contiguous()
         if ext() is not None and hasattr(ext(), "gemm_bf16_tn") and _native_ok(x2, weight):
             return _NativeLinear.apply(x, weight, residual, EPI_RESIDUAL if residual is not None else EPI_NONE)
+        if not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or (residual is not None and residual.requires_grad))):
+            y = skinny_linear(x2, weight, residual.reshape(-1, residual.shape[-1]) if residual is not None else None)
+            if y is not None:
+                return y.view(*x.shape[:-1], y.shape[-1])
     y = F.linear(x, weight)
     return y + residual if residual is not None else y
 
@@ -73,6 +117,10 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor) -> torch.Tensor
     """
     from unirl_b200.ops.activation import swiglu
 
+    if use_native(x) and not (torch.is_grad_enabled() and (x.requires_grad or weight_gate_up.requires_grad)) and weight_gate_up.shape[0] % 16 == 0:
+        y = skinny_linear(x.reshape(-1, x.shape[-1]), weight_gate_up, epilogue=EPI_SWIGLU)
+        if y is not None:
+            return y.view(*x.shape[:-1], y.shape[-1])
     return swiglu(linear(x, weight_gate_up))
 
 
@@ -84,4 +132,4 @@ def lora_linear(x: torch.Tensor, weight: torch.Tensor, lora_a: torch.Tensor, lor
     return y + bias if bias is not None else y
 
 
-__all__ = ["linear", "linear_swiglu", "lora_linear", "EPI_NONE", "EPI_RESIDUAL", "EPI_SWIGLU"]
+__all__ = ["linear", "skinny_linear", "linear_swiglu", "lora_linear", "EPI_NONE", "EPI_RESIDUAL", "EPI_SWIGLU"]

@@ -85,6 +85,36 @@ def case_gemm(args: argparse.Namespace) -> None:
         _emit(row)
 
 
+def case_skinny_gemm(args: argparse.Namespace) -> None:
+    """Decode-shaped GEMMs (weight-bandwidth bound): cluster split-K tcgen05 kernel vs the library GEMM, each timed over a ring of
+    distinct weight matrices larger than L2 so every call streams its weights from HBM."""
+    from unirl_b200.ops._ext import require_ext
+
+    C, pk = require_ext(), _peaks()
+    timer = _Timer(args.iters, flush=False)
+    shapes = [tuple(int(x) for x in s.split("x")) for s in (args.skinny_shapes or "128x6144x2560,128x2560x4096,128x19456x2560,128x2560x9728,256x2560x9728").split(",")]
+    for m, n, k in shapes:
+        ring = max(2, int(400e6 // (n * k * 2)) + 1)
+        a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        ws = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05 for _ in range(ring)]
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+
+        def ours():
+            for w in ws:
+                C.gemm_bf16_tn_skinny(a, w, None, out)
+
+        def lib():
+            for w in ws:
+                torch.matmul(a, w.t(), out=out)
+
+        t_ours, t_lib = timer(ours), timer(lib)
+        gb = (n * k + m * k + m * n) * 2 / 1e9
+        assert C.gemm_status(True) == 0, "a pipeline wait timed out"
+        _emit({"case": "skinny_gemm", "M": m, "N": n, "K": k, "tile_n": C.gemm_skinny_plan(m, n, k, False)[0], "cluster": C.gemm_skinny_plan(m, n, k, False)[1], "skinny_us": t_ours["best_ms"] / ring * 1e3,
+               "library_us": t_lib["best_ms"] / ring * 1e3, "skinny_gbs": gb / (t_ours["best_ms"] / ring) * 1e3,
+               "frac_of_peak": gb / (t_ours["best_ms"] / ring) * 1e3 / pk["hbm_gbs"], "library_gbs": gb / (t_lib["best_ms"] / ring) * 1e3, "peak": pk["kind"]})
+
+
 def case_decode_attention(args: argparse.Namespace) -> None:
     from unirl_b200.ops.attention import paged_decode_attention
 
@@ -378,7 +408,7 @@ def case_peer(args: argparse.Namespace) -> None:
     dist.destroy_process_group()
 
 
-CASES = {"gemm": case_gemm, "decode_attention": case_decode_attention, "linear_logprob": case_linear_logprob, "linear_sample": case_linear_sample,
+CASES = {"gemm": case_gemm, "skinny_gemm": case_skinny_gemm, "decode_attention": case_decode_attention, "linear_logprob": case_linear_logprob, "linear_sample": case_linear_sample,
          "elementwise": case_elementwise, "peer": case_peer, "decode_step": case_decode_step, "train_step": case_train_step, "attention": case_attention}
 
 
@@ -387,6 +417,7 @@ def main() -> None:
     ap.add_argument("case", choices=sorted(CASES))
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--shapes", default="18800x6144x2560,18800x2560x4096,18800x19456x2560,18800x2560x9728,8192x8192x8192", help="gemm: MxNxK list")
+    ap.add_argument("--skinny-shapes", default="", help="skinny_gemm: MxNxK list")
     ap.add_argument("--no-library", action="store_true", help="gemm: skip the library GEMM (for profiler captures)")
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--ctx", type=int, default=2688)

@@ -128,7 +128,10 @@ class FusedAllReduce:
 
             return x, (rmsnorm(x, norm_weight, eps) if norm_weight is not None else None)
         part = self._stage(T)
-        torch.matmul(inp, weight.t(), out=part)
+        from unirl_b200.ops.linear import skinny_linear
+
+        if skinny_linear(inp, weight, None, out=part) is None:
+            torch.matmul(inp, weight.t(), out=part)
         x = torch.empty_like(part)
         h = torch.empty_like(part) if norm_weight is not None else None
         self._C.peer_allreduce_residual_rmsnorm(self.arena.peer, part, residual, norm_weight, x, h, float(eps))
