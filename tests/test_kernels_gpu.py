@@ -485,3 +485,28 @@ def test_generator_with_shared_prefix_matches_unshared_generation():
     for a, b in zip(outs[0].log_probs, outs[1].log_probs):
         n = min(a.numel(), b.numel(), 4)
         assert float((a[:n] - b[:n]).abs().max()) < 0.05
+
+
+def test_linear_weight_grad_accumulates_into_fp32_buffer():
+    """The trainer hands its fp32 accumulator to the linear layer; dW must land there (twice after two backward passes) and
+    the parameter's own .grad is only a placeholder."""
+    from unirl_b200.ops.linear import linear
+
+    torch.manual_seed(21)
+    m, n, k = 640, 256, 192
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = torch.nn.Parameter((torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16))
+    buf = torch.zeros(n, k, device="cuda", dtype=torch.float32)
+    w._wgrad_accum = lambda: buf
+    gy = (torch.randn(m, n, device="cuda") * 0.2).to(torch.bfloat16)
+    ref_w = gy.float().t() @ x.detach().float()
+    ref_x = gy.float() @ w.detach().float()
+    for rep in (1, 2):
+        x.grad = None
+        linear(x, w).backward(gy)
+        torch.cuda.synchronize()
+        assert getattr(w, "_wgrad_fused", False), "the fused path did not run"
+        _close(buf, ref_w * rep, 2e-2 * rep, 1e-2, f"accumulated dW after {rep} pass(es)")
+        _close(x.grad, ref_x, 0.05, 2e-2, "dX")
+        w._wgrad_fused = False
+        w.grad = None

@@ -20,6 +20,7 @@ from unirl_b200.ops._ext import count_launch, ext, require_ext, use_native
 # fill the machine.  Decode-shaped GEMMs (M up to _MAX_SKINNY_M rows, no autograd) are weight-bandwidth bound and go to the
 # cluster split-K kernel: one tile per CTA, the K range split over a thread-block cluster and summed through distributed shared memory.
 _MIN_NATIVE_M = int(os.environ.get("UNIRL_B200_GEMM_MIN_M", "512"))
+_WGRAD_FUSION = os.environ.get("UNIRL_B200_WGRAD_FUSION", "1") != "0"
 _MAX_SKINNY_M = int(os.environ.get("UNIRL_B200_GEMM_SKINNY_MAX_M", "384"))
 # "unsplit": only shapes whose tiles fill a wave without splitting K (the cluster exchange costs about what the library's
 # split-K costs, so those shapes stay on the library GEMM); "all": every qualifying shape.
@@ -79,6 +80,9 @@ class _NativeLinear(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.has_res = residual is not None
         ctx.in_shape = x.shape
+        # set by the sharded trainer on its parameters: returns the fp32 gradient-accumulator view of this weight
+        ctx.accum = getattr(w, "_wgrad_accum", None) if _WGRAD_FUSION else None
+        ctx.param = w if ctx.accum is not None else None
         return y.view(*x.shape[:-1], y.shape[-1])
 
     @staticmethod
@@ -86,7 +90,18 @@ class _NativeLinear(torch.autograd.Function):
         x2, w = ctx.saved_tensors
         g2 = gy.reshape(-1, gy.shape[-1])
         gx = (g2 @ w).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
-        gw = (g2.t() @ x2) if ctx.needs_input_grad[1] else None
+        gw = None
+        if ctx.needs_input_grad[1]:
+            if ctx.accum is not None:
+                # dW accumulates into the fp32 buffer inside the GEMM (C = 1·C + dYᵀ·X, fp32 output): the bf16 dW and the
+                # separate add pass (12 bytes of traffic per parameter and micro-batch) disappear.  Autograd still needs a
+                # gradient object to fire the parameter's hook; an uninitialised placeholder costs nothing.
+                acc = ctx.accum()
+                torch.addmm(acc, g2.t(), x2, out_dtype=torch.float32, out=acc)
+                ctx.param._wgrad_fused = True
+                gw = torch.empty(w.shape, dtype=w.dtype, device=w.device)
+            else:
+                gw = g2.t() @ x2
         return gx, gw, (gy if ctx.has_res else None), None
 
 

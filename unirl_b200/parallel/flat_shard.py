@@ -268,6 +268,17 @@ class FlatShardedModel:
             for s in g.slots:
                 if s.param.requires_grad:
                     g._hooks.append(s.param.register_post_accumulate_grad_hook(self._make_hook(g, s)))
+                    # Linear layers that find this attribute accumulate their weight gradient straight into the fp32 buffer
+                    # (GEMM with beta = 1) instead of materialising a bf16 gradient that the hook then adds.
+                    s.param._wgrad_accum = self._make_accum(g, s)
+
+    @staticmethod
+    def _make_accum(g: FlatGroup, s: ParamSlot) -> Callable[[], torch.Tensor]:
+        def accum() -> torch.Tensor:
+            g.ensure_grad_buffers()
+            return g.grad_view(s)
+
+        return accum
 
     # ---- ZeRO-3: replicas exist only around their block's forward and backward ------------------------------------
     def _gather_into(self, out: torch.Tensor, shard: torch.Tensor) -> None:
@@ -302,7 +313,10 @@ class FlatShardedModel:
             if p.grad is None:
                 return
             g.ensure_grad_buffers()
-            g.grad_view(s).add_(p.grad)
+            if getattr(p, "_wgrad_fused", False):
+                p._wgrad_fused = False  # the producing GEMM already added into the fp32 buffer; p.grad is a placeholder
+            else:
+                g.grad_view(s).add_(p.grad)
             p.grad = None
             if self._sync_enabled and self.world > 1:
                 g._pending -= 1
