@@ -21,7 +21,7 @@ from unirl_b200.ops._ext import count_launch, ext, require_ext, use_native
 # cluster split-K kernel: one tile per CTA, the K range split over a thread-block cluster and summed through distributed shared memory.
 _MIN_NATIVE_M = int(os.environ.get("UNIRL_B200_GEMM_MIN_M", "512"))
 _WGRAD_FUSION = os.environ.get("UNIRL_B200_WGRAD_FUSION", "1") != "0"
-_MAX_SKINNY_M = int(os.environ.get("UNIRL_B200_GEMM_SKINNY_MAX_M", "384"))
+_MAX_SKINNY_M = int(os.environ.get("UNIRL_B200_GEMM_SKINNY_MAX_M", "128"))  # measured win at one 128-row tile; 256 rows (two tiles re-reading the weights) lose to the library
 # "unsplit": only shapes whose tiles fill a wave without splitting K (the cluster exchange costs about what the library's
 # split-K costs, so those shapes stay on the library GEMM); "all": every qualifying shape.
 _SKINNY_MODE = os.environ.get("UNIRL_B200_GEMM_SKINNY_MODE", "unsplit")

@@ -208,9 +208,22 @@ def case_decode_step(args: argparse.Namespace) -> None:
     if args.layers:
         cfg.num_hidden_layers = args.layers
     b, ctx, ps = args.batch, args.ctx, args.page_size
-    model = Qwen3Transformer(cfg, dtype=torch.bfloat16, device="cuda").init_weights(0).eval().requires_grad_(False)
+    tp, tpc, far = int(os.environ.get("WORLD_SIZE", "1")), None, None
+    if tp > 1:  # under torchrun: the ranks form one tensor-parallel group with the fused all-reduce of the rollout engine
+        import torch.distributed as dist
+
+        from unirl_b200.distributed.group.comm import Comm
+        from unirl_b200.models.qwen3.modeling import TPContext
+        from unirl_b200.parallel.fused_collectives import FusedAllReduce
+
+        local = int(os.environ.get("LOCAL_RANK", 0))
+        torch.cuda.set_device(local)
+        dist.init_process_group("cpu:gloo,cuda:nccl", device_id=torch.device("cuda", local))
+        far = FusedAllReduce(Comm.world(), max(b, 64), cfg.hidden_size, torch.device("cuda", local))
+        tpc = TPContext(int(os.environ["RANK"]), tp, far, fused=far)
+    model = Qwen3Transformer(cfg, dtype=torch.bfloat16, device="cuda", tp=tpc).init_weights(0).eval().requires_grad_(False)
     pages_per = (ctx + 1 + ps - 1) // ps
-    cache = PagedKVCache(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim, ps, b * pages_per, torch.bfloat16, "cuda")
+    cache = PagedKVCache(cfg.num_hidden_layers, cfg.num_key_value_heads // tp, cfg.head_dim, ps, b * pages_per, torch.bfloat16, "cuda")
     for t in cache.k + cache.v:
         t.normal_()
     bt = torch.randperm(b * pages_per, device="cuda").view(b, pages_per).to(torch.int32)
@@ -219,7 +232,7 @@ def case_decode_step(args: argparse.Namespace) -> None:
     meta = AttnMeta(mode="decode", positions=pos, k_cache=cache.k, v_cache=cache.v, block_tables=bt, seq_lens=(pos + 1).to(torch.int32),
                     slot_mapping=page * ps + pos % ps, max_kv_len=ctx + 1)
     C = require_ext()
-    meta.workspace = torch.empty(C.decode_workspace_size(b, cfg.num_attention_heads, cfg.head_dim, ctx + 1), dtype=torch.float32, device="cuda")
+    meta.workspace = torch.empty(C.decode_workspace_size(b, cfg.num_attention_heads // tp, cfg.head_dim, ctx + 1), dtype=torch.float32, device="cuda")
     tokens = torch.randint(0, cfg.vocab_size, (b,), device="cuda")
 
     @torch.no_grad()
@@ -231,13 +244,26 @@ def case_decode_step(args: argparse.Namespace) -> None:
     g = torch.cuda.CUDAGraph()
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
+    if far is not None:
+        far.align()
     with torch.cuda.graph(g, stream=s):
         step()
+        if far is not None:
+            far.align()
     graphed = _Timer(args.iters, flush=False)(g.replay)
+    if far is not None:
+        far.arena.check()
     n_param = sum(p.numel() for n, p in model.named_parameters() if not n.startswith("embed_tokens"))
-    gb = (n_param * 2 + 2.0 * b * ctx * cfg.num_key_value_heads * cfg.head_dim * 2 * cfg.num_hidden_layers) / 1e9
-    _emit({"case": "decode_step", "batch": b, "ctx": ctx, "layers": cfg.num_hidden_layers, "eager_ms": eager["median_ms"], "graph_ms": graphed["median_ms"],
-           "weights_plus_kv_gb": gb, "gbs": gb / graphed["median_ms"] * 1e3, "frac_of_peak": gb / graphed["median_ms"] * 1e3 / pk["hbm_gbs"], "peak": pk["kind"]})
+    gb = (n_param * 2 + 2.0 * b * ctx * (cfg.num_key_value_heads // tp) * cfg.head_dim * 2 * cfg.num_hidden_layers) / 1e9
+    if int(os.environ.get("RANK", "0")) == 0:
+        _emit({"case": "decode_step", "tp": tp, "batch": b, "ctx": ctx, "layers": cfg.num_hidden_layers, "eager_ms": eager["median_ms"],
+               "graph_ms": graphed["median_ms"], "weights_plus_kv_gb_per_gpu": gb, "gbs": gb / graphed["median_ms"] * 1e3,
+               "frac_of_peak": gb / graphed["median_ms"] * 1e3 / pk["hbm_gbs"], "peak": pk["kind"]})
+    if tp > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def case_train_step(args: argparse.Namespace) -> None:
