@@ -100,6 +100,27 @@ def test_wait_runs_out_and_reports_status():
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+def test_ulysses_exchange_data_path_one_device(mode):
+    """Four "ranks" whose staged tensors live on this device: every rank's pull must equal the permutation of the library path."""
+    C = _C()
+    torch.manual_seed(4)
+    W, B, l, Hp, D = 4, 2, 24, 3, 64
+    shape = (B, l, W * Hp, D) if mode == 0 else (B, W * l, Hp, D)
+    xs = [torch.randn(*shape, device="cuda").bfloat16() for _ in range(W)]
+    arenas = [x.reshape(-1).clone() for x in xs]
+    for r in range(W):
+        pc, flags, state = _local_comm(C, arenas, r, BIG)
+        out = C.peer_ulysses_exchange(pc, arenas[r], B, l, Hp, D, mode)
+        torch.cuda.synchronize()
+        assert int(state[4]) == 0 and int(state[0]) == 1
+        if mode == 0:  # out[b, p*l + t, hh] = x_p[b, t, r*Hp + hh]
+            want = torch.cat([x[:, :, r * Hp:(r + 1) * Hp] for x in xs], 1)
+        else:          # out[b, t, p*Hp + hh] = x_p[b, r*l + t, hh]
+            want = torch.cat([x[:, r * l:(r + 1) * l] for x in xs], 2)
+        assert torch.equal(out, want), (mode, r)
+
+
 def test_scatter_copy_table():
     from unirl_b200.distributed.weight_sync.full.reshard import CopyOp, execute_copy
     from unirl_b200.parallel.fused_collectives import reshard_scatter_local
@@ -173,6 +194,28 @@ def _two_rank_body(rank, world):
     gathered = [torch.zeros_like(results[1][1]) for _ in range(world)]
     dist.all_gather_object(gathered, results[1][1])
     out["replica_diff"] = float(max((g - gathered[0]).abs().max() for g in gathered))
+    # -- Ulysses attention: peer-memory exchange kernel vs pack + all-to-all + unpack, forward and backward
+    from unirl_b200.parallel.ulysses import UlyssesContext
+
+    torch.manual_seed(7 + rank)
+    B, l, Hh, D, n_text = 2, 96, 8, 64, 5
+    base = [torch.randn(B, n_text + l, Hh, D, device=dev).bfloat16() for _ in range(3)]
+    if n_text:  # text rows are replicated on every rank
+        for t in base:
+            t0 = t[:, :n_text].clone()
+            dist.broadcast(t0, 0)
+            t[:, :n_text] = t0
+    got = {}
+    for kind in ("nccl", "fused"):
+        ctx = UlyssesContext(comm, collectives=kind)
+        q, k, v = (t.clone().requires_grad_() for t in base)
+        o = ctx.attention(q, k, v, n_text)
+        (o.float() * torch.linspace(0.5, 1.5, o.numel(), device=dev).view_as(o)).sum().backward()
+        got[kind] = (o.detach().float(), q.grad.float(), k.grad.float(), v.grad.float())
+        if kind == "fused":
+            assert ctx._fused is not None, "the peer-memory exchange was not used"
+            ctx._fused.check()
+    out["ulysses_diff"] = float(max((a - b).abs().max() for a, b in zip(got["nccl"], got["fused"])))
     return out
 
 
@@ -184,3 +227,4 @@ def test_two_rank_fused_collectives_match_library():
         assert abs(o["norm_nccl"] - o["norm_fused"]) <= 1e-3 * max(1.0, o["norm_nccl"]), o
         assert o["param_diff"] <= 1e-2, o  # bf16 replicas after 3 steps
         assert o["replica_diff"] == 0.0, o  # every rank holds the same replica
+        assert o["ulysses_diff"] == 0.0, o  # the exchange only moves data: both paths must agree bit for bit

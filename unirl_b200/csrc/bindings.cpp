@@ -432,6 +432,18 @@ void peer_scatter_copy(const Tensor& table, int64_t n_ops, int64_t max_vecs) {
   const int rc = ub::peer_scatter_copy(table.data_ptr(), (int)n_ops, max_vecs, stream());
   TORCH_CHECK(rc == 0, "peer_scatter_copy: launch failure (code ", rc, ")");
 }
+// Ulysses exchange: `staged` is this rank's tensor inside its symmetric arena (same offset on every rank); returns the permuted pull.
+Tensor peer_ulysses_exchange(PyPeerComm& pc, const Tensor& staged, int64_t B, int64_t l, int64_t Hp, int64_t D, int64_t mode) {
+  chk(staged, "staged");
+  TORCH_CHECK(staged.scalar_type() == at::kBFloat16, "ulysses exchange: bf16 expected");
+  const int64_t P = pc.c.world;
+  TORCH_CHECK(staged.numel() == B * P * l * Hp * D, "ulysses exchange: staged tensor must hold B * P * l * Hp * D elements");
+  c10::cuda::CUDAGuard g(staged.device());
+  auto out = mode == 0 ? torch::empty({B, P * l, Hp, D}, staged.options()) : torch::empty({B, l, P * Hp, D}, staged.options());
+  const int rc = ub::peer_ulysses_exchange(pc.c, pc.offset_of(staged), out.data_ptr(), (int)B, (int)l, (int)Hp, (int)D, (int)mode, stream());
+  TORCH_CHECK(rc == 0, "peer_ulysses_exchange: bad arguments or launch failure (code ", rc, ")");
+  return out;
+}
 void peer_barrier(PyPeerComm& pc) {
   c10::cuda::CUDAGuard g(pc.state.device());
   const int rc = ub::peer_barrier(pc.c, stream());
@@ -515,6 +527,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_allreduce_residual_rmsnorm", &peer_allreduce_residual_rmsnorm);
   m.def("peer_reduce_scatter_sumsq", &peer_reduce_scatter_sumsq);
   m.def("peer_adamw_publish", &peer_adamw_publish);
+  m.def("peer_ulysses_exchange", &peer_ulysses_exchange);
   m.def("peer_scatter_copy", &peer_scatter_copy);
   m.def("peer_barrier", &peer_barrier);
   py::class_<ub::BlockAllocator>(m, "BlockAllocator")

@@ -91,6 +91,7 @@ int peer_allreduce_residual_rmsnorm(const PeerComm& c, int64_t part_offset, cons
 int peer_reduce_scatter_sumsq(const PeerComm& c, int64_t grad_offset, int64_t shard, float* out, float* sumsq, float scale, cudaStream_t s);
 int peer_adamw_publish(const PeerComm& c, int64_t replica_offset, int64_t shard, float* master, const float* grad, float* m, float* v, float* ema, float lr,
                        float b1, float b2, float eps, float wd, int64_t step, const float* clip, float ema_decay, cudaStream_t s);
+int peer_ulysses_exchange(const PeerComm& c, int64_t stage_offset, void* out, int B, int l, int Hp, int D, int mode, cudaStream_t s);
 int peer_scatter_copy(const void* ops_dev, int n_ops, int64_t max_vecs, cudaStream_t s);
 int peer_barrier(const PeerComm& c, cudaStream_t s);
 

@@ -245,6 +245,43 @@ __global__ void adamw_publish_kernel(PeerTable t, uint32_t* tick, uint32_t* ctr,
   peer_leave(t, tick, ctr, epoch, true, status, 325);
 }
 
+// ------------------------------------------------------------------------------------------ sequence <-> head exchange (Ulysses)
+// buf[p] + stage_offset is rank p's staged activation (bf16).  Every rank pulls ITS slice from all peers and writes it,
+// already permuted, into a private output tensor: the pack / all-to-all / unpack sequence of the library path becomes one pass.
+//   mode 0 (sequence shard -> head shard): staged x_p [B, l, P*Hp, D]  ->  out[b, p*l + t, hh, :] = x_p[b, t, rank*Hp + hh, :]
+//   mode 1 (head shard -> sequence shard): staged x_p [B, P*l, Hp, D]  ->  out[b, t, p*Hp + hh, :] = x_p[b, rank*l + t, hh, :]
+// The entry rendezvous says "every rank has staged its tensor", the exit rendezvous "every rank has finished reading mine".
+__global__ void ulysses_exchange_kernel(PeerTable t, uint32_t* tick, uint32_t* ctr, int64_t stage_offset, bf16* __restrict__ out, int B, int l, int Hp, int D,
+                                        int mode, int* status) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tick) + 1;
+  const bool ok = peer_enter(t, epoch, ctr, status, 350);
+  if (ok) {
+    const int P = t.world, r = t.rank;
+    const int64_t dv = D >> 3;                       // 16-byte vectors per head row
+    const int64_t row_v = (int64_t)Hp * dv;          // vectors of one (token, head-shard) row
+    const int64_t total = (int64_t)B * P * l * row_v;  // vectors of the output
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t v = i % row_v;       // (hh, d-vector) inside the head shard
+      int64_t rest = i / row_v;          // (b, p, t) in an order that keeps each peer's reads contiguous
+      const int tt = (int)(rest % l);
+      rest /= l;
+      const int p = (int)((rest + r) % P);  // start with a different peer on every rank: no incast on one link
+      const int64_t b = rest / P;
+      int64_t src, dst;
+      if (mode == 0) {
+        src = ((b * l + tt) * P + r) * row_v + v;            // x_p[b, t, r*Hp + hh, :]
+        dst = ((b * P + p) * l + tt) * row_v + v;            // out[b, p*l + t, hh, :]
+      } else {
+        src = ((b * P + r) * l + tt) * row_v + v;            // x_p[b, r*l + t, hh, :]
+        dst = ((b * l + tt) * P + p) * row_v + v;            // out[b, t, p*Hp + hh, :]
+      }
+      const uint4 val = reinterpret_cast<const uint4*>(static_cast<const bf16*>(t.buf[p]) + stage_offset)[src];
+      reinterpret_cast<uint4*>(out)[dst] = val;
+    }
+  }
+  peer_leave(t, tick, ctr, epoch, true, status, 355);
+}
+
 // ------------------------------------------------------------------------------------------ table-driven copies
 struct CopyDesc {
   const bf16* src;
@@ -319,6 +356,13 @@ int peer_adamw_publish(const PeerComm& c, int64_t replica_offset, int64_t shard,
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   adamw_publish_kernel<<<grid_for(shard / 8, 592), 256, 0, s>>>(make_table(c), c.tick, c.ctr, replica_offset, shard, master, grad, m, v, ema, lr, b1, b2, eps, wd,
                                                            bc1, bc2, clip, ema_decay, c.status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+int peer_ulysses_exchange(const PeerComm& c, int64_t stage_offset, void* out, int B, int l, int Hp, int D, int mode, cudaStream_t s) {
+  if (bad(c) || (D % 8) || (stage_offset % 8) || (reinterpret_cast<uintptr_t>(out) & 15) || B < 1 || l < 1 || Hp < 1) return 1;
+  const int64_t vecs = (int64_t)B * c.world * l * Hp * (D / 8);
+  ulysses_exchange_kernel<<<grid_for(vecs, 592), 256, 0, s>>>(make_table(c), c.tick, c.ctr, stage_offset, static_cast<bf16*>(out), B, l, Hp, D, mode, c.status);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

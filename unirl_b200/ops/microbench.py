@@ -430,6 +430,20 @@ def case_peer(args: argparse.Namespace) -> None:
         _emit({"case": "peer_trainer_collectives", "world": world, "numel": numel, **{k + "_ms": v for k, v in rows.items()},
                "rs_nvlink_gbs": rs_bytes / rows["fused_reduce_scatter_norm"] / 1e6, "publish_nvlink_gbs": ag_bytes / rows["fused_adamw_publish"] / 1e6,
                "nvlink_peer_copy_gbs_measured_reference": 770.0})
+    # -- Ulysses exchange (sequence shard -> head shard) of one WAN-sized activation: 40 heads x 128, 32760 / 8 tokens per rank
+    from unirl_b200.parallel.fused_collectives import FusedUlyssesExchange
+    from unirl_b200.parallel.ulysses import _a2a_seq_to_head
+
+    heads = 40 // world * world
+    xa = torch.randn(1, 4095, heads, 128, device=dev, dtype=torch.bfloat16)
+    ex = FusedUlyssesExchange(comm, dev, wait_s=20.0)
+    f = tmax(timer(lambda: ex.exchange(xa, 0))["median_ms"])
+    n = tmax(timer(lambda: _a2a_seq_to_head(xa, comm))["median_ms"])
+    ex.check()
+    if rank == 0:
+        moved = xa.numel() * 2 * (world - 1) / world  # bytes this rank pulls over NVLink
+        _emit({"case": "peer_ulysses_exchange", "world": world, "shape": list(xa.shape), "fused_ms": f, "library_pack_all_to_all_unpack_ms": n, "speedup": n / f,
+               "nvlink_gbs": moved / f / 1e6, "nvlink_peer_copy_gbs_measured_reference": 770.0})
     dist.barrier()
     dist.destroy_process_group()
 

@@ -158,6 +158,67 @@ def make_fused_all_reduce(comm: Comm, max_tokens: int = 16384, hidden: int = 0, 
     return FusedAllReduce(comm, max_tokens, hidden, device)
 
 
+# ------------------------------------------------------------------------------------------------ Ulysses exchange
+class FusedUlyssesExchange:
+    """Sequence-shard ↔ head-shard exchange of the Ulysses attention through peer memory: the activation is staged once in
+    this rank's symmetric arena and ONE kernel on every rank pulls its slice from all peers, writing it already permuted
+    (the library path packs, runs an all-to-all and unpacks: three passes and two extra buffers).  Differentiable: the
+    backward of one direction is the other direction."""
+
+    def __init__(self, comm: Comm, device: Any, wait_s: float = 60.0):
+        self.comm, self.device, self.wait_s = comm, torch.device(device), float(wait_s)
+        self.arena: Optional[PeerArena] = None
+        self._stage: Optional[torch.Tensor] = None
+        self._C = _ext.require_ext()
+
+    def _staging(self, numel: int) -> torch.Tensor:
+        if self._stage is None or self._stage.numel() < numel:  # collective and deterministic: every rank grows at the same call
+            cap = max(numel, 1 << 20)
+            self.arena = PeerArena(self.comm, cap * 2 + 512, self.device, self.wait_s)
+            self._stage = self.arena.take(cap, torch.bfloat16)
+        return self._stage[:numel]
+
+    def exchange(self, x: torch.Tensor, mode: int) -> torch.Tensor:
+        """``mode 0``: ``[B, l, P·Hp, D] → [B, P·l, Hp, D]``; ``mode 1``: ``[B, P·l, Hp, D] → [B, l, P·Hp, D]``."""
+        p = self.comm.size
+        if mode == 0:
+            b, l, h, d = x.shape
+            hp = h // p
+        else:
+            b, lp, hp, d = x.shape
+            l = lp // p
+        stage = self._staging(x.numel())
+        stage.view(x.shape).copy_(x)
+        out = self._C.peer_ulysses_exchange(self.arena.peer, stage, b, l, hp, d, mode)
+        _ext.count_launch()
+        return out
+
+    def supports(self, x: torch.Tensor) -> bool:
+        return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+
+    def check(self) -> None:
+        if self.arena is not None:
+            self.arena.check()
+
+
+class _FusedExchange(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, ex: "FusedUlyssesExchange", mode: int) -> torch.Tensor:
+        ctx.ex, ctx.mode = ex, mode
+        return ex.exchange(x.contiguous(), mode)
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        return ctx.ex.exchange(g.contiguous(), 1 - ctx.mode), None, None
+
+
+def make_fused_ulysses_exchange(comm: Comm, device: Any = None) -> Optional[FusedUlyssesExchange]:
+    device = device if device is not None else (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu")
+    if not peer_memory_available(comm, device):
+        return None
+    return FusedUlyssesExchange(comm, device)
+
+
 # ------------------------------------------------------------------------------------------------ sharded trainer
 class FusedShardComm(ShardComm):
     """Sharded-trainer collectives through peer memory: replicas and gradient buffers live in symmetric arenas."""
@@ -248,5 +309,5 @@ def reshard_scatter_local(plan: Sequence[Tuple[torch.Tensor, torch.Tensor, Any]]
     return True
 
 
-__all__ = ["PeerArena", "PeerCommError", "FusedAllReduce", "make_fused_all_reduce", "FusedShardComm", "reshard_scatter_local", "build_copy_table",
+__all__ = ["PeerArena", "PeerCommError", "FusedAllReduce", "make_fused_all_reduce", "FusedUlyssesExchange", "make_fused_ulysses_exchange", "FusedShardComm", "reshard_scatter_local", "build_copy_table",
            "peer_memory_available"]

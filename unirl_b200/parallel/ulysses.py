@@ -82,9 +82,28 @@ class _GatherHeads(torch.autograd.Function):
 
 
 class UlyssesContext:
-    def __init__(self, comm: Comm):
+    def __init__(self, comm: Comm, collectives: str = "fused"):
         self.comm = comm
         self.size, self.rank = comm.size, max(comm.rank, 0)
+        self.collectives = collectives  # fused (peer-memory exchange kernel) | nccl (pack + all-to-all + unpack)
+        self._fused: Any = None
+        self._fused_tried = False
+
+    def _exchange(self, x: torch.Tensor, mode: int) -> torch.Tensor:
+        """Sequence shard → head shard (``mode 0``) or back (``mode 1``), on the peer-memory kernel when the tensors allow it."""
+        if self.collectives == "fused" and x.is_cuda and not self._fused_tried:
+            self._fused_tried = True
+            try:
+                from unirl_b200.parallel.fused_collectives import make_fused_ulysses_exchange
+
+                self._fused = make_fused_ulysses_exchange(self.comm, x.device)
+            except Exception:  # noqa: BLE001  (no symmetric memory on this system: library path)
+                self._fused = None
+        if self._fused is not None and self._fused.supports(x):
+            from unirl_b200.parallel.fused_collectives import _FusedExchange
+
+            return _FusedExchange.apply(x, self._fused, mode)
+        return (_SeqToHead if mode == 0 else _HeadToSeq).apply(x.contiguous(), self.comm)
 
     # ---- sequence sharding of the latent stream ---------------------------------------------------------------
     def shard_sequence(self, x: torch.Tensor) -> torch.Tensor:
@@ -109,14 +128,14 @@ class UlyssesContext:
         p, hp = self.size, q.shape[2] // self.size
         if q.shape[2] % p:
             raise ValueError(f"{q.shape[2]} heads do not split over {p} sequence-parallel ranks")
-        lat = [_SeqToHead.apply(t[:, n_text:].contiguous(), self.comm) for t in (q, k, v)]
+        lat = [self._exchange(t[:, n_text:], 0) for t in (q, k, v)]
         if n_text:
             txt = [t[:, :n_text, self.rank * hp : (self.rank + 1) * hp] for t in (q, k, v)]
             qq, kk, vv = (torch.cat([a, b], 1) for a, b in zip(txt, lat))
         else:
             qq, kk, vv = lat
         o = dense_attention(qq, kk, vv)
-        out_lat = _HeadToSeq.apply(o[:, n_text:].contiguous(), self.comm)
+        out_lat = self._exchange(o[:, n_text:], 1)
         if not n_text:
             return out_lat
         return torch.cat([_GatherHeads.apply(o[:, :n_text], self.comm), out_lat], 1)
