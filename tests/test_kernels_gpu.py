@@ -510,3 +510,28 @@ def test_linear_weight_grad_accumulates_into_fp32_buffer():
         _close(x.grad, ref_x, 0.05, 2e-2, "dX")
         w._wgrad_fused = False
         w.grad = None
+
+
+def test_linear_logprob_weight_grad_accumulates_into_fp32_buffer():
+    from unirl_b200.ops.logprob import linear_logprob, linear_logprob_reference
+
+    torch.manual_seed(22)
+    t, v, k = 300, 4096, 256
+    h = (torch.randn(t, k, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = torch.nn.Parameter((torch.randn(v, k, device="cuda") * 0.05).to(torch.bfloat16))
+    tgt = torch.randint(0, v, (t,), device="cuda")
+    g = torch.randn(t, device="cuda")
+    buf = torch.zeros(v, k, device="cuda", dtype=torch.float32)
+    w._wgrad_accum = lambda: buf
+    linear_logprob(h, w, tgt, 0.8).backward(g)
+    torch.cuda.synchronize()
+    assert getattr(w, "_wgrad_fused", False)
+    hr = h.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    linear_logprob_reference(hr, wr, tgt, 0.8).backward(g)
+    _close(buf, wr.grad, 2.5e-2, 5e-2, "fused lm_head dW")
+    _close(h.grad, hr.grad, 2e-2, 5e-2, "lm_head dH")
+    shared = torch.nn.Parameter(w.detach().clone())
+    shared._wgrad_accum, shared._wgrad_shared = (lambda: buf), True
+    linear_logprob(h, shared, tgt, 0.8).backward(g)
+    assert not getattr(shared, "_wgrad_fused", False) and shared.grad is not None  # a shared weight keeps the ordinary gradient

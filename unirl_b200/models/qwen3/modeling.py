@@ -250,6 +250,8 @@ class Qwen3Transformer(nn.Module):
         self.layers = nn.ModuleList(Qwen3DecoderLayer(cfg, i, self.tp, dtype, device) for i in range(cfg.num_hidden_layers))
         self.norm = nn.Parameter(torch.empty(cfg.hidden_size, dtype=dtype, device=device))
         self.lm_head = None if cfg.tie_word_embeddings else nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
+        if cfg.tie_word_embeddings:
+            self.embed_tokens._wgrad_shared = True  # gradient arrives from the embedding lookup AND the output projection
 
     # ---- init ---------------------------------------------------------------------------------------
     @torch.no_grad()

@@ -41,6 +41,11 @@ class _LinearLogprob(torch.autograd.Function):
         count_launch(2)
         ctx.save_for_backward(hidden, weight, tgt, lse)
         ctx.temperature = float(temperature)
+        # set by the sharded trainer on its parameters: returns the fp32 gradient-accumulator view of this weight
+        # (not for a weight that also receives gradient from another use, e.g. tied input embeddings: `_wgrad_shared`)
+        fuse = os.environ.get("UNIRL_B200_WGRAD_FUSION", "1") != "0" and not getattr(weight, "_wgrad_shared", False)
+        ctx.accum = getattr(weight, "_wgrad_accum", None) if fuse else None
+        ctx.param = weight if ctx.accum is not None else None
         return logp
 
     @staticmethod
@@ -49,7 +54,12 @@ class _LinearLogprob(torch.autograd.Function):
         hidden, weight, tgt, lse = ctx.saved_tensors
         g = g.float().contiguous()
         d_hidden = torch.empty_like(hidden)
-        d_weight = torch.zeros_like(weight, dtype=torch.float32) if ctx.needs_input_grad[1] else None
+        # dW accumulates in fp32 INSIDE the GEMM (C = C + dZᵀ·H with fp32 output): chunk after chunk, and -- when the trainer
+        # exposes its accumulator -- straight into that buffer, so no [V, H] gradient is converted, added or copied afterwards.
+        fused_into_trainer = ctx.needs_input_grad[1] and ctx.accum is not None
+        d_weight = None
+        if ctx.needs_input_grad[1]:
+            d_weight = ctx.accum() if fused_into_trainer else torch.zeros_like(weight, dtype=torch.float32)
         for s in range(0, hidden.shape[0], _BWD_CHUNK):
             e = min(s + _BWD_CHUNK, hidden.shape[0])
             h = hidden[s:e]
@@ -58,7 +68,10 @@ class _LinearLogprob(torch.autograd.Function):
             count_launch()
             torch.matmul(z, weight, out=d_hidden[s:e])
             if d_weight is not None:
-                d_weight.add_((z.t() @ h).float())
+                torch.addmm(d_weight, z.t(), h, out_dtype=torch.float32, out=d_weight)
+        if fused_into_trainer:
+            ctx.param._wgrad_fused = True
+            return d_hidden, torch.empty(weight.shape, dtype=weight.dtype, device=weight.device), None, None
         return d_hidden, (d_weight.to(weight.dtype) if d_weight is not None else None), None, None
 
 
