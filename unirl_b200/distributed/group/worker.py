@@ -51,6 +51,8 @@ class Worker:
         self.world_size = world_size
         self.device = torch.device(device) if device is not None else pick_device(worker_id)
         if self.device.type == "cuda":
+            if self.device.index is None:  # a bare "cuda" means the process's current device
+                self.device = torch.device("cuda", torch.cuda.current_device())
             torch.cuda.set_device(self.device)
         self.inline = inline
         self._roles: Dict[str, Remote] = {}
