@@ -20,7 +20,8 @@ def _close(a, b, atol, rtol, what=""):
     assert bool((err <= tol).all()), f"{what}: max err {err.max().item():.4e} (tol {tol.max().item():.3e}), mean err {err.mean().item():.3e}"
 
 
-@pytest.mark.parametrize("rows,dim,dtype", [(7, 256, torch.bfloat16), (33, 2560, torch.bfloat16), (5, 100, torch.float32)])
+@pytest.mark.parametrize("rows,dim,dtype", [(7, 256, torch.bfloat16), (33, 2560, torch.bfloat16), (5, 100, torch.float32), (2051, 2560, torch.bfloat16),
+                                            (1500, 1536, torch.bfloat16), (1100, 3584, torch.bfloat16)])
 def test_rmsnorm_fwd_bwd(rows, dim, dtype):
     from unirl_b200.ops.norm import rmsnorm, rmsnorm_reference
 

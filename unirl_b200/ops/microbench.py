@@ -169,6 +169,12 @@ def case_linear_sample(args: argparse.Namespace) -> None:
            "frac_of_peak": gb / t["best_ms"] * 1e3 / pk["hbm_gbs"], "peak": pk["kind"]})
 
 
+def require_ext_():
+    from unirl_b200.ops._ext import require_ext
+
+    return require_ext()
+
+
 def case_elementwise(args: argparse.Namespace) -> None:
     from unirl_b200.ops.activation import swiglu
     from unirl_b200.ops.norm import rmsnorm
@@ -181,6 +187,11 @@ def case_elementwise(args: argparse.Namespace) -> None:
     r = timer(lambda: rmsnorm(x, w, 1e-6))
     _emit({"case": "rmsnorm", "tokens": t_, "hidden": h, "best_ms": r["best_ms"], "gbs": 2 * x.numel() * 2 / r["best_ms"] / 1e6,
            "frac_of_peak": 2 * x.numel() * 2 / r["best_ms"] / 1e6 / pk["hbm_gbs"], "peak": pk["kind"]})
+    C = require_ext_()
+    gy, rstd = torch.randn_like(x), torch.rand(t_, device="cuda") + 0.5
+    r = timer(lambda: C.rmsnorm_bwd(gy, x, w, rstd))
+    _emit({"case": "rmsnorm_bwd", "tokens": t_, "hidden": h, "best_ms": r["best_ms"], "gbs": 3 * x.numel() * 2 / r["best_ms"] / 1e6,
+           "frac_of_peak": 3 * x.numel() * 2 / r["best_ms"] / 1e6 / pk["hbm_gbs"], "peak": pk["kind"]})
     inter = args.intermediate
     gu = torch.randn(t_, 2 * inter, device="cuda", dtype=torch.bfloat16)
     r = timer(lambda: swiglu(gu))
