@@ -57,16 +57,30 @@ def lora_apply(module: nn.Module, param_name: str, x: torch.Tensor, y: torch.Ten
     if not table or param_name not in table:
         return y
     active = getattr(module, "_lora_active", "default")
+    parts = []  # (row_offset, rows, delta) of every active adapter on this fused weight
     for target in table[param_name]:
         ad = module.lora[_key(target, active)] if _key(target, active) in module.lora else None
-        if ad is None:
-            continue
-        d = ad.delta(x)
-        if ad.row_offset == 0 and ad.rows == y.shape[-1]:
-            y = y + d
-        else:
-            y = torch.cat([y[..., : ad.row_offset], y[..., ad.row_offset : ad.row_offset + ad.rows] + d, y[..., ad.row_offset + ad.rows :]], -1)
-    return y
+        if ad is not None:
+            parts.append((ad.row_offset, ad.rows, ad.delta(x)))
+    if not parts:
+        return y
+    parts.sort(key=lambda p: p[0])
+    width = y.shape[-1]
+    if len(parts) == 1 and parts[0][0] == 0 and parts[0][1] == width:
+        return y + parts[0][2]
+    # Adapters on named row ranges of one fused weight (q | k | v, gate | up): assemble ONE full-width update and add it once,
+    # instead of re-assembling the whole output per adapter.  Ranges without an adapter get zeros.
+    cols, cursor = [], 0
+    for off, rows, d in parts:
+        if off < cursor:
+            raise ValueError(f"overlapping adapters on {param_name}")
+        if off > cursor:
+            cols.append(d.new_zeros(*d.shape[:-1], off - cursor))
+        cols.append(d)
+        cursor = off + rows
+    if cursor < width:
+        cols.append(parts[0][2].new_zeros(*parts[0][2].shape[:-1], width - cursor))
+    return y + torch.cat(cols, -1)
 
 
 def _hosts(model: nn.Module) -> Iterator[Tuple[str, nn.Module]]:
