@@ -536,3 +536,44 @@ def test_linear_logprob_weight_grad_accumulates_into_fp32_buffer():
     shared._wgrad_accum, shared._wgrad_shared = (lambda: buf), True
     linear_logprob(h, shared, tgt, 0.8).backward(g)
     assert not getattr(shared, "_wgrad_fused", False) and shared.grad is not None  # a shared weight keeps the ordinary gradient
+
+
+def test_sharded_trainer_gradients_with_and_without_gemm_accumulation():
+    """One backward pass of a small decoder under the flat sharded trainer (one rank): the fp32 gradient buffer filled by the
+    GEMMs directly must match the buffer filled by bf16 weight gradients + the hook's add, and the gradient norm with it."""
+    import unirl_b200.ops.linear as L
+    from unirl_b200.distributed.group.comm import Comm
+    from unirl_b200.models.qwen3.modeling import AttnMeta, Qwen3Config, Qwen3Transformer
+    from unirl_b200.ops.logprob import linear_logprob
+    from unirl_b200.parallel.flat_shard import FlatShardedModel
+
+    def run(fused: bool):
+        torch.manual_seed(5)
+        cfg = Qwen3Config.tiny(vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2, head_dim=64)
+        model = Qwen3Transformer(cfg, dtype=torch.bfloat16, device="cuda").init_weights(0)
+        sh = FlatShardedModel(model, Comm.world(), block_class_names=("Qwen3DecoderLayer",))
+        old = L._WGRAD_FUSION
+        L._WGRAD_FUSION = fused
+        try:
+            n = 768  # >= 512 rows: the projections run on the tcgen05 GEMM, whose backward owns the accumulation
+            tokens = torch.randint(0, cfg.vocab_size, (n,), device="cuda")
+            meta = AttnMeta(mode="train", positions=torch.arange(n, device="cuda") % 256, cu_seqlens=torch.tensor([0, 256, 512, 768], dtype=torch.int32, device="cuda"),
+                            max_seqlen=256, seq_lens_host=[256, 256, 256])
+            sh.zero_grad()
+            sh.set_grad_sync(True)
+            h = model(tokens, meta)
+            (linear_logprob(h, model.output_weight, torch.roll(tokens, -1), 1.0).mean() * -1.0).backward()
+            sh.finish_grad_sync()
+            norm = float(sh.grad_norm())
+            grads = torch.cat([g.main_grad.detach().float().reshape(-1).clone() for g in sh.groups if g.main_grad is not None])
+            fused_flags = [getattr(p, "_wgrad_accum", None) is not None for p in model.parameters()]
+        finally:
+            L._WGRAD_FUSION = old
+        return norm, grads, any(fused_flags)
+
+    n1, g1, has_accum = run(True)
+    n0, g0, _ = run(False)
+    assert has_accum, "the trainer did not expose its accumulators"
+    assert abs(n1 - n0) <= 2e-2 * max(n0, 1e-6), (n1, n0)
+    denom = float(g0.abs().max())
+    assert float((g1 - g0).abs().max()) <= 2e-2 * denom, (float((g1 - g0).abs().max()), denom)
