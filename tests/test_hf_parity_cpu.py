@@ -77,3 +77,44 @@ def test_qwen25_vl_matches_transformers():
     back = model.hf_state_dict()
     for k, v in hf.state_dict().items():
         assert k in back and torch.equal(back[k].reshape(v.shape), v), k
+
+
+def test_bundles_load_checkpoint_directories(tmp_path):
+    """``config.json`` + ``*.safetensors`` written by the Hugging Face classes load through the bundles' public constructors."""
+    import json
+
+    from safetensors.torch import save_file
+
+    if not (hasattr(transformers, "Qwen3ForCausalLM") and hasattr(transformers, "Qwen2_5_VLForConditionalGeneration")):
+        pytest.skip("transformers build without the Qwen model classes")
+    from unirl_b200.models.qwen3.bundle import Qwen3Bundle
+    from unirl_b200.models.qwen3.config import Qwen3PipelineConfig
+    from unirl_b200.models.qwen_vl.bundle import QwenVLBundle
+    from unirl_b200.models.qwen_vl.config import QwenVLPipelineConfig
+
+    torch.manual_seed(1)
+    hc = transformers.Qwen3Config(vocab_size=320, hidden_size=64, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                  head_dim=32, max_position_embeddings=256, rope_theta=10000.0, tie_word_embeddings=False)
+    hf = transformers.Qwen3ForCausalLM(hc).float()
+    d = tmp_path / "qwen3"
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(d / "model.safetensors"))
+    (d / "config.json").write_text(json.dumps(hc.to_dict()))
+    b = Qwen3Bundle.from_config(Qwen3PipelineConfig(pretrained_model_ckpt_path=str(d), model_precision="fp32", device="cpu"))
+    assert b.model_config.rope_theta == 10000.0
+    assert torch.equal(b.transformer.embed_tokens.detach(), hf.state_dict()["model.embed_tokens.weight"])
+
+    vc = transformers.Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=512, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}, rope_theta=10000.0, tie_word_embeddings=False),
+        vision_config=dict(depth=2, hidden_size=32, num_heads=2, intermediate_size=48, patch_size=4, temporal_patch_size=2, spatial_merge_size=2, in_channels=3,
+                           out_hidden_size=64, window_size=16, fullatt_block_indexes=[1], tokens_per_second=1),
+        image_token_id=5, video_token_id=6, vision_start_token_id=4)
+    vl = transformers.Qwen2_5_VLForConditionalGeneration(vc).float()
+    d2 = tmp_path / "qwen_vl"
+    d2.mkdir()
+    save_file({k: v.contiguous() for k, v in vl.state_dict().items()}, str(d2 / "model.safetensors"))
+    (d2 / "config.json").write_text(json.dumps(vc.to_dict()))
+    vb = QwenVLBundle.from_config(QwenVLPipelineConfig(pretrained_model_ckpt_path=str(d2), model_precision="fp32", device="cpu"))
+    assert vb.model_config.vision.depth == 2 and vb.model_config.mrope_section == (2, 3, 3)
+    assert torch.equal(vb.transformer.visual.merge_fc2.detach(), vl.state_dict()["model.visual.merger.mlp.2.weight"])
