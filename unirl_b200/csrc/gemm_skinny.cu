@@ -79,14 +79,7 @@ __device__ __forceinline__ void report(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-// TMEM -> registers: this warp's 32 lanes x 8 consecutive fp32 columns.
-__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, float* r) {
-  uint32_t* u = reinterpret_cast<uint32_t*>(r);
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7])
-               : "r"(taddr)
-               : "memory");
-}
+// TMEM -> registers: this warp's 32 lanes x 16 consecutive fp32 columns.
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, float* r) {
   uint32_t* u = reinterpret_cast<uint32_t*>(r);
   asm volatile(
@@ -98,10 +91,6 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, float* r) {
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
-
-struct alignas(8) Pack4 {
-  __nv_bfloat162 h[2];
-};
 
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
