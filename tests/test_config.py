@@ -68,6 +68,11 @@ def test_recipe_validators_flag_cross_component_mistakes():
         validate_recipe(compose("diffusion/tiny_sd3_flowgrpo_cpu", overrides=["sampling.guidance_scale=5.0"]))
     with pytest.raises(ConfigValidationError, match="sde_indices"):
         validate_recipe(compose("diffusion/tiny_sd3_flowgrpo_cpu", overrides=["sampling.sde_indices=[0, 9]"]))
+    with pytest.raises(ConfigValidationError, match="not executed"):
+        validate_recipe(compose("ar/qwen3_4b_grpo_b200", overrides=["+train_parallel={cp: 2}"]))
+    with pytest.raises(ConfigValidationError, match="sp_size"):
+        validate_recipe(compose("diffusion/wan21_14b_dancegrpo_sp8_b200", overrides=["backend.fsdp_cfg.sp_size=4"]))
+    validate_recipe(compose("diffusion/wan21_14b_dancegrpo_sp8_b200", overrides=[]))
 
 
 def test_export_hf_full_and_lora(tmp_path):
