@@ -114,3 +114,21 @@ def test_native_diffusion_engine_own_weights_and_tensor_sync():
         assert abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-4
     finally:
         tr.shutdown()
+
+
+@pytest.mark.timeout(600)
+def test_secondary_benchmark_script_runs_on_cpu():
+    """``bench_diffusion.py`` (the Flow-DPPO samples/s benchmark) with the tiny preset: one JSON line with the agreed keys."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "bench_diffusion.py"), "--device", "cpu", "--preset", "tiny-sd3", "--prompts-per-gpu", "1",
+           "--samples-per-prompt", "4", "--micro-batch", "4", "--resolution", "64", "--inference-steps", "4", "--steps", "1", "--warmup", "1",
+           "reward.backend.in_channels=4", "+reward.backend.width=8", "backend.fsdp_cfg.activation_checkpointing=false"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=500, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    row = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert row["metric"] == "flowdppo_samples_per_s" and row["value"] > 0 and row["config"]["samples_per_prompt"] == 4 and row["steps"] == 1
