@@ -25,6 +25,8 @@ import sys
 import threading
 import time
 
+_T_START = time.time()  # the wall budget counts from here (or from the launcher's start, see _job_start)
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
@@ -44,6 +46,9 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--rollout-tp", type=int, default=0, help="0 = 2 when gpus >= 2 else 1")
     ap.add_argument("--algorithm", default="grpo", choices=["grpo", "drpo"])
+    ap.add_argument("--budget-s", type=float, default=float(os.environ.get("UNIRL_B200_BENCH_BUDGET_S", "780")),
+                    help="wall-clock budget of the whole run in seconds (launcher start to exit); warm-up and timed steps are capped to fit, "
+                         "the work inside a step never shrinks; 0 = no cap")
     ap.add_argument("--ckpt-layers", type=int, default=-1, help="recompute only the first N decoder blocks in backward (-1 = recipe default)")
     return ap.parse_args()
 
@@ -67,6 +72,62 @@ def reference_arm(args) -> None:
     if why is None:
         why = "reference AR recipes require an SGLang/vLLM rollout server, which is not installable offline"
     print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+def _job_start() -> float:
+    """Start of the job on the wall clock: the launcher's creation time when this rank was spawned by ``torch.distributed.run``
+    (its own start-up and rendezvous are part of what a caller's time limit sees), else the start of this script."""
+    try:
+        import psutil
+
+        parent = psutil.Process(os.getppid())
+        if any("torch.distributed.run" in a or a.endswith("torchrun") for a in parent.cmdline()):
+            return min(_T_START, parent.create_time())
+    except Exception:
+        pass
+    return _T_START
+
+
+class StepBudget:
+    """Caps the number of warm-up and timed steps so the run ends inside a wall budget.
+
+    Every rank measures its own step times; the decisions are taken on the slowest rank's numbers (MAX all-reduce), so all
+    ranks run the same number of steps.  At least ``min_warmup`` warm-up steps and one timed step always run."""
+
+    def __init__(self, budget_s: float, t_start: float, world: int, min_warmup: int = 3, teardown_s: float = 25.0):
+        self.budget_s, self.t_start, self.world, self.min_warmup, self.teardown_s = budget_s, t_start, world, min_warmup, teardown_s
+        self.step_s = 0.0
+
+    def observe(self, seconds: float) -> None:
+        self.step_s = seconds  # the latest step: the first one carries graph capture and allocator growth
+
+    def _agree(self, elapsed: float, step_s: float):
+        if self.world == 1:
+            return elapsed, step_s
+        import torch
+        import torch.distributed as dist
+
+        t = torch.tensor([elapsed, step_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]), float(t[1])
+
+    def steps_that_fit(self) -> int:
+        if self.budget_s <= 0:
+            return 1 << 30
+        elapsed, step_s = self._agree(time.time() - self.t_start, self.step_s)
+        left = self.budget_s - self.teardown_s - elapsed
+        return int(left // (step_s * 1.05)) if step_s > 0 else 1 << 30
+
+    def plan_warmup(self, done: int, requested: int, timed_requested: int) -> bool:
+        """True when another warm-up step should run."""
+        if done >= requested:
+            return False
+        if done < self.min_warmup:
+            return True
+        return self.steps_that_fit() - 1 >= min(timed_requested, 4)  # extra warm-up only while >= 4 timed steps still fit
+
+    def plan_timed(self, requested: int) -> int:
+        return max(1, min(requested, self.steps_that_fit()))
 
 
 class ClockSampler:
@@ -169,8 +230,15 @@ def main() -> None:
         return {"tokens": n_tok, "device_ms": dev_ms, "sync_ms": sync_ms, "loss": float(result.loss), "reward": reward, "h2d": h2d,
                 "d2h": n_tok * (8 + 4) + 8}
 
-    for i in range(args.warmup):
-        one_step(i)
+    budget = StepBudget(args.budget_s, _job_start(), world)
+    n_warm = 0
+    while budget.plan_warmup(n_warm, args.warmup, args.steps):
+        t_w = time.time()
+        one_step(n_warm)
+        torch.cuda.synchronize()
+        budget.observe(time.time() - t_w)
+        n_warm += 1
+    n_steps = budget.plan_timed(args.steps)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -179,7 +247,7 @@ def main() -> None:
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     t0 = time.perf_counter()
-    rows = [one_step(args.warmup + i) for i in range(args.steps)]
+    rows = [one_step(n_warm + i) for i in range(n_steps)]
     ev1.record()
     barrier()
     wall = time.perf_counter() - t0
@@ -193,23 +261,26 @@ def main() -> None:
     dev_ms, span_ms, wall_ms, sync_ms = t.tolist()
     tokens = sum(r["tokens"] for r in rows)
     if rank == 0:
-        out = {"metric": "rl_step_tokens_per_s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-               "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        out = {"metric": "rl_step_tokens_per_s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": n_steps,
+               "warmup": n_warm, "steps_requested": args.steps, "warmup_requested": args.warmup, "budget_s": args.budget_s,
+               "ms_per_step": dev_ms / n_steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                "dtype": "bf16", "data": "synthetic (uniform-random prompt token ids, random-init weights, token-hash reward)",
                "weight_sync_ms": sync_ms, "impl": "native",
                "config": {"model": "Qwen3-4B" if args.model == "qwen3-4b" else args.model, "algorithm": args.algorithm.upper(),
                           "global_batch": n_prompts * args.group_size, "prompts": n_prompts, "group_size": args.group_size,
                           "seq_len": f"prompt {args.prompt_min}-{args.prompt_max} + response <= {args.max_new_tokens}",
-                          "tokens_counted": "generated response tokens", "tokens_per_step": tokens // max(1, args.steps),
+                          "tokens_counted": "generated response tokens", "tokens_per_step": tokens // max(1, n_steps),
                           "micro_batch": args.micro_batch, "parallelism": f"dp{world} trainer (sharded optimizer), rollout tp{tp}",
                           "l2_policy": "inputs_exceed_l2 (8 GB of bf16 weights + KV cache streamed every decode step)"},
                "clocks": clocks,
                "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": rows[-1]["h2d"], "d2h_bytes_per_step": rows[-1]["d2h"],
-                       "ms_per_step": wall_ms / args.steps},
+                       "ms_per_step": wall_ms / n_steps},
                "gpu_launches": int(launches), "loss": rows[-1]["loss"], "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
-               "phases_device_ms_last_step": {k: round(v, 2) for k, v in rows[-1]["device_ms"].items()}, "device_span_ms_per_step": span_ms / args.steps}
+               "phases_device_ms_last_step": {k: round(v, 2) for k, v in rows[-1]["device_ms"].items()}, "device_span_ms_per_step": span_ms / n_steps}
         print(json.dumps(out))
     trainer.shutdown()
+    if world > 1 and dist.is_initialized():
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -253,3 +253,72 @@ def test_hsdp_four_ranks_match_flat_four_way_sharding():
     for k in flat[0][0]:
         torch.testing.assert_close(hs[0][0][k], flat[0][0][k], atol=2e-5, rtol=1e-4)  # reduction order differs (2-level vs flat)
         assert torch.equal(hs[0][0][k], hs[3][0][k])
+
+
+class _Routed(torch.nn.Module):
+    """Two 'experts' per block; a forward touches only the experts its ``route`` names, so the others get no gradient."""
+
+    def __init__(self, width=16, blocks=3):
+        super().__init__()
+        self.inp = torch.nn.Linear(width, width)
+        self.blocks = torch.nn.ModuleList(_RoutedBlock(width) for _ in range(blocks))
+        self.out = torch.nn.Linear(width, 1)
+
+    def forward(self, x, route):
+        x = self.inp(x)
+        for b, r in zip(self.blocks, route):
+            x = b(x, r)
+        return self.out(x).pow(2).mean()
+
+
+class _RoutedBlock(torch.nn.Module):
+    def __init__(self, width):
+        super().__init__()
+        self.experts = torch.nn.ModuleList(torch.nn.Linear(width, width) for _ in range(2))
+
+    def forward(self, x, r):
+        return x + sum(torch.tanh(self.experts[e](x)) for e in r)
+
+
+_ROUTES = {0: [(0,), (0, 1), (1,)], 1: [(1,), (), (0, 1)]}  # rank 1 gives the middle block no gradient at all
+
+
+def _routed_grads(rank, world, variant):
+    from unirl_b200.distributed.group.comm import Comm
+    from unirl_b200.parallel.flat_shard import FlatShardedModel
+
+    torch.manual_seed(0)
+    model = _Routed().float()
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(4, 16, generator=g) for _ in range(2)]
+    sh = FlatShardedModel(model, Comm.world() if world > 1 else None, block_class_names=("_RoutedBlock",), low_dtype=torch.float32,
+                          reshard_after_forward=variant == "zero3")
+    sh.zero_grad()
+    sh.set_grad_sync(True)
+    if world == 1:
+        (sum(model(xs[r], _ROUTES[r]) for r in range(2)) / 2).backward()
+    elif not (variant == "skip" and rank == 1):
+        model(xs[rank], _ROUTES[rank]).backward()
+    sh.finish_grad_sync()
+    out = {}
+    for gr in sh.groups:
+        out[gr.name] = (gr.rank, gr.grad_shard.detach().clone() if gr.grad_shard is not None else None)
+    return out, float(sh.grad_norm())
+
+
+def test_reduce_order_does_not_depend_on_which_parameters_got_gradients():
+    """Ranks route tokens to different experts, so different parameters receive gradients on each rank (one block gets none
+    on rank 1).  Every group must still be reduced against the SAME group of the peer: the sharded gradient equals the
+    single-process gradient of the averaged loss."""
+    ref, ref_norm = run_ranks(_routed_grads, 1, "zero2")[0]
+    for variant in ("zero2", "zero3"):
+        res = run_ranks(_routed_grads, 2, variant)
+        assert abs(res[0][1] - ref_norm) < 1e-5 and abs(res[1][1] - ref_norm) < 1e-5
+        for name, (_, full) in ref.items():
+            parts = [res[r][0][name][1] for r in range(2)]
+            torch.testing.assert_close(torch.cat(parts)[: full.numel()], full[: sum(p.numel() for p in parts)], atol=1e-6, rtol=1e-5)
+
+
+def test_rank_without_backward_still_joins_the_reductions():
+    res = run_ranks(_routed_grads, 2, "skip")
+    assert res[0][1] == res[1][1] and res[0][1] > 0

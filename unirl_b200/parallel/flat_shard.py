@@ -14,11 +14,12 @@ Two residency modes:
   optimizer step every rank republishes its updated bf16 shard (one all-gather per step — or, on
   the fused path, the AdamW kernel stores its shard straight into every peer's replica).
 * ``reshard_after_forward=True`` (ZeRO-3): only the local shard is resident between uses; groups
-  are gathered (with prefetch on a side stream) around their forward/backward.
+  are gathered around their forward/backward (the next block's gather is prefetched on a side stream).
 
 Gradient path: per-parameter post-accumulate hooks fold the bf16 autograd gradient into the fp32
 ``main_grad`` view; when the last micro-batch finishes a group, its reduce-scatter is launched on the
-communication stream (overlapping the rest of backward); the optimizer step then runs one fused
+communication stream (overlapping the rest of backward) — in a fixed group order that is the same on every
+rank, whichever parameters received gradients there; the optimizer step then runs one fused
 AdamW kernel per group over the flat shard with the clip coefficient read from a device scalar.
 
 The collectives go through a small ``ShardComm`` strategy object so the NCCL implementation (the
@@ -136,10 +137,12 @@ class FlatGroup:
         self.module: Optional[nn.Module] = None  # the block whose forward / backward brackets the gather (ZeRO-3)
         self.shard_resident: Optional[torch.Tensor] = None  # ZeRO-3: this rank's bf16 shard while the replica storage is released
         self._gathered = True
+        self._fetch: Any = None  # a gather in flight: True (issued inline) or the event recorded on the prefetch stream
 
     # ---- ZeRO-3 residency ---------------------------------------------------------------------------
     def release_replica(self) -> None:
         """Keep only this rank's shard; the replica's storage is handed back to the allocator (views stay valid objects)."""
+        self.join_fetch()
         if not self._gathered:
             return
         if self.shard_resident is None:
@@ -149,12 +152,32 @@ class FlatGroup:
         self.flat_param.untyped_storage().resize_(0)
         self._gathered = False
 
-    def restore_replica(self, gather: Callable[[torch.Tensor, torch.Tensor], None]) -> None:
-        if self._gathered:
+    def start_fetch(self, gather: Callable[[torch.Tensor, torch.Tensor], None], stream: Any = None) -> None:
+        """Begin rebuilding the replica from the shards: on ``stream`` when given (prefetch, the caller's stream goes on), else inline."""
+        if self._gathered or self._fetch is not None:
             return
         self.flat_param.untyped_storage().resize_(self.padded * self.flat_param.element_size())
-        gather(self.flat_param, self.shard_resident)
+        if stream is None:
+            gather(self.flat_param, self.shard_resident)
+            self._fetch = True
+        else:
+            stream.wait_stream(torch.cuda.current_stream())  # the storage was just handed out in the caller's stream order
+            with torch.cuda.stream(stream):
+                gather(self.flat_param, self.shard_resident)
+            self._fetch = stream.record_event()
+
+    def join_fetch(self) -> None:
+        """Make a fetch in flight visible to the current stream."""
+        if self._fetch is None:
+            return
+        if self._fetch is not True:
+            torch.cuda.current_stream().wait_event(self._fetch)
+        self._fetch = None
         self._gathered = True
+
+    def restore_replica(self, gather: Callable[[torch.Tensor, torch.Tensor], None]) -> None:
+        self.start_fetch(gather)
+        self.join_fetch()
 
     @staticmethod
     def padded_numel(named_params: Sequence[Tuple[str, nn.Parameter]], world: int) -> int:
@@ -211,6 +234,9 @@ class FlatShardedModel:
         self._sync_enabled = True
         self._norm_sq: Optional[torch.Tensor] = None
         self._comm_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" and self.world > 1 else None
+        self._reduce_on_ready = True  # ZeRO-2: a group is reduced as soon as its hooks have fired and its turn has come
+        self._schedule: Optional[List[FlatGroup]] = None
+        self._cursor = 0
         self._build_groups(block_class_names, root_wrap, low_dtype, master_dtype, trainable_only)
         self._install_hooks()
         if self.reshard_after_forward and self.world > 1:
@@ -285,16 +311,54 @@ class FlatShardedModel:
         self.comm.all_gather_into(out, shard)
 
     def _install_zero3_hooks(self) -> None:
-        """Block groups release their replica after forward and after backward and gather it back right before either.  The root
-        group (embeddings, final norm, head) stays resident: it is used at both ends of every pass."""
+        """Block groups release their replica after forward and after backward and gather it back before either; while block i
+        computes, the gather of the block that runs next (i+1 in forward, i-1 in backward) is already in flight on a side stream.
+        The root group (embeddings, final norm, head) stays resident: it is used at both ends of every pass.
+
+        Every collective of this mode is issued from a module hook, so its position in the sequence of collectives does not depend
+        on which parameters received gradients: gathers at block entry, and the reduce-scatter of every block after block i
+        when block i's backward begins (the rest at ``finish_grad_sync``).  All ranks must run the same micro-batches."""
         if getattr(self.shard_comm, "persistent_grads", False):
             raise ValueError("reshard_after_forward=True needs the library collectives (replica storage is released between uses)")
-        for g in self.groups:
-            if g.module is None or g.module is self.module:
-                continue
-            g._hooks.append(g.module.register_forward_pre_hook(lambda _m, _a, g=g: g.restore_replica(self._gather_into)))
-            g._hooks.append(g.module.register_forward_hook(lambda _m, _a, _o, g=g: g.release_replica()))
-            g._hooks.append(g.module.register_full_backward_pre_hook(lambda _m, _go, g=g: g.restore_replica(self._gather_into)))
+        self._z3_blocks = [g for g in self.groups if g.module is not None and g.module is not self.module]
+        self._z3_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        self._z3_in_backward = False
+        self._reduce_on_ready = False
+        for i, g in enumerate(self._z3_blocks):
+            g._hooks.append(g.module.register_forward_pre_hook(lambda _m, _a, i=i: self._z3_forward_pre(i)))
+            g._hooks.append(g.module.register_forward_hook(lambda _m, _a, _o, i=i: self._z3_forward_post(i)))
+            g._hooks.append(g.module.register_full_backward_pre_hook(lambda _m, _go, i=i: self._z3_backward_pre(i)))
+            g.release_replica()
+
+    def _z3_enter(self, i: int, step: int) -> None:
+        blocks = self._z3_blocks
+        blocks[i].start_fetch(self._gather_into)  # not prefetched (first block of a pass): gather in the compute stream
+        blocks[i].join_fetch()
+        j = i + step
+        if step and 0 <= j < len(blocks):
+            blocks[j].start_fetch(self._gather_into, self._z3_stream)
+
+    def _z3_forward_pre(self, i: int) -> None:
+        # inside backward this is the recomputation of a checkpointed block: its backward-pre hook already fetched it and its successor
+        self._z3_enter(i, 0 if self._z3_in_backward else 1)
+
+    def _z3_forward_post(self, i: int) -> None:
+        if not self._z3_in_backward:  # a recomputed block is about to run its backward: keep it
+            self._z3_blocks[i].release_replica()
+
+    def _z3_backward_pre(self, i: int) -> None:
+        if not self._z3_in_backward:
+            self._z3_in_backward = True
+            torch.autograd.Variable._execution_engine.queue_callback(self._z3_backward_done)
+        self._z3_enter(i, -1)
+        if self._sync_enabled and self.world > 1:
+            self._drain_schedule(force=True, before=self._z3_blocks[i])
+        for g in self._z3_blocks[i + 1:]:  # blocks whose backward is complete
+            g.release_replica()
+
+    def _z3_backward_done(self) -> None:
+        self._z3_in_backward = False
+        for g in self._z3_blocks:
             g.release_replica()
 
     def gather_all(self) -> None:
@@ -321,9 +385,9 @@ class FlatShardedModel:
             if self._sync_enabled and self.world > 1:
                 g._pending -= 1
                 if g._pending == 0:
-                    self._launch_reduce(g)
-                    if self.reshard_after_forward and g.module is not None and g.module is not self.module:
-                        g.release_replica()  # this block's backward is complete
+                    g._ready = True
+                    if self._reduce_on_ready:
+                        self._drain_schedule()
 
         return hook
 
@@ -344,6 +408,29 @@ class FlatShardedModel:
             for g in self.groups:
                 g._pending = sum(1 for s in g.slots if s.param.requires_grad)
                 g._reduced = False
+                g._ready = False
+            # Reductions are issued in ONE order on every rank: last block first (the order backward completes them), root
+            # group last.  A group whose hooks have all fired waits until every group ahead of it in this order has been
+            # issued; whatever is left (parameters that got no gradient on this rank: experts without tokens, a skipped
+            # micro-batch) is issued in the same order by ``finish_grad_sync``.  The n-th collective of a step therefore
+            # pairs the same group on all ranks no matter which parameters received gradients where.
+            self._schedule = [g for g in reversed(self.groups) if g.trainable]
+            self._cursor = 0
+
+    def _drain_schedule(self, force: bool = False, before: Optional[FlatGroup] = None) -> None:
+        """Issue the reductions of all groups at the head of the schedule that are ready (``force``: ready or not), stopping
+        in front of ``before`` when given."""
+        sched = self._schedule
+        if sched is None:
+            return
+        while self._cursor < len(sched):
+            g = sched[self._cursor]
+            if g is before or not (force or getattr(g, "_ready", False)):
+                break
+            if not getattr(g, "_reduced", False):
+                g.ensure_grad_buffers()
+                self._launch_reduce(g)
+            self._cursor += 1
 
     def _launch_reduce(self, g: FlatGroup) -> None:
         if g.expert_local:  # the gradient already sums over every rank's tokens: match the rank-averaged objective
@@ -369,10 +456,9 @@ class FlatShardedModel:
     def finish_grad_sync(self) -> None:
         """Reduce any group whose hooks did not all fire (unused params) and join the comm stream."""
         if self.world > 1:
-            for g in self.groups:
-                if g.trainable and not getattr(g, "_reduced", False):
-                    g.ensure_grad_buffers()
-                    self._launch_reduce(g)
+            if self._schedule is None:
+                self.set_grad_sync(True)
+            self._drain_schedule(force=True)
             if self._comm_stream is not None:
                 torch.cuda.current_stream().wait_stream(self._comm_stream)
 
@@ -429,9 +515,20 @@ class FlatShardedModel:
             g.master.copy_(g.param_shard.to(g.master_dtype))
 
     def optimizer_state_dict(self) -> Dict[str, Any]:
-        """Full (gathered) optimizer state keyed by parameter name — checkpoint-format compatible with AdamW."""
+        """Full (gathered) optimizer state keyed by parameter NAME, each entry ``{master, exp_avg, exp_avg_sq}`` — the checkpoint
+        key ``optimizer_state_dict`` is the reference's, the layout under it is this runtime's (a ``torch.optim.AdamW`` state dict
+        is keyed by integer index and has no fp32 master).  Parameters owned by one expert-parallel rank are not gathered: every
+        rank's copy is kept under ``<name>#ep<rank>``."""
         out: Dict[str, Any] = {}
         for g in self.groups:
+            if g.expert_local:
+                mine = {s.name: {k: getattr(g, k).float()[s.offset : s.offset + s.numel].view(s.shape).cpu().clone()
+                                 for k in ("master", "exp_avg", "exp_avg_sq")} for s in g.slots}
+                per_rank = self.comm.all_gather_object(mine) if self.comm.active else [mine]
+                for r, d in enumerate(per_rank):
+                    for name, st in d.items():
+                        out[f"{name}#ep{r}"] = st
+                continue
             full = {}
             for key in ("master", "exp_avg", "exp_avg_sq"):
                 t = getattr(g, key).float()
@@ -441,16 +538,26 @@ class FlatShardedModel:
         return out
 
     def load_optimizer_state_dict(self, sd: Dict[str, Any]) -> None:
+        import logging
+
+        matched = 0
         for g in self.groups:
             lo, hi = g.shard_range()
+            suffix = f"#ep{self.rank}" if g.expert_local else ""
             for key in ("master", "exp_avg", "exp_avg_sq"):
                 full = torch.zeros(g.padded, dtype=torch.float32)
                 for s in g.slots:
-                    if s.name in sd and key in sd[s.name]:
-                        full[s.offset : s.offset + s.numel] = sd[s.name][key].reshape(-1).float()
+                    entry = sd.get(s.name + suffix)
+                    if isinstance(entry, dict) and key in entry:
+                        full[s.offset : s.offset + s.numel] = entry[key].reshape(-1).float()
+                        matched += 1
                     elif key == "master":
                         full[s.offset : s.offset + s.numel] = s.param.data.reshape(-1).float().cpu()
                 getattr(g, key).copy_(full[lo:hi].to(getattr(g, key).dtype))
+        if sd and not matched:
+            logging.getLogger(__name__).warning(
+                "load_optimizer_state_dict: none of the %d entries matches a parameter name of this model (an index-keyed "
+                "torch.optim state dict?); moments start at zero and the master weights come from the loaded parameters", len(sd))
 
     def offload(self) -> None:
         """Move optimizer shards to pinned host memory (colocated rollout needs the HBM)."""

@@ -155,6 +155,15 @@ class FSDPBackend(Remote):
     def current_lr(self) -> float:
         return self.scheduler.lr
 
+    def any_rank(self, flag: bool) -> bool:
+        """``flag`` OR-ed over the trainer's ranks: whether to take an optimizer step is one decision for the whole group (a rank
+        whose micro-batches were all empty still joins the reductions with zero gradients)."""
+        if not self.comm.active:
+            return bool(flag)
+        t = torch.tensor([1.0 if flag else 0.0], device=self.sharded.device)
+        self.comm.all_reduce(t, op="max")
+        return bool(t.item() > 0)
+
     def optimizer_step(self, *, max_grad_norm: float) -> float:
         """Clip by global norm, skip on a non-finite norm (identical verdict on every rank), step, schedule, EMA."""
         sh, oc = self.sharded, self.optimizer_cfg

@@ -133,6 +133,8 @@ class TrainStack(Remote):
             micros.append(self.algorithm.compute_loss_and_backward(conditions=mt.conditions, segment=mt.segment, advantages=mt.advantages,
                                                                    training_progress=training_progress, loss_scale=scale))
         has_bwd = any(m.has_backward for m in micros)
+        if hasattr(be, "any_rank"):
+            has_bwd = be.any_rank(has_bwd)
         if has_bwd:
             grad_norm = float(be.optimizer_step(max_grad_norm=self.max_grad_norm))
         else:

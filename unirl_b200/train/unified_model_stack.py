@@ -61,6 +61,8 @@ class UnifiedModelTrainStack(Remote):
             if r.metrics:
                 metrics.append({f"{name}/{k}": v for k, v in r.metrics.items()})
         has_bwd = any(m.has_backward for m in micros)
+        if hasattr(be, "any_rank"):
+            has_bwd = be.any_rank(has_bwd)
         grad_norm = float(be.optimizer_step(max_grad_norm=self.max_grad_norm)) if has_bwd else 0.0
         be.on_rollout_end()
         return TrainStepResult(sum(m.loss for m in micros), grad_norm, float(be.current_lr), has_bwd, micros, aggregate_numeric_metrics(metrics))
