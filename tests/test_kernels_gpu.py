@@ -213,6 +213,68 @@ def test_gemm_tcgen05(m, n, k):
     _close(c2, ref + r.float(), 0.15, 2e-2, "gemm+residual")
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 520, 136), (1000, 2560, 6144), (2560, 9728, 1003), (72, 384, 128), (4096, 2560, 9728)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, True), (True, False), (False, False)])
+def test_gemm_tcgen05_operand_layouts(m, n, k, a_mn, b_mn):
+    """Every operand layout of the tcgen05 GEMM against an fp32 product: K-major / MN-major A and B (the layouts of the forward,
+    input-gradient and weight-gradient GEMMs), bf16 output, fp32 overwrite and fp32 accumulation."""
+    C = _C()
+    if (not a_mn and k % 8) or (not b_mn and k % 8) or (a_mn and m % 8):
+        pytest.skip("this layout needs 16-byte aligned rows")
+    torch.manual_seed(18)
+    a = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda") * 0.5).to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    c = C.gemm_bf16(a_in, b_in, a_mn, b_mn)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0, "a bounded wait expired inside the GEMM"
+    _close(c, ref, 0.2, 2e-2, "bf16 out")
+    acc = torch.full((m, n), 3.0, device="cuda")
+    C.gemm_bf16(a_in, b_in, a_mn, b_mn, acc, False)
+    _close(acc, ref, 0.05, 1e-2, "fp32 overwrite")
+    C.gemm_bf16(a_in, b_in, a_mn, b_mn, acc, True)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0
+    _close(acc, 2 * ref, 0.1, 1e-2, "fp32 accumulate")
+
+
+def test_gemm_tcgen05_strided_operands_and_output():
+    """Row-strided views (a column block of a wider matrix) as operands and as the fp32 accumulator."""
+    C = _C()
+    torch.manual_seed(19)
+    big_a = (torch.randn(700, 512, device="cuda") * 0.5).to(torch.bfloat16)
+    big_b = (torch.randn(700, 640, device="cuda") * 0.5).to(torch.bfloat16)
+    a, b = big_a[:, 128:384], big_b[:, 64:576]  # stored [K=700, M=256] and [K=700, N=512]
+    out = torch.zeros(256, 1024, device="cuda")
+    C.gemm_bf16(a, b, True, True, out[:, 256:768], True)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0
+    _close(out[:, 256:768], a.float().t() @ b.float(), 0.05, 1e-2, "strided dW")
+    assert float(out[:, :256].abs().max()) == 0 and float(out[:, 768:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("t,v,k,temp", [(100, 1000, 64, 1.0), (517, 4096, 256, 0.7)])
+def test_linear_dlogits_epilogue(t, v, k, temp):
+    C = _C()
+    torch.manual_seed(20)
+    h = (torch.randn(t, k, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(v, k, device="cuda") * 0.05).to(torch.bfloat16)
+    tgt = torch.randint(0, v, (t,), device="cuda", dtype=torch.int32)
+    g = torch.randn(t, device="cuda")
+    z = (h.float() @ w.float().t()) / temp
+    lse = torch.logsumexp(z, -1)
+    ref = (g / temp)[:, None] * (torch.nn.functional.one_hot(tgt.long(), v).float() - torch.softmax(z, -1))
+    dz = C.linear_dlogits(h, w, tgt, lse, g, temp, 0)
+    torch.cuda.synchronize()
+    assert C.gemm_status(True) == 0
+    _close(dz, ref, 2e-2, 2e-2, "dZ")
+    half = v // 2 // 8 * 8  # a vocabulary chunk that starts at a non-zero column
+    dz2 = C.linear_dlogits(h, w[half:], tgt, lse, g, temp, half)
+    _close(dz2, ref[:, half:], 2e-2, 2e-2, "dZ chunk")
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 6144, 2560), (128, 2560, 4096), (128, 19456, 2560), (77, 2560, 9728), (256, 2560, 4096), (130, 1096, 128)])
 def test_gemm_skinny_cluster_split_k(m, n, k):
     C = _C()

@@ -66,3 +66,25 @@ def test_noalloc_rejects_oversize_and_bad_shapes():
     assert lib.unirl_b200_paged_decode_attention_noalloc(p, p, p, p, p, p, 256, 64, 1, 128, 32, 2048, 65536, 1.0, None) == 3  # too large: refused before any launch
     assert lib.unirl_b200_paged_decode_attention_noalloc(p, p, p, p, p, p, 2, 8, 8, 96, 32, 4, 128, 1.0, None) == 1  # head_dim 96 unsupported
     torch.cuda.synchronize()
+
+
+def test_noalloc_call_after_setup_can_be_captured_and_replayed():
+    """setup() does everything that is per device (scratch address, kernel attributes), so a call made afterwards contains only
+    kernel launches: it is recorded into a CUDA graph on a side stream and replayed against fresh inputs."""
+    from unirl_b200.ops.attention import paged_decode_attention
+
+    lib = _lib()
+    assert lib.unirl_b200_decode_noalloc_setup() == 0
+    b, hq, hkv, d, page, max_len = 4, 16, 4, 128, 32, 500
+    q, kc, vc, bt, lens, max_pages = _case(b, hq, hkv, d, page, max_len, 7)
+    out = torch.zeros_like(q)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        rc = lib.unirl_b200_paged_decode_attention_noalloc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), lens.data_ptr(), out.data_ptr(), b, hq, hkv,
+                                                           d, page, max_pages, max_len, 1.0 / math.sqrt(d), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    q.copy_(torch.randn_like(q))  # the graph reads the same addresses: new contents, same launches
+    graph.replay()
+    torch.cuda.synchronize()
+    want = paged_decode_attention(q, kc, vc, bt, lens, 1.0 / math.sqrt(d), None, max_len)
+    torch.testing.assert_close(out.float(), want.float(), atol=2e-2, rtol=2e-2)

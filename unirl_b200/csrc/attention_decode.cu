@@ -333,6 +333,25 @@ int64_t decode_cascade_workspace_floats(int B, int Hq, int D, int num_splits) { 
 
 // Shared-prefix ("cascade") decode attention.  Groups of R consecutive sequences share their first pages: prefix_tables / prefix_lens
 // [B / R] describe the shared part, suffix_tables / suffix_lens [B] the rest.  R * (Hq / Hkv) must not exceed 16.
+// Opt-in dynamic shared memory of the four decode kernel instances on the CURRENT device.  Launchers call it on every launch (cheap
+// after the first time on a device); callers that are about to capture a stream call it once beforehand.
+int paged_decode_configure() {
+  static PerDeviceOnce once;
+  if (!once.claim()) return 0;
+  const size_t merge128 = (size_t)kDecWarps * 16 * (128 + 2) * sizeof(float), merge64 = (size_t)kDecWarps * 16 * (64 + 2) * sizeof(float);
+  const size_t n128 = (size_t)DecLayout<128>::kTotal > merge128 ? (size_t)DecLayout<128>::kTotal : merge128;
+  const size_t n64 = (size_t)DecLayout<64>::kTotal > merge64 ? (size_t)DecLayout<64>::kTotal : merge64;
+  if (cudaFuncSetAttribute(paged_decode_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)n128) != cudaSuccess ||
+      cudaFuncSetAttribute(paged_decode_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)n128) != cudaSuccess ||
+      cudaFuncSetAttribute(paged_decode_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)n64) != cudaSuccess ||
+      cudaFuncSetAttribute(paged_decode_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)n64) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 2;
+  }
+  once.done();
+  return 0;
+}
+
 int paged_decode_attention_cascade(const void* q, const void* kc, const void* vc, const int* prefix_tables, const int* prefix_lens, int max_pages_p,
                                    const int* suffix_tables, const int* suffix_lens, int max_pages_s, void* out, float* workspace, int B, int R, int Hq,
                                    int Hkv, int D, int page_size, int num_splits, float scale, cudaStream_t s) {
@@ -348,9 +367,9 @@ int paged_decode_attention_cascade(const void* q, const void* kc, const void* vc
   const size_t need = smem > merge_smem ? smem : merge_smem;
   const bool fast = page_size % kDecTile == 0;
   const float sl2 = scale * kLog2e;
+  if (paged_decode_configure() != 0) return 2;
 #define UB_CAS(DD, FF)                                                                                                                     \
   do {                                                                                                                                     \
-    if (cudaFuncSetAttribute(paged_decode_kernel<DD, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2; \
     launch_kernel(paged_decode_kernel<DD, FF>, grid, dim3(kDecWarps * 32), need, s, pdl_enabled(), (const bf16*)q, (const bf16*)kc, (const bf16*)vc, \
                   prefix_tables, prefix_lens, ws_o, ws_ml, Hq, Hkv, page_size, max_pages_p, num_splits, sl2, nullptr, nullptr, n_shared, R, suffix_tables, \
                   suffix_lens, max_pages_s);                                                                                               \
@@ -390,13 +409,9 @@ int paged_decode_attention(const void* q, const void* kc, const void* vc, const 
   const bool fast = page_size % kDecTile == 0;
   const float sl2 = scale * kLog2e;
   (void)status;
+  if (paged_decode_configure() != 0) return 2;
 #define UB_DEC(DD, FF)                                                                                                                     \
   do {                                                                                                                                     \
-    static bool cfg = false;                                                                                                               \
-    if (!cfg) {                                                                                                                            \
-      if (cudaFuncSetAttribute(paged_decode_kernel<DD, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess) return 2; \
-      cfg = true;                                                                                                                          \
-    }                                                                                                                                      \
     launch_kernel(paged_decode_kernel<DD, FF>, grid, dim3(kDecWarps * 32), need, s, pdl_enabled(), (const bf16*)q, (const bf16*)kc, (const bf16*)vc, \
                   block_tables, seq_lens, ws_o, ws_ml, Hq, Hkv, page_size, max_pages, num_splits, sl2, status,                             \
                   num_splits == 1 ? (bf16*)out : nullptr, 0, 1, nullptr, nullptr, 0);                                                      \

@@ -11,9 +11,14 @@
 //     or different host threads without ordering) race on it — serialise them on one stream or with events;
 //   * nothing in the array needs to start at zero: each split block writes its full partial (accumulator, max, sum)
 //     before the merge kernel of the same call reads it, so no clearing happens between calls;
-//   * the first call on each device resolves the array's device address (cudaGetSymbolAddress) and sets a kernel
-//     attribute; run unirl_b200_decode_noalloc_setup() or one warm-up call per device before capturing a stream.
+//   * the first call on each device resolves the array's device address (cudaGetSymbolAddress) and opts the decode
+//     kernels into their shared-memory size on that device; run unirl_b200_decode_noalloc_setup() (which does both) or
+//     one warm-up call per device before capturing a stream;
+//   * set-up state is kept per device and guarded by a mutex, so host threads may call in concurrently as far as the
+//     set-up is concerned (the shared array still needs the ordering described above).
 #include <cuda_runtime.h>
+
+#include <mutex>
 
 #include "noalloc.h"
 #include "ops.h"
@@ -25,10 +30,13 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) float g_decode_scratch[UNIRL_B200_NOALLOC_MAX_FLOATS];
 
 float* g_scratch_ptr[kMaxDevices] = {};  // per device: address of g_decode_scratch as seen by that device
+std::mutex g_setup_mutex;
 
 int current_scratch(float** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return UNIRL_B200_NOALLOC_SETUP_FAILED;
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
+  if (ub::paged_decode_configure() != 0) return UNIRL_B200_NOALLOC_SETUP_FAILED;
   if (g_scratch_ptr[dev] == nullptr) {
     float* p = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_scratch) != cudaSuccess || p == nullptr) {

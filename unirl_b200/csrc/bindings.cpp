@@ -6,6 +6,7 @@
 
 #include <limits>
 #include <map>
+#include <mutex>
 #include <tuple>
 
 #include "ops.h"
@@ -29,10 +30,17 @@ void chk(const Tensor& t, const char* name) {
 }
 const void* optr(const c10::optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
 
+// One device-side status word per GPU: kernels whose bounded waits run out record a code there and drain; the host reads it at
+// step boundaries (gemm_status).  The word lives on the device that launches the kernel.
 Tensor& gemm_status_tensor() {
-  static Tensor st;
-  if (!st.defined()) st = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA));
-  return st;
+  static std::mutex mu;
+  static std::map<int, Tensor> per_device;
+  const int dev = (int)c10::cuda::current_device();
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = per_device.find(dev);
+  if (it == per_device.end())
+    it = per_device.emplace(dev, torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev))).first;
+  return it->second;
 }
 
 // ---------------------------------------------------------------------------------------------- norms
@@ -164,6 +172,12 @@ void kv_cache_write(const Tensor& k, const Tensor& v, Tensor& kc, Tensor& vc, co
 std::vector<Tensor> policy_loss_fwd(const Tensor& n, const Tensor& o, const Tensor& a, const c10::optional<Tensor>& keep, int64_t kind, double p0, double p1) {
   chk(n, "new_logp"); chk(o, "old_logp"); chk(a, "advantages");
   TORCH_CHECK(n.scalar_type() == at::kFloat && o.scalar_type() == at::kFloat && a.scalar_type() == at::kFloat, "policy_loss: fp32 inputs expected");
+  TORCH_CHECK(o.numel() == n.numel() && a.numel() == n.numel(), "policy_loss: new_logp, old_logp and advantages must have the same number of elements (",
+              n.numel(), ", ", o.numel(), ", ", a.numel(), "); expand advantages to the token shape first");
+  TORCH_CHECK(o.device() == n.device() && a.device() == n.device(), "policy_loss: inputs on different devices");
+  if (keep.has_value() && keep->defined())
+    TORCH_CHECK(keep->is_cuda() && keep->is_contiguous() && keep->numel() == n.numel() && keep->element_size() == 1 && keep->device() == n.device(),
+                "policy_loss: keep mask must be a contiguous 1-byte tensor of the same size on the same device");
   c10::cuda::CUDAGuard g(n.device());
   auto loss = torch::empty_like(n), dloss = torch::empty_like(n);
   auto stats = torch::zeros({8}, n.options());
@@ -272,6 +286,40 @@ Tensor gemm_bf16_tn(const Tensor& a, const Tensor& b, const c10::optional<Tensor
   TORCH_CHECK(rc == 0, "gemm_bf16_tn: unsupported shape or launch failure (code ", rc, ") for M=", M, " N=", N, " K=", K);
   return c;
 }
+// C (+)= op(A)·op(B) on the tcgen05 kernel.  a_mn: `a` is stored [K, M] (e.g. dY for dW = dYᵀ·X); b_mn: `b` is stored [K, N] (e.g. W for
+// dX = dY·W).  Rows may be strided (stride(1) == 1).  `out`: bf16 [M, N] (overwritten) or fp32 [M, N] (C += with `accumulate`, else C =);
+// absent: a new bf16 tensor.
+Tensor gemm_bf16(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, c10::optional<Tensor> out, bool accumulate) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16: 2-D CUDA operands with unit inner stride");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.device() == b.device(), "gemm_bf16: bf16 operands on one device");
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm_bf16: contraction extents differ (", K, " vs ", Kb, ")");
+  c10::cuda::CUDAGuard g(a.device());
+  Tensor c = out.has_value() && out->defined() ? *out : torch::empty({M, N}, a.options());
+  TORCH_CHECK(c.is_cuda() && c.device() == a.device() && c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "gemm_bf16: out must be [M, N] on the operands' device");
+  const bool f32 = c.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || c.scalar_type() == at::kBFloat16, "gemm_bf16: out must be bf16 or fp32");
+  TORCH_CHECK(f32 || !accumulate, "gemm_bf16: accumulation needs an fp32 out");
+  const int rc = ub::gemm_bf16_general(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, (int)a.stride(0), (int)b.stride(0), (int)c.stride(0),
+                                       a_mn ? 1 : 0, b_mn ? 1 : 0, f32 ? 1 : 0, accumulate ? 1 : 0, gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16: unsupported shape / alignment or launch failure (code ", rc, ") for M=", M, " N=", N, " K=", K);
+  return c;
+}
+// dZ = g/T · (onehot(target) − softmax(h·Wᵀ/T)) for the vocabulary rows `w` (a row chunk starting at `col_offset`), bf16 [M, Vc].
+Tensor linear_dlogits(const Tensor& h, const Tensor& w, const Tensor& tgt, const Tensor& lse, const Tensor& gout, double temperature, int64_t col_offset) {
+  chk(h, "hidden"); chk(w, "weight"); chk(tgt, "targets"); chk(lse, "lse"); chk(gout, "grad");
+  TORCH_CHECK(h.dim() == 2 && w.dim() == 2 && h.size(1) == w.size(1) && h.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "linear_dlogits: bf16 [M,K] x [Vc,K]");
+  TORCH_CHECK(tgt.scalar_type() == at::kInt && lse.scalar_type() == at::kFloat && gout.scalar_type() == at::kFloat && tgt.numel() == h.size(0) &&
+              lse.numel() == h.size(0) && gout.numel() == h.size(0), "linear_dlogits: int32 targets, fp32 lse / grad, one per row");
+  c10::cuda::CUDAGuard g(h.device());
+  auto dz = torch::empty({h.size(0), w.size(0)}, h.options());
+  const int rc = ub::linear_dlogits(h.data_ptr(), w.data_ptr(), dz.data_ptr(), (int)h.size(0), (int)w.size(0), (int)h.size(1), (int)h.size(1), (int)w.size(1), (int)w.size(0),
+                                    tgt.data_ptr<int>(), lse.data_ptr<float>(), gout.data_ptr<float>(), (float)temperature, (int)col_offset,
+                                    gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "linear_dlogits: unsupported shape or launch failure (code ", rc, ")");
+  return dz;
+}
 // Decode-sized GEMM: one tile per CTA, K split over a thread-block cluster (see gemm_skinny.cu).  epilogue 0 / 1 (residual) / 2 (SwiGLU).
 Tensor gemm_bf16_tn_skinny(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& res, const c10::optional<Tensor>& out, int64_t epilogue) {
   chk(a, "a"); chk(b, "weight");
@@ -306,6 +354,8 @@ int64_t gemm_status(bool reset) {
   if (reset && v != 0) st.zero_();
   return v;
 }
+// Host-side write of the current device's status word (tests of the error path; no kernel is made to give up for them).
+void set_gemm_status(int64_t code) { gemm_status_tensor().fill_((int)code); }
 std::vector<Tensor> linear_logprob_fwd(const Tensor& h, const Tensor& w, const Tensor& tgt, double temperature) {
   chk(h, "hidden"); chk(w, "weight"); chk(tgt, "targets");
   TORCH_CHECK(h.dim() == 2 && w.dim() == 2 && h.size(1) == w.size(1) && tgt.scalar_type() == at::kInt && tgt.numel() == h.size(0), "linear_logprob: shapes");
@@ -351,6 +401,12 @@ Tensor paged_decode_attention(const Tensor& q, const Tensor& kc, const Tensor& v
   chk(q, "q"); chk(kc, "k_cache"); chk(vc, "v_cache"); chk(bt, "block_tables"); chk(sl, "seq_lens");
   TORCH_CHECK(q.dim() == 3 && kc.dim() == 4 && q.scalar_type() == at::kBFloat16 && kc.scalar_type() == at::kBFloat16, "decode attention: bf16 q [B,Hq,D], cache [P,Hkv,page,D]");
   TORCH_CHECK(bt.scalar_type() == at::kInt && sl.scalar_type() == at::kInt, "decode attention: int32 block_tables / seq_lens");
+  TORCH_CHECK(bt.dim() == 2 && bt.size(0) == q.size(0) && sl.numel() == q.size(0), "decode attention: block_tables [B, pages] and seq_lens [B] must match q's batch");
+  TORCH_CHECK(vc.sizes() == kc.sizes() && vc.scalar_type() == kc.scalar_type() && kc.size(3) == q.size(2), "decode attention: v_cache must have k_cache's shape and head_dim must match q");
+  TORCH_CHECK(kc.device() == q.device() && vc.device() == q.device() && bt.device() == q.device() && sl.device() == q.device(), "decode attention: tensors on different devices");
+  if (workspace.has_value() && workspace->defined())
+    TORCH_CHECK(workspace->is_cuda() && workspace->device() == q.device() && workspace->scalar_type() == at::kFloat && workspace->is_contiguous(),
+                "decode attention: workspace must be a contiguous float32 tensor on q's device");
   c10::cuda::CUDAGuard g(q.device());
   const int B = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)kc.size(1), page = (int)kc.size(2);
   const int kv_hint = max_kv_len > 0 ? (int)max_kv_len : (int)(bt.size(1) * page);
@@ -502,6 +558,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sde_replay_fwd", &sde_replay_fwd);
   m.def("sde_replay_bwd", &sde_replay_bwd);
   m.def("gemm_bf16_tn", &gemm_bf16_tn);
+  m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out") = py::none(),
+        py::arg("accumulate") = false);
+  m.def("linear_dlogits", &linear_dlogits);
   m.def("gemm_bf16_tn_skinny", &gemm_bf16_tn_skinny, py::arg("a"), py::arg("b"), py::arg("res") = py::none(), py::arg("out") = py::none(),
         py::arg("epilogue") = 0);
   m.def("gemm_skinny_plan", &gemm_skinny_plan);
@@ -511,6 +570,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }, py::arg("trace") = py::none(), py::arg("skip_a") = false);
   m.def("set_pdl", &ub::set_pdl);
   m.def("gemm_status", &gemm_status, py::arg("reset") = true);
+  m.def("set_gemm_status", &set_gemm_status);
+  m.def("per_device_first_use", [](std::vector<int> devices) {
+    // exercises the bookkeeping behind the per-device kernel-attribute caches: which calls in `devices` are first uses
+    unsigned char flags[ub::kMaxDevices] = {};
+    std::vector<bool> first;
+    for (int d : devices) first.push_back(ub::per_device_first_use(flags, ub::kMaxDevices, d));
+    return first;
+  });
   m.def("set_gemm_tile", &ub::set_gemm_tile);
   m.def("linear_logprob_fwd", &linear_logprob_fwd);
   m.def("linear_sample", &linear_sample);

@@ -6,6 +6,8 @@
 #pragma once
 
 #include <cuda_bf16.h>
+
+#include "ops.h"
 #include <cuda_runtime.h>
 #include <stdint.h>
 

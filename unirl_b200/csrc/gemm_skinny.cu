@@ -57,6 +57,14 @@ struct Layout {
   static_assert(kStageBytes % 1024 == 0 && (kBBytes / 2) % 1024 == 0, "swizzle atoms need 1024-byte aligned operand tiles");
 };
 
+// Diagnostics (per-CTA phase time stamps, an activation-load bypass that isolates weight streaming) are compiled in only with
+// -DUNIRL_B200_SKINNY_DIAG; in the product build the branches below fold away and set_gemm_skinny_debug() has no effect.
+#ifdef UNIRL_B200_SKINNY_DIAG
+constexpr bool kDiag = true;
+#else
+constexpr bool kDiag = false;
+#endif
+
 struct SkinnyParams {
   int M, N, K;   // N = output columns (SwiGLU: I, with B holding 2I rows)
   bf16* C;
@@ -68,7 +76,7 @@ struct SkinnyParams {
   int skip_a;                 // diagnostics: load the activation tile only for the first k-block (result is wrong; isolates weight streaming)
 };
 __device__ __forceinline__ void stamp(const SkinnyParams& p, int slot) {
-  if (p.trace) {
+  if (kDiag && p.trace) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     p.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + slot] = t;
@@ -153,21 +161,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       // the producer of the activations.  Under a programmatic launch this overlaps the pipeline fill with the predecessor.
       const int pre = num_kb < stages ? num_kb : stages;
       for (int j = 0; j < pre; ++j) {
-        const bool with_a = !(p.skip_a && j > 0);
+        const bool with_a = !(kDiag && p.skip_a && j > 0);
         mbar_expect_tx(full + j, with_a ? L::kStageBytes : L::kBBytes);
         load_b(kb_lo + j, j);
       }
       pdl_wait();
       for (int j = 0; j < pre; ++j)
-        if (!(p.skip_a && j > 0)) tma_load_2d(smem + j * L::kStageBytes, &tmA, (kb_lo + j) * BK, m0, full + j);
+        if (!(kDiag && p.skip_a && j > 0)) tma_load_2d(smem + j * L::kStageBytes, &tmA, (kb_lo + j) * BK, m0, full + j);
       for (int j = pre; j < num_kb; ++j) {
         const int stage = j % stages;
         if (!mbar_wait(empty + stage, ((j / stages) & 1) ^ 1)) {
           report(p.status, 121);
           break;
         }
-        mbar_expect_tx(full + stage, p.skip_a ? L::kBBytes : L::kStageBytes);
-        if (!p.skip_a) tma_load_2d(smem + stage * L::kStageBytes, &tmA, (kb_lo + j) * BK, m0, full + stage);
+        mbar_expect_tx(full + stage, (kDiag && p.skip_a) ? L::kBBytes : L::kStageBytes);
+        if (!(kDiag && p.skip_a)) tma_load_2d(smem + stage * L::kStageBytes, &tmA, (kb_lo + j) * BK, m0, full + stage);
         load_b(kb_lo + j, stage);
       }
       stamp(p, 1);
@@ -187,7 +195,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         tc_fence_after();
         const uint8_t* sA = smem + stage * L::kStageBytes;
-        const uint64_t da = make_desc_kmajor_sw128(p.skip_a ? smem : sA);
+        const uint64_t da = make_desc_kmajor_sw128((kDiag && p.skip_a) ? smem : sA);
         const uint64_t db = make_desc_kmajor_sw128(sA + L::kABytes);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k) umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
@@ -296,23 +304,16 @@ unsigned long long* g_trace = nullptr;  // diagnostics: set_gemm_skinny_debug
 int g_skip_a = 0;
 
 int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
+  return ub::num_sms();
 }
 
 template <int BN, bool SWIGLU>
 bool configure() {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce once;
+  if (once.claim()) {
     if (cudaFuncSetAttribute(gemm_skinny_kernel<BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<BN>::kTotal) != cudaSuccess) return false;
     if (cudaFuncSetAttribute(gemm_skinny_kernel<BN, SWIGLU>, cudaFuncAttributeNonPortableClusterSizeAllowed, 0) != cudaSuccess) cudaGetLastError();
-    configured = true;
+    once.done();
   }
   return true;
 }
@@ -418,8 +419,8 @@ int gemm_bf16_tn_skinny(const void* A, const void* B, void* C, const void* R, in
   gemm_skinny_plan(M, N, K, swiglu, &bn, &splits);
   SkinnyParams p{};
   p.M = M; p.N = N; p.K = K; p.C = static_cast<bf16*>(C); p.R = swiglu ? nullptr : static_cast<const bf16*>(R); p.ldc = ldc; p.up_row_offset = N; p.status = status;
-  p.trace = g_trace;
-  p.skip_a = g_skip_a;
+  p.trace = kDiag ? g_trace : nullptr;
+  p.skip_a = kDiag ? g_skip_a : 0;
   const int m_tiles = (M + BM - 1) / BM;
   const int out_cols = swiglu ? bn / 2 : bn;
   const int tiles = (N + out_cols - 1) / out_cols;

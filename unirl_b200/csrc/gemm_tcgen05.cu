@@ -1,5 +1,7 @@
-// Persistent warp-specialised bf16 GEMM for sm_100a:  C[M,N] = A[M,K] · B[N,K]ᵀ  (both operands K-major),
-// fp32 accumulation in TMEM, operands staged by TMA into 128-byte-swizzled shared memory.
+// Persistent warp-specialised bf16 GEMM for sm_100a:  C[M,N] = op(A) · op(B), fp32 accumulation in TMEM, operands staged by
+// TMA into 128-byte-swizzled shared memory.  Each operand is either K-major (contraction index contiguous in memory:
+// A [M,K], B [N,K]) or MN-major (A stored [K,M], B stored [K,N]), so the forward (Y = X·Wᵀ), the input gradient
+// (dX = dY·W: B MN-major) and the weight gradient (dW = dYᵀ·X: both MN-major) run on the same kernel without a transpose pass.
 //
 //   warp 0      TMA producer   (one lane): waits `empty[s]`, arms `full[s]` with the byte count, issues 2-3 tile loads
 //   warp 1      MMA issuer     (one lane): waits `full[s]`, issues 4 x tcgen05.mma (K = 16 each) per 64-wide k-block,
@@ -9,7 +11,9 @@
 //
 // Two TMEM accumulator buffers (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
 // Epilogues:  STORE (bf16 C) | RESIDUAL (C = acc + R) | SWIGLU (acc = [gate | up] -> silu(gate)·up) |
-//             LSE (per-row partial max / sum-exp / target logit / Gumbel-arg-max of acc/T; logits never leave the SM).
+//             LSE (per-row partial max / sum-exp / target logit / Gumbel-arg-max of acc/T; logits never leave the SM) |
+//             ACC_F32 (fp32 C += acc, or C = acc: weight gradients land in the trainer's fp32 accumulator) |
+//             DLOGITS (bf16 C = g[row]/T · (onehot(target) − exp(acc/T − lse[row])): the log-prob backward's dZ).
 //
 // Every mbarrier wait is bounded; on expiry the role records a code in `status[0]` and all roles drain out,
 // TMEM is released and the kernel returns.
@@ -50,6 +54,13 @@ struct GemmParams {
   const int64_t* step_tensor;
   int64_t step;
   int* status;            // [1] error word (0 = ok)
+  // ACC_F32 epilogue
+  float* Cf;              // [M, ldc] fp32
+  int accumulate;         // 1: C += acc, 0: C = acc
+  // DLOGITS epilogue (targets, inv_temp as above)
+  const float* lse;       // [M] log-sum-exp of the scaled logits
+  const float* gout;      // [M] upstream gradient of the token log-prob
+  int col_offset;         // global vocabulary index of column 0 of this launch (chunked vocabulary)
 };
 
 template <int BN>
@@ -81,7 +92,7 @@ __device__ __forceinline__ void report(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool AMN = false, bool BMN = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
                     const GemmParams p) {
@@ -143,8 +154,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           uint8_t* sA = smem + stage * L::kStageBytes;
           uint8_t* sB = sA + L::kABytes;
           mbar_expect_tx(full + stage, L::kStageBytes);
-          tma_load_2d(sA, &tmA, kb * BK, m0, full + stage);
-          if (EPI == kEpiSwiGLU) {
+          if (AMN) {  // A stored [K, M]: one [64 k] x [64 m] box per 64 rows of the tile
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sA + i * (BK * 128), &tmA, m0 + i * 64, kb * BK, full + stage);
+          } else {
+            tma_load_2d(sA, &tmA, kb * BK, m0, full + stage);
+          }
+          if (BMN) {  // B stored [K, N]
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sB + i * (BK * 128), &tmB, n_idx * BN + i * 64, kb * BK, full + stage);
+          } else if (EPI == kEpiSwiGLU) {
             const int n0 = n_idx * (BN / 2);
             tma_load_2d(sB, &tmB, kb * BK, n0, full + stage);
             tma_load_2d(sB + L::kBBytes / 2, &tmB, kb * BK, p.up_row_offset + n0, full + stage);
@@ -161,7 +180,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, AMN, BMN);
+      constexpr uint32_t kStepA = AMN ? (16 * 128) >> 4 : 32 >> 4;  // descriptor start-address advance per K = 16 (16-byte units)
+      constexpr uint32_t kStepB = BMN ? (16 * 128) >> 4 : 32 >> 4;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -182,10 +203,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           tc_fence_after();
           const uint8_t* sA = smem + stage * L::kStageBytes;
-          const uint64_t da = make_desc_kmajor_sw128(sA);
-          const uint64_t db = make_desc_kmajor_sw128(sA + L::kABytes);
+          const uint64_t da = AMN ? make_desc_mnmajor_sw128(sA, BK * 128) : make_desc_kmajor_sw128(sA);
+          const uint64_t db = BMN ? make_desc_mnmajor_sw128(sA + L::kABytes, BK * 128) : make_desc_kmajor_sw128(sA + L::kABytes);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) umma_bf16(d_addr, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / 16; ++k) umma_bf16(d_addr, da + kStepA * k, db + kStepB * k, idesc, (kb | k) != 0);
           umma_commit(empty + stage);
           if (++stage == kStages) {
             stage = 0;
@@ -214,12 +235,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(q * 32) << 16);
 
-      if (EPI == kEpiStore || EPI == kEpiResidual || EPI == kEpiSwiGLU) {
+      if (EPI == kEpiStore || EPI == kEpiResidual || EPI == kEpiSwiGLU || EPI == kEpiDLogits) {
         // Accumulator -> bf16 -> swizzled shared-memory box -> one TMA store per 32 x 64 box.  A thread owns one row
         // of the box (128 bytes = 8 chunks of 16 bytes); chunk j of row r lives at r * 128 + ((j ^ (r & 7)) << 4).
         constexpr int kOutCols = (EPI == kEpiSwiGLU) ? BN / 2 : BN;
         const int n0 = n_idx * kOutCols;
         uint8_t* warp_stage = store_smem + q * (2 * L::kStoreChunk);
+        float dl_lse = 0.f, dl_g = 0.f;
+        int dl_tgt = -1;
+        if (EPI == kEpiDLogits && row_ok) {
+          dl_lse = p.lse[row];
+          dl_g = p.gout[row] * p.inv_temp;
+          dl_tgt = p.targets[row] - p.col_offset - n0;  // column of the target inside this tile (or outside [0, BN))
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < kOutCols; c0 += 64) {
           if (n0 + c0 >= p.N) break;  // uniform over the warp: the rest of the tile is outside the matrix
@@ -239,6 +267,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             } else {
               tmem_ld_32x32(t_row + c0 + h * 32, acc);
               tmem_ld_wait();
+              if (EPI == kEpiDLogits) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const float pj = __expf(acc[j] * p.inv_temp - dl_lse);
+                  acc[j] = dl_g * ((c0 + h * 32 + j == dl_tgt ? 1.f : 0.f) - pj);
+                }
+              }
               if (EPI == kEpiResidual && row_ok) {
                 const bf16* rrow = p.R + static_cast<int64_t>(row) * p.ldc + n0 + c0 + h * 32;
 #pragma unroll
@@ -267,6 +302,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tma_store_commit();
           }
           ++store_ctr;
+        }
+      } else if (EPI == kEpiAccF32) {
+        // fp32 read-modify-write straight from the accumulator: a thread owns one row and moves 128 bytes per chunk.
+        const int n0 = n_idx * BN;
+        float* crow = p.Cf + static_cast<int64_t>(row) * p.ldc + n0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= p.N) break;
+          float acc[32];
+          tmem_ld_32x32(t_row + c0, acc);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (n0 + c0 + g * 4 < p.N) {  // N is a multiple of 4
+                float4* dst = reinterpret_cast<float4*>(crow + c0 + g * 4);
+                float4 v = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
+                if (p.accumulate) {
+                  const float4 o = *dst;
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *dst = v;
+              }
+            }
+          }
         }
       } else {  // kEpiLSE
         const int n0 = n_idx * BN;
@@ -420,32 +480,100 @@ bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int64_t rows, int6
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int num_sms() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+int num_sms() {
+  static int n[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  if (!n[dev]) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    n[dev] = v > 0 ? v : 148;
   }
-  return n;
-}
-
-template <int BN, int EPI>
-static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmParams& p, cudaStream_t s) {
-  using L = SmemLayout<BN>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return 2;
-    configured = true;
-  }
-  const int tiles = p.num_m_tiles * p.num_n_tiles;
-  const int grid = tiles < num_sms() ? tiles : num_sms();
-  gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, L::kTotal, s>>>(tmA, tmB, tmC, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+  return n[dev];
 }
 
 int g_force_bn = 0;  // tuning hook: 0 = heuristic, 128 / 256 = forced tile width
+
+template <int BN, int EPI, bool AMN = false, bool BMN = false>
+static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmParams& p, cudaStream_t s) {
+  using L = SmemLayout<BN>;
+  static PerDeviceOnce once;  // one per template instance
+  if (once.claim()) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, AMN, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return 2;
+    once.done();
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  gemm_tcgen05_kernel<BN, EPI, AMN, BMN><<<grid, kGemmThreads, L::kTotal, s>>>(tmA, tmB, tmC, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+// Row-major bf16 matrix [rows = contraction extent, cols = M or N extent] read as an MN-major operand: boxes of 64 rows x 64 columns.
+static bool make_tensor_map_mn(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+  return make_tensor_map_bf16(out, base, rows, cols, ld, BK);
+}
+
+// General form:  C[M,N] (+)= op(A)·op(B).
+//   a_mn = 0: A is [M,K] (lda >= K);  a_mn = 1: A is stored [K,M] (lda >= M)
+//   b_mn = 0: B is [N,K] (ldb >= K);  b_mn = 1: B is stored [K,N] (ldb >= N)
+//   out_f32 = 0: bf16 C;  out_f32 = 1: fp32 C, `accumulate` selects C += or C =
+// Returns 0 on success, 1 for an unsupported shape / alignment, 2-3 for launch failures.
+int gemm_bf16_general(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate,
+                      int* status, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return out_f32 && accumulate ? 0 : 1;
+  if ((N % 8) || (ldc % 8) || (lda % 8) || (ldb % 8) || (a_mn && (M % 8)) || (!a_mn && (K % 8)) || (!b_mn && (K % 8))) return 1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.status = status;
+  p.C = static_cast<bf16*>(C); p.Cf = static_cast<float*>(C); p.accumulate = accumulate;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  const bool wide = g_force_bn ? g_force_bn == 256 : (N >= 256 * 2 || N % 256 == 0);
+  const int BN = wide ? 256 : 128;
+  p.num_n_tiles = (N + BN - 1) / BN;
+  CUtensorMap tmA, tmB, tmC;
+  if (a_mn ? !make_tensor_map_mn(&tmA, A, K, M, lda) : !make_tensor_map_bf16(&tmA, A, M, K, lda, BM)) return 1;
+  if (b_mn ? !make_tensor_map_mn(&tmB, B, K, N, ldb) : !make_tensor_map_bf16(&tmB, B, N, K, ldb, BN)) return 1;
+  if (out_f32) {
+    tmC = tmA;  // unused
+  } else if (!make_tensor_map_bf16(&tmC, C, M, N, ldc, 32)) {
+    return 1;
+  }
+#define UB_GO(BNV, EPIV, AV, BV) return launch_variant<BNV, EPIV, AV, BV>(tmA, tmB, tmC, p, s)
+#define UB_LAYOUT(BNV, EPIV)                              \
+  do {                                                    \
+    if (a_mn && b_mn) UB_GO(BNV, EPIV, true, true);       \
+    if (a_mn) UB_GO(BNV, EPIV, true, false);              \
+    if (b_mn) UB_GO(BNV, EPIV, false, true);              \
+    UB_GO(BNV, EPIV, false, false);                       \
+  } while (0)
+  if (out_f32) {
+    if (wide) UB_LAYOUT(256, kEpiAccF32);
+    UB_LAYOUT(128, kEpiAccF32);
+  }
+  if (wide) UB_LAYOUT(256, kEpiStore);
+  UB_LAYOUT(128, kEpiStore);
+#undef UB_LAYOUT
+#undef UB_GO
+  return 1;
+}
+
+// dZ[M, Vc] = g/T · (onehot(target − col_offset) − exp(H·Wᵀ/T − lse)) for a chunk of Vc vocabulary rows of W: the logits are
+// recomputed on the tensor cores and turned into their gradient in the epilogue, so no pass over materialised logits is needed.
+int linear_dlogits(const void* H, const void* W, void* dZ, int M, int Vc, int K, int ldh, int ldw, int ldz, const int* targets, const float* lse,
+                   const float* gout, float temperature, int col_offset, int* status, cudaStream_t s) {
+  if (M <= 0 || Vc <= 0) return 0;
+  if ((K % 8) || (Vc % 8) || (ldz % 8)) return 1;
+  constexpr int BN = 256;
+  GemmParams p{};
+  p.M = M; p.N = Vc; p.K = K; p.ldc = ldz; p.status = status; p.C = static_cast<bf16*>(dZ);
+  p.num_m_tiles = (M + BM - 1) / BM;
+  p.num_n_tiles = (Vc + BN - 1) / BN;
+  p.targets = targets; p.lse = lse; p.gout = gout; p.inv_temp = 1.f / temperature; p.col_offset = col_offset;
+  CUtensorMap tmA, tmB, tmC;
+  if (!make_tensor_map_bf16(&tmA, H, M, K, ldh, BM) || !make_tensor_map_bf16(&tmB, W, Vc, K, ldw, BN) || !make_tensor_map_bf16(&tmC, dZ, M, Vc, ldz, 32)) return 1;
+  return launch_variant<BN, kEpiDLogits>(tmA, tmB, tmC, p, s);
+}
+
 void set_gemm_tile(int bn) { g_force_bn = bn; }
 
 // C[M,N] = A[M,K]·B[N,K]ᵀ (+R).  Returns 0 on success, non-zero when the shape/alignment is unsupported (caller falls back).

@@ -21,8 +21,9 @@ extern "C" {
 // Workspace (floats) a call with these sizes needs; compare against UNIRL_B200_NOALLOC_MAX_FLOATS.
 int64_t unirl_b200_decode_noalloc_workspace_floats(int batch, int q_heads, int kv_heads, int head_dim, int max_kv_len);
 
-// One-time set-up for the CURRENT device (resolves the scratch array's address).  Idempotent.  Call it once per
-// device before any stream capture; the attention call below also performs it on first use.
+// One-time set-up for the CURRENT device: resolves the scratch array's address and opts the decode kernels into their
+// shared-memory size on this device.  Idempotent and safe to call from several host threads.  Call it once per device
+// before any stream capture; the attention call below also performs it on first use.
 int unirl_b200_decode_noalloc_setup(void);
 
 // out[b, h, :] = softmax(q[b, h, :] . K_b^T * scale) V_b over the first seq_lens[b] cached tokens of sequence b.

@@ -14,6 +14,34 @@ constexpr int kEpiStore = 0;
 constexpr int kEpiResidual = 1;
 constexpr int kEpiSwiGLU = 2;
 constexpr int kEpiLSE = 3;
+constexpr int kEpiAccF32 = 4;
+constexpr int kEpiDLogits = 5;
+
+// Kernel attributes (opt-in dynamic shared memory, cluster size) belong to ONE device's context, so "already configured" is
+// remembered per device.  `claim()` returns true when the current device still needs the attribute calls; `done()` records that
+// they succeeded.  Two host threads racing on the same device at worst both issue the (idempotent) attribute calls.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  volatile unsigned char flag[kMaxDevices] = {};
+  int dev = -1;
+  bool claim() {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+      dev = -1;
+      return true;  // unknown device: configure every time
+    }
+    return flag[dev] == 0;
+  }
+  void done() {
+    if (dev >= 0) flag[dev] = 1;
+  }
+};
+// Index-only variant of the bookkeeping above, unit-testable on the host: returns true the first time `dev` is seen.
+inline bool per_device_first_use(unsigned char* flags, int n, int dev) {
+  if (dev < 0 || dev >= n) return true;
+  const bool first = flags[dev] == 0;
+  flags[dev] = 1;
+  return first;
+}
 
 // ---- elementwise.cu ----------------------------------------------------------------------------------
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t R, int D, float eps, int dtype, cudaStream_t s);
@@ -49,6 +77,11 @@ void sde_replay_bwd(const float* g_mean, const float* g_logp, const float* mean,
                     int64_t B, int64_t N, int mode, cudaStream_t s);
 
 // ---- gemm_tcgen05.cu -------------------------------------------------------------------------------------
+int gemm_bf16_general(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate,
+                      int* status, cudaStream_t s);
+int linear_dlogits(const void* H, const void* W, void* dZ, int M, int Vc, int K, int ldh, int ldw, int ldz, const int* targets, const float* lse,
+                   const float* gout, float temperature, int col_offset, int* status, cudaStream_t s);
+int num_sms();  // SM count of the current device (cached per device)
 int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
                  cudaStream_t s);
 // Decode-sized GEMM (M of a few hundred rows): one 128 x {128,144} tile per CTA, K split over a thread-block cluster and reduced
@@ -56,7 +89,7 @@ int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, in
 void set_pdl(bool on);  // programmatic dependent launch for the decode-sized kernels (default on)
 void gemm_skinny_plan(int M, int N, int K, bool swiglu, int* bn_out, int* splits_out);
 void set_gemm_skinny_splits(int splits);  // tuning hook: 0 = heuristic
-void set_gemm_skinny_debug(unsigned long long* trace, int skip_a);  // diagnostics: per-CTA phase timestamps [CTAs, 8]; skip_a isolates weight streaming (wrong result)
+void set_gemm_skinny_debug(unsigned long long* trace, int skip_a);  // effective only in builds with -DUNIRL_B200_SKINNY_DIAG: per-CTA phase timestamps [CTAs, 8]; skip_a isolates weight streaming (wrong result)
 int gemm_bf16_tn_skinny(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
                         cudaStream_t s);
 int lse_num_tiles(int V);
@@ -66,6 +99,7 @@ int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int l
                float* logp_out, int64_t* tok_out, int* status, cudaStream_t s);
 
 // ---- attention_decode.cu -----------------------------------------------------------------------------------
+int paged_decode_configure();  // per-device kernel attributes of the decode kernels (idempotent; call before stream capture)
 int decode_num_splits(int B, int Hkv, int max_kv_len);
 int64_t decode_workspace_floats(int B, int Hq, int D, int num_splits);
 int64_t decode_cascade_workspace_floats(int B, int Hq, int D, int num_splits);

@@ -101,9 +101,25 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_sw128(const void* smem_tile
   d |= static_cast<uint64_t>(2) << 61;                      // layout: SWIZZLE_128B
   return d;
 }
-// Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, both operands K-major.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+// Shared-memory matrix descriptor for an MN-major operand: the tile is stored as boxes of [64 k-rows] x [64 elements along M or N]
+// (128-byte rows, 128-byte swizzle as TMA writes them), one box per 64 elements of the M / N extent, `box_bytes` apart.
+// Row r of a box holds contraction index r; 8-row groups are 1024 bytes apart (SBO); the next 64 elements along M / N are
+// `box_bytes` further (LBO).  One MMA of K = 16 consumes 16 rows = 2048 bytes: advance the start address by that per k-step.
+__device__ __forceinline__ uint64_t make_desc_mnmajor_sw128(const void* smem_tile, uint32_t box_bytes) {
+  const uint32_t addr = smem_u32(smem_tile);
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((box_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset
+  d |= static_cast<uint64_t>(1024u >> 4) << 32;                  // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: bf16 x bf16 -> fp32.  a_mn / b_mn: the operand is MN-major (its M / N extent is the
+// contiguous one in shared memory) instead of K-major.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn = false, bool b_mn = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.

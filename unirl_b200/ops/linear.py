@@ -1,9 +1,9 @@
 """Linear layers (K1): ``y = x · Wᵀ`` with optional fused epilogues.
 
-Forward on CUDA goes to the hand-written tcgen05/TMEM GEMM (TMA-fed, persistent, 128×256 tiles)
-for the fused variants (SwiGLU epilogue, residual add, LoRA add); the plain variant may use the
-library GEMM.  Backward uses plain library GEMMs (``dX = dY·W``, ``dW = dYᵀ·X``): those are
-unfused contractions where cuBLAS is the stated baseline.
+Forward and backward on CUDA go to the hand-written tcgen05/TMEM GEMM (TMA-fed, persistent, 128×256 tiles).  The kernel
+takes each operand K-major or MN-major, so ``dX = dY·W`` reads ``W`` as stored and ``dW = dYᵀ·X`` reads ``dY`` and ``X``
+as stored (no transpose pass); the weight gradient accumulates in fp32 straight into the trainer's buffer from the
+epilogue.  ``UNIRL_B200_GEMM_BWD=library`` restores library GEMMs in backward (A/B measurements).
 """
 
 from __future__ import annotations
@@ -25,7 +25,14 @@ _MAX_SKINNY_M = int(os.environ.get("UNIRL_B200_GEMM_SKINNY_MAX_M", "128"))  # me
 # "unsplit": only shapes whose tiles fill a wave without splitting K (the cluster exchange costs about what the library's
 # split-K costs, so those shapes stay on the library GEMM); "all": every qualifying shape.
 _SKINNY_MODE = os.environ.get("UNIRL_B200_GEMM_SKINNY_MODE", "unsplit")
+_BWD_NATIVE = os.environ.get("UNIRL_B200_GEMM_BWD", "native") == "native"
 _plan_cache: dict = {}
+
+
+def _bwd_native_ok(g2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor) -> bool:
+    return (_BWD_NATIVE and g2.dtype == torch.bfloat16 and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and g2.shape[0] >= _MIN_NATIVE_M
+            and g2.shape[1] % 8 == 0 and x2.shape[1] % 8 == 0 and g2.stride(1) == 1 and g2.stride(0) % 8 == 0
+            and hasattr(ext(), "gemm_bf16"))
 
 
 def _skinny_unsplit(m: int, n: int, k: int, swiglu: bool) -> bool:
@@ -89,6 +96,24 @@ class _NativeLinear(torch.autograd.Function):
     def backward(ctx, gy):
         x2, w = ctx.saved_tensors
         g2 = gy.reshape(-1, gy.shape[-1])
+        if _bwd_native_ok(g2, x2, w):
+            C = require_ext()
+            gx = gw = None
+            if ctx.needs_input_grad[0]:
+                gx = C.gemm_bf16(g2, w, False, True).view(ctx.in_shape)  # dX = dY·W, W read as stored ([N, K] = MN-major B)
+                count_launch()
+            if ctx.needs_input_grad[1]:
+                if ctx.accum is not None:
+                    # dW += dYᵀ·X with both operands read as stored; fp32 accumulation into the trainer's buffer happens in the epilogue,
+                    # so neither a bf16 dW nor a separate add pass exists.  Autograd still needs a gradient object to fire the
+                    # parameter's hook; an uninitialised placeholder costs nothing.
+                    C.gemm_bf16(g2, x2, True, True, ctx.accum(), True)
+                    ctx.param._wgrad_fused = True
+                    gw = torch.empty(w.shape, dtype=w.dtype, device=w.device)
+                else:
+                    gw = C.gemm_bf16(g2, x2, True, True)
+                count_launch()
+            return gx, gw, (gy if ctx.has_res else None), None
         gx = (g2 @ w).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
         gw = None
         if ctx.needs_input_grad[1]:

@@ -3,9 +3,9 @@
 CUDA forward: the tcgen05 GEMM runs over vocab tiles with an epilogue that reduces each 128×N
 accumulator tile (still in TMEM) to per-row ``(max, Σexp, target logit)`` partials; a merge kernel
 folds the partials into ``lse`` and ``logp``.  Logits never reach HBM.
-CUDA backward: per token chunk, logits are recomputed by the same GEMM into a bf16 scratch,
-turned in place into ``dZ = g/T · (onehot − softmax)`` by one kernel, then ``dH = dZ·W`` and
-``dW += dZᵀ·H`` are plain GEMMs.
+CUDA backward: per token chunk, the same GEMM recomputes the logits and its epilogue turns each accumulator tile
+into ``dZ = g/T · (onehot − softmax)`` (bf16; the logits themselves are never written), then ``dH = dZ·W`` and
+``dW += dZᵀ·H`` run on the tcgen05 GEMM with the operands read as stored and fp32 accumulation of ``dW`` in the epilogue.
 Reference (CPU + oracle): chunked fp32 ``x[target]/T − logsumexp(x/T)``, as the reference framework does in
 ``unirl/models/qwen3/ar.py:74-99`` with ``torch.utils.checkpoint``.
 """
@@ -60,9 +60,18 @@ class _LinearLogprob(torch.autograd.Function):
         d_weight = None
         if ctx.needs_input_grad[1]:
             d_weight = ctx.accum() if fused_into_trainer else torch.zeros_like(weight, dtype=torch.float32)
+        native = (os.environ.get("UNIRL_B200_GEMM_BWD", "native") == "native" and hasattr(C, "linear_dlogits") and weight.shape[0] % 8 == 0
+                  and weight.is_contiguous())
         for s in range(0, hidden.shape[0], _BWD_CHUNK):
             e = min(s + _BWD_CHUNK, hidden.shape[0])
             h = hidden[s:e]
+            if native:
+                z = C.linear_dlogits(h, weight, tgt[s:e], lse[s:e], g[s:e], ctx.temperature, 0)  # dZ from the recompute GEMM's epilogue
+                C.gemm_bf16(z, weight, False, True, d_hidden[s:e], False)  # dH = dZ·W
+                if d_weight is not None:
+                    C.gemm_bf16(z, h, True, True, d_weight, True)  # dW += dZᵀ·H
+                count_launch(3)
+                continue
             z = h @ weight.t()  # bf16 scratch [chunk, V]
             C.logprob_dlogits_inplace(z, tgt[s:e], lse[s:e], g[s:e], ctx.temperature)
             count_launch()

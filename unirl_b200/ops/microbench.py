@@ -85,6 +85,31 @@ def case_gemm(args: argparse.Namespace) -> None:
         _emit(row)
 
 
+def case_gemm_bwd(args: argparse.Namespace) -> None:
+    """The two backward GEMMs of ``Y[M,N] = X[M,K]·W[N,K]ᵀ`` for every forward shape given: ``dX = dY·W`` (W read as stored) and
+    ``dW += dYᵀ·X`` (both read as stored, fp32 accumulation in the epilogue) on the tcgen05 kernel vs the library calls."""
+    from unirl_b200.ops._ext import require_ext
+
+    C, pk, timer = require_ext(), _peaks(), _Timer(args.iters)
+    shapes = [tuple(int(x) for x in s.split("x")) for s in args.shapes.split(",")]
+    for m, n, k in shapes:
+        x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+        gy = torch.randn(m, n, device="cuda", dtype=torch.bfloat16)
+        acc = torch.zeros(n, k, device="cuda", dtype=torch.float32)
+        fl = 2.0 * m * n * k
+        dx = timer(lambda: C.gemm_bf16(gy, w, False, True))
+        dw = timer(lambda: C.gemm_bf16(gy, x, True, True, acc, True))
+        row = {"case": "gemm_bwd", "M": m, "N": n, "K": k, "dx_ms": dx["best_ms"], "dx_tflops": fl / dx["best_ms"] / 1e9, "dw_ms": dw["best_ms"],
+               "dw_tflops": fl / dw["best_ms"] / 1e9, "peak": pk["kind"], "peak_tflops": pk["tflops"]}
+        if not args.no_library:
+            ldx = timer(lambda: gy @ w)
+            ldw = timer(lambda: torch.addmm(acc, gy.t(), x, out_dtype=torch.float32, out=acc))
+            row.update(library_dx_tflops=fl / ldx["best_ms"] / 1e9, library_dw_tflops=fl / ldw["best_ms"] / 1e9)
+        assert C.gemm_status(True) == 0, "a pipeline wait timed out"
+        _emit(row)
+
+
 def case_skinny_gemm(args: argparse.Namespace) -> None:
     """Decode-shaped GEMMs (weight-bandwidth bound): cluster split-K tcgen05 kernel vs the library GEMM, each timed over a ring of
     distinct weight matrices larger than L2 so every call streams its weights from HBM."""
@@ -459,7 +484,7 @@ def case_peer(args: argparse.Namespace) -> None:
     dist.destroy_process_group()
 
 
-CASES = {"gemm": case_gemm, "skinny_gemm": case_skinny_gemm, "decode_attention": case_decode_attention, "linear_logprob": case_linear_logprob, "linear_sample": case_linear_sample,
+CASES = {"gemm": case_gemm, "gemm_bwd": case_gemm_bwd, "skinny_gemm": case_skinny_gemm, "decode_attention": case_decode_attention, "linear_logprob": case_linear_logprob, "linear_sample": case_linear_sample,
          "elementwise": case_elementwise, "peer": case_peer, "decode_step": case_decode_step, "train_step": case_train_step, "attention": case_attention}
 
 

@@ -68,6 +68,9 @@ class PeerArena:
         self.rank, self.world = comm.rank, comm.size
         self.peer = C.PeerComm([int(p) for p in self._hdl.buffer_ptrs], [int(p) for p in self._flag_h.buffer_ptrs], self.rank, self.state, float(wait_s))
         self._cursor = 0
+        from unirl_b200.ops.status import register_checker
+
+        register_checker(self)  # status word read at every step boundary (check_device_status)
 
     def take(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """Bump-allocate a zeroed 256-byte aligned view of this rank's part of the arena."""

@@ -166,6 +166,10 @@ class NativeARRolloutEngine(BaseRolloutEngine):
             stop.add(int(ar.stop_token_id))
         prompts = unpad_prompts(cond.input_ids, cond.attention_mask)
         out = self.generator.generate(prompts, max_new_tokens=max_new, temperature=temp, top_k=top_k, top_p=top_p, stop_token_ids=sorted(stop))
+        if torch.device(self.device or "cpu").type == "cuda":
+            from unirl_b200.ops.status import check_device_status
+
+            check_device_status("end of rollout batch")  # the batch's tokens were just read on the host: no extra stall
         seg = pack_text_segment(out.tokens, out.log_probs, out.finished)
         decoded = None
         if c.detokenize:

@@ -155,6 +155,10 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
             for name, t in resp.tracks.items():
                 if t.segment is not None and getattr(t.segment, "sigmas", None) is not None:
                     verify_sigmas(t.segment.sigmas, req.sigmas, who=f"native diffusion engine, track {name!r}")
+        if torch.cuda.is_available() and any(p.is_cuda for p in model.parameters()):
+            from unirl_b200.ops.status import check_device_status
+
+            check_device_status("end of diffusion rollout batch")
         return resp
 
     # ---- life cycle -------------------------------------------------------------------------------------------

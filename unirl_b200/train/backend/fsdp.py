@@ -171,6 +171,10 @@ class FSDPBackend(Remote):
         norm_t = sh.grad_norm()
         grad_norm = float(norm_t)  # the one host sync of the step: also the skip verdict
         sh.shard_comm.check()  # a peer wait that ran out of time raises here instead of training on a partial reduction
+        if sh.device.type == "cuda":
+            from unirl_b200.ops.status import check_device_status
+
+            check_device_status("optimizer step")  # GEMM / attention status word and every live peer arena
         if not math.isfinite(grad_norm):
             logger.warning("non-finite grad norm (%s) at optimizer step %d; skipping the update", grad_norm, self._optimizer_step_count)
             sh.zero_grad()
