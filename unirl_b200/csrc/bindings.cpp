@@ -421,6 +421,54 @@ Tensor paged_decode_attention(const Tensor& q, const Tensor& kc, const Tensor& v
   return out;
 }
 
+// Packed-sequence flash attention (tcgen05).  q [T, Hq, D], k / v [T, Hkv, D]: bf16, dense in the last two dimensions, rows may be strided
+// (views into a fused qkv buffer); cu_seqlens int32 [B + 1].  Returns {out [T, Hq, D], lse fp32 [Hq, T]}.
+std::vector<Tensor> attn_varlen_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu, int64_t max_seqlen, bool causal, double scale) {
+  (void)max_seqlen;
+  TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && cu.is_cuda() && q.device() == k.device() && q.device() == v.device() && q.device() == cu.device(),
+              "attn_varlen_fwd: CUDA tensors on one device");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16,
+              "attn_varlen_fwd: bf16 [T, H, D] tensors");
+  TORCH_CHECK(k.sizes() == v.sizes() && q.size(0) == k.size(0) && q.size(2) == k.size(2), "attn_varlen_fwd: q / k / v shapes");
+  auto dense = [](const Tensor& t) { return t.stride(2) == 1 && t.stride(1) == t.size(2) && t.stride(0) % 8 == 0; };
+  TORCH_CHECK(dense(q) && dense(k) && dense(v), "attn_varlen_fwd: heads and features must be dense, row stride a multiple of 8 elements");
+  TORCH_CHECK(cu.scalar_type() == at::kInt && cu.is_contiguous() && cu.numel() >= 2, "attn_varlen_fwd: int32 cu_seqlens [B + 1]");
+  c10::cuda::CUDAGuard g(q.device());
+  const int T = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)k.size(1), B = (int)cu.numel() - 1;
+  auto out = torch::empty({T, Hq, D}, q.options());
+  auto lse = torch::empty({Hq, T}, q.options().dtype(torch::kFloat));
+  const int rc = ub::flash_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), cu.data_ptr<int>(), out.data_ptr(), lse.data_ptr<float>(), T, B, Hq, Hkv, D,
+                                         q.stride(0), k.stride(0), v.stride(0), (int64_t)Hq * D, (float)scale, causal ? 1 : 0,
+                                         gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "attn_varlen_fwd: unsupported configuration or launch failure (code ", rc, "); head_dim must be 64 or 128");
+  return {out, lse};
+}
+
+// Gradients of attn_varlen_fwd: returns {dq [T, Hq, D], dk [T, Hkv, D], dv [T, Hkv, D]} (bf16, dense).
+std::vector<Tensor> attn_varlen_bwd(const Tensor& d_out, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse, const Tensor& cu,
+                                    int64_t max_seqlen, bool causal, double scale) {
+  (void)max_seqlen;
+  auto dense = [](const Tensor& t) { return t.dim() == 3 && t.stride(2) == 1 && t.stride(1) == t.size(2) && t.stride(0) % 8 == 0; };
+  TORCH_CHECK(q.is_cuda() && dense(q) && dense(k) && dense(v) && dense(out) && dense(d_out), "attn_varlen_bwd: bf16 [T, H, D] tensors, dense heads / features");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 &&
+              d_out.scalar_type() == at::kBFloat16, "attn_varlen_bwd: bf16 tensors");
+  TORCH_CHECK(out.sizes() == q.sizes() && d_out.sizes() == q.sizes() && k.sizes() == v.sizes() && k.size(0) == q.size(0) && k.size(2) == q.size(2), "attn_varlen_bwd: shapes");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.dim() == 2 && lse.size(0) == q.size(1) && lse.size(1) == q.size(0), "attn_varlen_bwd: lse fp32 [Hq, T]");
+  TORCH_CHECK(cu.scalar_type() == at::kInt && cu.is_contiguous() && cu.numel() >= 2, "attn_varlen_bwd: int32 cu_seqlens [B + 1]");
+  for (const Tensor* t : {&k, &v, &out, &d_out, &lse, &cu}) TORCH_CHECK(t->is_cuda() && t->device() == q.device(), "attn_varlen_bwd: tensors on different devices");
+  c10::cuda::CUDAGuard g(q.device());
+  const int T = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)k.size(1), B = (int)cu.numel() - 1;
+  auto dq = torch::empty({T, Hq, D}, q.options());
+  auto dk = torch::zeros({T, Hkv, D}, q.options());  // rows outside every sequence stay zero
+  auto dv = torch::zeros({T, Hkv, D}, q.options());
+  auto ws = torch::empty({ub::flash_attention_bwd_workspace_floats(T, Hq, D)}, q.options().dtype(torch::kFloat));
+  const int rc = ub::flash_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr<float>(), cu.data_ptr<int>(),
+                                         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr<float>(), T, B, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0),
+                                         out.stride(0), d_out.stride(0), (float)scale, causal ? 1 : 0, gemm_status_tensor().data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "attn_varlen_bwd: unsupported configuration or launch failure (code ", rc, ")");
+  return {dq, dk, dv};
+}
+
 // ---------------------------------------------------------------------------------------------- peer-memory collectives
 // Python owns the symmetric allocations (torch symmetric memory); this object only carries their addresses.
 struct PyPeerComm {
@@ -557,6 +605,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sde_sample_fwd", &sde_sample_fwd);
   m.def("sde_replay_fwd", &sde_replay_fwd);
   m.def("sde_replay_bwd", &sde_replay_bwd);
+  m.def("attn_varlen_fwd", &attn_varlen_fwd);
+  m.def("attn_varlen_bwd", &attn_varlen_bwd);
   m.def("gemm_bf16_tn", &gemm_bf16_tn);
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out") = py::none(),
         py::arg("accumulate") = false);

@@ -304,29 +304,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ++store_ctr;
         }
       } else if (EPI == kEpiAccF32) {
-        // fp32 read-modify-write straight from the accumulator: a thread owns one row and moves 128 bytes per chunk.
+        // fp32 output: 32 x 32 boxes (128-byte rows) staged in swizzled shared memory, then ONE TMA reduce-add (C += acc, done at the
+        // memory side: the SM never reads C) or TMA store (C = acc) per box.  `tmC` is the fp32 map of C here.
         const int n0 = n_idx * BN;
-        float* crow = p.Cf + static_cast<int64_t>(row) * p.ldc + n0;
+        uint8_t* warp_stage = store_smem + q * (2 * L::kStoreChunk);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (n0 + c0 >= p.N) break;
+          if (n0 + c0 >= p.N) break;  // uniform over the warp
+          uint8_t* sbuf = warp_stage + (store_ctr & 1) * L::kStoreChunk;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
           float acc[32];
           tmem_ld_32x32(t_row + c0, acc);
           tmem_ld_wait();
-          if (row_ok) {
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (n0 + c0 + g * 4 < p.N) {  // N is a multiple of 4
-                float4* dst = reinterpret_cast<float4*>(crow + c0 + g * 4);
-                float4 v = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
-                if (p.accumulate) {
-                  const float4 o = *dst;
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *dst = v;
-              }
-            }
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<float4*>(sbuf + lane * 128 + ((g ^ (lane & 7)) << 4)) = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
+          fence_async_proxy();
+          __syncwarp();
+          if (lane == 0) {
+            if (p.accumulate) tma_reduce_add_2d(&tmC, sbuf, n0 + c0, m0 + q * 32);
+            else tma_store_2d(&tmC, sbuf, n0 + c0, m0 + q * 32);
+            tma_store_commit();
           }
+          ++store_ctr;
         }
       } else {  // kEpiLSE
         const int n0 = n_idx * BN;
@@ -508,6 +509,19 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
+// Row-major fp32 matrix [rows, cols]: boxes of 32 rows x 32 columns (128-byte rows) with 128B swizzle, for the epilogue's stores / reductions.
+bool make_tensor_map_f32_32x32(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 4) & 15)) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Row-major bf16 matrix [rows = contraction extent, cols = M or N extent] read as an MN-major operand: boxes of 64 rows x 64 columns.
 static bool make_tensor_map_mn(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld) {
   return make_tensor_map_bf16(out, base, rows, cols, ld, BK);
@@ -522,7 +536,7 @@ int gemm_bf16_general(const void* A, const void* B, void* C, int M, int N, int K
                       int* status, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return out_f32 && accumulate ? 0 : 1;
-  if ((N % 8) || (ldc % 8) || (lda % 8) || (ldb % 8) || (a_mn && (M % 8)) || (!a_mn && (K % 8)) || (!b_mn && (K % 8))) return 1;
+  if ((N % 8) || (ldc % (out_f32 ? 4 : 8)) || (lda % 8) || (ldb % 8) || (a_mn && (M % 8)) || (!a_mn && (K % 8)) || (!b_mn && (K % 8))) return 1;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.status = status;
   p.C = static_cast<bf16*>(C); p.Cf = static_cast<float*>(C); p.accumulate = accumulate;
@@ -533,11 +547,7 @@ int gemm_bf16_general(const void* A, const void* B, void* C, int M, int N, int K
   CUtensorMap tmA, tmB, tmC;
   if (a_mn ? !make_tensor_map_mn(&tmA, A, K, M, lda) : !make_tensor_map_bf16(&tmA, A, M, K, lda, BM)) return 1;
   if (b_mn ? !make_tensor_map_mn(&tmB, B, K, N, ldb) : !make_tensor_map_bf16(&tmB, B, N, K, ldb, BN)) return 1;
-  if (out_f32) {
-    tmC = tmA;  // unused
-  } else if (!make_tensor_map_bf16(&tmC, C, M, N, ldc, 32)) {
-    return 1;
-  }
+  if (out_f32 ? !make_tensor_map_f32_32x32(&tmC, C, M, N, ldc) : !make_tensor_map_bf16(&tmC, C, M, N, ldc, 32)) return 1;
 #define UB_GO(BNV, EPIV, AV, BV) return launch_variant<BNV, EPIV, AV, BV>(tmA, tmB, tmC, p, s)
 #define UB_LAYOUT(BNV, EPIV)                              \
   do {                                                    \

@@ -98,6 +98,15 @@ int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int l
                float* tgt_logit, float* pbest, int* pbest_idx, float* pbest_z, uint64_t seed, int64_t step, const int64_t* step_tensor, float* lse_out,
                float* logp_out, int64_t* tok_out, int* status, cudaStream_t s);
 
+// ---- attention_fwd.cu / attention_bwd.cu (tcgen05 flash attention over packed sequences) ---------------------------------
+int flash_attention_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens, void* out, float* lse, int T, int B, int Hq, int Hkv, int D,
+                        int64_t ldq, int64_t ldk, int64_t ldv, int64_t ldo, float scale, int causal, int* status, cudaStream_t s);
+
+int64_t flash_attention_bwd_workspace_floats(int T, int Hq, int D);
+int flash_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, const int* cu_seqlens, void* dq, void* dk,
+                        void* dv, float* workspace, int T, int B, int Hq, int Hkv, int D, int64_t ldq, int64_t ldk, int64_t ldv, int64_t ldo, int64_t lddo,
+                        float scale, int causal, int* status, cudaStream_t s);
+
 // ---- attention_decode.cu -----------------------------------------------------------------------------------
 int paged_decode_configure();  // per-device kernel attributes of the decode kernels (idempotent; call before stream capture)
 int decode_num_splits(int B, int Hkv, int max_kv_len);

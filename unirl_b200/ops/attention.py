@@ -42,26 +42,33 @@ def varlen_attention_reference(q, k, v, cu_seqlens, causal: bool = True, scale: 
 
 
 def _varlen_impl() -> str:
-    """``native`` when the extension carries the varlen kernels, else the ``flash_attn`` library kernels.
-
-    The library path is a stop-gap for the packed prefill / training attention only; decode attention,
-    which dominates rollout time, is always the native paged kernel.
-    """
+    """``native``: the tcgen05 flash-attention kernels of this package (forward and backward); ``library``: cuDNN / flash-attn.
+    ``UNIRL_B200_VARLEN_ATTN`` selects (``auto`` = native)."""
     want = os.environ.get("UNIRL_B200_VARLEN_ATTN", "auto")
+    if want == "library":
+        return "library"
     C = require_ext()
-    if want in ("auto", "native") and hasattr(C, "attn_varlen_fwd"):
+    if hasattr(C, "attn_varlen_fwd") and hasattr(C, "attn_varlen_bwd"):
         return "native"
     if want == "native":
-        raise RuntimeError("UNIRL_B200_VARLEN_ATTN=native but the extension has no attn_varlen_fwd")
+        raise RuntimeError("UNIRL_B200_VARLEN_ATTN=native but the extension has no attn_varlen_fwd / attn_varlen_bwd")
     return "library"
+
+
+def _rows_ok(t: torch.Tensor) -> torch.Tensor:
+    """The kernels read ``[T, H, D]`` through TMA: heads and features dense, row stride a multiple of 8 elements, 16-byte aligned base.
+    Views into a fused qkv buffer qualify as they are; anything else is copied."""
+    if t.stride(2) == 1 and t.stride(1) == t.shape[2] and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
 
 
 class _VarlenAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
         C = require_ext()
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
+        q, k, v = _rows_ok(q), _rows_ok(k), _rows_ok(v)
+        cu = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
         out, lse = C.attn_varlen_fwd(q, k, v, cu, int(max_seqlen), bool(causal), float(scale))
         count_launch()
         ctx.save_for_backward(q, k, v, out, lse, cu)
@@ -73,7 +80,7 @@ class _VarlenAttention(torch.autograd.Function):
         C = require_ext()
         q, k, v, out, lse, cu = ctx.saved_tensors
         max_seqlen, causal, scale = ctx.cfg
-        dq, dk, dv = C.attn_varlen_bwd(g_out.contiguous(), q, k, v, out, lse, cu, max_seqlen, causal, scale)
+        dq, dk, dv = C.attn_varlen_bwd(_rows_ok(g_out), q, k, v, out, lse, cu, max_seqlen, causal, scale)
         count_launch(3)
         return dq, dk, dv, None, None, None, None
 
@@ -121,10 +128,8 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen: Optional[int] = None, caus
     if use_native(q):
         if q.dtype not in (torch.bfloat16, torch.float16):
             return varlen_attention_reference(q, k, v, cu_seqlens, causal, scale)
-        if _varlen_impl() == "native":
-            if max_seqlen is None:
-                max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
-            return _VarlenAttention.apply(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        if _varlen_impl() == "native" and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[1] % k.shape[1] == 0:
+            return _VarlenAttention.apply(q, k, v, cu_seqlens, int(max_seqlen or 0), causal, scale)
         if lens_host is not None and os.environ.get("UNIRL_B200_DENSE_ATTN", "1") == "1" and q.shape[-1] in (64, 128):
             out = _padded_dense(q, k, v, [int(n) for n in lens_host], causal, scale)
             if out is not None:

@@ -377,6 +377,15 @@ def case_attention(args: argparse.Namespace) -> None:
             row.update({f"dense_{name}_fwd_bwd_ms": t["median_ms"], f"dense_{name}_fwd_bwd_tflops": 3.5 * flops_f / t["median_ms"] / 1e9})
         except Exception as e:  # noqa: BLE001
             row[f"dense_{name}_error"] = str(e)[:120]
+    try:
+        def dense_fwd():
+            with torch.no_grad(), sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+                F.scaled_dot_product_attention(qd, kd, vd, is_causal=True, enable_gqa=hq != hkv)
+
+        t = timer(dense_fwd)
+        row.update(dense_cudnn_fwd_ms=t["median_ms"], dense_cudnn_fwd_tflops=flops_f / t["median_ms"] / 1e9)
+    except Exception as e:  # noqa: BLE001
+        row["dense_cudnn_fwd_error"] = str(e)[:120]
     row.update(frac_of_peak=row["packed_fwd_bwd_tflops"] / pk["tflops"], peak=pk["kind"])
     _emit(row)
 
