@@ -169,6 +169,59 @@ def test_adamw_and_sum_squares():
     _close(sum_squares(grad), grad.float().pow(2).sum(), 1e-2, 1e-4, "sum_squares")
 
 
+def _kept_mask(z, top_k, top_p):
+    """The reference sampler's truncation on fp32 rows without ties: True where an entry survives."""
+    filt = z.clone()
+    if top_k and top_k < z.shape[-1]:
+        kth = torch.topk(filt, top_k, -1).values[..., -1:]
+        filt = filt.masked_fill(filt < kth, float("-inf"))
+    if top_p < 1.0:
+        sv, si = torch.sort(filt, -1, descending=True)
+        pr = torch.softmax(sv, -1)
+        drop = pr.cumsum(-1) - pr > top_p
+        sv = sv.masked_fill(drop, float("-inf"))
+        filt = torch.full_like(filt, float("-inf")).scatter(-1, si, sv)
+    return torch.isfinite(filt)
+
+
+@pytest.mark.parametrize("top_k,top_p", [(5, 1.0), (0, 0.8), (50, 0.9), (1, 1.0), (0, 0.05)])
+def test_truncated_sampling_kernel(top_k, top_p):
+    """Top-k / top-p sampling by radix selection: draws stay inside the reference's kept set, the recorded log-prob is the
+    full-vocabulary one, and the draw frequencies follow the renormalised probabilities."""
+    from unirl_b200.ops.sampling import sample
+
+    torch.manual_seed(31)
+    b, v, temp = 16, 1000, 0.7
+    logits = torch.randn(b, v, device="cuda") * 2.0
+    z = logits / temp
+    keep = _kept_mask(z, top_k, top_p)
+    full_lp = torch.log_softmax(z, -1)
+    probs = torch.softmax(z.masked_fill(~keep, float("-inf")), -1)
+    draws = 3000
+    counts = torch.zeros(b, v, device="cuda")
+    for step in range(draws):
+        tok, lp = sample(logits, temp, top_k, top_p, seed=7, step=step)
+        assert bool(keep.gather(1, tok[:, None]).all()), "a draw fell outside the kept set"
+        if step < 3:
+            torch.testing.assert_close(lp, full_lp.gather(1, tok[:, None]).squeeze(1), atol=1e-4, rtol=1e-4)
+        counts.scatter_add_(1, tok[:, None], torch.ones(b, 1, device="cuda"))
+    freq = counts / draws
+    assert float((freq - probs).abs().max()) < 0.05, "draw frequencies do not follow the truncated distribution"
+
+
+def test_truncated_sampling_large_vocab_bf16_is_deterministic():
+    C = _C()
+    torch.manual_seed(32)
+    logits = (torch.randn(8, 151936, device="cuda") * 3.0).bfloat16()
+    a = C.sample_truncated(logits, 1.0, 40, 0.95, 3, 11)
+    b = C.sample_truncated(logits, 1.0, 40, 0.95, 3, 11)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "same (seed, step) must give the same draw (tensor-parallel ranks rely on it)"
+    z = logits.float()
+    kth = torch.topk(z, 40, -1).values[:, -1:]
+    assert bool((z.gather(1, a[0][:, None]) >= kth).all())
+    torch.testing.assert_close(a[1], torch.log_softmax(z, -1).gather(1, a[0][:, None]).squeeze(1), atol=2e-3, rtol=1e-3)
+
+
 @pytest.mark.parametrize("name", ["flow", "cps", "dance"])
 def test_sde_step_matches_strategy(name):
     from unirl_b200.ops.sde_step import sde_step

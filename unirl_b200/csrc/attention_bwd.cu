@@ -15,8 +15,9 @@
 //   warp 0      loader  : K, V once; Q_i / dO_i ring (2 stages)
 //   warp 1      issuer  : the five MMAs of an iteration
 //   warps 4..7  compute : one key row per thread
-// TMEM columns (512): Sᵀ/Pᵀ (then dQ) | dPᵀ/dSᵀ | dV | dK.
+// TMEM columns (512): Sᵀ/Pᵀ | dPᵀ/dSᵀ (then dQ) | dV | dK.
 // Every wait is bounded and watches a CTA-wide abort flag (see attention_fwd.cu).
+#include "attn_math.cuh"
 #include "common.cuh"
 #include "ops.h"
 #include "tcgen05.cuh"
@@ -45,7 +46,8 @@ struct BwdLayout {
   static constexpr int kQ = 2 * kTileBytes;
   static constexpr int kdO = kQ + kStages * kTileBytes;
   static constexpr int kdS = kdO + kStages * kTileBytes;    // [128 keys x 128 queries] bf16 = 2 boxes; later the fp32 staging of dQ
-  static constexpr int kBars = kdS + 2 * kBoxBytes;
+  static constexpr int kStat = kdS + 2 * kBoxBytes;         // two buffers of {lse·log2e, Δ} for 128 queries (2 KB)
+  static constexpr int kBars = kStat + 2 * 2 * kTile * 4;
   static constexpr int kTotal = kBars + 256;
 };
 
@@ -132,9 +134,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* sdp_full = qdo_empty + kStages; // 1: Sᵀ and dPᵀ are in TMEM
   uint64_t* pds_ready = sdp_full + 1;       // 1 (4 arrivals): Pᵀ / dSᵀ written
   uint64_t* dq_full = pds_ready + 1;        // 1: dV, dK updated, dQ tile in TMEM
-  uint64_t* s_free = dq_full + 1;           // 1 (4 arrivals): dQ tile read out, the Sᵀ columns may be overwritten
+  uint64_t* s_free = dq_full + 1;           // 1 (4 arrivals): dQ tile read out, the dPᵀ columns may be overwritten
   uint64_t* dkv_full = s_free + 1;          // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkv_full + 1);
+  uint64_t* stat_ready = dkv_full + 1;      // 2 (128 arrivals each): the statistics buffer of an iteration is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_ready + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -153,6 +156,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(dq_full, 1);
     mbar_init(s_free, 4);
     mbar_init(dkv_full, 1);
+    mbar_init(stat_ready, 128);
+    mbar_init(stat_ready + 1, 128);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
@@ -207,18 +212,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int st = it % kStages;
         const uint8_t* sQ = smem + L::kQ + st * L::kTileBytes;
         const uint8_t* sdO = smem + L::kdO + st * L::kTileBytes;
-        if (!wait_or_abort(qdo_full + st, (it / kStages) & 1, abort_flag) || !wait_or_abort(s_free, (it & 1) ^ 1, abort_flag)) {
+        if (!wait_or_abort(qdo_full + st, (it / kStages) & 1, abort_flag)) {
           give_up(p.status, 153, abort_flag);
           ok = false;
           break;
         }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {  // Sᵀ = K·Qᵀ
+        for (int k = 0; k < D / 16; ++k) {  // Sᵀ = K·Qᵀ (runs while the compute warps still drain the previous dQ tile from the dPᵀ columns)
           const int box = k / 4, kk = k % 4;
           umma_bf16(tmem_base + kColS, make_desc_kmajor_sw128(smem + L::kK + box * L::kBoxBytes) + 2 * kk, make_desc_kmajor_sw128(sQ + box * L::kBoxBytes) + 2 * kk,
                     idesc_s, k != 0);
         }
+        if (!wait_or_abort(s_free, (it & 1) ^ 1, abort_flag)) {  // the previous dQ tile has been read out of the dPᵀ columns
+          give_up(p.status, 159, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {  // dPᵀ = V·dOᵀ
           const int box = k / 4, kk = k % 4;
@@ -241,8 +252,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < kTile / 16; ++k)  // dK += dSᵀ·Q
           umma_bf16_ts(tmem_base + kColdK, tmem_base + kColdP + k * 8, d_Q + kStepMN * k, idesc_ts, it > 0 || k != 0);
 #pragma unroll
-        for (int k = 0; k < kTile / 16; ++k)  // dQ = dS·K     (contraction over the 128 keys; overwrites the Sᵀ columns)
-          umma_bf16(tmem_base + kColS, d_dS + kStepMN * k, d_K + kStepMN * k, idesc_dq, k != 0);
+        for (int k = 0; k < kTile / 16; ++k)  // dQ = dS·K     (contraction over the 128 keys; overwrites the dPᵀ / dSᵀ columns, after dK has read them)
+          umma_bf16(tmem_base + kColdP, d_dS + kStepMN * k, d_K + kStepMN * k, idesc_dq, k != 0);
         umma_commit(dq_full);
         umma_commit(qdo_empty + st);
       }
@@ -264,15 +275,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int g = it / (n_q - i_first), i = i_first + it % (n_q - i_first);
       const int head = kv_head * G + g;
       const int qt0 = i * kTile;  // first query position of the tile
-      // per-query statistics of this tile: lane l keeps queries l, 32 + l, 64 + l, 96 + l; the inner loop broadcasts them by shuffle
-      // (no block-level barrier anywhere in this role: a warp that gives up must not strand the others)
-      float st_lse[4], st_delta[4];
-#pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        const int qp = qt0 + k4 * 32 + lane;
+      // per-query statistics of this tile, shared by the four compute warps: thread r fills entry r of buffer (it & 1); an mbarrier
+      // (bounded wait, never a block barrier: a warp that gives up must not strand the others) tells when all 128 entries are there.
+      // The buffer written now was last read two iterations ago, and every warp has passed this iteration's dq_full wait since.
+      float* stat = reinterpret_cast<float*>(smem + L::kStat) + (it & 1) * 2 * kTile;
+      {
+        const int qp = qt0 + r;
         const bool qv = qp < seq_len;
-        st_lse[k4] = qv ? p.lse[static_cast<int64_t>(head) * p.T + seq_start + qp] * 1.4426950408889634f : INFINITY;  // exp2(x - inf) = 0
-        st_delta[k4] = qv ? p.delta[static_cast<int64_t>(head) * p.T + seq_start + qp] : 0.f;
+        stat[r] = qv ? p.lse[static_cast<int64_t>(head) * p.T + seq_start + qp] * 1.4426950408889634f : INFINITY;  // exp2(x - inf) = 0
+        stat[kTile + r] = qv ? p.delta[static_cast<int64_t>(head) * p.T + seq_start + qp] : 0.f;
+        mbar_arrive(stat_ready + (it & 1));
+      }
+      if (!__all_sync(0xffffffffu, wait_or_abort(stat_ready + (it & 1), (it >> 1) & 1, abort_flag))) {
+        give_up(p.status, 158, abort_flag);
+        ok = false;
+        break;
       }
       if (!__all_sync(0xffffffffu, wait_or_abort(sdp_full, it & 1, abort_flag))) {
         give_up(p.status, 155, abort_flag);
@@ -299,17 +316,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int qi = hlf * 64 + c + e;
-            const float q_lse = __shfl_sync(0xffffffffu, st_lse[qi >> 5], qi & 31);
-            const float q_delta = __shfl_sync(0xffffffffu, st_delta[qi >> 5], qi & 31);
-            float pv = fast_exp2(fmaf(s[c + e], p.scale_log2, -q_lse));
+            const float q_lse = stat[qi], q_delta = stat[kTile + qi];  // same address in every lane: one broadcast read, vectorised by the compiler
+            const float xarg = fmaf(s[c + e], p.scale_log2, -q_lse);
+            float pv = e == 0 ? exp2_mufu(xarg) : exp2_poly(xarg);  // half of the exponentials on the FMA pipes (see attn_math.cuh)
             if (!key_ok || (diag && qt0 + qi < kpos)) pv = 0.f;
             pr[e] = pv;
             ds[e] = pv * (dp[c + e] - q_delta) * p.scale;
           }
-          const bf162 hp = __floats2bfloat162_rn(pr[0], pr[1]);
-          const bf162 hd = __floats2bfloat162_rn(ds[0], ds[1]);
-          pp[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
-          dd[c / 2] = *reinterpret_cast<const uint32_t*>(&hd);
+          pp[c / 2] = pack_bf16x2_pos(pr[0], pr[1]);
+          dd[c / 2] = pack_bf16x2_rne(ds[0], ds[1]);
         }
         tmem_st_32x32(tmem_base + kColS + lane_off + hlf * 32, pp);
         tmem_st_32x32(tmem_base + kColdP + lane_off + hlf * 32, dd);
@@ -339,7 +354,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           __syncwarp();
         }
         float a[32];
-        tmem_ld_32x32(tmem_base + kColS + lane_off + c * 32, a);
+        tmem_ld_32x32(tmem_base + kColdP + lane_off + c * 32, a);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 8; ++j)

@@ -19,6 +19,7 @@
 // zero fill) and are never stored; keys beyond the end (or above the diagonal under the causal mask) get probability zero.
 // Every mbarrier wait is bounded and watches a CTA-wide abort flag: on expiry the role records a code in `status`, raises the flag,
 // every role leaves its loop, TMEM is released and the kernel returns.
+#include "attn_math.cuh"
 #include "common.cuh"
 #include "ops.h"
 #include "tcgen05.cuh"
@@ -303,8 +304,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int c = 0; c < 64; ++c)
             if (kv0 + hlf * 64 + c > limit) s[c] = -INFINITY;
         }
+        // eight independent chains: with two softmax warps per scheduler a 64-long dependent chain would sit on the critical path
+        float m8[8];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, s[c]);
+        for (int e = 0; e < 8; ++e) m8[e] = s[e];
+#pragma unroll
+        for (int c = 8; c < 64; c += 8)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) m8[e] = fmaxf(m8[e], s[c + e]);
+        mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))));
       }
       mx *= p.scale_log2;
       // lazy maximum: keep the value in use unless this row's maximum outgrew it by more than the threshold
@@ -327,7 +335,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;  // a row with no visible key so far: every s is -inf, p = 0
       // Pass 2: probabilities.  P (bf16, two per column) overwrites S from column 0: the 32 columns written for one half lie inside
       // the 64 columns just read for it, and every thread touches its own row only.
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
         float s[64];
@@ -337,19 +345,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
-          float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));
-          float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
+          // one exponential of each pair on the special-function unit, the other on the FMA pipes; the bf16 pair is packed with
+          // integer instructions: the three pipes then take comparable time per tile (see attn_math.cuh)
+          float p0 = exp2_mufu(fmaf(s[c], p.scale_log2, -m_eff));
+          float p1 = exp2_poly(fmaf(s[c + 1], p.scale_log2, -m_eff));
           if (need_mask) {
             if (kv0 + hlf * 64 + c > limit) p0 = 0.f;
             if (kv0 + hlf * 64 + c + 1 > limit) p1 = 0.f;
           }
-          rs += p0 + p1;
-          const bf162 h = __floats2bfloat162_rn(p0, p1);
-          pk[c / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          rs4[(c >> 1) & 3] += p0 + p1;
+          pk[c / 2] = pack_bf16x2_pos(p0, p1);
         }
         tmem_st_32x32(t_s + hlf * 32, pk);
       }
-      l_sum += rs;
+      l_sum += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();

@@ -1,0 +1,40 @@
+// Arithmetic helpers of the attention kernels.  The softmax of a 128 x 128 score tile needs 16384 exponentials and 8192 fp32 -> bf16
+// pair conversions; on the special-function unit (16 lanes per clock per SM) alone that is more time than the tile's two MMAs take.
+// So part of the exponentials is evaluated on the FMA pipes and the conversion is done with integer instructions.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ub {
+
+__device__ __forceinline__ float exp2_mufu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 2^x for x <= 0 without the special-function unit: x = j + f with j = round(x), f in [-0.5, 0.5]; 2^f by a cubic (relative error
+// 7.6e-5, far below bf16 resolution), 2^j by adding j to the exponent field.  Inputs below -126 (including -inf) return about 1e-38.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float magic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  const float t = x + magic;
+  const float f = x - (t - magic);
+  float p = fmaf(0.05521667f, f, 0.24261489f);
+  p = fmaf(p, f, 0.69325271f);
+  p = fmaf(p, f, 0.99992761f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+
+// Two non-negative floats -> packed bf16x2 (a in the low half), rounding half up, on the integer pipes.
+__device__ __forceinline__ uint32_t pack_bf16x2_pos(float a, float b) {
+  return __byte_perm(__float_as_uint(a) + 0x8000u, __float_as_uint(b) + 0x8000u, 0x7632);
+}
+// Any sign: round to nearest even through the integer pipes (NaN not expected).
+__device__ __forceinline__ uint32_t pack_bf16x2_rne(float a, float b) {
+  const uint32_t ua = __float_as_uint(a), ub_ = __float_as_uint(b);
+  return __byte_perm(ua + 0x7FFFu + ((ua >> 16) & 1u), ub_ + 0x7FFFu + ((ub_ >> 16) & 1u), 0x7632);
+}
+
+}  // namespace ub

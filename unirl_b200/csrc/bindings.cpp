@@ -202,16 +202,43 @@ void logprob_dlogits_inplace(Tensor& z, const Tensor& tgt, const Tensor& lse, co
 }
 
 // ---------------------------------------------------------------------------------------------- sampler / optimiser
+// Optional per-row random-stream keys: both [B] int64 on the logits' device, or both absent.
+std::pair<const int64_t*, const int64_t*> rng_keys(const c10::optional<Tensor>& rows, const c10::optional<Tensor>& steps, int64_t B, const torch::Device& dev) {
+  const bool a = rows.has_value() && rows->defined(), b = steps.has_value() && steps->defined();
+  TORCH_CHECK(a == b, "sampler: rng_rows and rng_steps come together");
+  if (!a) return {nullptr, nullptr};
+  TORCH_CHECK(rows->scalar_type() == at::kLong && steps->scalar_type() == at::kLong && rows->numel() >= B && steps->numel() >= B && rows->is_contiguous() &&
+              steps->is_contiguous() && rows->device() == dev && steps->device() == dev, "sampler: rng_rows / rng_steps must be contiguous int64 [B] on the logits' device");
+  return {rows->data_ptr<int64_t>(), steps->data_ptr<int64_t>()};
+}
 std::vector<Tensor> sample_full(const Tensor& logits, double temperature, int64_t seed, int64_t step, const c10::optional<Tensor>& step_tensor,
-                                c10::optional<Tensor> tok_out, c10::optional<Tensor> logp_out) {
+                                c10::optional<Tensor> tok_out, c10::optional<Tensor> logp_out, const c10::optional<Tensor>& rng_rows,
+                                const c10::optional<Tensor>& rng_steps) {
   chk(logits, "logits");
+  const auto rk = rng_keys(rng_rows, rng_steps, logits.size(0), logits.device());
   TORCH_CHECK(logits.dim() == 2, "sample: logits must be [B, V]");
   c10::cuda::CUDAGuard g(logits.device());
   Tensor tok = tok_out.has_value() && tok_out->defined() ? *tok_out : torch::empty({logits.size(0)}, logits.options().dtype(torch::kLong));
   Tensor lp = logp_out.has_value() && logp_out->defined() ? *logp_out : torch::empty({logits.size(0)}, logits.options().dtype(torch::kFloat));
   ub::sample_full(logits.data_ptr(), logits.size(0), logits.size(1), (float)temperature, (uint64_t)seed, step,
                   step_tensor.has_value() && step_tensor->defined() ? step_tensor->data_ptr<int64_t>() : nullptr, tok.data_ptr<int64_t>(),
-                  lp.data_ptr<float>(), dt(logits), stream());
+                  lp.data_ptr<float>(), dt(logits), stream(), rk.first, rk.second);
+  return {tok, lp};
+}
+std::vector<Tensor> sample_truncated(const Tensor& logits, double temperature, int64_t top_k, double top_p, int64_t seed, int64_t step,
+                                     const c10::optional<Tensor>& step_tensor, c10::optional<Tensor> tok_out, c10::optional<Tensor> logp_out,
+                                     const c10::optional<Tensor>& rng_rows, const c10::optional<Tensor>& rng_steps) {
+  chk(logits, "logits");
+  const auto rk = rng_keys(rng_rows, rng_steps, logits.size(0), logits.device());
+  TORCH_CHECK(logits.dim() == 2 && temperature > 0 && logits.size(1) < (int64_t(1) << 18), "sample_truncated: logits [B, V < 2^18], temperature > 0");
+  c10::cuda::CUDAGuard g(logits.device());
+  Tensor tok = tok_out.has_value() && tok_out->defined() ? *tok_out : torch::empty({logits.size(0)}, logits.options().dtype(torch::kLong));
+  Tensor lp = logp_out.has_value() && logp_out->defined() ? *logp_out : torch::empty({logits.size(0)}, logits.options().dtype(torch::kFloat));
+  TORCH_CHECK(tok.scalar_type() == at::kLong && lp.scalar_type() == at::kFloat && tok.numel() == logits.size(0) && lp.numel() == logits.size(0) && tok.is_cuda() && lp.is_cuda(),
+              "sample_truncated: outputs must be int64 / fp32 [B] on the device");
+  ub::sample_truncated(logits.data_ptr(), logits.size(0), logits.size(1), (float)temperature, (int)top_k, (float)top_p, (uint64_t)seed, step,
+                       step_tensor.has_value() && step_tensor->defined() ? step_tensor->data_ptr<int64_t>() : nullptr, tok.data_ptr<int64_t>(), lp.data_ptr<float>(),
+                       dt(logits), stream(), rk.first, rk.second);
   return {tok, lp};
 }
 void adamw_step(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, c10::optional<Tensor> low, c10::optional<Tensor> ema, double lr, double b1,
@@ -372,7 +399,9 @@ std::vector<Tensor> linear_logprob_fwd(const Tensor& h, const Tensor& w, const T
   TORCH_CHECK(rc == 0, "linear_logprob_fwd: launch failure (code ", rc, ")");
   return {logp, lse};
 }
-std::vector<Tensor> linear_sample(const Tensor& h, const Tensor& w, double temperature, int64_t seed, int64_t step, const c10::optional<Tensor>& step_tensor) {
+std::vector<Tensor> linear_sample(const Tensor& h, const Tensor& w, double temperature, int64_t seed, int64_t step, const c10::optional<Tensor>& step_tensor,
+                                  const c10::optional<Tensor>& rng_rows, const c10::optional<Tensor>& rng_steps) {
+  const auto rk = rng_keys(rng_rows, rng_steps, h.size(0), h.device());
   chk(h, "hidden"); chk(w, "weight");
   TORCH_CHECK(h.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && h.size(1) == w.size(1), "linear_sample: bf16 [M,K] x [V,K]");
   c10::cuda::CUDAGuard g(h.device());
@@ -386,7 +415,7 @@ std::vector<Tensor> linear_sample(const Tensor& h, const Tensor& w, double tempe
   const int rc = ub::linear_lse(h.data_ptr(), w.data_ptr(), (int)M, (int)V, (int)K, (int)K, (int)K, nullptr, (float)temperature, pmax.data_ptr<float>(),
                                 psum.data_ptr<float>(), nullptr, pb.data_ptr<float>(), pi.data_ptr<int>(), pz.data_ptr<float>(), (uint64_t)seed, step,
                                 step_tensor.has_value() && step_tensor->defined() ? step_tensor->data_ptr<int64_t>() : nullptr, nullptr,
-                                logp.data_ptr<float>(), tok.data_ptr<int64_t>(), gemm_status_tensor().data_ptr<int>(), stream());
+                                logp.data_ptr<float>(), tok.data_ptr<int64_t>(), gemm_status_tensor().data_ptr<int>(), stream(), rk.first, rk.second);
   TORCH_CHECK(rc == 0, "linear_sample: launch failure (code ", rc, ")");
   return {tok, logp};
 }
@@ -599,7 +628,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("policy_loss_fwd", &policy_loss_fwd);
   m.def("mean_sq_diff_rows", &mean_sq_diff_rows);
   m.def("logprob_dlogits_inplace", &logprob_dlogits_inplace);
-  m.def("sample_full", &sample_full);
+  m.def("sample_full", &sample_full, py::arg("logits"), py::arg("temperature"), py::arg("seed"), py::arg("step"), py::arg("step_tensor") = py::none(),
+        py::arg("tok_out") = py::none(), py::arg("logp_out") = py::none(), py::arg("rng_rows") = py::none(), py::arg("rng_steps") = py::none());
+  m.def("sample_truncated", &sample_truncated, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"), py::arg("seed"), py::arg("step"),
+        py::arg("step_tensor") = py::none(), py::arg("tok_out") = py::none(), py::arg("logp_out") = py::none(), py::arg("rng_rows") = py::none(),
+        py::arg("rng_steps") = py::none());
   m.def("adamw_step", &adamw_step);
   m.def("sum_squares", &sum_squares);
   m.def("sde_sample_fwd", &sde_sample_fwd);
@@ -630,7 +663,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("set_gemm_tile", &ub::set_gemm_tile);
   m.def("linear_logprob_fwd", &linear_logprob_fwd);
-  m.def("linear_sample", &linear_sample);
+  m.def("linear_sample", &linear_sample, py::arg("hidden"), py::arg("weight"), py::arg("temperature"), py::arg("seed"), py::arg("step"),
+        py::arg("step_tensor") = py::none(), py::arg("rng_rows") = py::none(), py::arg("rng_steps") = py::none());
   m.def("decode_workspace_size", &decode_workspace_size);
   m.def("paged_decode_attention", &paged_decode_attention);
   m.def("paged_decode_attention_cascade", &paged_decode_attention_cascade);

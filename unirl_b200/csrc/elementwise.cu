@@ -962,7 +962,8 @@ void logprob_dlogits_inplace(void* z, const int* tgt, const float* lse, const fl
 // One block per row: online (max, sum-exp) of z/T, Gumbel-max draw with Philox keyed on (seed, step, row, col/4).
 template <typename T>
 __global__ void sample_full_kernel(const T* __restrict__ logits, int64_t V, float temperature, uint64_t seed, int64_t step,
-                                   const int64_t* __restrict__ step_tensor, int64_t* __restrict__ tok_out, float* __restrict__ logp_out) {
+                                   const int64_t* __restrict__ step_tensor, int64_t* __restrict__ tok_out, float* __restrict__ logp_out,
+                                   const int64_t* __restrict__ rng_rows, const int64_t* __restrict__ rng_steps) {
   __shared__ float s_val[32];
   __shared__ float s_aux[32];
   __shared__ int s_idx[32];
@@ -970,12 +971,13 @@ __global__ void sample_full_kernel(const T* __restrict__ logits, int64_t V, floa
   const T* z = logits + row * V;
   const bool greedy = temperature <= 0.f;
   const float inv_t = greedy ? 1.f : 1.f / temperature;
-  const uint64_t stp = (uint64_t)(step_tensor ? *step_tensor : step);
+  const uint64_t stp = (uint64_t)(rng_steps ? rng_steps[row] : (step_tensor ? *step_tensor : step));
+  const uint32_t rng_row = rng_rows ? (uint32_t)rng_rows[row] : (uint32_t)row;
   float m = -INFINITY, l = 0.f, best = -INFINITY;
   int best_i = 0;
   for (int64_t c4 = (int64_t)threadIdx.x * 4; c4 < V; c4 += (int64_t)blockDim.x * 4) {
     uint4 rnd = make_uint4(0, 0, 0, 0);
-    if (!greedy) rnd = philox4x32(make_uint4((uint32_t)(c4 >> 2), (uint32_t)row, (uint32_t)stp, (uint32_t)(stp >> 32)),
+    if (!greedy) rnd = philox4x32(make_uint4((uint32_t)(c4 >> 2), rng_row, (uint32_t)stp, (uint32_t)(stp >> 32)),
                                   make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
     const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
 #pragma unroll
@@ -1045,10 +1047,10 @@ __global__ void sample_full_kernel(const T* __restrict__ logits, int64_t V, floa
   }
 }
 void sample_full(const void* logits, int64_t B, int64_t V, float temperature, uint64_t seed, int64_t step, const int64_t* step_tensor,
-                 int64_t* tok, float* logp, int dtype, cudaStream_t s) {
+                 int64_t* tok, float* logp, int dtype, cudaStream_t s, const int64_t* rng_rows, const int64_t* rng_steps) {
   if (B == 0) return;
-  if (dtype == kBF16) sample_full_kernel<bf16><<<(unsigned)B, 1024, 0, s>>>((const bf16*)logits, V, temperature, seed, step, step_tensor, tok, logp);
-  else sample_full_kernel<float><<<(unsigned)B, 1024, 0, s>>>((const float*)logits, V, temperature, seed, step, step_tensor, tok, logp);
+  if (dtype == kBF16) sample_full_kernel<bf16><<<(unsigned)B, 1024, 0, s>>>((const bf16*)logits, V, temperature, seed, step, step_tensor, tok, logp, rng_rows, rng_steps);
+  else sample_full_kernel<float><<<(unsigned)B, 1024, 0, s>>>((const float*)logits, V, temperature, seed, step, step_tensor, tok, logp, rng_rows, rng_steps);
 }
 
 // ===================================================================================== AdamW

@@ -53,6 +53,8 @@ struct GemmParams {
   uint64_t seed;
   const int64_t* step_tensor;
   int64_t step;
+  const int64_t* rng_rows;   // [M] or null: the random stream of row r is keyed on rng_rows[r] instead of r ...
+  const int64_t* rng_steps;  // [M] or null: ... and on rng_steps[r] instead of the common step (draws independent of batch placement)
   int* status;            // [1] error word (0 = ok)
   // ACC_F32 epilogue
   float* Cf;              // [M, ldc] fp32
@@ -333,7 +335,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int n0 = n_idx * BN;
         const int tgt = (row_ok && p.targets) ? p.targets[row] : -1;
         const bool sampling = p.pbest != nullptr;
-        const uint64_t stp = static_cast<uint64_t>(p.step_tensor ? *p.step_tensor : p.step);
+        const uint64_t stp = static_cast<uint64_t>(p.rng_steps ? (row_ok ? p.rng_steps[row] : 0) : (p.step_tensor ? *p.step_tensor : p.step));
+        const uint32_t rng_row = p.rng_rows ? static_cast<uint32_t>(row_ok ? p.rng_rows[row] : 0) : static_cast<uint32_t>(row);
         float mx = -INFINITY, sum = 0.f, best = -INFINITY, best_z = 0.f;
         int best_i = 0;
 #pragma unroll 1
@@ -364,7 +367,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int j4 = 0; j4 < 32; j4 += 4) {
               const int col = n0 + c0 + j4;
-              const uint4 rnd = philox4x32(make_uint4(static_cast<uint32_t>(col >> 2), static_cast<uint32_t>(row), static_cast<uint32_t>(stp),
+              const uint4 rnd = philox4x32(make_uint4(static_cast<uint32_t>(col >> 2), rng_row, static_cast<uint32_t>(stp),
                                                       static_cast<uint32_t>(stp >> 32)),
                                            make_uint2(static_cast<uint32_t>(p.seed), static_cast<uint32_t>(p.seed >> 32)));
               const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
@@ -618,7 +621,7 @@ int lse_num_tiles(int V) { return (V + 255) / 256; }
 // Fused vocab projection + log-softmax statistics.  Workspace: pmax/psum [M, NT] (+ pbest/pbest_idx/pbest_z when sampling).
 int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int ldw, const int* targets, float temperature, float* pmax, float* psum,
                float* tgt_logit, float* pbest, int* pbest_idx, float* pbest_z, uint64_t seed, int64_t step, const int64_t* step_tensor,
-               float* lse_out, float* logp_out, int64_t* tok_out, int* status, cudaStream_t s) {
+               float* lse_out, float* logp_out, int64_t* tok_out, int* status, cudaStream_t s, const int64_t* rng_rows, const int64_t* rng_steps) {
   if (M <= 0) return 0;
   if (K % 8) return 1;
   constexpr int BN = 256;
@@ -628,6 +631,7 @@ int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int l
   p.num_n_tiles = lse_num_tiles(V);
   p.targets = targets; p.inv_temp = 1.f / temperature; p.pmax = pmax; p.psum = psum; p.tgt_logit = tgt_logit;
   p.pbest = pbest; p.pbest_idx = pbest_idx; p.pbest_z = pbest_z; p.seed = seed; p.step = step; p.step_tensor = step_tensor;
+  p.rng_rows = rng_rows; p.rng_steps = rng_steps;
   CUtensorMap tmA, tmB;
   if (!make_tensor_map_bf16(&tmA, H, M, K, ldh, BM) || !make_tensor_map_bf16(&tmB, W, V, K, ldw, BN)) return 1;
   const int rc = launch_variant<BN, kEpiLSE>(tmA, tmB, tmA, p, s);  // no C matrix: the third map is unused

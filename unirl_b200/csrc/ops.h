@@ -64,8 +64,13 @@ void policy_loss_fwd(const float* newlp, const float* oldlp, const float* adv, c
 void mean_sq_diff_rows(const void* a, const void* b, float* out, int64_t R, int64_t C, int dtype, cudaStream_t s);
 void logprob_dlogits_inplace(void* z, const int* tgt, const float* lse, const float* g, int64_t R, int64_t V, float temperature, int dtype,
                              cudaStream_t s);
+// rng_rows / rng_steps (both [B] int64 or both null): key the random stream of row r on (rng_rows[r], rng_steps[r]) instead of (r, step), so the
+// draw of a sequence's t-th token does not depend on which batch row it occupies or how many steps other sequences have taken.
 void sample_full(const void* logits, int64_t B, int64_t V, float temperature, uint64_t seed, int64_t step, const int64_t* step_tensor, int64_t* tok,
-                 float* logp, int dtype, cudaStream_t s);
+                 float* logp, int dtype, cudaStream_t s, const int64_t* rng_rows = nullptr, const int64_t* rng_steps = nullptr);
+void sample_truncated(const void* logits, int64_t B, int64_t V, float temperature, int top_k, float top_p, uint64_t seed, int64_t step,
+                      const int64_t* step_tensor, int64_t* tok, float* logp, int dtype, cudaStream_t s, const int64_t* rng_rows = nullptr,
+                      const int64_t* rng_steps = nullptr);
 void adamw_step(float* master, const void* grad, int grad_dtype, float* m, float* v, void* low, int low_dtype, float* ema, int64_t n, float lr, float b1,
                 float b2, float eps, float wd, int64_t step, float grad_scale, const float* grad_scale_tensor, float ema_decay, cudaStream_t s);
 void sum_squares(const void* x, float* out, int64_t n, int dtype, cudaStream_t s);
@@ -96,7 +101,7 @@ int lse_num_tiles(int V);
 void set_gemm_tile(int bn);
 int linear_lse(const void* H, const void* W, int M, int V, int K, int ldh, int ldw, const int* targets, float temperature, float* pmax, float* psum,
                float* tgt_logit, float* pbest, int* pbest_idx, float* pbest_z, uint64_t seed, int64_t step, const int64_t* step_tensor, float* lse_out,
-               float* logp_out, int64_t* tok_out, int* status, cudaStream_t s);
+               float* logp_out, int64_t* tok_out, int* status, cudaStream_t s, const int64_t* rng_rows = nullptr, const int64_t* rng_steps = nullptr);
 
 // ---- attention_fwd.cu / attention_bwd.cu (tcgen05 flash attention over packed sequences) ---------------------------------
 int flash_attention_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens, void* out, float* lse, int T, int B, int Hq, int Hkv, int D,

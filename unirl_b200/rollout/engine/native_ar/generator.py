@@ -1,6 +1,14 @@
 """Batched autoregressive generation over a paged KV cache with a host-free decode step.
 
-Per wave of sequences:
+Scheduling is continuous (``continuous=True``, the default): up to ``max_running`` sequences decode together; every
+``poll_interval`` steps the host reads the finished flags, retires finished sequences (their pages go back to the allocator),
+admits queued prompts into the freed rows (chunked prefill) and -- once nothing is queued -- compacts the live rows to the front
+and switches to the CUDA graph of a smaller batch-size bucket, so the number of decode steps follows the sum of the response
+lengths instead of (longest response) x (number of waves).  The random stream of a sequence is keyed on (sequence index, token
+index), so its draws do not depend on where or when it runs.  Reference behaviour replaced: one request per sample handed to the
+serving engine's continuous batching (``unirl/rollout/engine/sglang_llm/engine.py:373-581``).
+
+``continuous=False`` keeps fixed waves.  Per wave of sequences:
 
 1. pages for ``prompt + max_new_tokens`` are reserved up front, so block tables are static;
 2. prompts are prefilled *packed* (no padding) in token-budgeted chunks;
@@ -39,8 +47,9 @@ class GenerationOutput:
 class ARGenerator:
     def __init__(self, model: Any, *, page_size: int = 64, max_running: int = 256, prefill_token_budget: int = 16384,
                  kv_cache_tokens: Optional[int] = None, use_cuda_graph: bool = True, poll_interval: int = 64, seed: int = 0,
-                 cache_dtype: Optional[torch.dtype] = None, share_prefix: bool = True):
+                 cache_dtype: Optional[torch.dtype] = None, share_prefix: bool = True, continuous: bool = True):
         self.model = model
+        self.continuous = bool(continuous)
         self.share_prefix = bool(share_prefix)  # samples of one prompt share its KV pages and read them once per decode step
         self.cfg = model.cfg
         self.page_size, self.max_running = int(page_size), int(max_running)
@@ -91,10 +100,14 @@ class ARGenerator:
         steps = 0
         seed = self.seed + self._calls if seed is None else int(seed)
         self._calls += 1
+        if self.continuous and n:
+            t, l, f, steps = self._run_continuous(list(prompts), max_new_tokens, temperature, top_k, top_p, stop_token_ids, seed,
+                                                  None if extras is None else list(extras))
+            return GenerationOutput(t, l, f, steps)
         for lo in range(0, n, self.max_running):
             idx = list(range(lo, min(n, lo + self.max_running)))
-            t, l, f, s = self._run_wave([prompts[i] for i in idx], max_new_tokens, temperature, top_k, top_p, stop_token_ids, seed + lo,
-                                        None if extras is None else [extras[i] for i in idx])
+            t, l, f, s = self._run_wave([prompts[i] for i in idx], max_new_tokens, temperature, top_k, top_p, stop_token_ids, seed,
+                                        None if extras is None else [extras[i] for i in idx], first_id=lo)
             for j, i in enumerate(idx):
                 toks[i], lps[i] = t[j], l[j]
             fin[lo : lo + len(idx)] = f
@@ -103,7 +116,7 @@ class ARGenerator:
 
     # ---- one wave -------------------------------------------------------------------------------------
     def _run_wave(self, prompts: List[torch.Tensor], max_new: int, temperature: float, top_k: int, top_p: float,
-                  stop_ids: Optional[Sequence[int]], seed: int, extras: Optional[List[Any]] = None):
+                  stop_ids: Optional[Sequence[int]], seed: int, extras: Optional[List[Any]] = None, first_id: int = 0):
         dev, ps, b = self.device, self.page_size, len(prompts)
         rope_offset = torch.zeros(b, dtype=torch.long, device=dev)
         plens = [int(p.numel()) for p in prompts]
@@ -163,6 +176,7 @@ class ARGenerator:
         st = _DecodeState(b, max_new, dev)
         st.positions.copy_(torch.tensor(plens, dtype=torch.long))  # index at which the next fed token is written
         st.rope_offset.copy_(rope_offset)
+        st.rng_ids.add_(first_id)  # random streams are keyed on the sequence's index in the whole call
         first_tok, first_lp = self._sample(last_hidden, temperature, top_k, top_p, seed, 0, st)
         st.record(first_tok, first_lp, stop)
         meta = AttnMeta(mode="decode", positions=st.rope_pos, k_cache=cache.k, v_cache=cache.v, block_tables=block_tables,
@@ -189,7 +203,7 @@ class ARGenerator:
             hidden = self.model(st.cur_tokens, meta)
             tok, lp = self._sample(hidden, temperature, top_k, top_p, seed, None, st)
             st.record(tok, lp, stop)
-            st.positions.add_(1)
+            st.advance()
 
         n_steps = 1
         if max_new > 1:
@@ -207,7 +221,253 @@ class ARGenerator:
         out_t, out_l = st.out_tokens.cpu(), st.out_logp.cpu()
         toks = [out_t[k, : int(lens[k])].clone() for k in range(b)]
         lps = [out_l[k, : int(lens[k])].clone() for k in range(b)]
-        return toks, lps, st.finished.cpu(), n_steps
+        stop_set = {int(x) for x in stop.tolist()}
+        done = torch.tensor([bool(int(lens[k])) and int(toks[k][-1]) in stop_set for k in range(b)], dtype=torch.bool)  # False: cut at max_new_tokens
+        return toks, lps, done, n_steps
+
+    # ---- continuous batching ----------------------------------------------------------------------------
+    def _run_continuous(self, prompts: List[torch.Tensor], max_new: int, temperature: float, top_k: int, top_p: float,
+                        stop_ids: Optional[Sequence[int]], seed: int, extras: Optional[List[Any]] = None):
+        """All sequences of the call through one running batch of at most ``max_running`` rows (see the module docstring).
+
+        Sequences are scheduled in *groups*: ``rows`` consecutive samples of one prompt that share its KV pages (1 without sharing).
+        A group holds ``rows`` adjacent batch rows from admission until all its members have finished."""
+        from collections import deque
+
+        dev, ps, n = self.device, self.page_size, len(prompts)
+        plens = [int(p.numel()) for p in prompts]
+        rows = self._shared_rows(prompts) if (extras is None and dev.type == "cuda" and self.share_prefix) else 1
+        n_groups = n // rows
+        cap_g = max(1, min(n_groups, self.max_running // rows))
+        cap = cap_g * rows
+        shared_pages = [(pl // ps if rows > 1 else 0) for pl in plens]
+        own_pages = [math.ceil((pl - sp * ps + max_new) / ps) for pl, sp in zip(plens, shared_pages)]
+        group_pages = [shared_pages[g * rows] + sum(own_pages[g * rows : (g + 1) * rows]) for g in range(n_groups)]
+        cache = self.ensure_cache((sum(sorted(group_pages, reverse=True)[:cap_g]) + 1) * ps)
+        cache.allocator.reset()
+        scratch = int(cache.allocator.allocate(1)[0])  # rows without a sequence point here: their (ignored) KV writes touch no live page
+        max_pages = max(s_ + o for s_, o in zip(shared_pages, own_pages))
+        w_pre, w_suf = max(1, max(shared_pages)), max(own_pages)
+        bt_host = torch.full((cap, max_pages), scratch, dtype=torch.int32)
+        pre_host = torch.full((cap_g, w_pre), scratch, dtype=torch.int32)
+        suf_host = torch.full((cap, w_suf), scratch, dtype=torch.int32)
+        block_tables, pre_t, suf_t = bt_host.to(dev), pre_host.to(dev), suf_host.to(dev)
+        stop = torch.tensor(list(stop_ids) if stop_ids else [self.cfg.eos_token_id], dtype=torch.long, device=dev)
+        stop_set = {int(x) for x in stop.tolist()}
+
+        st = _DecodeState(cap, max_new, dev)
+        st.finished.fill_(True)  # every row starts empty
+        cascade = rows > 1 and dev.type == "cuda"
+        if cascade:
+            st.prefix_len = torch.zeros(cap, dtype=torch.int32, device=dev)
+            st.suffix_lens = torch.zeros(cap, dtype=torch.int32, device=dev)
+        prefix_len_g = torch.zeros(cap_g, dtype=torch.int32, device=dev)
+        max_kv = max(plens) + max_new
+        C = None
+        if dev.type == "cuda":
+            from unirl_b200.ops._ext import ext
+
+            C = ext()
+        layer0 = self.model.layers[0]
+
+        toks: List[Optional[torch.Tensor]] = [None] * n
+        lps: List[Optional[torch.Tensor]] = [None] * n
+        fin_out = torch.zeros(n, dtype=torch.bool)
+        pending = deque(range(n_groups))
+        slot_group: List[Optional[int]] = [None] * cap_g  # group held by every group-slot
+        slot_pages: List[List[int]] = [[] for _ in range(cap_g)]
+
+        def admit(slots: List[int]) -> None:
+            """Give each listed free group-slot the next queued group: pages, prefill, first token."""
+            groups = [pending.popleft() for _ in slots]
+            new_rows: List[int] = []
+            for slot, g in zip(slots, groups):
+                lead_seq = g * rows
+                lead = cache.allocator.allocate(shared_pages[lead_seq]) if shared_pages[lead_seq] else []
+                held = list(lead)
+                pre_host[slot].fill_(scratch)
+                if lead:
+                    pre_host[slot, : len(lead)] = torch.tensor(lead, dtype=torch.int32)
+                for j in range(rows):
+                    seq, row = lead_seq + j, slot * rows + j
+                    own = cache.allocator.allocate(own_pages[seq])
+                    held += list(own)
+                    bt_host[row].fill_(scratch)
+                    suf_host[row].fill_(scratch)
+                    if lead:
+                        bt_host[row, : len(lead)] = torch.tensor(lead, dtype=torch.int32)
+                    bt_host[row, len(lead) : len(lead) + len(own)] = torch.tensor(own, dtype=torch.int32)
+                    suf_host[row, : len(own)] = torch.tensor(own, dtype=torch.int32)
+                    new_rows.append(row)
+                slot_group[slot], slot_pages[slot] = g, held
+            rsel = torch.tensor(new_rows, device=dev)
+            gsel = torch.tensor(slots, device=dev)
+            block_tables[rsel] = bt_host[new_rows].to(dev)
+            suf_t[rsel] = suf_host[new_rows].to(dev)
+            pre_t[gsel] = pre_host[slots].to(dev)
+            # prefill the group leaders, packed, in token-budgeted chunks
+            seq_of_row = [slot_group[r // rows] * rows + r % rows for r in new_rows]  # type: ignore[operator]
+            leaders = [k for k in range(len(new_rows)) if new_rows[k] % rows == 0]
+            hidden_new = torch.empty(len(new_rows), self.cfg.hidden_size, dtype=self.model.embed_tokens.dtype, device=dev)
+            offsets = torch.zeros(len(new_rows), dtype=torch.long, device=dev)
+            i = 0
+            while i < len(leaders):
+                j, tot = i, 0
+                while j < len(leaders) and (j == i or tot + plens[seq_of_row[leaders[j]]] <= self.prefill_token_budget):
+                    tot += plens[seq_of_row[leaders[j]]]
+                    j += 1
+                ks = leaders[i:j]
+                out = torch.empty(len(ks), self.cfg.hidden_size, dtype=hidden_new.dtype, device=dev)
+                deltas = torch.zeros(len(ks), dtype=torch.long, device=dev) if rows == 1 else None
+                self._prefill([prompts[seq_of_row[k]] for k in ks], [plens[seq_of_row[k]] for k in ks], block_tables[rsel[ks]], cache, out,
+                              None if extras is None else [extras[seq_of_row[k]] for k in ks], deltas)
+                for u in range(rows):  # followers start from their leader's last hidden state
+                    hidden_new[torch.tensor([k + u for k in ks], device=dev)] = out
+                if deltas is not None:
+                    offsets[torch.tensor(ks, device=dev)] = deltas
+                i = j
+            if rows > 1:
+                # the prompt's tail (tokens past its last whole page) lives in the leader's first own page: copy it to the followers
+                follow = [k for k in range(len(new_rows)) if new_rows[k] % rows and plens[seq_of_row[k]] % ps]
+                if follow:
+                    src = torch.tensor([int(suf_host[new_rows[k] // rows * rows, 0]) for k in follow], device=dev)
+                    dst = torch.tensor([int(suf_host[new_rows[k], 0]) for k in follow], device=dev)
+                    for layer_k, layer_v in zip(cache.k, cache.v):
+                        layer_k[dst] = layer_k[src]
+                        layer_v[dst] = layer_v[src]
+            # row state + first token
+            ids = torch.tensor(seq_of_row, dtype=torch.long, device=dev)
+            st.positions[rsel] = torch.tensor([plens[q] for q in seq_of_row], dtype=torch.long, device=dev)
+            st.rope_offset[rsel] = offsets
+            st.lengths[rsel] = 0
+            st.rng_ids[rsel] = ids
+            if cascade:
+                st.prefix_len[rsel] = torch.tensor([shared_pages[q] * ps for q in seq_of_row], dtype=torch.int32, device=dev)
+                prefix_len_g[gsel] = torch.tensor([shared_pages[slot_group[sl] * rows] * ps for sl in slots], dtype=torch.int32, device=dev)  # type: ignore[operator]
+            w = self.model.output_weight
+            if dev.type == "cuda":
+                tok, lp = S.linear_sample(hidden_new, w, temperature, top_k, top_p, seed=seed, rng_rows=ids, rng_steps=torch.zeros_like(ids))
+            else:
+                if st.cpu_gen is None:
+                    st.cpu_gen = torch.Generator().manual_seed(seed)
+                tok, lp = S.sample_reference(torch.nn.functional.linear(hidden_new, w), temperature, top_k, top_p, st.cpu_gen)
+            st.out_tokens[rsel, 0] = tok
+            st.out_logp[rsel, 0] = lp.float()
+            st.cur_tokens[rsel] = tok
+            st.lengths[rsel] = 1
+            st.finished[rsel] = (tok.unsqueeze(1) == stop.unsqueeze(0)).any(1) | (max_new <= 1)
+
+        def retire(slot: int) -> None:
+            g = slot_group[slot]
+            lo = slot * rows
+            lens = st.lengths[lo : lo + rows].cpu()
+            out_t, out_l = st.out_tokens[lo : lo + rows].cpu(), st.out_logp[lo : lo + rows].cpu()
+            for j in range(rows):
+                seq = g * rows + j  # type: ignore[operator]
+                toks[seq], lps[seq] = out_t[j, : int(lens[j])].clone(), out_l[j, : int(lens[j])].clone()
+                fin_out[seq] = bool(int(lens[j])) and int(toks[seq][-1]) in stop_set
+            cache.allocator.free(slot_pages[slot])
+            slot_group[slot], slot_pages[slot] = None, []
+            bt_host[lo : lo + rows].fill_(scratch)
+            suf_host[lo : lo + rows].fill_(scratch)
+            pre_host[slot].fill_(scratch)
+            block_tables[lo : lo + rows] = scratch
+            suf_t[lo : lo + rows] = scratch
+            pre_t[slot] = scratch
+            st.positions[lo : lo + rows] = 0
+            if cascade:
+                st.prefix_len[lo : lo + rows] = 0
+                prefix_len_g[slot] = 0
+
+        def compact(n_live_slots: int) -> None:
+            """Move the live group-slots to the front (order kept), so a smaller bucket covers them."""
+            live = [sl for sl in range(cap_g) if slot_group[sl] is not None]
+            dead = [sl for sl in range(cap_g) if slot_group[sl] is None]
+            order = live + dead
+            if order == list(range(cap_g)):
+                return
+            gperm = torch.tensor(order, device=dev)
+            rperm = (gperm.unsqueeze(1) * rows + torch.arange(rows, device=dev)).reshape(-1)
+            for name in _DecodeState._ROW_FIELDS:
+                t = getattr(st, name)
+                if t is not None:
+                    t.copy_(t[rperm])
+            for t in (block_tables, suf_t):
+                t.copy_(t[rperm])
+            pre_t.copy_(pre_t[gperm])
+            prefix_len_g.copy_(prefix_len_g[gperm])
+            hperm = rperm.cpu()
+            bt_host.copy_(bt_host[hperm])
+            suf_host.copy_(suf_host[hperm])
+            pre_host.copy_(pre_host[gperm.cpu()])
+            slot_group[:] = [slot_group[sl] for sl in order]
+            slot_pages[:] = [slot_pages[sl] for sl in order]
+
+        # batch-size buckets: one captured graph each; the running batch only ever shrinks through them
+        buckets = sorted({cap} | {b for b in (cap_g >> k for k in range(1, 8)) for b in [b * rows] if b >= max(8, rows) and b < cap}, reverse=True)
+        runners: Dict[int, Any] = {}
+        ws_floats = 0
+        if C is not None:
+            for b in buckets:
+                ws_floats = max(ws_floats, int(C.decode_cascade_workspace_size(b, rows, layer0.n_q, layer0.n_kv, self.cfg.head_dim, max_kv)) if cascade
+                                else int(C.decode_workspace_size(b, layer0.n_q, self.cfg.head_dim, max_kv)))
+        workspace = torch.empty(ws_floats, dtype=torch.float32, device=dev) if ws_floats else None
+
+        def runner_for(b: int):
+            if b in runners:
+                return runners[b]
+            v = st.view(b)
+            bt_b = block_tables[:b]
+            meta = AttnMeta(mode="decode", positions=v.rope_pos, k_cache=cache.k, v_cache=cache.v, block_tables=bt_b, seq_lens=v.seq_lens,
+                            slot_mapping=v.slots, max_kv_len=max_kv)
+            meta.workspace = workspace
+            if cascade:
+                from types import SimpleNamespace
+
+                meta.cascade = SimpleNamespace(prefix_tables=pre_t[: b // rows], prefix_lens=prefix_len_g[: b // rows], suffix_tables=suf_t[:b],
+                                               suffix_lens=v.suffix_lens, rows=rows)
+
+            def step() -> None:
+                v.prepare(bt_b, ps)
+                hidden = self.model(v.cur_tokens, meta)
+                tok, lp = self._sample(hidden, temperature, top_k, top_p, seed, None, v)
+                v.record(tok, lp, stop)
+                v.advance()
+
+            step()  # one eager step per bucket: one-time kernel attribute / library workspace set-up must not happen under capture
+            runners[b] = self._graphed(step, b, max_new, temperature, top_k, top_p) if self.use_cuda_graph else step
+            return runners[b]
+
+        admit(list(range(min(cap_g, len(pending)))))
+        b_act, n_steps = cap, 1
+        while True:
+            live_slots = [sl for sl in range(cap_g) if slot_group[sl] is not None]
+            if not live_slots and not pending:
+                break
+            fresh = b_act not in runners
+            run = runner_for(b_act)
+            burst = self.poll_interval - (1 if fresh else 0)
+            for _ in range(max(0, burst)):
+                run()
+            n_steps += self.poll_interval
+            fin = st.finished[:b_act].cpu().view(-1, rows).all(1)  # the one D2H read per `poll_interval` steps
+            freed = [sl for sl in range(b_act // rows) if slot_group[sl] is not None and bool(fin[sl])]
+            for sl in freed:
+                retire(sl)
+            if pending:
+                free = [sl for sl in range(b_act // rows) if slot_group[sl] is None][: len(pending)]
+                if free:
+                    admit(free)
+            else:
+                n_live = sum(1 for sl in range(cap_g) if slot_group[sl] is not None)
+                smaller = [b for b in buckets if b < b_act and b >= n_live * rows]
+                if n_live and smaller:
+                    compact(n_live)
+                    b_act = min(smaller)
+        fused = getattr(getattr(self.model, "tp", None), "fused", None)
+        if fused is not None:
+            fused.align()
+        return toks, lps, fin_out, n_steps
 
     def _shared_rows(self, prompts: List[torch.Tensor]) -> int:
         """How many consecutive sequences can share a prefix job: the largest R in {4, 2} such that the batch is made of chunks of R
@@ -243,7 +503,8 @@ class ARGenerator:
         """Vocab projection + sampling of the last hidden states (fused on CUDA; see ``ops.sampling.linear_sample``)."""
         w = self.model.output_weight
         if hidden.is_cuda:
-            return S.linear_sample(hidden, w, temperature, top_k, top_p, seed=seed, step=0 if step is None else step, step_tensor=st.step_counter)
+            return S.linear_sample(hidden, w, temperature, top_k, top_p, seed=seed, step=0 if step is None else step, step_tensor=st.step_counter,
+                                   rng_rows=st.rng_ids, rng_steps=st.lengths)
         if st.cpu_gen is None:
             st.cpu_gen = torch.Generator().manual_seed(seed)
         return S.sample_reference(torch.nn.functional.linear(hidden, w), temperature, top_k, top_p, st.cpu_gen)
@@ -289,8 +550,27 @@ class _DecodeState:
         self.finished = z(torch.bool, b)
         self.step_counter = z(torch.long, 1)
         self.rows = torch.arange(b, device=dev)
+        self.rng_ids = torch.arange(b, device=dev)  # sequence index that keys the row's random stream (with `lengths` as the token index)
         self.max_new = max_new
         self.cpu_gen: Optional[torch.Generator] = None
+
+    _ROW_FIELDS = ("out_tokens", "out_logp", "cur_tokens", "positions", "slots", "rope_offset", "rope_pos", "seq_lens", "lengths", "finished", "rng_ids",
+                   "prefix_len", "suffix_lens")
+
+    def view(self, b: int) -> "_DecodeState":
+        """The first ``b`` rows as a state of their own (tensors are views: a CUDA graph captured on them follows later in-place updates)."""
+        v = object.__new__(_DecodeState)
+        v.__dict__.update(self.__dict__)
+        for name in self._ROW_FIELDS:
+            t = getattr(self, name)
+            setattr(v, name, None if t is None else t[:b])
+        v.rows = self.rows[:b]
+        return v
+
+    def advance(self) -> None:
+        """Move every LIVE row to its next cache index; a finished row stays where it is (it keeps rewriting one slot of its own pages
+        until it is retired, instead of walking past the pages reserved for it)."""
+        self.positions.add_((~self.finished).long())
 
     def record(self, tok: torch.Tensor, lp: torch.Tensor, stop: torch.Tensor) -> None:
         """Append the sampled token for every unfinished row, then latch EOS."""
