@@ -88,6 +88,11 @@ def parse_cli(argv: Sequence[str]) -> Tuple[Optional[str], Optional[str], List[s
             next(it, None)
         elif a == "--resolve":
             flags["resolve"] = True
+        elif a == "--profile":  # bracket a window of steps for a profiler and emit NVTX ranges (utils/profiling.py)
+            overrides.append("+profile.enabled=true")
+        elif a.startswith("--profile="):  # --profile=START:COUNT
+            st, _, cnt = a.split("=", 1)[1].partition(":")
+            overrides += ["+profile.enabled=true", f"+profile.start_step={int(st or 3)}", f"+profile.num_steps={int(cnt or 1)}"]
         elif a.endswith((".yaml", ".yml")) and name is None and "=" not in a:
             name = a
         else:

@@ -318,13 +318,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const int qi = hlf * 64 + c + e;
             const float q_lse = stat[qi], q_delta = stat[kTile + qi];  // same address in every lane: one broadcast read, vectorised by the compiler
             const float xarg = fmaf(s[c + e], p.scale_log2, -q_lse);
-            float pv = e == 0 ? exp2_mufu(xarg) : exp2_poly(xarg);  // half of the exponentials on the FMA pipes (see attn_math.cuh)
+            float pv = exp2_mufu(xarg);
             if (!key_ok || (diag && qt0 + qi < kpos)) pv = 0.f;
             pr[e] = pv;
             ds[e] = pv * (dp[c + e] - q_delta) * p.scale;
           }
-          pp[c / 2] = pack_bf16x2_pos(pr[0], pr[1]);
-          dd[c / 2] = pack_bf16x2_rne(ds[0], ds[1]);
+          pp[c / 2] = pack_bf16x2_cvt(pr[0], pr[1]);
+          dd[c / 2] = pack_bf16x2_cvt(ds[0], ds[1]);
         }
         tmem_st_32x32(tmem_base + kColS + lane_off + hlf * 32, pp);
         tmem_st_32x32(tmem_base + kColdP + lane_off + hlf * 32, dd);

@@ -27,6 +27,12 @@ __device__ __forceinline__ float exp2_poly(float x) {
   return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
+// Two floats -> packed bf16x2 (a in the low half) with the conversion instruction.
+__device__ __forceinline__ uint32_t pack_bf16x2_cvt(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
 // Two non-negative floats -> packed bf16x2 (a in the low half), rounding half up, on the integer pipes.
 __device__ __forceinline__ uint32_t pack_bf16x2_pos(float a, float b) {
   return __byte_perm(__float_as_uint(a) + 0x8000u, __float_as_uint(b) + 0x8000u, 0x7632);

@@ -404,6 +404,14 @@ class DevicePool:
     def reset_transfer_queue_buffers(self) -> None:
         """Per-rollout reclaim hook of the queue transport; the worker-local store frees by refcount."""
 
+    def local_role(self, handle: Any) -> Any:
+        """The role object behind ``handle`` when it lives in this process (inline and spmd pools), else ``None``.  For read-only
+        inspection by the driver (metrics); calls still go through the handle."""
+        lw = self.local_worker
+        if lw is None and self.backend == "inline" and self.workers:
+            lw = getattr(self.workers[0], "worker", None) or (self.workers[0] if hasattr(self.workers[0], "_roles") else None)
+        return None if lw is None else getattr(lw, "_roles", {}).get(getattr(handle, "role_name", None))
+
     # ---- roles -----------------------------------------------------------------------------------------
     def create_remote(self, role_cls: Any, devices: Sequence[int], role_name: Optional[str] = None,
                       parallel: Optional[Dict[str, int]] = None, **init_kwargs: Any) -> Any:

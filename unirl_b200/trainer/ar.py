@@ -143,8 +143,38 @@ class ARTrainer(BaseTrainer):
                 t.segment._set_cu(track.segment.cu_seqlens)
         self.wandb_logger.log_rollout_step(rollout_id, result, light, step_time_s=time.perf_counter() - t0,
                                            trunc_len=getattr(self.sampling_params, "max_new_tokens", None),
-                                           timings=None, sync_stats=sync_stats, device_ms=dict(self.phase_timer.device_ms))
+                                           timings=None, sync_stats=sync_stats, device_ms=dict(self.phase_timer.device_ms),
+                                           roofline=self._roofline_info(req))
         return result, mean_reward
+
+    def _roofline_info(self, req: Any) -> Optional[Dict[str, Any]]:
+        """Static inputs of the per-step roofline metrics, when the bundle lives in this process (inline / spmd pools)."""
+        info = getattr(self, "_roofline_static", None)
+        if info is None:
+            info = {}
+            try:
+                bundle = self.pool.local_role(self.bundle) if hasattr(self.pool, "local_role") else None
+                model = getattr(bundle, "transformer", None)
+                if model is not None:
+                    cfg = model.cfg
+                    n = sum(p.numel() for name, p in model.named_parameters() if not name.startswith("embed_tokens"))
+                    info = {"n_params": n, "kv_bytes_per_token": 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim * 2}
+            except Exception:  # noqa: BLE001 - metrics only
+                info = {}
+            self._roofline_static = info
+        if not info:
+            return None
+        out = dict(info)
+        try:
+            pt = req.primitives.get("prompt_tokens") if hasattr(req, "primitives") else None
+            mask = getattr(pt, "attention_mask", None)
+            if mask is not None:
+                out["prompt_len_mean"] = float(mask.float().sum(-1).mean())
+        except Exception:  # noqa: BLE001
+            pass
+        world = max(1, int(getattr(self, "num_devices", 1)))
+        out["decode_batch"] = max(1, len(getattr(req, "sample_ids", [])) // world)
+        return out
 
     def evaluate(self, rollout_id: int) -> float:
         inputs = self.data_source.get_eval_samples(self.eval_num_prompts)

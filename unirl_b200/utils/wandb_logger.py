@@ -35,6 +35,9 @@ STEP_PHASE_SPECS: Tuple[Tuple[str, str, str], ...] = (
 _STEP_PHASE_SPECS = STEP_PHASE_SPECS
 
 
+from unirl_b200.utils.profiling import nvtx_range  # noqa: E402
+
+
 class PhaseTimer:
     def __init__(self) -> None:
         self.timings = PhaseTimings()
@@ -54,7 +57,8 @@ class PhaseTimer:
                 ev[0].record()
             t0 = time.perf_counter()
             try:
-                return fn(*a, **k)
+                with nvtx_range(f"phase/{phase}"):
+                    return fn(*a, **k)
             finally:
                 self.timings.add(phase, time.perf_counter() - t0)
                 if ev is not None:
@@ -79,12 +83,25 @@ def install_phase_timing(trainer: Any) -> PhaseTimer:
             if callable(fn) and not getattr(fn, "_phase_timed", False):
                 setattr(obj, method, timer.wrap(phase, fn))
 
+    from unirl_b200.utils.profiling import ProfileWindow
+
+    cfg = getattr(trainer, "cfg", None)
+    window = ProfileWindow.from_cfg(cfg.get("profile") if hasattr(cfg, "get") else None)
+    trainer.profile_window = window
+    calls = [0]
+
     @functools.wraps(inner)
     def train_step(*a: Any, **k: Any) -> Any:
         _wrap_collaborators()
         timer.reset()
+        window.step_begin(calls[0])
         t0 = time.perf_counter()
-        out = inner(*a, **k)
+        try:
+            with nvtx_range(f"train_step/{calls[0]}"):
+                out = inner(*a, **k)
+        finally:
+            window.step_end(calls[0])
+            calls[0] += 1
         timer.timings.step_time_s = time.perf_counter() - t0
         trainer.last_phase_timings = timer.timings
         return out
@@ -131,7 +148,7 @@ class UniRLWandBLogger:
 
     def log_rollout_step(self, rollout_id: int, result: Any, resp: Any, *, step_time_s: float, trunc_len: Optional[int] = None,
                          timings: Optional[PhaseTimings] = None, sync_stats: Optional[Dict[str, float]] = None,
-                         device_ms: Optional[Dict[str, float]] = None) -> Dict[str, Any]:
+                         device_ms: Optional[Dict[str, float]] = None, roofline: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
         step = rollout_id + 1
         row: Dict[str, Any] = {"rollout/step": step, "perf/step_time_s": float(step_time_s)}
         n_samples = n_tokens = 0
@@ -164,6 +181,20 @@ class UniRLWandBLogger:
             row[f"perf/{k}_device_ms"] = float(v)
         for k, v in (sync_stats or {}).items():
             row[f"sync/{k}"] = float(v)
+        if roofline and device_ms:
+            # device-timed phases against the measured peaks: kernel/train_roofline_frac, kernel/decode_roofline_frac (utils/profiling.py)
+            from unirl_b200.utils.profiling import roofline_metrics
+
+            lens_all = [getattr(t.segment, "lengths", None) for t in getattr(resp, "tracks", {}).values() if t.segment is not None]
+            lens_all = [x for x in lens_all if isinstance(x, torch.Tensor) and x.numel()]
+            if lens_all:
+                resp_lens = torch.cat([x.float().cpu() for x in lens_all])
+                prompt_mean = float(roofline.get("prompt_len_mean", 0.0))
+                row.update(roofline_metrics(n_params=int(roofline["n_params"]), train_tokens=int(resp_lens.sum() + prompt_mean * resp_lens.numel()),
+                                            train_ms=float(device_ms.get("train", 0.0)), decode_tokens=int(resp_lens.sum()), decode_steps=int(resp_lens.max()),
+                                            rollout_ms=float(device_ms.get("rollout", 0.0)), kv_bytes_per_token=int(roofline.get("kv_bytes_per_token", 0)),
+                                            mean_context=prompt_mean + float(resp_lens.max()) / 2, batch=int(roofline.get("decode_batch", resp_lens.numel())),
+                                            weight_bytes=roofline.get("weight_bytes")))
         self._emit(row)
         per_update = getattr(result, "per_update", ()) or ({**dict(getattr(result, "metrics", {})), "loss": getattr(result, "loss", 0.0),
                                                             "grad_norm": getattr(result, "grad_norm", 0.0)},)
