@@ -65,3 +65,48 @@ def test_unified_trainer_one_step_for_two_tracks(tmp_path):
         assert (tmp_path / "rollout_000000.jsonl").exists()
     finally:
         tr.shutdown()
+
+
+@pytest.mark.timeout(600)
+def test_unified_trainer_with_an_engine_pair_and_the_memory_choreography(tmp_path):
+    """Two engines with weights of their own: extract → offload → wake → push → rollout (P → P·N → P·N·M) → sleep → onload → train.
+    The adapter the engines hold after a synced step equals the trainer's; rewrites earn the mean reward of their images."""
+    import json
+
+    from unirl_b200.train_unified_model import main
+
+    calls = []
+    cfg = compose("unified_model/tiny_unified_two_engines_cpu", overrides=[])
+    tr = UnifiedModelTrainer(cfg=cfg, batch_size=cfg.batch_size, bundle_cfg=cfg.bundle, pipeline_cfg=cfg.pipeline, backend_cfg=cfg.backend,
+                             ar_rollout_cfg=cfg.ar_rollout, dit_rollout_cfg=cfg.dit_rollout, sync_cfg=cfg.sync, enable_fsdp_offload=True,
+                             reward_cfg=cfg.reward, ar_algorithm_cfg=cfg.ar_algorithm, image_algorithm_cfg=cfg.image_algorithm, stack_cfg=cfg.stack,
+                             data_source_cfg=cfg.data_source, sampling_cfg=cfg.sampling, logging_cfg=None, rollout_dump_dir=str(tmp_path))
+    try:
+        for name in ("offload", "onload"):  # record the order of the choreography
+            inner = getattr(tr.backend, name)
+            setattr(tr.backend, name, (lambda inner=inner, name=name: (calls.append(name), inner())[1]))
+        for tag, eng in (("ar", tr.ar_rollouts[0]), ("dit", tr.dit_rollouts[0])):
+            for name in ("wake_up", "sleep", "set_lora_from_tensors"):
+                inner = getattr(eng, name)
+                setattr(eng, name, (lambda *a, inner=inner, n=f"{tag}.{name}", **k: (calls.append(n), inner(*a, **k))[1]))
+        tr.train(num_rollouts=2)
+        first = calls[: calls.index("offload", 2) + 1] if calls.count("offload") > 1 else calls
+        assert first[:2] == ["onload", "offload"], first  # extract with the trainer resident, then make room
+        assert first.index("ar.wake_up") > first.index("offload") and first.index("ar.set_lora_from_tensors") > first.index("dit.wake_up")
+        assert first.index("ar.sleep") > first.index("dit.set_lora_from_tensors") and first.index("onload", 1) > first.index("dit.sleep")
+        rows = [json.loads(l) for l in open(tmp_path / "rollout_000001.jsonl")]
+        ar = [r for r in rows if r.get("track") == "ar"]
+        img = [r for r in rows if r.get("track") == "image"]
+        assert len(ar) == 2 * 2 and len(img) == 2 * 2 * 2  # P·N rewrites, P·N·M images
+        for a in ar:
+            kids = [i["reward"] for i in img if i["parent_id"] == a["sample_id"]]
+            assert len(kids) == 2 and abs(a["reward"] - sum(kids) / 2) < 1e-5
+        # the engines' adapters follow the trainer's (second step synced after the first optimizer step)
+        tr.backend.onload()
+        mine = {k: v for k, v in tr.backend.compute_local_param_checksums()[0].items() if "lora_" in k}
+        theirs = {k: v for k, v in tr.dit_rollouts[0].compute_local_param_checksums()[0].items() if "lora_" in k}
+        assert mine and len(theirs) == len(mine)
+        train_rows = [r for r in tr.wandb_logger.history if "train/step" in r]
+        assert len(train_rows) == 2 and any(k.startswith("train/ar/") for k in train_rows[0]) and any(k.startswith("train/image/") for k in train_rows[0])
+    finally:
+        tr.shutdown()

@@ -21,7 +21,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import Any, List, Optional, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -176,6 +176,21 @@ class _ParamSet(nn.Module):
         self.q_norm, self.k_norm = _p(d, dtype=dtype, device=device), _p(d, dtype=dtype, device=device)
         self.o = _p(h, c.num_heads * d, dtype=dtype, device=device)
         self.ffn = MoEFFN(c, dtype, device) if c.num_experts else _FFN(h, c.intermediate_size, dtype, device)
+        self._rows = (c.num_heads * d, c.num_kv_heads * d, h)
+
+    def lora_targets(self) -> Dict[str, Tuple[str, int, int]]:
+        """Adapter targets of the attention projections: named row ranges of the fused weights (the unified model is trained with one
+        LoRA over its shared backbone, ``unirl/trainer/unified_model.py:133``)."""
+        nq, nkv, h = self._rows
+        return {"q_proj": ("qkv", 0, nq), "k_proj": ("qkv", nq, nkv), "v_proj": ("qkv", nq + nkv, nkv), "qkv": ("qkv", 0, nq + 2 * nkv), "o_proj": ("o", 0, h)}
+
+    def proj(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        y = linear(x, getattr(self, name))
+        if getattr(self, "_lora_index", None):
+            from unirl_b200.train.inject import lora_apply
+
+            y = lora_apply(self, name, x, y)
+        return y
 
 
 class UnifiedLayer(nn.Module):
@@ -199,7 +214,7 @@ class UnifiedLayer(nn.Module):
         c = self.c
         b, l, _ = x.shape
         nq, nkv, d = c.num_heads, c.num_kv_heads, c.head_dim
-        qkv = self._route(x, gen, lambda s, t: linear(rmsnorm(t.reshape(-1, t.shape[-1]), s.norm1, c.eps).view(t.shape), s.qkv))
+        qkv = self._route(x, gen, lambda s, t: s.proj(rmsnorm(t.reshape(-1, t.shape[-1]), s.norm1, c.eps).view(t.shape), "qkv"))
         q, k, v = qkv.split([nq * d, nkv * d, nkv * d], -1)
         q, k, v = q.view(b, l, nq, d), k.view(b, l, nkv, d), v.view(b, l, nkv, d)
         s0 = self.sets[0]
@@ -212,7 +227,7 @@ class UnifiedLayer(nn.Module):
             cache["k"], cache["v"] = k, v
         a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask, enable_gqa=nq != nkv)
         a = a.transpose(1, 2).reshape(b, l, nq * d)
-        x = x + self._route(a, gen, lambda s, t: linear(t, s.o))
+        x = x + self._route(a, gen, lambda s, t: s.proj(t, "o"))
         return x + self._route(x, gen, lambda s, t: s.ffn(rmsnorm(t.reshape(-1, t.shape[-1]), s.norm2, c.eps).view(t.shape)))
 
 

@@ -129,7 +129,10 @@ class UnifiedPipeline(Pipeline):
         strs = [t.to_str() for t in texts.to_list()]
         tracks: Dict[str, RolloutTrack] = {}
         image_cond = (req.request_conditions or {}).get("image")
-        wants_text = mode in ("t2t", "i2t") or bool(self.bundle.config.recaption)
+        cot = req.primitives.get("cot_text")  # a rewrite produced elsewhere (the AR engine of a two-engine rollout): condition on it, do not regenerate
+        wants_text = mode in ("t2t", "i2t") or (bool(self.bundle.config.recaption) and cot is None)
+        if cot is not None:
+            strs = [f"{s} {c.to_str()}".strip() for s, c in zip(strs, cot.to_list())]
         if wants_text:
             ar = get_ar_params(req.sampling_params) or ARSamplingParams(max_new_tokens=32)
             conds = UnifiedConditions(prompt=self._tokens(strs), image=image_cond)

@@ -123,7 +123,8 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
                            device=c.device or self.device, init_seed=c.init_seed, **c.pipeline_overrides)
             self.pipeline = pipe_cls.from_config(pcfg)
             if self._trainer_pipeline is not None:  # start from the trainer's weights
-                self._load_named({n: p.detach() for n, p in self._trainer_pipeline.bundle.transformer.named_parameters()})
+                # base weights only: adapters arrive through set_lora_from_tensors
+                self._load_named({n: p.detach() for n, p in self._trainer_pipeline.bundle.transformer.named_parameters() if ".lora." not in n})
             self.pipeline.bundle.transformer.eval().requires_grad_(False)
         self.schedule_policy = self.pipeline.build_schedule_policy()
         if c.use_cuda_graph and torch.device(self.device or "cpu").type == "cuda":
@@ -132,7 +133,7 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
     # ---- generate -------------------------------------------------------------------------------------------
     def _regions(self) -> Dict[str, Sequence[torch.nn.Module]]:
         b = self.pipeline.bundle
-        return {"transformer": [b.transformer], "text_encoder": list(b.text_encoders), "vae": [b.vae]}
+        return {"transformer": [b.transformer], "text_encoder": list(getattr(b, "text_encoders", ()) or ()), "vae": [b.vae] if getattr(b, "vae", None) is not None else []}
 
     @distributed(dispatch_mode=Dispatch.DP_SCATTER)
     def generate(self, req: RolloutReq) -> RolloutResp:
@@ -262,6 +263,7 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
     @distributed(dispatch_mode=Dispatch.BROADCAST)
     def set_lora_from_tensors(self, adapter_name: str, lora_tensors: Dict[str, torch.Tensor], *, peft_config: Optional[dict] = None) -> int:
         """Install / refresh LoRA adapters from in-memory tensors keyed ``<module path>.<target>.lora_{A,B}.<adapter>.weight``."""
+        lora_tensors = getattr(lora_tensors, "value", lora_tensors)  # payloads pushed through the controller travel in an opaque wrapper
         from unirl_b200.train import inject
 
         model = self.pipeline.bundle.transformer
