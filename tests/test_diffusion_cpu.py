@@ -126,9 +126,11 @@ def test_secondary_benchmark_script_runs_on_cpu():
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, os.path.join(root, "bench_diffusion.py"), "--device", "cpu", "--preset", "tiny-sd3", "--prompts-per-gpu", "1",
-           "--samples-per-prompt", "4", "--micro-batch", "4", "--resolution", "64", "--inference-steps", "4", "--steps", "1", "--warmup", "1",
-           "reward.backend.in_channels=4", "+reward.backend.width=8", "backend.fsdp_cfg.activation_checkpointing=false"]
+           "--samples-per-prompt", "4", "--micro-batch", "4", "--resolution", "64", "--inference-steps", "4", "--train-timesteps", "2", "--text-len", "7",
+           "--steps", "1", "--warmup", "1", "reward.backend.in_channels=4", "+reward.backend.width=8", "backend.fsdp_cfg.activation_checkpointing=false",
+           "backend.lora_cfg.rank=4", "backend.lora_cfg.alpha=8"]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=500, cwd=root)
     assert out.returncode == 0, out.stderr[-2000:]
     row = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
     assert row["metric"] == "flowdppo_samples_per_s" and row["value"] > 0 and row["config"]["samples_per_prompt"] == 4 and row["steps"] == 1
+    assert row["config"]["trained_timesteps"] == 2 and row["config"]["text_tokens"] == 7 and row["e2e"]["h2d_bytes_per_step"] > 0 and row["lora_sync_ms"] > 0

@@ -228,3 +228,86 @@ def test_two_rank_fused_collectives_match_library():
         assert o["param_diff"] <= 1e-2, o  # bf16 replicas after 3 steps
         assert o["replica_diff"] == 0.0, o  # every rank holds the same replica
         assert o["ulysses_diff"] == 0.0, o  # the exchange only moves data: both paths must agree bit for bit
+
+
+def test_gemm_with_allreduce_epilogue_data_path_one_device():
+    """The GEMM whose epilogue pushes its partial into every rank's staging area and sums all partials: data path on one device (the
+    "ranks" are arenas of this device, run one after the other; their flag areas are pre-filled so that no rank waits)."""
+    C = _C()
+    torch.manual_seed(3)
+    W, M, N, K = 4, 96, 2560, 1024
+    slot = 128 * N
+    stage_elems, flag_words = 2 * W * slot, W * 1024
+    arenas = [torch.zeros(stage_elems * 2 + flag_words * 4 + 256, dtype=torch.uint8, device="cuda") for _ in range(W)]
+    stages = [a[: stage_elems * 2].view(torch.bfloat16) for a in arenas]
+    flags = [a[stage_elems * 2 : stage_elems * 2 + flag_words * 4].view(torch.int32) for a in arenas]
+    for f in flags:
+        f.fill_(BIG)
+    xs = [(torch.randn(M, K, device="cuda") * 0.3).bfloat16() for _ in range(W)]
+    ws = [(torch.randn(N, K, device="cuda") * 0.05).bfloat16() for _ in range(W)]
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    want = sum((x.float() @ w.float().t()).bfloat16().float() for x, w in zip(xs, ws)) + res.float()
+    outs = []
+    for rnd in range(2):  # first round fills every slot; second round (fresh epoch words) sees all partials
+        for r in range(W):
+            state = torch.zeros(8, dtype=torch.int32, device="cuda")
+            pad = torch.full((64,), BIG, dtype=torch.int32, device="cuda")
+            pc = C.PeerComm([a.data_ptr() for a in arenas], [pad.data_ptr()] * W, r, state, 5.0)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            C.gemm_skinny_allreduce(pc, stages[r], flags[r], xs[r], ws[r], res, out)
+            torch.cuda.synchronize()
+            assert int(state[4]) == 0 and int(state[0]) == 1, "no wait may time out; the epoch word advances by one"
+            if rnd == 1:
+                outs.append(out)
+    for out in outs:
+        _close = (out.float() - want).abs().max().item()
+        assert _close < 0.1, _close
+        assert torch.equal(out, outs[0]), "every rank must produce the same bits"
+
+
+def _gemm_allreduce_body(rank, world):
+    import torch.distributed as dist
+
+    from unirl_b200.distributed.group.comm import Comm
+    from unirl_b200.parallel.fused_collectives import FusedAllReduce
+
+    dev = torch.device("cuda", rank)
+    comm = Comm.world()
+    H, K = 2560, 2048
+    far = FusedAllReduce(comm, max_tokens=512, hidden=H, device=dev, wait_s=10.0)
+    out = {"max_err": 0.0, "rank_diff": 0.0, "fused_calls": 0}
+    torch.manual_seed(11 + rank)
+    w = (torch.randn(H, K, device=dev) * 0.05).bfloat16()
+    nw = (1 + 0.1 * torch.randn(H, device=dev)).bfloat16()
+    dist.broadcast(nw, 0)
+    for T in (1, 64, 128, 200, 256):
+        for rep in range(3):  # consecutive calls alternate the staging halves
+            x = (torch.randn(T, K, device=dev) * 0.3).bfloat16()
+            res = torch.randn(T, H, device=dev).bfloat16()
+            dist.broadcast(res, 0)
+            xo, ho = far.proj_reduce_norm(x, w, res, nw, 1e-6)
+            ref = (x.float() @ w.float().t()).bfloat16().float()
+            dist.all_reduce(ref)
+            ref = ref + res.float()
+            out["max_err"] = max(out["max_err"], float((xo.float() - ref).abs().max()))
+            gathered = [torch.empty_like(xo) for _ in range(world)]
+            dist.all_gather(gathered, xo)
+            out["rank_diff"] = max(out["rank_diff"], max(float((g.float() - xo.float()).abs().max()) for g in gathered))
+            hf = xo.float()
+            href = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+            out["max_err"] = max(out["max_err"], float((ho.float() - href).abs().max()) * 0.5)
+    far.arena.check()
+    out["fused_calls"] = far.fused_calls
+    return out
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gemm_with_allreduce_epilogue_matches_library(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
+    outs = run_ranks(_gemm_allreduce_body, world, cuda=True, timeout=300)
+    for o in outs:
+        assert o["fused_calls"] == 15, o  # every call went through the GEMM with the all-reduce epilogue
+        assert o["max_err"] < 0.15, o
+        assert o["rank_diff"] == 0.0, o  # tensor-parallel ranks must hold identical activations

@@ -19,7 +19,6 @@
 // zero fill) and are never stored; keys beyond the end (or above the diagonal under the causal mask) get probability zero.
 // Every mbarrier wait is bounded and watches a CTA-wide abort flag: on expiry the role records a code in `status`, raises the flag,
 // every role leaves its loop, TMEM is released and the kernel returns.
-#include "attn_math.cuh"
 #include "common.cuh"
 #include "ops.h"
 #include "tcgen05.cuh"
@@ -105,17 +104,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-
-// Which unit evaluates the exponentials of a pair and how the pair is packed to bf16 (measured choices; see attn_math.cuh).
-#ifndef FA_EXP0
-#define FA_EXP0 exp2_mufu
-#endif
-#ifndef FA_EXP1
-#define FA_EXP1 exp2_mufu
-#endif
-#ifndef FA_PACK
-#define FA_PACK pack_bf16x2_cvt
-#endif
 
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 1)
@@ -302,32 +290,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // keys beyond the end of the sequence, and keys above the diagonal, are masked; whole tiles below both limits skip the test
       const int limit = p.causal ? min(seq_len - 1, qpos) : seq_len - 1;  // last visible key of this row
       const bool need_mask = kv0 + kTileKV - 1 > (p.causal ? min(seq_len - 1, q0 + tile * kTileQ) : seq_len - 1);
-      // The S row is read twice, 32 columns at a time (TMEM reads are cheap, registers are not), and every read is issued one chunk
-      // ahead of its use, so the TMEM latency hides behind the arithmetic of the previous chunk.
-      float ra[32], rb[32];
-      auto chunk_max = [&](const float* s, int c0, float acc) {
-        float m4[4] = {acc, -INFINITY, -INFINITY, -INFINITY};
+      // Pass 1: the row maximum.  The S row is read 64 columns at a time (twice in total: TMEM reads are cheap, registers are not).
+      float mx = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float v = (need_mask && kv0 + c0 + c > limit) ? -INFINITY : s[c];
-          m4[c & 3] = fmaxf(m4[c & 3], v);
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        float s[64];
+        tmem_ld_32x32(t_s + hlf * 64, s);
+        tmem_ld_32x32(t_s + hlf * 64 + 32, s + 32);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (kv0 + hlf * 64 + c > limit) s[c] = -INFINITY;
         }
-        return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      };
-      // ---- pass 1: row maximum
-      tmem_ld_32x32(t_s, ra);
-      tmem_ld_wait();
-      tmem_ld_32x32(t_s + 32, rb);
-      float mx = chunk_max(ra, 0, -INFINITY);
-      tmem_ld_wait();
-      tmem_ld_32x32(t_s + 64, ra);
-      mx = chunk_max(rb, 32, mx);
-      tmem_ld_wait();
-      tmem_ld_32x32(t_s + 96, rb);
-      mx = chunk_max(ra, 64, mx);
-      tmem_ld_wait();
-      tmem_ld_32x32(t_s, ra);  // first chunk of pass 2
-      mx = chunk_max(rb, 96, mx);
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, s[c]);
+      }
       mx *= p.scale_log2;
       // lazy maximum: keep the value in use unless this row's maximum outgrew it by more than the threshold
       const bool grow = mx > m_used + kRescaleThreshold;
@@ -347,37 +325,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       m_used = m_new;
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;  // a row with no visible key so far: every s is -inf, p = 0
-      // ---- pass 2: probabilities.  P (bf16, two per column) overwrites S from column 0; the 32 columns stored after two chunks lie
-      // inside the 64 columns already consumed, and every thread touches its own row only.
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[32];
-      auto chunk_exp = [&](const float* s, int c0, uint32_t* out) {
+      // Pass 2: probabilities.  P (bf16, two per column) overwrites S from column 0: the 32 columns written for one half lie inside
+      // the 64 columns just read for it, and every thread touches its own row only.
+      float rs = 0.f;
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float p0 = FA_EXP0(fmaf(s[c], p.scale_log2, -m_eff));
-          float p1 = FA_EXP1(fmaf(s[c + 1], p.scale_log2, -m_eff));
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        float s[64];
+        tmem_ld_32x32(t_s + hlf * 64, s);
+        tmem_ld_32x32(t_s + hlf * 64 + 32, s + 32);
+        tmem_ld_wait();
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));
+          float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
           if (need_mask) {
-            if (kv0 + c0 + c > limit) p0 = 0.f;
-            if (kv0 + c0 + c + 1 > limit) p1 = 0.f;
+            if (kv0 + hlf * 64 + c > limit) p0 = 0.f;
+            if (kv0 + hlf * 64 + c + 1 > limit) p1 = 0.f;
           }
-          rs4[(c >> 1) & 3] += p0 + p1;
-          out[c / 2] = FA_PACK(p0, p1);
+          rs += p0 + p1;
+          const bf162 h = __floats2bfloat162_rn(p0, p1);
+          pk[c / 2] = *reinterpret_cast<const uint32_t*>(&h);
         }
-      };
-      tmem_ld_wait();
-      tmem_ld_32x32(t_s + 32, rb);
-      chunk_exp(ra, 0, pk);
-      tmem_ld_wait();
-      tmem_ld_32x32(t_s + 64, ra);
-      chunk_exp(rb, 32, pk + 16);
-      tmem_st_32x32(t_s, pk);
-      tmem_ld_wait();
-      tmem_ld_32x32(t_s + 96, rb);
-      chunk_exp(ra, 64, pk);
-      tmem_ld_wait();
-      chunk_exp(rb, 96, pk + 16);
-      tmem_st_32x32(t_s + 32, pk);
-      l_sum += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        tmem_st_32x32(t_s + hlf * 32, pk);
+      }
+      l_sum += rs;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();

@@ -1,6 +1,9 @@
 // Arithmetic helpers of the attention kernels.  The softmax of a 128 x 128 score tile needs 16384 exponentials and 8192 fp32 -> bf16
-// pair conversions; on the special-function unit (16 lanes per clock per SM) alone that is more time than the tile's two MMAs take.
-// So part of the exponentials is evaluated on the FMA pipes and the conversion is done with integer instructions.
+// pair conversions on the special-function unit (16 lanes per clock per SM).  Alternatives that move work to the FMA and integer pipes
+// are kept here: on B200 they measured SLOWER in the forward kernel (1.27 ms with the conversion instruction, 1.32 ms with integer
+// packing, 1.56 ms with half of the exponentials as polynomials, 4 x 4700 tokens, 32 heads), because the softmax warps are bound by
+// instruction issue, not by one pipe; the kernels therefore use exp2_mufu and pack_bf16x2_cvt.  Splitting every score row over two
+// threads (16 softmax warps forward, 8 compute warps backward) did not help either: 1.41 ms forward, backward unchanged.
 #pragma once
 
 #include <cuda_runtime.h>

@@ -536,6 +536,21 @@ void peer_allreduce_residual_rmsnorm(PyPeerComm& pc, const Tensor& part, c10::op
                                                      (float)eps, stream());
   TORCH_CHECK(rc == 0, "peer_allreduce_residual_rmsnorm: unsupported shape or launch failure (code ", rc, ")");
 }
+// x_out = sum over tensor-parallel ranks of (a · wᵀ) (+ residual), the all-reduce done inside the GEMM epilogue.  `stage` (bf16, 2 * world * slot
+// elements) and `flags` (int32, world * 1024, zeroed at start-up) are views into this rank's symmetric arena.
+void gemm_skinny_allreduce(PyPeerComm& pc, const Tensor& stage, const Tensor& flags, const Tensor& a, const Tensor& w, c10::optional<Tensor> residual, Tensor& x_out) {
+  chk(a, "a"); chk(w, "weight"); chk(x_out, "x_out"); chk(stage, "stage"); chk(flags, "flags");
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1) && a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_skinny_allreduce: bf16 A [M,K], W [N,K]");
+  TORCH_CHECK(x_out.scalar_type() == at::kBFloat16 && x_out.dim() == 2 && x_out.size(0) == a.size(0) && x_out.size(1) == w.size(0), "gemm_skinny_allreduce: x_out [M, N] bf16");
+  TORCH_CHECK(stage.scalar_type() == at::kBFloat16 && flags.scalar_type() == at::kInt && flags.numel() >= (int64_t)pc.c.world * 1024 && stage.numel() % (2 * pc.c.world) == 0,
+              "gemm_skinny_allreduce: stage bf16 [2 * world * slot], flags int32 [world * 1024]");
+  if (residual.has_value() && residual->defined()) { chk(*residual, "residual"); TORCH_CHECK(residual->sizes() == x_out.sizes() && residual->scalar_type() == at::kBFloat16, "gemm_skinny_allreduce: residual"); }
+  c10::cuda::CUDAGuard g(a.device());
+  const int64_t slot = stage.numel() / (2 * pc.c.world);
+  const int rc = ub::gemm_skinny_allreduce(pc.c, pc.offset_of(stage) * 2, pc.offset_of(flags) * 4, slot, a.data_ptr(), w.data_ptr(), x_out.data_ptr(), optr(residual),
+                                           (int)a.size(0), (int)w.size(0), (int)a.size(1), (int)a.size(1), (int)w.size(1), (int)w.size(0), stream());
+  TORCH_CHECK(rc == 0, "gemm_skinny_allreduce: unsupported shape or launch failure (code ", rc, ")");
+}
 void peer_reduce_scatter_sumsq(PyPeerComm& pc, const Tensor& grad_full, Tensor& out, c10::optional<Tensor> sumsq, double scale) {
   chk(grad_full, "grad"); chk(out, "out");
   TORCH_CHECK(grad_full.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat && grad_full.numel() == out.numel() * pc.c.world, "peer reduce-scatter: fp32, grad = world * out");
@@ -676,6 +691,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("offset_of", &PyPeerComm::offset_of)
       .def_readonly("state", &PyPeerComm::state);
   m.def("peer_allreduce_residual_rmsnorm", &peer_allreduce_residual_rmsnorm);
+  m.def("gemm_skinny_allreduce", &gemm_skinny_allreduce);
   m.def("peer_reduce_scatter_sumsq", &peer_reduce_scatter_sumsq);
   m.def("peer_adamw_publish", &peer_adamw_publish);
   m.def("peer_ulysses_exchange", &peer_ulysses_exchange);

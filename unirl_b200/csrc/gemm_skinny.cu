@@ -65,7 +65,23 @@ constexpr bool kDiag = true;
 constexpr bool kDiag = false;
 #endif
 
+// Tensor-parallel all-reduce inside the epilogue (row-parallel projection: every rank holds a K-slice of the weight, the outputs add up).
+// Each CTA pushes the bf16 partial of the rows it finishes into EVERY rank's staging area (plain peer stores), publishes one flag per
+// peer and CTA, waits for the same CTA of every peer, and sums the partials in rank order out of its own memory -- bit-identical on
+// all ranks, no second kernel, and the NVLink exchange of one tile overlaps the arithmetic of the others.
+struct SkinnyAllReduce {
+  int64_t stage[kMaxPeers];  // base of every rank's staging area, bf16 [2 halves][world][slot_elems] (halves alternate with the epoch)
+  int64_t flags[kMaxPeers];  // base of every rank's flag area, uint32 [world][kArMaxCtas]
+  int rank = 0, world = 1;   // world <= 1: no all-reduce
+  int64_t slot_elems = 0;    // elements between two source ranks' slots (>= M * N)
+  uint32_t* tick = nullptr;  // communicator epoch word (this rank)
+  uint32_t* ctr = nullptr;   // block counter (this rank)
+  unsigned long long wait_ns = 20000000000ull;
+};
+constexpr int kArMaxCtas = 1024;
+
 struct SkinnyParams {
+  SkinnyAllReduce ar;
   int M, N, K;   // N = output columns (SwiGLU: I, with B holding 2I rows)
   bf16* C;
   const bf16* R;
@@ -99,6 +115,18 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, float* r) {
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 3, 256;" ::: "memory"); }  // the 8 epilogue warps (every one reaches it: no early exits in part 2)
 
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -260,6 +288,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int row_lo = split * rows_per, row_hi = min(BM, row_lo + rows_per);
     const int items = max(row_hi - row_lo, 0) * CH;
     const int slot_bytes = rows_per * L::kPitch;
+    const bool all_reduce = !SWIGLU && p.ar.world > 1;
+    uint32_t epoch = 0;
+    int cta = 0;
+    if (all_reduce) {
+      epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.tick) + 1;  // the predecessor (and its tick update) is complete: pdl_wait above
+      cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    }
+    const int64_t half_off = all_reduce ? static_cast<int64_t>(epoch & 1u) * p.ar.world * p.ar.slot_elems : 0;
     for (int idx = threadIdx.x - 64; idx < items; idx += kEpiThreads) {
       const int i = idx / CH, ch = idx - i * CH;
       const int row = m0 + row_lo + i, col = n0 + ch * 8;
@@ -279,6 +315,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
       }
       const int64_t o = static_cast<int64_t>(row) * p.ldc + col;
+      if (all_reduce) {
+        // this rank's partial, rounded to bf16 once, goes into slot `rank` of every rank's staging area (its own included, so that
+        // every rank later adds exactly the same numbers)
+        Pack8 pk;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pk.h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        const int64_t at = half_off + static_cast<int64_t>(p.ar.rank) * p.ar.slot_elems + static_cast<int64_t>(row) * p.N + col;
+        for (int q = 0; q < p.ar.world; ++q) *reinterpret_cast<Pack8*>(reinterpret_cast<bf16*>(p.ar.stage[q]) + at) = pk;
+        continue;
+      }
       if (SWIGLU) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = silu_mul(acc[e], up[e]);
@@ -289,6 +335,60 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int e = 0; e < 8; ++e) acc[e] += r[e];
       }
       store8(p.C + o, acc);
+    }
+    if (all_reduce) {
+      __threadfence_system();  // this thread's peer stores are ordered before the flag below
+      epilogue_sync();
+      const int t = threadIdx.x - 64;
+      if (t < p.ar.world && t != p.ar.rank) {  // one thread per peer: publish, then wait for that peer's CTA of the same index
+        st_release_sys_u32(reinterpret_cast<uint32_t*>(p.ar.flags[t]) + p.ar.rank * kArMaxCtas + cta, epoch);
+        const uint32_t* f = reinterpret_cast<const uint32_t*>(p.ar.flags[p.ar.rank]) + t * kArMaxCtas + cta;
+        const unsigned long long t0 = global_ns();
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys_u32(f) - epoch) < 0) {
+          if ((++spins & 63u) == 0) {
+            if (global_ns() - t0 > p.ar.wait_ns) {
+              report(p.status, 330 + t);  // the sum below is then wrong; the host raises at its next status check
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+      }
+      epilogue_sync();
+      const bf16* mine = reinterpret_cast<const bf16*>(p.ar.stage[p.ar.rank]) + half_off;
+      for (int idx = threadIdx.x - 64; idx < items; idx += kEpiThreads) {
+        const int i = idx / CH, ch = idx - i * CH;
+        const int row = m0 + row_lo + i, col = n0 + ch * 8;
+        if (row >= p.M || col >= p.N) continue;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int q = 0; q < p.ar.world; ++q) {  // rank order on every rank
+          float v[8];
+          load8(mine + static_cast<int64_t>(q) * p.ar.slot_elems + static_cast<int64_t>(row) * p.N + col, v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += v[e];
+        }
+        const int64_t o = static_cast<int64_t>(row) * p.ldc + col;
+        if (p.R) {
+          float r[8];
+          load8(p.R + o, r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += r[e];
+        }
+        store8(p.C + o, acc);
+      }
+      // the last CTA of the grid advances the communicator's epoch
+      epilogue_sync();
+      if (threadIdx.x == 64) {
+        __threadfence();
+        if (atomicAdd(p.ar.ctr, 1u) == gridDim.x * gridDim.y * gridDim.z - 1) {
+          p.ar.ctr[0] = 0;
+          __threadfence();
+          *p.ar.tick = epoch;
+        }
+      }
     }
   }
   __syncthreads();
@@ -428,6 +528,33 @@ int gemm_bf16_tn_skinny(const void* A, const void* B, void* C, const void* R, in
   if (!make_tensor_map_bf16(&tmA, A, M, K, lda, BM)) return 1;
   if (!make_tensor_map_bf16(&tmB, B, swiglu ? 2 * static_cast<int64_t>(N) : N, K, ldb, out_cols)) return 1;
   if (swiglu) return bn == 144 ? launch<144, true>(tmA, tmB, p, tiles, m_tiles, splits, s) : launch<128, true>(tmA, tmB, p, tiles, m_tiles, splits, s);
+  return bn == 144 ? launch<144, false>(tmA, tmB, p, tiles, m_tiles, splits, s) : launch<128, false>(tmA, tmB, p, tiles, m_tiles, splits, s);
+}
+
+// Row-parallel projection with the tensor-parallel all-reduce in the epilogue: C = sum over ranks of A_rank · B_rankᵀ (+ R).
+// `comm` carries every rank's arena base; `stage_off` / `flag_off` are byte offsets (the same on every rank) of the staging area
+// (bf16 [2][world][slot_elems]) and of the flag area (uint32 [world][1024], zero-initialised) inside the arena.
+int gemm_skinny_allreduce(const PeerComm& c, int64_t stage_off, int64_t flag_off, int64_t slot_elems, const void* A, const void* B, void* C, const void* R, int M,
+                          int N, int K, int lda, int ldb, int ldc, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (c.world < 2 || c.world > kMaxPeers || !c.tick || !c.ctr || static_cast<int64_t>(M) * N > slot_elems) return 1;
+  if ((K % 8) || (N % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(C) & 15) || (R && (reinterpret_cast<uintptr_t>(R) & 15)) || (stage_off & 15) || (slot_elems % 8)) return 1;
+  int bn = 128, splits = 1;
+  gemm_skinny_plan(M, N, K, false, &bn, &splits);
+  SkinnyParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = static_cast<bf16*>(C); p.R = static_cast<const bf16*>(R); p.ldc = ldc; p.up_row_offset = N; p.status = c.status;
+  p.trace = nullptr; p.skip_a = 0;
+  for (int r = 0; r < c.world; ++r) {
+    p.ar.stage[r] = c.bufs[r] + stage_off;
+    p.ar.flags[r] = c.bufs[r] + flag_off;
+  }
+  p.ar.rank = c.rank; p.ar.world = c.world; p.ar.slot_elems = slot_elems; p.ar.tick = c.tick; p.ar.ctr = c.ctr; p.ar.wait_ns = c.wait_ns;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int tiles = (N + bn - 1) / bn;
+  if (static_cast<int64_t>(tiles) * m_tiles * splits > kArMaxCtas) return 1;
+  CUtensorMap tmA, tmB;
+  if (!make_tensor_map_bf16(&tmA, A, M, K, lda, BM)) return 1;
+  if (!make_tensor_map_bf16(&tmB, B, N, K, ldb, bn)) return 1;
   return bn == 144 ? launch<144, false>(tmA, tmB, p, tiles, m_tiles, splits, s) : launch<128, false>(tmA, tmB, p, tiles, m_tiles, splits, s);
 }
 

@@ -142,5 +142,8 @@ int peer_adamw_publish(const PeerComm& c, int64_t replica_offset, int64_t shard,
 int peer_ulysses_exchange(const PeerComm& c, int64_t stage_offset, void* out, int B, int l, int Hp, int D, int mode, cudaStream_t s);
 int peer_scatter_copy(const void* ops_dev, int n_ops, int64_t max_vecs, cudaStream_t s);
 int peer_barrier(const PeerComm& c, cudaStream_t s);
+// gemm_skinny.cu: row-parallel projection with the tensor-parallel all-reduce inside the GEMM epilogue (peer stores + per-CTA flags)
+int gemm_skinny_allreduce(const PeerComm& c, int64_t stage_off, int64_t flag_off, int64_t slot_elems, const void* A, const void* B, void* C, const void* R, int M,
+                          int N, int K, int lda, int ldb, int ldc, cudaStream_t s);
 
 }  // namespace ub

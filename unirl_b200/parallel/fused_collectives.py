@@ -103,9 +103,24 @@ class FusedAllReduce:
     """
 
     def __init__(self, comm: Comm, max_tokens: int, hidden: int, device: Any, wait_s: float = 20.0):
+        import os
+
         self.max_tokens, self.hidden = int(max_tokens), int(hidden)
-        self.arena = PeerArena(comm, 2 * self.max_tokens * self.hidden * 2 + 512, device, wait_s)
+        # decode-sized projections run GEMM + all-reduce as ONE kernel: every rank's epilogue stores its partial tile into every peer
+        # (slot per source rank, two halves alternating with the epoch) and sums the peers' tiles once their per-CTA flags arrive
+        self.fused_rows = int(os.environ.get("UNIRL_B200_TP_FUSED_GEMM_MAX_M", "256")) if os.environ.get("UNIRL_B200_TP_FUSED_GEMM", "1") == "1" else 0
+        self.fused_rows = min(self.fused_rows, self.max_tokens)
+        world = comm.size
+        slot = self.fused_rows * self.hidden
+        extra = (2 * world * slot * 2 + world * 1024 * 4 + 1024) if self.fused_rows else 0
+        self.arena = PeerArena(comm, 2 * self.max_tokens * self.hidden * 2 + 512 + extra, device, wait_s)
         self._halves = [self.arena.take(self.max_tokens * self.hidden, torch.bfloat16) for _ in range(2)]
+        self._gemm_stage = self.arena.take(2 * world * slot, torch.bfloat16) if self.fused_rows else None
+        self._gemm_flags = self.arena.take(world * 1024, torch.int32) if self.fused_rows else None
+        if self.fused_rows:
+            torch.cuda.synchronize(device)
+            comm.barrier()  # every rank's flag area is zero before any peer publishes into it
+        self.fused_calls = 0
         self._half = 0
         self._C = _ext.require_ext()
         self.comm = comm
@@ -130,6 +145,18 @@ class FusedAllReduce:
             from unirl_b200.ops.norm import rmsnorm
 
             return x, (rmsnorm(x, norm_weight, eps) if norm_weight is not None else None)
+        if (0 < T <= self.fused_rows and inp.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and inp.shape[1] % 64 == 0 and weight.shape[0] == self.hidden
+                and self.hidden % 8 == 0 and self.hidden >= 1024 and weight.is_contiguous() and hasattr(self._C, "gemm_skinny_allreduce")):
+            x = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=inp.device)
+            self._C.gemm_skinny_allreduce(self.arena.peer, self._gemm_stage, self._gemm_flags, inp.contiguous(), weight,
+                                          residual.contiguous() if residual is not None else None, x)
+            _ext.count_launch()
+            self.fused_calls += 1
+            if norm_weight is None:
+                return x, None
+            from unirl_b200.ops.norm import rmsnorm
+
+            return x, rmsnorm(x, norm_weight, eps)
         part = self._stage(T)
         from unirl_b200.ops.linear import skinny_linear
 
