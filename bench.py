@@ -227,8 +227,9 @@ def main() -> None:
         n_tok = int(round(rollout_row.get("rollout/response_length_mean", 0.0) * n_prompts * args.group_size))
         dev_ms = dict(trainer.phase_timer.device_ms)
         sync_ms = float(trainer.last_sync_stats.get("sync_ms", 0.0))
+        m = dict(getattr(result, "metrics", {}) or {})
         return {"tokens": n_tok, "device_ms": dev_ms, "sync_ms": sync_ms, "loss": float(result.loss), "reward": reward, "h2d": h2d,
-                "d2h": n_tok * (8 + 4) + 8}
+                "d2h": n_tok * (8 + 4) + 8, "logp_gap": (m.get("rollout_replay_logp_absdiff_mean"), m.get("rollout_replay_logp_absdiff_max"))}
 
     budget = StepBudget(args.budget_s, _job_start(), world)
     n_warm = 0
@@ -275,7 +276,8 @@ def main() -> None:
                "clocks": clocks,
                "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": rows[-1]["h2d"], "d2h_bytes_per_step": rows[-1]["d2h"],
                        "ms_per_step": wall_ms / n_steps},
-               "gpu_launches": int(launches), "loss": rows[-1]["loss"], "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
+               "gpu_launches": int(launches), "loss": rows[-1]["loss"],
+               "rollout_replay_logp_absdiff": {"mean": rows[-1]["logp_gap"][0], "max": rows[-1]["logp_gap"][1]}, "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                "phases_device_ms_last_step": {k: round(v, 2) for k, v in rows[-1]["device_ms"].items()}, "device_span_ms_per_step": span_ms / n_steps}
         print(json.dumps(out))
     trainer.shutdown()

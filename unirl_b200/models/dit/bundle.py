@@ -53,9 +53,24 @@ class DiTBundle(Bundle):
         else:
             from safetensors.torch import load_file
 
-            missing, unexpected = model.load_state_dict(load_file(os.path.join(path, "transformer.safetensors")), strict=False)
-            if missing or unexpected:
-                raise RuntimeError(f"checkpoint/key mismatch: missing {missing[:5]} unexpected {unexpected[:5]}")
+            native = os.path.join(path, "transformer.safetensors")
+            if os.path.exists(native):
+                missing, unexpected = model.load_state_dict(load_file(native), strict=False)
+                if missing or unexpected:
+                    raise RuntimeError(f"checkpoint/key mismatch: missing {missing[:5]} unexpected {unexpected[:5]}")
+            else:
+                # a diffusers layout: <path>/transformer/diffusion_pytorch_model*.safetensors in the family's own key grammar
+                import glob
+
+                from unirl_b200.models.dit.hf_keys import load_diffusers_transformer
+
+                shards = sorted(glob.glob(os.path.join(path, "transformer", "diffusion_pytorch_model*.safetensors")))
+                if not shards:
+                    raise FileNotFoundError(f"{path}: neither transformer.safetensors nor transformer/diffusion_pytorch_model*.safetensors")
+                sd = {}
+                for f in shards:
+                    sd.update(load_file(f))
+                load_diffusers_transformer(model, sd, spec.transformer.name, strict=True)
         encoders = [TextEncoder(c, dtype=dtype, device=device).init_weights(config.init_seed + 1 + i) for i, c in enumerate(spec.text_encoders)]
         toks = [load_tokenizer(None, c.vocab_size, True) for c in spec.text_encoders]
         vae = LatentVAE(spec.vae, device=device).init_weights(config.init_seed + 7)

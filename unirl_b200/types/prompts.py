@@ -20,15 +20,20 @@ class RolloutInputs(Batch):
         return len(self.sample_ids) if self.sample_ids else super().batch_size
 
     def expand(self, samples_per_prompt: int) -> "RolloutInputs":
-        """Each prompt ``k`` times, siblings adjacent; ids become ``prompt:<gid>:sample:<j>``."""
-        k = int(samples_per_prompt)
-        if k < 1:
-            raise ValueError(f"samples_per_prompt must be >= 1, got {k}")
-        if k == 1:
+        """Fan every prompt out to ``samples_per_prompt`` rows that stay next to each other (the layout group-relative advantages
+        expect).  Row ``j`` of the prompt with group id ``<gid>`` is named ``prompt:<gid>:sample:<j>``, the id grammar rewards,
+        noise recipes and logs key on; with one sample per prompt the batch is returned unchanged."""
+        fan_out = int(samples_per_prompt)
+        if fan_out <= 0:
+            raise ValueError(f"RolloutInputs.expand: need at least one sample per prompt (got samples_per_prompt={samples_per_prompt!r})")
+        if fan_out == 1:
             return self
-        out = self.repeat_interleave(k)
-        out.sample_ids = [f"prompt:{g}:sample:{j}" for g in self.group_ids for j in range(k)]
-        return out
+        widened = self.repeat_interleave(fan_out)
+        names: List[str] = []
+        for gid in self.group_ids:
+            names.extend(f"prompt:{gid}:sample:{j}" for j in range(fan_out))
+        widened.sample_ids = names
+        return widened
 
 
 __all__ = ["RolloutInputs"]
