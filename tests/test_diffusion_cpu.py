@@ -128,7 +128,7 @@ def test_secondary_benchmark_script_runs_on_cpu():
     cmd = [sys.executable, os.path.join(root, "bench_diffusion.py"), "--device", "cpu", "--preset", "tiny-sd3", "--prompts-per-gpu", "1",
            "--samples-per-prompt", "4", "--micro-batch", "4", "--resolution", "64", "--inference-steps", "4", "--train-timesteps", "2", "--text-len", "7",
            "--steps", "1", "--warmup", "1", "reward.backend.in_channels=4", "+reward.backend.width=8", "backend.fsdp_cfg.activation_checkpointing=false",
-           "backend.lora_cfg.rank=4", "backend.lora_cfg.alpha=8"]
+           "backend.lora_cfg.rank=4", "backend.lora_cfg.alpha=8", "rollout.config.forward_batch_size=2"]  # the sampler engine runs the 4 samples as two calls
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=500, cwd=root)
     assert out.returncode == 0, out.stderr[-2000:]
     row = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])

@@ -109,3 +109,42 @@ def test_torchrun_spmd_backend_two_cpu_ranks():
 
     reports = re.findall(r"rollout 2/2  loss=\S+  grad_norm=\S+  lr=\S+  reward=\d+\.\d{4}", p.stdout)  # the two ranks' lines may share one output line
     assert len(reports) == 2 and reports[0] == reports[1], "both ranks run the same controller and agree on the step metrics"
+
+
+def _lora_cfg(extra):
+    ov = [o for o in _COLOC if not o.startswith(("num_devices", "rollout.config.tp_size", "rollout_parallel", "+pool_backend"))]
+    return compose("ar/qwen3_4b_grpo_lora_b200", overrides=ov + ["backend.lora_cfg.rank=4", "backend.lora_cfg.alpha=8", "rollout.config.model_precision=fp32",
+                                                                 "+rollout.config.share_trainer_weights=false", "backend.optimizer_cfg.learning_rate=5.0e-3"] + extra)
+
+
+def _assert_lora_engine_follows_trainer(tr):
+    tr.train(num_rollouts=3, weight_sync_interval=1)
+    rows = [r for r in tr.wandb_logger.history if "train/step" in r]
+    # the third rollout is sampled by an engine that folded two updates of the adapters into weights of its own
+    assert abs(rows[-1]["train/ratio_mean"] - 1.0) < 1e-3 and rows[-1]["train/rollout_replay_logp_absdiff_max"] < 1e-3
+    assert tr.rollout.get_weight_version()[0] >= 2
+
+
+@pytest.mark.timeout(600)
+def test_lora_sync_into_an_engine_with_weights_of_its_own():
+    tr = _trainer(_lora_cfg(["num_devices=1", "rollout.config.tp_size=1", "rollout_parallel={tp: 1}", "+pool_backend=inline"]))
+    try:
+        before = tr.rollout.compute_local_param_checksums()[0]
+        _assert_lora_engine_follows_trainer(tr)
+        after = tr.rollout.compute_local_param_checksums()[0]
+        changed = {k for k in before if before[k] != after[k]}
+        assert changed and all(k.rsplit(".", 1)[-1] in ("qkv_proj", "o_proj", "gate_up_proj", "down_proj") for k in changed)
+        # withdrawing the adapters gives the base weights back, bit for bit
+        tr.rollout.set_lora_from_tensors("default", {}, peft_config={"r": 4, "lora_alpha": 8})
+        assert tr.rollout.compute_local_param_checksums()[0] == before
+    finally:
+        tr.shutdown()
+
+
+@pytest.mark.timeout(900)
+def test_lora_sync_into_a_tp2_engine_over_gloo():
+    tr = _trainer(_lora_cfg(["num_devices=2", "rollout.config.tp_size=2", "rollout_parallel={tp: 2}", "+pool_backend=mp", "rollout.config.max_running_requests=16"]))
+    try:
+        _assert_lora_engine_follows_trainer(tr)
+    finally:
+        tr.shutdown()

@@ -74,6 +74,10 @@ def test_diffusers_state_dict_lands_in_the_native_module(preset, family):
     assert not any(k.startswith(("joint_blocks", "single_blocks")) for k in hf), "the synthetic checkpoint uses the published key grammar only"
     if family == "sd3":
         hf["pos_embed.proj.weight"] = hf["pos_embed.proj.weight"].view(cfg.hidden_size, cfg.in_channels, cfg.patch_size[1], cfg.patch_size[2])  # a conv kernel, as published
+        pe = cfg.patch_size[1] * cfg.patch_size[2]
+        for suf in ("weight", "bias"):  # ... and the output projection keeps the channel last inside a patch
+            t = hf[f"proj_out.{suf}"]
+            hf[f"proj_out.{suf}"] = t.reshape(-1, pe, *t.shape[1:]).transpose(0, 1).reshape(t.shape)
     dst = DiTTransformer(cfg, dtype=torch.float32, device="cpu").init_weights(2)
     missing, unexpected = load_diffusers_transformer(dst, hf, preset, strict=True)
     assert not missing and not unexpected
@@ -102,3 +106,129 @@ def test_bridge_reports_shape_mismatch_and_unplaced_tensors():
     short = {k: v for k, v in hf.items() if "transformer_blocks.1.ff.net.2" not in k}
     with pytest.raises(KeyError, match="got no value"):
         load_diffusers_transformer(DiTTransformer(cfg, dtype=torch.float32, device="cpu"), short, "tiny-sd3")
+
+
+# ---- WAN: an independent statement of the published forward (WanTransformer3DModel, text-to-video), written against the published key names
+def _wan_reference(sd, cfg, latents, t, text):
+    import math
+
+    import torch.nn.functional as F
+
+    h, nh, hd = cfg.hidden_size, cfg.num_heads, cfg.head_dim
+    lin = lambda x, k: F.linear(x, sd[f"{k}.weight"], sd.get(f"{k}.bias"))  # noqa: E731
+    rms = lambda x, w: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.eps) * w  # noqa: E731
+    ln = lambda x: F.layer_norm(x, (h,), eps=cfg.eps)  # noqa: E731
+    b, c, f, hh, ww = latents.shape
+    pf, ph, pw = cfg.patch_size
+    x = F.conv3d(latents, sd["patch_embedding.weight"], sd["patch_embedding.bias"], stride=(pf, ph, pw))  # [b, h, F, H, W]
+    grid = x.shape[2:]
+    x = x.flatten(2).transpose(1, 2)
+    # rotary tables: the head dimension is split over (frame, row, column); consecutive pairs rotate together
+    pos = torch.stack(torch.meshgrid(*[torch.arange(n) for n in grid], indexing="ij"), -1).reshape(-1, 3).float()
+    ang = torch.cat([pos[:, a : a + 1] / (cfg.rope_theta ** (torch.arange(0, d, 2).float() / d))[None] for a, d in enumerate(cfg.rope_axes)], -1)
+    rot = torch.polar(torch.ones_like(ang), ang)  # [L, hd / 2] complex
+
+    def rope(v):  # [b, L, nh, hd]
+        vc = torch.view_as_complex(v.float().reshape(*v.shape[:-1], -1, 2))
+        return torch.view_as_real(vc * rot[None, :, None, :]).flatten(-2)
+
+    half = cfg.time_freq_dim // 2
+    freqs = torch.exp(-math.log(10000.0) * torch.arange(half).float() / half)
+    emb = t.float()[:, None] * freqs[None]
+    temb = lin(F.silu(lin(torch.cat([emb.cos(), emb.sin()], -1), "condition_embedder.time_embedder.linear_1")), "condition_embedder.time_embedder.linear_2")
+    tproj = lin(F.silu(temb), "condition_embedder.time_proj").unflatten(1, (6, -1))
+    ctx = lin(F.gelu(lin(text, "condition_embedder.text_embedder.linear_1"), approximate="tanh"), "condition_embedder.text_embedder.linear_2")
+
+    def attend(q, k, v):
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        return o.transpose(1, 2).flatten(2)
+
+    for i in range(cfg.num_cross_blocks):
+        p = f"blocks.{i}"
+        sh1, sc1, g1, sh2, sc2, g2 = (sd[f"{p}.scale_shift_table"] + tproj).unbind(1)
+        y = ln(x) * (1 + sc1[:, None]) + sh1[:, None]
+        q = rms(lin(y, f"{p}.attn1.to_q"), sd[f"{p}.attn1.norm_q.weight"]).unflatten(2, (nh, hd))
+        k = rms(lin(y, f"{p}.attn1.to_k"), sd[f"{p}.attn1.norm_k.weight"]).unflatten(2, (nh, hd))
+        v = lin(y, f"{p}.attn1.to_v").unflatten(2, (nh, hd))
+        x = x + lin(attend(rope(q), rope(k), v), f"{p}.attn1.to_out.0") * g1[:, None]
+        y = F.layer_norm(x, (h,), sd[f"{p}.norm2.weight"], sd[f"{p}.norm2.bias"], cfg.eps)
+        q = rms(lin(y, f"{p}.attn2.to_q"), sd[f"{p}.attn2.norm_q.weight"]).unflatten(2, (nh, hd))
+        k = rms(lin(ctx, f"{p}.attn2.to_k"), sd[f"{p}.attn2.norm_k.weight"]).unflatten(2, (nh, hd))
+        v = lin(ctx, f"{p}.attn2.to_v").unflatten(2, (nh, hd))
+        x = x + lin(attend(q, k, v), f"{p}.attn2.to_out.0")
+        y = ln(x) * (1 + sc2[:, None]) + sh2[:, None]
+        x = x + lin(F.gelu(lin(y, f"{p}.ffn.net.0.proj"), approximate="tanh"), f"{p}.ffn.net.2") * g2[:, None]
+    shift, scale = (sd["scale_shift_table"] + temb[:, None]).unbind(1)
+    x = lin(ln(x) * (1 + scale[:, None]) + shift[:, None], "proj_out")
+    x = x.reshape(b, *grid, pf, ph, pw, -1).permute(0, 7, 1, 4, 2, 5, 3, 6)
+    return x.reshape(b, -1, grid[0] * pf, grid[1] * ph, grid[2] * pw)
+
+
+def test_wan_checkpoint_in_published_layout_matches_the_published_forward():
+    from unirl_b200.models.dit.hf_keys import wan_from_diffusers
+
+    cfg = PRESETS["tiny-wan"]().transformer
+    h, m, g = cfg.hidden_size, cfg.mlp_dim, torch.Generator().manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.2  # noqa: E731
+    sd = {"patch_embedding.weight": rnd(h, cfg.in_channels, *cfg.patch_size), "patch_embedding.bias": rnd(h), "scale_shift_table": rnd(1, 2, h),
+          "proj_out.weight": rnd(cfg.in_channels * 4, h), "proj_out.bias": rnd(cfg.in_channels * 4)}
+    for name, (i, o) in {"condition_embedder.time_embedder.linear_1": (cfg.time_freq_dim, h), "condition_embedder.time_embedder.linear_2": (h, h),
+                         "condition_embedder.time_proj": (h, 6 * h), "condition_embedder.text_embedder.linear_1": (cfg.text_dim, h),
+                         "condition_embedder.text_embedder.linear_2": (h, h)}.items():
+        sd[f"{name}.weight"], sd[f"{name}.bias"] = rnd(o, i), rnd(o)
+    for b in range(cfg.num_cross_blocks):
+        p = f"blocks.{b}"
+        sd[f"{p}.scale_shift_table"] = rnd(1, 6, h)
+        for a in ("attn1", "attn2"):
+            for pr in ("to_q", "to_k", "to_v", "to_out.0"):
+                sd[f"{p}.{a}.{pr}.weight"], sd[f"{p}.{a}.{pr}.bias"] = rnd(h, h), rnd(h)
+            sd[f"{p}.{a}.norm_q.weight"], sd[f"{p}.{a}.norm_k.weight"] = 1 + rnd(h), 1 + rnd(h)
+        sd[f"{p}.norm2.weight"], sd[f"{p}.norm2.bias"] = 1 + rnd(h), rnd(h)
+        sd[f"{p}.ffn.net.0.proj.weight"], sd[f"{p}.ffn.net.0.proj.bias"] = rnd(m, h), rnd(m)
+        sd[f"{p}.ffn.net.2.weight"], sd[f"{p}.ffn.net.2.bias"] = rnd(h, m), rnd(h)
+    model = DiTTransformer(cfg, dtype=torch.float32, device="cpu").init_weights(3)
+    missing, unexpected = load_diffusers_transformer(model, sd, "tiny-wan", strict=True)
+    assert not missing and not unexpected
+    assert set(wan_from_diffusers(sd, cfg.num_cross_blocks, strict=True)) == set(model.state_dict())
+    lat, t, text = torch.randn(2, cfg.in_channels, 3, 8, 12, generator=g), torch.tensor([0.3, 0.9]) * 1000, torch.randn(2, 7, cfg.text_dim, generator=g)
+    with torch.no_grad():
+        got, want = model(lat, t, text), _wan_reference(sd, cfg, lat, t, text)
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
+    with pytest.raises(KeyError, match="image-to-video"):
+        wan_from_diffusers({**sd, "condition_embedder.image_embedder.ff.net.0.proj.weight": rnd(4, 4)}, cfg.num_cross_blocks)
+
+
+def test_sd3_position_table_follows_the_published_formula_and_is_taken_from_the_checkpoint():
+    """The table a random-init SD3 model computes equals the published construction (numpy restatement below); a checkpoint's stored table
+    replaces it; the output projection's rows are reordered from channel-last to channel-first patches."""
+    import numpy as np
+
+    from unirl_b200.models.dit.modeling import sincos_2d_table
+
+    dim, size, base = 32, 12, 4
+    gh = np.arange(size, dtype=np.float32) / (size / base)
+    gw = np.arange(size, dtype=np.float32) / (size / base)
+    grid = np.stack(np.meshgrid(gw, gh), 0).reshape(2, 1, size, size)  # the column coordinate comes first
+
+    def one_d(d, pos):
+        omega = 1.0 / 10000 ** (np.arange(d // 2, dtype=np.float64) / (d / 2.0))
+        out = np.einsum("m,d->md", pos.reshape(-1), omega)
+        return np.concatenate([np.sin(out), np.cos(out)], 1)
+
+    want = np.concatenate([one_d(dim // 2, grid[0]), one_d(dim // 2, grid[1])], 1)  # [size * size, dim]
+    got = sincos_2d_table(dim, size, "cpu", base).reshape(size * size, dim)
+    np.testing.assert_allclose(got.numpy(), want, rtol=1e-5, atol=1e-6)
+
+    cfg = PRESETS["tiny-sd3"]().transformer
+    src = DiTTransformer(cfg, dtype=torch.float32, device="cpu").init_weights(1)
+    hf = _to_diffusers(src.state_dict(), cfg, "sd3")
+    pe = cfg.patch_size[1] * cfg.patch_size[2]
+    for suf in ("weight", "bias"):  # a published checkpoint keeps the channel last inside a patch
+        t = hf[f"proj_out.{suf}"]
+        hf[f"proj_out.{suf}"] = t.reshape(-1, pe, *t.shape[1:]).transpose(0, 1).reshape(t.shape)
+    stored = torch.randn(1, cfg.pos_embed_max_size ** 2, cfg.hidden_size)
+    hf["pos_embed.pos_embed"] = stored
+    dst = DiTTransformer(cfg, dtype=torch.float32, device="cpu").init_weights(2)
+    load_diffusers_transformer(dst, hf, "tiny-sd3", strict=True)
+    assert torch.equal(dst.pos_table.reshape(-1), stored.reshape(-1))
+    assert torch.equal(dst.final_proj.weight, src.final_proj.weight) and torch.equal(dst.final_proj.bias, src.final_proj.bias)

@@ -274,6 +274,9 @@ def _gemm_allreduce_body(rank, world):
     dev = torch.device("cuda", rank)
     comm = Comm.world()
     H, K = 2560, 2048
+    import os
+
+    os.environ["UNIRL_B200_TP_FUSED_GEMM_MAX_M"] = "256"  # exercise the two-tile case as well
     far = FusedAllReduce(comm, max_tokens=512, hidden=H, device=dev, wait_s=10.0)
     out = {"max_err": 0.0, "rank_diff": 0.0, "fused_calls": 0}
     torch.manual_seed(11 + rank)

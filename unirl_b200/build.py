@@ -39,6 +39,26 @@ def _stale(out: str, deps: List[str]) -> bool:
     return not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps)
 
 
+def _defines_for(src: str, headers: List[str]) -> List[str]:
+    """Development switches: ``UNIRL_B200_NVCC_DEFINES=NAME[,NAME=VALUE...]`` adds ``-DNAME`` to the translation units that mention the
+    name (directly or through a header of this package), e.g. ``UNIRL_B200_ATTN_DIAG`` (phase timers in the attention kernels) or
+    ``UNIRL_B200_SKINNY_DIAG``.  The product build sets none."""
+    want = [d for d in os.environ.get("UNIRL_B200_NVCC_DEFINES", "").split(",") if d]
+    if not want:
+        return []
+    text = open(src).read()
+    for h in headers:
+        if f'"{os.path.basename(h)}"' in text:
+            text += open(h).read()
+    return [d for d in want if d.split("=")[0] in text]
+
+
+def _defines_changed(out: str, defs: List[str]) -> bool:
+    stamp = out + ".defs"
+    old = open(stamp).read() if os.path.exists(stamp) else ""
+    return old != ",".join(defs)
+
+
 def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> str:
     import torch
     from torch.utils.cpp_extension import include_paths, library_paths
@@ -52,9 +72,12 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     jobs = []
     for f in cu:
         out = os.path.join(OBJ, f + ".o")
-        if force or _stale(out, [os.path.join(CSRC, f)] + headers):
+        defs = _defines_for(os.path.join(CSRC, f), headers)
+        if force or _stale(out, [os.path.join(CSRC, f)] + headers) or _defines_changed(out, defs):
             cmd = [NVCC, "-c", os.path.join(CSRC, f), "-o", out, "-O3", "-std=c++17", "-lineinfo", "--use_fast_math", *ARCH,
-                   "-Xcompiler", "-fPIC", f"-I{CSRC}", "--expt-relaxed-constexpr"]
+                   "-Xcompiler", "-fPIC", f"-I{CSRC}", "--expt-relaxed-constexpr", *[f"-D{d}" for d in defs]]
+            with open(out + ".defs", "w") as fh:
+                fh.write(",".join(defs))
             if ptxas_info:
                 cmd += ["-Xptxas", "-v"]
             jobs.append(cmd)

@@ -206,8 +206,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idesc_ts = make_idesc_bf16(kTile, D, false, true);       // dV, dK: A from TMEM, B as stored (MN-major)
       constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, D, true, true);        // dQ: A = dSᵀ as stored (MN-major), B = K as stored
       constexpr uint32_t kStepMN = (16 * 128) >> 4;
+      ATTN_DIAG_DECL(5);
       bool ok = wait_or_abort(kv_full, 0, abort_flag);
       if (!ok) give_up(p.status, 152, abort_flag);
+      ATTN_DIAG_LAP(0);
       for (int it = 0; it < iters && ok; ++it) {
         const int st = it % kStages;
         const uint8_t* sQ = smem + L::kQ + st * L::kTileBytes;
@@ -217,6 +219,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           ok = false;
           break;
         }
+        ATTN_DIAG_LAP(1);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {  // Sᵀ = K·Qᵀ (runs while the compute warps still drain the previous dQ tile from the dPᵀ columns)
@@ -229,6 +232,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           ok = false;
           break;
         }
+        ATTN_DIAG_LAP(2);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {  // dPᵀ = V·dOᵀ
@@ -242,6 +246,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           ok = false;
           break;
         }
+        ATTN_DIAG_LAP(3);
         tc_fence_after();
         const uint64_t d_dO = make_desc_mnmajor_sw128(sdO, L::kBoxBytes), d_Q = make_desc_mnmajor_sw128(sQ, L::kBoxBytes);
         const uint64_t d_K = make_desc_mnmajor_sw128(smem + L::kK, L::kBoxBytes), d_dS = make_desc_mnmajor_sw128(smem + L::kdS, L::kBoxBytes);
@@ -256,8 +261,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_bf16(tmem_base + kColdP, d_dS + kStepMN * k, d_K + kStepMN * k, idesc_dq, k != 0);
         umma_commit(dq_full);
         umma_commit(qdo_empty + st);
+        ATTN_DIAG_LAP(4);
       }
       if (ok) umma_commit(dkv_full);
+      ATTN_DIAG_FLUSH(0, 5, true);
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ compute warps: one key row per thread
@@ -271,6 +278,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t* stage0 = smem + L::kdS + q * 4096;                 // this warp's 32 rows of box 0 / box 1: its two fp32 staging buffers for dQ
     uint8_t* stage1 = smem + L::kdS + L::kBoxBytes + q * 4096;
     bool ok = true;
+    ATTN_DIAG_DECL(8);
     for (int it = 0; it < iters; ++it) {
       const int g = it / (n_q - i_first), i = i_first + it % (n_q - i_first);
       const int head = kv_head * G + g;
@@ -291,15 +299,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = false;
         break;
       }
+      ATTN_DIAG_LAP(0);
       if (!__all_sync(0xffffffffu, wait_or_abort(sdp_full, it & 1, abort_flag))) {
         give_up(p.status, 155, abort_flag);
         ok = false;
         break;
       }
+      ATTN_DIAG_LAP(1);
       tc_fence_after();
       // this warp's staging buffers (its dSᵀ rows) may still be read by the reduce of the previous iteration
       if (lane == 0) tma_store_wait_read<0>();
       __syncwarp();
+      ATTN_DIAG_LAP(2);
       const bool diag = p.causal && qt0 < kv0 + kTile;  // some queries of this tile come before some keys
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
@@ -334,42 +345,54 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<uint4*>(dst + ((j ^ (r & 7)) << 4)) = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
       }
+      ATTN_DIAG_LAP(3);
       tmem_st_wait();
       fence_async_proxy();  // the dSᵀ rows are read by the tensor core through the async proxy
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_ready);
+      ATTN_DIAG_LAP(4);
       // ---- dQ tile of this iteration: TMEM -> fp32 staging -> TMA reduce-add into the global accumulator
       if (!__all_sync(0xffffffffu, wait_or_abort(dq_full, it & 1, abort_flag))) {
         give_up(p.status, 156, abort_flag);
         ok = false;
         break;
       }
+      ATTN_DIAG_LAP(5);
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint8_t* sbuf = (c & 1) ? stage1 : stage0;
-        if (c >= 2) {
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-        }
-        float a[32];
-        tmem_ld_32x32(tmem_base + kColdP + lane_off + c * 32, a);
-        tmem_ld_wait();
+      {
+        // the whole dQ row in one round of TMEM loads (one exposed load latency instead of one per 32 columns), then the columns go out
+        // through the two staging buffers, 32 at a time
+        float a[D];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<float4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_float4(a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
-        fence_async_proxy();
+        for (int c = 0; c < D / 32; ++c) tmem_ld_32x32(tmem_base + kColdP + lane_off + c * 32, a + c * 32);
+        tmem_ld_wait();
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_2d(&tmdQ, sbuf, head * D + c * 32, seq_start + qt0 + q * 32);
-          tma_store_commit();
+        ATTN_DIAG_LAP(6);
+        if (lane == 0) mbar_arrive(s_free);  // the dPᵀ columns are free again: the issuer may start the next iteration's dPᵀ while the tile leaves
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint8_t* sbuf = (c & 1) ? stage1 : stage0;
+          if (c >= 2) {
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_float4(a[c * 32 + 4 * j], a[c * 32 + 4 * j + 1], a[c * 32 + 4 * j + 2], a[c * 32 + 4 * j + 3]);
+          fence_async_proxy();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_2d(&tmdQ, sbuf, head * D + c * 32, seq_start + qt0 + q * 32);
+            tma_store_commit();
+          }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);
+      ATTN_DIAG_LAP(7);
     }
+    ATTN_DIAG_FLUSH(8, 8, warp == 4 && lane == 0);
     if (ok) {
       if (!__all_sync(0xffffffffu, wait_or_abort(dkv_full, 0, abort_flag))) {
         give_up(p.status, 157, abort_flag);
@@ -478,5 +501,8 @@ int flash_attention_bwd(const void* q, const void* k, const void* v, const void*
   f32_to_bf16_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, s>>>(dq_acc, static_cast<bf16*>(dq), n8);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
+
+// Phase-timer table of the backward kernel; all zero unless built with -DUNIRL_B200_ATTN_DIAG.
+ATTN_DIAG_DEFINE_READER(attention_bwd_diag_read)
 
 }  // namespace ub

@@ -7,9 +7,9 @@
 //   warp 0        loader     : TMA loads of Q (once) and of the K / V ring (128 keys per stage, two stages)
 //   warp 1        MMA issuer : S_i = Q_i·K_jᵀ into TMEM (both operands K-major from shared memory), then O_i += P_i·V_j with P_i read
 //                              from TMEM (it overwrites the first half of S_i's columns) and V_j read as stored (MN-major B operand)
-//   warps 4..7    softmax of tile 0: tcgen05.ld one S row per thread, running max / sum in the log2 domain, P -> bf16 -> tcgen05.st
-//   warps 8..11   softmax of tile 1 (same code); while one group does exponentials the other group's MMAs run
-//   (warps 2, 3 idle, so that each softmax group is one aligned group of four warps covering the four TMEM lane quarters in order)
+//   warps 2..5    softmax of tile 0: tcgen05.ld one whole S row per thread, running max / sum in the log2 domain, P -> bf16 -> tcgen05.st
+//   warps 6..9    softmax of tile 1 (same code); while one group does exponentials the other group's MMAs run
+//   (four consecutive warps cover the four TMEM lane quarters, warp index modulo 4, in some order)
 //
 // The running maximum is updated lazily: O is rescaled only when a row's maximum grew by more than 2^8 since the value in use, so the
 // accumulator read-modify-write in TMEM is rare; the final normalisation uses the exact sum for the maximum in use.
@@ -21,6 +21,7 @@
 // every role leaves its loop, TMEM is released and the kernel returns.
 #include "common.cuh"
 #include "ops.h"
+#include "attn_math.cuh"
 #include "tcgen05.cuh"
 
 #include <cuda.h>
@@ -37,7 +38,7 @@ constexpr int kTileQ = 128;      // rows per query tile (= TMEM lanes)
 constexpr int kTilesQ = 2;       // query tiles per CTA
 constexpr int kTileKV = 128;     // keys per K / V stage
 constexpr int kKvStages = 2;
-constexpr int kFaThreads = 384;  // warp group 0: loader, issuer (+2 idle warps); warp groups 1 and 2: softmax of tile 0 / 1
+constexpr int kFaThreads = 320;  // warp 0: loader, warp 1: issuer, warps 2-5: softmax of tile 0, warps 6-9: softmax of tile 1 (200 registers each)
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 template <int D>
@@ -205,6 +206,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idesc_qk = make_idesc_bf16(kTileQ, kTileKV, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(kTileQ, D, false, true);
       bool ok = true;
+      ATTN_DIAG_DECL(6);
       // S_i = Q_i · K_jᵀ: contraction over D in steps of 16; 64 columns per swizzled box
       auto issue_qk = [&](int i, int st) {
         const uint8_t* sq = smem + L::kQ + i * L::kTileBytes;
@@ -236,18 +238,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(k_empty + 0);
       }
+      ATTN_DIAG_LAP(0);
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j % kKvStages, nst = (j + 1) % kKvStages;
         if (!wait_or_abort(v_full + st, (j / kKvStages) & 1, abort_flag)) {
           give_up(p.status, 144, abort_flag);
           break;
         }
+        ATTN_DIAG_LAP(1);
         for (int i = 0; i < kTilesQ; ++i) {
           if (!wait_or_abort(p_ready + i, j & 1, abort_flag)) {
             give_up(p.status, 145, abort_flag);
             ok = false;
             break;
           }
+          ATTN_DIAG_LAP(2 + i);
           tc_fence_after();
           issue_pv(i, st, j > 0);
           if (j + 1 < n_kv) {
@@ -256,21 +261,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               ok = false;
               break;
             }
+            ATTN_DIAG_LAP(4);
             tc_fence_after();
             issue_qk(i, nst);
             umma_commit(s_full + i);  // also covers O_i += P_i·V_j: the softmax group may rescale O_i once it sees S_i
           } else {
             umma_commit(o_full + i);
           }
+          ATTN_DIAG_LAP(5);
         }
         if (!ok) break;
         umma_commit(v_empty + st);
         if (j + 1 < n_kv) umma_commit(k_empty + nst);
       }
+      ATTN_DIAG_FLUSH(32, 6, true);
     }
-  } else if (warp >= 4) {
+  } else {
     // ------------------------------------------------------------------ softmax groups
-    const int tile = (warp - 4) >> 2;  // 0 or 1
+    const int tile = (warp - 2) >> 2;  // 0 or 1
     const int q = warp & 3;            // TMEM lane quarter of this warp
     const int r = q * 32 + lane;       // row inside the tile
     const int qpos = q0 + tile * kTileQ + r;  // position inside the sequence
@@ -279,34 +287,39 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t t_o = tmem_base + kColO + tile * kTileKV + (static_cast<uint32_t>(q * 32) << 16);
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
+    ATTN_DIAG_DECL(7);
     for (int j = 0; j < n_kv; ++j) {
       if (!__all_sync(0xffffffffu, wait_or_abort(s_full + tile, j & 1, abort_flag))) {  // one verdict per warp: the TMEM accesses below are warp-collective
         give_up(p.status, 147, abort_flag);
         ok = false;
         break;
       }
+      ATTN_DIAG_LAP(0);
       tc_fence_after();
       const int kv0 = j * kTileKV;
       // keys beyond the end of the sequence, and keys above the diagonal, are masked; whole tiles below both limits skip the test
       const int limit = p.causal ? min(seq_len - 1, qpos) : seq_len - 1;  // last visible key of this row
       const bool need_mask = kv0 + kTileKV - 1 > (p.causal ? min(seq_len - 1, q0 + tile * kTileQ) : seq_len - 1);
-      // Pass 1: the row maximum.  The S row is read 64 columns at a time (twice in total: TMEM reads are cheap, registers are not).
-      float mx = -INFINITY;
+      // The whole S row in ONE round of TMEM loads (four loads in flight, one wait): the load latency is paid once per tile instead of
+      // once per chunk and pass -- it sits on the critical path, because the tensor cores wait for this tile's P.
+      float s[kTileKV];
 #pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) {
-        float s[64];
-        tmem_ld_32x32(t_s + hlf * 64, s);
-        tmem_ld_32x32(t_s + hlf * 64 + 32, s + 32);
-        tmem_ld_wait();
-        if (need_mask) {
+      for (int c = 0; c < kTileKV / 32; ++c) tmem_ld_32x32(t_s + c * 32, s + c * 32);
+      tmem_ld_wait();
+      ATTN_DIAG_LAP(1);
+      if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (kv0 + hlf * 64 + c > limit) s[c] = -INFINITY;
-        }
-#pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, s[c]);
+        for (int c = 0; c < kTileKV; ++c)
+          if (kv0 + c > limit) s[c] = -INFINITY;
       }
-      mx *= p.scale_log2;
+      float m8[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) m8[e] = s[e];
+#pragma unroll
+      for (int c = 8; c < kTileKV; c += 8)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m8[e] = fmaxf(m8[e], s[c + e]);
+      float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))) * p.scale_log2;
       // lazy maximum: keep the value in use unless this row's maximum outgrew it by more than the threshold
       const bool grow = mx > m_used + kRescaleThreshold;
       const float m_new = grow ? mx : m_used;
@@ -324,41 +337,34 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       m_used = m_new;
+      ATTN_DIAG_LAP(2);
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;  // a row with no visible key so far: every s is -inf, p = 0
-      // Pass 2: probabilities.  P (bf16, two per column) overwrites S from column 0: the 32 columns written for one half lie inside
-      // the 64 columns just read for it, and every thread touches its own row only.
-      float rs = 0.f;
+      // probabilities in place: the bf16 pairs take over the registers of the scores they replace; P then overwrites S from column 0
+      uint32_t* pk = reinterpret_cast<uint32_t*>(s);
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) {
-        float s[64];
-        tmem_ld_32x32(t_s + hlf * 64, s);
-        tmem_ld_32x32(t_s + hlf * 64 + 32, s + 32);
-        tmem_ld_wait();
-        uint32_t pk[32];
-#pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));
-          float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
-          if (need_mask) {
-            if (kv0 + hlf * 64 + c > limit) p0 = 0.f;
-            if (kv0 + hlf * 64 + c + 1 > limit) p1 = 0.f;
-          }
-          rs += p0 + p1;
-          const bf162 h = __floats2bfloat162_rn(p0, p1);
-          pk[c / 2] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        tmem_st_32x32(t_s + hlf * 32, pk);
+      for (int c = 0; c < kTileKV; c += 2) {
+        const float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));      // masked scores are -inf: exp2 gives 0
+        const float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
+        rs4[(c >> 1) & 3] += p0 + p1;
+        const bf162 h = __floats2bfloat162_rn(p0, p1);
+        pk[c / 2] = *reinterpret_cast<const uint32_t*>(&h);
       }
-      l_sum += rs;
+      l_sum += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      ATTN_DIAG_LAP(3);
+#pragma unroll
+      for (int c = 0; c < kTileKV / 64; ++c) tmem_st_32x32(t_s + c * 32, pk + c * 32);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready + tile);
+      ATTN_DIAG_LAP(4);
     }
     if (ok) {
       if (!__all_sync(0xffffffffu, wait_or_abort(o_full + tile, 0, abort_flag))) {
         give_up(p.status, 148, abort_flag);
       } else {
+        ATTN_DIAG_LAP(5);
         tc_fence_after();
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
         bf16* orow = p.O + static_cast<int64_t>(seq_start + qpos) * p.ldo + head * D;
@@ -378,8 +384,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         if (row_ok) p.lse[static_cast<int64_t>(head) * p.T + seq_start + qpos] = m_used * 0.6931471805599453f + __logf(l_sum);
+        ATTN_DIAG_LAP(6);
       }
     }
+    ATTN_DIAG_FLUSH(40 + tile * 8, 7, lane == 0 && ((warp - 2) & 3) == 0);
   }
 
   tc_fence_before();
@@ -425,5 +433,8 @@ int flash_attention_fwd(const void* q, const void* k, const void* v, const int* 
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
+
+// Phase-timer table of the forward kernel (64 counters of clock cycles); all zero unless built with -DUNIRL_B200_ATTN_DIAG.
+ATTN_DIAG_DEFINE_READER(attention_fwd_diag_read)
 
 }  // namespace ub

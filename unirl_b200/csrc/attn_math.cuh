@@ -11,6 +11,47 @@
 
 namespace ub {
 
+// Phase timers of the attention kernels, compiled in only with -DUNIRL_B200_ATTN_DIAG (a development build: the product build has none
+// of this).  A role accumulates clock64() differences per phase in registers and adds them to g_attn_diag[slot] when it leaves; the
+// host reads the table of a translation unit with the reader ATTN_DIAG_DEFINE_READER defines there.  Slots: forward issuer 32.., forward softmax of tile 0 / 1 40.. / 48..,
+// backward issuer 0.., backward compute warp 8.. .
+#ifdef UNIRL_B200_ATTN_DIAG
+constexpr bool kAttnDiag = true;
+static __device__ unsigned long long g_attn_diag[64];  // one table per translation unit (no relocatable device code in this build)
+#define ATTN_DIAG_DECL(n) unsigned long long diag_acc[n] = {}; long long diag_t = clock64()
+#define ATTN_DIAG_LAP(slot)                      \
+  do {                                           \
+    const long long diag_now = clock64();        \
+    diag_acc[slot] += diag_now - diag_t;         \
+    diag_t = diag_now;                           \
+  } while (0)
+#define ATTN_DIAG_FLUSH(base, n, pred)                                                          \
+  do {                                                                                          \
+    if (pred)                                                                                   \
+      for (int diag_i = 0; diag_i < (n); ++diag_i) atomicAdd(&g_attn_diag[(base) + diag_i], diag_acc[diag_i]); \
+  } while (0)
+#define ATTN_DIAG_DEFINE_READER(name)                                                                        \
+  int name(unsigned long long* out, int reset) {                                                             \
+    if (cudaMemcpyFromSymbol(out, g_attn_diag, sizeof(unsigned long long) * 64) != cudaSuccess) return -1;  \
+    if (reset) {                                                                                             \
+      unsigned long long zeros[64] = {};                                                                     \
+      if (cudaMemcpyToSymbol(g_attn_diag, zeros, sizeof(zeros)) != cudaSuccess) return -1;                   \
+    }                                                                                                        \
+    return 64;                                                                                               \
+  }
+#else
+constexpr bool kAttnDiag = false;
+#define ATTN_DIAG_DEFINE_READER(name)                   \
+  int name(unsigned long long* out, int reset) {        \
+    for (int i = 0; i < 64; ++i) out[i] = 0;            \
+    (void)reset;                                        \
+    return 0;                                           \
+  }
+#define ATTN_DIAG_DECL(n) do { } while (0)
+#define ATTN_DIAG_LAP(slot) do { } while (0)
+#define ATTN_DIAG_FLUSH(base, n, pred) do { } while (0)
+#endif
+
 __device__ __forceinline__ float exp2_mufu(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

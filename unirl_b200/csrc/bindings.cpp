@@ -655,6 +655,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sde_replay_bwd", &sde_replay_bwd);
   m.def("attn_varlen_fwd", &attn_varlen_fwd);
   m.def("attn_varlen_bwd", &attn_varlen_bwd);
+  m.def("attn_diag", [](bool backward, bool reset) {  // phase timers of the attention kernels: empty unless built with -DUNIRL_B200_ATTN_DIAG
+    unsigned long long t[64];
+    const int n = backward ? ub::attention_bwd_diag_read(t, reset) : ub::attention_fwd_diag_read(t, reset);
+    TORCH_CHECK(n >= 0, "attn_diag: reading the timer table failed");
+    return std::vector<int64_t>(t, t + n);
+  });
   m.def("gemm_bf16_tn", &gemm_bf16_tn);
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out") = py::none(),
         py::arg("accumulate") = false);

@@ -108,6 +108,9 @@ int flash_attention_fwd(const void* q, const void* k, const void* v, const int* 
                         int64_t ldq, int64_t ldk, int64_t ldv, int64_t ldo, float scale, int causal, int* status, cudaStream_t s);
 
 int64_t flash_attention_bwd_workspace_floats(int T, int Hq, int D);
+// Phase timers of the attention kernels (clock cycles per phase, 64 slots each); return 0 and zeros unless built with -DUNIRL_B200_ATTN_DIAG.
+int attention_fwd_diag_read(unsigned long long* out, int reset);
+int attention_bwd_diag_read(unsigned long long* out, int reset);
 int flash_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, const int* cu_seqlens, void* dq, void* dk,
                         void* dv, float* workspace, int T, int B, int Hq, int Hkv, int D, int64_t ldq, int64_t ldk, int64_t ldv, int64_t ldo, int64_t lddo,
                         float scale, int causal, int* status, cudaStream_t s);

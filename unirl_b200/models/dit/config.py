@@ -71,20 +71,21 @@ PRESETS: Dict[str, Callable[[], FamilySpec]] = {
     # ---- Stable Diffusion 3.5 Medium: 24 MMDiT blocks, 1536 wide, dual attention in the first 13, sin-cos table 384
     "sd35-medium": lambda: FamilySpec(
         DiTConfig(name="sd35-medium", hidden_size=1536, num_heads=24, head_dim=64, in_channels=16, num_joint_blocks=24, dual_attention_blocks=tuple(range(13)),
-                  text_dim=4096, pooled_dim=2048, pos_embed="sincos2d", pos_embed_max_size=384, final_text_block=False),
+                  text_dim=4096, pooled_dim=2048, pos_embed="sincos2d", pos_embed_max_size=384, pos_embed_base_size=64, final_text_block=False),
         [TextEncoderConfig.clip_l(), TextEncoderConfig.clip_g(), TextEncoderConfig.t5_xxl()], "sd3", VAEConfig(), 3.0, False, "cps"),
     "tiny-sd3": lambda: FamilySpec(_tiny("tiny-sd3", pos_embed="sincos2d", dual_attention_blocks=(0,), final_text_block=False, pooled_dim=64), _tiny_text(3), "sd3",
                                    VAEConfig.tiny(), 3.0, False, "cps"),
     # ---- WAN 2.1: cross-attention video DiT (14B: 40 blocks x 5120, 1.3B: 30 x 1536), UMT5 text, 3-D rope
     "wan21-14b": lambda: FamilySpec(
         DiTConfig(name="wan21-14b", hidden_size=5120, num_heads=40, head_dim=128, in_channels=16, num_joint_blocks=0, num_cross_blocks=40, ffn_dim=13824, text_dim=4096,
-                  pooled_dim=0, rope_axes=(44, 42, 42), is_video=True),
+                  pooled_dim=0, rope_axes=(44, 42, 42), is_video=True, qk_norm_scope="full", text_in_layers=2, final_modulation="table"),
         [TextEncoderConfig.umt5_xxl()], "single", VAEConfig(latent_channels=16, scaling_factor=1.0, shift_factor=0.0), 3.0, False, "dance"),
     "wan21-1.3b": lambda: FamilySpec(
         DiTConfig(name="wan21-1.3b", hidden_size=1536, num_heads=12, head_dim=128, in_channels=16, num_joint_blocks=0, num_cross_blocks=30, ffn_dim=8960, text_dim=4096,
-                  pooled_dim=0, rope_axes=(44, 42, 42), is_video=True),
+                  pooled_dim=0, rope_axes=(44, 42, 42), is_video=True, qk_norm_scope="full", text_in_layers=2, final_modulation="table"),
         [TextEncoderConfig.umt5_xxl()], "single", VAEConfig(latent_channels=16, scaling_factor=1.0, shift_factor=0.0), 3.0, False, "dance"),
-    "tiny-wan": lambda: FamilySpec(_tiny("tiny-wan", num_joint_blocks=0, num_cross_blocks=2, pooled_dim=0, is_video=True), _tiny_text(), "single", VAEConfig.tiny(), 3.0,
+    "tiny-wan": lambda: FamilySpec(_tiny("tiny-wan", num_joint_blocks=0, num_cross_blocks=2, pooled_dim=0, is_video=True, qk_norm_scope="full", text_in_layers=2,
+                                         final_modulation="table"), _tiny_text(), "single", VAEConfig.tiny(), 3.0,
                                    False, "dance"),
     # ---- Qwen-Image: 60 joint blocks x 3072, packed 2x2 latents (64 channels), LLM text tower, dynamic shift
     "qwen-image": lambda: FamilySpec(

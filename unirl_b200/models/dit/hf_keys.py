@@ -8,8 +8,9 @@ Families covered: the joint-block (MMDiT) layouts -- Stable Diffusion 3.x (``SD3
 stream models (``FluxTransformer2DModel`` naming: FLUX.2 klein, HunyuanVideo, Z-Image single-stream) and Qwen-Image
 (``QwenImageTransformer2DModel``).  The reference loads these through diffusers itself (``unirl/models/sd3/bundle.py``,
 ``unirl/models/qwen_image/bundle.py``, ``unirl/models/flux2_klein/bundle.py``); here the published weights go straight into the native module.
-WAN's cross-attention blocks differ in structure (full-width q/k norms, a two-layer text embedder, table-based final modulation) and
-keep loading native checkpoints.
+WAN 2.1 / 2.2 text-to-video (``WanTransformer3DModel``: cross-attention blocks with full-width q/k norms, a two-layer text embedder and
+table-based modulation; ``unirl/models/wan21/diffusion.py:62-158``) has a bridge of its own; the image-to-video checkpoints carry an
+extra image embedder that the native module does not have and are refused.
 """
 
 from __future__ import annotations
@@ -83,6 +84,16 @@ def _single_block(w: _Writer, s: str, d: str) -> None:
     w.put(f"{d}.out_proj", f"{s}.proj_out")  # diffusers applies it to cat(attention, mlp): the same column order as here
 
 
+def _channel_major_out(w: _Writer, patch_elems: int) -> None:
+    """SD3 and WAN un-patchify their output with the channel LAST inside a patch (row ``p * C + c`` of ``proj_out``); the native module
+    keeps the channel first, as on the input side (row ``c * P + p``).  Reorder the rows of the output projection accordingly."""
+    for suf in ("weight", "bias"):
+        k = f"final_proj.{suf}"
+        if k in w.out and patch_elems > 1:
+            t = w.out[k]
+            w.out[k] = t.reshape(patch_elems, -1, *t.shape[1:]).transpose(0, 1).reshape(t.shape)
+
+
 def _finish(w: _Writer, strict: bool) -> Dict[str, Tensor]:
     if "patch_embed.weight" in w.out and w.out["patch_embed.weight"].dim() > 2:  # a conv patch embedder: [h, c, (t,) p, p] -> [h, c * t * p * p]
         w.out["patch_embed.weight"] = w.out["patch_embed.weight"].flatten(1)
@@ -93,7 +104,7 @@ def _finish(w: _Writer, strict: bool) -> Dict[str, Tensor]:
     return w.out
 
 
-def sd3_from_diffusers(sd: Dict[str, Tensor], num_joint_blocks: int, dual: Iterable[int] = (), strict: bool = False) -> Dict[str, Tensor]:
+def sd3_from_diffusers(sd: Dict[str, Tensor], num_joint_blocks: int, dual: Iterable[int] = (), strict: bool = False, patch_elems: int = 4) -> Dict[str, Tensor]:
     w = _Writer(sd)
     w.put("patch_embed", "pos_embed.proj")
     w.put("time_in.0", "time_text_embed.timestep_embedder.linear_1")
@@ -108,6 +119,7 @@ def sd3_from_diffusers(sd: Dict[str, Tensor], num_joint_blocks: int, dual: Itera
     for i in range(num_joint_blocks):
         _joint_block(w, f"transformer_blocks.{i}", f"joint_blocks.{i}", mod=("norm1.linear", "norm1_context.linear"), img_mlp=("ff.net.0.proj", "ff.net.2"),
                      txt_mlp=("ff_context.net.0.proj", "ff_context.net.2"), dual=i in dual)
+    _channel_major_out(w, patch_elems)
     return _finish(w, strict)
 
 
@@ -148,13 +160,52 @@ def qwen_image_from_diffusers(sd: Dict[str, Tensor], num_joint_blocks: int, stri
     return _finish(w, strict)
 
 
+def wan_from_diffusers(sd: Dict[str, Tensor], num_cross_blocks: int, strict: bool = False, patch_elems: int = 4) -> Dict[str, Tensor]:
+    """``WanTransformer3DModel`` naming (``condition_embedder.*``, ``blocks.<i>.attn1 / attn2 / ffn / norm2 / scale_shift_table``)."""
+    if any(k.startswith("condition_embedder.image_embedder") for k in sd):
+        raise KeyError("image-to-video WAN checkpoints (condition_embedder.image_embedder.*) are not supported by the native module")
+    w = _Writer(sd)
+    w.put("patch_embed", "patch_embedding")  # a Conv3d kernel [h, c, 1, 2, 2]: flattened to the patchify order (c, t, rows, cols) below
+    w.put("time_in.0", "condition_embedder.time_embedder.linear_1")
+    w.put("time_in.1", "condition_embedder.time_embedder.linear_2")
+    w.put("time_proj", "condition_embedder.time_proj")
+    w.put("text_in", "condition_embedder.text_embedder.linear_1")
+    w.put("text_in2", "condition_embedder.text_embedder.linear_2")
+    w.put("final_proj", "proj_out")
+    if "scale_shift_table" in sd:
+        w.out["final_table"] = sd["scale_shift_table"].reshape(2, -1)
+        w.used.add("scale_shift_table")
+    for i in range(num_cross_blocks):
+        s_, d = f"blocks.{i}", f"cross_blocks.{i}"
+        if f"{s_}.scale_shift_table" in sd:
+            w.out[f"{d}.modulation"] = sd[f"{s_}.scale_shift_table"].reshape(6, -1)
+            w.used.add(f"{s_}.scale_shift_table")
+        w.fuse(f"{d}.self_attn.qkv", [f"{s_}.attn1.to_q", f"{s_}.attn1.to_k", f"{s_}.attn1.to_v"])
+        w.put(f"{d}.self_attn.out", f"{s_}.attn1.to_out.0")
+        w.raw(f"{d}.self_attn.q_norm", f"{s_}.attn1.norm_q.weight")
+        w.raw(f"{d}.self_attn.k_norm", f"{s_}.attn1.norm_k.weight")
+        w.put(f"{d}.cross_q", f"{s_}.attn2.to_q")
+        w.fuse(f"{d}.cross_kv", [f"{s_}.attn2.to_k", f"{s_}.attn2.to_v"])
+        w.put(f"{d}.cross_out", f"{s_}.attn2.to_out.0")
+        w.raw(f"{d}.cross_q_norm", f"{s_}.attn2.norm_q.weight")
+        w.raw(f"{d}.cross_k_norm", f"{s_}.attn2.norm_k.weight")
+        w.put(f"{d}.cross_norm", f"{s_}.norm2")
+        w.put(f"{d}.mlp.fc1", f"{s_}.ffn.net.0.proj")
+        w.put(f"{d}.mlp.fc2", f"{s_}.ffn.net.2")
+    _channel_major_out(w, patch_elems)
+    return _finish(w, strict)
+
+
 def bridge_for(preset: str) -> Optional[Callable[..., Dict[str, Tensor]]]:
     """The bridge of a preset family, or ``None`` when the family loads native checkpoints only."""
     p = preset.lower()
     if "sd3" in p:
-        return lambda sd, cfg, strict=False: sd3_from_diffusers(sd, cfg.num_joint_blocks, cfg.dual_attention_blocks, strict)
+        return lambda sd, cfg, strict=False: sd3_from_diffusers(sd, cfg.num_joint_blocks, cfg.dual_attention_blocks, strict,
+                                                                 cfg.patch_size[0] * cfg.patch_size[1] * cfg.patch_size[2])
     if "qwen-image" in p or "qwen_image" in p:
         return lambda sd, cfg, strict=False: qwen_image_from_diffusers(sd, cfg.num_joint_blocks, strict)
+    if "wan" in p:
+        return lambda sd, cfg, strict=False: wan_from_diffusers(sd, cfg.num_cross_blocks, strict, cfg.patch_size[0] * cfg.patch_size[1] * cfg.patch_size[2])
     if any(k in p for k in ("flux", "hunyuan-video", "z-image")) and "15" not in p:
         return lambda sd, cfg, strict=False: flux_from_diffusers(sd, cfg.num_joint_blocks, cfg.num_single_blocks, strict)
     return None
@@ -172,6 +223,11 @@ def load_diffusers_transformer(model: torch.nn.Module, sd: Dict[str, Tensor], pr
     if bad:
         k = bad[0]
         raise ValueError(f"shape mismatch for {k}: checkpoint {tuple(native[k].shape)} vs module {tuple(own[k].shape)} ({len(bad)} in total)")
+    table = native.pop("pos_embed_table", None)  # SD3 stores its sin-cos table [1, S * S, h]: take it as published instead of recomputing it
+    if table is not None and getattr(model, "pos_table", None) is not None:
+        if table.numel() != model.pos_table.numel():
+            raise ValueError(f"position table of {table.numel()} values does not fit the module's {tuple(model.pos_table.shape)}")
+        model.pos_table.copy_(table.reshape(model.pos_table.shape).to(model.pos_table.dtype))
     missing, unexpected = model.load_state_dict({k: v for k, v in native.items() if k in own}, strict=False)
     unexpected = list(unexpected) + [k for k in native if k not in own]
     if strict and missing:
@@ -179,4 +235,4 @@ def load_diffusers_transformer(model: torch.nn.Module, sd: Dict[str, Tensor], pr
     return list(missing), unexpected
 
 
-__all__ = ["sd3_from_diffusers", "flux_from_diffusers", "qwen_image_from_diffusers", "bridge_for", "load_diffusers_transformer"]
+__all__ = ["sd3_from_diffusers", "flux_from_diffusers", "qwen_image_from_diffusers", "wan_from_diffusers", "bridge_for", "load_diffusers_transformer"]

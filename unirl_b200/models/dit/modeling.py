@@ -59,6 +59,7 @@ class DiTConfig:
     qk_norm: bool = True
     pos_embed: str = "rope"  # "sincos2d" (additive table) | "rope" (axial rotary)
     pos_embed_max_size: int = 192
+    pos_embed_base_size: Optional[int] = None  # grid size the sin-cos coordinates are normalised to (SD3: 64); None: unscaled
     rope_axes: Tuple[int, int, int] = (16, 24, 24)  # head_dim split over (frame, row, col); must sum to head_dim
     rope_theta: float = 10000.0
     guidance_embed: bool = False
@@ -68,6 +69,9 @@ class DiTConfig:
     vae_scale_factor: int = 8
     vae_temporal_factor: int = 4
     final_text_block: bool = True  # False: the last joint block does not update the text stream (SD3 "context_pre_only")
+    qk_norm_scope: str = "head"  # "head": RMS norm per head over head_dim | "full": one RMS norm over the whole projection (WAN)
+    text_in_layers: int = 1  # 2: text embedder is Linear -> GELU(tanh) -> Linear (WAN)
+    final_modulation: str = "linear"  # "linear": Linear(silu(vec)) -> (shift, scale) | "table": learned [2, h] table + vec (WAN)
 
     def __post_init__(self) -> None:
         self.patch_size = tuple(int(p) for p in self.patch_size)
@@ -103,15 +107,16 @@ def timestep_embedding(t: torch.Tensor, dim: int, max_period: float = 10000.0) -
     return torch.cat([torch.cos(args), torch.sin(args)], -1)
 
 
-def sincos_2d_table(dim: int, size: int, device: Any = "cpu") -> torch.Tensor:
-    """``[size, size, dim]`` fixed 2-D sin-cos table (half of the channels per axis)."""
-    def axis(n: int, d: int) -> torch.Tensor:
-        omega = 1.0 / (10000 ** (torch.arange(d // 2, dtype=torch.float64) / (d / 2)))
-        out = torch.arange(n, dtype=torch.float64)[:, None] * omega[None]
-        return torch.cat([out.sin(), out.cos()], -1)
-
-    rows, cols = axis(size, dim // 2), axis(size, dim // 2)
-    return torch.cat([rows[:, None].expand(size, size, -1), cols[None].expand(size, size, -1)], -1).float().to(device)
+def sincos_2d_table(dim: int, size: int, device: Any = "cpu", base_size: Optional[int] = None) -> torch.Tensor:
+    """``[size, size, dim]`` fixed 2-D sin-cos table as published with SD3: coordinates ``arange(size) * base_size / size`` (``base_size`` is
+    the training grid, 64 for the 1024-pixel models; ``None`` leaves them unscaled), the first half of the channels encodes the column and
+    the second half the row, each half as ``[sin | cos]`` over ``dim / 4`` frequencies ``10000^(-2 i / (dim / 2))``."""
+    half = dim // 2
+    omega = 1.0 / (10000 ** (torch.arange(half // 2, dtype=torch.float64) / (half / 2)))
+    coord = torch.arange(size, dtype=torch.float64) * ((base_size / size) if base_size else 1.0)
+    ang = coord[:, None] * omega[None]
+    axis = torch.cat([ang.sin(), ang.cos()], -1)  # [size, dim / 2]
+    return torch.cat([axis[None].expand(size, size, -1), axis[:, None].expand(size, size, -1)], -1).float().to(device)
 
 
 def axial_rope(cfg: DiTConfig, grid: Tuple[int, int, int], device: Any, text_len: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -164,9 +169,18 @@ def _heads(x: torch.Tensor, n: int) -> torch.Tensor:
 
 
 def _qk_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """RMS norm of ``x [..., heads, head_dim]``: per head when ``w`` has ``head_dim`` entries, over all heads jointly when it has ``heads * head_dim``."""
     if w is None:
         return x
+    if w.numel() != x.shape[-1]:
+        return rmsnorm(x.reshape(-1, w.numel()), w, eps).view_as(x)
     return rmsnorm(x.reshape(-1, x.shape[-1]), w, eps).view_as(x)
+
+
+def _qk_norm_param(cfg: "DiTConfig", dtype: Any, device: Any) -> Optional[nn.Parameter]:
+    if not cfg.qk_norm:
+        return None
+    return nn.Parameter(torch.ones(cfg.hidden_size if cfg.qk_norm_scope == "full" else cfg.head_dim, dtype=dtype, device=device))
 
 
 class _Attn(nn.Module):
@@ -176,8 +190,7 @@ class _Attn(nn.Module):
         super().__init__()
         h = cfg.hidden_size
         self.qkv = _Lin(h, 3 * h, True, dtype, device, {names[0]: (0, h), names[1]: (h, h), names[2]: (2 * h, h)})
-        self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
-        self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.q_norm, self.k_norm = _qk_norm_param(cfg, dtype, device), _qk_norm_param(cfg, dtype, device)
         self.out = _Lin(h, h, True, dtype, device, {names[3]: (0, h)}) if out_proj else None
         self.n, self.eps = cfg.num_heads, cfg.eps
 
@@ -287,8 +300,7 @@ class CrossBlock(nn.Module):
         self.self_attn = _Attn(cfg, True, dtype, device)
         self.cross_q = _Lin(h, h, True, dtype, device, {"attn2.to_q": (0, h)})
         self.cross_kv = _Lin(h, 2 * h, True, dtype, device, {"attn2.to_k": (0, h), "attn2.to_v": (h, h)})
-        self.cross_q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
-        self.cross_k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
+        self.cross_q_norm, self.cross_k_norm = _qk_norm_param(cfg, dtype, device), _qk_norm_param(cfg, dtype, device)
         self.cross_out = _Lin(h, h, True, dtype, device, {"attn2.to_out.0": (0, h)})
         self.cross_norm = nn.LayerNorm(h, eps=cfg.eps, dtype=dtype, device=device)
         self.mlp = _MLP(cfg, dtype, device)
@@ -324,14 +336,19 @@ class DiTTransformer(nn.Module):
         self.pooled_in = nn.ModuleList([_Lin(cfg.pooled_dim, h, True, dtype, device), _Lin(h, h, True, dtype, device)]) if cfg.pooled_dim else None
         self.guidance_in = nn.ModuleList([_Lin(cfg.time_freq_dim, h, True, dtype, device), _Lin(h, h, True, dtype, device)]) if cfg.guidance_embed else None
         self.text_in = _Lin(cfg.text_dim, h, True, dtype, device)
+        self.text_in2 = _Lin(h, h, True, dtype, device) if cfg.text_in_layers == 2 else None
         self.time_proj = _Lin(h, 6 * h, True, dtype, device) if cfg.num_cross_blocks else None
         self.joint_blocks = nn.ModuleList(JointBlock(cfg, i, dtype, device) for i in range(cfg.num_joint_blocks))
         self.single_blocks = nn.ModuleList(SingleBlock(cfg, i, dtype, device) for i in range(cfg.num_single_blocks))
         self.cross_blocks = nn.ModuleList(CrossBlock(cfg, i, dtype, device) for i in range(cfg.num_cross_blocks))
-        self.final_mod = _Lin(h, 2 * h, True, dtype, device)
+        if cfg.final_modulation == "table":
+            self.final_mod = None
+            self.final_table = nn.Parameter(torch.zeros(2, h, dtype=dtype, device=device))
+        else:
+            self.final_mod = _Lin(h, 2 * h, True, dtype, device)
         self.final_proj = _Lin(h, (cfg.out_channels or cfg.in_channels) * cfg.patch_size[0] * cfg.patch_size[1] * cfg.patch_size[2], True, dtype, device)
         if cfg.pos_embed == "sincos2d":
-            self.register_buffer("pos_table", sincos_2d_table(h, cfg.pos_embed_max_size, device).to(dtype), persistent=False)
+            self.register_buffer("pos_table", sincos_2d_table(h, cfg.pos_embed_max_size, device, cfg.pos_embed_base_size).to(dtype), persistent=False)
         self._rope_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
 
     # ---- init ------------------------------------------------------------------------------------------
@@ -397,6 +414,8 @@ class DiTTransformer(nn.Module):
         if self.guidance_in is not None and guidance is not None:
             vec = vec + self.guidance_in[1](F.silu(self.guidance_in[0](timestep_embedding(guidance, cfg.time_freq_dim).to(dtype))))
         txt = self.text_in(text.to(dtype))
+        if self.text_in2 is not None:
+            txt = self.text_in2(F.gelu(txt, approximate="tanh"))
         nt = txt.shape[1]
         sp = self.sp if (self.sp is not None and self.sp.size > 1) else None
         if sp is not None:
@@ -422,7 +441,10 @@ class DiTTransformer(nn.Module):
             cross_ctx = AttnContext(cos, sin, 0, sp, text_mask)
             for blk in self.cross_blocks:
                 img = run(blk, img, txt, tproj, cross_ctx)
-        shift, scale = self.final_mod(F.silu(vec)).chunk(2, -1)
+        if self.final_mod is None:
+            shift, scale = (self.final_table.unsqueeze(0) + vec.unsqueeze(1)).unbind(1)
+        else:
+            shift, scale = self.final_mod(F.silu(vec)).chunk(2, -1)
         out = self.final_proj(layernorm_modulate(img, shift, scale, cfg.eps))
         if sp is not None:
             out = sp.gather_sequence(out)

@@ -104,8 +104,14 @@ class LatentVAE(nn.Module):
             reps = torch.tensor([1] + [c.temporal_factor] * (f - 1), device=z.device)
             z = z.repeat_interleave(reps, dim=2).permute(0, 2, 1, 3, 4).reshape(-1, ch, h, w)
         p = next(self.parameters())
-        x = self.dec(self.dec_in(z.to(p.dtype)))
-        img = (self.dec_out(F.silu(self.dec_norm(x))).float() / 2 + 0.5).clamp(0, 1)
+        # The widest decoder activation is [n, 128, 8H, 8W]: decode about four megapixels of output at a time (4 images at 1024 x 1024),
+        # so a rollout batch of any size needs a bounded workspace.
+        step = max(1, (1 << 22) // max(1, 64 * z.shape[-2] * z.shape[-1]))
+        outs = []
+        for i in range(0, z.shape[0], step):
+            x = self.dec(self.dec_in(z[i : i + step].to(p.dtype)))
+            outs.append((self.dec_out(F.silu(self.dec_norm(x))).float() / 2 + 0.5).clamp(0, 1))
+        img = outs[0] if len(outs) == 1 else torch.cat(outs, 0)
         return img.view(b, -1, *img.shape[1:]) if video else img
 
     @torch.no_grad()

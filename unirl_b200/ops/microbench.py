@@ -387,6 +387,18 @@ def case_attention(args: argparse.Namespace) -> None:
     except Exception as e:  # noqa: BLE001
         row["dense_cudnn_fwd_error"] = str(e)[:120]
     row.update(frac_of_peak=row["packed_fwd_bwd_tflops"] / pk["tflops"], peak=pk["kind"])
+    from unirl_b200.ops._ext import require_ext
+
+    C = require_ext()
+    if C.attn_diag(False, True):  # a build with phase timers (-DUNIRL_B200_ATTN_DIAG): one clean forward + backward, cycles per phase summed over CTAs
+        packed()
+        torch.cuda.synchronize()
+        f, bw = C.attn_diag(False, True), C.attn_diag(True, True)
+        row["diag_fwd_issuer"] = dict(zip(("start", "wait_v", "wait_p0", "wait_p1", "wait_k", "issue"), f[32:38]))
+        for t in (0, 1):
+            row[f"diag_fwd_softmax{t}"] = dict(zip(("wait_s", "tmem_ld", "max", "exp", "st_arrive", "wait_o", "epilogue"), f[40 + 8 * t : 47 + 8 * t]))
+        row["diag_bwd_issuer"] = dict(zip(("wait_kv", "wait_qdo", "s_then_wait_free", "dp_then_wait_pds", "issue"), bw[0:5]))
+        row["diag_bwd_compute"] = dict(zip(("stats", "wait_sdp", "wait_store", "elementwise", "st_fence_arrive", "wait_dq", "dq_read", "dq_stage"), bw[8:16]))
     _emit(row)
 
 

@@ -23,7 +23,7 @@ import torch
 from unirl_b200.distributed.group.dispatch import Dispatch, distributed
 from unirl_b200.models.qwen3.bundle import resolve_model_config
 from unirl_b200.models.qwen3.chat_template import Qwen3ChatTemplateStage, pad_right
-from unirl_b200.models.qwen3.modeling import Qwen3Transformer, TPContext, shard_param
+from unirl_b200.models.qwen3.modeling import Qwen3Transformer, TPContext, shard_param, tp_slice_spec
 from unirl_b200.models.tokenizer import load_tokenizer
 from unirl_b200.models.types.contracts import unpad_prompts
 from unirl_b200.models.qwen3.ar import pack_text_segment
@@ -59,6 +59,7 @@ class NativeARRolloutEngine(BaseRolloutEngine):
         self._shares_trainer = False
         self._sync_groups: Dict[str, Any] = {}
         self._asleep = False
+        self._lora_base: Dict[str, torch.Tensor] = {}  # pristine copies of the weights that currently carry a folded-in adapter
 
     # ---- construction ----------------------------------------------------------------------------------
     def setup(self, *a: Any, **k: Any) -> None:
@@ -187,6 +188,7 @@ class NativeARRolloutEngine(BaseRolloutEngine):
             self._host_weights = {n: p.detach().to("cpu", non_blocking=True) for n, p in self.model.named_parameters()}
             for p in self.model.parameters():
                 p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+            self._lora_base = {n: t.to("cpu", non_blocking=True) for n, t in self._lora_base.items()}
         self._asleep = True
 
     @distributed(dispatch_mode=Dispatch.BROADCAST)
@@ -197,6 +199,7 @@ class NativeARRolloutEngine(BaseRolloutEngine):
             for n, p in self.model.named_parameters():
                 p.data = host[n].to(dev, non_blocking=True)
             self._host_weights = None
+            self._lora_base = {n: t.to(dev, non_blocking=True) for n, t in self._lora_base.items()}
         self._asleep = False
 
     @property
@@ -215,8 +218,71 @@ class NativeARRolloutEngine(BaseRolloutEngine):
         n = 0
         if not self._shares_trainer:
             for bucket in serialized_named_tensors:
-                n += self._load_full({k[len(track_prefix):] if track_prefix and k.startswith(track_prefix) else k: v for k, v in bucket.items()})
+                named = {k[len(track_prefix):] if track_prefix and k.startswith(track_prefix) else k: v for k, v in bucket.items()}
+                n += self._load_full(named)
+                for k in named:  # a new base replaces the one an adapter was folded into
+                    self._lora_base.pop(k, None)
         self.weight_version += 1
+        return n
+
+    @distributed(dispatch_mode=Dispatch.BROADCAST)
+    @torch.no_grad()
+    def set_lora_from_tensors(self, adapter_name: str, lora_tensors: Dict[str, torch.Tensor], *, peft_config: Optional[dict] = None) -> int:
+        """Install / refresh LoRA adapters from in-memory tensors keyed ``[<prefix>]model.layers.<i>.<self_attn|mlp>.<target>.lora_{A,B}[.<adapter>].weight``.
+
+        The engine folds the adapters into its own copy of the weights: ``W[rows] = W_base[rows] + (alpha / r) * B @ A`` in fp32, for the
+        row block of the fused weight the target names, sharded like the weight under tensor parallelism.  Decode therefore runs the same
+        fused kernels and captured graphs as without adapters (the storage is updated in place), at the cost of one extra copy of each
+        adapted weight (kept so that every sync starts from the pristine base instead of accumulating rounding).  A target that was
+        adapted before and is missing from this call gets its base back.  Returns the number of adapter pairs applied.
+        Parity: the engine-side half of ``unirl/distributed/weight_sync/lora/*`` (the stock engines load adapters through their own
+        LoRA managers).
+        """
+        import re
+
+        lora_tensors = getattr(lora_tensors, "value", lora_tensors)  # payloads pushed through the controller travel in an opaque wrapper
+        self.weight_version += 1
+        if self._shares_trainer:  # the trainer's module already carries the live adapters
+            return 0
+        pc = peft_config or {}
+        scale = float(pc.get("lora_alpha", 16)) / float(pc.get("r", 8))
+        c, tp = self.model.cfg, self.model.tp
+        d, nq, nkv, inter = c.head_dim, c.num_attention_heads, c.num_key_value_heads, c.intermediate_size
+        where = {"q_proj": ("qkv_proj", 0), "k_proj": ("qkv_proj", nq * d), "v_proj": ("qkv_proj", (nq + nkv) * d), "o_proj": ("o_proj", 0),
+                 "gate_proj": ("gate_up_proj", 0), "up_proj": ("gate_up_proj", inter), "down_proj": ("down_proj", 0)}
+        pat = re.compile(r"(?:^|\.)layers\.(\d+)\.(?:self_attn|mlp)\.(\w+)\.lora_([AB])(?:\.[^.]+)?\.weight$")
+        pairs: Dict[Any, Dict[str, torch.Tensor]] = {}
+        for k, v in lora_tensors.items():
+            m = pat.search(k)
+            if m is None or m.group(2) not in where:
+                continue
+            pairs.setdefault((int(m.group(1)), m.group(2)), {})[m.group(3)] = v
+        by_param: Dict[str, List[Any]] = {}
+        for (li, target), ab in pairs.items():
+            if "A" not in ab or "B" not in ab:
+                raise ValueError(f"LoRA payload has only one of lora_A / lora_B for layer {li} {target}")
+            pname, off = where[target]
+            by_param.setdefault(f"layers.{li}.{pname}", []).append((off, ab["A"], ab["B"]))
+        own = dict(self.model.named_parameters())
+        n = 0
+        for name in [k for k in self._lora_base if k not in by_param]:  # adapters withdrawn: back to the base
+            own[name].copy_(self._lora_base.pop(name))
+        for name, parts in by_param.items():
+            p = own[name]
+            base = self._lora_base.get(name)
+            if base is None:
+                base = self._lora_base[name] = p.detach().clone()
+            kind, _ = tp_slice_spec(name, c)
+            rows = p.shape[0] * (tp.size if kind == "rows" else 1)
+            cols = p.shape[1] * (tp.size if kind == "cols" else 1)
+            delta = torch.zeros(rows, cols, dtype=torch.float32, device=p.device)
+            for off, a, b in parts:
+                a, b = a.to(p.device, torch.float32), b.to(p.device, torch.float32)
+                if a.shape[1] != cols or off + b.shape[0] > rows or a.shape[0] != b.shape[1]:
+                    raise ValueError(f"LoRA shapes A{tuple(a.shape)} B{tuple(b.shape)} do not fit {name} [{rows}, {cols}] at row {off}")
+                delta[off : off + b.shape[0]].addmm_(b, a, alpha=scale)
+                n += 1
+            p.copy_((base.float() + shard_param(delta, name, c, tp.rank, tp.size)).to(p.dtype))
         return n
 
     @distributed(dispatch_mode=Dispatch.BROADCAST)
