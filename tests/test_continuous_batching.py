@@ -80,5 +80,8 @@ def test_continuous_batching_on_gpu_with_shared_prefixes_and_graphs():
     same = sum(int(torch.equal(a, b)) for a, b in pairs)
     assert head >= int(0.9 * len(prompts)) and same >= int(0.5 * len(prompts)), f"{head} of {len(prompts)} sequences agree on 12 tokens, {same} on all"
     assert outs[True].num_steps < 0.95 * outs[False].num_steps, (outs[True].num_steps, outs[False].num_steps)
-    total = sum(int(t.numel()) for t in outs[True].tokens)
-    assert outs[True].num_steps <= total / 32 + 96 + 16
+    # A group of 4 samples shares its prompt pages and leaves the batch when its longest member stops, so a slot is busy for the
+    # group's maximum length, not for its own: with geometric lengths that is about twice the mean.  Bound: the group-maximum lengths
+    # packed perfectly into the 8 group slots, plus one full-length tail.
+    lens = torch.tensor([int(t.numel()) for t in outs[True].tokens]).view(-1, 4)
+    assert outs[True].num_steps <= int(lens.max(1).values.sum()) / 8 + 96 + 16, (outs[True].num_steps, lens.max(1).values.sum())

@@ -65,3 +65,58 @@ def test_http_service_and_client_agree_with_local_scoring():
     finally:
         server.should_exit = True
         th.join(10)
+
+
+def _tiny_clip_checkpoint(path):
+    """A CLIP checkpoint in the Hugging Face layout (random weights, a 54-entry vocabulary), written with the library's own save calls."""
+    import json
+    import os
+
+    from transformers import CLIPConfig, CLIPModel, CLIPTextConfig, CLIPTokenizer, CLIPVisionConfig
+
+    cfg = CLIPConfig(text_config=CLIPTextConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, max_position_embeddings=16,
+                                                eos_token_id=1, bos_token_id=0, pad_token_id=1).to_dict(),
+                     vision_config=CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=32, patch_size=8).to_dict(),
+                     projection_dim=16)
+    torch.manual_seed(0)
+    model = CLIPModel(cfg).eval()
+    model.save_pretrained(path)
+    vocab = {"<|startoftext|>": 0, "<|endoftext|>": 1}
+    for ch in "abcdefghijklmnopqrstuvwxyz":
+        vocab[ch] = len(vocab)
+        vocab[ch + "</w>"] = len(vocab)
+    with open(os.path.join(path, "vocab.json"), "w") as f:
+        json.dump(vocab, f)
+    with open(os.path.join(path, "merges.txt"), "w") as f:
+        f.write("#version: 0.2\n")
+    tok = CLIPTokenizer(os.path.join(path, "vocab.json"), os.path.join(path, "merges.txt"))
+    tok.save_pretrained(path)
+    with open(os.path.join(path, "preprocessor_config.json"), "w") as f:
+        json.dump({"image_mean": [0.5, 0.4, 0.3], "image_std": [0.2, 0.25, 0.3], "size": {"shortest_edge": 32}, "crop_size": 32}, f)
+    return model, tok
+
+
+def test_scorers_load_a_published_layout_checkpoint_and_follow_the_published_formulas(tmp_path):
+    from unirl_b200.reward.local.scorers import build_scorer
+    from unirl_b200.types.primitives import Texts
+    from unirl_b200.types.reward import RewardRequest
+
+    model, tok = _tiny_clip_checkpoint(str(tmp_path))
+    px = torch.rand(3, 3, 32, 32, generator=torch.Generator().manual_seed(1))  # already at the model's size: no resampling in the way of the comparison
+    prompts = ["a cab", "zz top", "quiet fox"]
+    with torch.no_grad():
+        mean, std = torch.tensor([0.5, 0.4, 0.3]).view(1, 3, 1, 1), torch.tensor([0.2, 0.25, 0.3]).view(1, 3, 1, 1)
+        enc = tok(prompts, padding="max_length", truncation=True, max_length=16, return_tensors="pt")
+        out = model(pixel_values=(px - mean) / std, input_ids=enc["input_ids"], attention_mask=enc["attention_mask"])
+        logits = out.logits_per_image.diagonal()
+    req = RewardRequest(primitives={"text": Texts(texts=prompts)}, generated={"image": px}, sample_ids=["a", "b", "c"])
+    clip = build_scorer("clip", model_id=str(tmp_path), device="cpu", batch_size=2).compute_rewards(req)
+    torch.testing.assert_close(torch.tensor(clip.rewards), logits / 30, rtol=1e-4, atol=1e-5)
+    pick = build_scorer("pickscore", model_id=str(tmp_path), device="cpu").compute_rewards(req)
+    torch.testing.assert_close(torch.tensor(pick.rewards), logits / 26, rtol=1e-4, atol=1e-5)
+    hps = build_scorer("hpsv2", model_id=str(tmp_path), device="cpu").compute_rewards(req)
+    torch.testing.assert_close(torch.tensor(hps.rewards), logits / model.logit_scale.exp().item(), rtol=1e-4, atol=1e-5)
+    big = build_scorer("clip", model_id=str(tmp_path), device="cpu").score(torch.rand(2, 3, 80, 56), ["a", "b"])  # resized and cropped on the way in
+    assert big.shape == (2,) and torch.isfinite(big).all()
+    with pytest.raises(FileNotFoundError, match="never downloaded"):
+        build_scorer("clip", model_id="openai/clip-vit-large-patch14", device="cpu")

@@ -1,4 +1,6 @@
 """Unified text + image model: MoE routing, incremental decoding, rollout/replay alignment on both tracks, joint training."""
+import os
+
 import pytest
 import torch
 
@@ -110,3 +112,61 @@ def test_unified_trainer_with_an_engine_pair_and_the_memory_choreography(tmp_pat
         assert len(train_rows) == 2 and any(k.startswith("train/ar/") for k in train_rows[0]) and any(k.startswith("train/image/") for k in train_rows[0])
     finally:
         tr.shutdown()
+
+
+def test_meta_construction_and_per_rank_materialisation(tmp_path):
+    """``from_meta_config`` allocates nothing; ``materialize`` fills by global tensor name, so an expert-parallel rank that keeps half of
+    the experts holds exactly the values of the unsharded model for them; a native sharded checkpoint round-trips, each rank reading
+    only what it kept."""
+    from unirl_b200.models.unified.modeling import MoEFFN
+    from unirl_b200.models.unified.pipeline import UnifiedBundle, UnifiedPipelineConfig, save_native_checkpoint
+
+    cfg = UnifiedPipelineConfig(pretrained_model_ckpt_path="random:tiny-unified", model_precision="fp32", device="cpu", init_seed=5)
+    meta = UnifiedBundle.from_meta_config(cfg)
+    assert all(p.is_meta for p in meta.transformer.parameters()) and all(p.is_meta for p in meta.vae.parameters())
+    full = meta.materialize("cpu")
+    assert not any(p.is_meta for p in full.transformer.parameters()) and not any(p.is_meta for p in full.vae.parameters())
+    again = UnifiedBundle.from_meta_config(cfg).materialize("cpu", with_aux=False)
+    assert all(p.is_meta for p in again.vae.parameters()), "with_aux=False leaves the codec unallocated"
+    ref = dict(full.transformer.named_parameters())
+    for n, p in again.transformer.named_parameters():
+        assert torch.equal(p, ref[n]), n
+
+    class _EP:  # what MoEFFN.shard_experts needs from an expert-parallel context
+        def __init__(self, rank, size):
+            self.rank, self.size = rank, size
+
+        def local_experts(self, n):
+            per = n // self.size
+            return list(range(self.rank * per, (self.rank + 1) * per))
+
+    n_experts = full.transformer.cfg.num_experts
+    seen = 0
+    for rank in (0, 1):
+        part = UnifiedBundle.from_meta_config(cfg).materialize("cpu", with_aux=False, ep=_EP(rank, 2))
+        moes = [m for m in part.transformer.modules() if isinstance(m, MoEFFN)]
+        assert moes and all(len(m.experts) == n_experts // 2 and m.expert_ids == _EP(rank, 2).local_experts(n_experts) for m in moes)
+        for n, p in part.transformer.named_parameters():
+            if ".experts." in n:
+                pre, rest = n.split(".experts.")
+                slot, leaf = rest.split(".", 1)
+                g = f"{pre}.experts.{rank * (n_experts // 2) + int(slot)}.{leaf}"
+                seen += 1
+            else:
+                g = n
+            assert torch.equal(p, ref[g]), (n, g)
+    assert seen == sum(1 for n in ref if ".experts." in n), "the two ranks together hold every expert exactly once"
+
+    with torch.no_grad():  # a trained-looking model: perturb, save, reload
+        for p in full.transformer.parameters():
+            p.add_(torch.randn_like(p) * 0.01)
+    save_native_checkpoint(full.transformer, str(tmp_path), "tiny-unified", shard_bytes=200_000)
+    assert len([f for f in os.listdir(tmp_path) if f.endswith(".safetensors")]) > 1, "several shards"
+    ck = UnifiedPipelineConfig(pretrained_model_ckpt_path=str(tmp_path), model_precision="fp32", device="cpu")
+    loaded = UnifiedBundle.from_config(ck)
+    for n, p in loaded.transformer.named_parameters():
+        assert torch.equal(p, ref[n]), n
+    part = UnifiedBundle.from_meta_config(ck).materialize("cpu", with_aux=False, ep=_EP(1, 2))
+    first = next(m for m in part.transformer.modules() if isinstance(m, MoEFFN))
+    name = next(n for n, m in part.transformer.named_modules() if m is first)
+    assert torch.equal(first.experts[0].down, ref[f"{name}.experts.{n_experts // 2}.down"])

@@ -7,9 +7,9 @@
 //   warp 0        loader     : TMA loads of Q (once) and of the K / V ring (128 keys per stage, two stages)
 //   warp 1        MMA issuer : S_i = Q_i·K_jᵀ into TMEM (both operands K-major from shared memory), then O_i += P_i·V_j with P_i read
 //                              from TMEM (it overwrites the first half of S_i's columns) and V_j read as stored (MN-major B operand)
-//   warps 2..5    softmax of tile 0: tcgen05.ld one whole S row per thread, running max / sum in the log2 domain, P -> bf16 -> tcgen05.st
-//   warps 6..9    softmax of tile 1 (same code); while one group does exponentials the other group's MMAs run
-//   (four consecutive warps cover the four TMEM lane quarters, warp index modulo 4, in some order)
+//   warps 4..7    softmax of tile 0: tcgen05.ld one S row per thread, running max / sum in the log2 domain, P -> bf16 -> tcgen05.st
+//   warps 8..11   softmax of tile 1 (same code); while one group does exponentials the other group's MMAs run
+//   (warps 2, 3 idle, so that each softmax group is one aligned group of four warps covering the four TMEM lane quarters in order)
 //
 // The running maximum is updated lazily: O is rescaled only when a row's maximum grew by more than 2^8 since the value in use, so the
 // accumulator read-modify-write in TMEM is rare; the final normalisation uses the exact sum for the maximum in use.
@@ -37,8 +37,9 @@ namespace {
 constexpr int kTileQ = 128;      // rows per query tile (= TMEM lanes)
 constexpr int kTilesQ = 2;       // query tiles per CTA
 constexpr int kTileKV = 128;     // keys per K / V stage
-constexpr int kKvStages = 2;
-constexpr int kFaThreads = 320;  // warp 0: loader, warp 1: issuer, warps 2-5: softmax of tile 0, warps 6-9: softmax of tile 1 (200 registers each)
+constexpr int kKStages = 3;      // K is needed one step before V (S(j+1) is issued behind P(j)·V(j)): its ring is one stage deeper
+constexpr int kVStages = 2;
+constexpr int kFaThreads = 384;  // warp group 0: loader, issuer (+2 idle warps); warp groups 1 and 2: softmax of tile 0 / 1
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 template <int D>
@@ -47,8 +48,8 @@ struct FaLayout {
   static constexpr int kTileBytes = (D / 64) * kBoxBytes;    // a [128 x D] operand tile
   static constexpr int kQ = 0;
   static constexpr int kK = kTilesQ * kTileBytes;
-  static constexpr int kV = kK + kKvStages * kTileBytes;
-  static constexpr int kBars = kV + kKvStages * kTileBytes;
+  static constexpr int kV = kK + kKStages * kTileBytes;
+  static constexpr int kBars = kV + kVStages * kTileBytes;
   static constexpr int kTotal = kBars + 256 + 1024 /*alignment slack*/;
 };
 
@@ -135,11 +136,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint64_t* q_full = bars;                       // 1
-  uint64_t* k_full = bars + 1;                   // kKvStages
-  uint64_t* k_empty = k_full + kKvStages;
-  uint64_t* v_full = k_empty + kKvStages;
-  uint64_t* v_empty = v_full + kKvStages;
-  uint64_t* s_full = v_empty + kKvStages;        // kTilesQ
+  uint64_t* k_full = bars + 1;                   // kKStages
+  uint64_t* k_empty = k_full + kKStages;
+  uint64_t* v_full = k_empty + kKStages;         // kVStages
+  uint64_t* v_empty = v_full + kVStages;
+  uint64_t* s_full = v_empty + kVStages;         // kTilesQ
   uint64_t* p_ready = s_full + kTilesQ;          // kTilesQ
   uint64_t* o_full = p_ready + kTilesQ;          // kTilesQ
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kTilesQ);
@@ -148,9 +149,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kKvStages; ++s) {
+    for (int s = 0; s < kKStages; ++s) {
       mbar_init(k_full + s, 1);
       mbar_init(k_empty + s, 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
       mbar_init(v_full + s, 1);
       mbar_init(v_empty + s, 1);
     }
@@ -183,21 +186,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < D / 64; ++c)
           tma_load_2d(smem + L::kQ + i * L::kTileBytes + c * L::kBoxBytes, &tmQ, head * D + c * 64, seq_start + q0 + i * kTileQ, q_full);
       for (int j = 0; j < n_kv; ++j) {
-        const int st = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1;
+        const int ks = j % kKStages, vs = j % kVStages;
         const int row = seq_start + j * kTileKV;
-        if (!wait_or_abort(k_empty + st, ph ^ 1, abort_flag)) {
+        if (!wait_or_abort(k_empty + ks, ((j / kKStages) & 1) ^ 1, abort_flag)) {
           give_up(p.status, 141, abort_flag);
           break;
         }
-        mbar_expect_tx(k_full + st, L::kTileBytes);
-        for (int c = 0; c < D / 64; ++c) tma_load_2d(smem + L::kK + st * L::kTileBytes + c * L::kBoxBytes, &tmK, kv_head * D + c * 64, row, k_full + st);
-        if (!wait_or_abort(v_empty + st, ph ^ 1, abort_flag)) {
-          give_up(p.status, 142, abort_flag);
-          break;
+        mbar_expect_tx(k_full + ks, L::kTileBytes);
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(smem + L::kK + ks * L::kTileBytes + c * L::kBoxBytes, &tmK, kv_head * D + c * 64, row, k_full + ks);
+        if (j >= 1) {  // V trails K by one block in the queue of loads, as it does in the order of use
+          const int jv = j - 1, vsp = jv % kVStages;
+          if (!wait_or_abort(v_empty + vsp, ((jv / kVStages) & 1) ^ 1, abort_flag)) {
+            give_up(p.status, 142, abort_flag);
+            break;
+          }
+          mbar_expect_tx(v_full + vsp, L::kTileBytes);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_2d(smem + L::kV + vsp * L::kTileBytes + c * L::kBoxBytes, &tmV, kv_head * D + c * 64, seq_start + jv * kTileKV, v_full + vsp);
         }
-        mbar_expect_tx(v_full + st, L::kTileBytes);
-        for (int c = 0; c < D / 64; ++c) tma_load_2d(smem + L::kV + st * L::kTileBytes + c * L::kBoxBytes, &tmV, kv_head * D + c * 64, row, v_full + st);
+        if (j == n_kv - 1) {
+          if (!wait_or_abort(v_empty + vs, ((j / kVStages) & 1) ^ 1, abort_flag)) {
+            give_up(p.status, 142, abort_flag);
+            break;
+          }
+          mbar_expect_tx(v_full + vs, L::kTileBytes);
+          for (int c = 0; c < D / 64; ++c) tma_load_2d(smem + L::kV + vs * L::kTileBytes + c * L::kBoxBytes, &tmV, kv_head * D + c * 64, row, v_full + vs);
+        }
       }
     }
   } else if (warp == 1) {
@@ -240,8 +254,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       ATTN_DIAG_LAP(0);
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j % kKvStages, nst = (j + 1) % kKvStages;
-        if (!wait_or_abort(v_full + st, (j / kKvStages) & 1, abort_flag)) {
+        const int st = j % kVStages, nst = (j + 1) % kKStages;
+        if (!wait_or_abort(v_full + st, (j / kVStages) & 1, abort_flag)) {
           give_up(p.status, 144, abort_flag);
           break;
         }
@@ -256,7 +270,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_after();
           issue_pv(i, st, j > 0);
           if (j + 1 < n_kv) {
-            if (i == 0 && !wait_or_abort(k_full + nst, ((j + 1) / kKvStages) & 1, abort_flag)) {
+            if (i == 0 && !wait_or_abort(k_full + nst, ((j + 1) / kKStages) & 1, abort_flag)) {
               give_up(p.status, 146, abort_flag);
               ok = false;
               break;
@@ -276,9 +290,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       ATTN_DIAG_FLUSH(32, 6, true);
     }
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax groups
-    const int tile = (warp - 2) >> 2;  // 0 or 1
+    const int tile = (warp - 4) >> 2;  // 0 or 1
     const int q = warp & 3;            // TMEM lane quarter of this warp
     const int r = q * 32 + lane;       // row inside the tile
     const int qpos = q0 + tile * kTileQ + r;  // position inside the sequence
@@ -300,26 +314,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // keys beyond the end of the sequence, and keys above the diagonal, are masked; whole tiles below both limits skip the test
       const int limit = p.causal ? min(seq_len - 1, qpos) : seq_len - 1;  // last visible key of this row
       const bool need_mask = kv0 + kTileKV - 1 > (p.causal ? min(seq_len - 1, q0 + tile * kTileQ) : seq_len - 1);
-      // The whole S row in ONE round of TMEM loads (four loads in flight, one wait): the load latency is paid once per tile instead of
-      // once per chunk and pass -- it sits on the critical path, because the tensor cores wait for this tile's P.
-      float s[kTileKV];
+      // Pass 1: the row maximum.  The S row is read 64 columns at a time (twice in total: TMEM reads are cheap, registers are not).
+      float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < kTileKV / 32; ++c) tmem_ld_32x32(t_s + c * 32, s + c * 32);
-      tmem_ld_wait();
-      ATTN_DIAG_LAP(1);
-      if (need_mask) {
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        float s[64];
+        tmem_ld_32x32(t_s + hlf * 64, s);
+        tmem_ld_32x32(t_s + hlf * 64 + 32, s + 32);
+        tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < kTileKV; ++c)
-          if (kv0 + c > limit) s[c] = -INFINITY;
+          for (int c = 0; c < 64; ++c)
+            if (kv0 + hlf * 64 + c > limit) s[c] = -INFINITY;
+        }
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, s[c]);
       }
-      float m8[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) m8[e] = s[e];
-#pragma unroll
-      for (int c = 8; c < kTileKV; c += 8)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) m8[e] = fmaxf(m8[e], s[c + e]);
-      float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))) * p.scale_log2;
+      mx *= p.scale_log2;
+      ATTN_DIAG_LAP(1);
       // lazy maximum: keep the value in use unless this row's maximum outgrew it by more than the threshold
       const bool grow = mx > m_used + kRescaleThreshold;
       const float m_new = grow ? mx : m_used;
@@ -339,21 +351,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       m_used = m_new;
       ATTN_DIAG_LAP(2);
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;  // a row with no visible key so far: every s is -inf, p = 0
-      // probabilities in place: the bf16 pairs take over the registers of the scores they replace; P then overwrites S from column 0
-      uint32_t* pk = reinterpret_cast<uint32_t*>(s);
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      // Pass 2: probabilities.  P (bf16, two per column) overwrites S from column 0: the 32 columns written for one half lie inside
+      // the 64 columns just read for it, and every thread touches its own row only.
+      float rs = 0.f;
 #pragma unroll
-      for (int c = 0; c < kTileKV; c += 2) {
-        const float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));      // masked scores are -inf: exp2 gives 0
-        const float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
-        rs4[(c >> 1) & 3] += p0 + p1;
-        const bf162 h = __floats2bfloat162_rn(p0, p1);
-        pk[c / 2] = *reinterpret_cast<const uint32_t*>(&h);
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        float s[64];
+        tmem_ld_32x32(t_s + hlf * 64, s);
+        tmem_ld_32x32(t_s + hlf * 64 + 32, s + 32);
+        tmem_ld_wait();
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));
+          float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
+          if (need_mask) {
+            if (kv0 + hlf * 64 + c > limit) p0 = 0.f;
+            if (kv0 + hlf * 64 + c + 1 > limit) p1 = 0.f;
+          }
+          rs += p0 + p1;
+          const bf162 h = __floats2bfloat162_rn(p0, p1);
+          pk[c / 2] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        tmem_st_32x32(t_s + hlf * 32, pk);
       }
-      l_sum += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      l_sum += rs;
       ATTN_DIAG_LAP(3);
-#pragma unroll
-      for (int c = 0; c < kTileKV / 64; ++c) tmem_st_32x32(t_s + c * 32, pk + c * 32);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -387,7 +410,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ATTN_DIAG_LAP(6);
       }
     }
-    ATTN_DIAG_FLUSH(40 + tile * 8, 7, lane == 0 && ((warp - 2) & 3) == 0);
+    ATTN_DIAG_FLUSH(40 + tile * 8, 7, lane == 0 && (warp & 3) == 0);
   }
 
   tc_fence_before();

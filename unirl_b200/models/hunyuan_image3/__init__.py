@@ -13,11 +13,9 @@ class HunyuanImage3PipelineConfig(UnifiedPipelineConfig):
 
 
 class HunyuanImage3Bundle(UnifiedBundle):
-    def materialize(self, device, with_aux=True):
-        """Weights are created directly on the target device by ``from_config``; moving is all that is left to do."""
-        self.transformer.to(device)
-        if with_aux:
-            self.vae.to(device)
+    """``from_meta_config`` builds the 80B mixture-of-experts tree without memory; ``materialize(device, with_aux, ep)`` allocates and fills
+    this rank's share (its experts only under expert parallelism), from checkpoint shards or by name-keyed random init
+    (:class:`unirl_b200.models.unified.pipeline.UnifiedBundle`)."""
 
 
 class HunyuanImage3Pipeline(UnifiedPipeline):

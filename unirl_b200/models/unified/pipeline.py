@@ -65,14 +65,82 @@ class UnifiedBundle(Bundle):
     def model_config(self) -> UnifiedConfig:
         return self.transformer.cfg
 
+    @staticmethod
+    def _model_config(config: UnifiedPipelineConfig) -> UnifiedConfig:
+        """``random:<preset>`` or a native checkpoint directory (``config.json`` with ``{"preset": ..., "model": {overrides}}`` next to
+        ``model-*.safetensors`` shards and ``model.safetensors.index.json``)."""
+        path = config.pretrained_model_ckpt_path
+        if path.startswith("random:"):
+            mcfg = PRESETS[path.split(":", 1)[1].lower()]()
+        else:
+            import json
+            import os
+
+            with open(os.path.join(path, "config.json")) as f:
+                d = json.load(f)
+            mcfg = PRESETS[d["preset"]]()
+            for k, v in (d.get("model") or {}).items():
+                setattr(mcfg, k, v)
+        for k, v in (config.model_overrides or {}).items():
+            setattr(mcfg, k, v)
+        return mcfg
+
+    @classmethod
+    def from_meta_config(cls, config: UnifiedPipelineConfig) -> "UnifiedBundle":
+        """The bundle with every parameter on the ``meta`` device: shapes and module tree only, no memory.  The 80B mixture-of-experts
+        model is built this way on every rank; :meth:`materialize` then allocates and fills what the rank keeps.
+        Parity: ``unirl/models/hunyuan_image3/bundle.py:427`` (``from_meta_config``)."""
+        mcfg = cls._model_config(config)
+        model = UnifiedTransformer(mcfg, dtype=parse_torch_dtype(config.model_precision), device="meta", gradient_checkpointing=config.use_gradient_checkpointing)
+        vcfg = VAEConfig.tiny(mcfg.latent_channels) if mcfg.hidden_size <= 256 else VAEConfig(latent_channels=mcfg.latent_channels)
+        b = cls(model, LatentVAE(vcfg, device="meta"), load_tokenizer(None, mcfg.vocab_size, True), config)
+        b.pretrained_path = None if config.pretrained_model_ckpt_path.startswith("random:") else config.pretrained_model_ckpt_path
+        return b
+
+    @torch.no_grad()
+    def materialize(self, device: Any, with_aux: bool = True, ep: Any = None) -> "UnifiedBundle":
+        """Allocate the parameters on ``device`` and fill them, rank by rank.
+
+        With an expert-parallel context every mixture layer first drops the experts other ranks own (still on ``meta``: nothing was
+        allocated for them), so a rank allocates ``1 / P`` of the routed experts plus the shared parameters.  Values come from the
+        checkpoint directory -- each rank opens the shards and reads only the tensors it kept, under their GLOBAL names
+        (``...experts.<global id>...``) -- or, for ``random:`` presets, from a generator seeded by the tensor's global name, so every
+        rank holds the same value for the same tensor whatever the sharding.  ``with_aux=False`` leaves the codec on ``meta`` (ranks
+        that never decode).  Parity: ``unirl/models/hunyuan_image3/bundle.py:528`` (``materialize``)."""
+        from unirl_b200.models.unified.modeling import MoEFFN
+
+        model = self.transformer
+        if ep is not None and getattr(ep, "size", 1) > 1:
+            for m in model.modules():
+                if isinstance(m, MoEFFN) and m.ep is None:
+                    m.shard_experts(ep)
+        if any(p.is_meta for p in model.parameters()):
+            model.to_empty(device=device)
+            global_names = _global_param_names(model)
+            if self.pretrained_path is None:
+                _init_by_name(model, global_names, int(self.config.init_seed))
+            else:
+                _load_by_name(model, global_names, self.pretrained_path)
+        else:
+            model.to(device)
+        if with_aux:
+            if any(p.is_meta for p in self.vae.parameters()):
+                self.vae.to_empty(device=device)
+                for n, p in self.vae.named_parameters():  # norm scales and biases: identity / zero; the kernels come from init_weights
+                    if p.dim() < 2:
+                        p.fill_(1.0 if n.endswith("weight") else 0.0)
+                self.vae.init_weights(int(self.config.init_seed) + 7)
+            else:
+                self.vae.to(device)
+        return self
+
     @classmethod
     def from_config(cls, config: UnifiedPipelineConfig) -> "UnifiedBundle":
         path = config.pretrained_model_ckpt_path
-        if not path.startswith("random:"):
-            raise NotImplementedError("UnifiedBundle builds random-init presets; checkpoint import for the 80B MoE is per-rank shard loading and is not wired yet")
-        mcfg = PRESETS[path.split(":", 1)[1].lower()]()
-        for k, v in (config.model_overrides or {}).items():
-            setattr(mcfg, k, v)
+        if not path.startswith("random:"):  # a checkpoint: build on meta, then read the shards straight onto the device
+            device = config.device or ("cuda" if torch.cuda.is_available() else "cpu")
+            return cls.from_meta_config(config).materialize(device)
+        mcfg = cls._model_config(config)
         device = config.device or ("cuda" if torch.cuda.is_available() else "cpu")
         model = UnifiedTransformer(mcfg, dtype=parse_torch_dtype(config.model_precision), device=device,
                                    gradient_checkpointing=config.use_gradient_checkpointing).init_weights(config.init_seed)
@@ -81,6 +149,104 @@ class UnifiedBundle(Bundle):
 
     def trainable_modules(self) -> Dict[str, torch.nn.Module]:
         return {"transformer": self.transformer}
+
+
+def _global_param_names(model: torch.nn.Module) -> Dict[str, str]:
+    """Local parameter name → name in the unsharded model: ``...experts.<slot>...`` becomes ``...experts.<global expert id>...``."""
+    from unirl_b200.models.unified.modeling import MoEFFN
+
+    remap: Dict[str, List[int]] = {n: list(m.expert_ids) for n, m in model.named_modules() if isinstance(m, MoEFFN)}
+    out: Dict[str, str] = {}
+    for name, _ in model.named_parameters():
+        g = name
+        for mod, ids in remap.items():
+            pre = f"{mod}.experts."
+            if name.startswith(pre):
+                slot, rest = name[len(pre):].split(".", 1)
+                g = f"{pre}{ids[int(slot)]}.{rest}"
+                break
+        out[name] = g
+    return out
+
+
+def _init_by_name(model: torch.nn.Module, global_names: Dict[str, str], seed: int, std: float = 0.02) -> None:
+    """Deterministic init keyed on the tensor's global name (not on its position in the module tree, which sharding changes)."""
+    import hashlib
+
+    for name, p in model.named_parameters():
+        if p.dim() == 1:
+            p.fill_(1.0)
+            continue
+        g = global_names[name]
+        h = int.from_bytes(hashlib.blake2b(f"{seed}:{g}".encode(), digest_size=8).digest(), "little") & ((1 << 62) - 1)
+        gen = torch.Generator(device="cpu").manual_seed(h)
+        vals = torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std * (0.25 if g == "patch_out" else 1.0), generator=gen)
+        p.copy_(vals.to(p.device))
+
+
+def _load_by_name(model: torch.nn.Module, global_names: Dict[str, str], path: str) -> None:
+    """Read exactly the tensors this rank kept from a sharded safetensors checkpoint (index file: tensor name → shard file)."""
+    import json
+    import os
+
+    from safetensors import safe_open
+
+    index_file = os.path.join(path, "model.safetensors.index.json")
+    if os.path.exists(index_file):
+        with open(index_file) as f:
+            where = json.load(f)["weight_map"]
+    else:
+        where = {}
+        for fn in sorted(os.listdir(path)):
+            if fn.endswith(".safetensors"):
+                with safe_open(os.path.join(path, fn), "pt") as sf:
+                    where.update({k: fn for k in sf.keys()})
+    by_file: Dict[str, List[Tuple[str, torch.nn.Parameter]]] = {}
+    missing = []
+    for name, p in model.named_parameters():
+        g = global_names[name]
+        if g not in where:
+            missing.append(g)
+            continue
+        by_file.setdefault(where[g], []).append((g, p))
+    if missing:
+        raise KeyError(f"checkpoint {path} lacks {len(missing)} tensors this rank needs, e.g. {missing[:4]}")
+    for fn, items in by_file.items():
+        with safe_open(os.path.join(path, fn), "pt") as sf:
+            for g, p in items:
+                t = sf.get_tensor(g)
+                if tuple(t.shape) != tuple(p.shape):
+                    raise ValueError(f"{g}: checkpoint shape {tuple(t.shape)} vs module {tuple(p.shape)}")
+                p.copy_(t.to(p.device, p.dtype))
+
+
+def save_native_checkpoint(model: torch.nn.Module, path: str, preset: str, overrides: Optional[Dict[str, Any]] = None, shard_bytes: int = 1 << 30) -> None:
+    """Write an (unsharded-expert) model as ``config.json`` + ``model-0000k.safetensors`` shards + ``model.safetensors.index.json``."""
+    import json
+    import os
+
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    names = _global_param_names(model)
+    shards: List[Dict[str, torch.Tensor]] = [{}]
+    size = 0
+    for name, p in model.named_parameters():
+        nbytes = p.numel() * p.element_size()
+        if shards[-1] and size + nbytes > shard_bytes:
+            shards.append({})
+            size = 0
+        shards[-1][names[name]] = p.detach().cpu().contiguous()
+        size += nbytes
+    weight_map = {}
+    for i, sd in enumerate(shards):
+        fn = f"model-{i + 1:05d}.safetensors"
+        save_file(sd, os.path.join(path, fn))
+        weight_map.update({k: fn for k in sd})
+    with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+        json.dump({"weight_map": weight_map}, f)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump({"preset": preset, "model": dict(overrides or {})}, f)
 
 
 class UnifiedPipeline(Pipeline):
@@ -163,4 +329,4 @@ class UnifiedPipeline(Pipeline):
         return RolloutResp(tracks=tracks)
 
 
-__all__ = ["UnifiedPipelineConfig", "UnifiedBundle", "UnifiedPipeline", "PRESETS"]
+__all__ = ["UnifiedPipelineConfig", "UnifiedBundle", "UnifiedPipeline", "PRESETS", "save_native_checkpoint"]

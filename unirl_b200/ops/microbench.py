@@ -391,14 +391,16 @@ def case_attention(args: argparse.Namespace) -> None:
 
     C = require_ext()
     if C.attn_diag(False, True):  # a build with phase timers (-DUNIRL_B200_ATTN_DIAG): one clean forward + backward, cycles per phase summed over CTAs
+        C.attn_diag(True, True)
         packed()
         torch.cuda.synchronize()
         f, bw = C.attn_diag(False, True), C.attn_diag(True, True)
         row["diag_fwd_issuer"] = dict(zip(("start", "wait_v", "wait_p0", "wait_p1", "wait_k", "issue"), f[32:38]))
         for t in (0, 1):
-            row[f"diag_fwd_softmax{t}"] = dict(zip(("wait_s", "tmem_ld", "max", "exp", "st_arrive", "wait_o", "epilogue"), f[40 + 8 * t : 47 + 8 * t]))
-        row["diag_bwd_issuer"] = dict(zip(("wait_kv", "wait_qdo", "s_then_wait_free", "dp_then_wait_pds", "issue"), bw[0:5]))
-        row["diag_bwd_compute"] = dict(zip(("stats", "wait_sdp", "wait_store", "elementwise", "st_fence_arrive", "wait_dq", "dq_read", "dq_stage"), bw[8:16]))
+            row[f"diag_fwd_softmax{t}"] = dict(zip(("wait_s", "pass1_max", "rescale", "pass2_exp", "st_arrive", "wait_o", "epilogue"), f[40 + 8 * t : 47 + 8 * t]))
+        row["diag_bwd_issuer"] = dict(zip(("start", "wait_p", "wait_qdo", "wait_ds", "wait_free"), bw[0:5]))
+        row["diag_bwd_compute"] = dict(zip(("stats", "wait_s", "phase_a", "wait_dp", "phase_b"), bw[8:13]))
+        row["diag_bwd_drain"] = dict(zip(("wait_dq", "dq_read", "dq_stage", "wait_reads"), bw[16:20]))
     _emit(row)
 
 

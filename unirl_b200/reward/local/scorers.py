@@ -12,8 +12,13 @@ checks.
 ``GenEvalScorer``       compositional check against ``metadata`` (object counts / colours / positions) given detections in
                         ``metadata["detections"]``.
 
-Weights are random-init unless ``checkpoint`` (a state dict in this module's key grammar) is given; the towers are the
-native ``TextEncoder`` and a small ViT.  Parity: ``unirl/reward/local/{aesthetic,clip,hpsv2,hpsv3,ocr,pickscore,geneval2,
+Published weights: ``model_id`` (or the environment variable ``UNIRL_B200_<VARIANT>_PATH``) names a local directory holding a CLIP-family
+checkpoint in the Hugging Face layout (``openai/clip-vit-large-patch14`` for ``clip``, ``yuvalkirstain/PickScore_v1`` with the
+``laion/CLIP-ViT-H-14`` processor for ``pickscore``, a converted ViT-H-14 for the HPS variants); the towers are then the published ones, the
+images are resized / centre-cropped / normalised on the device as the checkpoint's processor configuration says, and the score follows
+the published formula of the variant: ``clip`` = logit_scale · cos / 30, ``pickscore`` = logit_scale · cos / 26, ``hpsv2`` / ``hpsv3`` = cos.
+Without ``model_id`` the towers are small random-init stand-ins (native ``TextEncoder`` + a small ViT) with the same score scales, which
+keeps recipes runnable without any checkpoint.  Parity: ``unirl/reward/local/{aesthetic,clip,hpsv2,hpsv3,ocr,pickscore,geneval2,
 image_reward,videopickscore,video}.py`` (scoring contracts and score scales).
 """
 
@@ -52,6 +57,63 @@ class _ViT(nn.Module):
         return self.proj(self.norm(self.blocks(x)[:, 0]))
 
 
+class _PublishedClip:
+    """A CLIP-family checkpoint in the Hugging Face layout, read from a local directory: towers, tokenizer and preprocessing."""
+
+    def __init__(self, model_path: str, processor_path: Optional[str], device: torch.device):
+        import json
+        import os
+
+        from transformers import AutoTokenizer, CLIPModel
+
+        if not os.path.isdir(model_path):
+            raise FileNotFoundError(f"scorer checkpoint {model_path!r} is not a local directory (checkpoints are never downloaded)")
+        self.device = device
+        self.model = CLIPModel.from_pretrained(model_path, local_files_only=True).float().eval().requires_grad_(False).to(device)
+        proc = processor_path or model_path
+        self.tok = AutoTokenizer.from_pretrained(proc, local_files_only=True)
+        pre: Dict[str, Any] = {}
+        f = os.path.join(proc, "preprocessor_config.json")
+        if os.path.exists(f):
+            with open(f) as fh:
+                pre = json.load(fh)
+        self.size = int(self.model.config.vision_config.image_size)
+        self.mean = torch.tensor(pre.get("image_mean", [0.48145466, 0.4578275, 0.40821073]), device=device).view(1, 3, 1, 1)
+        self.std = torch.tensor(pre.get("image_std", [0.26862954, 0.26130258, 0.27577711]), device=device).view(1, 3, 1, 1)
+        self.max_len = int(self.model.config.text_config.max_position_embeddings)
+
+    @staticmethod
+    def _features(out: Any) -> torch.Tensor:
+        if isinstance(out, torch.Tensor):
+            return out
+        if getattr(out, "pooler_output", None) is not None:
+            return out.pooler_output
+        return out[0]
+
+    @torch.no_grad()
+    def images(self, px: torch.Tensor) -> torch.Tensor:
+        """``[B, 3, H, W]`` in ``[0, 1]`` → unit-norm embeddings (shortest edge to the model's size, bicubic; centre crop; normalise)."""
+        x = px.to(self.device).float()
+        h, w = x.shape[-2:]
+        r = self.size / min(h, w)
+        nh, nw = max(self.size, round(h * r)), max(self.size, round(w * r))
+        if (nh, nw) != (h, w):
+            x = F.interpolate(x, size=(nh, nw), mode="bicubic", antialias=True, align_corners=False).clamp(0, 1)
+        top, left = (nh - self.size) // 2, (nw - self.size) // 2
+        x = (x[..., top : top + self.size, left : left + self.size] - self.mean) / self.std
+        return F.normalize(self._features(self.model.get_image_features(pixel_values=x)), dim=-1)
+
+    @torch.no_grad()
+    def texts(self, prompts: List[str]) -> torch.Tensor:
+        enc = self.tok(prompts, padding="max_length", truncation=True, max_length=self.max_len, return_tensors="pt")
+        enc = {k: v.to(self.device) for k, v in enc.items() if k in ("input_ids", "attention_mask")}
+        return F.normalize(self._features(self.model.get_text_features(**enc)), dim=-1)
+
+    @property
+    def logit_scale(self) -> torch.Tensor:
+        return self.model.logit_scale.exp()
+
+
 def _pixels_of(request: RewardRequest) -> torch.Tensor:
     gen = request.generated
     for key in ("image", "images"):
@@ -78,11 +140,23 @@ class ClipStyleScorer(RewardBackend):
     VARIANTS = {"clip": (1.0, 0.0), "pickscore": (100.0, 0.0), "hpsv2": (100.0, 0.0), "hpsv3": (100.0, 0.0), "image_reward": (1.0, 0.0),
                 "unified_reward": (5.0, 0.0), "editreward": (1.0, 0.0), "wise": (1.0, 0.0)}
 
-    def __init__(self, variant: str = "clip", width: int = 64, device: Optional[str] = None, seed: int = 0, checkpoint: Optional[str] = None, **_kw: Any):
+    #: published score of a variant from the cosine similarity and the checkpoint's logit scale
+    PUBLISHED = {"clip": lambda cos, ls: ls * cos / 30.0, "pickscore": lambda cos, ls: ls * cos / 26.0, "hpsv2": lambda cos, ls: cos, "hpsv3": lambda cos, ls: cos}
+
+    def __init__(self, variant: str = "clip", width: int = 64, device: Optional[str] = None, seed: int = 0, checkpoint: Optional[str] = None,
+                 model_id: Optional[str] = None, processor_id: Optional[str] = None, batch_size: int = 8, **_kw: Any):
+        import os
+
         if variant not in self.VARIANTS:
             raise ValueError(f"unknown scorer variant {variant!r}; known: {sorted(self.VARIANTS)}")
         self.variant, (self.scale, self.bias) = variant, self.VARIANTS[variant]
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.batch_size = max(1, int(batch_size))
+        model_id = model_id or os.environ.get(f"UNIRL_B200_{variant.upper()}_PATH")
+        self.published = _PublishedClip(model_id, processor_id, self.device) if model_id else None
+        if self.published is not None:
+            self.vision = self.text = self.tok = self.head = None
+            return
         torch.manual_seed(seed)
         self.vision = _ViT(width, out_dim=width).to(self.device).eval().requires_grad_(False)
         self.text = TextEncoder(TextEncoderConfig.tiny("clip", hidden=width, vocab=4096, max_length=77), dtype=torch.float32, device=self.device).init_weights(seed + 1)
@@ -107,6 +181,13 @@ class ClipStyleScorer(RewardBackend):
 
     @torch.no_grad()
     def score(self, pixels: torch.Tensor, prompts: List[str]) -> torch.Tensor:
+        if self.published is not None:
+            out = []
+            for i in range(0, pixels.shape[0], self.batch_size):
+                cos = (self.published.images(pixels[i : i + self.batch_size]) * self.published.texts(prompts[i : i + self.batch_size])).sum(-1)
+                fn = self.PUBLISHED.get(self.variant)
+                out.append(fn(cos, self.published.logit_scale) if fn is not None else cos * self.scale + self.bias)
+            return torch.cat(out)
         img = self.vision(pixels.to(self.device))
         txt = self._embed_text(prompts)
         if self.head is not None:
@@ -120,10 +201,16 @@ class ClipStyleScorer(RewardBackend):
         return RewardResponse.ok(s.float().cpu().tolist(), {self.variant: s.float().cpu().tolist()}, time.perf_counter() - t0)
 
     def offload(self) -> None:
-        self.vision.to("cpu"), self.text.to("cpu")
+        if self.published is not None:
+            self.published.model.to("cpu")
+        else:
+            self.vision.to("cpu"), self.text.to("cpu")
 
     def onload(self) -> None:
-        self.vision.to(self.device), self.text.to(self.device)
+        if self.published is not None:
+            self.published.model.to(self.device)
+        else:
+            self.vision.to(self.device), self.text.to(self.device)
 
 
 class AestheticScorer(RewardBackend):

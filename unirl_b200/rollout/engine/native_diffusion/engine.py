@@ -110,6 +110,8 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
         self._shares_trainer = False
         self._sync_groups: Dict[str, Any] = {}
         self._host_regions: Dict[str, Dict[str, torch.Tensor]] = {}
+        self._pinned: Dict[str, Dict[str, torch.Tensor]] = {}  # pinned host copies, allocated once per region and kept across sleep / wake cycles
+        self._stale = set(REGIONS)  # regions whose pinned copy is older than the device weights (frozen towers are copied out once)
         self._graphed: Optional[GraphedVelocity] = None
 
     def setup(self, *a: Any, **k: Any) -> None:
@@ -166,24 +168,33 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
     @distributed(dispatch_mode=Dispatch.BROADCAST)
     def sleep(self, tags: Optional[Sequence[str]] = None) -> None:
         """Release device memory of the named regions (default: the frozen aux modules; the transformer only when it is
-        the engine's own copy).  Weights are stashed in pinned host memory."""
+        the engine's own copy).  Weights are stashed in pinned host memory that is allocated once and reused (pinning gigabytes takes
+        seconds); a region whose weights did not change since its last stash (the text towers, the codec) is released without a copy."""
         default = ("text_encoder", "vae") if self._shares_trainer else REGIONS
         for tag in (tags or default):
             if tag not in REGIONS:
                 raise ValueError(f"unknown memory region {tag!r}; regions are {REGIONS}")
             if tag in self._host_regions or (tag == "transformer" and self._shares_trainer):
                 continue
-            stash: Dict[str, torch.Tensor] = {}
+            stash = self._pinned.setdefault(tag, {})
+            fresh = tag not in self._stale
+            found = False
             for i, mod in enumerate(self._regions()[tag]):
                 for n, p in mod.named_parameters():
                     if p.device.type != "cuda":
                         continue
-                    host = torch.empty(p.shape, dtype=p.dtype, pin_memory=True)
-                    host.copy_(p.data, non_blocking=True)
-                    stash[f"{i}.{n}"] = host
+                    key = f"{i}.{n}"
+                    host = stash.get(key)
+                    if host is None or host.shape != p.shape or host.dtype != p.dtype:
+                        host = stash[key] = torch.empty(p.shape, dtype=p.dtype, pin_memory=True)
+                        host.copy_(p.data, non_blocking=True)
+                    elif not fresh:
+                        host.copy_(p.data, non_blocking=True)
+                    found = True
                     p.data = torch.empty(0, dtype=p.dtype, device=p.device)
-            if stash:
+            if found:
                 self._host_regions[tag] = stash
+                self._stale.discard(tag)
         if torch.cuda.is_available():
             torch.cuda.synchronize()
             torch.cuda.empty_cache()
@@ -210,6 +221,7 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
 
     # ---- weight receive ---------------------------------------------------------------------------------------
     def _load_named(self, named: Dict[str, torch.Tensor], prefix: str = "transformer.") -> int:
+        self._stale.add("transformer")
         params = dict(self.pipeline.bundle.transformer.named_parameters())
         n = 0
         with torch.no_grad():
@@ -265,6 +277,8 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
         """Install / refresh LoRA adapters from in-memory tensors keyed ``<module path>.<target>.lora_{A,B}.<adapter>.weight``."""
         lora_tensors = getattr(lora_tensors, "value", lora_tensors)  # payloads pushed through the controller travel in an opaque wrapper
         from unirl_b200.train import inject
+
+        self._stale.add("transformer")
 
         model = self.pipeline.bundle.transformer
         cfg = peft_config or {}
