@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--prompt-min", type=int, default=256)
     ap.add_argument("--prompt-max", type=int, default=1024)
     ap.add_argument("--micro-batch", type=int, default=4)
-    ap.add_argument("--rollout-tp", type=int, default=0, help="0 = 2 when gpus >= 2 else 1")
+    ap.add_argument("--rollout-tp", type=int, default=1, help="tensor-parallel degree of each rollout engine (1: one engine per GPU that aliases the trainer replica; 2: fused TP all-reduce + reshard weight sync)")
     ap.add_argument("--algorithm", default="grpo", choices=["grpo", "drpo"])
     ap.add_argument("--budget-s", type=float, default=float(os.environ.get("UNIRL_B200_BENCH_BUDGET_S", "780")),
                     help="wall-clock budget of the whole run in seconds (launcher start to exit); warm-up and timed steps are capped to fit, "
@@ -186,7 +186,7 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device")
     torch.cuda.set_device(local)
     require_ext()
-    tp = args.rollout_tp or (2 if world >= 2 else 1)
+    tp = max(1, args.rollout_tp)
     preset = {"qwen3-4b": "random:qwen3-4b", "tiny": "random:tiny"}[args.model]
     vocab = 151936 if args.model == "qwen3-4b" else 4096
     n_prompts = args.prompts_per_gpu * world

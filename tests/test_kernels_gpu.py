@@ -248,6 +248,35 @@ def test_sde_step_matches_strategy(name):
     _close(v.grad, vr.grad, 1e-4, 2e-2, "replay dv")
 
 
+def test_sde_step_with_guidance_combined_in_the_kernel():
+    """Two branches of a classifier-free-guidance pass go to the step kernel separately: same transition, log-prob and gradients as the
+    combination formed first (fp32 reference), in sampling and in differentiable replay."""
+    from unirl_b200.ops.sde_step import sde_step
+    from unirl_b200.sde import get_sigma_schedule, make_strategy
+
+    torch.manual_seed(11)
+    st = make_strategy("flow")
+    sig = get_sigma_schedule(10, 3.0).cuda()
+    g = 4.5
+    x = torch.randn(3, 16, 32, 32, device="cuda")
+    vc, vu = torch.randn_like(x).requires_grad_(), torch.randn_like(x).requires_grad_()
+    noise = torch.randn(x.shape, device="cuda")
+    prev, lp, mean = sde_step(st, vc, x, sig[2], sig[3], eta=0.7, noise=noise, noise_pred_uncond=vu, guidance_scale=g)
+    ref_v = (vu + g * (vc - vu)).detach()
+    rprev, rlp, rmean = st.denoise(ref_v, x, sig[2], sig[3], eta=0.7, noise=noise)
+    _close(prev, rprev, 1e-5, 1e-5, "prev")
+    _close(mean, rmean, 1e-5, 1e-5, "mean")
+    _close(lp, rlp, 1e-3, 1e-3, "logp")
+    _, lp2, m2 = sde_step(st, vc, x, sig[2], sig[3], eta=0.7, prev_sample=prev, noise_pred_uncond=vu, guidance_scale=g)
+    rc, ru = vc.detach().clone().requires_grad_(), vu.detach().clone().requires_grad_()
+    _, rlp2, rm2 = st.denoise(ru + g * (rc - ru), x, sig[2], sig[3], eta=0.7, prev_sample=prev)
+    _close(lp2, rlp2, 1e-3, 1e-3, "replay logp")
+    (lp2.sum() + 0.01 * m2.sum()).backward()
+    (rlp2.sum() + 0.01 * rm2.sum()).backward()
+    _close(vc.grad, rc.grad, 1e-4, 2e-2, "replay dv_cond")
+    _close(vu.grad, ru.grad, 1e-4, 2e-2, "replay dv_uncond")
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 512, 320), (1000, 6144, 2560), (257, 2560, 9728), (64, 384, 128)])
 def test_gemm_tcgen05(m, n, k):
     C = _C()

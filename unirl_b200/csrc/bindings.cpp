@@ -262,7 +262,16 @@ Tensor sum_squares(const Tensor& x) {
 }
 
 // ---------------------------------------------------------------------------------------------- SDE
-std::vector<Tensor> sde_sample_fwd(const Tensor& v, const Tensor& x, const Tensor& noise, const Tensor& ax, const Tensor& av, const Tensor& sd, int64_t mode) {
+// `v_uncond`: the unconditional branch of a classifier-free-guidance pass (same shape and dtype as `v`, which is then the conditional
+// branch); the guided velocity v_u + guidance (v - v_u) is formed inside the kernel.
+static const void* uncond_ptr(const c10::optional<Tensor>& vu, const Tensor& v) {
+  if (!vu.has_value() || !vu->defined()) return nullptr;
+  TORCH_CHECK(vu->is_cuda() && vu->is_contiguous() && vu->sizes() == v.sizes() && vu->scalar_type() == v.scalar_type() && vu->device() == v.device(),
+              "sde step: v_uncond must match noise_pred (shape, dtype, device) and be contiguous");
+  return vu->data_ptr();
+}
+std::vector<Tensor> sde_sample_fwd(const Tensor& v, const Tensor& x, const Tensor& noise, const Tensor& ax, const Tensor& av, const Tensor& sd, int64_t mode,
+                                   const c10::optional<Tensor>& v_uncond, double guidance) {
   chk(v, "noise_pred"); chk(x, "sample"); chk(noise, "noise");
   TORCH_CHECK(v.sizes() == x.sizes() && v.scalar_type() == x.scalar_type() && noise.scalar_type() == at::kFloat, "sde_sample: mismatch");
   c10::cuda::CUDAGuard g(v.device());
@@ -270,10 +279,11 @@ std::vector<Tensor> sde_sample_fwd(const Tensor& v, const Tensor& x, const Tenso
   auto f32 = v.options().dtype(torch::kFloat);
   auto prev = torch::empty(v.sizes(), f32), mean = torch::empty(v.sizes(), f32), logp = torch::zeros({B}, f32);
   ub::sde_sample_fwd(v.data_ptr(), x.data_ptr(), noise.data_ptr<float>(), ax.data_ptr<float>(), av.data_ptr<float>(), sd.data_ptr<float>(),
-                     prev.data_ptr<float>(), mean.data_ptr<float>(), logp.data_ptr<float>(), B, N, (int)mode, dt(v), stream());
+                     prev.data_ptr<float>(), mean.data_ptr<float>(), logp.data_ptr<float>(), B, N, (int)mode, dt(v), stream(), uncond_ptr(v_uncond, v), (float)guidance);
   return {prev, mean, logp};
 }
-std::vector<Tensor> sde_replay_fwd(const Tensor& v, const Tensor& x, const Tensor& prev, const Tensor& ax, const Tensor& av, const Tensor& sd, int64_t mode) {
+std::vector<Tensor> sde_replay_fwd(const Tensor& v, const Tensor& x, const Tensor& prev, const Tensor& ax, const Tensor& av, const Tensor& sd, int64_t mode,
+                                   const c10::optional<Tensor>& v_uncond, double guidance) {
   chk(v, "noise_pred"); chk(x, "sample"); chk(prev, "prev_sample");
   TORCH_CHECK(v.sizes() == x.sizes() && v.scalar_type() == x.scalar_type() && prev.scalar_type() == x.scalar_type(), "sde_replay: mismatch");
   c10::cuda::CUDAGuard g(v.device());
@@ -281,20 +291,24 @@ std::vector<Tensor> sde_replay_fwd(const Tensor& v, const Tensor& x, const Tenso
   auto f32 = v.options().dtype(torch::kFloat);
   auto mean = torch::empty(v.sizes(), f32), logp = torch::zeros({B}, f32);
   ub::sde_replay_fwd(v.data_ptr(), x.data_ptr(), prev.data_ptr(), ax.data_ptr<float>(), av.data_ptr<float>(), sd.data_ptr<float>(), mean.data_ptr<float>(),
-                     logp.data_ptr<float>(), B, N, (int)mode, dt(v), stream());
+                     logp.data_ptr<float>(), B, N, (int)mode, dt(v), stream(), uncond_ptr(v_uncond, v), (float)guidance);
   return {mean, logp};
 }
+// Returns dL/dv, or {dL/dv_cond, dL/dv_uncond} stacked as [2, ...] when `guided` (the forward formed v_u + guidance (v_c - v_u)).
 Tensor sde_replay_bwd(const c10::optional<Tensor>& g_mean, const Tensor& g_logp, const Tensor& mean, const Tensor& prev, const Tensor& av,
-                      const Tensor& sd, int64_t mode) {
+                      const Tensor& sd, int64_t mode, bool guided, double guidance) {
   chk(mean, "mean");
   c10::cuda::CUDAGuard g(mean.device());
   auto prev32 = prev.to(torch::kFloat).contiguous();
   const int64_t B = mean.size(0), N = mean.numel() / B;
-  auto gv = torch::empty_like(mean);
+  std::vector<int64_t> shape = mean.sizes().vec();
+  if (guided) shape.insert(shape.begin(), 2);
+  auto gv = torch::empty(shape, mean.options());
   Tensor gm;
   if (g_mean.has_value() && g_mean->defined()) gm = g_mean->to(torch::kFloat).contiguous();
   ub::sde_replay_bwd(gm.defined() ? gm.data_ptr<float>() : nullptr, g_logp.data_ptr<float>(), mean.data_ptr<float>(), prev32.data_ptr<float>(),
-                     av.data_ptr<float>(), sd.data_ptr<float>(), gv.data_ptr<float>(), B, N, (int)mode, stream());
+                     av.data_ptr<float>(), sd.data_ptr<float>(), gv.data_ptr<float>(), B, N, (int)mode, stream(),
+                     guided ? gv.data_ptr<float>() + mean.numel() : nullptr, (float)guidance);
   return gv;
 }
 
@@ -650,9 +664,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("rng_steps") = py::none());
   m.def("adamw_step", &adamw_step);
   m.def("sum_squares", &sum_squares);
-  m.def("sde_sample_fwd", &sde_sample_fwd);
-  m.def("sde_replay_fwd", &sde_replay_fwd);
-  m.def("sde_replay_bwd", &sde_replay_bwd);
+  m.def("sde_sample_fwd", &sde_sample_fwd, py::arg("v"), py::arg("x"), py::arg("noise"), py::arg("a_x"), py::arg("a_v"), py::arg("std"), py::arg("mode"),
+        py::arg("v_uncond") = py::none(), py::arg("guidance") = 1.0);
+  m.def("sde_replay_fwd", &sde_replay_fwd, py::arg("v"), py::arg("x"), py::arg("prev"), py::arg("a_x"), py::arg("a_v"), py::arg("std"), py::arg("mode"),
+        py::arg("v_uncond") = py::none(), py::arg("guidance") = 1.0);
+  m.def("sde_replay_bwd", &sde_replay_bwd, py::arg("g_mean"), py::arg("g_logp"), py::arg("mean"), py::arg("prev"), py::arg("a_v"), py::arg("std"), py::arg("mode"),
+        py::arg("guided") = false, py::arg("guidance") = 1.0);
   m.def("attn_varlen_fwd", &attn_varlen_fwd);
   m.def("attn_varlen_bwd", &attn_varlen_bwd);
   m.def("attn_diag", [](bool backward, bool reset) {  // phase timers of the attention kernels: empty unless built with -DUNIRL_B200_ATTN_DIAG

@@ -1109,9 +1109,9 @@ void sum_squares(const void* x, float* out, int64_t n, int dtype, cudaStream_t s
 constexpr float kHalfLog2Pi = 0.91893853320467274178f;
 
 template <typename T, bool kSample>
-__global__ void sde_fwd_kernel(const T* __restrict__ v, const T* __restrict__ x, const float* __restrict__ noise, const T* __restrict__ prev_in,
-                               const float* __restrict__ a_x, const float* __restrict__ a_v, const float* __restrict__ stdv, float* __restrict__ prev_out,
-                               float* __restrict__ mean, float* __restrict__ logp, int64_t N, int mode) {
+__global__ void sde_fwd_kernel(const T* __restrict__ v, const T* __restrict__ v_uncond, float guidance, const T* __restrict__ x, const float* __restrict__ noise,
+                               const T* __restrict__ prev_in, const float* __restrict__ a_x, const float* __restrict__ a_v, const float* __restrict__ stdv,
+                               float* __restrict__ prev_out, float* __restrict__ mean, float* __restrict__ logp, int64_t N, int mode) {
   __shared__ float scratch[32];
   const int b = blockIdx.y;
   const float ax = a_x[b], av = a_v[b], sd = stdv[b];
@@ -1119,7 +1119,12 @@ __global__ void sde_fwd_kernel(const T* __restrict__ v, const T* __restrict__ x,
   float acc = 0.f;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < N; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t idx = (int64_t)b * N + i;
-    const float mu = ax * to_f(x[idx]) + av * to_f(v[idx]);
+    float vv = to_f(v[idx]);
+    if (v_uncond) {  // classifier-free guidance: v = v_u + g (v_c - v_u), `v` is the conditional branch
+      const float vu = to_f(v_uncond[idx]);
+      vv = vu + guidance * (vv - vu);
+    }
+    const float mu = ax * to_f(x[idx]) + av * vv;
     float p;
     if (kSample) {
       p = to_f(from_f<T>(mu + sd * noise[idx]));
@@ -1136,14 +1141,20 @@ __global__ void sde_fwd_kernel(const T* __restrict__ v, const T* __restrict__ x,
 }
 __global__ void sde_replay_bwd_kernel(const float* __restrict__ g_mean, const float* __restrict__ g_logp, const float* __restrict__ mean,
                                       const float* __restrict__ prev, const float* __restrict__ a_v, const float* __restrict__ stdv,
-                                      float* __restrict__ g_v, int64_t N, int mode) {
+                                      float* __restrict__ g_v, float* __restrict__ g_v_uncond, float guidance, int64_t N, int mode) {
   const int b = blockIdx.y;
   const float av = a_v[b], sd = stdv[b];
   const float k = g_logp[b] / (float)N * (mode == 0 ? 1.f / (sd * sd) : 2.f);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < N; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t idx = (int64_t)b * N + i;
     const float gm = (g_mean ? g_mean[idx] : 0.f) + k * (prev[idx] - mean[idx]);
-    g_v[idx] = gm * av;
+    const float gv = gm * av;
+    if (g_v_uncond) {  // guided velocity v_u + g (v_c - v_u): d/dv_c = g, d/dv_u = 1 - g
+      g_v[idx] = guidance * gv;
+      g_v_uncond[idx] = (1.f - guidance) * gv;
+    } else {
+      g_v[idx] = gv;
+    }
   }
 }
 static dim3 sde_grid(int64_t B, int64_t N) {
@@ -1151,22 +1162,28 @@ static dim3 sde_grid(int64_t B, int64_t N) {
   if (bx > 296) bx = 296;
   return dim3((unsigned)bx, (unsigned)B);
 }
+// `v_uncond` (may be null) is the unconditional branch of a classifier-free-guidance pass; the guided velocity v_u + g (v - v_u) is formed in
+// the kernel and never stored.
 void sde_sample_fwd(const void* v, const void* x, const float* noise, const float* a_x, const float* a_v, const float* stdv, float* prev, float* mean,
-                    float* logp, int64_t B, int64_t N, int mode, int dtype, cudaStream_t s) {
+                    float* logp, int64_t B, int64_t N, int mode, int dtype, cudaStream_t s, const void* v_uncond, float guidance) {
   if (B * N == 0) return;
-  if (dtype == kBF16) sde_fwd_kernel<bf16, true><<<sde_grid(B, N), 256, 0, s>>>((const bf16*)v, (const bf16*)x, noise, nullptr, a_x, a_v, stdv, prev, mean, logp, N, mode);
-  else sde_fwd_kernel<float, true><<<sde_grid(B, N), 256, 0, s>>>((const float*)v, (const float*)x, noise, nullptr, a_x, a_v, stdv, prev, mean, logp, N, mode);
+  if (dtype == kBF16)
+    sde_fwd_kernel<bf16, true><<<sde_grid(B, N), 256, 0, s>>>((const bf16*)v, (const bf16*)v_uncond, guidance, (const bf16*)x, noise, nullptr, a_x, a_v, stdv, prev, mean, logp, N, mode);
+  else
+    sde_fwd_kernel<float, true><<<sde_grid(B, N), 256, 0, s>>>((const float*)v, (const float*)v_uncond, guidance, (const float*)x, noise, nullptr, a_x, a_v, stdv, prev, mean, logp, N, mode);
 }
 void sde_replay_fwd(const void* v, const void* x, const void* prev, const float* a_x, const float* a_v, const float* stdv, float* mean, float* logp,
-                    int64_t B, int64_t N, int mode, int dtype, cudaStream_t s) {
+                    int64_t B, int64_t N, int mode, int dtype, cudaStream_t s, const void* v_uncond, float guidance) {
   if (B * N == 0) return;
-  if (dtype == kBF16) sde_fwd_kernel<bf16, false><<<sde_grid(B, N), 256, 0, s>>>((const bf16*)v, (const bf16*)x, nullptr, (const bf16*)prev, a_x, a_v, stdv, nullptr, mean, logp, N, mode);
-  else sde_fwd_kernel<float, false><<<sde_grid(B, N), 256, 0, s>>>((const float*)v, (const float*)x, nullptr, (const float*)prev, a_x, a_v, stdv, nullptr, mean, logp, N, mode);
+  if (dtype == kBF16)
+    sde_fwd_kernel<bf16, false><<<sde_grid(B, N), 256, 0, s>>>((const bf16*)v, (const bf16*)v_uncond, guidance, (const bf16*)x, nullptr, (const bf16*)prev, a_x, a_v, stdv, nullptr, mean, logp, N, mode);
+  else
+    sde_fwd_kernel<float, false><<<sde_grid(B, N), 256, 0, s>>>((const float*)v, (const float*)v_uncond, guidance, (const float*)x, nullptr, (const float*)prev, a_x, a_v, stdv, nullptr, mean, logp, N, mode);
 }
 void sde_replay_bwd(const float* g_mean, const float* g_logp, const float* mean, const float* prev, const float* a_v, const float* stdv, float* g_v,
-                    int64_t B, int64_t N, int mode, cudaStream_t s) {
+                    int64_t B, int64_t N, int mode, cudaStream_t s, float* g_v_uncond, float guidance) {
   if (B * N == 0) return;
-  sde_replay_bwd_kernel<<<sde_grid(B, N), 256, 0, s>>>(g_mean, g_logp, mean, prev, a_v, stdv, g_v, N, mode);
+  sde_replay_bwd_kernel<<<sde_grid(B, N), 256, 0, s>>>(g_mean, g_logp, mean, prev, a_v, stdv, g_v, g_v_uncond, guidance, N, mode);
 }
 
 }  // namespace ub

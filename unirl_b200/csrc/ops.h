@@ -75,11 +75,11 @@ void adamw_step(float* master, const void* grad, int grad_dtype, float* m, float
                 float b2, float eps, float wd, int64_t step, float grad_scale, const float* grad_scale_tensor, float ema_decay, cudaStream_t s);
 void sum_squares(const void* x, float* out, int64_t n, int dtype, cudaStream_t s);
 void sde_sample_fwd(const void* v, const void* x, const float* noise, const float* a_x, const float* a_v, const float* stdv, float* prev, float* mean,
-                    float* logp, int64_t B, int64_t N, int mode, int dtype, cudaStream_t s);
+                    float* logp, int64_t B, int64_t N, int mode, int dtype, cudaStream_t s, const void* v_uncond = nullptr, float guidance = 1.f);
 void sde_replay_fwd(const void* v, const void* x, const void* prev, const float* a_x, const float* a_v, const float* stdv, float* mean, float* logp,
-                    int64_t B, int64_t N, int mode, int dtype, cudaStream_t s);
+                    int64_t B, int64_t N, int mode, int dtype, cudaStream_t s, const void* v_uncond = nullptr, float guidance = 1.f);
 void sde_replay_bwd(const float* g_mean, const float* g_logp, const float* mean, const float* prev, const float* a_v, const float* stdv, float* g_v,
-                    int64_t B, int64_t N, int mode, cudaStream_t s);
+                    int64_t B, int64_t N, int mode, cudaStream_t s, float* g_v_uncond = nullptr, float guidance = 1.f);
 
 // ---- gemm_tcgen05.cu -------------------------------------------------------------------------------------
 int gemm_bf16_general(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate,

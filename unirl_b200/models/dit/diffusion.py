@@ -69,6 +69,26 @@ class DiTDiffusionStage:
     # ---- one velocity evaluation ---------------------------------------------------------------------------
     def _velocity(self, x: torch.Tensor, sigma: torch.Tensor, cond: DiTConditions, p: DiTDiffusionParams) -> torch.Tensor:
         """Guided velocity at ``(x, σ)``; ``σ`` is ``[B]`` in ``[0, 1]`` (the transformer sees ``1000·σ``)."""
+        vc, vu = self._branches(x, sigma, cond, p)
+        return vc if vu is None else self._guided(vu, vc, p)
+
+    @property
+    def _plain_guidance(self) -> bool:
+        """True when the family uses the textbook combination ``v_u + g·(v_c − v_u)``, which the SDE-step kernel can form itself."""
+        return type(self)._guided is DiTDiffusionStage._guided
+
+    def _step_inputs(self, x: torch.Tensor, sigma: torch.Tensor, cond: DiTConditions, p: DiTDiffusionParams):
+        """``(noise_pred, keyword arguments)`` for :func:`sde_step`: with plain guidance the two branches go to the kernel separately."""
+        vc, vu = self._branches(x, sigma, cond, p)
+        if vu is None:
+            return vc, {}
+        if self._plain_guidance:
+            return vc, {"noise_pred_uncond": vu, "guidance_scale": float(p.guidance_scale)}
+        return self._guided(vu, vc, p), {}
+
+    def _branches(self, x: torch.Tensor, sigma: torch.Tensor, cond: DiTConditions, p: DiTDiffusionParams) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """One transformer evaluation at ``(x, σ)``: ``(v_cond, v_uncond)`` from one batched pass under classifier-free guidance,
+        ``(v, None)`` otherwise."""
         model = self.bundle.transformer
         t = sigma.to(x.device).float().reshape(-1).expand(x.shape[0]) * 1000.0
         txt = cond.text
@@ -81,7 +101,7 @@ class DiTDiffusionStage:
             guidance = torch.full((x.shape[0],), float(g) * 1000.0, device=x.device)
         use_cfg = p.true_cfg and p.guidance_scale > 1.0 and cond.negative_text is not None
         if not use_cfg:
-            return model(inp, t, txt.embeds, txt.pooled, txt.attn_mask, guidance).float()
+            return model(inp, t, txt.embeds, txt.pooled, txt.attn_mask, guidance).float(), None
         neg = cond.negative_text
         width = max(txt.embeds.shape[1], neg.embeds.shape[1])
         pad = lambda e: torch.nn.functional.pad(e, (0, 0, 0, width - e.shape[1]))  # noqa: E731
@@ -91,7 +111,7 @@ class DiTDiffusionStage:
         mask = None if txt.attn_mask is None or neg.attn_mask is None else torch.cat([padm(neg.attn_mask, neg.embeds), padm(txt.attn_mask, txt.embeds)])
         v = model(torch.cat([inp, inp]), torch.cat([t, t]), emb, pooled, mask, None if guidance is None else torch.cat([guidance, guidance])).float()
         vu, vc = v.chunk(2)
-        return self._guided(vu, vc, p)
+        return vc, vu
 
     def _guided(self, v_uncond: torch.Tensor, v_cond: torch.Tensor, p: DiTDiffusionParams) -> torch.Tensor:
         """Classifier-free guidance combination (families override, e.g. norm-corrected CFG)."""
@@ -117,13 +137,14 @@ class DiTDiffusionStage:
         logps, means = [], []
         cond = conditions.to_device(dev) if hasattr(conditions, "to_device") else conditions
         for i in range(steps):
+            fused = i in sde and tdt == torch.float32
             with torch.autocast(dev.type, dtype=self.autocast_dtype, enabled=self.autocast_dtype != torch.float32 and dev.type == "cuda"):
-                v = self._velocity(x, sig[i], cond, params)
+                v, cfg_kw = self._step_inputs(x, sig[i], cond, params) if fused else (self._velocity(x, sig[i], cond, params), {})
             if i in sde:
                 noise = torch.stack([torch.randn(x.shape[1:], dtype=torch.float32, generator=torch.Generator().manual_seed(step_noise_seed(seed, sid, i)))
                                      for sid in ids]).to(dev)
-                if tdt == torch.float32:
-                    x, logp, mean = sde_step(strategy, v, x, sig[i], sig[i + 1], eta=params.eta, sigma_max=params.sigma_max, step_index=i, noise=noise)
+                if fused:  # the guidance combination, the transition and its log-prob in one pass over the latent
+                    x, logp, mean = sde_step(strategy, v, x, sig[i], sig[i + 1], eta=params.eta, sigma_max=params.sigma_max, step_index=i, noise=noise, **cfg_kw)
                 else:  # the stored sample is rounded to the trajectory dtype BEFORE its log-prob is taken, so replay sees the same value
                     x, logp, mean = strategy.denoise(v, x.to(tdt), sig[i], sig[i + 1], eta=params.eta, sigma_max=params.sigma_max, step_index=i, noise=noise)
                 logps.append(logp.float())
@@ -151,8 +172,8 @@ class DiTDiffusionStage:
         for i in steps:
             x, nxt = segment.latents_at(i).to(dev).float(), segment.latents_at(i + 1).to(dev).float()
             with torch.autocast(dev.type, dtype=self.autocast_dtype, enabled=self.autocast_dtype != torch.float32 and dev.type == "cuda"):
-                v = self._velocity(x, sig[i], cond, params)
-            _, logp, mean = sde_step(strategy, v, x, sig[i], sig[i + 1], eta=params.eta, prev_sample=nxt, sigma_max=params.sigma_max, step_index=i)
+                v, cfg_kw = self._step_inputs(x, sig[i], cond, params)
+            _, logp, mean = sde_step(strategy, v, x, sig[i], sig[i + 1], eta=params.eta, prev_sample=nxt, sigma_max=params.sigma_max, step_index=i, **cfg_kw)
             logps.append(logp.float())
             means.append(mean.float())
         return ReplayResult(log_probs=torch.stack(logps, 1), prev_sample_means=torch.stack(means, 1))

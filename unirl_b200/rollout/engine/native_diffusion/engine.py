@@ -51,11 +51,11 @@ class NativeDiffusionEngineConfig:
 
 
 class GraphedVelocity:
-    """Replays the guided-velocity evaluation of a stage from a CUDA graph once shapes are known to be static."""
+    """Replays the transformer evaluation of a stage (both guidance branches) from a CUDA graph once shapes are known to be static."""
 
     def __init__(self, stage: Any):
         self.stage = stage
-        self._orig = stage._velocity
+        self._orig = stage._branches
         self._key: Any = None
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._x = self._sigma = self._out = None
@@ -63,10 +63,10 @@ class GraphedVelocity:
         self._calls = 0
 
     def install(self) -> None:
-        self.stage._velocity = self.__call__
+        self.stage._branches = self.__call__
 
     def remove(self) -> None:
-        self.stage._velocity = self._orig
+        self.stage._branches = self._orig
         self.reset()
 
     def reset(self) -> None:
@@ -74,7 +74,7 @@ class GraphedVelocity:
         self._key = self._x = self._sigma = self._out = self._cond = self._p = None
         self._calls = 0
 
-    def __call__(self, x: torch.Tensor, sigma: torch.Tensor, cond: Any, p: Any) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, sigma: torch.Tensor, cond: Any, p: Any):
         if not x.is_cuda or torch.is_grad_enabled():
             return self._orig(x, sigma, cond, p)
         key = (tuple(x.shape), x.dtype, id(cond), float(p.guidance_scale))
@@ -95,7 +95,7 @@ class GraphedVelocity:
         self._x.copy_(x)
         self._sigma.copy_(sigma.reshape(1))
         self._graph.replay()
-        return self._out.clone()
+        return tuple(None if o is None else o.clone() for o in self._out)
 
 
 class NativeDiffusionRolloutEngine(BaseRolloutEngine):
