@@ -120,3 +120,53 @@ def test_scorers_load_a_published_layout_checkpoint_and_follow_the_published_for
     assert big.shape == (2,) and torch.isfinite(big).all()
     with pytest.raises(FileNotFoundError, match="never downloaded"):
         build_scorer("clip", model_id="openai/clip-vit-large-patch14", device="cpu")
+
+
+def test_service_config_validation_and_gpu_ledger():
+    from unirl_b200_reward_service.config import RewardModelCfg, ServiceCfg, from_dict
+    from unirl_b200_reward_service.workers import WorkerPool
+
+    with pytest.raises(ValueError, match="num_replicas"):
+        RewardModelCfg(name="clip", num_replicas=0)
+    with pytest.raises(ValueError, match="num_gpus"):
+        RewardModelCfg(name="clip", num_gpus=-1)
+    with pytest.raises(ValueError, match="duplicate"):
+        from_dict({"rewards": [{"name": "clip"}, {"name": "clip"}]})
+    cfg = from_dict({"isolation": "thread", "gpu_ids": [4, 5, 6], "rewards": [{"name": "ocr", "num_replicas": 2, "num_gpus": 1}, {"name": "geneval"}]})
+    assert cfg.gpus_needed() == 2
+    pool = WorkerPool(cfg)
+    try:
+        assert pool.owned["ocr"] == [[4], [5]] and pool.owned["geneval"] == [[]], "whole GPUs, each owned by one replica"
+        with pytest.raises(ValueError, match="GPUs"):
+            pool.add(RewardModelCfg(name="geneval2", num_gpus=2))  # one GPU left
+        with pytest.raises(KeyError):
+            pool.get("no-such-reward")
+    finally:
+        pool.close()
+    with pytest.raises(ValueError, match="need 4 GPUs"):
+        WorkerPool(ServiceCfg(rewards=[RewardModelCfg(name="ocr", num_replicas=2, num_gpus=2)], gpu_ids=[0, 1]))
+
+
+@pytest.mark.parametrize("isolation", ["thread", "process"])
+def test_request_form_routes_each_request_to_its_rewards_and_isolates_failures(isolation):
+    from unirl_b200_reward_service.app import RewardGateway
+    from unirl_b200_reward_service.config import from_dict
+
+    cfg = from_dict({"isolation": isolation, "gpu_ids": [],
+                     "rewards": [{"name": "ocr", "num_replicas": 2}, {"name": "sharp", "scorer": "clip", "kwargs": {"seed": 3, "device": "cpu"}}]})
+    gw = RewardGateway(config=cfg)
+    try:
+        png = encode_image(torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(0)))
+        reqs = [{"prompt": 'a sign that says "hello"', "image_png_b64": png, "rewards": ["ocr", "sharp"], "metadata": {"ocr_text": "hello"}},
+                {"prompt": 'a sign that says "world"', "image_png_b64": png, "rewards": ["ocr"], "metadata": {"ocr_text": "word"}},
+                {"prompt": "a cat", "image_png_b64": png, "rewards": ["sharp", "no-such-reward"]}]
+        out = gw.score({"requests": reqs})["results"]
+        assert out[0]["rewards"]["ocr"] == 1.0 and set(out[0]["rewards"]) == {"ocr", "sharp"} and not out[0]["errors"]
+        assert 0.0 < out[1]["rewards"]["ocr"] < 1.0 and set(out[1]["rewards"]) == {"ocr"}
+        assert "sharp" in out[2]["rewards"] and "no-such-reward" in out[2]["errors"] and "no-such-reward" not in out[2]["rewards"]
+        again = gw.score({"requests": reqs[:1]})["results"][0]["rewards"]
+        assert again["ocr"] == out[0]["rewards"]["ocr"] and abs(again["sharp"] - out[0]["rewards"]["sharp"]) < 1e-5, "replicas of a group agree"
+        st = gw.stats()
+        assert st["ocr"]["replicas"] == 2 and st["ocr"]["calls"] == 2 and st["sharp"]["errors"] == 0
+    finally:
+        gw.close()
