@@ -248,6 +248,53 @@ def test_sde_step_matches_strategy(name):
     _close(v.grad, vr.grad, 1e-4, 2e-2, "replay dv")
 
 
+@pytest.mark.parametrize("dtype,shape", [(torch.float32, (2, 70, 96)), (torch.bfloat16, (3, 333, 1536))])
+def test_layernorm_modulate_backward_kernel(dtype, shape):
+    """adaLN with gradients: dx, dshift, dscale of the kernel pair against autograd through the fp32 PyTorch statement."""
+    from unirl_b200.ops.norm import layernorm_modulate, layernorm_modulate_reference
+
+    torch.manual_seed(13)
+    b, l, d = shape
+    x = torch.randn(b, l, d, device="cuda").to(dtype).requires_grad_()
+    sh = (torch.randn(b, d, device="cuda") * 0.3).to(dtype).requires_grad_()
+    sc = (torch.randn(b, d, device="cuda") * 0.3).to(dtype).requires_grad_()
+    xr, shr, scr = (t.detach().float().requires_grad_() for t in (x, sh, sc))
+    y = layernorm_modulate(x, sh, sc, 1e-6)
+    yr = layernorm_modulate_reference(xr, shr, scr, 1e-6)
+    g = torch.randn_like(yr)
+    y.backward(g.to(dtype))
+    yr.backward(g)
+    tol = 3e-2 if dtype == torch.bfloat16 else 2e-4
+    _close(y, yr, tol, tol, "adaLN forward")
+    _close(x.grad, xr.grad, tol, tol, "dx")
+    _close(sh.grad, shr.grad, tol * (l ** 0.5), tol, "dshift (a sum over the tokens)")
+    _close(sc.grad, scr.grad, tol * (l ** 0.5), tol, "dscale")
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_table_driven_rotary_kernel(interleaved, dtype):
+    """Rotation by per-token tables shared over the batch: forward and gradient against the fp32 PyTorch statement, both pairings."""
+    from unirl_b200.ops.rope import rope_table, rope_table_reference
+
+    torch.manual_seed(12)
+    b, l, h, d = 2, 37, 3, 64
+    ang = torch.rand(l, d // 2, device="cuda") * 6.28
+    cos, sin = ang.cos(), ang.sin()
+    x = torch.randn(b, l, h, d, device="cuda").to(dtype).requires_grad_()
+    xr = x.detach().float().requires_grad_()
+    y, yr = rope_table(x, cos, sin, interleaved), rope_table_reference(xr, cos, sin, interleaved)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(y, yr, tol, tol, "rotated")
+    g = torch.randn_like(yr)
+    y.backward(g.to(dtype))
+    yr.backward(g)
+    _close(x.grad, xr.grad, tol, tol, "gradient (the rotation by the opposite angle)")
+    # three leading dimensions collapse the same way as two
+    x3 = torch.randn(l, h, d, device="cuda").to(dtype)
+    _close(rope_table(x3, cos, sin, interleaved), rope_table_reference(x3.float(), cos, sin, interleaved), tol, tol, "no batch dimension")
+
+
 def test_sde_step_with_guidance_combined_in_the_kernel():
     """Two branches of a classifier-free-guidance pass go to the step kernel separately: same transition, log-prob and gradients as the
     combination formed first (fp32 reference), in sampling and in differentiable replay."""

@@ -105,6 +105,34 @@ std::vector<Tensor> qk_norm_rope_fwd(const Tensor& qkv, const c10::optional<Tens
                        rstd.data_ptr<float>(), T, (int)Hq, (int)Hkv, (int)D, (float)eps, dt(qkv), stream());
   return {q, k, v, rstd};
 }
+std::vector<Tensor> layernorm_modulate_bwd(const Tensor& dy, const Tensor& x, const Tensor& scale, double eps) {
+  chk(dy, "dy"); chk(x, "x"); chk(scale, "scale");
+  TORCH_CHECK(x.dim() == 3 && dy.sizes() == x.sizes() && scale.dim() == 2 && scale.size(0) == x.size(0) && scale.size(1) == x.size(2), "layernorm_modulate_bwd: shapes");
+  TORCH_CHECK(dy.scalar_type() == x.scalar_type() && scale.scalar_type() == x.scalar_type() && dy.device() == x.device() && scale.device() == x.device(),
+              "layernorm_modulate_bwd: dtypes / devices");
+  c10::cuda::CUDAGuard g(x.device());
+  auto dx = torch::empty_like(x);
+  auto f32 = x.options().dtype(torch::kFloat);
+  auto dshift = torch::zeros({x.size(0), x.size(2)}, f32), dscale = torch::zeros({x.size(0), x.size(2)}, f32);
+  const bool ok = ub::layernorm_modulate_bwd(dy.data_ptr(), x.data_ptr(), scale.data_ptr(), dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(),
+                                             x.size(0), (int)x.size(1), (int)x.size(2), (float)eps, dt(x), stream());
+  TORCH_CHECK(ok, "layernorm_modulate_bwd: rows of ", x.size(2), " elements are too wide for the kernel");
+  return {dx, dshift, dscale};
+}
+// Rotary embedding from per-token tables: x [..., L, H, D] (any leading batch dimensions), cos / sin fp32 [L, D / 2].
+Tensor rope_table(const Tensor& x, const Tensor& cos_t, const Tensor& sin_t, bool interleaved, bool backward) {
+  chk(x, "x"); chk(cos_t, "cos"); chk(sin_t, "sin");
+  TORCH_CHECK(x.dim() >= 3 && cos_t.dim() == 2 && cos_t.sizes() == sin_t.sizes() && cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat,
+              "rope_table: x [..., L, H, D], cos / sin fp32 [L, D / 2]");
+  const int64_t D = x.size(-1), H = x.size(-2), L = x.size(-3);
+  TORCH_CHECK(D % 2 == 0 && cos_t.size(0) == L && cos_t.size(1) == D / 2, "rope_table: table shape [", cos_t.size(0), ", ", cos_t.size(1), "] does not fit x");
+  TORCH_CHECK(cos_t.device() == x.device() && sin_t.device() == x.device(), "rope_table: tensors on different devices");
+  c10::cuda::CUDAGuard g(x.device());
+  auto y = torch::empty_like(x);
+  ub::rope_table(x.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), y.data_ptr(), x.numel() / (H * D), (int)H, (int)D, L, interleaved ? 1 : 0,
+                 backward ? -1.f : 1.f, dt(x), stream());
+  return y;
+}
 // Inference variant: QK-norm + RoPE + KV-cache write in one launch.  `dense_kv` keeps the [T, Hkv, D] k / v outputs (prefill needs
 // them for the packed attention); decode reads the cache only and skips them.
 std::vector<Tensor> qk_norm_rope_cache_fwd(const Tensor& qkv, const Tensor& qw, const Tensor& kw, const Tensor& pos, Tensor& kc, Tensor& vc, const Tensor& slots,
@@ -648,9 +676,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("layernorm_modulate_fwd", &layernorm_modulate_fwd);
+  m.def("layernorm_modulate_bwd", &layernorm_modulate_bwd);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("qk_norm_rope_cache_fwd", &qk_norm_rope_cache_fwd);
+  m.def("rope_table", &rope_table);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("kv_cache_write", &kv_cache_write);

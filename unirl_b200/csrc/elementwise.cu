@@ -76,6 +76,56 @@ __global__ void layernorm_modulate_kernel(const T* __restrict__ x, const T* __re
 }
 
 
+// Backward of y = LayerNorm(x)·(1 + scale[b]) + shift[b] (no affine parameters): with x̂ = (x − μ)·r and g = dy·(1 + scale),
+//   dx = r·(g − mean(g) − x̂·mean(g·x̂)),   dshift[b] = Σ_l dy,   dscale[b] = Σ_l dy·x̂.
+// One CTA owns up to `rows_per_cta` consecutive tokens of ONE batch element (grid.y = batch); a warp takes every 8th of them.  The
+// statistics are recomputed from x (nothing was saved in the forward).  The per-column sums of the CTA's rows are collected in shared
+// memory and added to the fp32 outputs once per CTA.
+template <typename T>
+__global__ void layernorm_modulate_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ scale, T* __restrict__ dx,
+                                              float* __restrict__ dshift, float* __restrict__ dscale, int L, int D, float eps, int rows_per_cta) {
+  extern __shared__ float ln_acc[];  // [2][D]
+  const int b = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) ln_acc[c] = 0.f;
+  __syncthreads();
+  const int l0 = blockIdx.x * rows_per_cta, l1 = min(L, l0 + rows_per_cta);
+  const T* sc = scale + (int64_t)b * D;
+  for (int l = l0 + warp; l < l1; l += nwarp) {
+    const int64_t row = ((int64_t)b * L + l) * D;
+    float s = 0.f;
+    for (int c = lane; c < D; c += 32) s += to_f(x[row + c]);
+    const float mu = warp_sum(s) / D;
+    float v = 0.f;
+    for (int c = lane; c < D; c += 32) {
+      const float d = to_f(x[row + c]) - mu;
+      v += d * d;
+    }
+    const float r = rsqrtf(warp_sum(v) / D + eps);
+    float sg = 0.f, sgx = 0.f;
+    for (int c = lane; c < D; c += 32) {
+      const float xh = (to_f(x[row + c]) - mu) * r;
+      const float g = to_f(dy[row + c]) * (1.f + to_f(sc[c]));
+      sg += g;
+      sgx += g * xh;
+    }
+    const float mg = warp_sum(sg) / D, mgx = warp_sum(sgx) / D;
+    for (int c = lane; c < D; c += 32) {
+      const float xh = (to_f(x[row + c]) - mu) * r;
+      const float d = to_f(dy[row + c]);
+      const float g = d * (1.f + to_f(sc[c]));
+      dx[row + c] = from_f<T>(r * (g - mg - xh * mgx));
+      atomicAdd(&ln_acc[c], d);
+      atomicAdd(&ln_acc[D + c], d * xh);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    atomicAdd(dshift + (int64_t)b * D + c, ln_acc[c]);
+    atomicAdd(dscale + (int64_t)b * D + c, ln_acc[D + c]);
+  }
+}
+
 // ===================================================================================== vectorised bf16 fast paths
 // Rows are processed with 16-byte accesses and held in registers between the reduction and the write, so every
 // operand crosses HBM exactly once.  Used when the dtype is bf16 and the row length is a multiple of 8.
@@ -588,6 +638,21 @@ void layernorm_modulate_fwd(const void* x, const void* shift, const void* scale,
     layernorm_modulate_kernel<float><<<(unsigned)(B * L), norm_threads(D), 0, s>>>((const float*)x, (const float*)shift, (const float*)scale, (float*)y, L, D, eps);
 }
 
+// dshift / dscale: fp32 [B, D], zero-initialised by the caller.  Returns false when the row is too wide for the shared-memory sums.
+bool layernorm_modulate_bwd(const void* dy, const void* x, const void* scale, void* dx, float* dshift, float* dscale, int64_t B, int L, int D, float eps,
+                            int dtype, cudaStream_t s) {
+  if (B * L == 0) return true;
+  const size_t smem = 2 * static_cast<size_t>(D) * sizeof(float);
+  if (smem > 48 * 1024) return false;
+  const int rows_per_cta = 32;
+  const dim3 grid((unsigned)((L + rows_per_cta - 1) / rows_per_cta), (unsigned)B);
+  if (dtype == kBF16)
+    layernorm_modulate_bwd_kernel<bf16><<<grid, 256, smem, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)scale, (bf16*)dx, dshift, dscale, L, D, eps, rows_per_cta);
+  else
+    layernorm_modulate_bwd_kernel<float><<<grid, 256, smem, s>>>((const float*)dy, (const float*)x, (const float*)scale, (float*)dx, dshift, dscale, L, D, eps, rows_per_cta);
+  return true;
+}
+
 // ===================================================================================== QK-norm + RoPE
 // One warp per (token, head).  Heads [0, Hq) are q, [Hq, Hq+Hkv) are k (normalised + rotated), the
 // remaining Hkv heads are v (copied).  inv_freq[D/2] comes from the host so that angles match the
@@ -730,6 +795,46 @@ int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, cons
     launch_kernel(qk_norm_rope_fwd_vec_kernel<256>, g, dim3(128), 0, s, pdl_enabled() && T <= kPdlMaxRows, (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, pos,
                   inv_freq, (bf16*)q, (bf16*)k, (bf16*)v, nullptr, T, Hq, Hkv, eps, (bf16*)kc, (bf16*)vc, slots, page_size, chunks);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+// ===================================================================================== table-driven rotary embedding
+// y = rotate(x) for x [rows, H, D] by per-token angles given as tables cos / sin [L, D / 2]: row r of x uses table row r % L (a batch of
+// B sequences of L tokens shares one table).  Two pairings: interleaved (elements 2i, 2i+1 rotate together: the axial 3-D embedding
+// of the diffusion transformers) and half-split (i, i + D/2: the multimodal 3-axis embedding of the vision-language decoder, whose
+// per-frequency axis choice is baked into the tables).  `sign` = -1 rotates backwards, which is the gradient of the forward rotation.
+// One warp per (row, head); fp32 arithmetic.
+template <typename T, bool kInterleaved>
+__global__ void rope_table_kernel(const T* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn, T* __restrict__ y, int64_t rows, int H, int D,
+                                  int64_t L, float sign) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp >= rows * H) return;
+  const int64_t r = warp / H;
+  const int half = D >> 1;
+  const float* c = cs + (r % L) * half;
+  const float* s = sn + (r % L) * half;
+  const T* src = x + warp * D;
+  T* dst = y + warp * D;
+  for (int i = lane; i < half; i += 32) {
+    const int ia = kInterleaved ? 2 * i : i, ib = kInterleaved ? 2 * i + 1 : i + half;
+    const float a = to_f(src[ia]), b = to_f(src[ib]);
+    const float cc = c[i], ss = s[i] * sign;
+    dst[ia] = from_f<T>(a * cc - b * ss);
+    dst[ib] = from_f<T>(a * ss + b * cc);
+  }
+}
+void rope_table(const void* x, const float* cos_t, const float* sin_t, void* y, int64_t rows, int H, int D, int64_t L, int interleaved, float sign, int dtype,
+                cudaStream_t s) {
+  const int64_t warps = rows * H;
+  if (warps == 0) return;
+  const unsigned grid = (unsigned)((warps + 7) / 8);
+  if (dtype == kBF16) {
+    if (interleaved) rope_table_kernel<bf16, true><<<grid, 256, 0, s>>>((const bf16*)x, cos_t, sin_t, (bf16*)y, rows, H, D, L, sign);
+    else rope_table_kernel<bf16, false><<<grid, 256, 0, s>>>((const bf16*)x, cos_t, sin_t, (bf16*)y, rows, H, D, L, sign);
+  } else {
+    if (interleaved) rope_table_kernel<float, true><<<grid, 256, 0, s>>>((const float*)x, cos_t, sin_t, (float*)y, rows, H, D, L, sign);
+    else rope_table_kernel<float, false><<<grid, 256, 0, s>>>((const float*)x, cos_t, sin_t, (float*)y, rows, H, D, L, sign);
+  }
 }
 
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, float* rstd,

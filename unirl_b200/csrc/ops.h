@@ -48,6 +48,8 @@ void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t R, 
 void add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, int64_t R, int D, float eps, int dtype, cudaStream_t s);
 void rmsnorm_bwd(const void* gy, const void* x, const void* w, const float* rstd, void* gx, float* gw, int64_t R, int D, int dtype, cudaStream_t s);
 void layernorm_modulate_fwd(const void* x, const void* shift, const void* scale, void* y, int64_t B, int L, int D, float eps, int dtype, cudaStream_t s);
+bool layernorm_modulate_bwd(const void* dy, const void* x, const void* scale, void* dx, float* dshift, float* dscale, int64_t B, int L, int D, float eps,
+                            int dtype, cudaStream_t s);  // dshift / dscale fp32 [B, D], zeroed by the caller; false: D too wide (> 6144)
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, float* rstd,
                       int64_t T, int Hq, int Hkv, int D, float eps, int dtype, cudaStream_t s);
 void qk_norm_rope_bwd(const void* gq, const void* gk, const void* gv, const void* qkv, const void* qw, const void* kw, const int* pos,
@@ -55,6 +57,10 @@ void qk_norm_rope_bwd(const void* gq, const void* gk, const void* gv, const void
                       cudaStream_t s);
 int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq, void* q, void* k, void* v, void* kc, void* vc,
                            const int64_t* slots, int64_t T, int Hq, int Hkv, int D, int page_size, float eps, cudaStream_t s);
+// y = rotate(x [rows, H, D]) by per-token tables cos / sin [L, D / 2] (table row = row % L); interleaved: pairs (2i, 2i+1), else (i, i + D/2);
+// sign -1 = the backward rotation.
+void rope_table(const void* x, const float* cos_t, const float* sin_t, void* y, int64_t rows, int H, int D, int64_t L, int interleaved, float sign, int dtype,
+                cudaStream_t s);
 void swiglu_fwd(const void* gu, void* out, int64_t rows, int I, int dtype, cudaStream_t s);
 void swiglu_bwd(const void* gy, const void* gu, void* g_gu, int64_t rows, int I, int dtype, cudaStream_t s);
 void kv_cache_write(const void* k, const void* v, void* kc, void* vc, const int64_t* slots, int64_t T, int Hkv, int D, int page_size, int dtype,

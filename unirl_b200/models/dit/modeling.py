@@ -134,7 +134,11 @@ def axial_rope(cfg: DiTConfig, grid: Tuple[int, int, int], device: Any, text_len
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """Interleaved-pair rotation of ``x [B, L, H, D]`` by per-token angles ``[L, D/2]``."""
+    """Interleaved-pair rotation of ``x [B, L, H, D]`` by per-token angles ``[L, D/2]`` (one kernel each way on CUDA)."""
+    if x.is_cuda:
+        from unirl_b200.ops.rope import rope_table
+
+        return rope_table(x, cos, sin, True)
     xf = x.float().unflatten(-1, (-1, 2))
     a, b = xf[..., 0], xf[..., 1]
     c, s = cos[None, :, None, :], sin[None, :, None, :]

@@ -116,19 +116,21 @@ class UnifiedDiffusionStage(DiTDiffusionStage):
     def __init__(self, bundle: Any, default_strategy: str = "flow", autocast_precision: str = "bf16"):
         super().__init__(bundle, default_strategy, autocast_precision)
 
-    def _velocity(self, x: torch.Tensor, sigma: torch.Tensor, cond: UnifiedConditions, p: DiTDiffusionParams) -> torch.Tensor:
+    def _branches(self, x: torch.Tensor, sigma: torch.Tensor, cond: UnifiedConditions, p: DiTDiffusionParams):
+        """``(v_cond, v_uncond | None)`` of one transformer evaluation in image mode (the base class combines them, or hands both to the
+        SDE-step kernel)."""
         m = self.bundle.transformer
         t = sigma.to(x.device).float().reshape(-1).expand(x.shape[0]) * 1000.0
         ids, mask = cond.prompt.input_ids.to(x.device), cond.prompt.attention_mask.to(x.device)
         if not (p.guidance_scale > 1.0 and cond.negative_prompt is not None):
-            return m.forward_image(ids, mask, x, t).float()
+            return m.forward_image(ids, mask, x, t).float(), None
         nids, nmask = cond.negative_prompt.input_ids.to(x.device), cond.negative_prompt.attention_mask.to(x.device)
         width = max(ids.shape[1], nids.shape[1])
         pad = lambda a, v: torch.nn.functional.pad(a, (0, width - a.shape[1]), value=v)  # noqa: E731
         v = m.forward_image(torch.cat([pad(nids, int(m.cfg.pad_token_id)), pad(ids, int(m.cfg.pad_token_id))]), torch.cat([pad(nmask, 0), pad(mask, 0)]),
                             torch.cat([x, x]), torch.cat([t, t])).float()
         vu, vc = v.chunk(2)
-        return self._guided(vu, vc, p)
+        return vc, vu
 
 
 __all__ = ["UnifiedConditions", "UnifiedARStage", "UnifiedDiffusionStage"]

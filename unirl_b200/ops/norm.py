@@ -69,12 +69,34 @@ def layernorm_modulate_reference(x: torch.Tensor, shift: torch.Tensor, scale: to
     return (y * (1 + scale.float().unsqueeze(1)) + shift.float().unsqueeze(1)).to(x.dtype)
 
 
-def layernorm_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    if use_native(x) and not (torch.is_grad_enabled() and (x.requires_grad or shift.requires_grad or scale.requires_grad)):
-        C = require_ext()
-        out = C.layernorm_modulate_fwd(x.contiguous(), shift.contiguous(), scale.contiguous(), float(eps))
+class _LayerNormModulate(torch.autograd.Function):
+    """adaLN forward and backward as one kernel each; the statistics are recomputed in the backward (nothing saved but the inputs)."""
+
+    @staticmethod
+    def forward(ctx, x, shift, scale, eps: float):
+        x, shift, scale = x.contiguous(), shift.contiguous(), scale.contiguous()
+        out = require_ext().layernorm_modulate_fwd(x, shift, scale, float(eps))
         count_launch()
+        ctx.save_for_backward(x, scale)
+        ctx.eps, ctx.mod_dtype = float(eps), shift.dtype
         return out
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, scale = ctx.saved_tensors
+        dx, dshift, dscale = require_ext().layernorm_modulate_bwd(gy.contiguous(), x, scale, ctx.eps)
+        count_launch()
+        return dx, dshift.to(ctx.mod_dtype), dscale.to(ctx.mod_dtype), None
+
+
+def layernorm_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    if use_native(x) and x.dim() == 3 and shift.dtype == x.dtype and scale.dtype == x.dtype:
+        if not (torch.is_grad_enabled() and (x.requires_grad or shift.requires_grad or scale.requires_grad)):
+            out = require_ext().layernorm_modulate_fwd(x.contiguous(), shift.contiguous(), scale.contiguous(), float(eps))
+            count_launch()
+            return out
+        if x.shape[-1] <= 6144:
+            return _LayerNormModulate.apply(x, shift, scale, eps)
     return layernorm_modulate_reference(x, shift, scale, eps)
 
 

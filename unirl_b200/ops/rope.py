@@ -86,6 +86,47 @@ def qk_norm_rope_cached(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_w
     return q, k, v
 
 
+class _RopeTable(torch.autograd.Function):
+    """Rotation by per-token tables; the gradient is the rotation by the opposite angle."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin, interleaved: bool):
+        y = require_ext().rope_table(x.contiguous(), cos, sin, bool(interleaved), False)
+        count_launch()
+        ctx.save_for_backward(cos, sin)
+        ctx.interleaved = bool(interleaved)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        cos, sin = ctx.saved_tensors
+        gx = require_ext().rope_table(gy.contiguous(), cos, sin, ctx.interleaved, True)
+        count_launch()
+        return gx, None, None, None
+
+
+def rope_table_reference(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """fp32 statement of the table-driven rotation: ``x [..., L, H, D]``, ``cos / sin [L, D/2]``."""
+    xf = x.float()
+    c, s = cos.float().unsqueeze(-2), sin.float().unsqueeze(-2)  # [L, 1, D/2]
+    if interleaved:
+        p = xf.unflatten(-1, (-1, 2))
+        a, b = p[..., 0], p[..., 1]
+        return torch.stack([a * c - b * s, a * s + b * c], -1).flatten(-2).to(x.dtype)
+    h = x.shape[-1] // 2
+    a, b = xf[..., :h], xf[..., h:]
+    return torch.cat([a * c - b * s, b * c + a * s], -1).to(x.dtype)
+
+
+def rope_table(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """Rotate ``x [..., L, H, D]`` by per-token angle tables ``cos / sin [L, D/2]`` (any leading batch dimensions share the tables).
+    ``interleaved``: pairs ``(2i, 2i+1)`` (axial 3-D rotary of the diffusion transformers); otherwise ``(i, i + D/2)`` (3-axis rotary of
+    the vision-language decoder).  One kernel forward, one backward."""
+    if use_native(x) and x.dtype in (torch.bfloat16, torch.float32):
+        return _RopeTable.apply(x, cos.float().contiguous(), sin.float().contiguous(), bool(interleaved))
+    return rope_table_reference(x, cos, sin, interleaved)
+
+
 def mrope_cos_sin(positions3: torch.Tensor, head_dim: int, theta: float, sections: Tuple[int, int, int]) -> Tuple[torch.Tensor, torch.Tensor]:
     """Multimodal rotary tables: frequency ``j`` takes its position from the temporal, height or width axis according to
     ``sections`` (counts of frequencies per axis, summing to ``head_dim / 2``).  ``positions3`` is ``[3, T]``."""
@@ -99,8 +140,19 @@ def mrope_cos_sin(positions3: torch.Tensor, head_dim: int, theta: float, section
 def mrope_qk(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], positions3: torch.Tensor, n_q: int, n_kv: int,
              head_dim: int, theta: float, eps: float, sections: Tuple[int, int, int]):
     """QK-norm + 3-axis rotary for vision-language prompts (prefill / training; decode positions collapse to one axis
-    and take the fused kernel).  Differentiable PyTorch composition."""
+    and take the fused kernel).  On CUDA: the per-head RMS-norm kernel, then the table-driven rotary kernel (both differentiable);
+    elsewhere the PyTorch composition below."""
     t = qkv.shape[0]
+    if use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float32):
+        from unirl_b200.ops.norm import rmsnorm
+
+        q, k, v = qkv.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], -1)
+        q, k = q.reshape(t, n_q, head_dim), k.reshape(t, n_kv, head_dim)
+        if q_weight is not None:
+            q = rmsnorm(q.reshape(-1, head_dim), q_weight, eps).view(t, n_q, head_dim)
+            k = rmsnorm(k.reshape(-1, head_dim), k_weight, eps).view(t, n_kv, head_dim)
+        cos, sin = mrope_cos_sin(positions3, head_dim, theta, sections)
+        return rope_table(q, cos, sin, False), rope_table(k, cos, sin, False), v.reshape(t, n_kv, head_dim).contiguous()
     q, k, v = qkv.float().split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], -1)
     q, k = q.view(t, n_q, head_dim), k.view(t, n_kv, head_dim)
     if q_weight is not None:
@@ -111,4 +163,4 @@ def mrope_qk(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Opti
     return _rotate(q, cos, sin).to(qkv.dtype), _rotate(k, cos, sin).to(qkv.dtype), v.reshape(t, n_kv, head_dim).to(qkv.dtype)
 
 
-__all__ = ["qk_norm_rope", "qk_norm_rope_reference", "qk_norm_rope_cached", "rope_cos_sin", "mrope_qk", "mrope_cos_sin"]
+__all__ = ["qk_norm_rope", "qk_norm_rope_reference", "qk_norm_rope_cached", "rope_cos_sin", "mrope_qk", "mrope_cos_sin", "rope_table", "rope_table_reference"]
