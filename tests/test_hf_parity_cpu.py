@@ -118,3 +118,61 @@ def test_bundles_load_checkpoint_directories(tmp_path):
     vb = QwenVLBundle.from_config(QwenVLPipelineConfig(pretrained_model_ckpt_path=str(d2), model_precision="fp32", device="cpu"))
     assert vb.model_config.vision.depth == 2 and vb.model_config.mrope_section == (2, 3, 3)
     assert torch.equal(vb.transformer.visual.merge_fc2.detach(), vl.state_dict()["model.visual.merger.mlp.2.weight"])
+
+
+@pytest.mark.parametrize("act,proj", [("quick_gelu", True), ("gelu", False)])
+def test_clip_text_tower_matches_transformers(tmp_path, act, proj):
+    """Published-layout CLIP text checkpoints (with and without the projection head) land in the native encoder: last and penultimate
+    hidden states and the pooled vector agree with ``transformers``."""
+    from transformers import CLIPTextConfig, CLIPTextModel, CLIPTextModelWithProjection
+
+    from unirl_b200.models.dit.text_keys import load_hf_text_encoder
+
+    torch.manual_seed(0)
+    hc = CLIPTextConfig(vocab_size=99, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, max_position_embeddings=16, hidden_act=act,
+                        projection_dim=24, eos_token_id=98, bos_token_id=97, pad_token_id=98)
+    hf = (CLIPTextModelWithProjection if proj else CLIPTextModel)(hc).eval()
+    hf.save_pretrained(tmp_path)
+    enc, cfg = load_hf_text_encoder(str(tmp_path), dtype=torch.float32)
+    assert cfg.act == act and cfg.projection_dim == (24 if proj else 0)
+    ids = torch.randint(0, 97, (3, 16))
+    ids[:, 0] = 97
+    for b, n in enumerate((5, 16, 9)):
+        ids[b, n - 1:] = 98  # EOS, then padding with the same id: the pooled vector is taken at the FIRST one
+    with torch.no_grad():
+        out = hf(input_ids=ids, output_hidden_states=True)
+        seq, pooled = enc(ids)
+    torch.testing.assert_close(seq, out.hidden_states[-2], rtol=1e-4, atol=1e-5)  # SD3 conditions on the penultimate layer
+    want = out.text_embeds if proj else out.pooler_output
+    torch.testing.assert_close(pooled, want, rtol=1e-4, atol=1e-5)
+    enc.cfg.penultimate = False
+    torch.testing.assert_close(enc(ids)[0], out.last_hidden_state, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("umt5", [False, True])
+def test_t5_encoder_matches_transformers(tmp_path, umt5):
+    """T5 v1.1 (one shared relative-position table) and UMT5 (one per layer) encoders: hidden states agree with ``transformers``,
+    padding masked."""
+    from transformers import T5Config, T5EncoderModel, UMT5Config, UMT5EncoderModel
+
+    from unirl_b200.models.dit.text_keys import load_hf_text_encoder
+
+    torch.manual_seed(1)
+    kw = dict(vocab_size=120, d_model=32, d_kv=8, d_ff=48, num_layers=3, num_heads=4, relative_attention_num_buckets=8, relative_attention_max_distance=20,
+              feed_forward_proj="gated-gelu", dropout_rate=0.0)
+    hf = (UMT5EncoderModel(UMT5Config(**kw)) if umt5 else T5EncoderModel(T5Config(**kw))).eval()
+    with torch.no_grad():  # the library initialises some tables identically across layers: make every tensor distinct
+        for p in hf.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+    hf.save_pretrained(tmp_path)
+    enc, cfg = load_hf_text_encoder(str(tmp_path), dtype=torch.float32)
+    assert cfg.rel_bias_per_layer == umt5 and cfg.kind == "t5"
+    ids = torch.randint(1, 120, (2, 23))
+    mask = torch.ones(2, 23, dtype=torch.long)
+    mask[1, 15:] = 0
+    with torch.no_grad():
+        want = hf(input_ids=ids, attention_mask=mask).last_hidden_state
+        got, pooled = enc(ids, mask)
+    assert pooled is None
+    torch.testing.assert_close(got[0], want[0], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(got[1, :15], want[1, :15], rtol=1e-4, atol=1e-5)

@@ -71,8 +71,22 @@ class DiTBundle(Bundle):
                 for f in shards:
                     sd.update(load_file(f))
                 load_diffusers_transformer(model, sd, spec.transformer.name, strict=True)
-        encoders = [TextEncoder(c, dtype=dtype, device=device).init_weights(config.init_seed + 1 + i) for i, c in enumerate(spec.text_encoders)]
-        toks = [load_tokenizer(None, c.vocab_size, True) for c in spec.text_encoders]
+        encoders, toks = [], []
+        for i, c in enumerate(spec.text_encoders):
+            # diffusers layout: text_encoder, text_encoder_2, text_encoder_3 (+ tokenizer, tokenizer_2, ...) next to the transformer
+            suffix = "" if i == 0 else f"_{i + 1}"
+            enc_dir = None if path.startswith("random:") else os.path.join(path, "text_encoder" + suffix)
+            if enc_dir and os.path.isdir(enc_dir) and c.kind in ("clip", "t5"):
+                from unirl_b200.models.dit.text_keys import load_hf_text_encoder
+
+                enc, loaded_cfg = load_hf_text_encoder(enc_dir, dtype=dtype, device=device)
+                loaded_cfg.max_length, loaded_cfg.penultimate = c.max_length, c.penultimate  # sequence length and layer choice are the family's
+                spec.text_encoders[i] = loaded_cfg
+                encoders.append(enc)
+                toks.append(load_tokenizer(os.path.join(path, "tokenizer" + suffix), loaded_cfg.vocab_size, True))
+            else:
+                encoders.append(TextEncoder(c, dtype=dtype, device=device).init_weights(config.init_seed + 1 + i))
+                toks.append(load_tokenizer(None, c.vocab_size, True))
         vae = LatentVAE(spec.vae, device=device).init_weights(config.init_seed + 7)
         return cls(model, encoders, vae, toks, config, spec)
 

@@ -38,14 +38,16 @@ class TextEncoderConfig:
     rel_buckets: int = 32
     rel_max_distance: int = 128
     eps: float = 1e-6
+    act: str = "gelu"  # CLIP MLP activation: "gelu" (open_clip bigG) | "quick_gelu" (OpenAI CLIP-L)
+    rel_bias_per_layer: bool = False  # UMT5: every layer owns a relative-position table (T5: the first layer's is shared)
 
     @classmethod
     def clip_l(cls) -> "TextEncoderConfig":
-        return cls("clip", 49408, 768, 12, 12, 3072, 77, 768)
+        return cls("clip", 49408, 768, 12, 12, 3072, 77, 768, eos_token_id=49407, act="quick_gelu")
 
     @classmethod
     def clip_g(cls) -> "TextEncoderConfig":
-        return cls("clip", 49408, 1280, 32, 20, 5120, 77, 1280)
+        return cls("clip", 49408, 1280, 32, 20, 5120, 77, 1280, eos_token_id=49407)
 
     @classmethod
     def t5_xxl(cls) -> "TextEncoderConfig":
@@ -53,7 +55,7 @@ class TextEncoderConfig:
 
     @classmethod
     def umt5_xxl(cls) -> "TextEncoderConfig":
-        return cls("t5", 256384, 4096, 24, 64, 10240, 512, 0, False)
+        return cls("t5", 256384, 4096, 24, 64, 10240, 512, 0, False, rel_bias_per_layer=True)
 
     @classmethod
     def tiny(cls, kind: str = "clip", hidden: int = 32, vocab: int = 512, max_length: int = 16) -> "TextEncoderConfig":
@@ -72,6 +74,7 @@ class _Layer(nn.Module):
         self.out = nn.Linear(h, h, bias=bias, dtype=dtype, device=device)
         self.fc1 = nn.Linear(h, c.ffn_dim * (1 if c.kind == "clip" else 2), bias=bias, dtype=dtype, device=device)
         self.fc2 = nn.Linear(c.ffn_dim, h, bias=bias, dtype=dtype, device=device)
+        self.rel_bias = nn.Embedding(c.rel_buckets, c.num_heads, dtype=dtype, device=device) if (c.kind == "t5" and c.rel_bias_per_layer) else None
 
     def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
         b, l, h = x.shape
@@ -81,7 +84,7 @@ class _Layer(nn.Module):
         x = x + self.out(a.transpose(1, 2).reshape(b, l, h))
         y = self.fc1(self.norm2(x))
         if self.c.kind == "clip":
-            y = F.gelu(y)
+            y = y * torch.sigmoid(1.702 * y) if self.c.act == "quick_gelu" else F.gelu(y)
         else:
             g, u = y.chunk(2, -1)
             y = F.gelu(g, approximate="tanh") * u
@@ -95,7 +98,7 @@ class TextEncoder(nn.Module):
         h = cfg.hidden_size
         self.embed = nn.Embedding(cfg.vocab_size, h, dtype=dtype, device=device)
         self.pos = nn.Embedding(cfg.max_length, h, dtype=dtype, device=device) if cfg.kind == "clip" else None
-        self.rel_bias = nn.Embedding(cfg.rel_buckets, cfg.num_heads, dtype=dtype, device=device) if cfg.kind == "t5" else None
+        self.rel_bias = nn.Embedding(cfg.rel_buckets, cfg.num_heads, dtype=dtype, device=device) if (cfg.kind == "t5" and not cfg.rel_bias_per_layer) else None
         self.layers = nn.ModuleList(_Layer(cfg, dtype, device) for _ in range(cfg.num_layers))
         self.final_norm = nn.LayerNorm(h, eps=1e-5, dtype=dtype, device=device) if cfg.kind == "clip" else nn.RMSNorm(h, eps=cfg.eps, dtype=dtype, device=device)
         self.projection = nn.Linear(h, cfg.projection_dim, bias=False, dtype=dtype, device=device) if cfg.projection_dim else None
@@ -112,8 +115,9 @@ class TextEncoder(nn.Module):
                 p.fill_(1.0)
         return self.requires_grad_(False).eval()
 
-    def _t5_bias(self, l: int, device: Any) -> torch.Tensor:
+    def _t5_bias(self, l: int, device: Any, table: Optional[nn.Embedding] = None) -> torch.Tensor:
         c = self.cfg
+        table = table if table is not None else self.rel_bias
         rel = torch.arange(l, device=device)[None, :] - torch.arange(l, device=device)[:, None]
         nb = c.rel_buckets // 2
         ret = (rel > 0).long() * nb
@@ -121,7 +125,7 @@ class TextEncoder(nn.Module):
         exact = nb // 2
         large = exact + (torch.log(n.float().clamp(min=1) / exact) / math.log(c.rel_max_distance / exact) * (nb - exact)).long()
         bucket = ret + torch.where(n < exact, n, large.clamp(max=nb - 1))
-        return self.rel_bias(bucket).permute(2, 0, 1)[None]  # [1, heads, L, L]
+        return table(bucket).permute(2, 0, 1)[None]  # [1, heads, L, L]
 
     @torch.no_grad()
     def forward(self, ids: torch.Tensor, mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -135,12 +139,16 @@ class TextEncoder(nn.Module):
         neg = torch.finfo(x.dtype).min
         if c.kind in ("clip", "llm"):
             bias = torch.full((l, l), neg, dtype=x.dtype, device=ids.device).triu(1)[None, None]
-        elif c.kind == "t5":
+        elif c.kind == "t5" and not c.rel_bias_per_layer:
             bias = self._t5_bias(l, ids.device).to(x.dtype)
-        if mask is not None and c.kind == "t5":
-            bias = bias + (1.0 - mask[:, None, None, :].to(x.dtype)) * neg
+        pad = None if (mask is None or c.kind != "t5") else (1.0 - mask[:, None, None, :].to(x.dtype)) * neg
+        if pad is not None and bias is not None:
+            bias = bias + pad
         hidden_states = []
         for layer in self.layers:
+            if c.kind == "t5" and c.rel_bias_per_layer:
+                bias = self._t5_bias(l, ids.device, layer.rel_bias).to(x.dtype)
+                bias = bias if pad is None else bias + pad
             x = layer(x, bias)
             hidden_states.append(x)
         last = self.final_norm(x)
