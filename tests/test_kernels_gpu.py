@@ -563,6 +563,41 @@ def test_rollout_replay_parity_and_train_step_tiny():
     assert pipe.bundle.transformer.layers[0].qkv_proj.grad is not None
 
 
+@pytest.mark.parametrize("cascade", [False, True])
+def test_decode_bookkeeping_kernels_match_the_tensor_op_path(cascade):
+    """record + advance and prepare as one kernel each: every state tensor identical to the element-wise composition, over several steps,
+    with stop tokens, the length limit and rows that are already finished."""
+    from unirl_b200.rollout.engine.native_ar.generator import _DecodeState
+
+    torch.manual_seed(21)
+    b, max_new, ps, pages = 37, 6, 16, 12
+    dev = torch.device("cuda")
+    states = [_DecodeState(b, max_new, dev) for _ in range(2)]
+    pos0 = torch.randint(0, 100, (b,), device=dev)
+    off = torch.randint(0, 50, (b,), device=dev)
+    bt = torch.randint(1, 500, (b, pages), device=dev, dtype=torch.int32)
+    stop = torch.tensor([3, 7], device=dev)
+    for st in states:
+        st.positions.copy_(pos0)
+        st.rope_offset.copy_(off)
+        st.finished[::5] = True
+        if cascade:
+            st.prefix_len = torch.randint(0, 3, (b,), device=dev, dtype=torch.int32) * ps
+            st.suffix_lens = torch.zeros(b, dtype=torch.int32, device=dev)
+    ref, fused = states
+    ref._native = lambda: None  # the tensor-op composition
+    for step in range(8):
+        tok = torch.randint(0, 10, (b,), device=dev)
+        lp = -torch.rand(b, device=dev)
+        for st in states:
+            st.prepare(bt, ps)
+            st.record(tok, lp, stop, fuse_advance=True)
+            st.advance()
+        for name in ("out_tokens", "out_logp", "cur_tokens", "positions", "slots", "rope_pos", "seq_lens", "lengths", "finished", "step_counter") + (("suffix_lens",) if cascade else ()):
+            assert torch.equal(getattr(ref, name), getattr(fused, name)), (name, step)
+    assert bool(fused.finished.all()) and int(fused.step_counter) == 8
+
+
 def test_rope_with_fused_cache_write_matches_two_step_path():
     from unirl_b200.ops.attention import kv_cache_write
     from unirl_b200.ops.rope import qk_norm_rope, qk_norm_rope_cached

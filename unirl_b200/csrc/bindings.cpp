@@ -119,6 +119,42 @@ std::vector<Tensor> layernorm_modulate_bwd(const Tensor& dy, const Tensor& x, co
   TORCH_CHECK(ok, "layernorm_modulate_bwd: rows of ", x.size(2), " elements are too wide for the kernel");
   return {dx, dshift, dscale};
 }
+// Decode-loop bookkeeping.  Every state tensor is a (row-)view of the generator's state: first dimension B, unit stride inside a row.
+static void chk_rows(const Tensor& t, int64_t B, at::ScalarType ty, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == ty && t.dim() >= 1 && t.size(0) == B && t.stride(t.dim() - 1) == 1, "decode bookkeeping: ", name,
+              " must be a CUDA tensor of ", B, " rows with the expected dtype");
+}
+void decode_record_advance(const Tensor& tok, const Tensor& lp, const Tensor& stop, Tensor& out_tokens, Tensor& out_logp, Tensor& cur_tokens, Tensor& lengths,
+                           Tensor& finished, Tensor& positions, Tensor& step_counter) {
+  const int64_t B = tok.size(0);
+  chk_rows(tok, B, at::kLong, "tok"); chk_rows(lp, B, at::kFloat, "lp"); chk_rows(out_tokens, B, at::kLong, "out_tokens"); chk_rows(out_logp, B, at::kFloat, "out_logp");
+  chk_rows(cur_tokens, B, at::kLong, "cur_tokens"); chk_rows(lengths, B, at::kLong, "lengths"); chk_rows(finished, B, at::kBool, "finished");
+  chk_rows(positions, B, at::kLong, "positions");
+  TORCH_CHECK(tok.is_contiguous() && lp.is_contiguous() && stop.is_cuda() && stop.scalar_type() == at::kLong && stop.is_contiguous() && out_tokens.dim() == 2 &&
+                  out_logp.sizes() == out_tokens.sizes() && out_logp.stride(0) == out_tokens.stride(0) && step_counter.scalar_type() == at::kLong,
+              "decode_record_advance: argument layout");
+  c10::cuda::CUDAGuard g(tok.device());
+  ub::decode_record_advance(tok.data_ptr<int64_t>(), lp.data_ptr<float>(), stop.data_ptr<int64_t>(), (int)stop.numel(), out_tokens.data_ptr<int64_t>(),
+                            out_logp.data_ptr<float>(), out_tokens.stride(0), cur_tokens.data_ptr<int64_t>(), lengths.data_ptr<int64_t>(),
+                            reinterpret_cast<uint8_t*>(finished.data_ptr<bool>()), positions.data_ptr<int64_t>(), step_counter.data_ptr<int64_t>(), (int)B,
+                            out_tokens.size(1), stream());
+}
+void decode_prepare(const Tensor& positions, const Tensor& block_tables, int64_t page_size, const Tensor& rope_offset, Tensor& slots, Tensor& seq_lens, Tensor& rope_pos,
+                    const c10::optional<Tensor>& prefix_len, const c10::optional<Tensor>& suffix_lens) {
+  const int64_t B = positions.size(0);
+  chk_rows(positions, B, at::kLong, "positions"); chk_rows(block_tables, B, at::kInt, "block_tables"); chk_rows(rope_offset, B, at::kLong, "rope_offset");
+  chk_rows(slots, B, at::kLong, "slots"); chk_rows(seq_lens, B, at::kInt, "seq_lens"); chk_rows(rope_pos, B, at::kLong, "rope_pos");
+  const bool cascade = suffix_lens.has_value() && suffix_lens->defined();
+  if (cascade) {
+    TORCH_CHECK(prefix_len.has_value() && prefix_len->defined(), "decode_prepare: suffix_lens needs prefix_len");
+    chk_rows(*prefix_len, B, at::kInt, "prefix_len"); chk_rows(*suffix_lens, B, at::kInt, "suffix_lens");
+  }
+  TORCH_CHECK(block_tables.dim() == 2 && page_size > 0, "decode_prepare: block_tables [B, pages]");
+  c10::cuda::CUDAGuard g(positions.device());
+  ub::decode_prepare(positions.data_ptr<int64_t>(), block_tables.data_ptr<int>(), block_tables.stride(0), (int)page_size, rope_offset.data_ptr<int64_t>(),
+                     slots.data_ptr<int64_t>(), seq_lens.data_ptr<int>(), rope_pos.data_ptr<int64_t>(), cascade ? prefix_len->data_ptr<int>() : nullptr,
+                     cascade ? suffix_lens->data_ptr<int>() : nullptr, (int)B, stream());
+}
 // Rotary embedding from per-token tables: x [..., L, H, D] (any leading batch dimensions), cos / sin fp32 [L, D / 2].
 Tensor rope_table(const Tensor& x, const Tensor& cos_t, const Tensor& sin_t, bool interleaved, bool backward) {
   chk(x, "x"); chk(cos_t, "cos"); chk(sin_t, "sin");
@@ -681,6 +717,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("qk_norm_rope_cache_fwd", &qk_norm_rope_cache_fwd);
   m.def("rope_table", &rope_table);
+  m.def("decode_record_advance", &decode_record_advance);
+  m.def("decode_prepare", &decode_prepare);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("kv_cache_write", &kv_cache_write);

@@ -797,6 +797,63 @@ int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, cons
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
+// ===================================================================================== decode-loop bookkeeping
+// The per-step state updates of the generator (append the sampled token, latch the stop condition, advance the cache index; then derive
+// cache slot, KV length and rotary position of the token fed next) as two launches instead of about thirty element-wise library
+// kernels.  One thread per batch row; every tensor is updated in place so a captured graph can own them.
+__global__ void decode_record_advance_kernel(const int64_t* __restrict__ tok, const float* __restrict__ lp, const int64_t* __restrict__ stop, int n_stop,
+                                             int64_t* __restrict__ out_tokens, float* __restrict__ out_logp, int64_t out_stride, int64_t* __restrict__ cur_tokens,
+                                             int64_t* __restrict__ lengths, uint8_t* __restrict__ finished, int64_t* __restrict__ positions,
+                                             int64_t* __restrict__ step_counter, int B, int64_t max_new) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r == 0) *step_counter += 1;
+  if (r >= B) return;
+  const bool live = finished[r] == 0;
+  const int64_t t = tok[r];
+  int64_t len = lengths[r];
+  if (live) {
+    const int64_t col = len < max_new - 1 ? len : max_new - 1;
+    out_tokens[r * out_stride + col] = t;
+    out_logp[r * out_stride + col] = lp[r];
+    len += 1;
+    lengths[r] = len;
+  }
+  cur_tokens[r] = t;
+  bool fin = !live || len >= max_new;
+  for (int i = 0; i < n_stop; ++i) fin |= (t == stop[i]);
+  finished[r] = fin ? 1 : 0;
+  if (!fin) positions[r] += 1;  // a finished row stays where it is: it keeps rewriting one slot of its own pages until it is retired
+}
+__global__ void decode_prepare_kernel(const int64_t* __restrict__ positions, const int* __restrict__ block_tables, int64_t bt_stride, int page_size,
+                                      const int64_t* __restrict__ rope_offset, int64_t* __restrict__ slots, int* __restrict__ seq_lens,
+                                      int64_t* __restrict__ rope_pos, const int* __restrict__ prefix_len, int* __restrict__ suffix_lens, int B) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= B) return;
+  const int64_t pos = positions[r];
+  const int64_t page = block_tables[r * bt_stride + pos / page_size];
+  slots[r] = page * page_size + pos % page_size;
+  seq_lens[r] = static_cast<int>(pos + 1);
+  rope_pos[r] = pos + rope_offset[r];
+  if (suffix_lens) suffix_lens[r] = static_cast<int>(pos + 1) - prefix_len[r];
+}
+void decode_record_advance(const int64_t* tok, const float* lp, const int64_t* stop, int n_stop, int64_t* out_tokens, float* out_logp, int64_t out_stride,
+                           int64_t* cur_tokens, int64_t* lengths, uint8_t* finished, int64_t* positions, int64_t* step_counter, int B, int64_t max_new,
+                           cudaStream_t s) {
+  if (B <= 0) return;
+  launch_kernel(decode_record_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, pdl_enabled(), tok, lp, stop, n_stop, out_tokens, out_logp, out_stride, cur_tokens, lengths,
+             finished, positions, step_counter, B, max_new);
+}
+void decode_prepare(const int64_t* positions, const int* block_tables, int64_t bt_stride, int page_size, const int64_t* rope_offset, int64_t* slots, int* seq_lens,
+                    int64_t* rope_pos, const int* prefix_len, int* suffix_lens, int B, cudaStream_t s) {
+  if (B <= 0) return;
+  launch_kernel(decode_prepare_kernel, dim3((B + 127) / 128), dim3(128), 0, s, pdl_enabled(), positions, block_tables, bt_stride, page_size, rope_offset, slots, seq_lens, rope_pos,
+             prefix_len, suffix_lens, B);
+}
+
 // ===================================================================================== table-driven rotary embedding
 // y = rotate(x) for x [rows, H, D] by per-token angles given as tables cos / sin [L, D / 2]: row r of x uses table row r % L (a batch of
 // B sequences of L tokens shares one table).  Two pairings: interleaved (elements 2i, 2i+1 rotate together: the axial 3-D embedding

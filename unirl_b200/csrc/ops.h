@@ -61,6 +61,13 @@ int qk_norm_rope_cache_fwd(const void* qkv, const void* qw, const void* kw, cons
 // sign -1 = the backward rotation.
 void rope_table(const void* x, const float* cos_t, const float* sin_t, void* y, int64_t rows, int H, int D, int64_t L, int interleaved, float sign, int dtype,
                 cudaStream_t s);
+// Decode-loop bookkeeping (one thread per batch row, all tensors updated in place): append the sampled token and its log-prob for live
+// rows, latch stop tokens / the length limit, advance live rows' cache index; then derive cache slot, KV length and rotary position.
+void decode_record_advance(const int64_t* tok, const float* lp, const int64_t* stop, int n_stop, int64_t* out_tokens, float* out_logp, int64_t out_stride,
+                           int64_t* cur_tokens, int64_t* lengths, uint8_t* finished, int64_t* positions, int64_t* step_counter, int B, int64_t max_new,
+                           cudaStream_t s);
+void decode_prepare(const int64_t* positions, const int* block_tables, int64_t bt_stride, int page_size, const int64_t* rope_offset, int64_t* slots, int* seq_lens,
+                    int64_t* rope_pos, const int* prefix_len, int* suffix_lens, int B, cudaStream_t s);
 void swiglu_fwd(const void* gu, void* out, int64_t rows, int I, int dtype, cudaStream_t s);
 void swiglu_bwd(const void* gy, const void* gu, void* g_gu, int64_t rows, int I, int dtype, cudaStream_t s);
 void kv_cache_write(const void* k, const void* v, void* kc, void* vc, const int64_t* slots, int64_t T, int Hkv, int D, int page_size, int dtype,

@@ -202,7 +202,7 @@ class ARGenerator:
             st.prepare(block_tables, ps)
             hidden = self.model(st.cur_tokens, meta)
             tok, lp = self._sample(hidden, temperature, top_k, top_p, seed, None, st)
-            st.record(tok, lp, stop)
+            st.record(tok, lp, stop, fuse_advance=True)
             st.advance()
 
         n_steps = 1
@@ -431,7 +431,7 @@ class ARGenerator:
                 v.prepare(bt_b, ps)
                 hidden = self.model(v.cur_tokens, meta)
                 tok, lp = self._sample(hidden, temperature, top_k, top_p, seed, None, v)
-                v.record(tok, lp, stop)
+                v.record(tok, lp, stop, fuse_advance=True)
                 v.advance()
 
             step()  # one eager step per bucket: one-time kernel attribute / library workspace set-up must not happen under capture
@@ -553,6 +553,7 @@ class _DecodeState:
         self.rng_ids = torch.arange(b, device=dev)  # sequence index that keys the row's random stream (with `lengths` as the token index)
         self.max_new = max_new
         self.cpu_gen: Optional[torch.Generator] = None
+        self._advanced = False
 
     _ROW_FIELDS = ("out_tokens", "out_logp", "cur_tokens", "positions", "slots", "rope_offset", "rope_pos", "seq_lens", "lengths", "finished", "rng_ids",
                    "prefix_len", "suffix_lens")
@@ -570,10 +571,31 @@ class _DecodeState:
     def advance(self) -> None:
         """Move every LIVE row to its next cache index; a finished row stays where it is (it keeps rewriting one slot of its own pages
         until it is retired, instead of walking past the pages reserved for it)."""
+        if self._advanced:  # the fused record kernel already did it
+            self._advanced = False
+            return
         self.positions.add_((~self.finished).long())
 
-    def record(self, tok: torch.Tensor, lp: torch.Tensor, stop: torch.Tensor) -> None:
-        """Append the sampled token for every unfinished row, then latch EOS."""
+    def _native(self) -> Any:
+        if not self.positions.is_cuda:
+            return None
+        from unirl_b200.ops._ext import ext
+
+        C = ext()
+        return C if C is not None and hasattr(C, "decode_record_advance") else None
+
+    def record(self, tok: torch.Tensor, lp: torch.Tensor, stop: torch.Tensor, fuse_advance: bool = False) -> None:
+        """Append the sampled token for every unfinished row, then latch EOS.  On CUDA one kernel does this and (``fuse_advance``) the
+        advance of the cache index that follows it in the decode step."""
+        C = self._native() if fuse_advance else None
+        if C is not None:
+            from unirl_b200.ops._ext import count_launch
+
+            C.decode_record_advance(tok.contiguous(), lp.float().contiguous(), stop.contiguous(), self.out_tokens, self.out_logp, self.cur_tokens, self.lengths,
+                                    self.finished, self.positions, self.step_counter)
+            count_launch()
+            self._advanced = True
+            return
         live = ~self.finished
         col = self.lengths.clamp(max=self.max_new - 1)
         self.out_tokens[self.rows, col] = torch.where(live, tok, self.out_tokens[self.rows, col])
@@ -585,7 +607,14 @@ class _DecodeState:
         self.step_counter.add_(1)
 
     def prepare(self, block_tables: torch.Tensor, page_size: int) -> None:
-        """``positions[b]`` is the index of the token fed this step: derive its cache slot and the KV length."""
+        """``positions[b]`` is the index of the token fed this step: derive its cache slot and the KV length (one kernel on CUDA)."""
+        C = self._native()
+        if C is not None and block_tables.dtype == torch.int32:
+            from unirl_b200.ops._ext import count_launch
+
+            C.decode_prepare(self.positions, block_tables, int(page_size), self.rope_offset, self.slots, self.seq_lens, self.rope_pos, self.prefix_len, self.suffix_lens)
+            count_launch()
+            return
         page = block_tables.gather(1, (self.positions // page_size).unsqueeze(1)).squeeze(1).long()
         self.slots.copy_(page * page_size + self.positions % page_size)
         self.seq_lens.copy_((self.positions + 1).to(torch.int32))
