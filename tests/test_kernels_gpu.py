@@ -558,7 +558,9 @@ def test_rollout_replay_parity_and_train_step_tiny():
     tr = resp.tracks["ar"]
     new = pipe.ar.replay(Qwen3ARConditions.from_dict(tr.conditions), segment=tr.segment, temperature=1.0)
     diff = (new.detach().cpu() - tr.segment.log_probs).abs()
-    assert diff.mean() < 0.03 and diff.max() < 0.3, f"rollout/replay gap too large: mean {diff.mean():.4f} max {diff.max():.4f}"
+    # Measured on this model (three seeds): mean 0.0012-0.0015, max 0.0046-0.0070 -- the same size as either path's distance from an fp32
+    # replay (mean 0.0018), i.e. bf16 rounding of two different kernel sequences.  Bounds at about three times that.
+    assert diff.mean() < 0.004 and diff.max() < 0.02, f"rollout/replay gap too large: mean {diff.mean():.4f} max {diff.max():.4f}"
     new.sum().backward()
     assert pipe.bundle.transformer.layers[0].qkv_proj.grad is not None
 
@@ -577,12 +579,13 @@ def test_decode_bookkeeping_kernels_match_the_tensor_op_path(cascade):
     off = torch.randint(0, 50, (b,), device=dev)
     bt = torch.randint(1, 500, (b, pages), device=dev, dtype=torch.int32)
     stop = torch.tensor([3, 7], device=dev)
+    shared = torch.randint(0, 3, (b,), device=dev, dtype=torch.int32) * ps
     for st in states:
         st.positions.copy_(pos0)
         st.rope_offset.copy_(off)
         st.finished[::5] = True
         if cascade:
-            st.prefix_len = torch.randint(0, 3, (b,), device=dev, dtype=torch.int32) * ps
+            st.prefix_len = shared.clone()
             st.suffix_lens = torch.zeros(b, dtype=torch.int32, device=dev)
     ref, fused = states
     ref._native = lambda: None  # the tensor-op composition

@@ -334,6 +334,7 @@ class DiTTransformer(nn.Module):
                  sp: Optional[Any] = None):
         super().__init__()
         self.cfg, self.sp, self.gradient_checkpointing = cfg, sp, gradient_checkpointing
+        self.checkpoint_layers: Optional[int] = None  # recompute only the first N blocks in backward (None = all): 180 GB of HBM holds the rest
         h = cfg.hidden_size
         self.patch_embed = _Lin(cfg.patch_dim, h, True, dtype, device)
         self.time_in = nn.ModuleList([_Lin(cfg.time_freq_dim, h, True, dtype, device), _Lin(h, h, True, dtype, device)])
@@ -432,7 +433,14 @@ class DiTTransformer(nn.Module):
                 cos, sin = sp.shard_rope(cos, joint_text), sp.shard_rope(sin, joint_text)
         ctx = AttnContext(cos, sin, nt, sp, text_mask)
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
-        run = (lambda blk, *a: torch.utils.checkpoint.checkpoint(blk, *a, use_reentrant=False)) if ckpt else (lambda blk, *a: blk(*a))
+        n_ckpt = None if self.checkpoint_layers is None else int(self.checkpoint_layers)
+        done = [0]
+
+        def run(blk: nn.Module, *a: Any):  # blocks are counted in execution order: joint, single, cross
+            use = ckpt and (n_ckpt is None or done[0] < n_ckpt)
+            done[0] += 1
+            return torch.utils.checkpoint.checkpoint(blk, *a, use_reentrant=False) if use else blk(*a)
+
         for blk in self.joint_blocks:
             img, txt = run(blk, img, txt, vec, ctx)
         if len(self.single_blocks):

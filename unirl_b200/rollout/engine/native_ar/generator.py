@@ -25,6 +25,8 @@ truncation), which is exactly what the trainer's replay recomputes.
 
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple
@@ -582,6 +584,8 @@ class _DecodeState:
         from unirl_b200.ops._ext import ext
 
         C = ext()
+        if os.environ.get("UNIRL_B200_DECODE_BOOKKEEPING", "1") == "0":  # A/B switch: the element-wise composition
+            return None
         return C if C is not None and hasattr(C, "decode_record_advance") else None
 
     def record(self, tok: torch.Tensor, lp: torch.Tensor, stop: torch.Tensor, fuse_advance: bool = False) -> None:
