@@ -134,3 +134,51 @@ def test_secondary_benchmark_script_runs_on_cpu():
     row = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
     assert row["metric"] == "flowdppo_samples_per_s" and row["value"] > 0 and row["config"]["samples_per_prompt"] == 4 and row["steps"] == 1
     assert row["config"]["trained_timesteps"] == 2 and row["config"]["text_tokens"] == 7 and row["e2e"]["h2d_bytes_per_step"] > 0 and row["lora_sync_ms"] > 0
+
+
+def test_family_specific_stages_z_image_hunyuan_video_and_hunyuan_video15():
+    """Behaviour the three families add to the generic core: Z-Image's reversed time / negated output / ``cond + g (cond - uncond)``
+    guidance; HunyuanVideo's single guided pass and cropped prompt template; HunyuanVideo-1.5's channel packing of the transformer input."""
+    from unirl_b200.models.dit.diffusion import DiTDiffusionParams
+    from unirl_b200.models.hunyuan_video import HunyuanVideoPipeline, HunyuanVideoPipelineConfig
+    from unirl_b200.models.hunyuan_video.pipeline import PROMPT_PREFIX
+    from unirl_b200.models.hunyuan_video15 import HunyuanVideo15Pipeline, HunyuanVideo15PipelineConfig
+    from unirl_b200.models.z_image import ZImagePipeline, ZImagePipelineConfig
+    from unirl_b200.models.dit.conditions import DiTConditions
+
+    kw = dict(model_precision="fp32", autocast_precision="fp32", device="cpu")
+    # ---- Z-Image
+    z = ZImagePipeline.from_config(ZImagePipelineConfig(pretrained_model_ckpt_path="random:tiny-z-image", **kw))
+    cond = DiTConditions(text=z.text_embed.embed(["a red cube", "a tree"]), negative_text=z.text_embed.embed(["", ""]))
+    x, sig = torch.randn(2, *z.latent_shape(DiffusionSamplingParams(height=64, width=64))), torch.tensor([0.3])
+    p = DiTDiffusionParams(guidance_scale=0.5)
+    vc, vu = z.diffusion._branches(x, sig, cond, p)
+    model = z.bundle.transformer
+    want = -model(x, (1 - sig).expand(2) * 1000.0, cond.text.embeds, None, cond.text.attn_mask).float()
+    torch.testing.assert_close(vc, want, rtol=1e-4, atol=1e-5)
+    assert vu is not None, "guidance is on for any positive scale"
+    torch.testing.assert_close(z.diffusion._velocity(x, sig, cond, p), vc + 0.5 * (vc - vu))
+    assert z.diffusion._branches(x, sig, cond, DiTDiffusionParams(guidance_scale=0.0))[1] is None
+    # ---- HunyuanVideo: one pass whatever the guidance scale; the template prefix is not part of the conditioning sequence
+    hv = HunyuanVideoPipeline.from_config(HunyuanVideoPipelineConfig(pretrained_model_ckpt_path="random:tiny-hunyuan-video", max_sequence_length=300, **kw))
+    emb = hv.text_embed.embed(["a dog runs", "a dog runs", "night city"])
+    tok = hv.bundle.tokenizers[0]
+    longest = max(len(tok.encode(s + "<|eot_id|>")) for s in ("a dog runs", "night city")) + 1
+    assert emb.embeds.shape[1] == min(longest, hv.bundle.text_encoders[0].cfg.max_length) < len(tok.encode(PROMPT_PREFIX)), "the template prefix is cropped off"
+    assert torch.equal(emb.embeds[0], emb.embeds[1]) and emb.pooled is not None
+    hcond = DiTConditions(text=emb, negative_text=emb)
+    xv = torch.randn(3, *hv.latent_shape(DiffusionSamplingParams(height=32, width=32, num_frames=5)))
+    v, none = hv.diffusion._branches(xv, torch.tensor([0.7]), hcond, DiTDiffusionParams(guidance_scale=6.0))
+    assert none is None and v.shape == xv.shape
+    v2, _ = hv.diffusion._branches(xv, torch.tensor([0.7]), hcond, DiTDiffusionParams(guidance_scale=1.0))
+    assert not torch.allclose(v, v2), "the guidance scale enters through its embedding"
+    # ---- HunyuanVideo-1.5: latents keep the output width; the transformer sees latents + conditioning latents + mask
+    h15 = HunyuanVideo15Pipeline.from_config(HunyuanVideo15PipelineConfig(pretrained_model_ckpt_path="random:tiny-hunyuan-video15", **kw))
+    shape = h15.latent_shape(DiffusionSamplingParams(height=32, width=32, num_frames=5))
+    t15 = h15.bundle.transformer.cfg
+    assert shape[0] == t15.out_channels == 4 and t15.in_channels == 9
+    x15 = torch.randn(2, *shape)
+    c15 = DiTConditions(text=h15.text_embed.embed(["a", "b"]))
+    packed = h15.diffusion._model_input(x15, c15)
+    assert packed.shape[1] == 9 and torch.equal(packed[:, :4], x15) and float(packed[:, 4:].abs().sum()) == 0.0
+    assert h15.diffusion._velocity(x15, torch.tensor([0.5]), c15, DiTDiffusionParams(guidance_scale=1.0)).shape == x15.shape

@@ -92,9 +92,7 @@ class DiTDiffusionStage:
         model = self.bundle.transformer
         t = sigma.to(x.device).float().reshape(-1).expand(x.shape[0]) * 1000.0
         txt = cond.text
-        inp = x
-        if cond.image is not None and cond.image.latents is not None and getattr(self.bundle, "concat_image_latents", False):
-            inp = torch.cat([x, cond.image.latents.to(x)], 1)
+        inp = self._model_input(x, cond)
         guidance = None
         if model.cfg.guidance_embed:
             g = p.distilled_guidance_scale if p.distilled_guidance_scale is not None else p.guidance_scale
@@ -112,6 +110,13 @@ class DiTDiffusionStage:
         v = model(torch.cat([inp, inp]), torch.cat([t, t]), emb, pooled, mask, None if guidance is None else torch.cat([guidance, guidance])).float()
         vu, vc = v.chunk(2)
         return vc, vu
+
+    def _model_input(self, x: torch.Tensor, cond: DiTConditions) -> torch.Tensor:
+        """What the transformer sees for the latent ``x`` (families override): image-to-video bundles append the conditioning image's
+        latents along the channel axis."""
+        if cond.image is not None and cond.image.latents is not None and getattr(self.bundle, "concat_image_latents", False):
+            return torch.cat([x, cond.image.latents.to(x)], 1)
+        return x
 
     def _guided(self, v_uncond: torch.Tensor, v_cond: torch.Tensor, p: DiTDiffusionParams) -> torch.Tensor:
         """Classifier-free guidance combination (families override, e.g. norm-corrected CFG)."""

@@ -53,9 +53,9 @@ class DiTPipeline(Pipeline):
     def latent_shape_for(cls, spec: Any, d: DiffusionSamplingParams) -> Tuple[int, ...]:
         t = spec.transformer
         h, w = int(d.height) // t.vae_scale_factor, int(d.width) // t.vae_scale_factor
-        c = t.in_channels
+        c = t.out_channels or t.in_channels  # the latent has the transformer's OUTPUT width; extra input channels carry conditioning
         if spec.packed_latents:  # 2x2 spatial patches are folded into channels before the transformer
-            c, h, w = t.in_channels, h // 2, w // 2
+            h, w = h // 2, w // 2
         if t.is_video:
             return (c, (int(d.num_frames) - 1) // t.vae_temporal_factor + 1, h, w)
         return (c, h, w)
