@@ -86,6 +86,19 @@ def test_colocated_dp2_trainer_with_tp2_rollout_over_gloo():
         assert trn[0] == trn[1], "both trainer ranks hold the same replica"
         replicated = [k for k in eng[0] if k.endswith("layernorm") or k.endswith("norm") or "embed" in k]
         assert replicated and all(eng[0][k] == eng[1][k] == trn[0][k] for k in replicated)
+        # payloads that arrive already sharded, one entry per tensor-parallel rank: every rank copies its own entry
+        from unirl_b200.distributed.weight_sync.checksum import fingerprint_tensor
+        from unirl_b200.models.qwen3.bundle import resolve_model_config
+        from unirl_b200.models.qwen3.modeling import shard_param
+
+        mcfg = resolve_model_config("random:tiny", {})
+        g = torch.Generator().manual_seed(5)
+        name = "layers.0.qkv_proj"
+        full = torch.randn(((mcfg.num_attention_heads + 2 * mcfg.num_key_value_heads) * mcfg.head_dim, mcfg.hidden_size), generator=g)
+        shards = [{name: shard_param(full, name, mcfg, r, 2).contiguous()} for r in range(2)]
+        assert tr.rollout.update_weights_from_tensor(serialized_named_tensors=shards, load_format="per_tp_rank") == [1, 1]
+        after = tr.rollout.compute_local_param_checksums()
+        assert [after[r][name] for r in range(2)] == [fingerprint_tensor(shards[r][name]) for r in range(2)]
     finally:
         tr.shutdown()
 

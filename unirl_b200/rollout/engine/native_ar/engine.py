@@ -214,9 +214,26 @@ class NativeARRolloutEngine(BaseRolloutEngine):
     @distributed(dispatch_mode=Dispatch.BROADCAST)
     def update_weights_from_tensor(self, *, serialized_named_tensors: List[Any], target_modules: Optional[List[str]] = None,
                                    load_format: Optional[str] = None, flush_cache: bool = True, track_prefix: str = "") -> int:
-        """``serialized_named_tensors``: list of ``{name: full tensor}`` dicts (same process ⇒ no serialisation)."""
+        """``serialized_named_tensors``: list of ``{name: full tensor}`` dicts (same process ⇒ no serialisation), every rank slicing its
+        own shard out of the full tensors.  ``load_format="per_tp_rank"``: the list has one entry per tensor-parallel rank and entry ``i``
+        already holds rank ``i``'s shards (the sender resharded); each rank copies its own entry as is."""
         n = 0
-        if not self._shares_trainer:
+        if not self._shares_trainer and load_format == "per_tp_rank":
+            tp = self.model.tp
+            if len(serialized_named_tensors) != tp.size:
+                raise ValueError(f"per_tp_rank payload has {len(serialized_named_tensors)} entries for {tp.size} tensor-parallel ranks")
+            own = dict(self.model.named_parameters())
+            with torch.no_grad():
+                for k, v in serialized_named_tensors[tp.rank].items():
+                    k = k[len(track_prefix):] if track_prefix and k.startswith(track_prefix) else k
+                    if k not in own:
+                        continue
+                    if tuple(v.shape) != tuple(own[k].shape):
+                        raise ValueError(f"per_tp_rank payload: {k} has shape {tuple(v.shape)}, this rank's shard is {tuple(own[k].shape)}")
+                    own[k].copy_(v.to(own[k].device))
+                    self._lora_base.pop(k, None)
+                    n += 1
+        elif not self._shares_trainer:
             for bucket in serialized_named_tensors:
                 named = {k[len(track_prefix):] if track_prefix and k.startswith(track_prefix) else k: v for k, v in bucket.items()}
                 n += self._load_full(named)
