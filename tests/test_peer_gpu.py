@@ -121,6 +121,41 @@ def test_ulysses_exchange_data_path_one_device(mode):
         assert torch.equal(out, want), (mode, r)
 
 
+@pytest.mark.parametrize("D,local_cols,bias", [(64, 0, True), (128, 256, True), (64, 128, False)])
+def test_head_scatter_projection_data_path_one_device(D, local_cols, bias):
+    """The QKV GEMM whose epilogue stores every head's columns into the rank that owns the head: four "ranks" whose receive buffers live on
+    this device, run one after the other (the kernel itself never waits for a peer).  Each buffer must end up holding, for its heads,
+    every rank's tokens at their place in the gathered sequence; trailing local columns come back as an ordinary matrix."""
+    from unirl_b200.parallel.fused_collectives import FusedHeadScatterProjection as F
+
+    C = _C()
+    torch.manual_seed(5)
+    W, B, l, heads, K = 4, 2, 200, 8, 512  # 400 rows per rank: three full 128-row tiles and a ragged one, rows crossing the batch boundary inside a tile
+    hp, parts = heads // W, 3
+    n = parts * heads * D + local_cols
+    recv = [torch.full((parts * B * W * l * hp * D,), float("nan"), device="cuda").bfloat16() for _ in range(W)]
+    xs = [(torch.randn(B, l, K, device="cuda") * 0.5).bfloat16() for _ in range(W)]
+    w = (torch.randn(n, K, device="cuda") * 0.05).bfloat16()
+    b = (torch.randn(n, device="cuda") * 0.1).bfloat16() if bias else None
+    for r in range(W):
+        table = F.pack_table(F.route_rows([t.data_ptr() for t in recv], r, W, B, l, heads, D, parts, n), "cuda")
+        rest = C.gemm_bf16_route(xs[r].view(B * l, K), w, b, table, l, local_cols)
+        torch.cuda.synchronize()
+        assert C.gemm_status(True) == 0
+        y = xs[r].view(B * l, K).float() @ w.float().t() + (b.float() if bias else 0.0)
+        if local_cols:
+            torch.testing.assert_close(rest.float(), y[:, n - local_cols:], atol=3e-2, rtol=2e-2)
+        else:
+            assert rest.numel() == 0
+    for dst in range(W):
+        got = recv[dst].view(parts, B, W * l, hp, D).float()
+        assert not torch.isnan(got).any(), "every element of the receive buffer is written exactly by its owner"
+        for src in range(W):
+            y = (xs[src].view(B * l, K).float() @ w.float().t() + (b.float() if bias else 0.0))[:, : parts * heads * D].view(B, l, parts, heads, D)
+            want = y[:, :, :, dst * hp:(dst + 1) * hp].permute(2, 0, 1, 3, 4)  # [parts, B, l, hp, D]
+            torch.testing.assert_close(got[:, :, src * l:(src + 1) * l], want, atol=3e-2, rtol=2e-2)
+
+
 def test_scatter_copy_table():
     from unirl_b200.distributed.weight_sync.full.reshard import CopyOp, execute_copy
     from unirl_b200.parallel.fused_collectives import reshard_scatter_local
@@ -216,6 +251,30 @@ def _two_rank_body(rank, world):
             assert ctx._fused is not None, "the peer-memory exchange was not used"
             ctx._fused.check()
     out["ulysses_diff"] = float(max((a - b).abs().max() for a, b in zip(got["nccl"], got["fused"])))
+    # -- the same exchange done by the QKV projection's own epilogue: a joint-block DiT under sequence parallelism, fused vs library form
+    from unirl_b200.models.dit.modeling import DiTConfig, DiTTransformer
+
+    cfg = DiTConfig(hidden_size=512, num_heads=8, head_dim=64, num_joint_blocks=2, num_single_blocks=0, text_dim=64, pooled_dim=32, rope_axes=(16, 24, 24), in_channels=4)
+    res = {}
+    for kind in ("nccl", "fused"):
+        ctx = UlyssesContext(comm, collectives=kind)
+        torch.manual_seed(21)
+        model = DiTTransformer(cfg, dtype=torch.bfloat16, device=dev, sp=ctx).init_weights(1)
+        torch.manual_seed(22)
+        lat, tt, txt, pooled = torch.randn(2, 4, 64, 64, device=dev), torch.tensor([700.0, 100.0], device=dev), torch.randn(2, 7, 64, device=dev), torch.randn(2, 32, device=dev)
+        y = model(lat, tt, txt, pooled)
+        y.float().square().mean().backward()
+        g = torch.cat([p.grad.float().flatten() for p in model.parameters() if p.grad is not None])
+        res[kind] = (y.detach().float(), g)
+        if kind == "fused":
+            assert ctx._scatter is not None and ctx._scatter.calls >= 2, "the projection with the exchange in its epilogue was not used"
+            ctx._scatter.check()
+            with torch.no_grad():  # inference form: the attention reads the symmetric receive buffers in place
+                y2 = model(lat, tt, txt, pooled)
+            out["scatter_infer_diff"] = float((y2.float() - res[kind][0]).abs().max())
+    scale = float(res["nccl"][0].abs().max())
+    out["scatter_fwd_rel"] = float((res["nccl"][0] - res["fused"][0]).abs().max()) / scale
+    out["scatter_grad_rel"] = float((res["nccl"][1] - res["fused"][1]).abs().max()) / float(res["nccl"][1].abs().max())
     return out
 
 
@@ -228,6 +287,8 @@ def test_two_rank_fused_collectives_match_library():
         assert o["param_diff"] <= 1e-2, o  # bf16 replicas after 3 steps
         assert o["replica_diff"] == 0.0, o  # every rank holds the same replica
         assert o["ulysses_diff"] == 0.0, o  # the exchange only moves data: both paths must agree bit for bit
+        # q / k norm and rotary embedding run after the exchange in the fused form and the bias is added in fp32 before rounding: bf16-level agreement
+        assert o["scatter_fwd_rel"] < 3e-2 and o["scatter_grad_rel"] < 5e-2 and o["scatter_infer_diff"] == 0.0, o
 
 
 def test_gemm_with_allreduce_epilogue_data_path_one_device():

@@ -35,6 +35,18 @@ def test_rollout_and_replay_agree_with_images():
     assert float((lp.detach() - tr.segment.log_probs).abs().max()) < 1e-4
     part = conds.slice(1, 3)  # the image lists travel with the prompt rows
     assert len(part.pixel_values) == 2 and torch.equal(part.pixel_values[0], conds.pixel_values[1])
+    # a policy may SAMPLE the placeholder id: in the response it is an ordinary token (the decode step embedded it as text), so the replay
+    # of a response that contains it must neither look for a vision feature nor move the positions of what follows
+    seg = tr.segment
+    forced = seg.tokens.clone()
+    forced[1] = pipe.ar.model.transformer.cfg.image_token_id
+    original, seg.tokens = seg.tokens, forced
+    try:
+        lp2 = pipe.ar.replay(conds, segment=seg, temperature=1.0)
+    finally:
+        seg.tokens = original
+    assert lp2.shape == lp.shape and torch.isfinite(lp2).all()
+    assert float((lp2[0] - lp[0]).abs()) < 1e-5  # the token before the forced one sees the same context
 
 
 @pytest.mark.timeout(600)

@@ -30,6 +30,77 @@ def _body(rank, world):
     return out
 
 
+class _GlooHeadScatter:
+    """Stand-in for the GEMM whose epilogue stores head tiles to their owners: same contract (``[B, l, K]`` → ``[parts, B, P·l, H/P, D]``
+    in a buffer that is reused two calls later), the data moved by a library all-to-all.  Lets the model-side logic of the fused form
+    (norm and rotary embedding after the exchange, text heads sliced, backward through the inverse exchange) run on CPU ranks."""
+
+    def __init__(self, comm):
+        self.comm, self.calls, self._bufs, self._flip = comm, 0, [None, None], 0
+
+    def supports(self, x, weight, heads, head_dim):
+        return True
+
+    def project(self, x, weight, bias, heads, head_dim, parts=3):
+        from unirl_b200.parallel.ulysses import _a2a_seq_to_head
+
+        b, l, _ = x.shape
+        y = x.reshape(b * l, -1) @ weight.t()
+        if bias is not None:
+            y = y + bias
+        y = y.view(b, l, parts, heads, head_dim)
+        out = torch.stack([_a2a_seq_to_head(y[:, :, i].contiguous(), self.comm) for i in range(parts)])
+        i = self._flip
+        self._flip ^= 1
+        if self._bufs[i] is None or self._bufs[i].shape != out.shape:
+            self._bufs[i] = torch.empty_like(out)
+        self._bufs[i].copy_(out)  # reused like the symmetric receive buffers: a caller that keeps a view past the next call but one reads garbage
+        self.calls += 1
+        return self._bufs[i], None
+
+
+def _body_fused(rank, world):
+    from unirl_b200.distributed.group.comm import Comm
+    from unirl_b200.models.dit.modeling import DiTConfig, DiTTransformer
+    from unirl_b200.parallel.ulysses import UlyssesContext
+
+    out = {}
+    for name, cfg in (("joint", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=3, num_single_blocks=0, text_dim=32, pooled_dim=24,
+                                          rope_axes=(4, 6, 6), in_channels=4)),
+                      ("joint-sincos", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=3, text_dim=32, pooled_dim=24, pos_embed="sincos2d",
+                                                 pos_embed_max_size=8, dual_attention_blocks=(0,), in_channels=4)),
+                      ("cross-video", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=0, num_cross_blocks=3, text_dim=32, pooled_dim=0,
+                                                rope_axes=(4, 6, 6), in_channels=4, is_video=True))):
+        torch.manual_seed(0)
+        ref = DiTTransformer(cfg, dtype=torch.float32).init_weights(1)
+        ctx = UlyssesContext(Comm.world())
+        ctx._scatter, ctx._scatter_tried = _GlooHeadScatter(ctx.comm), True
+        sp = DiTTransformer(cfg, dtype=torch.float32, sp=ctx).init_weights(1)
+        x = torch.randn(2, 4, 3, 8, 8) if cfg.is_video else torch.randn(2, 4, 8, 8)
+        t, txt = torch.tensor([700.0, 100.0]), torch.randn(2, 5, 32)
+        pooled = torch.randn(2, 24) if cfg.pooled_dim else None
+        a, b = ref(x, t, txt, pooled), sp(x, t, txt, pooled)
+        a.square().mean().backward()
+        b.square().mean().backward()
+        ga = torch.cat([p.grad.flatten() for p in ref.parameters() if p.grad is not None])
+        gb = torch.cat([p.grad.flatten() for p in sp.parameters() if p.grad is not None])
+        out[name] = (float((a - b).abs().max()), ga, gb, ctx._scatter.calls)
+    return out
+
+
+def test_sequence_parallel_with_exchange_inside_the_projection_matches_single_rank():
+    """The fused form of the attention input (projection that delivers head shards, q / k norm and rotary embedding after the exchange)
+    against the single-rank model, forward and every gradient; the projection's data movement is played by a library all-to-all here."""
+    r0, r1 = run_ranks(_body_fused, 2)
+    for name in r0:
+        assert r0[name][3] >= 3, (name, r0[name][3])  # the fused form was taken in every block
+        assert r0[name][0] < 1e-5 and r1[name][0] < 1e-5, (name, r0[name][0])
+        ga, g0, g1 = r0[name][1], r0[name][2], r1[name][2]
+        summed = g0 + g1
+        ok = ((summed - ga).abs() < 1e-4) | (((g0 - ga).abs() < 1e-4) & ((g1 - ga).abs() < 1e-4))
+        assert bool(ok.all()), (name, int((~ok).sum()), ok.numel())
+
+
 def test_sequence_parallel_dit_matches_single_rank():
     r0, r1 = run_ranks(_body, 2)
     for name in r0:

@@ -13,7 +13,11 @@
 // Epilogues:  STORE (bf16 C) | RESIDUAL (C = acc + R) | SWIGLU (acc = [gate | up] -> silu(gate)·up) |
 //             LSE (per-row partial max / sum-exp / target logit / Gumbel-arg-max of acc/T; logits never leave the SM) |
 //             ACC_F32 (fp32 C += acc, or C = acc: weight gradients land in the trainer's fp32 accumulator) |
-//             DLOGITS (bf16 C = g[row]/T · (onehot(target) − exp(acc/T − lse[row])): the log-prob backward's dZ).
+//             DLOGITS (bf16 C = g[row]/T · (onehot(target) − exp(acc/T − lse[row])): the log-prob backward's dZ) |
+//             ROUTE (bf16 acc + bias, every 64-column box stored through a routing table: the box's rows go to a destination
+//                    matrix of their own, which may be another GPU's memory mapped into this process -- the sequence-shard to
+//                    head-shard exchange of sequence-parallel attention happens in the QKV projection's epilogue, with plain
+//                    16-byte stores; no TMA touches the peer's memory).
 //
 // Every mbarrier wait is bounded; on expiry the role records a code in `status[0]` and all roles drain out,
 // TMEM is released and the kernel returns.
@@ -33,6 +37,14 @@ using namespace sm100;
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kGemmThreads = 192;
+
+// Destination of one 64-column box of the ROUTE epilogue: element (row, c) of the box lands at base + drow * stride + c with
+// drow = row + (row / rows_per_batch) * extra.  base == nullptr: the box goes to the ordinary C matrix at its own columns.
+struct RouteEntry {
+  bf16* base;
+  int32_t stride;
+  int32_t extra;
+};
 
 struct GemmParams {
   int M, N, K;            // N = number of OUTPUT columns of C (for SWIGLU: I; B has 2I rows)
@@ -63,6 +75,10 @@ struct GemmParams {
   const float* lse;       // [M] log-sum-exp of the scaled logits
   const float* gout;      // [M] upstream gradient of the token log-prob
   int col_offset;         // global vocabulary index of column 0 of this launch (chunked vocabulary)
+  // ROUTE epilogue
+  const RouteEntry* route;  // one entry per 64-column box of the output
+  const bf16* bias;         // [N] or null, added before the store
+  int rows_per_batch;       // rows of one batch element (the destination row is row + (row / rows_per_batch) * entry.extra)
 };
 
 template <int BN>
@@ -305,6 +321,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           ++store_ctr;
         }
+      } else if (EPI == kEpiRoute) {
+        // bf16 box of 32 rows x 64 columns staged in swizzled shared memory exactly as for a TMA store, then read back so that
+        // eight consecutive lanes write the 128 contiguous bytes of one row: the destination of a box comes from the routing table.
+        const int n0 = n_idx * BN;
+        uint8_t* sbuf = store_smem + q * (2 * L::kStoreChunk);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          if (n0 + c0 >= p.N) break;  // uniform over the warp
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float acc[32];
+            tmem_ld_32x32(t_row + c0 + h * 32, acc);
+            tmem_ld_wait();
+            if (p.bias) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (n0 + c0 + h * 32 + g * 8 < p.N) {
+                  float bv[8];
+                  load8(p.bias + n0 + c0 + h * 32 + g * 8, bv);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) acc[g * 8 + j] += bv[j];
+                }
+              }
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              Pack8 pk;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) pk.h[j] = __floats2bfloat162_rn(acc[g * 8 + 2 * j], acc[g * 8 + 2 * j + 1]);
+              *reinterpret_cast<Pack8*>(sbuf + lane * 128 + (((h * 4 + g) ^ (lane & 7)) << 4)) = pk;
+            }
+          }
+          __syncwarp();
+          const RouteEntry e = p.route[(n0 + c0) >> 6];
+          bf16* dbase = e.base ? e.base : p.C + n0 + c0;
+          const int64_t dstride = e.base ? e.stride : p.ldc;
+          const int jc = lane & 7;
+          if (n0 + c0 + jc * 8 < p.N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3);
+              const int grow = m0 + q * 32 + r;
+              if (grow < p.M) {
+                const int64_t drow = e.base ? grow + static_cast<int64_t>(grow / p.rows_per_batch) * e.extra : grow;
+                *reinterpret_cast<Pack8*>(dbase + drow * dstride + jc * 8) = *reinterpret_cast<const Pack8*>(sbuf + r * 128 + ((jc ^ (r & 7)) << 4));
+              }
+            }
+          }
+          __syncwarp();  // the box is read before the next one overwrites it
+        }
       } else if (EPI == kEpiAccF32) {
         // fp32 output: 32 x 32 boxes (128-byte rows) staged in swizzled shared memory, then ONE TMA reduce-add (C += acc, done at the
         // memory side: the SM never reads C) or TMA store (C = acc) per box.  `tmC` is the fp32 map of C here.
@@ -399,6 +465,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (lane == 0) mbar_arrive(tempty + buf);
     }
     if (lane == 0) tma_store_wait_all<0>();  // shared memory must outlive every store that reads it
+    if (EPI == kEpiRoute) __threadfence_system();  // stores into a peer's memory are ordered before the rendezvous kernel that follows
   }
 
   tc_fence_before();
@@ -614,6 +681,24 @@ int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, in
   if (!make_tensor_map_bf16(&tmB, B, N, K, ldb, BN)) return 1;
   if (epilogue == kEpiResidual) return wide ? launch_variant<256, kEpiResidual>(tmA, tmB, tmC, p, s) : launch_variant<128, kEpiResidual>(tmA, tmB, tmC, p, s);
   return wide ? launch_variant<256, kEpiStore>(tmA, tmB, tmC, p, s) : launch_variant<128, kEpiStore>(tmA, tmB, tmC, p, s);
+}
+
+// C = A[M,K]·B[N,K]ᵀ + bias with every 64-column box of the result stored where `route` (device array of N / 64 entries) says.
+// Boxes whose entry has no base go to C[M, ldc] (may be null when no entry needs it).  N must be a multiple of 64.
+int gemm_bf16_route(const void* A, const void* B, const void* bias, void* C, int M, int N, int K, int lda, int ldb, int ldc, const void* route,
+                    int rows_per_batch, int* status, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) || (N % 64) || (lda % 8) || (ldb % 8) || (C && (ldc % 8)) || rows_per_batch <= 0 || !route) return 1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = static_cast<bf16*>(C); p.ldc = ldc; p.status = status;
+  p.route = static_cast<const RouteEntry*>(route); p.bias = static_cast<const bf16*>(bias); p.rows_per_batch = rows_per_batch;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  const bool wide = g_force_bn ? g_force_bn == 256 : (N >= 256 * 2 || N % 256 == 0);
+  const int BN = wide ? 256 : 128;
+  p.num_n_tiles = (N + BN - 1) / BN;
+  CUtensorMap tmA, tmB;
+  if (!make_tensor_map_bf16(&tmA, A, M, K, lda, BM) || !make_tensor_map_bf16(&tmB, B, N, K, ldb, BN)) return 1;
+  return wide ? launch_variant<256, kEpiRoute>(tmA, tmB, tmA, p, s) : launch_variant<128, kEpiRoute>(tmA, tmB, tmA, p, s);  // no TMA store: third map unused
 }
 
 int lse_num_tiles(int V) { return (V + 255) / 256; }

@@ -219,6 +219,8 @@ class AttnContext:
     def __init__(self, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], text_len: int, sp: Optional[Any] = None,
                  text_mask: Optional[torch.Tensor] = None):
         self.cos, self.sin, self.text_len, self.sp, self.text_mask = cos, sin, text_len, sp, text_mask
+        self.cos_full: Optional[torch.Tensor] = None  # unsharded tables [text + all latent tokens] for attention on head shards
+        self.sin_full: Optional[torch.Tensor] = None
 
     def rope(self, q: torch.Tensor, k: torch.Tensor, offset: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
         if self.cos is None:
@@ -231,6 +233,31 @@ class AttnContext:
         if self.sp is not None and self.sp.size > 1:
             return self.sp.attention(q, k, v, n_text)
         return dense_attention(q, k, v)
+
+    def fused_sp_attention(self, attn: "_Attn", x: torch.Tensor, text_qkv: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+                           rope: bool = True) -> Optional[torch.Tensor]:
+        """Sequence-parallel attention of the latent stream ``x [B, l, hidden]`` (already normalised and modulated) with the sequence → head
+        exchange done by the QKV projection itself: the GEMM's epilogue stores every head's columns into the rank that owns the head.
+        q / k norm and the rotary embedding then run on this rank's heads over the whole sequence.  ``text_qkv``: projected, normalised
+        text tokens (replicated, all heads), joined in front.  Returns ``[B, n_text + l, H, D]`` like :meth:`attend`, or None when this
+        projection cannot take the fused form (no peer memory, an adapter on the projection, a q / k norm that spans heads)."""
+        sp = self.sp
+        if sp is None or sp.size <= 1 or getattr(attn.qkv, "_lora_index", None):
+            return None
+        hd = attn.qkv.weight.shape[0] // (3 * attn.n)
+        if any(w is not None and w.numel() != hd for w in (attn.q_norm, attn.k_norm)) or not sp.can_scatter_project(x, attn.qkv.weight, attn.n):
+            return None
+        q, k, v = sp.scatter_project(x, attn.qkv.weight, attn.qkv.bias, attn.n).unbind(0)  # [B, P·l, H/P, D]
+        q, k = _qk_norm(q, attn.q_norm, attn.eps), _qk_norm(k, attn.k_norm, attn.eps)
+        nt = 0
+        if text_qkv is not None and text_qkv[0].shape[1]:
+            nt, hp = text_qkv[0].shape[1], attn.n // sp.size
+            tq, tk, tv = (t[:, :, sp.rank * hp : (sp.rank + 1) * hp] for t in text_qkv)
+            q, k, v = torch.cat([tq, q], 1), torch.cat([tk, k], 1), torch.cat([tv, v], 1)
+        if rope and self.cos_full is not None:
+            off = self.cos_full.shape[0] - q.shape[1]  # tables carry the text rows in front; a latent-only call skips them
+            q, k = apply_rope(q, self.cos_full[off:], self.sin_full[off:]), apply_rope(k, self.cos_full[off:], self.sin_full[off:])
+        return sp.finish(dense_attention(q, k, v), nt)
 
 
 class JointBlock(nn.Module):
@@ -255,17 +282,23 @@ class JointBlock(nn.Module):
         img_n = layernorm_modulate(img, im[0], im[1], eps)
         img_n2 = layernorm_modulate(img, im[6], im[7], eps) if self.dual else None  # both norms see the block input
         txt_n = layernorm_modulate(txt, tm[0], tm[1], eps)
-        qi, ki, vi = self.img_attn.project(img_n)
         qt, kt, vt = self.txt_attn.project(txt_n)
         nt = txt.shape[1]
-        q, k, v = torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1)
-        if ctx.cos is not None:
-            q, k = ctx.rope(q, k)
-        a = ctx.attend(q, k, v, nt).flatten(-2)
+        a = ctx.fused_sp_attention(self.img_attn, img_n, (qt, kt, vt))
+        if a is None:
+            qi, ki, vi = self.img_attn.project(img_n)
+            q, k, v = torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1)
+            if ctx.cos is not None:
+                q, k = ctx.rope(q, k)
+            a = ctx.attend(q, k, v, nt)
+        a = a.flatten(-2)
         img = img + im[2].unsqueeze(1) * self.img_attn.out(a[:, nt:])
         if self.dual:
-            q2, k2, v2 = self.img_attn2.project(img_n2)
-            img = img + im[8].unsqueeze(1) * self.img_attn2.out(ctx.attend(q2, k2, v2, 0).flatten(-2))
+            a2 = ctx.fused_sp_attention(self.img_attn2, img_n2, rope=False)
+            if a2 is None:
+                q2, k2, v2 = self.img_attn2.project(img_n2)
+                a2 = ctx.attend(q2, k2, v2, 0)
+            img = img + im[8].unsqueeze(1) * self.img_attn2.out(a2.flatten(-2))
         img = img + im[5].unsqueeze(1) * self.img_mlp(layernorm_modulate(img, im[3], im[4], eps))
         if self.update_text:
             txt = txt + tm[2].unsqueeze(1) * self.txt_attn.out(a[:, :nt])
@@ -312,9 +345,13 @@ class CrossBlock(nn.Module):
     def forward(self, img: torch.Tensor, txt: torch.Tensor, tproj: torch.Tensor, ctx: AttnContext) -> torch.Tensor:
         c = self.cfg
         m = (tproj.unflatten(-1, (6, -1)) + self.modulation.unsqueeze(0)).unbind(1)
-        q, k, v = self.self_attn.project(layernorm_modulate(img, m[0], m[1], c.eps))
-        q, k = ctx.rope(q, k)
-        img = img + m[2].unsqueeze(1) * self.self_attn.out(ctx.attend(q, k, v, 0).flatten(-2))
+        img_n = layernorm_modulate(img, m[0], m[1], c.eps)
+        a = ctx.fused_sp_attention(self.self_attn, img_n)
+        if a is None:
+            q, k, v = self.self_attn.project(img_n)
+            q, k = ctx.rope(q, k)
+            a = ctx.attend(q, k, v, 0)
+        img = img + m[2].unsqueeze(1) * self.self_attn.out(a.flatten(-2))
         xq = _qk_norm(_heads(self.cross_q(self.cross_norm(img)), c.num_heads), self.cross_q_norm, c.eps)
         xk, xv = self.cross_kv(txt).chunk(2, -1)
         xk = _qk_norm(_heads(xk, c.num_heads), self.cross_k_norm, c.eps)
@@ -425,13 +462,15 @@ class DiTTransformer(nn.Module):
         sp = self.sp if (self.sp is not None and self.sp.size > 1) else None
         if sp is not None:
             img = sp.shard_sequence(img)
-        cos = sin = None
+        cos = sin = cos_full = sin_full = None
         if cfg.pos_embed == "rope":
             joint_text = nt if (cfg.num_joint_blocks or cfg.num_single_blocks) else 0
             cos, sin = self._rope(grid, joint_text, img.device)
             if sp is not None:
+                cos_full, sin_full = cos, sin
                 cos, sin = sp.shard_rope(cos, joint_text), sp.shard_rope(sin, joint_text)
         ctx = AttnContext(cos, sin, nt, sp, text_mask)
+        ctx.cos_full, ctx.sin_full = cos_full, sin_full
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
         n_ckpt = None if self.checkpoint_layers is None else int(self.checkpoint_layers)
         done = [0]
@@ -451,6 +490,7 @@ class DiTTransformer(nn.Module):
         if len(self.cross_blocks):
             tproj = self.time_proj(F.silu(vec))
             cross_ctx = AttnContext(cos, sin, 0, sp, text_mask)
+            cross_ctx.cos_full, cross_ctx.sin_full = cos_full, sin_full
             for blk in self.cross_blocks:
                 img = run(blk, img, txt, tproj, cross_ctx)
         if self.final_mod is None:

@@ -47,7 +47,7 @@ class QwenVLARStage(Qwen3ARStage):
         meta = AttnMeta(mode="train", cu_seqlens=cu_dev, max_seqlen=max_len)
         full = [torch.cat([p.to(torch.long).cpu(), r.to(torch.long).cpu()]) for p, r in zip(prompts, responses)]
         extras = conditions.extras() or [None] * len(full)
-        model.prepare_multimodal(full, extras, meta)
+        model.prepare_multimodal(full, extras, meta, prompt_lens=[len(p) for p in prompts])
         hidden = model(tokens, meta)
         return linear_logprob(hidden.index_select(0, pred_index), model.output_weight, targets, float(temperature))
 

@@ -309,24 +309,37 @@ class QwenVLTransformer(Qwen3Transformer):
         elif strict:
             raise KeyError("checkpoint holds no vision tower tensors (visual.* / model.visual.*)")
 
-    def embed_multimodal(self, tokens: torch.Tensor, pixel_values: Optional[torch.Tensor], grid_thw: Optional[torch.Tensor]) -> torch.Tensor:
+    def embed_multimodal(self, tokens: torch.Tensor, pixel_values: Optional[torch.Tensor], grid_thw: Optional[torch.Tensor],
+                         placeholder_region: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``placeholder_region`` (bool per token): where a placeholder id stands for a vision feature.  A policy may SAMPLE a placeholder id
+        in its response; there it is an ordinary token with its text embedding, as it was when the decode step embedded it."""
         x = self.embed_tokens[tokens]
         if pixel_values is None or grid_thw is None or not pixel_values.numel():
             return x
         feats = self.visual(pixel_values.to(x.device), grid_thw.cpu())
         mask = (tokens == self.cfg.image_token_id) | (tokens == self.cfg.video_token_id)
+        if placeholder_region is not None:
+            mask = mask & placeholder_region.to(mask.device)
         if int(mask.sum()) != feats.shape[0]:
             raise ValueError(f"{int(mask.sum())} image placeholder tokens but {feats.shape[0]} vision features")
         return x.masked_scatter(mask.unsqueeze(-1), feats.to(x.dtype))
 
-    def prepare_multimodal(self, prompts: Sequence[torch.Tensor], extras: Sequence[Any], meta: AttnMeta) -> torch.Tensor:
-        """Packed multimodal prefill / replay set-up.  ``extras[i]``: ``{"pixel_values": [n_i, patch_dim], "image_grid_thw": [k_i, 3]}`` or ``None``."""
+    def prepare_multimodal(self, prompts: Sequence[torch.Tensor], extras: Sequence[Any], meta: AttnMeta,
+                           prompt_lens: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """Packed multimodal prefill / replay set-up.  ``extras[i]``: ``{"pixel_values": [n_i, patch_dim], "image_grid_thw": [k_i, 3]}`` or ``None``.
+        ``prompt_lens[i]``: sequence ``i`` is prompt + response and only its first ``prompt_lens[i]`` tokens may hold vision placeholders;
+        the response continues the positions one per token (what the decode loop did), whatever ids it contains."""
         dev = self.embed_tokens.device
-        pos, deltas, pvs, grids = [], [], [], []
-        for p, e in zip(prompts, extras):
+        pos, deltas, pvs, grids, region = [], [], [], [], []
+        for i, (p, e) in enumerate(zip(prompts, extras)):
             g = e.get("image_grid_thw") if e else None
             g = g if g is not None and len(g) else torch.zeros(0, 3, dtype=torch.long)
-            pp, d = mrope_positions(p.cpu(), g.tolist(), self.cfg)
+            n = len(p) if prompt_lens is None else int(prompt_lens[i])
+            pp, d = mrope_positions(p[:n].cpu(), g.tolist(), self.cfg)
+            if n < len(p):
+                tail = torch.arange(n, len(p), dtype=pp.dtype) + int(d)
+                pp = torch.cat([pp, tail.unsqueeze(0).expand(pp.shape[0], -1)], 1)
+            region.append(torch.arange(len(p)) < n)
             pos.append(pp)
             deltas.append(d)
             if e and e.get("pixel_values") is not None and len(g):
@@ -334,7 +347,8 @@ class QwenVLTransformer(Qwen3Transformer):
                 grids.append(torch.as_tensor(g).long())
         tokens = torch.cat([p.to(torch.long) for p in prompts]).to(dev)
         meta.positions = torch.cat(pos, 1).to(dev)
-        meta.input_embeds = self.embed_multimodal(tokens, torch.cat(pvs) if pvs else None, torch.cat(grids) if grids else None)
+        meta.input_embeds = self.embed_multimodal(tokens, torch.cat(pvs) if pvs else None, torch.cat(grids) if grids else None,
+                                                  torch.cat(region) if prompt_lens is not None else None)
         return torch.tensor(deltas, dtype=torch.long)
 
 

@@ -130,6 +130,18 @@ class _NativeLinear(torch.autograd.Function):
         return gx, gw, (gy if ctx.has_res else None), None
 
 
+def linear_grads(g2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, need_x: bool = True, need_w: bool = True):
+    """``(dX, dW)`` of ``y = x2 · wᵀ`` for an upstream gradient ``g2 [M, N]``: the tcgen05 GEMM with the operands read as stored, the
+    library for shapes it does not take.  For autograd functions that produce ``y`` in a form of their own."""
+    if _bwd_native_ok(g2, x2, w):
+        C = require_ext()
+        gx = C.gemm_bf16(g2, w, False, True) if need_x else None
+        gw = C.gemm_bf16(g2, x2, True, True) if need_w else None
+        count_launch((1 if need_x else 0) + (1 if need_w else 0))
+        return gx, gw
+    return (g2 @ w if need_x else None), (g2.t() @ x2 if need_w else None)
+
+
 EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
 
 

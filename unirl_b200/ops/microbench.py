@@ -503,6 +503,36 @@ def case_peer(args: argparse.Namespace) -> None:
         moved = xa.numel() * 2 * (world - 1) / world  # bytes this rank pulls over NVLink
         _emit({"case": "peer_ulysses_exchange", "world": world, "shape": list(xa.shape), "fused_ms": f, "library_pack_all_to_all_unpack_ms": n, "speedup": n / f,
                "nvlink_gbs": moved / f / 1e6, "nvlink_peer_copy_gbs_measured_reference": 770.0})
+    # -- the same exchange inside the QKV projection: WAN-14B geometry (hidden 5120, 40 heads x 128, 32760 / 8 tokens per rank) and SD3.5-M
+    # (hidden 1536, 24 heads x 64, 4096 / world tokens, batch 8); "separate" = projection GEMM, bias add, then the exchange kernel per q / k / v
+    from unirl_b200.ops.linear import linear
+    from unirl_b200.parallel.fused_collectives import FusedHeadScatterProjection
+
+    sc = FusedHeadScatterProjection(comm, dev, wait_s=20.0)
+    for label, (bsz, l, hidden, nh, hd) in (("wan14b", (1, 4095, 5120, 40 // world * world, 128)), ("sd35m", (8, 4096 // world, 1536, 24 // world * world, 64))):
+        xin = torch.randn(bsz, l, hidden, device=dev, dtype=torch.bfloat16)
+        wq = torch.randn(3 * nh * hd, hidden, device=dev, dtype=torch.bfloat16) * 0.02
+        bq = torch.randn(3 * nh * hd, device=dev, dtype=torch.bfloat16)
+
+        def separate():
+            y = (linear(xin, wq) + bq).view(bsz, l, 3, nh, hd)
+            return [ex.exchange(y[:, :, i].contiguous(), 0) for i in range(3)]
+
+        def fused():
+            return sc.project(xin, wq, bq, nh, hd, 3)
+
+        def gemm_only():
+            return linear(xin, wq)
+
+        f, n, g = tmax(timer(fused)["median_ms"]), tmax(timer(separate)["median_ms"]), tmax(timer(gemm_only)["median_ms"])
+        sc.check()
+        ex.check()
+        if rank == 0:
+            moved = bsz * l * 3 * nh * hd * 2 * (world - 1) / world  # bytes this rank stores into its peers
+            flops = 2.0 * bsz * l * hidden * 3 * nh * hd
+            _emit({"case": "peer_qkv_projection_with_exchange", "geometry": label, "world": world, "tokens_per_rank": bsz * l, "fused_ms": f, "separate_ms": n, "gemm_alone_ms": g,
+                   "speedup": n / f, "exchange_cost_over_gemm_ms": f - g, "fused_tflops": flops / f / 1e9, "nvlink_gbs_if_not_overlapped": moved / max(f - g, 1e-6) / 1e6,
+                   "roofline_ms": max(flops / (_peaks()["tflops"] * 1e9), moved / 770e6), "nvlink_peer_copy_gbs_measured_reference": 770.0})
     dist.barrier()
     dist.destroy_process_group()
 

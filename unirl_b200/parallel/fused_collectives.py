@@ -251,6 +251,94 @@ def make_fused_ulysses_exchange(comm: Comm, device: Any = None) -> Optional[Fuse
     return FusedUlyssesExchange(comm, device)
 
 
+class FusedHeadScatterProjection:
+    """QKV projection whose epilogue IS the sequence-shard → head-shard exchange: the tcgen05 GEMM stores every 64-column box of its
+    output straight into the memory of the rank that owns the box's head, at the row this rank's tokens have in the gathered sequence
+    (plain 16-byte stores on the symmetric mapping; no staging copy, no separate exchange pass).  One rendezvous kernel follows the GEMM;
+    after it ``recv[part, b, p·l + t, hh, :]`` on rank ``r`` holds rank ``p``'s token ``t``, head ``r·Hp + hh`` of part (q, k, v).
+
+    Two receive buffers alternate call by call: a peer may start the next projection's stores while this rank still reads the previous
+    result, but never the one before it (every call ends in a rendezvous that all ranks enter only after consuming the older buffer).
+    Columns past the routed parts (the MLP half of a fused single-stream projection) stay local and are returned as they are."""
+
+    def __init__(self, comm: Comm, device: Any, wait_s: float = 60.0):
+        self.comm, self.device, self.wait_s = comm, torch.device(device), float(wait_s)
+        self.arena: Optional[PeerArena] = None
+        self._recv: List[torch.Tensor] = []
+        self._tables: Dict[Tuple, torch.Tensor] = {}
+        self._flip = 0
+        self.calls = 0
+        self._C = _ext.require_ext()
+
+    def _buffers(self, numel: int) -> None:
+        if not self._recv or self._recv[0].numel() < numel:  # collective and deterministic: every rank grows at the same call
+            cap = max(numel, 1 << 20)
+            self.arena = PeerArena(self.comm, 2 * (cap * 2 + 256) + 512, self.device, self.wait_s)
+            self._recv = [self.arena.take(cap, torch.bfloat16) for _ in range(2)]
+            self._tables.clear()
+            self._flip = 0
+
+    @staticmethod
+    def route_rows(peer_bases: Sequence[int], rank: int, world: int, B: int, l: int, heads: int, head_dim: int, parts: int, n_cols: int) -> List[Tuple[int, int, int]]:
+        """Routing table rows ``(address, stride, extra)`` per 64-column box for an output of ``n_cols`` columns laid out
+        ``[parts x heads x head_dim | local columns]``; ``peer_bases[p]`` is the byte address of rank ``p``'s receive buffer."""
+        hp = heads // world
+        rows: List[Tuple[int, int, int]] = []
+        for col in range(0, n_cols, 64):
+            if col >= parts * heads * head_dim:
+                rows.append((0, 0, 0))
+                continue
+            part, rem = divmod(col, heads * head_dim)
+            head, d0 = divmod(rem, head_dim)
+            dst, hl = divmod(head, hp)
+            elem = part * B * world * l * hp * head_dim + rank * l * hp * head_dim + hl * head_dim + d0
+            rows.append((int(peer_bases[dst]) + 2 * elem, hp * head_dim, (world - 1) * l))
+        return rows
+
+    @staticmethod
+    def pack_table(rows: Sequence[Tuple[int, int, int]], device: Any) -> torch.Tensor:
+        return torch.tensor([[a, s | (e << 32)] for a, s, e in rows], dtype=torch.int64).to(device)
+
+    def supports(self, x: torch.Tensor, weight: torch.Tensor, heads: int, head_dim: int) -> bool:
+        return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and head_dim % 64 == 0 and heads % self.comm.size == 0
+                and weight.shape[0] % 64 == 0 and weight.shape[1] % 64 == 0 and x.dim() == 3 and hasattr(self._C, "gemm_bf16_route"))
+
+    def project(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int, head_dim: int, parts: int = 3) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """``x [B, l, K]`` → ``(recv [parts, B, P·l, Hp, D]`` — a view of a symmetric buffer that the call after next overwrites —, local columns or None)``."""
+        world, rank = self.comm.size, self.comm.rank
+        b, l, _ = x.shape
+        hp, n = heads // world, weight.shape[0]
+        numel = parts * b * world * l * hp * head_dim
+        self._buffers(numel)
+        buf = self._flip
+        self._flip ^= 1
+        key = (buf, b, l, heads, head_dim, parts, n)
+        table = self._tables.get(key)
+        if table is None:
+            off = self._recv[buf].data_ptr() - self.arena._buf.data_ptr()
+            bases = [int(pb) + off for pb in self.arena._hdl.buffer_ptrs]
+            table = self.pack_table(self.route_rows(bases, rank, world, b, l, heads, head_dim, parts, n), x.device)
+            self._tables[key] = table
+        local_cols = n - parts * heads * head_dim
+        rest = self._C.gemm_bf16_route(x.reshape(b * l, -1).contiguous(), weight, bias, table, l, local_cols)
+        _ext.count_launch()
+        self.arena.barrier()  # every rank's stores into this rank's buffer have landed
+        self.calls += 1
+        out = self._recv[buf][:numel].view(parts, b, world * l, hp, head_dim)
+        return out, (rest.view(b, l, local_cols) if local_cols else None)
+
+    def check(self) -> None:
+        if self.arena is not None:
+            self.arena.check()
+
+
+def make_fused_head_scatter(comm: Comm, device: Any = None) -> Optional[FusedHeadScatterProjection]:
+    device = device if device is not None else (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu")
+    if not peer_memory_available(comm, device):
+        return None
+    return FusedHeadScatterProjection(comm, device)
+
+
 # ------------------------------------------------------------------------------------------------ sharded trainer
 class FusedShardComm(ShardComm):
     """Sharded-trainer collectives through peer memory: replicas and gradient buffers live in symmetric arenas."""

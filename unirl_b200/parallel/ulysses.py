@@ -14,6 +14,7 @@ part of the model code so the trainer uses it too.
 
 from __future__ import annotations
 
+import os
 from typing import Any, Optional
 
 import torch
@@ -81,6 +82,32 @@ class _GatherHeads(torch.autograd.Function):
         return g[:, :, r * ctx.hp : (r + 1) * ctx.hp].contiguous(), None
 
 
+class _ScatterProject(torch.autograd.Function):
+    """``x [B, l, K]`` → ``[parts, B, P·l, H/P, D]``: the projection GEMM stores each head's columns into the owning rank's memory from its
+    epilogue (forward).  Backward brings the gradient back with the head → sequence exchange and runs the two projection-gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], sp: "UlyssesContext", heads: int, head_dim: int, parts: int):
+        out, _ = sp._scatter.project(x, weight, bias, heads, head_dim, parts)
+        ctx.sp, ctx.parts, ctx.has_bias = sp, parts, bias is not None
+        if any(ctx.needs_input_grad[:3]):
+            ctx.save_for_backward(x, weight)
+            return out.clone()  # the symmetric buffer is overwritten two calls later; what autograd keeps must not live there
+        return out
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        from unirl_b200.ops.linear import linear_grads
+
+        x, weight = ctx.saved_tensors
+        sp = ctx.sp
+        b, l, _ = x.shape
+        gy = torch.cat([sp._exchange(g[i].contiguous(), 1).reshape(b * l, -1) for i in range(ctx.parts)], 1)  # [B·l, parts·H·D]
+        gx, gw = linear_grads(gy, x.reshape(b * l, -1), weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        gb = gy.sum(0).to(weight.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return (gx.view_as(x) if gx is not None else None), gw, gb, None, None, None, None
+
+
 class UlyssesContext:
     def __init__(self, comm: Comm, collectives: str = "fused"):
         self.comm = comm
@@ -88,6 +115,28 @@ class UlyssesContext:
         self.collectives = collectives  # fused (peer-memory exchange kernel) | nccl (pack + all-to-all + unpack)
         self._fused: Any = None
         self._fused_tried = False
+        self._scatter: Any = None  # FusedHeadScatterProjection: the exchange inside the QKV projection's epilogue
+        self._scatter_tried = False
+        self.fuse_projection = os.environ.get("UNIRL_B200_ULYSSES_FUSED_QKV", "1") == "1"
+
+    # ---- projection + exchange in one kernel --------------------------------------------------------------------
+    def can_scatter_project(self, x: torch.Tensor, weight: torch.Tensor, heads: int) -> bool:
+        """True when the QKV projection of ``x [B, l, K]`` can run as the GEMM whose epilogue stores head tiles to their owners."""
+        if not (self.fuse_projection and self.collectives == "fused" and self.size > 1 and x.dim() == 3):
+            return False
+        if not self._scatter_tried and x.is_cuda:
+            self._scatter_tried = True
+            try:
+                from unirl_b200.parallel.fused_collectives import make_fused_head_scatter
+
+                self._scatter = make_fused_head_scatter(self.comm, x.device)
+            except Exception:  # noqa: BLE001  (no symmetric memory on this system: projection, then exchange)
+                self._scatter = None
+        return self._scatter is not None and weight.shape[0] % (3 * heads) == 0 and self._scatter.supports(x, weight, heads, weight.shape[0] // (3 * heads))
+
+    def scatter_project(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int) -> torch.Tensor:
+        """``x [B, l, K]`` (this rank's tokens) → ``[3, B, P·l, H/P, D]`` (all tokens, this rank's heads) in one GEMM + one rendezvous."""
+        return _ScatterProject.apply(x, weight, bias, self, heads, weight.shape[0] // (3 * heads), 3)
 
     def _exchange(self, x: torch.Tensor, mode: int) -> torch.Tensor:
         """Sequence shard → head shard (``mode 0``) or back (``mode 1``), on the peer-memory kernel when the tensors allow it."""
@@ -134,7 +183,10 @@ class UlyssesContext:
             qq, kk, vv = (torch.cat([a, b], 1) for a, b in zip(txt, lat))
         else:
             qq, kk, vv = lat
-        o = dense_attention(qq, kk, vv)
+        return self.finish(dense_attention(qq, kk, vv), n_text)
+
+    def finish(self, o: torch.Tensor, n_text: int = 0) -> torch.Tensor:
+        """Attention output ``[B, n_text + L, H/P, D]`` (all tokens, this rank's heads) → ``[B, n_text + L/P, H, D]``."""
         out_lat = self._exchange(o[:, n_text:], 1)
         if not n_text:
             return out_lat
