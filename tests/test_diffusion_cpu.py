@@ -182,3 +182,34 @@ def test_family_specific_stages_z_image_hunyuan_video_and_hunyuan_video15():
     packed = h15.diffusion._model_input(x15, c15)
     assert packed.shape[1] == 9 and torch.equal(packed[:, :4], x15) and float(packed[:, 4:].abs().sum()) == 0.0
     assert h15.diffusion._velocity(x15, torch.tensor([0.5]), c15, DiTDiffusionParams(guidance_scale=1.0)).shape == x15.shape
+
+
+def test_qwen_image_text_stage_with_a_language_model_tower():
+    """Qwen-Image's conditioning: chat template, decoder-only language model (the package's own decoder behind the encoder interface),
+    system prefix cut off, zero rows and a mask at the padding, no pooled vector, identical prompts encoded once."""
+    from unirl_b200.models.dit.llm_tower import LLMTextTower
+    from unirl_b200.models.qwen3.modeling import Qwen3Config
+    from unirl_b200.models.qwen_image import QwenImagePipeline, QwenImagePipelineConfig
+    from unirl_b200.models.qwen_image.pipeline import PROMPT_PREFIX, PROMPT_SUFFIX, QwenImageTextEmbedStage
+
+    pipe = QwenImagePipeline.from_config(QwenImagePipelineConfig(pretrained_model_ckpt_path="random:tiny-qwen-image", model_precision="fp32", autocast_precision="fp32",
+                                                                 device="cpu", max_sequence_length=64))
+    assert isinstance(pipe.text_embed, QwenImageTextEmbedStage)
+    tok = pipe.bundle.tokenizers[0]
+    tdim = pipe.bundle.spec.transformer.text_dim
+    tower = LLMTextTower(Qwen3Config.tiny(vocab_size=512, hidden_size=tdim, head_dim=16, attention_bias=True, qk_norm=False), dtype=torch.float32).init_weights(3)
+    stage = QwenImageTextEmbedStage([tower], [tok], "single", tdim, 64)
+    prompts = ["a red cube on a table", "a tree", "a red cube on a table"]
+    emb = stage.embed(prompts)
+    crop = len(tok.encode(PROMPT_PREFIX))
+    lens = [len(tok.encode(PROMPT_PREFIX + s + PROMPT_SUFFIX)) - crop for s in prompts]
+    assert emb.pooled is None and emb.embeds.shape == (3, max(lens), tdim) and emb.attn_mask.sum(1).tolist() == lens
+    assert torch.equal(emb.embeds[0], emb.embeds[2])
+    assert float(emb.embeds[1, lens[1]:].abs().max()) == 0.0 and float(emb.embeds[1, : lens[1]].abs().min(0).values.max()) > 0.0
+    # the kept rows are the tower's hidden states of the templated prompt from the end of the prefix on (causal: padding cannot reach them)
+    ids = torch.tensor([[int(i) % 512 for i in tok.encode(PROMPT_PREFIX + "a tree" + PROMPT_SUFFIX)]])
+    full, _ = tower(ids, torch.ones_like(ids))
+    torch.testing.assert_close(emb.embeds[1, : lens[1]], full[0, crop:], rtol=1e-4, atol=1e-5)
+    # the pipeline's own stage (stand-in tower of the random preset) follows the same contract
+    e2 = pipe.text_embed.embed(prompts)
+    assert e2.embeds.shape[:2] == emb.embeds.shape[:2] and e2.pooled is None

@@ -176,3 +176,90 @@ def test_t5_encoder_matches_transformers(tmp_path, umt5):
     assert pooled is None
     torch.testing.assert_close(got[0], want[0], rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(got[1, :15], want[1, :15], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("family", ["qwen2", "llama", "qwen3"])
+def test_llm_text_tower_matches_transformers(tmp_path, family):
+    """Decoder-only text towers (Qwen-Image: Qwen2.5-VL's language model; HunyuanVideo: LLaMA; Z-Image: Qwen3) loaded from a checkpoint
+    directory: last hidden states of a right-padded batch agree with ``transformers`` at every real token and are zero at the padding."""
+    from unirl_b200.models.dit.llm_tower import LLMTextTower
+    from unirl_b200.models.dit.text_keys import load_hf_text_encoder
+
+    torch.manual_seed(2)
+    kw = dict(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+              rms_norm_eps=1e-6, rope_theta=10000.0, eos_token_id=7)
+    if family == "qwen2":
+        hf = transformers.Qwen2Model(transformers.Qwen2Config(**kw))
+    elif family == "llama":
+        hf = transformers.LlamaModel(transformers.LlamaConfig(**kw, attention_bias=False))
+    else:
+        if not hasattr(transformers, "Qwen3Model"):
+            pytest.skip("transformers build without Qwen3")
+        hf = transformers.Qwen3Model(transformers.Qwen3Config(**kw, head_dim=16))
+    hf = hf.eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.add_(torch.randn_like(p) * 0.02)  # biases and norm scales away from their constant initial values
+    hf.save_pretrained(tmp_path)
+    tower, info = load_hf_text_encoder(str(tmp_path), dtype=torch.float32)
+    assert isinstance(tower, LLMTextTower) and info.kind == "llm" and info.hidden_size == 64 and info.eos_token_id == 7
+    assert (tower.decoder.layers[0].qkv_bias is not None) == (family == "qwen2") and (tower.decoder.layers[0].q_norm is not None) == (family == "qwen3")
+    ids = torch.randint(8, 300, (3, 21))
+    mask = torch.ones(3, 21, dtype=torch.long)
+    mask[0, 9:], mask[2, 17:] = 0, 0
+    with torch.no_grad():
+        want = hf(input_ids=ids, attention_mask=mask).last_hidden_state
+        got, pooled = tower(ids, mask)
+    assert pooled is None and got.shape == want.shape
+    keep = mask.bool()
+    torch.testing.assert_close(got[keep], want[keep], rtol=1e-4, atol=2e-5)
+    assert float(got[~keep].abs().max()) == 0.0
+
+
+def test_llm_text_tower_reads_the_language_model_of_a_vision_language_checkpoint():
+    """Key grammars of vision-language files: ``model.language_model.*`` and ``language_model.model.*`` map to the decoder, vision and
+    head tensors are left out; the configuration's text part is used."""
+    from unirl_b200.models.dit.llm_tower import decoder_config_from_hf, language_model_tensors
+
+    sd = {"model.language_model.layers.0.input_layernorm.weight": torch.ones(4), "model.visual.blocks.0.norm1.weight": torch.ones(4),
+          "language_model.model.norm.weight": torch.ones(4), "visual.merger.mlp.0.weight": torch.ones(2, 2), "lm_head.weight": torch.ones(3, 4),
+          "model.embed_tokens.weight": torch.ones(3, 4)}
+    got = language_model_tensors(sd)
+    assert sorted(got) == ["model.embed_tokens.weight", "model.layers.0.input_layernorm.weight", "model.norm.weight"]
+    cfg = decoder_config_from_hf({"model_type": "qwen2_5_vl", "vision_config": {"depth": 2, "hidden_size": 8},
+                                  "text_config": {"model_type": "qwen2_5_vl_text", "vocab_size": 50, "hidden_size": 32, "intermediate_size": 48, "num_hidden_layers": 1,
+                                                  "num_attention_heads": 4, "num_key_value_heads": 2, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6}})
+    assert cfg.attention_bias and not cfg.qk_norm and cfg.head_dim == 8 and cfg.rope_theta == 1000000.0 and cfg.num_hidden_layers == 1
+
+
+def test_qwen_image_bundle_loads_its_language_model_tower_from_the_checkpoint(tmp_path):
+    """A checkpoint directory with the transformer and a ``text_encoder`` folder written by ``transformers`` (a Qwen2 decoder): the bundle
+    builds the package's own decoder as the text tower, and the Qwen-Image text stage returns that model's hidden states past the template prefix."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from unirl_b200.models.dit.llm_tower import LLMTextTower
+    from unirl_b200.models.qwen_image import QwenImagePipeline, QwenImagePipelineConfig
+    from unirl_b200.models.qwen_image.pipeline import PROMPT_PREFIX, PROMPT_SUFFIX
+
+    torch.manual_seed(4)
+    rnd = QwenImagePipeline.from_config(QwenImagePipelineConfig(pretrained_model_ckpt_path="random:tiny-qwen-image", model_precision="fp32", autocast_precision="fp32", device="cpu"))
+    tdim = rnd.bundle.spec.transformer.text_dim
+    save_file({k: v.contiguous() for k, v in rnd.bundle.transformer.state_dict().items()}, str(tmp_path / "transformer.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({"preset": "tiny-qwen-image"}))
+    hf = transformers.Qwen2Model(transformers.Qwen2Config(vocab_size=512, hidden_size=tdim, intermediate_size=2 * tdim, num_hidden_layers=2, num_attention_heads=4,
+                                                          num_key_value_heads=2, max_position_embeddings=512, rope_theta=10000.0, eos_token_id=3)).eval().float()
+    hf.save_pretrained(tmp_path / "text_encoder")
+    pipe = QwenImagePipeline.from_config(QwenImagePipelineConfig(pretrained_model_ckpt_path=str(tmp_path), model_precision="fp32", autocast_precision="fp32", device="cpu",
+                                                                 max_sequence_length=64))
+    tower = pipe.bundle.text_encoders[0]
+    assert isinstance(tower, LLMTextTower) and tower.cfg.hidden_size == tdim
+    assert torch.equal(tower.decoder.embed_tokens.detach(), hf.state_dict()["embed_tokens.weight"])
+    tok = pipe.bundle.tokenizers[0]  # no tokenizer folder: the byte tokenizer stands in, the tower does not care
+    emb = pipe.text_embed.embed(["a red cube"])
+    ids = torch.tensor([[int(i) % 512 for i in tok.encode(PROMPT_PREFIX + "a red cube" + PROMPT_SUFFIX)]])
+    with torch.no_grad():
+        want = hf(input_ids=ids).last_hidden_state[:, len(tok.encode(PROMPT_PREFIX)):][:, :64]
+    torch.testing.assert_close(emb.embeds, want, rtol=1e-4, atol=2e-5)
+    assert emb.pooled is None and int(emb.attn_mask.sum()) == want.shape[1]

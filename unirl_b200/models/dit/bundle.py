@@ -76,7 +76,7 @@ class DiTBundle(Bundle):
             # diffusers layout: text_encoder, text_encoder_2, text_encoder_3 (+ tokenizer, tokenizer_2, ...) next to the transformer
             suffix = "" if i == 0 else f"_{i + 1}"
             enc_dir = None if path.startswith("random:") else os.path.join(path, "text_encoder" + suffix)
-            if enc_dir and os.path.isdir(enc_dir) and c.kind in ("clip", "t5"):
+            if enc_dir and os.path.isdir(enc_dir) and c.kind in ("clip", "t5", "llm"):  # "llm": a Qwen / LLaMA decoder, loaded into the package's own
                 from unirl_b200.models.dit.text_keys import load_hf_text_encoder
 
                 enc, loaded_cfg = load_hf_text_encoder(enc_dir, dtype=dtype, device=device)

@@ -500,6 +500,7 @@ class DiTTransformer(nn.Module):
         out = self.final_proj(layernorm_modulate(img, shift, scale, cfg.eps))
         if sp is not None:
             out = sp.gather_sequence(out)
+            sp.end_forward()
         return self.unpatchify(out, grid, video)
 
     def lora_target_modules(self, patterns: Sequence[str] = ("qkv", "out", "fc1", "fc2", "in_proj", "out_proj", "cross_q", "cross_kv", "cross_out")) -> List[str]:

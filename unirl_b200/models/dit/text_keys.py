@@ -80,6 +80,16 @@ def t5_from_hf(sd: Dict[str, Tensor], num_layers: int, per_layer_bias: bool) -> 
     return out
 
 
+_DECODER_TYPES = ("qwen2", "qwen2_vl", "qwen2_5_vl", "qwen3", "llama", "llava", "mistral")
+
+
+def is_decoder_llm(hf: Dict[str, Any]) -> bool:
+    """True for the configuration of a decoder-only language model (possibly inside a vision-language wrapper)."""
+    mt = str(hf.get("model_type", "")).lower()
+    tmt = str((hf.get("text_config") or {}).get("model_type", "")).lower()
+    return mt in _DECODER_TYPES or tmt.replace("_text", "") in _DECODER_TYPES
+
+
 def load_hf_text_encoder(path: str, dtype: torch.dtype = torch.bfloat16, device: Any = "cpu") -> Tuple[TextEncoder, TextEncoderConfig]:
     """A text-encoder directory in the Hugging Face layout (``config.json`` + ``model*.safetensors``) → a native, frozen ``TextEncoder``."""
     import glob
@@ -88,6 +98,11 @@ def load_hf_text_encoder(path: str, dtype: torch.dtype = torch.bfloat16, device:
 
     with open(os.path.join(path, "config.json")) as f:
         hf = json.load(f)
+    if is_decoder_llm(hf):  # Qwen2 / Qwen2.5-VL / Qwen3 / LLaMA towers: the package's own decoder behind the encoder interface
+        from unirl_b200.models.dit.llm_tower import LLMTextTower
+
+        tower = LLMTextTower.from_hf(path, dtype=dtype, device=device)
+        return tower, tower.cfg
     cfg = config_from_hf(hf)
     sd: Dict[str, Tensor] = {}
     for fn in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
@@ -104,4 +119,4 @@ def load_hf_text_encoder(path: str, dtype: torch.dtype = torch.bfloat16, device:
     return enc.requires_grad_(False).eval(), cfg
 
 
-__all__ = ["config_from_hf", "clip_text_from_hf", "t5_from_hf", "load_hf_text_encoder"]
+__all__ = ["config_from_hf", "clip_text_from_hf", "t5_from_hf", "load_hf_text_encoder", "is_decoder_llm"]

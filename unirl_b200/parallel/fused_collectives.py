@@ -327,6 +327,14 @@ class FusedHeadScatterProjection:
         out = self._recv[buf][:numel].view(parts, b, world * l, hp, head_dim)
         return out, (rest.view(b, l, local_cols) if local_cols else None)
 
+    def align(self) -> None:
+        """End a forward pass on buffer 0.  A pass with an odd number of projections would otherwise begin its next run (a replayed CUDA graph
+        repeats the captured buffer order) on the buffer its last projection used, which a peer may still be reading: one more rendezvous
+        makes every rank finish reading first."""
+        if self._flip:
+            self.arena.barrier()
+            self._flip = 0
+
     def check(self) -> None:
         if self.arena is not None:
             self.arena.check()

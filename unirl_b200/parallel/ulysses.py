@@ -154,6 +154,11 @@ class UlyssesContext:
             return _FusedExchange.apply(x, self._fused, mode)
         return (_SeqToHead if mode == 0 else _HeadToSeq).apply(x.contiguous(), self.comm)
 
+    def end_forward(self) -> None:
+        """Called by the model after its last block: leaves the projection's receive buffers in their starting order."""
+        if self._scatter is not None and hasattr(self._scatter, "align"):
+            self._scatter.align()
+
     # ---- sequence sharding of the latent stream ---------------------------------------------------------------
     def shard_sequence(self, x: torch.Tensor) -> torch.Tensor:
         l = x.shape[1]
