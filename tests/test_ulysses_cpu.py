@@ -41,7 +41,7 @@ class _GlooHeadScatter:
     def supports(self, x, weight, heads, head_dim):
         return True
 
-    def project(self, x, weight, bias, heads, head_dim, parts=3):
+    def project(self, x, weight, bias, heads, head_dim, parts=3, stat_parts=0):
         from unirl_b200.parallel.ulysses import _a2a_seq_to_head
 
         b, l, _ = x.shape
@@ -49,6 +49,7 @@ class _GlooHeadScatter:
         if bias is not None:
             y = y + bias
         y = y.view(b, l, parts, heads, head_dim)
+        sq = y[:, :, :stat_parts].float().pow(2).sum((-1, -2)).permute(2, 0, 1).contiguous() if stat_parts else None  # [stat_parts, B, l]
         out = torch.stack([_a2a_seq_to_head(y[:, :, i].contiguous(), self.comm) for i in range(parts)])
         i = self._flip
         self._flip ^= 1
@@ -56,7 +57,7 @@ class _GlooHeadScatter:
             self._bufs[i] = torch.empty_like(out)
         self._bufs[i].copy_(out)  # reused like the symmetric receive buffers: a caller that keeps a view past the next call but one reads garbage
         self.calls += 1
-        return self._bufs[i], None
+        return (self._bufs[i], None, sq) if stat_parts else (self._bufs[i], None)
 
 
 def _body_fused(rank, world):
@@ -70,12 +71,20 @@ def _body_fused(rank, world):
                       ("joint-sincos", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=3, text_dim=32, pooled_dim=24, pos_embed="sincos2d",
                                                  pos_embed_max_size=8, dual_attention_blocks=(0,), in_channels=4)),
                       ("cross-video", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=0, num_cross_blocks=3, text_dim=32, pooled_dim=0,
-                                                rope_axes=(4, 6, 6), in_channels=4, is_video=True))):
+                                                rope_axes=(4, 6, 6), in_channels=4, is_video=True)),
+                      ("cross-video-norm-over-heads", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=0, num_cross_blocks=3, text_dim=32, pooled_dim=0,
+                                                                rope_axes=(4, 6, 6), in_channels=4, is_video=True, qk_norm_scope="full"))):
         torch.manual_seed(0)
         ref = DiTTransformer(cfg, dtype=torch.float32).init_weights(1)
+        if cfg.qk_norm_scope == "full":  # norm scales away from one, so that the weight slices and their gradients are really exercised
+            with torch.no_grad():
+                for n, p in ref.named_parameters():
+                    if n.endswith(("q_norm", "k_norm")):
+                        p.add_(torch.randn_like(p) * 0.2)
         ctx = UlyssesContext(Comm.world())
-        ctx._scatter, ctx._scatter_tried = _GlooHeadScatter(ctx.comm), True
+        ctx._scatter, ctx._scatter_tried, ctx.fuse_projection_norm_over_heads = _GlooHeadScatter(ctx.comm), True, True
         sp = DiTTransformer(cfg, dtype=torch.float32, sp=ctx).init_weights(1)
+        sp.load_state_dict(ref.state_dict())
         x = torch.randn(2, 4, 3, 8, 8) if cfg.is_video else torch.randn(2, 4, 8, 8)
         t, txt = torch.tensor([700.0, 100.0]), torch.randn(2, 5, 32)
         pooled = torch.randn(2, 24) if cfg.pooled_dim else None

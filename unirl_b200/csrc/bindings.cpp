@@ -391,24 +391,31 @@ Tensor gemm_bf16_tn(const Tensor& a, const Tensor& b, const c10::optional<Tensor
   TORCH_CHECK(rc == 0, "gemm_bf16_tn: unsupported shape or launch failure (code ", rc, ") for M=", M, " N=", N, " K=", K);
   return c;
 }
-// Projection whose output columns are routed box by box (64 columns): `route` is an int64 CUDA tensor [N / 64, 2] holding per box the destination
-// address (0 = the returned local matrix, at the box's own columns) and stride | extra << 32 (see ops.h).  Destinations may be peer memory.
+// Projection whose output columns are routed box by box (64 columns): `route` is an int64 CUDA tensor [N / 64, 3] holding per box the destination
+// address (0 = the returned local matrix, at the box's own columns), stride | extra << 32, and the statistics slot (-1: none; see ops.h).  Destinations may be peer memory.
 // `local_cols`: width of the returned local matrix (0: nothing is returned); local boxes are the LAST local_cols columns of the output.
-Tensor gemm_bf16_route(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, const Tensor& route, int64_t rows_per_batch, int64_t local_cols) {
+Tensor gemm_bf16_route(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, const Tensor& route, int64_t rows_per_batch, int64_t local_cols,
+                       const c10::optional<Tensor>& rowsq) {
   chk(a, "a"); chk(b, "weight");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm route: A [M,K] and B [N,K] expected");
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm route: bf16 operands expected");
   const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
   TORCH_CHECK(N % 64 == 0 && local_cols % 64 == 0 && local_cols >= 0 && local_cols <= N, "gemm route: N and local_cols must be multiples of 64");
-  TORCH_CHECK(route.is_cuda() && route.device() == a.device() && route.scalar_type() == at::kLong && route.is_contiguous() && route.numel() == (N / 64) * 2,
-              "gemm route: int64 routing table [N / 64, 2] on the operands' device");
+  TORCH_CHECK(route.is_cuda() && route.device() == a.device() && route.scalar_type() == at::kLong && route.is_contiguous() && route.numel() == (N / 64) * 3,
+              "gemm route: int64 routing table [N / 64, 3] on the operands' device");
+  float* sq = nullptr;
+  if (rowsq.has_value() && rowsq->defined()) {
+    TORCH_CHECK(rowsq->is_cuda() && rowsq->device() == a.device() && rowsq->scalar_type() == at::kFloat && rowsq->is_contiguous() && rowsq->numel() % M == 0,
+                "gemm route: rowsq must be a contiguous fp32 CUDA tensor [slots, M]");
+    sq = rowsq->data_ptr<float>();
+  }
   if (bias.has_value() && bias->defined()) { chk(*bias, "bias"); TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N, "gemm route: bf16 bias [N]"); }
   c10::cuda::CUDAGuard g(a.device());
   auto c = torch::empty({M, local_cols}, a.options());
   // the kernel addresses a local box as C + column, with C the matrix of ALL columns: shift the base so that column N - local_cols is c's first
   void* cbase = local_cols ? static_cast<void*>(static_cast<at::BFloat16*>(c.data_ptr()) - (N - local_cols)) : nullptr;
   const int rc = ub::gemm_bf16_route(a.data_ptr(), b.data_ptr(), optr(bias), cbase, (int)M, (int)N, (int)K, (int)K, (int)K, (int)(local_cols ? local_cols : 8),
-                                     route.data_ptr(), (int)rows_per_batch, gemm_status_tensor().data_ptr<int>(), stream());
+                                     route.data_ptr(), (int)rows_per_batch, sq, gemm_status_tensor().data_ptr<int>(), stream());
   TORCH_CHECK(rc == 0, "gemm_bf16_route: unsupported shape or launch failure (code ", rc, ") for M=", M, " N=", N, " K=", K);
   return c;
 }
@@ -770,7 +777,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16_tn", &gemm_bf16_tn);
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out") = py::none(),
         py::arg("accumulate") = false);
-  m.def("gemm_bf16_route", &gemm_bf16_route);
+  m.def("gemm_bf16_route", &gemm_bf16_route, py::arg("a"), py::arg("b"), py::arg("bias"), py::arg("route"), py::arg("rows_per_batch"), py::arg("local_cols"),
+        py::arg("rowsq") = py::none());
   m.def("linear_dlogits", &linear_dlogits);
   m.def("gemm_bf16_tn_skinny", &gemm_bf16_tn_skinny, py::arg("a"), py::arg("b"), py::arg("res") = py::none(), py::arg("out") = py::none(),
         py::arg("epilogue") = 0);

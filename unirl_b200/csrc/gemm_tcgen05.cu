@@ -40,10 +40,14 @@ constexpr int kGemmThreads = 192;
 
 // Destination of one 64-column box of the ROUTE epilogue: element (row, c) of the box lands at base + drow * stride + c with
 // drow = row + (row / rows_per_batch) * extra.  base == nullptr: the box goes to the ordinary C matrix at its own columns.
+// slot >= 0: the box also adds, per row, the sum of squares of its 64 values to rowsq[slot * M + row] (the statistic of an RMS norm
+// that spans all heads of a token and is applied after the exchange).
 struct RouteEntry {
   bf16* base;
   int32_t stride;
   int32_t extra;
+  int32_t slot;
+  int32_t pad;
 };
 
 struct GemmParams {
@@ -79,6 +83,7 @@ struct GemmParams {
   const RouteEntry* route;  // one entry per 64-column box of the output
   const bf16* bias;         // [N] or null, added before the store
   int rows_per_batch;       // rows of one batch element (the destination row is row + (row / rows_per_batch) * entry.extra)
+  float* rowsq;             // [slots, M] fp32, zeroed by the caller, or null
 };
 
 template <int BN>
@@ -329,6 +334,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 64) {
           if (n0 + c0 >= p.N) break;  // uniform over the warp
+          const RouteEntry e = p.route[(n0 + c0) >> 6];
+          float sq = 0.f;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             float acc[32];
@@ -349,12 +356,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int g = 0; g < 4; ++g) {
               Pack8 pk;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) pk.h[j] = __floats2bfloat162_rn(acc[g * 8 + 2 * j], acc[g * 8 + 2 * j + 1]);
+              for (int j = 0; j < 4; ++j) {
+                pk.h[j] = __floats2bfloat162_rn(acc[g * 8 + 2 * j], acc[g * 8 + 2 * j + 1]);
+                const float2 rounded = __bfloat1622float2(pk.h[j]);  // the statistic of the values as stored
+                sq += rounded.x * rounded.x + rounded.y * rounded.y;
+              }
               *reinterpret_cast<Pack8*>(sbuf + lane * 128 + (((h * 4 + g) ^ (lane & 7)) << 4)) = pk;
             }
           }
+          if (p.rowsq && e.slot >= 0 && row_ok) atomicAdd(p.rowsq + static_cast<int64_t>(e.slot) * p.M + row, sq);
           __syncwarp();
-          const RouteEntry e = p.route[(n0 + c0) >> 6];
           bf16* dbase = e.base ? e.base : p.C + n0 + c0;
           const int64_t dstride = e.base ? e.stride : p.ldc;
           const int jc = lane & 7;
@@ -683,15 +694,15 @@ int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, in
   return wide ? launch_variant<256, kEpiStore>(tmA, tmB, tmC, p, s) : launch_variant<128, kEpiStore>(tmA, tmB, tmC, p, s);
 }
 
-// C = A[M,K]·B[N,K]ᵀ + bias with every 64-column box of the result stored where `route` (device array of N / 64 entries) says.
+// C = A[M,K]·B[N,K]ᵀ + bias with every 64-column box of the result stored where `route` (device array of N / 64 entries of 24 bytes) says.
 // Boxes whose entry has no base go to C[M, ldc] (may be null when no entry needs it).  N must be a multiple of 64.
 int gemm_bf16_route(const void* A, const void* B, const void* bias, void* C, int M, int N, int K, int lda, int ldb, int ldc, const void* route,
-                    int rows_per_batch, int* status, cudaStream_t s) {
+                    int rows_per_batch, float* rowsq, int* status, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (N % 64) || (lda % 8) || (ldb % 8) || (C && (ldc % 8)) || rows_per_batch <= 0 || !route) return 1;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = static_cast<bf16*>(C); p.ldc = ldc; p.status = status;
-  p.route = static_cast<const RouteEntry*>(route); p.bias = static_cast<const bf16*>(bias); p.rows_per_batch = rows_per_batch;
+  p.route = static_cast<const RouteEntry*>(route); p.bias = static_cast<const bf16*>(bias); p.rows_per_batch = rows_per_batch; p.rowsq = rowsq;
   p.num_m_tiles = (M + BM - 1) / BM;
   const bool wide = g_force_bn ? g_force_bn == 256 : (N >= 256 * 2 || N % 256 == 0);
   const int BN = wide ? 256 : 128;

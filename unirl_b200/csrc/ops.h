@@ -101,10 +101,11 @@ int gemm_bf16_general(const void* A, const void* B, void* C, int M, int N, int K
 int linear_dlogits(const void* H, const void* W, void* dZ, int M, int Vc, int K, int ldh, int ldw, int ldz, const int* targets, const float* lse,
                    const float* gout, float temperature, int col_offset, int* status, cudaStream_t s);
 int num_sms();  // SM count of the current device (cached per device)
-// Y = A·Bᵀ + bias with every 64-column box of Y stored through a routing table (device array of N / 64 entries {bf16* base; int32 stride; int32 extra}:
-// element (row, c) of the box -> base + (row + (row / rows_per_batch) * extra) * stride + c; a null base sends the box to C[M, ldc]).
+// Y = A·Bᵀ + bias with every 64-column box of Y stored through a routing table (device array of N / 64 entries
+// {bf16* base; int32 stride; int32 extra; int32 slot; int32 pad}: element (row, c) of the box -> base + (row + (row / rows_per_batch) * extra) * stride + c;
+// a null base sends the box to C[M, ldc]; slot >= 0 adds the row's sum of squares over the box to rowsq[slot * M + row], zeroed by the caller).
 int gemm_bf16_route(const void* A, const void* B, const void* bias, void* C, int M, int N, int K, int lda, int ldb, int ldc, const void* route,
-                    int rows_per_batch, int* status, cudaStream_t s);
+                    int rows_per_batch, float* rowsq, int* status, cudaStream_t s);
 int gemm_bf16_tn(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int epilogue, int* status,
                  cudaStream_t s);
 // Decode-sized GEMM (M of a few hundred rows): one 128 x {128,144} tile per CTA, K split over a thread-block cluster and reduced

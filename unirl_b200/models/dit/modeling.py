@@ -240,15 +240,24 @@ class AttnContext:
         exchange done by the QKV projection itself: the GEMM's epilogue stores every head's columns into the rank that owns the head.
         q / k norm and the rotary embedding then run on this rank's heads over the whole sequence.  ``text_qkv``: projected, normalised
         text tokens (replicated, all heads), joined in front.  Returns ``[B, n_text + l, H, D]`` like :meth:`attend`, or None when this
-        projection cannot take the fused form (no peer memory, an adapter on the projection, a q / k norm that spans heads)."""
+        projection cannot take the fused form (no peer memory, an adapter on the projection, q / k norms of different scopes)."""
         sp = self.sp
         if sp is None or sp.size <= 1 or getattr(attn.qkv, "_lora_index", None):
             return None
         hd = attn.qkv.weight.shape[0] // (3 * attn.n)
-        if any(w is not None and w.numel() != hd for w in (attn.q_norm, attn.k_norm)) or not sp.can_scatter_project(x, attn.qkv.weight, attn.n):
+        if not sp.can_scatter_project(x, attn.qkv.weight, attn.n):
             return None
-        q, k, v = sp.scatter_project(x, attn.qkv.weight, attn.qkv.bias, attn.n).unbind(0)  # [B, P·l, H/P, D]
-        q, k = _qk_norm(q, attn.q_norm, attn.eps), _qk_norm(k, attn.k_norm, attn.eps)
+        over_heads = attn.q_norm is not None and attn.k_norm is not None and attn.q_norm.numel() == attn.n * hd and attn.k_norm.numel() == attn.n * hd
+        if over_heads and not getattr(sp, "fuse_projection_norm_over_heads", False):
+            return None
+        if over_heads:
+            # a norm over all heads of a token (WAN): its statistic comes out of the projection's epilogue, the scaling happens after the exchange
+            q, k, v = sp.scatter_project_normed(x, attn.qkv.weight, attn.qkv.bias, attn.q_norm, attn.k_norm, attn.n, attn.eps)
+        elif any(w is not None and w.numel() != hd for w in (attn.q_norm, attn.k_norm)):
+            return None
+        else:
+            q, k, v = sp.scatter_project(x, attn.qkv.weight, attn.qkv.bias, attn.n).unbind(0)  # [B, P·l, H/P, D]
+            q, k = _qk_norm(q, attn.q_norm, attn.eps), _qk_norm(k, attn.k_norm, attn.eps)
         nt = 0
         if text_qkv is not None and text_qkv[0].shape[1]:
             nt, hp = text_qkv[0].shape[1], attn.n // sp.size

@@ -275,36 +275,47 @@ class FusedHeadScatterProjection:
             cap = max(numel, 1 << 20)
             self.arena = PeerArena(self.comm, 2 * (cap * 2 + 256) + 512, self.device, self.wait_s)
             self._recv = [self.arena.take(cap, torch.bfloat16) for _ in range(2)]
+            # `take` zeroes the views with a memset queued on THIS rank's stream.  A faster peer's projection may store into them as soon as
+            # it has its own table, so every rank's memset must have run before any rank goes on (at 8 ranks a late memset wiped rows that a
+            # peer had already delivered).
+            torch.cuda.synchronize(self.device)
+            self.comm.barrier()
             self._tables.clear()
             self._flip = 0
 
     @staticmethod
-    def route_rows(peer_bases: Sequence[int], rank: int, world: int, B: int, l: int, heads: int, head_dim: int, parts: int, n_cols: int) -> List[Tuple[int, int, int]]:
-        """Routing table rows ``(address, stride, extra)`` per 64-column box for an output of ``n_cols`` columns laid out
-        ``[parts x heads x head_dim | local columns]``; ``peer_bases[p]`` is the byte address of rank ``p``'s receive buffer."""
+    def route_rows(peer_bases: Sequence[int], rank: int, world: int, B: int, l: int, heads: int, head_dim: int, parts: int, n_cols: int,
+                   stat_parts: int = 0) -> List[Tuple[int, int, int, int]]:
+        """Routing table rows ``(address, stride, extra, slot)`` per 64-column box for an output of ``n_cols`` columns laid out
+        ``[parts x heads x head_dim | local columns]``; ``peer_bases[p]`` is the byte address of rank ``p``'s receive buffer.  The boxes of
+        the first ``stat_parts`` parts also add their rows' sums of squares to statistic ``slot = part``."""
         hp = heads // world
-        rows: List[Tuple[int, int, int]] = []
+        rows: List[Tuple[int, int, int, int]] = []
         for col in range(0, n_cols, 64):
             if col >= parts * heads * head_dim:
-                rows.append((0, 0, 0))
+                rows.append((0, 0, 0, -1))
                 continue
             part, rem = divmod(col, heads * head_dim)
             head, d0 = divmod(rem, head_dim)
             dst, hl = divmod(head, hp)
             elem = part * B * world * l * hp * head_dim + rank * l * hp * head_dim + hl * head_dim + d0
-            rows.append((int(peer_bases[dst]) + 2 * elem, hp * head_dim, (world - 1) * l))
+            rows.append((int(peer_bases[dst]) + 2 * elem, hp * head_dim, (world - 1) * l, part if part < stat_parts else -1))
         return rows
 
     @staticmethod
-    def pack_table(rows: Sequence[Tuple[int, int, int]], device: Any) -> torch.Tensor:
-        return torch.tensor([[a, s | (e << 32)] for a, s, e in rows], dtype=torch.int64).to(device)
+    def pack_table(rows: Sequence[Tuple[int, ...]], device: Any) -> torch.Tensor:
+        """Rows ``(address, stride, extra[, slot])`` → the device table of 24-byte entries; ``slot`` (default -1: none) names the row-statistic a box adds to."""
+        return torch.tensor([[r[0], r[1] | (r[2] << 32), (r[3] if len(r) > 3 else -1) & 0xFFFFFFFF] for r in rows], dtype=torch.int64).to(device)
 
     def supports(self, x: torch.Tensor, weight: torch.Tensor, heads: int, head_dim: int) -> bool:
         return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and head_dim % 64 == 0 and heads % self.comm.size == 0
                 and weight.shape[0] % 64 == 0 and weight.shape[1] % 64 == 0 and x.dim() == 3 and hasattr(self._C, "gemm_bf16_route"))
 
-    def project(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int, head_dim: int, parts: int = 3) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-        """``x [B, l, K]`` → ``(recv [parts, B, P·l, Hp, D]`` — a view of a symmetric buffer that the call after next overwrites —, local columns or None)``."""
+    def project(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int, head_dim: int, parts: int = 3,
+                stat_parts: int = 0) -> Tuple[torch.Tensor, ...]:
+        """``x [B, l, K]`` → ``(recv [parts, B, P·l, Hp, D]`` — a view of a symmetric buffer that the call after next overwrites —, local columns or None)``;
+        with ``stat_parts > 0`` a third item: ``[stat_parts, B, l]`` fp32, per token of THIS rank the sum of squares over all heads of each of the
+        first ``stat_parts`` parts (what an RMS norm spanning the heads needs, gathered by the caller)."""
         world, rank = self.comm.size, self.comm.rank
         b, l, _ = x.shape
         hp, n = heads // world, weight.shape[0]
@@ -312,20 +323,22 @@ class FusedHeadScatterProjection:
         self._buffers(numel)
         buf = self._flip
         self._flip ^= 1
-        key = (buf, b, l, heads, head_dim, parts, n)
+        key = (buf, b, l, heads, head_dim, parts, n, stat_parts)
         table = self._tables.get(key)
         if table is None:
             off = self._recv[buf].data_ptr() - self.arena._buf.data_ptr()
             bases = [int(pb) + off for pb in self.arena._hdl.buffer_ptrs]
-            table = self.pack_table(self.route_rows(bases, rank, world, b, l, heads, head_dim, parts, n), x.device)
+            table = self.pack_table(self.route_rows(bases, rank, world, b, l, heads, head_dim, parts, n, stat_parts), x.device)
             self._tables[key] = table
         local_cols = n - parts * heads * head_dim
-        rest = self._C.gemm_bf16_route(x.reshape(b * l, -1).contiguous(), weight, bias, table, l, local_cols)
+        rowsq = torch.zeros(stat_parts, b * l, dtype=torch.float32, device=x.device) if stat_parts else None
+        rest = self._C.gemm_bf16_route(x.reshape(b * l, -1).contiguous(), weight, bias, table, l, local_cols, rowsq)
         _ext.count_launch()
         self.arena.barrier()  # every rank's stores into this rank's buffer have landed
         self.calls += 1
         out = self._recv[buf][:numel].view(parts, b, world * l, hp, head_dim)
-        return out, (rest.view(b, l, local_cols) if local_cols else None)
+        rest = rest.view(b, l, local_cols) if local_cols else None
+        return (out, rest, rowsq.view(stat_parts, b, l)) if stat_parts else (out, rest)
 
     def align(self) -> None:
         """End a forward pass on buffer 0.  A pass with an odd number of projections would otherwise begin its next run (a replayed CUDA graph

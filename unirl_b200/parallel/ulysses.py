@@ -108,6 +108,54 @@ class _ScatterProject(torch.autograd.Function):
         return (gx.view_as(x) if gx is not None else None), gw, gb, None, None, None, None
 
 
+class _ScatterProjectNormed(torch.autograd.Function):
+    """:class:`_ScatterProject` followed by an RMS norm of q and k that spans ALL heads of a token (WAN), applied after the exchange.
+
+    The norm's statistic — the sum of squares of a token's q (k) over every head — is accumulated by the projection's epilogue on the rank
+    that owns the token and all-gathered (two floats per token); each rank then scales its own heads: ``q · rsqrt(ss / (H·D) + eps) · w``.
+    Backward is the same norm's backward with the one cross-head reduction (``Σ_{h,d} g · w · q`` per token) summed over ranks."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, wq, wk, sp: "UlyssesContext", heads: int, head_dim: int, eps: float):
+        out, _, sq = sp._scatter.project(x, weight, bias, heads, head_dim, 3, stat_parts=2)
+        ss = torch.cat(sp.comm.all_gather(sq.contiguous()), 2)  # [2, B, P·l]: rank p's tokens at p·l + t, like the exchanged sequence
+        r = torch.rsqrt(ss / float(heads * head_dim) + eps)
+        hp = heads // sp.size
+        cols = slice(sp.rank * hp * head_dim, (sp.rank + 1) * hp * head_dim)
+        q, k, v = out.unbind(0)
+        qn = (q * r[0][..., None, None] * wq[cols].view(hp, head_dim).float()).to(q.dtype)
+        kn = (k * r[1][..., None, None] * wk[cols].view(hp, head_dim).float()).to(k.dtype)
+        ctx.sp, ctx.dims, ctx.has_bias = sp, (heads, head_dim, cols), bias is not None
+        if any(ctx.needs_input_grad[:5]):
+            ctx.save_for_backward(x, weight, q.clone(), k.clone(), r, wq, wk)
+            v = v.clone()  # the symmetric buffer is overwritten two calls later
+        return qn, kn, v
+
+    @staticmethod
+    def backward(ctx, gq: torch.Tensor, gk: torch.Tensor, gv: torch.Tensor):
+        from unirl_b200.ops.linear import linear_grads
+
+        x, weight, q, k, r, wq, wk = ctx.saved_tensors
+        sp = ctx.sp
+        heads, head_dim, cols = ctx.dims
+        hp = heads // sp.size
+        t, z, gw = [], [], []
+        for g, raw, rr, w in ((gq, q, r[0], wq), (gk, k, r[1], wk)):
+            g32, z32 = g.float(), raw.float()
+            gw.append(torch.zeros_like(w, dtype=torch.float32).index_put_((torch.arange(cols.start, cols.stop, device=w.device),),
+                                                                         (g32 * z32 * rr[..., None, None]).sum((0, 1)).flatten()).to(w.dtype))
+            t.append(g32 * w[cols].view(hp, head_dim).float())
+            z.append(z32)
+        dr = sp.comm.all_reduce(torch.stack([(t[0] * z[0]).sum((-1, -2)), (t[1] * z[1]).sum((-1, -2))]))  # [2, B, P·l], summed over the ranks' heads
+        dss = dr * (-0.5) * r.pow(3) / float(heads * head_dim)
+        graw = [(t[i] * r[i][..., None, None] + 2.0 * z[i] * dss[i][..., None, None]).to(x.dtype) for i in range(2)]
+        b, l, _ = x.shape
+        gy = torch.cat([sp._exchange(g.contiguous(), 1).reshape(b * l, -1) for g in (graw[0], graw[1], gv)], 1)
+        gx, gwt = linear_grads(gy, x.reshape(b * l, -1), weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        gb = gy.sum(0).to(weight.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return (gx.view_as(x) if gx is not None else None), gwt, gb, gw[0], gw[1], None, None, None, None
+
+
 class UlyssesContext:
     def __init__(self, comm: Comm, collectives: str = "fused"):
         self.comm = comm
@@ -118,6 +166,8 @@ class UlyssesContext:
         self._scatter: Any = None  # FusedHeadScatterProjection: the exchange inside the QKV projection's epilogue
         self._scatter_tried = False
         self.fuse_projection = os.environ.get("UNIRL_B200_ULYSSES_FUSED_QKV", "1") == "1"
+        # the variant for q / k norms that span all heads of a token (row statistics from the epilogue, norm after the exchange) is opt-in
+        self.fuse_projection_norm_over_heads = os.environ.get("UNIRL_B200_ULYSSES_FUSED_QKV_NORM_OVER_HEADS", "0") == "1"
 
     # ---- projection + exchange in one kernel --------------------------------------------------------------------
     def can_scatter_project(self, x: torch.Tensor, weight: torch.Tensor, heads: int) -> bool:
@@ -133,6 +183,11 @@ class UlyssesContext:
             except Exception:  # noqa: BLE001  (no symmetric memory on this system: projection, then exchange)
                 self._scatter = None
         return self._scatter is not None and weight.shape[0] % (3 * heads) == 0 and self._scatter.supports(x, weight, heads, weight.shape[0] // (3 * heads))
+
+    def scatter_project_normed(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], wq: torch.Tensor, wk: torch.Tensor, heads: int,
+                               eps: float):
+        """As :meth:`scatter_project`, with the q / k RMS norm that spans all heads of a token applied after the exchange → ``(q, k, v)``."""
+        return _ScatterProjectNormed.apply(x, weight, bias, wq, wk, self, heads, weight.shape[0] // (3 * heads), float(eps))
 
     def scatter_project(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int) -> torch.Tensor:
         """``x [B, l, K]`` (this rank's tokens) → ``[3, B, P·l, H/P, D]`` (all tokens, this rank's heads) in one GEMM + one rendezvous."""
