@@ -48,7 +48,9 @@ class _GlooHeadScatter:
         y = x.reshape(b * l, -1) @ weight.t()
         if bias is not None:
             y = y + bias
-        y = y.view(b, l, parts, heads, head_dim)
+        n_head_cols = parts * heads * head_dim
+        rest = y[:, n_head_cols:].reshape(b, l, -1) if y.shape[1] > n_head_cols else None
+        y = y[:, :n_head_cols].view(b, l, parts, heads, head_dim)
         sq = y[:, :, :stat_parts].float().pow(2).sum((-1, -2)).permute(2, 0, 1).contiguous() if stat_parts else None  # [stat_parts, B, l]
         out = torch.stack([_a2a_seq_to_head(y[:, :, i].contiguous(), self.comm) for i in range(parts)])
         i = self._flip
@@ -57,7 +59,7 @@ class _GlooHeadScatter:
             self._bufs[i] = torch.empty_like(out)
         self._bufs[i].copy_(out)  # reused like the symmetric receive buffers: a caller that keeps a view past the next call but one reads garbage
         self.calls += 1
-        return (self._bufs[i], None, sq) if stat_parts else (self._bufs[i], None)
+        return (self._bufs[i], rest, sq) if stat_parts else (self._bufs[i], rest)
 
 
 def _body_fused(rank, world):
@@ -68,6 +70,8 @@ def _body_fused(rank, world):
     out = {}
     for name, cfg in (("joint", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=3, num_single_blocks=0, text_dim=32, pooled_dim=24,
                                           rope_axes=(4, 6, 6), in_channels=4)),
+                      ("joint+single", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=1, num_single_blocks=2, text_dim=32, pooled_dim=24,
+                                                 rope_axes=(4, 6, 6), in_channels=4)),
                       ("joint-sincos", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=3, text_dim=32, pooled_dim=24, pos_embed="sincos2d",
                                                  pos_embed_max_size=8, dual_attention_blocks=(0,), in_channels=4)),
                       ("cross-video", DiTConfig(hidden_size=64, num_heads=4, head_dim=16, num_joint_blocks=0, num_cross_blocks=3, text_dim=32, pooled_dim=0,

@@ -22,6 +22,15 @@ from unirl_b200.types.conditions.base import Modality
 from unirl_b200.utils.dtypes import parse_torch_dtype
 
 
+def _is_image_kl(vae_dir: str) -> bool:
+    """True for the ``vae`` folder of an image checkpoint whose codec is the published 2-D KL auto-encoder (SD3 / SD3.5 / FLUX-style)."""
+    import json
+
+    with open(os.path.join(vae_dir, "config.json")) as f:
+        d = json.load(f)
+    return d.get("_class_name", "AutoencoderKL") == "AutoencoderKL" and "block_out_channels" in d
+
+
 class DiTBundle(Bundle):
     def __init__(self, transformer: DiTTransformer, text_encoders: Any, vae: LatentVAE, tokenizers: Any, config: DiTPipelineConfig, spec: FamilySpec):
         super().__init__()
@@ -87,7 +96,13 @@ class DiTBundle(Bundle):
             else:
                 encoders.append(TextEncoder(c, dtype=dtype, device=device).init_weights(config.init_seed + 1 + i))
                 toks.append(load_tokenizer(None, c.vocab_size, True))
-        vae = LatentVAE(spec.vae, device=device).init_weights(config.init_seed + 7)
+        vae_dir = None if path.startswith("random:") else os.path.join(path, "vae")
+        if vae_dir and os.path.exists(os.path.join(vae_dir, "config.json")) and _is_image_kl(vae_dir):
+            from unirl_b200.models.dit.vae_kl import AutoencoderKL
+
+            vae = AutoencoderKL.from_hf(vae_dir, device=device)  # fp32, as the codec is used
+        else:
+            vae = LatentVAE(spec.vae, device=device).init_weights(config.init_seed + 7)
         return cls(model, encoders, vae, toks, config, spec)
 
     def trainable_modules(self) -> Dict[str, torch.nn.Module]:

@@ -258,15 +258,45 @@ class AttnContext:
         else:
             q, k, v = sp.scatter_project(x, attn.qkv.weight, attn.qkv.bias, attn.n).unbind(0)  # [B, P·l, H/P, D]
             q, k = _qk_norm(q, attn.q_norm, attn.eps), _qk_norm(k, attn.k_norm, attn.eps)
+        return self._attend_head_shard(q, k, v, attn.n, text_qkv, rope)
+
+    def _attend_head_shard(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, text_qkv: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]],
+                           rope: bool) -> torch.Tensor:
+        """Attention on this rank's heads over all tokens (``q, k, v [B, P·l, H/P, D]``, already normalised) with the replicated text tokens'
+        heads sliced in front, rotary embedding from the unsharded tables, and the way back to ``[B, n_text + l, H, D]``."""
+        sp = self.sp
         nt = 0
         if text_qkv is not None and text_qkv[0].shape[1]:
-            nt, hp = text_qkv[0].shape[1], attn.n // sp.size
+            nt, hp = text_qkv[0].shape[1], heads // sp.size
             tq, tk, tv = (t[:, :, sp.rank * hp : (sp.rank + 1) * hp] for t in text_qkv)
             q, k, v = torch.cat([tq, q], 1), torch.cat([tk, k], 1), torch.cat([tv, v], 1)
         if rope and self.cos_full is not None:
             off = self.cos_full.shape[0] - q.shape[1]  # tables carry the text rows in front; a latent-only call skips them
             q, k = apply_rope(q, self.cos_full[off:], self.sin_full[off:]), apply_rope(k, self.cos_full[off:], self.sin_full[off:])
         return sp.finish(dense_attention(q, k, v), nt)
+
+    def fused_sp_single(self, blk: "SingleBlock", xn: torch.Tensor, n_text: int) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        """Single-stream block under sequence parallelism: ``xn [B, n_text + l, hidden]`` is text (replicated) in front of this rank's latent
+        tokens, and ONE projection makes q, k, v and the MLP input.  The latent rows go through the GEMM whose epilogue delivers the head
+        columns to their owners and keeps the MLP columns here; the few text rows take the ordinary projection.  Returns the attention
+        output ``[B, n_text + l, H, D]`` and the MLP input ``[B, n_text + l, mlp]``, or None when the fused form does not apply."""
+        sp, c = self.sp, blk.cfg
+        if sp is None or sp.size <= 1 or getattr(blk.in_proj, "_lora_index", None):
+            return None
+        if any(w is not None and w.numel() != c.head_dim for w in (blk.q_norm, blk.k_norm)):
+            return None
+        lat = xn[:, n_text:]
+        if not sp.can_scatter_project(lat, blk.in_proj.weight, c.num_heads, c.head_dim):
+            return None
+        qkv, m_lat = sp.scatter_project(lat, blk.in_proj.weight, blk.in_proj.bias, c.num_heads, c.head_dim)
+        q, k, v = qkv.unbind(0)
+        q, k = _qk_norm(q, blk.q_norm, c.eps), _qk_norm(k, blk.k_norm, c.eps)
+        text_qkv, m = None, m_lat
+        if n_text:
+            tq, tk, tv, m_txt = blk.in_proj(xn[:, :n_text]).split([c.hidden_size, c.hidden_size, c.hidden_size, c.mlp_dim], -1)
+            text_qkv = (_qk_norm(_heads(tq, c.num_heads), blk.q_norm, c.eps), _qk_norm(_heads(tk, c.num_heads), blk.k_norm, c.eps), _heads(tv, c.num_heads))
+            m = torch.cat([m_txt, m_lat], 1)
+        return self._attend_head_shard(q, k, v, c.num_heads, text_qkv, True), m
 
 
 class JointBlock(nn.Module):
@@ -329,12 +359,16 @@ class SingleBlock(nn.Module):
     def forward(self, x: torch.Tensor, vec: torch.Tensor, ctx: AttnContext, n_text: int) -> torch.Tensor:
         c = self.cfg
         shift, scale, gate = self.mod(F.silu(vec)).chunk(3, -1)
-        y = self.in_proj(layernorm_modulate(x, shift, scale, c.eps))
-        q, k, v, m = y.split([c.hidden_size, c.hidden_size, c.hidden_size, c.mlp_dim], -1)
-        q, k = _qk_norm(_heads(q, c.num_heads), self.q_norm, c.eps), _qk_norm(_heads(k, c.num_heads), self.k_norm, c.eps)
-        q, k = ctx.rope(q, k)
-        a = ctx.attend(q, k, _heads(v, c.num_heads), n_text).flatten(-2)
-        return x + gate.unsqueeze(1) * self.out_proj(torch.cat([a, F.gelu(m, approximate="tanh")], -1))
+        xn = layernorm_modulate(x, shift, scale, c.eps)
+        fused = ctx.fused_sp_single(self, xn, n_text)
+        if fused is not None:
+            a, m = fused
+        else:
+            q, k, v, m = self.in_proj(xn).split([c.hidden_size, c.hidden_size, c.hidden_size, c.mlp_dim], -1)
+            q, k = _qk_norm(_heads(q, c.num_heads), self.q_norm, c.eps), _qk_norm(_heads(k, c.num_heads), self.k_norm, c.eps)
+            q, k = ctx.rope(q, k)
+            a = ctx.attend(q, k, _heads(v, c.num_heads), n_text)
+        return x + gate.unsqueeze(1) * self.out_proj(torch.cat([a.flatten(-2), F.gelu(m, approximate="tanh")], -1))
 
 
 class CrossBlock(nn.Module):

@@ -88,21 +88,27 @@ class _ScatterProject(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], sp: "UlyssesContext", heads: int, head_dim: int, parts: int):
-        out, _ = sp._scatter.project(x, weight, bias, heads, head_dim, parts)
-        ctx.sp, ctx.parts, ctx.has_bias = sp, parts, bias is not None
+        out, rest = sp._scatter.project(x, weight, bias, heads, head_dim, parts)
+        ctx.sp, ctx.parts, ctx.has_bias, ctx.has_rest = sp, parts, bias is not None, rest is not None
         if any(ctx.needs_input_grad[:3]):
             ctx.save_for_backward(x, weight)
-            return out.clone()  # the symmetric buffer is overwritten two calls later; what autograd keeps must not live there
-        return out
+            out = out.clone()  # the symmetric buffer is overwritten two calls later; what autograd keeps must not live there
+        if rest is None:  # columns past the head parts (the MLP half of a single-stream block's one projection) stay on this rank
+            rest = out.new_zeros(0)
+            ctx.mark_non_differentiable(rest)
+        return out, rest
 
     @staticmethod
-    def backward(ctx, g: torch.Tensor):
+    def backward(ctx, g: torch.Tensor, g_rest: Optional[torch.Tensor]):
         from unirl_b200.ops.linear import linear_grads
 
         x, weight = ctx.saved_tensors
         sp = ctx.sp
         b, l, _ = x.shape
-        gy = torch.cat([sp._exchange(g[i].contiguous(), 1).reshape(b * l, -1) for i in range(ctx.parts)], 1)  # [B·l, parts·H·D]
+        cols = [sp._exchange(g[i].contiguous(), 1).reshape(b * l, -1) for i in range(ctx.parts)]  # [B·l, H·D] each
+        if ctx.has_rest:
+            cols.append(g_rest.reshape(b * l, -1) if g_rest is not None else x.new_zeros(b * l, weight.shape[0] - sum(c.shape[1] for c in cols)))
+        gy = torch.cat(cols, 1)
         gx, gw = linear_grads(gy, x.reshape(b * l, -1), weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
         gb = gy.sum(0).to(weight.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return (gx.view_as(x) if gx is not None else None), gw, gb, None, None, None, None
@@ -170,8 +176,9 @@ class UlyssesContext:
         self.fuse_projection_norm_over_heads = os.environ.get("UNIRL_B200_ULYSSES_FUSED_QKV_NORM_OVER_HEADS", "0") == "1"
 
     # ---- projection + exchange in one kernel --------------------------------------------------------------------
-    def can_scatter_project(self, x: torch.Tensor, weight: torch.Tensor, heads: int) -> bool:
-        """True when the QKV projection of ``x [B, l, K]`` can run as the GEMM whose epilogue stores head tiles to their owners."""
+    def can_scatter_project(self, x: torch.Tensor, weight: torch.Tensor, heads: int, head_dim: Optional[int] = None) -> bool:
+        """True when the QKV projection of ``x [B, l, K]`` can run as the GEMM whose epilogue stores head tiles to their owners.
+        ``head_dim``: given when the weight has more rows than ``3 · heads · head_dim`` (trailing columns that stay local)."""
         if not (self.fuse_projection and self.collectives == "fused" and self.size > 1 and x.dim() == 3):
             return False
         if not self._scatter_tried and x.is_cuda:
@@ -182,16 +189,22 @@ class UlyssesContext:
                 self._scatter = make_fused_head_scatter(self.comm, x.device)
             except Exception:  # noqa: BLE001  (no symmetric memory on this system: projection, then exchange)
                 self._scatter = None
-        return self._scatter is not None and weight.shape[0] % (3 * heads) == 0 and self._scatter.supports(x, weight, heads, weight.shape[0] // (3 * heads))
+        if head_dim is None:
+            if weight.shape[0] % (3 * heads):
+                return False
+            head_dim = weight.shape[0] // (3 * heads)
+        return self._scatter is not None and weight.shape[0] >= 3 * heads * head_dim and self._scatter.supports(x, weight, heads, head_dim)
 
     def scatter_project_normed(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], wq: torch.Tensor, wk: torch.Tensor, heads: int,
                                eps: float):
         """As :meth:`scatter_project`, with the q / k RMS norm that spans all heads of a token applied after the exchange → ``(q, k, v)``."""
         return _ScatterProjectNormed.apply(x, weight, bias, wq, wk, self, heads, weight.shape[0] // (3 * heads), float(eps))
 
-    def scatter_project(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int) -> torch.Tensor:
-        """``x [B, l, K]`` (this rank's tokens) → ``[3, B, P·l, H/P, D]`` (all tokens, this rank's heads) in one GEMM + one rendezvous."""
-        return _ScatterProject.apply(x, weight, bias, self, heads, weight.shape[0] // (3 * heads), 3)
+    def scatter_project(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int, head_dim: Optional[int] = None):
+        """``x [B, l, K]`` (this rank's tokens) → ``[3, B, P·l, H/P, D]`` (all tokens, this rank's heads) in one GEMM + one rendezvous.
+        With ``head_dim`` given and more weight rows than ``3 · heads · head_dim``: ``(that, local [B, l, rest])``."""
+        out, rest = _ScatterProject.apply(x, weight, bias, self, heads, head_dim or weight.shape[0] // (3 * heads), 3)
+        return out if head_dim is None else (out, rest)
 
     def _exchange(self, x: torch.Tensor, mode: int) -> torch.Tensor:
         """Sequence shard → head shard (``mode 0``) or back (``mode 1``), on the peer-memory kernel when the tensors allow it."""
