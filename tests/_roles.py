@@ -41,3 +41,12 @@ class Echo(Remote):
     @distributed
     def square(self, x):
         return x * x
+
+    @distributed
+    def combine(self, a, b, c):
+        """Three row-aligned inputs (two fp32, one int64): what a consumer of several fields of one producer looks like."""
+        return a + 10.0 * b + c.to(a.dtype)
+
+    @distributed
+    def three(self, x):
+        return {"a": x, "b": x * 2.0, "c": (x * 3.0).long()}

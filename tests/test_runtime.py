@@ -90,6 +90,12 @@ def test_mp_pool_collectives_errors_and_timeouts():
         assert [r.owner for r in out["y"].refs] == [0, 1]
         got = solo.run(out["y"])["y"].local().flatten().tolist()  # worker 0's rows hop to worker 1 over gloo
         assert got == [0.0, 3.0, 9.0, 12.0]
+        # three fields of one producer consumed on another worker: they travel as one message per dtype, not one per tensor
+        f = c.three(torch.arange(4.0).view(4, 1))
+        before = pool.store_stats()[0]["messages_sent"]
+        got = solo.combine(f["a"], f["b"], f["c"]).local().flatten().tolist()
+        assert got == [0.0, 24.0, 48.0, 72.0]
+        assert pool.store_stats()[0]["messages_sent"] - before == 2  # fp32 rows of a and b together, int64 rows of c
         with pytest.raises(WorkerError, match="boom from rank"):
             c.boom()
         with pytest.raises(WorkerTimeout, match="stall"):

@@ -19,7 +19,7 @@ import multiprocessing as mp
 import os
 import time
 import weakref
-from typing import Any, Callable, Dict, List, Optional, Sequence, Set
+from typing import Any, Callable, Dict, List, Optional, Sequence, Set, Tuple
 
 import torch
 
@@ -336,23 +336,27 @@ class DevicePool:
     def move(self, hops: Sequence[tuple]) -> Dict[tuple, TensorRef]:
         """Execute ``(src, dst, ref)`` hops; returns ``{(*ref.ident, dst): new_ref}``."""
         mapping: Dict[tuple, TensorRef] = {}
-        for src, dst, ref in hops:
+        pairs: Dict[Tuple[int, int], List[TensorRef]] = {}
+        for src, dst, ref in hops:  # everything between the same two workers travels together (one message per dtype)
+            pairs.setdefault((src, dst), []).append(ref)
+        for (src, dst), refs in pairs.items():
             if self.backend == "spmd":
                 new = None
                 if self.my_rank == src:
-                    self.local_worker.transport.send(ref, dst)
+                    self.local_worker.transport.send_many(refs, dst)
                 if self.my_rank == dst:
-                    new = self.local_worker.transport.recv(ref, src)
+                    new = self.local_worker.transport.recv_many(refs, src)
                 new = self.world_comm.broadcast_object(new, src=dst)
             elif self.backend == "inline":
-                self.workers[src].submit("transport_op", "send", ref, dst).result()
-                new = self.workers[dst].submit("transport_op", "recv", ref, src).result()
+                self.workers[src].submit("transport_op", "send_many", refs, dst).result()
+                new = self.workers[dst].submit("transport_op", "recv_many", refs, src).result()
             else:
-                fs = self.workers[src].submit("transport_op", "send", ref, dst)
-                fr = self.workers[dst].submit("transport_op", "recv", ref, src)
+                fs = self.workers[src].submit("transport_op", "send_many", refs, dst)
+                fr = self.workers[dst].submit("transport_op", "recv_many", refs, src)
                 fs.result()
                 new = fr.result()
-            mapping[(*ref.ident, dst)] = self.adopt(new)
+            for ref, n in zip(refs, new):
+                mapping[(*ref.ident, dst)] = self.adopt(n)
         return mapping
 
     def fetch(self, refs: Sequence[TensorRef]) -> torch.Tensor:

@@ -294,7 +294,7 @@ class TensorTransport(abc.ABC):
             s.release()
 
 
-REMOTE_OPS = frozenset({"incref", "decref", "send", "recv", "get_cpu", "tensor_op", "stats", "clear"})
+REMOTE_OPS = frozenset({"incref", "decref", "send", "recv", "send_many", "recv_many", "get_cpu", "tensor_op", "stats", "clear"})
 
 
 class WorkerLocalTransport(TensorTransport):
@@ -352,6 +352,37 @@ class WorkerLocalTransport(TensorTransport):
         self.comm.recv(buf, src)
         return self.store.put(buf)
 
+    # Several refs between the same two workers travel as ONE message per (dtype, device kind): the rows are packed into a flat buffer on
+    # the sender and handed out as views of the received buffer (one NCCL / gloo launch per pair instead of one per tensor).
+    @staticmethod
+    def _pack_groups(refs: Sequence[TensorRef]) -> List[Tuple[Tuple[torch.dtype, bool], List[int]]]:
+        groups: Dict[Tuple[torch.dtype, bool], List[int]] = {}
+        for i, r in enumerate(refs):
+            groups.setdefault((r.dtype, r.device.startswith("cuda")), []).append(i)
+        return list(groups.items())
+
+    def send_many(self, refs: Sequence[TensorRef], dst: int) -> int:
+        """Returns the number of messages sent."""
+        n = 0
+        for _key, idx in self._pack_groups(refs):
+            parts = [self._resolve(refs[i]).contiguous().reshape(-1) for i in idx]
+            self.comm.send(parts[0] if len(parts) == 1 else torch.cat(parts), dst)
+            n += 1
+        self.messages_sent = getattr(self, "messages_sent", 0) + n
+        return n
+
+    def recv_many(self, refs: Sequence[TensorRef], src: int) -> List[TensorRef]:
+        out: List[Optional[TensorRef]] = [None] * len(refs)
+        for (dtype, on_cuda), idx in self._pack_groups(refs):
+            sizes = [int(torch.Size(refs[i].shape).numel()) for i in idx]
+            buf = torch.empty(sum(sizes), dtype=dtype, device=self.device if on_cuda else torch.device("cpu"))
+            self.comm.recv(buf, src)
+            off = 0
+            for i, n in zip(idx, sizes):
+                out[i] = self.store.put(buf[off : off + n].view(refs[i].shape))
+                off += n
+        return out  # type: ignore[return-value]
+
     def get_cpu(self, ref: TensorRef) -> torch.Tensor:
         return self._resolve(ref).detach().cpu()
 
@@ -368,7 +399,7 @@ class WorkerLocalTransport(TensorTransport):
         return self.store.put(out)
 
     def stats(self) -> Dict[str, int]:
-        return {"tensors": len(self.store), "bytes": self.store.nbytes()}
+        return {"tensors": len(self.store), "bytes": self.store.nbytes(), "messages_sent": getattr(self, "messages_sent", 0)}
 
     def clear(self) -> None:
         self.store.clear()
