@@ -157,14 +157,57 @@ class _Lin(nn.Module):
         self.weight = nn.Parameter(torch.empty(o, i, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(o, dtype=dtype, device=device)) if bias else None
         self._targets = dict(targets or {})
+        # tensor parallelism (sampler only): "col" = this rank keeps the output features ``tp_index`` (rows of the weight, entries of the
+        # bias); "row" = it keeps the input features ``tp_index`` (columns) and the partial outputs are summed over the ranks
+        self.tp: Optional[Any] = None
+        self.tp_mode: Optional[str] = None
+        self.tp_index: Optional[torch.Tensor] = None
+        self._targets_full: Dict[str, Tuple[int, int]] = {}
 
     def lora_targets(self) -> Dict[str, Tuple[str, int, int]]:
         return {name: ("weight", off, rows) for name, (off, rows) in self._targets.items()}
+
+    def shard(self, tp: Any, mode: str, index: torch.Tensor) -> None:
+        """Keep this rank's slice of the weight in place (``index`` ascending)."""
+        with torch.no_grad():
+            idx = index.to(self.weight.device)
+            self.weight = nn.Parameter(self.weight.data.index_select(0 if mode == "col" else 1, idx).contiguous(), requires_grad=False)
+            if mode == "col" and self.bias is not None:
+                self.bias = nn.Parameter(self.bias.data.index_select(0, idx).contiguous(), requires_grad=False)
+        self.tp, self.tp_mode, self.tp_index = tp, mode, index.cpu()
+        self._targets_full = dict(self._targets)
+        if mode == "col":  # adapter-addressable row ranges move with the rows that were kept
+            kept, off = {}, 0
+            for name, (o, rows) in sorted(self._targets.items(), key=lambda kv: kv[1][0]):
+                n = int(((self.tp_index >= o) & (self.tp_index < o + rows)).sum())
+                kept[name] = (off, n)
+                off += n
+            self._targets = kept
+
+    def tp_slice(self, leaf: str, t: torch.Tensor) -> torch.Tensor:
+        """This rank's part of a full tensor arriving for parameter ``leaf`` (``weight`` / ``bias``) or for an adapter factor
+        ``<target>.lora_A`` ``[r, in]`` / ``<target>.lora_B`` ``[rows of the target, r]``."""
+        if self.tp_mode is None:
+            return t
+        idx = self.tp_index.to(t.device)
+        if leaf == "weight":
+            return t.index_select(0 if self.tp_mode == "col" else 1, idx)
+        if leaf == "bias":
+            return t.index_select(0, idx) if self.tp_mode == "col" else t
+        target, _, factor = leaf.rpartition(".")
+        if self.tp_mode == "row":
+            return t.index_select(1, idx) if factor == "lora_A" else t
+        if factor == "lora_B":
+            o, rows = self._targets_full[target]
+            return t.index_select(0, idx[(idx >= o) & (idx < o + rows)] - o)
+        return t
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = linear(x, self.weight)
         if getattr(self, "_lora_index", None):
             y = lora_apply(self, "weight", x, y)
+        if self.tp_mode == "row":
+            y = self.tp.reduce(y)
         return y if self.bias is None else y + self.bias
 
 
@@ -172,13 +215,40 @@ def _heads(x: torch.Tensor, n: int) -> torch.Tensor:
     return x.unflatten(-1, (n, -1))
 
 
-def _qk_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
-    """RMS norm of ``x [..., heads, head_dim]``: per head when ``w`` has ``head_dim`` entries, over all heads jointly when it has ``heads * head_dim``."""
+def _qk_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, tp: Optional[Any] = None) -> torch.Tensor:
+    """RMS norm of ``x [..., heads, head_dim]``: per head when ``w`` has ``head_dim`` entries, over all heads jointly when it has ``heads * head_dim``.
+    Under tensor parallelism ``x`` holds this rank's heads and ``w`` their scales; a norm over all heads sums its statistic over the ranks."""
     if w is None:
         return x
     if w.numel() != x.shape[-1]:
+        if tp is not None and tp.size > 1:
+            ss = tp.reduce(x.float().pow(2).sum((-1, -2)))
+            r = torch.rsqrt(ss / float(w.numel() * tp.size) + eps)
+            return (x.float() * r[..., None, None] * w.float().view(x.shape[-2], x.shape[-1])).to(x.dtype)
         return rmsnorm(x.reshape(-1, w.numel()), w, eps).view_as(x)
     return rmsnorm(x.reshape(-1, x.shape[-1]), w, eps).view_as(x)
+
+
+def _head_rows(offset: int, heads: int, head_dim: int, tp: Any) -> torch.Tensor:
+    """Rows ``offset + [rank · H/P · D, (rank + 1) · H/P · D)``: the heads a tensor-parallel rank owns inside one part of a fused projection."""
+    if heads % tp.size:
+        raise ValueError(f"{heads} heads do not split over {tp.size} tensor-parallel ranks")
+    n = heads // tp.size * head_dim
+    return torch.arange(offset + tp.rank * n, offset + (tp.rank + 1) * n)
+
+
+def _even_rows(offset: int, width: int, tp: Any) -> torch.Tensor:
+    if width % tp.size:
+        raise ValueError(f"a width of {width} does not split over {tp.size} tensor-parallel ranks")
+    n = width // tp.size
+    return torch.arange(offset + tp.rank * n, offset + (tp.rank + 1) * n)
+
+
+def _shard_norm(p: Optional[nn.Parameter], heads: int, head_dim: int, tp: Any) -> Optional[nn.Parameter]:
+    """A q / k norm scale over all heads keeps the entries of this rank's heads; a per-head scale is shared and stays whole."""
+    if p is None or p.numel() == head_dim:
+        return p
+    return nn.Parameter(p.data[_head_rows(0, heads, head_dim, tp).to(p.device)].contiguous(), requires_grad=False)
 
 
 def _qk_norm_param(cfg: "DiTConfig", dtype: Any, device: Any) -> Optional[nn.Parameter]:
@@ -197,10 +267,21 @@ class _Attn(nn.Module):
         self.q_norm, self.k_norm = _qk_norm_param(cfg, dtype, device), _qk_norm_param(cfg, dtype, device)
         self.out = _Lin(h, h, True, dtype, device, {names[3]: (0, h)}) if out_proj else None
         self.n, self.eps = cfg.num_heads, cfg.eps
+        self.tp: Optional[Any] = None
 
     def project(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         q, k, v = self.qkv(x).chunk(3, -1)
-        return _qk_norm(_heads(q, self.n), self.q_norm, self.eps), _qk_norm(_heads(k, self.n), self.k_norm, self.eps), _heads(v, self.n)
+        return _qk_norm(_heads(q, self.n), self.q_norm, self.eps, self.tp), _qk_norm(_heads(k, self.n), self.k_norm, self.eps, self.tp), _heads(v, self.n)
+
+    def shard(self, tp: Any) -> None:
+        """Tensor parallelism over heads: q / k / v rows of this rank's heads, the matching columns of the output projection."""
+        h = self.qkv.weight.shape[0] // 3
+        d = h // self.n
+        self.qkv.shard(tp, "col", torch.cat([_head_rows(o, self.n, d, tp) for o in (0, h, 2 * h)]))
+        if self.out is not None:
+            self.out.shard(tp, "row", _head_rows(0, self.n, d, tp))
+        self.q_norm, self.k_norm = _shard_norm(self.q_norm, self.n, d, tp), _shard_norm(self.k_norm, self.n, d, tp)
+        self.n, self.tp = self.n // tp.size, tp
 
 
 class _MLP(nn.Module):
@@ -211,6 +292,11 @@ class _MLP(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.fc2(F.gelu(self.fc1(x), approximate="tanh"))
+
+    def shard(self, tp: Any) -> None:
+        idx = _even_rows(0, self.fc1.weight.shape[0], tp)
+        self.fc1.shard(tp, "col", idx)
+        self.fc2.shard(tp, "row", idx)
 
 
 class AttnContext:
@@ -314,6 +400,11 @@ class JointBlock(nn.Module):
         self.img_mlp = _MLP(cfg, dtype, device)
         self.txt_mlp = _MLP(cfg, dtype, device, ("ff_context.net.0.proj", "ff_context.net.2")) if self.update_text else None
 
+    def shard(self, tp: Any) -> None:
+        for m in (self.img_attn, self.txt_attn, self.img_attn2, self.img_mlp, self.txt_mlp):
+            if m is not None:
+                m.shard(tp)
+
     def forward(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor, ctx: AttnContext) -> Tuple[torch.Tensor, torch.Tensor]:
         eps = self.cfg.eps
         im = self.img_mod(F.silu(vec)).chunk(9 if self.dual else 6, -1)
@@ -355,6 +446,15 @@ class SingleBlock(nn.Module):
         self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
         self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device)) if cfg.qk_norm else None
         self.out_proj = _Lin(h + m, h, True, dtype, device, {"proj_out": (0, h)})
+        self.n, self.hq, self.mq = cfg.num_heads, h, m  # heads, attention width and MLP width held by this rank
+
+    def shard(self, tp: Any) -> None:
+        c = self.cfg
+        h, m, d = c.hidden_size, c.mlp_dim, c.head_dim
+        mlp = _even_rows(0, m, tp)
+        self.in_proj.shard(tp, "col", torch.cat([_head_rows(o, c.num_heads, d, tp) for o in (0, h, 2 * h)] + [3 * h + mlp]))
+        self.out_proj.shard(tp, "row", torch.cat([_head_rows(0, c.num_heads, d, tp), h + mlp]))
+        self.n, self.hq, self.mq = c.num_heads // tp.size, h // tp.size, m // tp.size
 
     def forward(self, x: torch.Tensor, vec: torch.Tensor, ctx: AttnContext, n_text: int) -> torch.Tensor:
         c = self.cfg
@@ -364,10 +464,10 @@ class SingleBlock(nn.Module):
         if fused is not None:
             a, m = fused
         else:
-            q, k, v, m = self.in_proj(xn).split([c.hidden_size, c.hidden_size, c.hidden_size, c.mlp_dim], -1)
-            q, k = _qk_norm(_heads(q, c.num_heads), self.q_norm, c.eps), _qk_norm(_heads(k, c.num_heads), self.k_norm, c.eps)
+            q, k, v, m = self.in_proj(xn).split([self.hq, self.hq, self.hq, self.mq], -1)
+            q, k = _qk_norm(_heads(q, self.n), self.q_norm, c.eps), _qk_norm(_heads(k, self.n), self.k_norm, c.eps)
             q, k = ctx.rope(q, k)
-            a = ctx.attend(q, k, _heads(v, c.num_heads), n_text)
+            a = ctx.attend(q, k, _heads(v, self.n), n_text)
         return x + gate.unsqueeze(1) * self.out_proj(torch.cat([a.flatten(-2), F.gelu(m, approximate="tanh")], -1))
 
 
@@ -384,6 +484,18 @@ class CrossBlock(nn.Module):
         self.cross_out = _Lin(h, h, True, dtype, device, {"attn2.to_out.0": (0, h)})
         self.cross_norm = nn.LayerNorm(h, eps=cfg.eps, dtype=dtype, device=device)
         self.mlp = _MLP(cfg, dtype, device)
+        self.n, self.tp = cfg.num_heads, None
+
+    def shard(self, tp: Any) -> None:
+        c = self.cfg
+        h, d = c.hidden_size, c.head_dim
+        self.self_attn.shard(tp)
+        self.cross_q.shard(tp, "col", _head_rows(0, c.num_heads, d, tp))
+        self.cross_kv.shard(tp, "col", torch.cat([_head_rows(0, c.num_heads, d, tp), _head_rows(h, c.num_heads, d, tp)]))
+        self.cross_out.shard(tp, "row", _head_rows(0, c.num_heads, d, tp))
+        self.cross_q_norm, self.cross_k_norm = _shard_norm(self.cross_q_norm, c.num_heads, d, tp), _shard_norm(self.cross_k_norm, c.num_heads, d, tp)
+        self.mlp.shard(tp)
+        self.n, self.tp = c.num_heads // tp.size, tp
 
     def forward(self, img: torch.Tensor, txt: torch.Tensor, tproj: torch.Tensor, ctx: AttnContext) -> torch.Tensor:
         c = self.cfg
@@ -395,11 +507,11 @@ class CrossBlock(nn.Module):
             q, k = ctx.rope(q, k)
             a = ctx.attend(q, k, v, 0)
         img = img + m[2].unsqueeze(1) * self.self_attn.out(a.flatten(-2))
-        xq = _qk_norm(_heads(self.cross_q(self.cross_norm(img)), c.num_heads), self.cross_q_norm, c.eps)
+        xq = _qk_norm(_heads(self.cross_q(self.cross_norm(img)), self.n), self.cross_q_norm, c.eps, self.tp)
         xk, xv = self.cross_kv(txt).chunk(2, -1)
-        xk = _qk_norm(_heads(xk, c.num_heads), self.cross_k_norm, c.eps)
+        xk = _qk_norm(_heads(xk, self.n), self.cross_k_norm, c.eps, self.tp)
         mask = None if ctx.text_mask is None else ctx.text_mask[:, None, None, :].bool()
-        a = F.scaled_dot_product_attention(xq.transpose(1, 2), xk.transpose(1, 2), _heads(xv, c.num_heads).transpose(1, 2), attn_mask=mask)
+        a = F.scaled_dot_product_attention(xq.transpose(1, 2), xk.transpose(1, 2), _heads(xv, self.n).transpose(1, 2), attn_mask=mask)
         img = img + self.cross_out(a.transpose(1, 2).flatten(-2))
         return img + m[5].unsqueeze(1) * self.mlp(layernorm_modulate(img, m[3], m[4], c.eps))
 
@@ -414,6 +526,7 @@ class DiTTransformer(nn.Module):
                  sp: Optional[Any] = None):
         super().__init__()
         self.cfg, self.sp, self.gradient_checkpointing = cfg, sp, gradient_checkpointing
+        self.tp: Optional[Any] = None  # set by apply_tensor_parallel
         self.checkpoint_layers: Optional[int] = None  # recompute only the first N blocks in backward (None = all): 180 GB of HBM holds the rest
         h = cfg.hidden_size
         self.patch_embed = _Lin(cfg.patch_dim, h, True, dtype, device)
@@ -545,6 +658,45 @@ class DiTTransformer(nn.Module):
             out = sp.gather_sequence(out)
             sp.end_forward()
         return self.unpatchify(out, grid, video)
+
+    # ---- tensor parallelism (sampler) --------------------------------------------------------------------
+    def apply_tensor_parallel(self, tp: Any) -> "DiTTransformer":
+        """Shard every block over the heads / MLP width of ``tp`` (``rank``, ``size``, ``reduce``) in place: QKV, the MLP's first layer and
+        the cross-attention projections keep this rank's output features, the output projections and the MLP's second layer its input
+        features with their partial results summed over the ranks; embedders, modulation layers and the final layer stay whole.
+        Inference only.  Call after the full weights are in place; :meth:`tp_slice` cuts tensors that arrive later."""
+        if tp is None or tp.size <= 1:
+            return self
+        if self.sp is not None and getattr(self.sp, "size", 1) > 1:
+            raise ValueError("tensor and sequence parallelism of one DiT replica are not combined")
+        for blk in [*self.joint_blocks, *self.single_blocks, *self.cross_blocks]:
+            blk.shard(tp)
+        self.tp = tp
+        return self.requires_grad_(False).eval()
+
+    def tp_slice(self, name: str, t: torch.Tensor) -> torch.Tensor:
+        """This rank's part of the FULL tensor ``t`` of parameter ``name`` (or of a LoRA factor ``<module>.<target>.lora_{A,B}…``); tensors of
+        modules that are not sharded come back whole."""
+        if getattr(self, "tp", None) is None:
+            return t
+        mods = dict(self.named_modules())
+        parts = name.split(".")
+        for cut in range(len(parts) - 1, 0, -1):
+            mod = mods.get(".".join(parts[:cut]))
+            if isinstance(mod, _Lin):
+                leaf = ".".join(parts[cut:])
+                if ".lora_" in "." + leaf:  # "<target>.lora_A.<adapter>.weight" -> "<target>.lora_A"
+                    bits = leaf.split(".")
+                    k = next(i for i, b in enumerate(bits) if b.startswith("lora_"))
+                    leaf = ".".join(bits[: k + 1])
+                return mod.tp_slice(leaf, t)
+            if isinstance(mod, (_Attn, CrossBlock)) and parts[cut] in ("q_norm", "k_norm", "cross_q_norm", "cross_k_norm") and cut == len(parts) - 1:
+                own = getattr(mod, parts[cut])
+                if own is not None and own.numel() != t.numel():
+                    n_full = (mod.n if isinstance(mod, _Attn) else mod.n) * self.tp.size
+                    return t[_head_rows(0, n_full, t.numel() // n_full, self.tp).to(t.device)]
+                return t
+        return t
 
     def lora_target_modules(self, patterns: Sequence[str] = ("qkv", "out", "fc1", "fc2", "in_proj", "out_proj", "cross_q", "cross_kv", "cross_out")) -> List[str]:
         """Dotted names of the ``_Lin`` modules a LoRA recipe may wrap (attention and MLP projections inside blocks)."""

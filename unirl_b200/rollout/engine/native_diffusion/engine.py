@@ -47,6 +47,7 @@ class NativeDiffusionEngineConfig:
     use_cuda_graph: bool = True
     verify_sigmas: bool = True
     init_seed: int = 0
+    tp_size: int = 1  # tensor-parallel ranks per sampler replica (heads and MLP width of every block split; needs weights of the engine's own)
     pipeline_overrides: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -128,6 +129,17 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
                 # base weights only: adapters arrive through set_lora_from_tensors
                 self._load_named({n: p.detach() for n, p in self._trainer_pipeline.bundle.transformer.named_parameters() if ".lora." not in n})
             self.pipeline.bundle.transformer.eval().requires_grad_(False)
+        ri = self.rank_info
+        tp = max(int(c.tp_size), int(getattr(ri, "tp_size", 1) or 1))
+        if tp > 1:
+            if self._shares_trainer:
+                raise ValueError("a tensor-parallel sampler needs weights of its own: set share_trainer_weights=false")
+            if int(getattr(ri, "tp_size", 1) or 1) != tp:
+                raise ValueError(f"engine config tp_size={c.tp_size} but the handle was created with tp={ri.tp_size}; pass rollout_parallel={{tp: {c.tp_size}}}")
+            from unirl_b200.models.qwen3.modeling import TPContext
+
+            self.tp_comm = self.comm.split([list(range(g * tp, (g + 1) * tp)) for g in range(ri.world_size // tp)])
+            self.pipeline.bundle.transformer.apply_tensor_parallel(TPContext(ri.tp_rank, tp, lambda t: self.tp_comm.all_reduce(t)))
         self.schedule_policy = self.pipeline.build_schedule_policy()
         if c.use_cuda_graph and torch.device(self.device or "cpu").type == "cuda":
             self._graphed = GraphedVelocity(self.pipeline.diffusion)
@@ -222,13 +234,16 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
     # ---- weight receive ---------------------------------------------------------------------------------------
     def _load_named(self, named: Dict[str, torch.Tensor], prefix: str = "transformer.") -> int:
         self._stale.add("transformer")
-        params = dict(self.pipeline.bundle.transformer.named_parameters())
+        model = self.pipeline.bundle.transformer
+        params = dict(model.named_parameters())
         n = 0
         with torch.no_grad():
             for k, v in named.items():
                 k = k[len(prefix):] if k.startswith(prefix) else k
                 if k not in params:
                     raise KeyError(f"weight {k!r} does not exist in the engine's transformer")
+                if getattr(model, "tp", None) is not None:
+                    v = model.tp_slice(k, v)  # full tensors arrive; a tensor-parallel rank keeps its heads / its part of the MLP width
                 params[k].data.copy_(v.to(params[k].device, params[k].dtype))
                 n += 1
         return n
@@ -291,6 +306,8 @@ class NativeDiffusionRolloutEngine(BaseRolloutEngine):
             for k, v in lora_tensors.items():
                 k = k[len("base_model.model."):] if k.startswith("base_model.model.") else k
                 if k in own:
+                    if getattr(model, "tp", None) is not None:
+                        v = model.tp_slice(k, v)
                     own[k].data.copy_(v.to(own[k].device, own[k].dtype))
                     n += 1
         self.weight_version += 1
