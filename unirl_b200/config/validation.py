@@ -75,19 +75,23 @@ def validate_algorithm_horizon(cfg: Any) -> None:
 
 
 def validate_train_topology(cfg: Any) -> None:
-    """Parallel degrees the trainers do not execute are refused up front instead of being silently ignored: pipeline stages
-    (the dispatch layer rejects them for auto-backward anyway) and context parallelism (the attention component exists, no
-    trainer shards tokens over it yet).  Sequence parallelism must divide the device count and the DiT's head count."""
+    """Parallel degrees the trainers do not execute are refused up front instead of being silently ignored: pipeline stages (the
+    dispatch layer rejects them for auto-backward anyway).  Sequence parallelism (DiT) and context parallelism (autoregressive replay)
+    share the placement dimension ``train_parallel.sp``: the ranks of such a group receive the same samples; the backend option
+    (``fsdp_cfg.sp_size`` or ``fsdp_cfg.cp_size``) says which of the two the model runs.  The degree must divide the device count."""
     for key in ("train_parallel.pp", "train_parallel.cp", "backend.topology.pp_size", "backend.topology.cp_size"):
         v = _get(cfg, key)
         if v is not None and int(v) > 1:
-            raise ConfigValidationError(f"{key}={v}: this degree is not executed by any trainer (use dp / sp / tp / ep)")
+            raise ConfigValidationError(f"{key}={v}: this degree is not executed by any trainer (use dp / sp / tp / ep; context parallelism is "
+                                        "backend.fsdp_cfg.cp_size with train_parallel.sp)")
     sp = int(_get(cfg, "train_parallel.sp", 1))
     if sp > 1 and int(_get(cfg, "num_devices", 1)) % sp:
         raise ConfigValidationError(f"train_parallel.sp={sp} does not divide num_devices={_get(cfg, 'num_devices', 1)}")
-    fs = int(_get(cfg, "backend.fsdp_cfg.sp_size", 1) or 1)
-    if fs != sp and (fs > 1 or sp > 1):
-        raise ConfigValidationError(f"backend.fsdp_cfg.sp_size={fs} but train_parallel.sp={sp}")
+    fs, fc = int(_get(cfg, "backend.fsdp_cfg.sp_size", 1) or 1), int(_get(cfg, "backend.fsdp_cfg.cp_size", 1) or 1)
+    if fs > 1 and fc > 1:
+        raise ConfigValidationError("backend.fsdp_cfg.sp_size and cp_size are not combined")
+    if max(fs, fc) != sp and (max(fs, fc) > 1 or sp > 1):
+        raise ConfigValidationError(f"backend.fsdp_cfg.sp_size={fs} / cp_size={fc} but train_parallel.sp={sp}")
 
 
 VALIDATORS: List[Callable[[Any], None]] = [validate_train_topology, validate_batch_geometry, validate_rollout_parallelism, validate_sampling_consistency, validate_lora_sync,

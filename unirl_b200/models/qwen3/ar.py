@@ -129,12 +129,49 @@ class Qwen3ARStage:
         responses = [segment.tokens[cu[i] : cu[i + 1]] for i in range(len(cu) - 1)]
         if len(prompts) != len(responses):
             raise ValueError(f"replay: {len(prompts)} prompts vs {len(responses)} responses")
+        cp = getattr(model, "cp", None)
+        if cp is not None and cp.size > 1:
+            return self._replay_context_parallel(prompts, responses, cp, float(temperature))
         tokens, positions, cu_dev, max_len, pred_index, targets = build_replay_batch(prompts, responses, device)
         if not targets.numel():
             return torch.zeros(0, dtype=torch.float32, device=device)
         lens = [int(p.numel()) + int(r.numel()) for p, r in zip(prompts, responses)]
         hidden = model(tokens, AttnMeta(mode="train", positions=positions, cu_seqlens=cu_dev, max_seqlen=max_len, seq_lens_host=lens))
         return linear_logprob(hidden.index_select(0, pred_index), model.output_weight, targets, float(temperature))
+
+    def _replay_context_parallel(self, prompts: List[torch.Tensor], responses: List[torch.Tensor], cp: Any, temperature: float) -> torch.Tensor:
+        """Replay with every sequence cut over the context-parallel ranks: this rank runs the model on its chunk of each sequence (keys and
+        values gathered per layer), takes the log-probs of the response tokens it holds, and the ranks' pieces are summed into the full
+        vector, ordered like the packed segment, so the caller sees what the single-rank replay returns."""
+        from unirl_b200.parallel.context_parallel import PackedPlan, _SumOverRanks
+
+        model = self.model.transformer
+        device = model.embed_tokens.device
+        seqs = [torch.cat([p.to(torch.long).cpu(), r.to(torch.long).cpu()]) for p, r in zip(prompts, responses)]
+        plan = PackedPlan([int(s.numel()) for s in seqs], cp.size, cp.rank)
+        total = sum(int(r.numel()) for r in responses)
+        if not total:
+            return torch.zeros(0, dtype=torch.float32, device=device)
+        tokens = torch.cat([plan.local_slice(s, i) for i, s in enumerate(seqs)]).to(device)
+        meta = AttnMeta(mode="train", positions=plan.local_positions().to(device), cu_seqlens=plan.cu_q.to(device), max_seqlen=max(plan.chunk), cp_plan=plan, cp_comm=cp.comm)
+        hidden = model(tokens, meta)
+        rows, dest, tgt, off = [], [], [], 0
+        for i, (p, r) in enumerate(zip(prompts, responses)):
+            n_p, n_r = int(p.numel()), int(r.numel())
+            if n_r:
+                pred = torch.arange(n_p - 1, n_p + n_r - 1)  # position j predicts token j + 1
+                mine, local = plan.locate(i, pred)
+                rows.append(local)
+                dest.append(torch.arange(off, off + n_r)[mine])
+                tgt.append(seqs[i][pred[mine] + 1])
+            off += n_r
+        rows_t, dest_t, tgt_t = torch.cat(rows).to(device), torch.cat(dest).to(device), torch.cat(tgt).to(device)
+        full = torch.zeros(total, dtype=torch.float32, device=device)
+        if rows_t.numel():
+            full = full.index_put((dest_t,), linear_logprob(hidden.index_select(0, rows_t), model.output_weight, tgt_t, temperature).float())
+        else:
+            full = full + 0.0 * hidden.sum()  # a rank without response tokens still takes part in every collective of the backward pass
+        return _SumOverRanks.apply(full, cp.comm)
 
 
 __all__ = ["Qwen3ARStage", "Qwen3ARStep", "Qwen3ARParams", "pack_text_segment", "build_replay_batch"]

@@ -114,6 +114,8 @@ class AttnMeta:
     cascade: Optional[Any] = None  # shared-prefix decode: prefix_tables / prefix_lens / suffix_tables / suffix_lens / rows
     seq_lens_host: Optional[List[int]] = None  # packed sequence lengths as host ints (saves a device read in attention dispatch)
     input_embeds: Optional[torch.Tensor] = None  # [T, H]: replaces the token-embedding lookup (multimodal prompts)
+    cp_plan: Optional[Any] = None  # context parallelism: the packed stream holds this rank's chunk of every sequence (parallel.context_parallel.PackedPlan)
+    cp_comm: Optional[Any] = None  # ... and the group its keys / values are gathered over
 
 
 class Qwen3DecoderLayer(nn.Module):
@@ -191,6 +193,10 @@ class Qwen3DecoderLayer(nn.Module):
         if meta.mode == "decode":
             return A.paged_decode_attention(q, meta.k_cache[self.layer_idx], meta.v_cache[self.layer_idx], meta.block_tables,
                                             meta.seq_lens, self.scale, meta.workspace, meta.max_kv_len)
+        if meta.cp_plan is not None:
+            from unirl_b200.parallel.context_parallel import packed_attention
+
+            return packed_attention(q, k, v, meta.cp_plan, meta.cp_comm, self.scale)
         return A.varlen_attention(q, k, v, meta.cu_seqlens, meta.max_seqlen, True, self.scale, meta.seq_lens_host)
 
     def forward_infer(self, pending: Optional[torch.Tensor], x: torch.Tensor, meta: AttnMeta) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -243,6 +249,7 @@ class Qwen3Transformer(nn.Module):
                  gradient_checkpointing: bool = False):
         super().__init__()
         self.cfg = cfg
+        self.cp: Optional[Any] = None  # context-parallel group (parallel.context_parallel.ContextParallel) for the training replay; set by the trainer backend
         self.tp = tp or TPContext()
         self.gradient_checkpointing = gradient_checkpointing
         self.checkpoint_layers: Optional[int] = None  # recompute only the first N blocks in backward (None = all): 180 GB of HBM holds the rest

@@ -37,6 +37,9 @@ class QwenVLARStage(Qwen3ARStage):
 
     def replay(self, conditions: QwenVLARConditions, *, segment: TextSegment, temperature: float = 1.0) -> torch.Tensor:
         model = self.model.transformer
+        if getattr(model, "cp", None) is not None and model.cp.size > 1:
+            raise NotImplementedError("context parallelism is implemented for the text-only replay; vision-language prompts carry image features whose "
+                                      "placeholder spans would have to be cut over the ranks")
         device = model.embed_tokens.device
         prompts = unpad_prompts(conditions.prompt.input_ids, conditions.prompt.attention_mask)
         cu = segment.cu_seqlens.tolist()

@@ -15,7 +15,7 @@ Parity: the reference only forwards ``ring_degree`` / ``cp_size`` knobs to its e
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -99,4 +99,87 @@ def reference_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causa
     return _masked_attention(q, k, v, mask, scale)
 
 
-__all__ = ["ContextParallel", "reference_attention"]
+# ------------------------------------------------------------------------------------------------ packed sequences (AR replay)
+class PackedPlan:
+    """Placement of a packed micro-batch of sequences (lengths ``lens``) on one context-parallel rank.
+
+    Every sequence is cut into ``P`` chunks of ``n_i = ceil(L_i / P)`` tokens (the last chunks padded); rank ``r`` holds chunk ``r`` of
+    every sequence, packed sequence after sequence, so all ranks hold ``Σ n_i`` tokens.  Keys and values are all-gathered (rank-major) and
+    re-indexed per rank into, for every sequence, the chunks ``0 .. r`` in global order: exactly the prefix its queries may see, so the
+    attention is a packed causal attention with ``n_i`` queries against ``(r + 1) · n_i`` keys, aligned at the end (the convention of the
+    flash kernels).  Padding sits at the tail of a sequence, after every real token, and is never attended to by one.
+    """
+
+    def __init__(self, lens: Sequence[int], size: int, rank: int):
+        self.lens, self.size, self.rank = [int(n) for n in lens], int(size), int(rank)
+        self.chunk = [-(-n // self.size) for n in self.lens]
+        self.local_tokens = sum(self.chunk)
+        offs, idx, o = [], [], 0
+        for n in self.chunk:
+            offs.append(o)
+            o += n
+        self.offsets = offs
+        for i, n in enumerate(self.chunk):
+            for s in range(self.rank + 1):
+                idx.append(torch.arange(n) + s * self.local_tokens + offs[i])
+        self.kv_index = torch.cat(idx) if idx else torch.zeros(0, dtype=torch.long)
+        self.cu_q = torch.tensor([0] + list(torch.tensor(self.chunk).cumsum(0).tolist()), dtype=torch.int32)
+        self.cu_k = self.cu_q * (self.rank + 1)
+
+    def local_slice(self, seq: torch.Tensor, i: int, pad: int = 0) -> torch.Tensor:
+        """Chunk ``rank`` of sequence ``i`` (a 1-D tensor of its ``L_i`` tokens), padded to ``n_i``."""
+        n = self.chunk[i]
+        part = seq[self.rank * n : (self.rank + 1) * n]
+        return part if part.numel() == n else torch.cat([part, part.new_full((n - part.numel(),), pad)])
+
+    def local_positions(self) -> torch.Tensor:
+        return torch.cat([torch.arange(n) + self.rank * n for n in self.chunk]) if self.chunk else torch.zeros(0, dtype=torch.long)
+
+    def locate(self, i: int, pos: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """For global positions ``pos`` of sequence ``i``: which of them this rank holds (bool mask) and their rows in the local stream."""
+        n = self.chunk[i]
+        mine = (pos >= self.rank * n) & (pos < (self.rank + 1) * n)
+        return mine, pos[mine] - self.rank * n + self.offsets[i]
+
+
+class _SumOverRanks(torch.autograd.Function):
+    """Sum of per-rank partial vectors (each rank filled its own entries of a zero vector); the gradient of the sum reaches every rank whole."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Comm) -> torch.Tensor:
+        y = x.contiguous().clone()
+        comm.all_reduce(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        return g, None
+
+
+def packed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, plan: PackedPlan, comm: Comm, scale: float) -> torch.Tensor:
+    """Causal attention of this rank's packed query chunks ``q [T_loc, Hq, D]`` against the prefixes of their sequences, keys / values
+    ``[T_loc, Hkv, D]`` gathered over the group (differentiable: their gradients are summed over the ranks that read them)."""
+    idx = plan.kv_index.to(q.device)
+    kk = _GatherSeqSum.apply(k.unsqueeze(0), comm)[0].index_select(0, idx)
+    vv = _GatherSeqSum.apply(v.unsqueeze(0), comm)[0].index_select(0, idx)
+    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
+        try:
+            from flash_attn import flash_attn_varlen_func  # q and k of different lengths per sequence: the library kernel (causal mask aligned at the end)
+
+            cq, ck = plan.cu_q.to(q.device), plan.cu_k.to(q.device)
+            return flash_attn_varlen_func(q.contiguous(), kk.contiguous(), vv.contiguous(), cq, ck, max(plan.chunk), max(plan.chunk) * (plan.rank + 1), softmax_scale=float(scale),
+                                          causal=True)
+        except ImportError:
+            pass
+    out = torch.empty_like(q)
+    cq, ck = plan.cu_q.tolist(), plan.cu_k.tolist()
+    for i, n in enumerate(plan.chunk):
+        if not n:
+            continue
+        qi, ki, vi = q[cq[i] : cq[i + 1]], kk[ck[i] : ck[i + 1]], vv[ck[i] : ck[i + 1]]
+        mask = torch.arange(ki.shape[0], device=q.device)[None, :] <= (torch.arange(n, device=q.device)[:, None] + plan.rank * n)
+        out[cq[i] : cq[i + 1]] = _masked_attention(qi.unsqueeze(0), ki.unsqueeze(0), vi.unsqueeze(0), mask, scale)[0]
+    return out
+
+
+__all__ = ["ContextParallel", "PackedPlan", "packed_attention", "reference_attention"]

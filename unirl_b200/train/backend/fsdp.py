@@ -107,6 +107,25 @@ class FSDPBackend(Remote):
             for m in self.model.modules():
                 if hasattr(m, "sp") and hasattr(m, "patchify"):
                     m.sp = ctx
+        cp = int(getattr(self.fsdp_cfg, "cp_size", 1) or 1)
+        if cp > 1:
+            # Context parallelism of the autoregressive replay: the ranks of a group see the SAME sequences (placed like sequence-parallel
+            # peers: train_parallel={sp: cp}) and each runs its chunk of every sequence; partial gradients add up like under sp.
+            from unirl_b200.parallel.context_parallel import ContextParallel
+
+            if sp > 1:
+                raise ValueError("sp_size and cp_size are not combined")
+            if self.comm.size % cp:
+                raise ValueError(f"cp_size={cp} does not divide the trainer's {self.comm.size} ranks")
+            if self.rank_info.sp_size != cp:
+                raise ValueError(f"fsdp_cfg.cp_size={cp} but the role was placed with sp={self.rank_info.sp_size}; pass train_parallel={{sp: {cp}}}")
+            targets = [m for m in self.model.modules() if hasattr(m, "cp") and hasattr(m, "embed_tokens")]
+            if not targets:
+                raise ValueError("cp_size > 1 needs a model with a context-parallel replay (the autoregressive decoders)")
+            ctx = ContextParallel(self.comm.split([list(range(g * cp, (g + 1) * cp)) for g in range(self.comm.size // cp)]))
+            for m in targets:
+                m.cp = ctx
+            sp = cp  # gradient bookkeeping below: partial gradients of `cp` peers add up
         shard_group, replicate_group = self.comm, None
         hs = int(self.fsdp_cfg.hsdp_shard_size)
         if self.fsdp_cfg.fsdp_mode == "hybrid" and self.comm.size > hs and self.comm.size % hs == 0:

@@ -46,6 +46,7 @@ class FSDPConfig:
     reshard_after_forward: bool = False  # False: ZeRO-2, bf16 replica resident (default: HBM is plentiful); True: ZeRO-3, gather around each block
     activation_checkpointing: bool = False
     sp_size: int = 1  # Ulysses sequence-parallel degree inside one data-parallel replica (the role must be created with parallel={"sp": n})
+    cp_size: int = 1  # context-parallel ranks of the autoregressive replay (each sequence cut over the group); place the role with train_parallel={sp: cp_size}
     checkpoint_layers: Optional[int] = None  # with activation_checkpointing: recompute only the first N blocks (None = every block)
     use_torch_compile: bool = False  # accepted for recipe compatibility; there is no tracing compiler here
     defer_grad_sync: bool = False
