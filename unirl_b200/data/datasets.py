@@ -46,11 +46,18 @@ def load_jsonl(path: str, prompt_key: str = "prompt", image_key: Optional[str] =
             if prompt is None:
                 raise KeyError(f"{path}: row lacks '{prompt_key}' / question / text / problem")
             media = None
+            resolve = lambda u: u if os.path.isabs(u) or "://" in u else os.path.join(base, u)  # noqa: E731  (relative to the jsonl's folder)
             img = d.get(image_key or "image") or d.get("images")
             if img:
                 imgs = img if isinstance(img, list) else [img]
-                media = [MediaRef(i if os.path.isabs(i) or "://" in i else os.path.join(base, i), "image") for i in imgs]
-            meta = {k: v for k, v in d.items() if k not in (prompt_key, "image", "images")}
+                media = [MediaRef(resolve(i), "image") for i in imgs]
+            elif d.get("media_refs"):  # [{"modality": "image", "role": "condition", "uri": "images/7.png"}, ...]
+                media = [MediaRef(resolve(str(m["uri"])), str(m.get("modality", "image"))) for m in d["media_refs"] if m.get("uri")]
+            meta = {k: v for k, v in d.items() if k not in (prompt_key, "image", "images", "media_refs", "metadata")}
+            if isinstance(d.get("metadata"), dict):  # a nested metadata record is the row's metadata; sibling keys (prompt_id, ...) ride along
+                meta.update(d["metadata"])
+            elif d.get("metadata") is not None:
+                meta["metadata"] = d["metadata"]
             rows.append(_row(str(prompt), meta or None, media))
     return PromptDataset(rows)
 
