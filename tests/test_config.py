@@ -109,3 +109,17 @@ def test_export_hf_full_and_lora(tmp_path):
     assert export(str(tmp_path / "lora"), "random:tiny", str(tmp_path / "out_adapter"), adapter_only=True)["adapter"] == 1
     peft = load_file(str(tmp_path / "out_adapter" / "adapter_model.safetensors"))
     assert any(k.endswith("self_attn.q_proj.lora_A.default.weight") for k in peft)
+
+
+def test_relative_interpolations():
+    """``${.key}`` names a sibling, every further dot climbs one mapping (list entries count as a level), as in the recipes' schedulers
+    (``num_timesteps: ${..num_inference_steps}``)."""
+    from unirl_b200.config.node import ConfigNode, to_container
+
+    c = ConfigNode({"n": 10, "s": {"steps": 4, "sched": {"num": "${..steps}", "same": "${.num}", "abs": "${n}", "lst": [{"k": "${....steps}", "j": "${.k}"}]}}})
+    assert to_container(c)["s"]["sched"] == {"num": 4, "same": 4, "abs": 10, "lst": [{"k": 4, "j": 4}]}
+    assert c.s.sched.num == 4 and c.s.sched.lst[0].j == 4
+    import pytest
+
+    with pytest.raises(KeyError):
+        ConfigNode({"a": {"b": "${...x}"}}).a.b

@@ -170,3 +170,44 @@ def test_meta_construction_and_per_rank_materialisation(tmp_path):
     first = next(m for m in part.transformer.modules() if isinstance(m, MoEFFN))
     name = next(n for n, m in part.transformer.named_modules() if m is first)
     assert torch.equal(first.experts[0].down, ref[f"{name}.experts.{n_experts // 2}.down"])
+
+
+def test_bagel_guidance_window_and_renormalisation():
+    """Bagel's sampling knobs: the text guidance acts only inside ``cfg_interval`` of the schedule, and the guided velocity is scaled back
+    towards the conditional one's norm (whole-sample or per-token norms, clamped between ``cfg_renorm_min`` and 1)."""
+    import pytest
+
+    from unirl_b200.models.bagel import BagelDiffusionParams, BagelPipeline, BagelPipelineConfig, BagelStageParams
+
+    with pytest.raises(Exception):
+        BagelDiffusionParams(cfg_renorm_type="rows")
+    sp = BagelDiffusionParams(cfg_text_scale=4.0, cfg_interval=(0.4, 1.0), cfg_renorm_min=0.0, cfg_renorm_type="global", samples_per_prompt=2)
+    assert sp.num_inference_steps == 14 and sp.samples_per_prompt == 2
+    pipe = BagelPipeline.from_config(BagelPipelineConfig(pretrained_model_ckpt_path="random:tiny-mot", model_precision="fp32", autocast_precision="fp32", device="cpu"))
+    stage = pipe.diffusion
+    p = stage._stage_params(sp)
+    assert isinstance(p, BagelStageParams) and p.guidance_scale == 4.0 and p.cfg_interval == (0.4, 1.0) and p.eta == 1.0
+    torch.manual_seed(0)
+    vc, vu = torch.randn(2, 4, 6, 6), torch.randn(2, 4, 6, 6)
+    plain = vu + 4.0 * (vc - vu)
+    g = stage._guided(vu, vc, p)
+    ratio = (vc.flatten(1).norm(dim=1) / plain.flatten(1).norm(dim=1)).clamp(max=1.0)
+    torch.testing.assert_close(g, plain * ratio.view(2, 1, 1, 1))
+    assert torch.all(g.flatten(1).norm(dim=1) <= vc.flatten(1).norm(dim=1) * (1 + 1e-5))
+    pc = stage._stage_params(BagelDiffusionParams(cfg_text_scale=4.0, cfg_renorm_type="channel", cfg_renorm_min=0.5))
+    gc = stage._guided(vu, vc, pc)
+    r = (vc.norm(dim=1, keepdim=True) / (plain.norm(dim=1, keepdim=True) + 1e-8)).clamp(min=0.5, max=1.0)
+    torch.testing.assert_close(gc, plain * r)
+    # inside the window both branches are evaluated, outside only the conditional one
+    tok = pipe.bundle.tokenizer
+    from unirl_b200.models.unified.stages import UnifiedConditions
+    from unirl_b200.types.conditions import TextTokenCondition
+
+    ids = torch.tensor([[5, 6, 7, 8], [9, 10, 11, 12]])
+    cond = UnifiedConditions(prompt=TextTokenCondition(input_ids=ids, attention_mask=torch.ones_like(ids)),
+                             negative_prompt=TextTokenCondition(input_ids=torch.tensor([[1], [1]]), attention_mask=torch.ones(2, 1, dtype=torch.long)))
+    x = torch.randn(2, *pipe.latent_shape(sp))
+    inside = stage._branches(x, torch.tensor([0.7]), cond, p)
+    outside = stage._branches(x, torch.tensor([0.2]), cond, p)
+    assert inside[1] is not None and outside[1] is None and inside[0].shape == x.shape
+    del tok

@@ -2,8 +2,8 @@
 
 A minimal stand-in for OmegaConf's ``DictConfig`` (neither Hydra nor OmegaConf is a dependency):
 supports ``cfg.a.b``, ``cfg["a"]``, ``cfg.get(k, default)``, ``in``, iteration, and the resolvers
-used by the reference recipes — ``${oc.env:VAR}``, ``${oc.env:VAR,default}`` (nestable) and
-``${path.to.key}`` absolute references (``config/README.md`` of the reference describes the
+used by the reference recipes — ``${oc.env:VAR}``, ``${oc.env:VAR,default}`` (nestable), ``${oc.decode:…}``,
+``${path.to.key}`` absolute and ``${.sibling}`` / ``${..parent.key}`` relative references (``config/README.md`` of the reference describes the
 recipe grammar: flat single-file YAML, every object a ``_target_`` node).
 """
 
@@ -25,11 +25,12 @@ def _parse_scalar(text: str) -> Any:
 
 
 class ConfigNode:
-    __slots__ = ("_data", "_root")
+    __slots__ = ("_data", "_root", "_path")
 
-    def __init__(self, data: Dict[str, Any], root: Optional["ConfigNode"] = None):
+    def __init__(self, data: Dict[str, Any], root: Optional["ConfigNode"] = None, path: tuple = ()):
         object.__setattr__(self, "_data", data)
         object.__setattr__(self, "_root", root if root is not None else self)
+        object.__setattr__(self, "_path", tuple(path))  # keys from the root to this mapping: the anchor of relative references
 
     # ---- interpolation ------------------------------------------------------------------------
     def _lookup_path(self, path: str) -> Any:
@@ -57,12 +58,21 @@ class ConfigNode:
             if isinstance(d, str) and d.lower() in ("null", "none", "~"):
                 return None
             return d if d is None else str(d)
+        if expr.startswith("oc.decode:"):  # a string (typically from the environment) read as a YAML scalar: "true" -> True, "3" -> 3, "null" -> None
+            inner = self._resolve_str(expr[len("oc.decode:"):].strip())
+            return _parse_scalar(inner) if isinstance(inner, str) else inner
         if expr.startswith("oc.select:"):
             name, default = _split_top_comma(expr[len("oc.select:"):])
             try:
                 return self._lookup_path(name.strip())
             except KeyError:
                 return None if default is _MISSING else _parse_scalar(default.strip())
+        if expr.startswith("."):  # relative reference: ``${.key}`` a sibling in this mapping, ``${..key}`` one in the mapping above, ...
+            ups = len(expr) - len(expr.lstrip("."))
+            if ups - 1 > len(self._path):
+                raise KeyError(f"relative interpolation '{expr}' climbs above the root from '{'.'.join(self._path)}'")
+            base = self._path[: len(self._path) - (ups - 1)]
+            return self._lookup_path(".".join([*base, expr[ups:]]))
         return self._lookup_path(expr)
 
     def _resolve_str(self, s: str) -> Any:
@@ -99,12 +109,23 @@ class ConfigNode:
     def _resolve(self, v: Any) -> Any:
         return self._resolve_str(v) if isinstance(v, str) else v
 
-    def _wrap(self, v: Any) -> Any:
+    def _wrap(self, v: Any, key: Optional[str] = None) -> Any:
+        path = self._path if key is None else (*self._path, str(key))
+        if isinstance(v, str) and v.startswith("${") and v.endswith("}") and v.count("${") == 1 and ":" not in v:
+            # a whole-value reference (``params: ${sampling}``) stands for the node it names: relative references inside that node keep
+            # resolving against the place the node lives at, not the place it is referenced from
+            ref = v[2:-1].strip()
+            if ref.startswith("."):
+                ups = len(ref) - len(ref.lstrip("."))
+                ref = ".".join([*self._path[: len(self._path) - (ups - 1)], ref[ups:]]) if ups - 1 <= len(self._path) else ref
+            if not ref.startswith("."):
+                path = tuple(ref.split("."))
         v = self._resolve(v)
         if isinstance(v, dict):
-            return ConfigNode(v, self._root)
+            return ConfigNode(v, self._root, path)
         if isinstance(v, list):
-            return [self._wrap(x) for x in v]
+            holder = ConfigNode({}, self._root, path)  # entries of a list resolve relative references like the list's own mapping level
+            return [holder._wrap(x, str(i)) if isinstance(x, dict) else self._wrap(x) for i, x in enumerate(v)]
         return v
 
     # ---- mapping API ----------------------------------------------------------------------------
@@ -119,7 +140,7 @@ class ConfigNode:
         self._data[key] = to_container(value)
 
     def __getitem__(self, key: str) -> Any:
-        return self._wrap(self._data[key])
+        return self._wrap(self._data[key], key)
 
     def __setitem__(self, key: str, value: Any) -> None:
         self._data[key] = to_container(value)

@@ -48,4 +48,27 @@ class QueueTransport(WorkerLocalTransport):
         return n
 
 
-__all__ = ["QueueTransport"]
+# ---- configuration records of recipes written for the reference --------------------------------------------------------------
+# ``transfer_queue: {_target_: …simple.SimpleBackend, num_units, unit_size}`` and the Mooncake variant describe the storage behind the
+# GLOBAL queue plane.  On one NVSwitch box the queue lives in the workers' own memory whatever the record says; the records are kept so
+# that such recipes load, and the Mooncake one says so once.
+class SimpleBackend:
+    def __init__(self, num_units: int = 16, unit_size: int = 1024, **_kw: Any):
+        self.num_units, self.unit_size = int(num_units), int(unit_size)
+
+
+class MooncakeZeroCopyConfig:
+    def __init__(self, enable: bool = True, **kw: Any):
+        self.enable, self.options = bool(enable), dict(kw)
+
+
+class MooncakeBackend:
+    def __init__(self, metadata_server: str = "", master_server_address: str = "", protocol: str = "rdma", zero_copy: Any = None, **kw: Any):
+        import logging
+
+        self.metadata_server, self.master_server_address, self.protocol, self.zero_copy, self.options = metadata_server, master_server_address, protocol, zero_copy, dict(kw)
+        logging.getLogger(__name__).warning("transfer_queue: a Mooncake storage back end is configured; this build keeps the queue in the workers' memory "
+                                            "(single NVSwitch domain), the RDMA settings are not used")
+
+
+__all__ = ["QueueTransport", "SimpleBackend", "MooncakeBackend", "MooncakeZeroCopyConfig"]

@@ -44,6 +44,19 @@ class DiTDiffusionParams:
     true_cfg: bool = True  # False: guidance is an input embedding of the model, one pass per step
 
 
+def as_stage_params(params: Any) -> "DiTDiffusionParams":
+    """Stage parameters from whatever a recipe handed over: the stage's own dataclass, ``None`` (defaults), or the request-side sampling
+    parameters (recipes written for the reference pass ``params: ${sampling}``), whose matching fields are taken over."""
+    if isinstance(params, DiTDiffusionParams):
+        return params
+    if params is None:
+        return DiTDiffusionParams()
+    get = (lambda k: params.get(k)) if isinstance(params, dict) else (lambda k: getattr(params, k, None))
+    kw = {k: get(k) for k in ("guidance_scale", "eta", "sigma_max", "trajectory_precision", "distilled_guidance_scale", "true_cfg") if get(k) is not None}
+    strategy = get("strategy") if get("strategy") is not None else get("sde_strategy")
+    return DiTDiffusionParams(strategy=strategy, **kw)
+
+
 _ODE = StepStrategy()  # deterministic Euler transition for the steps outside the SDE set
 
 
@@ -71,6 +84,10 @@ class DiTDiffusionStage:
         """Guided velocity at ``(x, σ)``; ``σ`` is ``[B]`` in ``[0, 1]`` (the transformer sees ``1000·σ``)."""
         vc, vu = self._branches(x, sigma, cond, p)
         return vc if vu is None else self._guided(vu, vc, p)
+
+    def _stage_params(self, params: Any) -> DiTDiffusionParams:
+        """The stage's parameter record from what the caller passed (families with knobs of their own override)."""
+        return as_stage_params(params)
 
     @property
     def _plain_guidance(self) -> bool:
@@ -127,6 +144,7 @@ class DiTDiffusionStage:
     def diffuse(self, conditions: DiTConditions, *, schedule: torch.Tensor, params: DiTDiffusionParams, initial_noise: torch.Tensor,
                 sde_indices: Optional[Sequence[int]] = None, sample_ids: Optional[List[str]] = None, seed: int = 0) -> LatentSegment:
         dev = self.device
+        params = self._stage_params(params)
         sig = schedule.to(dev).float()
         steps = sig.numel() - 1
         sde = sorted(int(i) for i in (range(steps) if sde_indices is None else sde_indices)) if params.eta > 0 else []
@@ -167,6 +185,7 @@ class DiTDiffusionStage:
     # ---- training -------------------------------------------------------------------------------------------
     def replay(self, conditions: DiTConditions, *, segment: LatentSegment, params: DiTDiffusionParams, step_indices: Optional[List[int]] = None) -> ReplayResult:
         dev = self.device
+        params = self._stage_params(params)
         sig = segment.sigmas.to(dev).float()
         steps = [int(i) for i in (step_indices if step_indices is not None else segment.sde_indices.tolist())]
         strategy = _strategy(params.strategy, self.default_strategy)
@@ -187,7 +206,7 @@ class DiTDiffusionStage:
         dev = self.device
         cond = conditions.to_device(dev) if hasattr(conditions, "to_device") else conditions
         with torch.autocast(dev.type, dtype=self.autocast_dtype, enabled=self.autocast_dtype != torch.float32 and dev.type == "cuda"):
-            return self._velocity(sample.to(dev).float(), sigma, cond, params)
+            return self._velocity(sample.to(dev).float(), sigma, cond, self._stage_params(params))
 
 
-__all__ = ["DiTDiffusionStage", "DiTDiffusionParams"]
+__all__ = ["DiTDiffusionStage", "DiTDiffusionParams", "as_stage_params"]

@@ -29,10 +29,22 @@ from unirl_b200.types.sampling import DiffusionSamplingParams, get_diffusion_par
 class DiTPipeline(Pipeline):
     conditions_cls = DiTConditions
 
-    def __init__(self, bundle: DiTBundle):
+    def __init__(self, bundle: DiTBundle, *, shift: Optional[float] = None, autocast_precision: Optional[str] = None, trajectory_precision: Optional[str] = None,
+                 logprob_precision: Optional[str] = None, strategy: Any = None, **_ignored: Any):
+        """The keyword options are the ones recipes written for the reference pass to a pipeline built directly from its class
+        (``pipeline: {_target_: …Pipeline, shift, autocast_precision, trajectory_precision, logprob_precision, strategy}``): they override
+        the bundle's configuration; ``strategy`` (a step-strategy object or its name) becomes the family's default SDE strategy."""
         super().__init__()
         self.bundle = bundle
         cfg, spec = bundle.config, bundle.spec
+        for name, value in (("shift", shift), ("autocast_precision", autocast_precision), ("trajectory_precision", trajectory_precision),
+                            ("logprob_precision", logprob_precision)):
+            if value is not None and hasattr(cfg, name):
+                setattr(cfg, name, value)
+        if strategy is not None:
+            from unirl_b200.sde.kernels import STRATEGIES, StepStrategy
+
+            spec.default_strategy = next((k for k, c in STRATEGIES.items() if type(strategy) is c), spec.default_strategy) if isinstance(strategy, StepStrategy) else str(strategy)
         self.text_embed = TextEmbedStage(bundle.text_encoders, bundle.tokenizers, spec.text_combine, spec.transformer.text_dim, cfg.max_sequence_length)
         self.diffusion = DiTDiffusionStage(bundle, spec.default_strategy, cfg.autocast_precision)
         self.shift = float(cfg.shift if cfg.shift is not None else spec.shift)

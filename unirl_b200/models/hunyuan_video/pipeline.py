@@ -81,8 +81,8 @@ class HunyuanVideoDiffusionStage(DiTDiffusionStage):
 
 
 class HunyuanVideoPipeline(DiTPipeline):
-    def __init__(self, bundle):
-        super().__init__(bundle)
+    def __init__(self, bundle, **options):
+        super().__init__(bundle, **options)
         spec, cfg = bundle.spec, bundle.config
         self.diffusion = HunyuanVideoDiffusionStage(bundle, spec.default_strategy, cfg.autocast_precision)
         self.text_embed = HunyuanVideoTextEmbedStage(bundle.text_encoders, bundle.tokenizers, spec.text_combine, spec.transformer.text_dim, cfg.max_sequence_length,

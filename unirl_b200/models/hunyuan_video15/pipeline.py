@@ -46,8 +46,8 @@ class HunyuanVideo15DiffusionStage(DiTDiffusionStage):
 
 
 class HunyuanVideo15Pipeline(DiTPipeline):
-    def __init__(self, bundle):
-        super().__init__(bundle)
+    def __init__(self, bundle, **options):
+        super().__init__(bundle, **options)
         self.diffusion = HunyuanVideo15DiffusionStage(bundle, bundle.spec.default_strategy, bundle.config.autocast_precision)
 
     @classmethod

@@ -252,9 +252,13 @@ def save_native_checkpoint(model: torch.nn.Module, path: str, preset: str, overr
 class UnifiedPipeline(Pipeline):
     conditions_cls = UnifiedConditions
 
-    def __init__(self, bundle: UnifiedBundle):
+    def __init__(self, bundle: UnifiedBundle, *, shift: Optional[float] = None, autocast_precision: Optional[str] = None, **_options: Any):
         super().__init__()
         self.bundle = bundle
+        if shift is not None:
+            bundle.config.shift = float(shift)
+        if autocast_precision is not None:
+            bundle.config.autocast_precision = autocast_precision
         self.ar = UnifiedARStage(bundle)
         self.diffusion = UnifiedDiffusionStage(bundle, "flow", bundle.config.autocast_precision)
         self.image = self.diffusion  # the image track's stage

@@ -50,8 +50,8 @@ class ZImageDiffusionStage(DiTDiffusionStage):
 
 
 class ZImagePipeline(DiTPipeline):
-    def __init__(self, bundle):
-        super().__init__(bundle)
+    def __init__(self, bundle, **options):
+        super().__init__(bundle, **options)
         self.diffusion = ZImageDiffusionStage(bundle, bundle.spec.default_strategy, bundle.config.autocast_precision)
 
     @classmethod

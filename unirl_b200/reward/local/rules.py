@@ -141,6 +141,21 @@ class MathBoxedRewardScorer(_TextRuleBackend):
 
 
 @dataclass
+class MCExactMatchSpec:
+    """The rule needs no settings; the class exists because recipes name it under the backend's ``config``."""
+
+
+@dataclass
+class GSM8KExactMatchSpec:
+    pass
+
+
+@dataclass
+class MathBoxedSpec:
+    pass
+
+
+@dataclass
 class MathVerifySpec:
     timeout_s: float = 5.0
     boxed_only: bool = False
@@ -172,5 +187,6 @@ class MathVerifyRewardScorer(_TextRuleBackend):
         return 1.0 if pred is not None and math_equal(pred, last_boxed(gold) or gold) else 0.0
 
 
-__all__ = ["MCExactMatchRewardScorer", "GSM8KExactMatchRewardScorer", "MathBoxedRewardScorer", "MathVerifyRewardScorer", "MathVerifySpec",
+__all__ = ["MCExactMatchRewardScorer", "GSM8KExactMatchRewardScorer", "MathBoxedRewardScorer", "MathVerifyRewardScorer", "MathVerifySpec", "MCExactMatchSpec",
+           "GSM8KExactMatchSpec", "MathBoxedSpec",
            "last_boxed", "normalize_math", "math_equal", "strip_thinking"]

@@ -51,9 +51,27 @@ def decode_video(b64: str) -> torch.Tensor:
     return torch.from_numpy(np.load(io.BytesIO(base64.b64decode(b64)))).float() / 255.0
 
 
+class RemoteRewardSpec:
+    """Settings of the remote backend under the field names recipes written for the reference use (``config: {_target_: …RemoteRewardSpec,
+    base_url, required_rewards, reward_weights, batch_size, timeout, max_retries, input_kind, …}``; ``unirl/reward/remote.py:625-653``)."""
+
+    def __init__(self, base_url: str = "", required_rewards: Sequence[str] = (), reward_weights: Optional[Dict[str, float]] = None, batch_size: int = 8,
+                 timeout: float = 300.0, max_retries: int = 3, retry_delay: float = 1.0, input_kind: str = "image", raise_on_failure: bool = True, **extra: Any):
+        self.base_url, self.required_rewards, self.reward_weights = str(base_url), tuple(required_rewards), dict(reward_weights or {})
+        self.batch_size, self.timeout, self.max_retries, self.retry_delay = int(batch_size), float(timeout), int(max_retries), float(retry_delay)
+        self.input_kind, self.raise_on_failure, self.extra = str(input_kind), bool(raise_on_failure), dict(extra)
+
+
 class RemoteRewardBackend(RewardBackend):
-    def __init__(self, url: str, scorers: Sequence[str] = ("clip",), weights: Optional[Dict[str, float]] = None, batch_size: int = 16, concurrency: int = 4,
-                 max_retries: int = 5, timeout_s: float = 300.0, preferred_input_kind: str = "image", **_kw: Any):
+    def __init__(self, url: Optional[str] = None, scorers: Sequence[str] = ("clip",), weights: Optional[Dict[str, float]] = None, batch_size: int = 16, concurrency: int = 4,
+                 max_retries: int = 5, timeout_s: float = 300.0, preferred_input_kind: str = "image", config: Optional[RemoteRewardSpec] = None, **_kw: Any):
+        if config is not None:  # the spec form
+            url = url or config.base_url
+            scorers = tuple(config.required_rewards) or tuple(scorers)
+            weights = config.reward_weights or weights
+            batch_size, max_retries, timeout_s, preferred_input_kind = config.batch_size, config.max_retries, config.timeout, config.input_kind
+        if not url:
+            raise ValueError("RemoteRewardBackend needs the service's url (url=… or config.base_url)")
         self.url = url.rstrip("/")
         self.scorers, self.weights = list(scorers), dict(weights or {})
         self.batch_size, self.concurrency, self.max_retries, self.timeout_s = int(batch_size), int(concurrency), int(max_retries), float(timeout_s)
@@ -123,4 +141,4 @@ class RemoteRewardBackend(RewardBackend):
         return RewardResponse.ok(rewards, comps, time.perf_counter() - t0)
 
 
-__all__ = ["RemoteRewardBackend", "encode_image", "decode_image", "encode_video", "decode_video"]
+__all__ = ["RemoteRewardSpec", "RemoteRewardBackend", "encode_image", "decode_image", "encode_video", "decode_video"]

@@ -34,9 +34,19 @@ def extract_enhanced_prompt(text: str, user_prompt: str, marker: str = "<prompt>
 class ComposedRolloutEngine(BaseRolloutEngine):
     _component_name = "composed"
 
-    def __init__(self, *, ar: Any, diffusion: Any, pe_marker: str = "<prompt>", pe_end_marker: str = "</prompt>",
-                 ar_system_instruction: Optional[str] = None) -> None:
+    def __init__(self, *, ar: Any = None, diffusion: Any = None, pe_marker: str = "<prompt>", pe_end_marker: str = "</prompt>",
+                 ar_system_instruction: Optional[str] = None, config: Any = None, **_deps: Any) -> None:
         super().__init__()
+        if config is not None:  # the configuration-object form: children described by their own engine configurations
+            get = (lambda k: config.get(k)) if isinstance(config, dict) else (lambda k: getattr(config, k, None))
+            ar = ar if ar is not None else get("ar")
+            diffusion = diffusion if diffusion is not None else get("diffusion")
+            pe_marker = get("pe_marker") or pe_marker
+            ar_system_instruction = get("pe_instruction") or ar_system_instruction
+        ar = ar.make_engine() if hasattr(ar, "make_engine") else ar
+        diffusion = diffusion.make_engine() if hasattr(diffusion, "make_engine") else diffusion
+        if ar is None or diffusion is None:
+            raise ValueError("ComposedRolloutEngine needs an autoregressive and a diffusion child engine (objects, or configurations that can build them)")
         self.ar, self.diffusion = ar, diffusion
         self.pe_marker, self.pe_end_marker, self.ar_system_instruction = pe_marker, pe_end_marker, ar_system_instruction
 
