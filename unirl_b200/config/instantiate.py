@@ -15,45 +15,13 @@ from unirl_b200.config.node import ConfigNode, to_container
 
 RESERVED = frozenset({"_target_", "_partial_", "_recursive_", "_convert_", "_args_"})
 
-# recipes written for the reference name ``unirl.*`` / ``hydra.utils.*`` targets; map them here
-_ALIASES = {
-    "hydra.utils.get_class": "unirl_b200.config.instantiate.get_class",
-    "hydra.utils.get_method": "unirl_b200.config.instantiate.get_method",
-}
-
-
-# module paths of the reference that have no same-named module here (longest prefix first)
-_MODULE_ALIASES = tuple(sorted({
-    **{f"unirl_b200.reward.local.{m}": "unirl_b200.reward.local.specs"
-       for m in ("clip", "pickscore", "hpsv2", "hpsv3", "image_reward", "aesthetic", "ocr", "geneval2", "video", "video_pickscore", "registry")},
-    "unirl_b200.reward.local.base": "unirl_b200.reward.base",
-    # engines that drive external serving stacks in the reference: the native engines under the same class names
-    **{f"unirl_b200.rollout.engine.{pkg}.{mod}": "unirl_b200.rollout.engine.compat" for pkg in ("sglang", "sglang_llm", "vllm_omni") for mod in ("engine", "config")},
-    "unirl_b200.rollout.engine.composed.config": "unirl_b200.rollout.engine.compat",
-    "unirl_b200.distributed.tensor.backend.transfer_queue.simple": "unirl_b200.distributed.tensor.backend.transfer_queue",
-    "unirl_b200.distributed.tensor.backend.transfer_queue.mooncake": "unirl_b200.distributed.tensor.backend.transfer_queue",
-}.items(), key=lambda kv: -len(kv[0])))
-
-# class names the reference spells differently
-_NAME_ALIASES = {"WAN21Bundle": "Wan21Bundle", "WAN21Pipeline": "Wan21Pipeline", "WAN21PipelineConfig": "Wan21PipelineConfig", "WAN22Bundle": "Wan22Bundle",
-                 "WAN22Pipeline": "Wan22Pipeline", "WAN22PipelineConfig": "Wan22PipelineConfig"}
-
-
-def _translate(path: str) -> str:
-    if path in _ALIASES:
-        return _ALIASES[path]
-    if path == "unirl" or path.startswith("unirl."):
-        path = "unirl_b200" + path[len("unirl"):]
-    for old, new in _MODULE_ALIASES:
-        if path == old or path.startswith(old + "."):
-            return new + path[len(old):]
-    return path
+from unirl_b200.config.aliases import translate as _translate  # noqa: E402  (name tables for recipes written for the reference)
 
 
 def get_method(path: str) -> Any:
     """Import ``pkg.mod.Attr[.attr…]`` and return the object (class, function or classmethod)."""
     path = _translate(path)
-    parts = [_NAME_ALIASES.get(p, p) for p in path.split(".")]
+    parts = path.split(".")
     for cut in range(len(parts) - 1, 0, -1):
         try:
             obj: Any = importlib.import_module(".".join(parts[:cut]))

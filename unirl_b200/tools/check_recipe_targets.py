@@ -63,16 +63,31 @@ def _defines(path: str, names: List[str]) -> bool:
     return True
 
 
+def _translate(target: str) -> str:
+    """The name tables of ``config/aliases.py``, loaded from its file (pure data: no package import, so no torch)."""
+    global _ALIAS_NS
+    if _ALIAS_NS is None:
+        import runpy
+
+        _ALIAS_NS = runpy.run_path(os.path.join(_ROOT, "unirl_b200", "config", "aliases.py"))
+    return _ALIAS_NS["translate"](target)
+
+
+_ALIAS_NS: Any = None
+
+
 def resolve(target: str) -> bool:
     if target.startswith(_EXTERNAL_OK):
         return True
-    if target == "unirl" or target.startswith("unirl."):
-        target = "unirl_b200" + target[len("unirl"):]
-    parts = target.split(".")
+    parts = _translate(target).split(".")
     for cut in range(len(parts) - 1, 0, -1):
         f = _module_file(parts[:cut])
         if f is not None:
-            return _defines(f, parts[cut:])
+            rest = parts[cut:]
+            if _defines(f, rest):
+                return True
+            # a model family keeps its classes in fewer files than the reference: ``models.<family>.<file>.<Class>`` → the family's package
+            return len(rest) >= 2 and parts[:cut][-2:-1] == ["models"] and _defines(f, rest[1:])
     return False
 
 
