@@ -88,3 +88,27 @@ def test_a_recipe_spelled_the_reference_way_runs(tmp_path, monkeypatch):
         assert tr.backend.compute_local_param_checksums()[0] != before
     finally:
         tr.shutdown()
+
+
+@pytest.mark.timeout(600)
+def test_a_language_model_recipe_spelled_the_reference_way_runs(tmp_path, monkeypatch):
+    import json
+
+    from unirl_b200.rollout.engine.compat import SGLangLLMRolloutEngine
+    from unirl_b200.trainer.ar import ARTrainer
+
+    data = tmp_path / "math.jsonl"
+    data.write_text("".join(json.dumps({"prompt": f"What is {i}+{i}? Put the answer in \\boxed{{}}.", "metadata": {"answer": str(2 * i)}}) + "\n" for i in range(8)))
+    monkeypatch.setenv("DATA_PATH", str(data))
+    cfg = compose("compat/qwen3_grpo_reference_names_cpu")
+    assert cfg.data_source.args.run.eval_data_path == str(data)  # a default that is itself an environment reference
+    tr = ARTrainer(cfg=cfg, batch_size=cfg.batch_size, bundle_cfg=cfg.bundle, pipeline_cfg=cfg.pipeline, backend_cfg=cfg.backend, rollout_cfg=cfg.rollout,
+                   reward_cfg=cfg.reward, algorithm_cfg=cfg.algorithm, stack_cfg=cfg.stack, data_source_cfg=cfg.data_source, sampling_cfg=cfg.sampling,
+                   sync_cfg=cfg.get("sync"), logging_cfg=None)
+    try:
+        assert isinstance(tr.pool.local_role(tr.rollout), SGLangLLMRolloutEngine)
+        tr.train(num_rollouts=1)
+        rows = [r for r in tr.wandb_logger.history if "train/step" in r]
+        assert rows and abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-4
+    finally:
+        tr.shutdown()
