@@ -22,8 +22,8 @@ MODULE_ALIASES = tuple(sorted({
     "unirl_b200.distributed.tensor.backend.transfer_queue.mooncake": "unirl_b200.distributed.tensor.backend.transfer_queue",
 }.items(), key=lambda kv: -len(kv[0])))
 
-NAME_ALIASES = {"WAN21Bundle": "Wan21Bundle", "WAN21Pipeline": "Wan21Pipeline", "WAN21PipelineConfig": "Wan21PipelineConfig", "WAN22Bundle": "Wan22Bundle",
-                "WAN22Pipeline": "Wan22Pipeline", "WAN22PipelineConfig": "Wan22PipelineConfig"}
+NAME_ALIASES = {"WAN21Bundle": "Wan21Bundle", "WAN21Pipeline": "Wan21Pipeline", "WAN21PipelineConfig": "Wan21PipelineConfig", "WAN21Conditions": "Wan21Conditions",
+                "WAN22Bundle": "Wan22Bundle", "WAN22Pipeline": "Wan22Pipeline", "WAN22PipelineConfig": "Wan22PipelineConfig", "WAN22Conditions": "Wan22Conditions"}
 
 
 def translate(path: str) -> str:

@@ -23,8 +23,12 @@ from unirl_b200.utils.peft_merge import extract_lora_tensors
 
 
 class LoraWeightSyncBase(Remote):
-    def __init__(self, *, backend: Any, rollout: Any = None, adapter_name: str = "default", track_prefix: str = "", verify: bool = False) -> None:
+    def __init__(self, *, backend: Any, rollout: Any = None, adapter_name: str = "default", track_prefix: str = "", verify: bool = False,
+                 param_prefix: str = "") -> None:
+        """``param_prefix``: accepted for recipes written for the reference, where it names the engine-side module that holds the adapters
+        (``transformer.``); the native engines address their transformer directly, so the adapter keys travel without it."""
         super().__init__()
+        self._param_prefix = str(param_prefix or "")
         self._backend, self._rollout = backend, rollout
         self.adapter_name, self._track_prefix, self._verify = adapter_name, str(track_prefix or ""), bool(verify)
         self.weight_version = 0

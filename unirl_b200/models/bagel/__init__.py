@@ -103,6 +103,6 @@ class BagelPipeline(UnifiedPipeline):
         return cls(BagelBundle.from_config(config))
 
 
-BagelConditions = UnifiedConditions
+BagelConditions = BagelDiffusionConditions = UnifiedConditions
 
-__all__ = ["BagelPipelineConfig", "BagelBundle", "BagelPipeline", "BagelConditions", "BagelDiffusionParams", "BagelStageParams", "BagelDiffusionStage", "CFG_RENORM_TYPES"]
+__all__ = ["BagelPipelineConfig", "BagelBundle", "BagelPipeline", "BagelConditions", "BagelDiffusionConditions", "BagelDiffusionParams", "BagelStageParams", "BagelDiffusionStage", "CFG_RENORM_TYPES"]

@@ -24,6 +24,7 @@ class HunyuanImage3Pipeline(UnifiedPipeline):
         return cls(HunyuanImage3Bundle.from_config(config))
 
 
-HunyuanImage3Conditions = UnifiedConditions
+HunyuanImage3Conditions = HunyuanImage3ARConditions = HunyuanImage3DiffusionConditions = UnifiedConditions  # one record serves the text and the image track
 
-__all__ = ["HunyuanImage3PipelineConfig", "HunyuanImage3Bundle", "HunyuanImage3Pipeline", "HunyuanImage3Conditions"]
+__all__ = ["HunyuanImage3PipelineConfig", "HunyuanImage3Bundle", "HunyuanImage3Pipeline", "HunyuanImage3Conditions", "HunyuanImage3ARConditions",
+           "HunyuanImage3DiffusionConditions"]

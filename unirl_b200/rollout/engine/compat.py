@@ -146,11 +146,22 @@ class VLLMOmniEngineConfig:
 class _DiffusionCompat(NativeDiffusionRolloutEngine):
     _config_cls: Any = SGLangEngineConfig
 
-    def __init__(self, *, config: Any = None, pipeline: Any = None, **_deps: Any) -> None:
+    def __init__(self, *, config: Any = None, pipeline: Any = None, model_config: Any = None, strategy: Any = None, **_deps: Any) -> None:
+        """``model_config``: the trainer bundle's configuration record (recipes pass ``${bundle.config}``): the engine's own copy of the
+        model is built from the same checkpoint path and precisions.  ``strategy`` rides on the requests here and is not needed."""
         if isinstance(config, dict):
             config = self._config_cls(**config)
         if hasattr(config, "to_native"):
-            config = config.to_native()
+            native = config.to_native()
+            get = (lambda k: model_config.get(k)) if isinstance(model_config, dict) else (lambda k: getattr(model_config, k, None))
+            if model_config is not None:
+                explicit = getattr(config, "pretrained_model_ckpt_path", None) or getattr(config, "model_path", None) or (getattr(config, "engine_kwargs", None) or {}).get("model_path")
+                if not explicit and get("pretrained_model_ckpt_path"):
+                    native.pretrained_model_ckpt_path = str(get("pretrained_model_ckpt_path"))
+                for name in ("model_precision", "autocast_precision", "device"):
+                    if get(name) is not None:
+                        setattr(native, name, get(name))
+            config = native
         super().__init__(config=config, pipeline=pipeline)
 
 

@@ -43,8 +43,9 @@ class ARTrainer(BaseTrainer):
         self.data_source = instantiate(data_source_cfg)
         self.sampling_params = instantiate(sampling_cfg)
         self.weight_sync = None
-        self.separate = str(get("placement", "colocated")) == "separate"
-        rollout_fraction = float(get("rollout_fraction", 0.5))
+        # ``placement`` / ``rollout_fraction``; recipes written for the reference say ``layout`` and give the TRAINER's share (``train_fraction``)
+        self.separate = str(get("placement", get("layout", "colocated"))) == "separate"
+        rollout_fraction = float(get("rollout_fraction", 1.0 - float(get("train_fraction", 0.5))))
         rollout_parallel = get("rollout_parallel")
         rollout_parallel = dict(rollout_parallel) if rollout_parallel else None
         train_parallel = get("train_parallel")
@@ -73,7 +74,10 @@ class ARTrainer(BaseTrainer):
             with placement(self.pool, num_devices=n_roll):
                 self.rollout = remote(**rp, parallel=rollout_parallel)
                 self.reward = remote_cfg(reward_cfg)
-            if self.weight_sync is not None:
+            # across two device slabs: full weights travel by broadcast over a group of trainer rank 0 + engine ranks; LoRA adapters are
+            # small and go through the controller (extract on the trainer, set_lora_from_tensors on every engine rank)
+            self._sync_is_lora = self.weight_sync is not None and hasattr(getattr(self.weight_sync, "cls", None), "push")
+            if self.weight_sync is not None and not self._sync_is_lora:
                 from unirl_b200.distributed.weight_sync.driver import connect_nccl_sync
 
                 connect_nccl_sync(self.weight_sync, self.rollout)
@@ -103,7 +107,11 @@ class ARTrainer(BaseTrainer):
     def _sync_weights(self) -> Dict[str, float]:
         if self.weight_sync is None:
             return {}
-        if self.separate:
+        if self.separate and getattr(self, "_sync_is_lora", False):
+            from unirl_b200.distributed.weight_sync.lora.remote import sync_remote_lora
+
+            stats = sync_remote_lora(self.weight_sync, self.rollout)
+        elif self.separate:
             from unirl_b200.distributed.weight_sync.driver import drive_nccl_sync
 
             stats = drive_nccl_sync(self.weight_sync, self.rollout)
