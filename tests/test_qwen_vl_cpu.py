@@ -61,3 +61,45 @@ def test_vl_grpo_loop():
         assert len(rows) == 2 and abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-3
     finally:
         tr.shutdown()
+
+
+def _vl_trainer(overrides):
+    cfg = compose("ar/tiny_qwen_vl_grpo_cpu", overrides=overrides)
+    return ARTrainer(cfg=cfg, batch_size=cfg.batch_size, bundle_cfg=cfg.bundle, pipeline_cfg=cfg.pipeline, backend_cfg=cfg.backend, rollout_cfg=cfg.rollout,
+                     reward_cfg=cfg.reward, algorithm_cfg=cfg.algorithm, stack_cfg=cfg.stack, data_source_cfg=cfg.data_source, sampling_cfg=cfg.sampling,
+                     sync_cfg=cfg.get("sync"), logging_cfg=None)
+
+
+_ENGINE = ["rollout._target_=unirl_b200.rollout.engine.native_ar.engine.NativeARRolloutEngine", "~rollout.stage_attrs",
+           "+rollout.config={pretrained_model_ckpt_path: 'random:tiny-vl', model_precision: fp32, max_new_tokens: 8, detokenize: false, max_running_requests: 16}"]
+
+
+@pytest.mark.timeout(600)
+def test_vl_grpo_with_the_rollout_engine_sharing_the_trainers_weights():
+    """The dedicated rollout engine serves a vision-language policy: image preprocessing and the multimodal prefill run inside the engine,
+    on the trainer's replica when both share a device."""
+    tr = _vl_trainer(_ENGINE)
+    try:
+        tr.train(num_rollouts=2)
+        rows = [r for r in tr.wandb_logger.history if "train/step" in r]
+        assert len(rows) == 2 and abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-3 and abs(rows[1]["train/ratio_mean"] - 1.0) < 1e-3
+    finally:
+        tr.shutdown()
+
+
+@pytest.mark.timeout(900)
+def test_vl_grpo_with_a_tensor_parallel_rollout_engine_over_gloo():
+    """Two workers: a data-parallel trainer and ONE tensor-parallel engine (decoder sharded over both ranks, vision tower whole on each)
+    with weights of its own, refreshed from the trainer's full tensors every step; the replay reproduces the engine's log-probs."""
+    ov = _ENGINE[:2] + ["+rollout.config={pretrained_model_ckpt_path: 'random:tiny-vl', model_precision: fp32, max_new_tokens: 8, detokenize: false, "
+                        "max_running_requests: 16, tp_size: 2, share_trainer_weights: false, tp_collectives: nccl}",
+                        "num_devices=2", "pool_backend=mp", "+rollout_parallel={tp: 2}", "batch_size=4",
+                        "+sync={_target_: unirl_b200.distributed.weight_sync.full.tensor.TensorWeightSync}"]
+    tr = _vl_trainer(ov)
+    try:
+        tr.train(num_rollouts=2, weight_sync_interval=1)
+        rows = [r for r in tr.wandb_logger.history if "train/step" in r]
+        assert len(rows) == 2 and abs(rows[0]["train/ratio_mean"] - 1.0) < 1e-3 and abs(rows[1]["train/ratio_mean"] - 1.0) < 1e-3
+        assert rows[1]["train/rollout_replay_logp_absdiff_max"] < 1e-3
+    finally:
+        tr.shutdown()

@@ -368,6 +368,8 @@ def tp_slice_spec(name: str, cfg: Qwen3Config) -> Tuple[str, Tuple[int, ...]]:
     """
     d = cfg.head_dim
     leaf = name.rsplit(".", 1)[-1]
+    if name.startswith("visual.") or ".visual." in name:  # the vision tower of a vision-language model is whole on every rank
+        return "replicate", ()
     if leaf in ("qkv_proj", "qkv_bias"):
         return "rows", (cfg.num_attention_heads * d, cfg.num_key_value_heads * d, cfg.num_key_value_heads * d)
     if leaf == "gate_up_proj":

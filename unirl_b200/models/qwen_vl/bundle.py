@@ -50,6 +50,8 @@ class QwenVLBundle(Bundle):
             for shard in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
                 sd.update(load_file(shard))
             model.load_hf_state_dict(sd)
+        if getattr(config, "freeze_vision_tower", False):
+            model.visual.requires_grad_(False)
         tok = load_tokenizer(config.tokenizer_ckpt_path or (None if random_init else path), mcfg.vocab_size, config.trust_remote_code)
         return cls(model, tok, config)
 

@@ -27,9 +27,14 @@ from unirl_b200.types.sampling import ARSamplingParams, get_ar_params
 class QwenVLPipeline(Pipeline):
     conditions_cls = QwenVLARConditions
 
-    def __init__(self, bundle: QwenVLBundle, *, detokenize: bool = True, generator_kwargs: Optional[dict] = None):
+    def __init__(self, bundle: QwenVLBundle, *, detokenize: bool = True, generator_kwargs: Optional[dict] = None, max_prompt_length: Optional[int] = None,
+                 autocast_precision: Optional[str] = None, logprob_precision: Optional[str] = None, **_ignored: Any):
+        """The precision and prompt-length options override the bundle's configuration (recipes may give them on the pipeline)."""
         super().__init__()
         self.bundle = bundle
+        for name, value in (("max_prompt_length", max_prompt_length), ("autocast_precision", autocast_precision), ("logprob_precision", logprob_precision)):
+            if value is not None and hasattr(bundle.config, name):
+                setattr(bundle.config, name, value)
         self.ar = QwenVLARStage(bundle, bundle.config.autocast_precision, bundle.config.logprob_precision, generator_kwargs)
         self.detokenize = detokenize
 

@@ -83,14 +83,26 @@ class NativeARRolloutEngine(BaseRolloutEngine):
             self.tokenizer = b.tokenizer
         else:
             mcfg = resolve_model_config(cfg.pretrained_model_ckpt_path, cfg.model_overrides) if b is None else b.transformer.cfg
-            self.model = Qwen3Transformer(mcfg, dtype=parse_torch_dtype(cfg.model_precision), device=dev, tp=tpc)
+            model_cls = type(b.transformer) if b is not None and hasattr(b.transformer, "visual") else Qwen3Transformer  # a vision-language policy keeps its vision tower
+            self.model = model_cls(mcfg, dtype=parse_torch_dtype(cfg.model_precision), device=dev, tp=tpc)
             self._init_weights(b)
             self.model.eval().requires_grad_(False)
             self.tokenizer = b.tokenizer if b is not None else load_tokenizer(cfg.tokenizer_ckpt_path, mcfg.vocab_size)
-        self.generator = ARGenerator(self.model, page_size=cfg.page_size, max_running=cfg.max_running_requests,
-                                     prefill_token_budget=cfg.prefill_token_budget, kv_cache_tokens=cfg.kv_cache_tokens,
-                                     use_cuda_graph=cfg.use_cuda_graph, poll_interval=cfg.poll_interval, seed=cfg.seed,
-                                     share_prefix=bool(getattr(cfg, "share_prefix", True)))
+        gen_kw = dict(page_size=cfg.page_size, max_running=cfg.max_running_requests, prefill_token_budget=cfg.prefill_token_budget, kv_cache_tokens=cfg.kv_cache_tokens,
+                      use_cuda_graph=cfg.use_cuda_graph, poll_interval=cfg.poll_interval, seed=cfg.seed, share_prefix=bool(getattr(cfg, "share_prefix", True)))
+        self._vl_pipeline = None
+        if hasattr(self.model, "visual"):
+            # Vision-language policy: image preprocessing, placeholder expansion and the multimodal prefill are the model package's pipeline,
+            # run here on THIS engine's model (its own, possibly tensor-parallel, weights) with this engine's generator settings.
+            import types
+
+            from unirl_b200.models.qwen_vl.pipeline import QwenVLPipeline
+
+            view = types.SimpleNamespace(transformer=self.model, tokenizer=self.tokenizer, config=b.config, model_config=self.model.cfg)
+            self._vl_pipeline = QwenVLPipeline(view, detokenize=bool(cfg.detokenize), generator_kwargs=gen_kw)
+            self.generator = self._vl_pipeline.ar.generator
+            return
+        self.generator = ARGenerator(self.model, **gen_kw)
 
     def _make_all_reduce(self):
         comm = self.tp_comm
@@ -148,6 +160,8 @@ class NativeARRolloutEngine(BaseRolloutEngine):
     def generate(self, req: RolloutReq) -> RolloutResp:
         if self._asleep:
             self.wake_up()
+        if self._vl_pipeline is not None:
+            return self._vl_pipeline.generate(req)
         cond = (req.request_conditions or {}).get("prompt")
         if not isinstance(cond, TextTokenCondition):
             texts = req.primitives.get("text")
