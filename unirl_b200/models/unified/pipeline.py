@@ -44,8 +44,10 @@ class UnifiedPipelineConfig:
     device: Any = None
     autocast_precision: str = "bf16"
     trajectory_precision: str = "fp32"
+    logprob_precision: str = "fp32"
     use_gradient_checkpointing: bool = False
     shift: float = 3.0
+    guidance_scale: float = 1.0  # default guidance of the image stage when a request does not set one
     max_prompt_length: int = 512
     negative_prompt: str = ""
     recaption: bool = False

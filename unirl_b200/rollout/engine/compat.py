@@ -32,7 +32,14 @@ FAMILIES: Dict[str, Tuple[str, str, str]] = {
     "hunyuan_video": ("unirl_b200.models.hunyuan_video.HunyuanVideoPipeline", "unirl_b200.models.hunyuan_video.HunyuanVideoPipelineConfig", "random:hunyuan-video"),
     "hunyuan_video15": ("unirl_b200.models.hunyuan_video15.HunyuanVideo15Pipeline", "unirl_b200.models.hunyuan_video15.HunyuanVideo15PipelineConfig",
                         "random:hunyuan-video15"),
+    "hunyuan_image3": ("unirl_b200.models.hunyuan_image3.HunyuanImage3Pipeline", "unirl_b200.models.hunyuan_image3.HunyuanImage3PipelineConfig", "random:hunyuan-image3"),
+    "bagel": ("unirl_b200.models.bagel.BagelPipeline", "unirl_b200.models.bagel.BagelPipelineConfig", "random:bagel-7b"),
 }
+
+# configuration class of a model family (as recipes pass it to an engine through ``model_config: ${bundle.config}``) → family
+_FAMILY_OF_CONFIG = {"SD3PipelineConfig": "sd3", "Wan21PipelineConfig": "wan21", "Wan22PipelineConfig": "wan22", "QwenImagePipelineConfig": "qwen_image",
+                     "Flux2KleinPipelineConfig": "flux2_klein", "ZImagePipelineConfig": "z_image", "HunyuanVideoPipelineConfig": "hunyuan_video",
+                     "HunyuanVideo15PipelineConfig": "hunyuan_video15", "HunyuanImage3PipelineConfig": "hunyuan_image3", "BagelPipelineConfig": "bagel"}
 
 
 # ------------------------------------------------------------------------------------------------ language-model engine
@@ -77,12 +84,13 @@ class SGLangLLMRolloutEngine(NativeARRolloutEngine):
 
 # ------------------------------------------------------------------------------------------------ diffusion engines
 def _diffusion_config(model_path: Optional[str], family: str, *, forward_batch_size: Optional[int], tp_size: Optional[int], init_same_noise: bool = False,
-                      use_cuda_graph: bool = True, share_trainer_weights: bool = False) -> NativeDiffusionEngineConfig:
+                      use_cuda_graph: bool = True, share_trainer_weights: bool = False, pipeline_overrides: Optional[Dict[str, Any]] = None) -> NativeDiffusionEngineConfig:
     if family not in FAMILIES:
         raise ValueError(f"unknown diffusion model family {family!r}; known: {sorted(FAMILIES)}")
     pipe, pcfg, preset = FAMILIES[family]
     return NativeDiffusionEngineConfig(pipeline_cls=pipe, pipeline_config_cls=pcfg, pretrained_model_ckpt_path=model_path or preset, forward_batch_size=forward_batch_size,
-                                       tp_size=int(tp_size or 1), use_cuda_graph=use_cuda_graph, share_trainer_weights=share_trainer_weights)
+                                       tp_size=int(tp_size or 1), use_cuda_graph=use_cuda_graph, share_trainer_weights=share_trainer_weights,
+                                       pipeline_overrides=dict(pipeline_overrides or {}))
 
 
 @dataclass
@@ -135,9 +143,11 @@ class VLLMOmniEngineConfig:
     forward_batch_size: Optional[int] = None
     tensor_parallel_size: Optional[int] = None
 
-    def to_native(self) -> NativeDiffusionEngineConfig:
-        return _diffusion_config(self.model_path or None, self.model_family, forward_batch_size=self.forward_batch_size,
-                                 tp_size=self.tensor_parallel_size or self.omni_extra.get("tensor_parallel_size"))
+    def to_native(self, family: Optional[str] = None) -> NativeDiffusionEngineConfig:
+        # "ar_recaption" / "dit_recaption": the two engines of a unified model, one serving its text stage and one its image stage
+        overrides = {"recaption": True} if "recaption" in str(self.modality) else {}
+        return _diffusion_config(self.model_path or None, family or self.model_family, forward_batch_size=self.forward_batch_size,
+                                 tp_size=self.tensor_parallel_size or self.omni_extra.get("tensor_parallel_size"), pipeline_overrides=overrides)
 
     def make_engine(self, **deps: Any) -> "VLLMOmniRolloutEngine":
         return VLLMOmniRolloutEngine(config=self, **deps)
@@ -152,7 +162,8 @@ class _DiffusionCompat(NativeDiffusionRolloutEngine):
         if isinstance(config, dict):
             config = self._config_cls(**config)
         if hasattr(config, "to_native"):
-            native = config.to_native()
+            family = _FAMILY_OF_CONFIG.get(type(model_config).__name__) if model_config is not None else None
+            native = config.to_native(family) if family and isinstance(config, VLLMOmniEngineConfig) else config.to_native()
             get = (lambda k: model_config.get(k)) if isinstance(model_config, dict) else (lambda k: getattr(model_config, k, None))
             if model_config is not None:
                 explicit = getattr(config, "pretrained_model_ckpt_path", None) or getattr(config, "model_path", None) or (getattr(config, "engine_kwargs", None) or {}).get("model_path")

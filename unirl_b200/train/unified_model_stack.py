@@ -24,8 +24,16 @@ logger = logging.getLogger(__name__)
 
 class UnifiedModelTrainStack(Remote):
     def __init__(self, *, fsdp_backend: Any, ar_algorithm: Optional[StageAlgorithm], image_algorithm: Optional[StageAlgorithm], ar_micro_batch_size: int = 4,
-                 image_micro_batch_size: int = 4, max_grad_norm: float = 1.0, ar_loss_weight: float = 1.0, image_loss_weight: float = 1.0) -> None:
+                 image_micro_batch_size: int = 4, max_grad_norm: float = 1.0, ar_loss_weight: float = 1.0, image_loss_weight: float = 1.0,
+                 micro_batch_size: Optional[int] = None) -> None:
+        """``micro_batch_size``: one size for both tracks (the reference's single knob); the per-track sizes apply when it is not given."""
         super().__init__()
+        if micro_batch_size is not None:
+            if int(micro_batch_size) < 1:
+                raise ValueError(f"UnifiedModelTrainStack.micro_batch_size must be at least 1, got {micro_batch_size}")
+            ar_micro_batch_size = image_micro_batch_size = int(micro_batch_size)
+        if float(max_grad_norm) <= 0.0:
+            raise ValueError(f"UnifiedModelTrainStack.max_grad_norm must be positive, got {max_grad_norm}")
         self.fsdp_backend = fsdp_backend
         self.algorithms = {"ar": ar_algorithm, "image": image_algorithm}
         self.micro = {"ar": int(ar_micro_batch_size), "image": int(image_micro_batch_size)}

@@ -12,8 +12,9 @@ def main(cfg) -> None:
     trainer = UnifiedModelTrainer(cfg=cfg, batch_size=cfg.batch_size, bundle_cfg=cfg.bundle, pipeline_cfg=cfg.pipeline, backend_cfg=cfg.backend,
                                   rollout_cfg=cfg.get("rollout"), ar_rollout_cfg=cfg.get("ar_rollout"), dit_rollout_cfg=cfg.get("dit_rollout"),
                                   enable_fsdp_offload=bool(cfg.get("enable_fsdp_offload", False)), devices_per_replica=cfg.get("devices_per_replica"),
-                                  reward_cfg=cfg.reward, ar_algorithm_cfg=cfg.get("ar_algorithm"),
-                                  image_algorithm_cfg=cfg.get("image_algorithm"), stack_cfg=cfg.stack, data_source_cfg=cfg.data_source,
+                                  reward_cfg=cfg.reward, ar_algorithm_cfg=cfg.get("ar_algorithm") or (cfg.get("algorithm") or {}).get("ar"),
+                                  image_algorithm_cfg=cfg.get("image_algorithm") or (cfg.get("algorithm") or {}).get("image"), stack_cfg=cfg.stack,
+                                  data_source_cfg=cfg.data_source,
                                   sampling_cfg=cfg.sampling, sync_cfg=cfg.get("sync"), logging_cfg=cfg.get("logging"), mode=str(cfg.get("mode", "t2i")),
                                   rollout_dump_dir=cfg.get("rollout_dump_dir") or cfg.get("dump_dir"))
     try:
