@@ -112,13 +112,13 @@ class SGLangEngineConfig:
     scheduler_port: Optional[int] = None
     engine_kwargs: Optional[Dict[str, Any]] = field(default_factory=dict)
     pretrained_model_ckpt_path: Optional[str] = None
-    share_trainer_weights: bool = False
+    share_trainer_weights: Optional[bool] = None  # None: share the trainer's replica when the engine sits on the trainer's devices and is not tensor-parallel
 
     def to_native(self) -> NativeDiffusionEngineConfig:
         kw = dict(self.engine_kwargs or {})
         path = self.pretrained_model_ckpt_path or kw.get("model_path")
         return _diffusion_config(path, self.model_family, forward_batch_size=self.forward_batch_size, tp_size=self.tp_size, init_same_noise=self.init_same_noise,
-                                 use_cuda_graph=not bool(kw.get("disable_cuda_graph", False)), share_trainer_weights=self.share_trainer_weights)
+                                 use_cuda_graph=not bool(kw.get("disable_cuda_graph", False)), share_trainer_weights=bool(self.share_trainer_weights))
 
     def make_engine(self, **deps: Any) -> "SGLangRolloutEngine":
         return SGLangRolloutEngine(config=self, **deps)
@@ -172,6 +172,8 @@ class _DiffusionCompat(NativeDiffusionRolloutEngine):
                 for name in ("model_precision", "autocast_precision", "device"):
                     if get(name) is not None:
                         setattr(native, name, get(name))
+            if getattr(config, "share_trainer_weights", None) is None and pipeline is not None and int(native.tp_size) == 1:
+                native.share_trainer_weights = True  # same devices as the trainer: one replica serves both, weight sync becomes a no-op
             config = native
         super().__init__(config=config, pipeline=pipeline)
 

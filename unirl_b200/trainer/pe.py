@@ -33,10 +33,15 @@ class PETrainer(BaseTrainer):
         self.reward_propagation, self.adv_normalization_scope, self.normalize_adv_by_std = reward_propagation, adv_normalization_scope, bool(normalize_adv_by_std)
         self.data_source = instantiate(data_source_cfg)
         self.sampling_params = instantiate(sampling_cfg)
+        # Each policy brings its own rollout engine (``ar.rollout`` / ``diffusion.rollout``).  Recipes written for the reference describe the
+        # rollout once at top level instead: a train-side engine over both stages, or a composed engine whose configuration holds the
+        # two children's engine configurations; both forms are split into the per-policy engines here.
+        top = cfg.get("rollout") if hasattr(cfg, "get") else None
+        ar_roll, dit_roll, top_extra = self._split_top_rollout(top)
         with placement(self.pool, fraction=1.0, shared_workers=True):
-            self.ar = self._build_side(ar_cfg)
-            self.diffusion = self._build_side(diffusion_cfg)
-            extra = dict(composed_cfg) if composed_cfg else {}
+            self.ar = self._build_side(ar_cfg, ar_roll)
+            self.diffusion = self._build_side(diffusion_cfg, dit_roll)
+            extra = {**top_extra, **(dict(composed_cfg) if composed_cfg else {})}
             extra.pop("_target_", None)
             self.rollout = remote(ComposedRolloutEngine, ar=self.ar["rollout"], diffusion=self.diffusion["rollout"], **extra)
             self.reward = remote_cfg(reward_cfg)
@@ -51,7 +56,37 @@ class PETrainer(BaseTrainer):
         self._shape_of = lambda d: DiTPipeline.latent_shape_for(self._spec, d)
 
     @staticmethod
-    def _build_side(side: Any) -> Dict[str, Any]:
+    def _split_top_rollout(top: Any) -> Tuple[Any, Any, Dict[str, Any]]:
+        """A top-level ``rollout`` block → ``(AR engine block, diffusion engine block, options of the composed engine)``."""
+        if top is None:
+            return None, None, {}
+        from unirl_b200.config.aliases import translate
+        from unirl_b200.config.node import to_container
+
+        block = to_container(top, resolve=True)
+        target = translate(str(block.get("_target_", "")))
+        if target.endswith("TrainsideRolloutEngine"):
+            rest = {k: v for k, v in block.items() if k not in ("_target_", "stage_attrs")}
+            return ({"_target_": target, "stage_attrs": ["ar"], **{k: v for k, v in rest.items() if k != "forward_batch_size"}},
+                    {"_target_": target, "stage_attrs": ["diffusion"], **rest}, {})
+        if target.endswith("ComposedRolloutEngine"):
+            conf = dict(block.get("config") or {})
+            children = []
+            for key in ("ar", "diffusion"):
+                child = dict(conf.get(key) or {})
+                if not child:
+                    raise ValueError(f"rollout.config.{key}: the composed engine needs its {key} child's engine configuration")
+                # ``…sglang_llm.config.SGLangLLMEngineConfig`` names the configuration; the engine class sits beside it as ``…RolloutEngine``
+                cfg_target = translate(str(child["_target_"]))
+                engine = cfg_target.replace("EngineConfig", "RolloutEngine") if "EngineConfig" in cfg_target else cfg_target
+                extra = {"model_config": block["model_config"]} if key == "diffusion" and block.get("model_config") is not None else {}
+                children.append({"_target_": engine, "config": child, **extra})
+            opts = {k: v for k, v in (("pe_marker", conf.get("pe_marker")), ("ar_system_instruction", conf.get("pe_instruction"))) if v}
+            return children[0], children[1], opts
+        raise ValueError(f"rollout._target_={target!r}: a prompt-enhancement recipe's top-level rollout is a train-side or a composed engine")
+
+    @staticmethod
+    def _build_side(side: Any, rollout_block: Any = None) -> Dict[str, Any]:
         import inspect
 
         from unirl_b200.config.instantiate import parse_cfg
@@ -62,7 +97,7 @@ class PETrainer(BaseTrainer):
         algo_params = inspect.signature(parse_cfg(side.algorithm)["role_cls"]).parameters
         algorithm = remote_cfg(side.algorithm, pipeline=pipeline, **({"backend": backend} if "backend" in algo_params else {}))
         stack = remote_cfg(side.stack, fsdp_backend=backend, algorithm=algorithm)
-        rp = parse_cfg(side.rollout)
+        rp = parse_cfg(side.rollout if "rollout" in side else rollout_block)
         params = inspect.signature(rp["role_cls"]).parameters
         extra = {"pipeline": pipeline} if "pipeline" in params else ({"bundle": bundle} if "bundle" in params else {})
         rollout = remote(**rp, **extra)
