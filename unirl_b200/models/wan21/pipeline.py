@@ -22,6 +22,14 @@ class Wan21PipelineConfig(DiTPipelineConfig):
     pretrained_model_ckpt_path: str = "random:wan21-14b"
     image_to_video: bool = False
     max_sequence_length: int = 512
+    image_encoder_ckpt_path: Optional[str] = None  # image-to-video checkpoints: where the first frame's image encoder lives (None: beside the transformer)
+
+    def __post_init__(self) -> None:
+        parent = getattr(super(), "__post_init__", None)
+        if parent is not None:
+            parent()
+        if "i2v" in str(self.pretrained_model_ckpt_path).lower():  # the published image-to-video checkpoints say so in their name
+            self.image_to_video = True
 
 
 class Wan21Bundle(DiTBundle):
