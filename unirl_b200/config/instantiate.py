@@ -47,6 +47,26 @@ def get_class(path: str) -> type:
     return obj
 
 
+def call_target(fn: Any, *pos: Any, **kw: Any) -> Any:
+    """Call a recipe target.  A configuration dataclass that declares ``__extra_fields_ok__ = True`` (the model packages' pipeline
+    configurations) also takes fields it does not declare: recipes written for the reference carry settings of its own loaders there
+    (``use_lora``, ``lora_target_modules``, ``freeze_…``).  Such fields are kept as plain attributes of the object and named once in the log."""
+    import dataclasses
+
+    if isinstance(fn, type) and dataclasses.is_dataclass(fn) and getattr(fn, "__extra_fields_ok__", False):
+        known = {f.name for f in dataclasses.fields(fn) if f.init}
+        extra = {k: kw.pop(k) for k in list(kw) if k not in known}
+        obj = fn(*pos, **kw)
+        if extra:
+            import logging
+
+            for k, v in extra.items():
+                setattr(obj, k, v)
+            logging.getLogger(__name__).info("%s: fields without a declaration kept as attributes: %s", fn.__name__, sorted(extra))
+        return obj
+    return fn(*pos, **kw)
+
+
 def instantiate(node: Any, *args: Any, _recursive_: bool = True, **overrides: Any) -> Any:
     """Build the object a ``{_target_: …}`` node describes (nested nodes first)."""
     if isinstance(node, ConfigNode):
@@ -68,7 +88,7 @@ def instantiate(node: Any, *args: Any, _recursive_: bool = True, **overrides: An
     pos = list(node.get("_args_", [])) + list(args)
     if node.get("_partial_"):
         return functools.partial(fn, *pos, **kw)
-    return fn(*pos, **kw)
+    return call_target(fn, *pos, **kw)
 
 
 def parse_cfg(cfg: Any) -> Dict[str, Any]:
@@ -84,4 +104,4 @@ def parse_cfg(cfg: Any) -> Dict[str, Any]:
 
 parse_hydra_cfg = parse_cfg
 
-__all__ = ["get_method", "get_class", "instantiate", "parse_cfg", "parse_hydra_cfg", "RESERVED"]
+__all__ = ["get_method", "get_class", "instantiate", "call_target", "parse_cfg", "parse_hydra_cfg", "RESERVED"]

@@ -17,7 +17,7 @@ from typing import Any, Dict, List, Optional, Sequence
 
 import torch
 
-from unirl_b200.config.instantiate import RESERVED, get_method
+from unirl_b200.config.instantiate import RESERVED, call_target, get_method
 from unirl_b200.distributed.group.comm import Comm, MailboxComm, init_global_group
 from unirl_b200.distributed.group.remote import RankInfo, Remote
 from unirl_b200.distributed.tensor.transport import TensorMeta, TensorTransportRuntime, WorkerLocalTransport
@@ -89,7 +89,7 @@ class Worker:
         if isinstance(value, dict):
             built = {k: self._materialize(v) for k, v in value.items() if k not in RESERVED}
             if "_target_" in value:
-                return get_method(value["_target_"])(**built)
+                return call_target(get_method(value["_target_"]), **built)
             return built
         if isinstance(value, list):
             return [self._materialize(v) for v in value]

@@ -17,6 +17,7 @@ from unirl_b200.models.dit.vae import VAEConfig
 
 @dataclass
 class DiTPipelineConfig:
+    __extra_fields_ok__ = True  # recipes may carry fields of other loaders (config.instantiate.call_target keeps them as attributes)
     pretrained_model_ckpt_path: str = "random:tiny-sd3"
     model_precision: Any = "bf16"
     device: Any = None

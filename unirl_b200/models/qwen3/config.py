@@ -12,6 +12,7 @@ from typing import Any, Dict, List, Optional
 
 @dataclass
 class Qwen3PipelineConfig:
+    __extra_fields_ok__ = True  # recipes may carry fields of other loaders (config.instantiate.call_target keeps them as attributes)
     pretrained_model_ckpt_path: str = "random:tiny"
     tokenizer_ckpt_path: Optional[str] = None
     trust_remote_code: bool = True

@@ -81,13 +81,28 @@ def _p(*shape: int, dtype: Any, device: Any) -> nn.Parameter:
 
 
 class _FFN(nn.Module):
-    def __init__(self, h: int, m: int, dtype: Any, device: Any):
+    def __init__(self, h: int, m: int, dtype: Any, device: Any, tag: str = "mlp"):
         super().__init__()
         self.gate_up, self.down = _p(2 * m, h, dtype=dtype, device=device), _p(h, m, dtype=dtype, device=device)
+        self._m, self._h, self._tag = m, h, tag
+
+    def lora_targets(self) -> Dict[str, Tuple[str, int, int]]:
+        """``<tag>.gate_proj`` / ``.up_proj`` / ``.down_proj``: ``tag`` is ``mlp`` for the shared / understanding parameters and ``mlp_moe_gen``
+        for the generation parameters of a mixture-of-transformers layer (Bagel's adapter targets name them so)."""
+        t = self._tag
+        return {f"{t}.gate_proj": ("gate_up", 0, self._m), f"{t}.up_proj": ("gate_up", self._m, self._m), f"{t}.down_proj": ("down", 0, self._h)}
+
+    def _proj(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        y = linear(x, getattr(self, name))
+        if getattr(self, "_lora_index", None):
+            from unirl_b200.train.inject import lora_apply
+
+            y = lora_apply(self, name, x, y)
+        return y
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        g, u = linear(x, self.gate_up).chunk(2, -1)
-        return linear(F.silu(g) * u, self.down)
+        g, u = self._proj(x, "gate_up").chunk(2, -1)
+        return self._proj(F.silu(g) * u, "down")
 
 
 class MoEFFN(nn.Module):
@@ -168,21 +183,26 @@ def _rotate(x: torch.Tensor, ang: torch.Tensor) -> torch.Tensor:
 class _ParamSet(nn.Module):
     """Attention + FFN weights of one layer (one set per modality under mixture-of-transformers)."""
 
-    def __init__(self, c: UnifiedConfig, dtype: Any, device: Any):
+    def __init__(self, c: UnifiedConfig, dtype: Any, device: Any, generation: bool = False):
         super().__init__()
         h, d = c.hidden_size, c.head_dim
+        self._suffix = "_moe_gen" if generation else ""  # the generation parameter set of a mixture-of-transformers layer
         self.norm1, self.norm2 = _p(h, dtype=dtype, device=device), _p(h, dtype=dtype, device=device)
         self.qkv = _p((c.num_heads + 2 * c.num_kv_heads) * d, h, dtype=dtype, device=device)
         self.q_norm, self.k_norm = _p(d, dtype=dtype, device=device), _p(d, dtype=dtype, device=device)
         self.o = _p(h, c.num_heads * d, dtype=dtype, device=device)
-        self.ffn = MoEFFN(c, dtype, device) if c.num_experts else _FFN(h, c.intermediate_size, dtype, device)
+        self.ffn = MoEFFN(c, dtype, device) if c.num_experts else _FFN(h, c.intermediate_size, dtype, device, "mlp_moe_gen" if generation else "mlp")
         self._rows = (c.num_heads * d, c.num_kv_heads * d, h)
 
     def lora_targets(self) -> Dict[str, Tuple[str, int, int]]:
         """Adapter targets of the attention projections: named row ranges of the fused weights (the unified model is trained with one
         LoRA over its shared backbone, ``unirl/trainer/unified_model.py:133``)."""
         nq, nkv, h = self._rows
-        return {"q_proj": ("qkv", 0, nq), "k_proj": ("qkv", nq, nkv), "v_proj": ("qkv", nq + nkv, nkv), "qkv": ("qkv", 0, nq + 2 * nkv), "o_proj": ("o", 0, h)}
+        x = self._suffix  # "q_proj" / "q_proj_moe_gen": a recipe may adapt the two parameter sets of a mixture-of-transformers layer separately
+        out = {f"q_proj{x}": ("qkv", 0, nq), f"k_proj{x}": ("qkv", nq, nkv), f"v_proj{x}": ("qkv", nq + nkv, nkv), f"o_proj{x}": ("o", 0, h)}
+        if not x:
+            out["qkv"] = out["qkv_proj"] = ("qkv", 0, nq + 2 * nkv)  # the fused projection under both of its usual names (ask for one)
+        return out
 
     def proj(self, x: torch.Tensor, name: str) -> torch.Tensor:
         y = linear(x, getattr(self, name))
@@ -197,7 +217,7 @@ class UnifiedLayer(nn.Module):
     def __init__(self, c: UnifiedConfig, dtype: Any, device: Any):
         super().__init__()
         self.c = c
-        self.sets = nn.ModuleList(_ParamSet(c, dtype, device) for _ in range(2 if c.modality_experts else 1))
+        self.sets = nn.ModuleList(_ParamSet(c, dtype, device, generation=bool(i)) for i in range(2 if c.modality_experts else 1))
 
     def _route(self, x: torch.Tensor, gen: Optional[torch.Tensor], fn) -> torch.Tensor:
         """Apply ``fn(param_set, tokens)`` with set 1 on generated-image tokens (``gen`` mask) and set 0 elsewhere."""

@@ -39,6 +39,7 @@ PRESETS = {"tiny-unified": UnifiedConfig.tiny, "tiny-mot": lambda: UnifiedConfig
 
 @dataclass
 class UnifiedPipelineConfig:
+    __extra_fields_ok__ = True  # recipes may carry fields of other loaders (config.instantiate.call_target keeps them as attributes)
     pretrained_model_ckpt_path: str = "random:tiny-unified"
     model_precision: Any = "bf16"
     device: Any = None

@@ -104,7 +104,8 @@ def inject_lora(model: nn.Module, *, rank: int, alpha: float, target_modules: Se
             mod._lora_index = {}
             mod._lora_active = "default"
         for target, (param_name, off, rows) in targets.items():
-            if not any(w == target or w.endswith("." + target) for w in want):
+            # a recipe's pattern may carry more of the module path than the target's name ("attn.to_q" for "to_q") or less ("gate_proj" for "mlp.gate_proj")
+            if not any(w == target or w.endswith("." + target) or target.endswith("." + w) for w in want):
                 continue
             w = getattr(mod, param_name)
             ad = LoraAdapter(w.shape[1], rows, off, rank, alpha, dropout, w.dtype, w.device)

@@ -38,14 +38,33 @@ class DiffusionTrainer(ARTrainer):
 
     def __init__(self, *, cfg: Any, bundle_cfg: Any, **kw: Any) -> None:
         super().__init__(cfg=cfg, bundle_cfg=bundle_cfg, **kw)
+        from unirl_b200.config.aliases import translate
         from unirl_b200.models.dit.config import resolve_family
         from unirl_b200.models.dit.pipeline import DiTPipeline
 
         path = str(_cfg_get(bundle_cfg, "config.pretrained_model_ckpt_path", "random:tiny-sd3"))
+        shift = _cfg_get(bundle_cfg, "config.shift")
+        target = translate(str(_cfg_get(bundle_cfg, "_target_", "")))
+        if any(f".models.{fam}." in target for fam in ("bagel", "hunyuan_image3", "unified")):
+            # a unified text-and-image model trained on its image track only: latent geometry and schedule come from its own configuration
+            self._init_unified_geometry(bundle_cfg, shift)
+            return
         self._spec = resolve_family(path, dict(_cfg_get(bundle_cfg, "config.model_overrides", {}) or {}))
         self._shape_of = lambda d: DiTPipeline.latent_shape_for(self._spec, d)
-        shift = _cfg_get(bundle_cfg, "config.shift")
-        self._policy = self._make_policy(str(_cfg_get(bundle_cfg, "_target_", "")), shift)
+        self._policy = self._make_policy(target, shift)
+
+    def _init_unified_geometry(self, bundle_cfg: Any, shift: Optional[float]) -> None:
+        from unirl_b200.config.instantiate import instantiate
+        from unirl_b200.models.dit.vae import VAEConfig
+        from unirl_b200.models.unified.pipeline import UnifiedBundle
+        from unirl_b200.sde.runtime import FlowMatchSchedulePolicy
+
+        conf = instantiate(_cfg_get(bundle_cfg, "config"))
+        mcfg = UnifiedBundle._model_config(conf)
+        factor = (VAEConfig.tiny(mcfg.latent_channels) if mcfg.hidden_size <= 256 else VAEConfig(latent_channels=mcfg.latent_channels)).spatial_factor
+        self._spec = None
+        self._shape_of = lambda d: (int(mcfg.latent_channels), int(d.height) // factor, int(d.width) // factor)
+        self._policy = FlowMatchSchedulePolicy(shift=float(shift if shift is not None else getattr(conf, "shift", 3.0)), vae_scale_factor=factor, patch_size=mcfg.patch_size)
 
     def _make_policy(self, bundle_target: str, shift: Optional[float]) -> Any:
         from unirl_b200.sde.runtime import FlowMatchSchedulePolicy
