@@ -213,3 +213,23 @@ def test_qwen_image_text_stage_with_a_language_model_tower():
     # the pipeline's own stage (stand-in tower of the random preset) follows the same contract
     e2 = pipe.text_embed.embed(prompts)
     assert e2.embeds.shape[:2] == emb.embeds.shape[:2] and e2.pooled is None
+
+
+@pytest.mark.timeout(600)
+def test_engine_with_its_own_pipeline_samples_with_the_strategy_named_on_the_trainers_pipeline():
+    """``pipeline.strategy`` names a step strategy other than the family's default; the sampler engine has a pipeline of its own.  The
+    engine's emitted log-probs are the PPO anchor (``old_logp_source: rollout``), so the first update is on-policy only if the engine
+    sampled with the same strategy the trainer replays with."""
+    ov = ["rollout._target_=unirl_b200.rollout.engine.native_diffusion.engine.NativeDiffusionRolloutEngine", "~rollout.stage_attrs",
+          "+rollout.config={pipeline_cls: unirl_b200.models.sd3.pipeline.SD3Pipeline, pipeline_config_cls: unirl_b200.models.sd3.config.SD3PipelineConfig, "
+          "pretrained_model_ckpt_path: 'random:tiny-sd3', model_precision: fp32, autocast_precision: fp32, device: cpu, share_trainer_weights: false}",
+          "+sync={_target_: unirl_b200.distributed.weight_sync.full.tensor.TensorWeightSync}", "pipeline._target_=unirl_b200.models.sd3.pipeline.SD3Pipeline",
+          "+pipeline.strategy={_target_: unirl_b200.sde.kernels.FlowSDEStrategy}", "algorithm.old_logp_source=rollout"]
+    tr = _trainer(ov)
+    try:
+        assert tr._strategy_name in ("flow", "sde")
+        tr.train(num_rollouts=1, weight_sync_interval=1)
+        row = [r for r in tr.wandb_logger.history if "train/step" in r][0]
+        assert abs(row["train/ratio_mean"] - 1.0) < 1e-4, row["train/ratio_mean"]
+    finally:
+        tr.shutdown()

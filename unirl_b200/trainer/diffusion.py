@@ -44,6 +44,10 @@ class DiffusionTrainer(ARTrainer):
 
         path = str(_cfg_get(bundle_cfg, "config.pretrained_model_ckpt_path", "random:tiny-sd3"))
         shift = _cfg_get(bundle_cfg, "config.shift")
+        # A recipe may name the SDE step strategy on the TRAINER's pipeline (``pipeline.strategy``).  A rollout engine with a pipeline of its
+        # own would otherwise sample with its family's default while the trainer replays with the named one, and the two sets of log-probs
+        # would describe different transitions: the strategy therefore travels on every request.
+        self._strategy_name = self._strategy_of(kw.get("pipeline_cfg"))
         target = translate(str(_cfg_get(bundle_cfg, "_target_", "")))
         if any(f".models.{fam}." in target for fam in ("bagel", "hunyuan_image3", "unified")):
             # a unified text-and-image model trained on its image track only: latent geometry and schedule come from its own configuration
@@ -52,6 +56,20 @@ class DiffusionTrainer(ARTrainer):
         self._spec = resolve_family(path, dict(_cfg_get(bundle_cfg, "config.model_overrides", {}) or {}))
         self._shape_of = lambda d: DiTPipeline.latent_shape_for(self._spec, d)
         self._policy = self._make_policy(target, shift)
+
+    @staticmethod
+    def _strategy_of(pipeline_cfg: Any) -> Optional[str]:
+        node = _cfg_get(pipeline_cfg, "strategy") if pipeline_cfg is not None else None
+        if node is None:
+            return None
+        if isinstance(node, str):
+            return node
+        from unirl_b200.config.instantiate import get_method
+        from unirl_b200.sde.kernels import STRATEGIES
+
+        target = _cfg_get(node, "_target_")
+        cls = get_method(str(target)) if target else None
+        return next((name for name, c in STRATEGIES.items() if c is cls), None)
 
     def _init_unified_geometry(self, bundle_cfg: Any, shift: Optional[float]) -> None:
         from unirl_b200.config.instantiate import instantiate
@@ -84,6 +102,8 @@ class DiffusionTrainer(ARTrainer):
         inputs = inputs.expand(sp.samples_per_prompt)
         sde = d.resolve_sde_indices(rollout_id)
         sp = dataclasses.replace(sp, sde_indices=list(sde)) if dataclasses.is_dataclass(sp) and hasattr(sp, "sde_indices") else sp
+        if getattr(self, "_strategy_name", None) and dataclasses.is_dataclass(sp) and hasattr(sp, "sde_strategy") and sp.sde_strategy is None:
+            sp = dataclasses.replace(sp, sde_strategy=self._strategy_name)
         d = get_diffusion_params(sp)
         sigmas = self._policy.compute_sigma(num_inference_steps=int(d.num_inference_steps), height=int(d.height), width=int(d.width))
         gids = list(inputs.group_ids if d.init_same_noise else inputs.sample_ids)
