@@ -161,3 +161,16 @@ def test_lora_sync_into_a_tp2_engine_over_gloo():
         _assert_lora_engine_follows_trainer(tr)
     finally:
         tr.shutdown()
+
+
+def test_separate_layout_on_one_device_is_refused_with_a_message():
+    cfg = compose("ar/tiny_qwen3_grpo_cpu", overrides=["num_devices=1", "+pool_backend=inline"])
+    with pytest.raises(ValueError, match="separate layout needs at least one device"):
+        _trainer(cfg)
+
+
+def test_ipc_sync_accepts_the_shared_memory_switch_of_reference_recipes():
+    from unirl_b200.distributed.weight_sync.full.ipc import IPCWeightSync
+
+    sync = IPCWeightSync(backend=None, rollout=None, bucket_size_mb=4, lora_merged=True, use_shm=True)
+    assert sync.use_shm is True and sync._bucket_bytes == 4 << 20

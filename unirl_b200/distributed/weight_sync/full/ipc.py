@@ -19,8 +19,12 @@ from unirl_b200.distributed.weight_sync.full.base import FullWeightSync
 
 
 class IPCWeightSync(FullWeightSync):
-    def __init__(self, *a, staging_size_mb: int = 2048, **k) -> None:
+    def __init__(self, *a, staging_size_mb: int = 2048, use_shm: bool = False, **k) -> None:
+        """``use_shm`` is the reference's choice between a CUDA-IPC buffer and host shared memory for a receiver in another process
+        (``unirl/distributed/weight_sync/full/ipc.py:46``); sender and receiver share one process here, so both values take the same
+        device staging buffer and the field is only recorded."""
         super().__init__(*a, **k)
+        self.use_shm = bool(use_shm)
         self._staging_bytes = int(staging_size_mb) * 1024 * 1024
         self._staging: Dict[torch.dtype, torch.Tensor] = {}
 

@@ -67,6 +67,8 @@ class ARTrainer(BaseTrainer):
                     self.weight_sync = remote_cfg(sync_cfg, backend=self.backend, rollout=self.rollout)
         else:
             n_roll = max(1, int(round(self.pool.num_devices * rollout_fraction)))
+            if n_roll >= self.pool.num_devices:
+                raise ValueError(f"a separate layout needs at least one device for each of trainer and engine: {self.pool.num_devices} device(s), {n_roll} for the engine")
             with placement(self.pool, num_devices=self.pool.num_devices - n_roll):
                 self._build_train_roles(bundle_cfg, pipeline_cfg, backend_cfg, algorithm_cfg, stack_cfg)
                 if sync_cfg is not None:
