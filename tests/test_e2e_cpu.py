@@ -174,3 +174,10 @@ def test_ipc_sync_accepts_the_shared_memory_switch_of_reference_recipes():
 
     sync = IPCWeightSync(backend=None, rollout=None, bucket_size_mb=4, lora_merged=True, use_shm=True)
     assert sync.use_shm is True and sync._bucket_bytes == 4 << 20
+
+
+def test_full_sync_reads_the_older_field_spellings_some_reference_recipes_carry():
+    from unirl_b200.distributed.weight_sync.full.nccl import NCCLWeightSync
+
+    sync = NCCLWeightSync(backend=None, use_merged=True, param_name_prefix="transformer.", target_modules=["transformer"], group_name="weight_sync")
+    assert sync._lora_merged is True and sync._track_prefix == "transformer." and sync.target_modules == ["transformer"]

@@ -49,8 +49,15 @@ def apply_name_remap(name: str, rules: Dict[str, Optional[str]]) -> Optional[str
 
 class FullWeightSync(Remote):
     def __init__(self, *, backend: Any, rollout: Any = None, bucket_size_mb: int = 512, flush_cache: bool = True, lora_merged: bool = False,
-                 name_remap: Optional[Dict[str, Optional[str]]] = None, track_prefix: str = "", wire_dtype: Any = None) -> None:
+                 name_remap: Optional[Dict[str, Optional[str]]] = None, track_prefix: str = "", wire_dtype: Any = None,
+                 use_merged: Optional[bool] = None, param_name_prefix: Optional[str] = None, target_modules: Any = None) -> None:
+        """The last three are earlier spellings that some recipes of the reference still carry (its
+        ``examples/diffusion/hunyuan_video15_t2v_vllmomni_nccl_separate.yaml:214-221``): ``use_merged`` is ``lora_merged``,
+        ``param_name_prefix`` is ``track_prefix``, and ``target_modules`` named the one module this class always sends."""
         super().__init__()
+        lora_merged = bool(lora_merged) if use_merged is None else bool(use_merged)
+        track_prefix = track_prefix or (param_name_prefix or "")
+        self.target_modules = None if target_modules is None else list(target_modules)
         self._backend, self._rollout = backend, rollout
         self._bucket_bytes = int(bucket_size_mb) * 1024 * 1024
         self._flush_cache, self._lora_merged = bool(flush_cache), bool(lora_merged)
