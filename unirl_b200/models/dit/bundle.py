@@ -15,6 +15,7 @@ from unirl_b200.models.dit.config import DiTPipelineConfig, FamilySpec, resolve_
 from unirl_b200.models.dit.modeling import DiTTransformer
 from unirl_b200.models.dit.text_encoder import TextEncoder
 from unirl_b200.models.dit.vae import LatentVAE
+from unirl_b200.models.dit.vae_wan import AutoencoderKLWan, is_wan_vae
 from unirl_b200.models.tokenizer import load_tokenizer
 from unirl_b200.models.types import Bundle
 from unirl_b200.sde.runtime import FlowMatchSchedulePolicy
@@ -97,10 +98,13 @@ class DiTBundle(Bundle):
                 encoders.append(TextEncoder(c, dtype=dtype, device=device).init_weights(config.init_seed + 1 + i))
                 toks.append(load_tokenizer(None, c.vocab_size, True))
         vae_dir = None if path.startswith("random:") else os.path.join(path, "vae")
-        if vae_dir and os.path.exists(os.path.join(vae_dir, "config.json")) and _is_image_kl(vae_dir):
+        has_vae = bool(vae_dir) and os.path.exists(os.path.join(vae_dir, "config.json"))
+        if has_vae and _is_image_kl(vae_dir):
             from unirl_b200.models.dit.vae_kl import AutoencoderKL
 
             vae = AutoencoderKL.from_hf(vae_dir, device=device)  # fp32, as the codec is used
+        elif has_vae and is_wan_vae(vae_dir):
+            vae = AutoencoderKLWan.from_hf(vae_dir, device=device)  # the causal 3-D codec of WAN 2.1 / 2.2-14B and Qwen-Image
         else:
             vae = LatentVAE(spec.vae, device=device).init_weights(config.init_seed + 7)
         return cls(model, encoders, vae, toks, config, spec)

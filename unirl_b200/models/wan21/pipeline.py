@@ -47,12 +47,21 @@ class Wan21Bundle(DiTBundle):
         return b
 
     def first_frame_condition(self, image: torch.Tensor, num_latent_frames: int) -> ImageLatentCondition:
-        """``image [B, 3, H, W]`` in [0, 1] → ``[B, 20, F, h, w]``: mask (first latent frame = 1) ++ encoded frame padded with zeros."""
-        z = self.vae.encode(image)  # [B, 16, h, w]
-        b, c, h, w = z.shape
-        lat = torch.zeros(b, c, num_latent_frames, h, w, dtype=z.dtype, device=z.device)
-        lat[:, :, 0] = z
-        mask = torch.zeros(b, 4, num_latent_frames, h, w, dtype=z.dtype, device=z.device)
+        """``image [B, 3, H, W]`` in [0, 1] → ``[B, 20, F, h, w]``: mask (first latent frame = 1) ++ the codec's latents of the clip
+        "this frame, then grey" (``unirl/models/wan21/image_encode.py:75-125``: the published codec is causal in time, so the grey frames
+        encode to latents that depend on the first frame; a codec without a video encoder pads the encoded frame with zeros)."""
+        if hasattr(self.vae, "encode_video"):
+            t = (num_latent_frames - 1) * self.vae.cfg.temporal_factor + 1
+            clip = torch.full((image.shape[0], 3, t, *image.shape[-2:]), 0.5, dtype=image.dtype, device=image.device)  # 0 on the codec's [-1, 1] scale
+            clip[:, :, 0] = image
+            lat = self.vae.encode_video(clip)
+            b, c, _, h, w = lat.shape
+        else:
+            z = self.vae.encode(image)  # [B, 16, h, w]
+            b, c, h, w = z.shape
+            lat = torch.zeros(b, c, num_latent_frames, h, w, dtype=z.dtype, device=z.device)
+            lat[:, :, 0] = z
+        mask = torch.zeros(b, 4, num_latent_frames, h, w, dtype=lat.dtype, device=lat.device)
         mask[:, :, 0] = 1.0
         return ImageLatentCondition(latents=torch.cat([mask, lat], 1))
 
