@@ -233,3 +233,29 @@ def test_engine_with_its_own_pipeline_samples_with_the_strategy_named_on_the_tra
         assert abs(row["train/ratio_mean"] - 1.0) < 1e-4, row["train/ratio_mean"]
     finally:
         tr.shutdown()
+
+
+def test_image_to_video_request_carries_its_condition_images_into_rollout_and_replay():
+    """WAN image-to-video: ``primitives["image"]`` (one picture per sample) becomes the mask + first-frame latents beside the noisy
+    latents; the track keeps that condition, replay with it reproduces the rollout, and another picture gives another sample."""
+    from unirl_b200.models.wan21.pipeline import Wan21Pipeline, Wan21PipelineConfig
+    from unirl_b200.types.primitives import Images
+
+    pipe = Wan21Pipeline.from_config(Wan21PipelineConfig(pretrained_model_ckpt_path="random:tiny-wan", model_precision="fp32", autocast_precision="fp32", device="cpu",
+                                                         image_to_video=True))
+    req = _req(num_frames=9)
+    g = torch.Generator().manual_seed(4)
+    pics = torch.rand(3, 3, 48, 80, generator=g)  # another size than the request's: resized to height x width
+    req.primitives["image"] = Images(pixels=pics)
+    tr = pipe.generate(req).tracks["diffusion"]
+    c = pipe.latent_shape(req.sampling_params)[0]
+    img = tr.conditions["image"].latents
+    assert img.shape == (3, 4 + c, 3, 8, 8) and bool((img[:, :4, 0] == 1).all()) and bool((img[:, :4, 1:] == 0).all())
+    assert float((img[0, 4:, 0] - img[2, 4:, 0]).abs().max()) > 1e-4
+    seg = tr.segment
+    out = pipe.diffusion.replay(DiTConditions.from_dict(tr.conditions), segment=seg, params=DiTDiffusionParams(guidance_scale=3.0, true_cfg=True))
+    assert float((out.log_probs.detach() - seg.sde_logp).abs().max()) < 1e-5
+    req2 = _req(num_frames=9)
+    req2.primitives["image"] = Images(pixels=pics.flip(0))
+    other = pipe.generate(req2).tracks["diffusion"].segment
+    assert float((other.latents[:, -1] - seg.latents[:, -1]).abs().max()) > 1e-4

@@ -149,16 +149,16 @@ def test_clip_text_tower_matches_transformers(tmp_path, act, proj):
     torch.testing.assert_close(enc(ids)[0], out.last_hidden_state, rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("umt5", [False, True])
-def test_t5_encoder_matches_transformers(tmp_path, umt5):
+@pytest.mark.parametrize("umt5,d_kv", [(False, 8), (True, 8), (False, 6)])
+def test_t5_encoder_matches_transformers(tmp_path, umt5, d_kv):
     """T5 v1.1 (one shared relative-position table) and UMT5 (one per layer) encoders: hidden states agree with ``transformers``,
-    padding masked."""
+    padding masked; the third case has heads narrower than width / heads, as the byte-level ByT5 glyph encoder does."""
     from transformers import T5Config, T5EncoderModel, UMT5Config, UMT5EncoderModel
 
     from unirl_b200.models.dit.text_keys import load_hf_text_encoder
 
     torch.manual_seed(1)
-    kw = dict(vocab_size=120, d_model=32, d_kv=8, d_ff=48, num_layers=3, num_heads=4, relative_attention_num_buckets=8, relative_attention_max_distance=20,
+    kw = dict(vocab_size=120, d_model=32, d_kv=d_kv, d_ff=48, num_layers=3, num_heads=4, relative_attention_num_buckets=8, relative_attention_max_distance=20,
               feed_forward_proj="gated-gelu", dropout_rate=0.0)
     hf = (UMT5EncoderModel(UMT5Config(**kw)) if umt5 else T5EncoderModel(T5Config(**kw))).eval()
     with torch.no_grad():  # the library initialises some tables identically across layers: make every tensor distinct
@@ -166,7 +166,7 @@ def test_t5_encoder_matches_transformers(tmp_path, umt5):
             p.add_(torch.randn_like(p) * 0.05)
     hf.save_pretrained(tmp_path)
     enc, cfg = load_hf_text_encoder(str(tmp_path), dtype=torch.float32)
-    assert cfg.rel_bias_per_layer == umt5 and cfg.kind == "t5"
+    assert cfg.rel_bias_per_layer == umt5 and cfg.kind == "t5" and cfg.head_dim == (0 if d_kv == 8 else d_kv) and cfg.eos_token_id == 1
     ids = torch.randint(1, 120, (2, 23))
     mask = torch.ones(2, 23, dtype=torch.long)
     mask[1, 15:] = 0
@@ -263,3 +263,26 @@ def test_qwen_image_bundle_loads_its_language_model_tower_from_the_checkpoint(tm
         want = hf(input_ids=ids).last_hidden_state[:, len(tok.encode(PROMPT_PREFIX)):][:, :64]
     torch.testing.assert_close(emb.embeds, want, rtol=1e-4, atol=2e-5)
     assert emb.pooled is None and int(emb.attn_mask.sum()) == want.shape[1]
+
+
+def test_clip_vision_tower_matches_transformers(tmp_path):
+    """The image encoder of the WAN image-to-video checkpoints: penultimate hidden states agree with ``transformers``' ``CLIPVisionModel``."""
+    from transformers import CLIPVisionConfig as HFConfig
+    from transformers import CLIPVisionModel
+
+    from unirl_b200.models.dit.clip_vision import CLIPVisionTower
+
+    torch.manual_seed(5)
+    hf = CLIPVisionModel(HFConfig(hidden_size=32, intermediate_size=48, num_hidden_layers=3, num_attention_heads=4, image_size=28, patch_size=14, hidden_act="gelu")).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+    hf.save_pretrained(tmp_path)
+    tower = CLIPVisionTower.from_hf(str(tmp_path), dtype=torch.float32)
+    assert tower.cfg.num_tokens == 5
+    px = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        want = hf(pixel_values=px, output_hidden_states=True).hidden_states[-2]
+    torch.testing.assert_close(tower(px), want, rtol=1e-4, atol=1e-5)
+    pics = torch.rand(2, 3, 40, 60)
+    assert tower.encode(pics).shape == (2, 5, 32) and abs(float(tower.preprocess(torch.full((1, 3, 28, 28), 0.48145466))[0, 0].mean())) < 1e-6

@@ -117,9 +117,9 @@ PRESETS: Dict[str, Callable[[], FamilySpec]] = {
     "hunyuan-video15": lambda: FamilySpec(
         DiTConfig(name="hunyuan-video15", hidden_size=2048, num_heads=16, head_dim=128, in_channels=65, out_channels=32, patch_size=(1, 1, 1), num_joint_blocks=54, text_dim=3584,
                   pooled_dim=0, rope_axes=(16, 56, 56), is_video=True),
-        [TextEncoderConfig("llm", 151936, 3584, 28, 28, 18944, 1000, 0, False)], "single", VAEConfig(latent_channels=32, channel_mult=(1, 2, 4, 4, 4)), 7.0, False, "flow"),
+        [TextEncoderConfig("llm", 151936, 3584, 28, 28, 18944, 1000, 0, False), TextEncoderConfig.byt5_small()], "llm+glyph", VAEConfig(latent_channels=32, channel_mult=(1, 2, 4, 4, 4)), 7.0, False, "flow"),
     "tiny-hunyuan-video15": lambda: FamilySpec(_tiny("tiny-hunyuan-video15", in_channels=9, out_channels=4, patch_size=(1, 1, 1), pooled_dim=0, is_video=True),
-                                               [TextEncoderConfig.tiny("llm")], "single", VAEConfig.tiny(), 7.0, False, "flow"),
+                                               [TextEncoderConfig.tiny("llm"), TextEncoderConfig.tiny("t5", hidden=16)], "llm+glyph", VAEConfig.tiny(), 7.0, False, "flow"),
     "tiny-hunyuan-video": lambda: FamilySpec(_tiny("tiny-hunyuan-video", num_joint_blocks=1, num_single_blocks=1, guidance_embed=True, is_video=True),
                                              [TextEncoderConfig.tiny("llm"), TextEncoderConfig.tiny("clip")], "llm+clip", VAEConfig.tiny(), 7.0, False, "flow"),
 }

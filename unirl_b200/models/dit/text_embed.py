@@ -4,6 +4,8 @@
 ``combine="sd3"``       CLIP-L and CLIP-G penultimate hidden states concatenated channel-wise, zero-padded to the T5
                         width and prepended to the T5 sequence; pooled = [CLIP-L pooled, CLIP-G pooled].
 ``combine="llm+clip"``  LLM hidden states as the sequence, CLIP pooled vector as the pooled conditioning (HunyuanVideo).
+``combine="llm+glyph"`` LLM hidden states ++ a byte-level glyph encoder's hidden states of the prompt's quoted snippets, zero-padded
+                        to the LLM width, along the token axis (HunyuanVideo-1.5; its own stage adds the chat template).
 
 Identical prompts in a batch are encoded once (a GRPO batch repeats each prompt ``samples_per_prompt`` times).
 Parity: ``unirl/models/sd3/text_embed.py:51-140`` (triple encoder + dedupe), ``unirl/models/wan21/text_embed.py``.
@@ -11,6 +13,7 @@ Parity: ``unirl/models/sd3/text_embed.py:51-140`` (triple encoder + dedupe), ``u
 
 from __future__ import annotations
 
+import re
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -20,17 +23,57 @@ from unirl_b200.types.conditions import TextEmbedCondition
 from unirl_b200.types.primitives import Texts
 
 
+_QUOTED = re.compile(r"\"(.*?)\"|\u201c(.*?)\u201d")
+
+
+def glyph_text(prompt: str) -> Optional[str]:
+    """Quoted snippets of ``prompt`` (straight or curly quotes) as ``Text "a". Text "b". `` — first occurrences, in order; ``None``
+    without any (``unirl/models/hunyuan_video15/text_embed.py:56-72``)."""
+    found = [a or b for a, b in _QUOTED.findall(prompt or "")]
+    found = list(dict.fromkeys(found)) if len(found) > 1 else found
+    return (". ".join(f'Text "{t}"' for t in found) + ". ") if found else None
+
+
 class TextEmbedStage:
     def __init__(self, encoders: Sequence[Any], tokenizers: Sequence[Any], combine: str = "single", text_dim: Optional[int] = None,
-                 max_sequence_length: int = 256):
+                 max_sequence_length: int = 256, glyph_max_length: int = 256):
         self.encoders, self.tokenizers, self.combine = list(encoders), list(tokenizers), combine
         self.text_dim = text_dim
         self.max_sequence_length = int(max_sequence_length)
+        self.glyph_max_length = int(glyph_max_length)
+
+    def append_glyph_stream(self, strs: List[str], seq: torch.Tensor, mask: torch.Tensor, k: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``seq [B, L, D]`` / ``mask [B, L]`` of the prompts ``strs`` ++ the glyph encoder's (``encoders[k]``) hidden states of each
+        prompt's quoted snippets, zero-padded to ``D``, along the token axis; a prompt without quotes contributes masked zeros."""
+        enc = self.encoders[k]
+        if enc.cfg.hidden_size > seq.shape[-1]:
+            raise ValueError(f"the glyph encoder is wider ({enc.cfg.hidden_size}) than the conditioning sequence ({seq.shape[-1]})")
+        glyphs = [glyph_text(s) for s in strs]
+        some = [g for g in dict.fromkeys(glyphs) if g is not None]
+        g_len = 1
+        if some:
+            cap, self.max_sequence_length = self.max_sequence_length, self.glyph_max_length
+            try:
+                g_all, _, m_all = self._encode_one(k, some)
+            finally:
+                self.max_sequence_length = cap
+            g_all = g_all * m_all.unsqueeze(-1).to(g_all.dtype)
+            g_len = g_all.shape[1]
+        g_seq, g_mask = seq.new_zeros(len(strs), g_len, seq.shape[-1]), mask.new_zeros(len(strs), g_len)
+        for i, g in enumerate(glyphs):
+            if g is not None:
+                j = some.index(g)
+                g_seq[i, :, : g_all.shape[-1]] = g_all[j].to(g_seq.dtype)
+                g_mask[i] = m_all[j].to(g_mask.dtype)
+        return torch.cat([seq, g_seq], 1), torch.cat([mask, g_mask], 1)
 
     def _tokenize(self, tok: Any, texts: List[str], max_len: int, eos: int, vocab: int) -> Tuple[torch.Tensor, torch.Tensor]:
         rows = []
         for t in texts:
-            ids = [int(i) % vocab for i in tok.encode(t)][: max_len - 1] + [eos]
+            ids = [int(i) % vocab for i in tok.encode(t)]
+            if ids and ids[-1] == eos:  # a tokenizer that closes the sequence itself: one end marker, not two
+                ids = ids[:-1]
+            ids = ids[: max_len - 1] + [eos]
             rows.append(ids)
         width = max(len(r) for r in rows)
         ids = torch.zeros(len(rows), width, dtype=torch.long)
@@ -72,6 +115,11 @@ class TextEmbedStage:
         elif self.combine == "llm+clip":
             seq, _, mask = self._encode_one(0, ulist)
             _, pooled, _ = self._encode_one(1, ulist)
+        elif self.combine == "llm+glyph":
+            seq, pooled, mask = self._encode_one(0, ulist)
+            if self.text_dim and seq.shape[-1] < self.text_dim:
+                seq = F.pad(seq, (0, self.text_dim - seq.shape[-1]))
+            seq, mask = self.append_glyph_stream(ulist, seq * mask.unsqueeze(-1).to(seq.dtype), mask)
         else:
             raise ValueError(f"unknown text combine mode {self.combine!r}")
         if self.text_dim and seq.shape[-1] != self.text_dim:

@@ -40,6 +40,7 @@ class TextEncoderConfig:
     eps: float = 1e-6
     act: str = "gelu"  # CLIP MLP activation: "gelu" (open_clip bigG) | "quick_gelu" (OpenAI CLIP-L)
     rel_bias_per_layer: bool = False  # UMT5: every layer owns a relative-position table (T5: the first layer's is shared)
+    head_dim: int = 0  # 0: hidden_size / num_heads; ByT5 has 6 heads of 64 on a width of 1472
 
     @classmethod
     def clip_l(cls) -> "TextEncoderConfig":
@@ -52,6 +53,11 @@ class TextEncoderConfig:
     @classmethod
     def t5_xxl(cls) -> "TextEncoderConfig":
         return cls("t5", 32128, 4096, 24, 64, 10240, 256, 0, False)
+
+    @classmethod
+    def byt5_small(cls) -> "TextEncoderConfig":
+        """The byte-level glyph encoder of HunyuanVideo-1.5 (``google/byt5-small`` geometry: bytes + 3 special ids, EOS = 1)."""
+        return cls("t5", 384, 1472, 12, 6, 3584, 256, 0, False, eos_token_id=1, head_dim=64)
 
     @classmethod
     def umt5_xxl(cls) -> "TextEncoderConfig":
@@ -70,8 +76,9 @@ class _Layer(nn.Module):
         norm = (lambda: nn.LayerNorm(h, eps=1e-5, dtype=dtype, device=device)) if c.kind == "clip" else (lambda: nn.RMSNorm(h, eps=c.eps, dtype=dtype, device=device))
         self.norm1, self.norm2 = norm(), norm()
         bias = c.kind == "clip"
-        self.qkv = nn.Linear(h, 3 * h, bias=bias, dtype=dtype, device=device)
-        self.out = nn.Linear(h, h, bias=bias, dtype=dtype, device=device)
+        inner = (c.head_dim * c.num_heads) if c.head_dim else h
+        self.qkv = nn.Linear(h, 3 * inner, bias=bias, dtype=dtype, device=device)
+        self.out = nn.Linear(inner, h, bias=bias, dtype=dtype, device=device)
         self.fc1 = nn.Linear(h, c.ffn_dim * (1 if c.kind == "clip" else 2), bias=bias, dtype=dtype, device=device)
         self.fc2 = nn.Linear(c.ffn_dim, h, bias=bias, dtype=dtype, device=device)
         self.rel_bias = nn.Embedding(c.rel_buckets, c.num_heads, dtype=dtype, device=device) if (c.kind == "t5" and c.rel_bias_per_layer) else None
@@ -81,7 +88,7 @@ class _Layer(nn.Module):
         q, k, v = self.qkv(self.norm1(x)).view(b, l, 3, self.c.num_heads, -1).permute(2, 0, 3, 1, 4)
         scale = None if self.c.kind != "t5" else 1.0  # T5 folds the scale into its initialisation
         a = F.scaled_dot_product_attention(q, k, v, attn_mask=bias, scale=scale)
-        x = x + self.out(a.transpose(1, 2).reshape(b, l, h))
+        x = x + self.out(a.transpose(1, 2).reshape(b, l, -1))
         y = self.fc1(self.norm2(x))
         if self.c.kind == "clip":
             y = y * torch.sigmoid(1.702 * y) if self.c.act == "quick_gelu" else F.gelu(y)

@@ -29,13 +29,12 @@ def config_from_hf(cfg: Dict[str, Any]) -> TextEncoderConfig:
                                  eos_token_id=int(cfg.get("eos_token_id", 49407)), act=str(cfg.get("hidden_act", "quick_gelu")))
     if "t5" in mt:
         heads, d_kv, d_model = int(cfg["num_heads"]), int(cfg["d_kv"]), int(cfg["d_model"])
-        if heads * d_kv != d_model:
-            raise ValueError(f"T5 encoder with num_heads * d_kv = {heads * d_kv} != d_model = {d_model} is not supported by the native encoder")
         if "gated" not in str(cfg.get("feed_forward_proj", "gated-gelu")):
             raise ValueError("only the gated-GELU T5 variants (v1.1, UMT5) are supported")
         return TextEncoderConfig("t5", int(cfg["vocab_size"]), d_model, int(cfg["num_layers"]), heads, int(cfg["d_ff"]), 512, 0, False,
                                  rel_buckets=int(cfg.get("relative_attention_num_buckets", 32)), rel_max_distance=int(cfg.get("relative_attention_max_distance", 128)),
-                                 eps=float(cfg.get("layer_norm_epsilon", 1e-6)), rel_bias_per_layer="umt5" in mt)
+                                 eps=float(cfg.get("layer_norm_epsilon", 1e-6)), rel_bias_per_layer="umt5" in mt, eos_token_id=int(cfg.get("eos_token_id", 1)),
+                                 head_dim=0 if heads * d_kv == d_model else d_kv)
     raise ValueError(f"no text-encoder bridge for model_type {mt!r}")
 
 

@@ -39,12 +39,15 @@ class QwenImageBundle(DiTBundle):
 
 
 class QwenImageTextEmbedStage(TextEmbedStage):
-    """Chat-templated prompt → language-model hidden states, system prefix cut off, zero-padded to the batch maximum with a mask."""
+    """Chat-templated prompt → language-model hidden states, system prefix cut off, zero-padded to the batch maximum with a mask.
+    ``prefix`` / ``suffix`` / ``token_cap`` are class attributes so that a family with another template derives from this stage."""
+
+    prefix, suffix, token_cap = PROMPT_PREFIX, PROMPT_SUFFIX, TOKENIZER_MAX_LENGTH
 
     def __init__(self, *a: Any, use_template: bool = True, **k: Any):
         super().__init__(*a, **k)
-        if self.max_sequence_length > TOKENIZER_MAX_LENGTH:
-            raise ValueError(f"max_sequence_length cannot exceed {TOKENIZER_MAX_LENGTH} (the tokenizer's cap), got {self.max_sequence_length}")
+        if self.max_sequence_length > self.token_cap:
+            raise ValueError(f"max_sequence_length cannot exceed {self.token_cap} (the tokenizer's cap), got {self.max_sequence_length}")
         self.use_template = bool(use_template)
 
     @torch.no_grad()
@@ -55,11 +58,11 @@ class QwenImageTextEmbedStage(TextEmbedStage):
         enc, tok = self.encoders[0], self.tokenizers[0]
         c = enc.cfg
         dev = next(enc.parameters()).device
-        crop = len(tok.encode(PROMPT_PREFIX))  # 34 with the published tokenizer
+        crop = len(tok.encode(self.prefix))  # Qwen-Image: 34 with the published tokenizer
         uniq: Dict[str, int] = {}
         for s in strs:
             uniq.setdefault(s, len(uniq))
-        rows = [[int(i) % c.vocab_size for i in tok.encode(PROMPT_PREFIX + s + PROMPT_SUFFIX)][: TOKENIZER_MAX_LENGTH + crop] for s in uniq]
+        rows = [[int(i) % c.vocab_size for i in tok.encode(self.prefix + (s or " ") + self.suffix)][: self.token_cap + crop] for s in uniq]
         width = max(len(r) for r in rows)
         ids = torch.zeros(len(rows), width, dtype=torch.long)
         mask = torch.zeros(len(rows), width, dtype=torch.long)

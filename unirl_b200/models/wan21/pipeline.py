@@ -71,6 +71,19 @@ class Wan21Pipeline(DiTPipeline):
     def from_config(cls, config: Wan21PipelineConfig) -> "Wan21Pipeline":
         return cls(Wan21Bundle.from_config(config))
 
+    def _conditions(self, req: Any, d: Any):
+        """Image-to-video: the request's condition images (``primitives["image"]``, one per sample) become the mask + first-frame latents
+        the transformer reads beside the noisy latents (``unirl/models/wan21/pipeline.py`` runs its image-encode stage at this point)."""
+        cond = super()._conditions(req, d)
+        images = (req.primitives or {}).get("image")
+        if self.bundle.concat_image_latents and cond.image is None and images is not None:
+            px = images.pixels if hasattr(images, "pixels") else images
+            px = px.to(next(self.bundle.vae.parameters()).device).float()
+            if tuple(px.shape[-2:]) != (int(d.height), int(d.width)):
+                px = torch.nn.functional.interpolate(px, size=(int(d.height), int(d.width)), mode="bicubic", align_corners=False).clamp(0, 1)
+            cond.image = self.bundle.first_frame_condition(px, self.latent_shape(d)[1])
+        return cond
+
     def latent_shape(self, sampling: Any):
         shape = super().latent_shape(sampling)
         t = self.bundle.model_config
