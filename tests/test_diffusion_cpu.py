@@ -252,6 +252,8 @@ def test_image_to_video_request_carries_its_condition_images_into_rollout_and_re
     img = tr.conditions["image"].latents
     assert img.shape == (3, 4 + c, 3, 8, 8) and bool((img[:, :4, 0] == 1).all()) and bool((img[:, :4, 1:] == 0).all())
     assert float((img[0, 4:, 0] - img[2, 4:, 0]).abs().max()) > 1e-4
+    tokens = tr.conditions["image_embed"].embeds  # the image encoder's tokens, read by every block's cross-attention
+    assert tokens.shape == (3, pipe.bundle.image_encoder.cfg.num_tokens, pipe.bundle.model_config.image_dim) and pipe.bundle.model_config.image_dim > 0
     seg = tr.segment
     out = pipe.diffusion.replay(DiTConditions.from_dict(tr.conditions), segment=seg, params=DiTDiffusionParams(guidance_scale=3.0, true_cfg=True))
     assert float((out.log_probs.detach() - seg.sde_logp).abs().max()) < 1e-5

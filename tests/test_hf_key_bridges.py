@@ -109,7 +109,7 @@ def test_bridge_reports_shape_mismatch_and_unplaced_tensors():
 
 
 # ---- WAN: an independent statement of the published forward (WanTransformer3DModel, text-to-video), written against the published key names
-def _wan_reference(sd, cfg, latents, t, text):
+def _wan_reference(sd, cfg, latents, t, text, image=None):
     import math
 
     import torch.nn.functional as F
@@ -139,6 +139,13 @@ def _wan_reference(sd, cfg, latents, t, text):
     tproj = lin(F.silu(temb), "condition_embedder.time_proj").unflatten(1, (6, -1))
     ctx = lin(F.gelu(lin(text, "condition_embedder.text_embedder.linear_1"), approximate="tanh"), "condition_embedder.text_embedder.linear_2")
 
+    img_ctx = None
+    if image is not None:  # image-to-video: the image encoder's tokens through the checkpoint's image embedder
+        e = "condition_embedder.image_embedder"
+        y = F.layer_norm(image, (image.shape[-1],), sd[f"{e}.norm1.weight"], sd[f"{e}.norm1.bias"])
+        y = lin(F.gelu(lin(y, f"{e}.ff.net.0.proj")), f"{e}.ff.net.2")
+        img_ctx = F.layer_norm(y, (h,), sd[f"{e}.norm2.weight"], sd[f"{e}.norm2.bias"])
+
     def attend(q, k, v):
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
         return o.transpose(1, 2).flatten(2)
@@ -155,7 +162,11 @@ def _wan_reference(sd, cfg, latents, t, text):
         q = rms(lin(y, f"{p}.attn2.to_q"), sd[f"{p}.attn2.norm_q.weight"]).unflatten(2, (nh, hd))
         k = rms(lin(ctx, f"{p}.attn2.to_k"), sd[f"{p}.attn2.norm_k.weight"]).unflatten(2, (nh, hd))
         v = lin(ctx, f"{p}.attn2.to_v").unflatten(2, (nh, hd))
-        x = x + lin(attend(q, k, v), f"{p}.attn2.to_out.0")
+        o = attend(q, k, v)
+        if img_ctx is not None:  # a second attention of the same queries over the image tokens, added before the output projection
+            ki = rms(lin(img_ctx, f"{p}.attn2.add_k_proj"), sd[f"{p}.attn2.norm_added_k.weight"]).unflatten(2, (nh, hd))
+            o = o + attend(q, ki, lin(img_ctx, f"{p}.attn2.add_v_proj").unflatten(2, (nh, hd)))
+        x = x + lin(o, f"{p}.attn2.to_out.0")
         y = ln(x) * (1 + sc2[:, None]) + sh2[:, None]
         x = x + lin(F.gelu(lin(y, f"{p}.ffn.net.0.proj"), approximate="tanh"), f"{p}.ffn.net.2") * g2[:, None]
     shift, scale = (sd["scale_shift_table"] + temb[:, None]).unbind(1)
@@ -164,10 +175,15 @@ def _wan_reference(sd, cfg, latents, t, text):
     return x.reshape(b, -1, grid[0] * pf, grid[1] * ph, grid[2] * pw)
 
 
-def test_wan_checkpoint_in_published_layout_matches_the_published_forward():
+@pytest.mark.parametrize("i2v", [False, True])
+def test_wan_checkpoint_in_published_layout_matches_the_published_forward(i2v):
+    """``i2v``: the WAN 2.1 image-to-video layout — an image embedder and, in every block, keys / values for the image encoder's tokens."""
     from unirl_b200.models.dit.hf_keys import wan_from_diffusers
 
     cfg = PRESETS["tiny-wan"]().transformer
+    idim = 24
+    if i2v:
+        cfg.image_dim = idim
     h, m, g = cfg.hidden_size, cfg.mlp_dim, torch.Generator().manual_seed(0)
     rnd = lambda *s: torch.randn(*s, generator=g) * 0.2  # noqa: E731
     sd = {"patch_embedding.weight": rnd(h, cfg.in_channels, *cfg.patch_size), "patch_embedding.bias": rnd(h), "scale_shift_table": rnd(1, 2, h),
@@ -183,19 +199,30 @@ def test_wan_checkpoint_in_published_layout_matches_the_published_forward():
             for pr in ("to_q", "to_k", "to_v", "to_out.0"):
                 sd[f"{p}.{a}.{pr}.weight"], sd[f"{p}.{a}.{pr}.bias"] = rnd(h, h), rnd(h)
             sd[f"{p}.{a}.norm_q.weight"], sd[f"{p}.{a}.norm_k.weight"] = 1 + rnd(h), 1 + rnd(h)
+        if i2v:
+            for pr in ("add_k_proj", "add_v_proj"):
+                sd[f"{p}.attn2.{pr}.weight"], sd[f"{p}.attn2.{pr}.bias"] = rnd(h, h), rnd(h)
+            sd[f"{p}.attn2.norm_added_k.weight"] = 1 + rnd(h)
         sd[f"{p}.norm2.weight"], sd[f"{p}.norm2.bias"] = 1 + rnd(h), rnd(h)
         sd[f"{p}.ffn.net.0.proj.weight"], sd[f"{p}.ffn.net.0.proj.bias"] = rnd(m, h), rnd(m)
         sd[f"{p}.ffn.net.2.weight"], sd[f"{p}.ffn.net.2.bias"] = rnd(h, m), rnd(h)
+    if i2v:
+        e = "condition_embedder.image_embedder"
+        for name, (i, o) in {f"{e}.ff.net.0.proj": (idim, idim), f"{e}.ff.net.2": (idim, h)}.items():
+            sd[f"{name}.weight"], sd[f"{name}.bias"] = rnd(o, i), rnd(o)
+        sd[f"{e}.norm1.weight"], sd[f"{e}.norm1.bias"], sd[f"{e}.norm2.weight"], sd[f"{e}.norm2.bias"] = 1 + rnd(idim), rnd(idim), 1 + rnd(h), rnd(h)
     model = DiTTransformer(cfg, dtype=torch.float32, device="cpu").init_weights(3)
     missing, unexpected = load_diffusers_transformer(model, sd, "tiny-wan", strict=True)
     assert not missing and not unexpected
     assert set(wan_from_diffusers(sd, cfg.num_cross_blocks, strict=True)) == set(model.state_dict())
     lat, t, text = torch.randn(2, cfg.in_channels, 3, 8, 12, generator=g), torch.tensor([0.3, 0.9]) * 1000, torch.randn(2, 7, cfg.text_dim, generator=g)
+    image = torch.randn(2, 5, idim, generator=g) if i2v else None
     with torch.no_grad():
-        got, want = model(lat, t, text), _wan_reference(sd, cfg, lat, t, text)
+        got, want = model(lat, t, text, image_embeds=image), _wan_reference(sd, cfg, lat, t, text, image)
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
-    with pytest.raises(KeyError, match="image-to-video"):
-        wan_from_diffusers({**sd, "condition_embedder.image_embedder.ff.net.0.proj.weight": rnd(4, 4)}, cfg.num_cross_blocks)
+    if i2v:
+        with torch.no_grad():
+            assert float((model(lat, t, text) - got).abs().max()) > 1e-3, "the image tokens reach the output"
 
 
 def test_sd3_position_table_follows_the_published_formula_and_is_taken_from_the_checkpoint():

@@ -115,8 +115,11 @@ class DiTDiffusionStage:
             g = p.distilled_guidance_scale if p.distilled_guidance_scale is not None else p.guidance_scale
             guidance = torch.full((x.shape[0],), float(g) * 1000.0, device=x.device)
         use_cfg = p.true_cfg and p.guidance_scale > 1.0 and cond.negative_text is not None
+        ie = getattr(cond, "image_embed", None)
+        ie = None if (ie is None or ie.embeds is None) else ie.embeds.to(x.device)  # image-encoder tokens: the same for both guidance branches
+        extra = {} if ie is None else {"image_embeds": ie}
         if not use_cfg:
-            return model(inp, t, txt.embeds, txt.pooled, txt.attn_mask, guidance).float(), None
+            return model(inp, t, txt.embeds, txt.pooled, txt.attn_mask, guidance, **extra).float(), None
         neg = cond.negative_text
         width = max(txt.embeds.shape[1], neg.embeds.shape[1])
         pad = lambda e: torch.nn.functional.pad(e, (0, 0, 0, width - e.shape[1]))  # noqa: E731
@@ -124,7 +127,8 @@ class DiTDiffusionStage:
         emb = torch.cat([pad(neg.embeds), pad(txt.embeds)])
         pooled = None if txt.pooled is None else torch.cat([neg.pooled, txt.pooled])
         mask = None if txt.attn_mask is None or neg.attn_mask is None else torch.cat([padm(neg.attn_mask, neg.embeds), padm(txt.attn_mask, txt.embeds)])
-        v = model(torch.cat([inp, inp]), torch.cat([t, t]), emb, pooled, mask, None if guidance is None else torch.cat([guidance, guidance])).float()
+        extra = {} if ie is None else {"image_embeds": torch.cat([ie, ie])}
+        v = model(torch.cat([inp, inp]), torch.cat([t, t]), emb, pooled, mask, None if guidance is None else torch.cat([guidance, guidance]), **extra).float()
         vu, vc = v.chunk(2)
         return vc, vu
 

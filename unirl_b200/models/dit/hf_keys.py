@@ -162,9 +162,14 @@ def qwen_image_from_diffusers(sd: Dict[str, Tensor], num_joint_blocks: int, stri
 
 def wan_from_diffusers(sd: Dict[str, Tensor], num_cross_blocks: int, strict: bool = False, patch_elems: int = 4) -> Dict[str, Tensor]:
     """``WanTransformer3DModel`` naming (``condition_embedder.*``, ``blocks.<i>.attn1 / attn2 / ffn / norm2 / scale_shift_table``)."""
-    if any(k.startswith("condition_embedder.image_embedder") for k in sd):
-        raise KeyError("image-to-video WAN checkpoints (condition_embedder.image_embedder.*) are not supported by the native module")
     w = _Writer(sd)
+    i2v = any(k.startswith("condition_embedder.image_embedder.") for k in sd)  # WAN 2.1 image-to-video: image-encoder tokens as a second context
+    if i2v:
+        e = "condition_embedder.image_embedder"
+        w.put("image_in.norm1", f"{e}.norm1")
+        w.put("image_in.fc1", f"{e}.ff.net.0.proj")
+        w.put("image_in.fc2", f"{e}.ff.net.2")
+        w.put("image_in.norm2", f"{e}.norm2")
     w.put("patch_embed", "patch_embedding")  # a Conv3d kernel [h, c, 1, 2, 2]: flattened to the patchify order (c, t, rows, cols) below
     w.put("time_in.0", "condition_embedder.time_embedder.linear_1")
     w.put("time_in.1", "condition_embedder.time_embedder.linear_2")
@@ -189,6 +194,9 @@ def wan_from_diffusers(sd: Dict[str, Tensor], num_cross_blocks: int, strict: boo
         w.put(f"{d}.cross_out", f"{s_}.attn2.to_out.0")
         w.raw(f"{d}.cross_q_norm", f"{s_}.attn2.norm_q.weight")
         w.raw(f"{d}.cross_k_norm", f"{s_}.attn2.norm_k.weight")
+        if i2v:
+            w.fuse(f"{d}.cross_kv_img", [f"{s_}.attn2.add_k_proj", f"{s_}.attn2.add_v_proj"])
+            w.raw(f"{d}.cross_k_img_norm", f"{s_}.attn2.norm_added_k.weight")
         w.put(f"{d}.cross_norm", f"{s_}.norm2")
         w.put(f"{d}.mlp.fc1", f"{s_}.ffn.net.0.proj")
         w.put(f"{d}.mlp.fc2", f"{s_}.ffn.net.2")

@@ -46,6 +46,7 @@ class DiTConfig:
     num_heads: int = 24
     head_dim: int = 64
     in_channels: int = 16
+    image_dim: int = 0  # width of an image encoder's tokens read as a second cross-attention context (WAN 2.1 image-to-video: 1280); 0 = none
     out_channels: Optional[int] = None
     patch_size: Tuple[int, int, int] = (1, 2, 2)  # (frames, rows, cols) per token
     num_joint_blocks: int = 24
@@ -307,6 +308,7 @@ class AttnContext:
         self.cos, self.sin, self.text_len, self.sp, self.text_mask = cos, sin, text_len, sp, text_mask
         self.cos_full: Optional[torch.Tensor] = None  # unsharded tables [text + all latent tokens] for attention on head shards
         self.sin_full: Optional[torch.Tensor] = None
+        self.image_ctx: Optional[torch.Tensor] = None  # image-encoder tokens at model width, the second context of the cross blocks
 
     def rope(self, q: torch.Tensor, k: torch.Tensor, offset: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
         if self.cos is None:
@@ -483,6 +485,11 @@ class CrossBlock(nn.Module):
         self.cross_q_norm, self.cross_k_norm = _qk_norm_param(cfg, dtype, device), _qk_norm_param(cfg, dtype, device)
         self.cross_out = _Lin(h, h, True, dtype, device, {"attn2.to_out.0": (0, h)})
         self.cross_norm = nn.LayerNorm(h, eps=cfg.eps, dtype=dtype, device=device)
+        if cfg.image_dim:  # keys / values of the image encoder's tokens: their attention output is added to the text's
+            self.cross_kv_img = _Lin(h, 2 * h, True, dtype, device, {"attn2.add_k_proj": (0, h), "attn2.add_v_proj": (h, h)})
+            self.cross_k_img_norm = _qk_norm_param(cfg, dtype, device)
+        else:
+            self.cross_kv_img = self.cross_k_img_norm = None
         self.mlp = _MLP(cfg, dtype, device)
         self.n, self.tp = cfg.num_heads, None
 
@@ -494,6 +501,9 @@ class CrossBlock(nn.Module):
         self.cross_kv.shard(tp, "col", torch.cat([_head_rows(0, c.num_heads, d, tp), _head_rows(h, c.num_heads, d, tp)]))
         self.cross_out.shard(tp, "row", _head_rows(0, c.num_heads, d, tp))
         self.cross_q_norm, self.cross_k_norm = _shard_norm(self.cross_q_norm, c.num_heads, d, tp), _shard_norm(self.cross_k_norm, c.num_heads, d, tp)
+        if self.cross_kv_img is not None:
+            self.cross_kv_img.shard(tp, "col", torch.cat([_head_rows(0, c.num_heads, d, tp), _head_rows(h, c.num_heads, d, tp)]))
+            self.cross_k_img_norm = _shard_norm(self.cross_k_img_norm, c.num_heads, d, tp)
         self.mlp.shard(tp)
         self.n, self.tp = c.num_heads // tp.size, tp
 
@@ -512,8 +522,25 @@ class CrossBlock(nn.Module):
         xk = _qk_norm(_heads(xk, self.n), self.cross_k_norm, c.eps, self.tp)
         mask = None if ctx.text_mask is None else ctx.text_mask[:, None, None, :].bool()
         a = F.scaled_dot_product_attention(xq.transpose(1, 2), xk.transpose(1, 2), _heads(xv, self.n).transpose(1, 2), attn_mask=mask)
+        if self.cross_kv_img is not None and ctx.image_ctx is not None:
+            ik, iv = self.cross_kv_img(ctx.image_ctx).chunk(2, -1)
+            ik = _qk_norm(_heads(ik, self.n), self.cross_k_img_norm, c.eps, self.tp)
+            a = a + F.scaled_dot_product_attention(xq.transpose(1, 2), ik.transpose(1, 2), _heads(iv, self.n).transpose(1, 2))
         img = img + self.cross_out(a.transpose(1, 2).flatten(-2))
         return img + m[5].unsqueeze(1) * self.mlp(layernorm_modulate(img, m[3], m[4], c.eps))
+
+
+class _ImageEmbedder(nn.Module):
+    """Image-encoder tokens → model width: layer norm, two linear layers with a GELU between, layer norm (the ``image_embedder`` of the
+    WAN image-to-video checkpoints)."""
+
+    def __init__(self, i: int, o: int, dtype: Any, device: Any):
+        super().__init__()
+        self.norm1, self.norm2 = nn.LayerNorm(i, dtype=dtype, device=device), nn.LayerNorm(o, dtype=dtype, device=device)
+        self.fc1, self.fc2 = _Lin(i, i, True, dtype, device), _Lin(i, o, True, dtype, device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.norm2(self.fc2(F.gelu(self.fc1(self.norm1(x)))))
 
 
 class DiTTransformer(nn.Module):
@@ -536,6 +563,7 @@ class DiTTransformer(nn.Module):
         self.text_in = _Lin(cfg.text_dim, h, True, dtype, device)
         self.text_in2 = _Lin(h, h, True, dtype, device) if cfg.text_in_layers == 2 else None
         self.time_proj = _Lin(h, 6 * h, True, dtype, device) if cfg.num_cross_blocks else None
+        self.image_in = _ImageEmbedder(cfg.image_dim, h, dtype, device) if cfg.image_dim else None
         self.joint_blocks = nn.ModuleList(JointBlock(cfg, i, dtype, device) for i in range(cfg.num_joint_blocks))
         self.single_blocks = nn.ModuleList(SingleBlock(cfg, i, dtype, device) for i in range(cfg.num_single_blocks))
         self.cross_blocks = nn.ModuleList(CrossBlock(cfg, i, dtype, device) for i in range(cfg.num_cross_blocks))
@@ -598,7 +626,7 @@ class DiTTransformer(nn.Module):
 
     # ---- forward ---------------------------------------------------------------------------------------
     def forward(self, latents: torch.Tensor, timestep: torch.Tensor, text: torch.Tensor, pooled: Optional[torch.Tensor] = None,
-                text_mask: Optional[torch.Tensor] = None, guidance: Optional[torch.Tensor] = None) -> torch.Tensor:
+                text_mask: Optional[torch.Tensor] = None, guidance: Optional[torch.Tensor] = None, image_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg = self.cfg
         video = latents.dim() == 5
         dtype = self.patch_embed.weight.dtype
@@ -627,6 +655,7 @@ class DiTTransformer(nn.Module):
                 cos, sin = sp.shard_rope(cos, joint_text), sp.shard_rope(sin, joint_text)
         ctx = AttnContext(cos, sin, nt, sp, text_mask)
         ctx.cos_full, ctx.sin_full = cos_full, sin_full
+        ctx.image_ctx = self.image_in(image_embeds.to(dtype)) if (self.image_in is not None and image_embeds is not None) else None
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
         n_ckpt = None if self.checkpoint_layers is None else int(self.checkpoint_layers)
         done = [0]
@@ -646,7 +675,7 @@ class DiTTransformer(nn.Module):
         if len(self.cross_blocks):
             tproj = self.time_proj(F.silu(vec))
             cross_ctx = AttnContext(cos, sin, 0, sp, text_mask)
-            cross_ctx.cos_full, cross_ctx.sin_full = cos_full, sin_full
+            cross_ctx.cos_full, cross_ctx.sin_full, cross_ctx.image_ctx = cos_full, sin_full, ctx.image_ctx
             for blk in self.cross_blocks:
                 img = run(blk, img, txt, tproj, cross_ctx)
         if self.final_mod is None:

@@ -6,6 +6,7 @@ mask and the 16-channel encoded first frame to the noisy latents (36 input chann
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Any, Optional
 
@@ -14,7 +15,8 @@ import torch
 from unirl_b200.models.dit.bundle import DiTBundle
 from unirl_b200.models.dit.config import DiTPipelineConfig
 from unirl_b200.models.dit.pipeline import DiTPipeline
-from unirl_b200.types.conditions import ImageLatentCondition
+from unirl_b200.models.dit.clip_vision import CLIPVisionConfig, CLIPVisionTower
+from unirl_b200.types.conditions import ImageEmbedCondition, ImageLatentCondition
 
 
 @dataclass
@@ -23,6 +25,7 @@ class Wan21PipelineConfig(DiTPipelineConfig):
     image_to_video: bool = False
     max_sequence_length: int = 512
     image_encoder_ckpt_path: Optional[str] = None  # image-to-video checkpoints: where the first frame's image encoder lives (None: beside the transformer)
+    clip_vision: bool = True  # image-to-video: the transformer also reads an image encoder's tokens (WAN 2.1; the 2.2 checkpoints do not)
 
     def __post_init__(self) -> None:
         parent = getattr(super(), "__post_init__", None)
@@ -40,11 +43,34 @@ class Wan21Bundle(DiTBundle):
 
             from unirl_b200.models.dit.config import resolve_family
 
-            c = resolve_family(config.pretrained_model_ckpt_path).transformer.in_channels  # noisy + 4 mask + first-frame channels enter the patch embedding
-            config = replace(config, model_overrides={**config.model_overrides, "in_channels": 2 * c + 4, "out_channels": c})
+            base = resolve_family(config.pretrained_model_ckpt_path).transformer
+            c = base.in_channels  # noisy + 4 mask + first-frame channels enter the patch embedding
+            extra = {"in_channels": 2 * c + 4, "out_channels": c}
+            if config.clip_vision and "image_dim" not in config.model_overrides:
+                tiny = "tiny" in str(base.name)
+                extra["image_dim"] = CLIPVisionConfig.tiny().hidden_size if tiny else CLIPVisionConfig().hidden_size
+            config = replace(config, model_overrides={**config.model_overrides, **extra})
         b = super().from_config(config, sp)
         b.concat_image_latents = bool(config.image_to_video)
+        b.image_encoder = cls._load_image_encoder(config, b) if (config.image_to_video and b.model_config.image_dim) else None
         return b
+
+    @staticmethod
+    def _load_image_encoder(config: Wan21PipelineConfig, b: "Wan21Bundle") -> CLIPVisionTower:
+        """The checkpoint's ``image_encoder`` folder (or ``image_encoder_ckpt_path``); random weights for the ``random:`` presets."""
+        path = str(config.pretrained_model_ckpt_path)
+        device = next(b.transformer.parameters()).device
+        folder = config.image_encoder_ckpt_path or (None if path.startswith("random:") else os.path.join(path, "image_encoder"))
+        if folder and os.path.exists(os.path.join(folder, "config.json")):
+            return CLIPVisionTower.from_hf(folder, dtype=torch.float32, device=device)
+        c = CLIPVisionConfig.tiny() if b.model_config.image_dim == CLIPVisionConfig.tiny().hidden_size else CLIPVisionConfig(hidden_size=b.model_config.image_dim)
+        return CLIPVisionTower(c, torch.float32, device).init_weights(config.init_seed + 11)
+
+    def image_embed_condition(self, image: torch.Tensor) -> ImageEmbedCondition:
+        """``image [B, 3, H, W]`` in [0, 1] → the image encoder's penultimate hidden states, all tokens valid
+        (``unirl/models/wan21/clip_vision_encode.py:65-83``)."""
+        e = self.image_encoder.encode(image)
+        return ImageEmbedCondition(embeds=e, attn_mask=torch.ones(e.shape[:2], dtype=torch.long, device=e.device))
 
     def first_frame_condition(self, image: torch.Tensor, num_latent_frames: int) -> ImageLatentCondition:
         """``image [B, 3, H, W]`` in [0, 1] → ``[B, 20, F, h, w]``: mask (first latent frame = 1) ++ the codec's latents of the clip
@@ -82,6 +108,8 @@ class Wan21Pipeline(DiTPipeline):
             if tuple(px.shape[-2:]) != (int(d.height), int(d.width)):
                 px = torch.nn.functional.interpolate(px, size=(int(d.height), int(d.width)), mode="bicubic", align_corners=False).clamp(0, 1)
             cond.image = self.bundle.first_frame_condition(px, self.latent_shape(d)[1])
+            if self.bundle.image_encoder is not None and cond.image_embed is None:
+                cond.image_embed = self.bundle.image_embed_condition((images.pixels if hasattr(images, "pixels") else images).float())
         return cond
 
     def latent_shape(self, sampling: Any):

@@ -16,6 +16,7 @@ from unirl_b200.models.wan21.pipeline import Wan21Bundle, Wan21Pipeline, Wan21Pi
 @dataclass
 class Wan22PipelineConfig(Wan21PipelineConfig):
     boundary_ratio: float = 0.875
+    clip_vision: bool = False  # the 2.2 image-to-video checkpoints condition on the first frame's latents only
     num_train_timesteps: int = 1000  # the time scale the boundary is expressed on (σ · num_train_timesteps is what the experts see)
 
 
